@@ -1,0 +1,272 @@
+"""The cache manager: pages with a block table per request, and slots of fixed-size state.
+
+Every run-order entry of a model that keeps a cache declares a `CacheSpec`. Entries whose specs are
+equal form a group; a group of kind "pages" has one page pool and, per request, one block table that
+is valid for all its member entries at once (as a physical block of the reference is valid in all
+layers, dynalm/src/kv_cache/kv_cache.cpp:31-38). Groups with different needs (all keys, a window of
+them, another entry shape) have pools and tables of their own. A group with a window gives pages
+back as soon as every token in them lies behind the window of the request's next token. Entries of
+kind "state" get one row per request slot in an array [slots, *state_shape], zeroed when a slot is
+handed out; every request takes a slot whether or not the model has such entries.
+
+What is given back when: all pages and the slot when a request is freed (finished, cancelled,
+failed, or preempted for recompute: dynalm/src/runtime/sequence.cpp:44-63); windowed pages after
+`advance`.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..engine.context import CacheView
+from ..errors import InvalidArgument, ResourceExhausted
+from ..parts.base import CacheSpec
+from .pool import PagePool
+
+DEFAULT_PAGE_SIZE = 16      # tokens per page, the reference's block size (dynalm/src/runtime/engine.cpp:405)
+
+
+def _torch_dtype(name: Optional[str], default: torch.dtype) -> torch.dtype:
+    if name is None:
+        return default
+    return {"float32": torch.float32, "bfloat16": torch.bfloat16}[name]
+
+
+@dataclass
+class _Table:
+    pages: np.ndarray            # int32 [max_blocks], -1 = no page
+    first: int = 0               # blocks below `first` were given back (window)
+    length: int = 0              # blocks [first, length) hold pages
+
+
+class PageGroup:
+    def __init__(self, gid: int, spec: CacheSpec, page_size: int, num_pages: int, max_blocks: int):
+        self.gid = gid
+        self.spec = spec
+        self.page_size = page_size
+        self.pool = PagePool(num_pages)
+        self.max_blocks = max_blocks
+        self.members: List[int] = []                      # run-order entries
+        self.arrays: Dict[int, List[torch.Tensor]] = {}   # entry -> tensors [pages, page_size, *entry_shape]
+        self.tables: Dict[Hashable, _Table] = {}
+
+    def first_needed_block(self, next_pos: int) -> int:
+        """The lowest block a query at `next_pos` (or later) can still read."""
+        if self.spec.window <= 0:
+            return 0
+        return max(0, next_pos - self.spec.window + 1) // self.page_size
+
+    def blocks_needed(self, req, start_pos: int, total: int) -> int:
+        """New pages that holding `total` tokens needs, the next query being at `start_pos`."""
+        t = self.tables.get(req)
+        have_first, have_len = (t.first, t.length) if t is not None else (0, 0)
+        want_len = -(-total // self.page_size)
+        lo = max(have_len, self.first_needed_block(start_pos), have_first)
+        return max(0, want_len - lo)
+
+
+class CacheManager:
+    """Owns all cache memory of one model.
+
+    specs         per run-order entry, its CacheSpec or None (entries that read another entry's cache
+                  and entries without a cache give None)
+    max_tokens    tokens all live requests may hold at once; every "pages" group gets
+                  ceil(max_tokens / page_size) pages
+    max_requests  state slots, and the most requests alive at once
+    context       the longest a single request may grow (sets the width of block tables)
+    """
+
+    def __init__(self, specs: Sequence[Optional[CacheSpec]], page_size: int, max_tokens: int, max_requests: int,
+                 context: int, device, dtype: torch.dtype):
+        if page_size <= 0 or max_tokens <= 0 or max_requests <= 0 or context <= 0:
+            raise InvalidArgument("cache sizes must be positive")
+        self.page_size = int(page_size)
+        self.max_requests = int(max_requests)
+        self.context = int(context)
+        self.device = torch.device(device) if device is not None else None
+        self.dtype = dtype
+        self.num_pages = -(-int(max_tokens) // self.page_size)
+        self.max_blocks = -(-self.context // self.page_size)
+        self.groups: List[PageGroup] = []
+        self.entry_group: Dict[int, PageGroup] = {}
+        self.state_arrays: Dict[int, torch.Tensor] = {}
+        self.state_specs: Dict[int, CacheSpec] = {}
+        by_key: Dict[tuple, PageGroup] = {}
+        for entry, spec in enumerate(specs):
+            if spec is None:
+                continue
+            if spec.kind == "pages":
+                g = by_key.get(spec.group_key())
+                if g is None:
+                    g = PageGroup(len(self.groups), spec, self.page_size, self.num_pages, self.max_blocks)
+                    by_key[spec.group_key()] = g
+                    self.groups.append(g)
+                g.members.append(entry)
+                self.entry_group[entry] = g
+                if self.device is not None:
+                    dt = _torch_dtype(spec.dtype, dtype)
+                    g.arrays[entry] = [torch.zeros((self.num_pages, self.page_size) + tuple(spec.entry_shape),
+                                                   dtype=dt, device=self.device) for _ in range(spec.tensors)]
+            elif spec.kind == "state":
+                self.state_specs[entry] = spec
+                if self.device is not None:
+                    dt = _torch_dtype(spec.dtype, torch.float32)
+                    self.state_arrays[entry] = torch.zeros((self.max_requests,) + tuple(spec.state_shape),
+                                                           dtype=dt, device=self.device)
+            else:
+                raise InvalidArgument(f"cache spec of kind '{spec.kind}' is not known (pages, state)")
+        self._free_slots: List[int] = list(range(self.max_requests - 1, -1, -1))
+        self.slots: Dict[Hashable, int] = {}
+        self.tokens: Dict[Hashable, int] = {}     # tokens reserved so far per request
+
+    # ---- requests -----------------------------------------------------------------------------
+    def has_request(self, req) -> bool:
+        return req in self.slots
+
+    def add_request(self, req) -> int:
+        """Take a state slot (zeroed) for a new request; pages come with `reserve`."""
+        if req in self.slots:
+            raise InvalidArgument(f"request {req!r} is already live")
+        if not self._free_slots:
+            raise ResourceExhausted("no free request slot")
+        slot = self._free_slots.pop()
+        self.slots[req] = slot
+        self.tokens[req] = 0
+        for g in self.groups:
+            g.tables[req] = _Table(np.full(g.max_blocks, -1, dtype=np.int32))
+        for arr in self.state_arrays.values():
+            arr[slot].zero_()
+        return slot
+
+    def pages_needed(self, req, total: int, start_pos: Optional[int] = None) -> int:
+        """The most pages any group must still allocate so that `req` holds `total` tokens."""
+        start = self.tokens.get(req, 0) if start_pos is None else start_pos
+        return max((g.blocks_needed(req, start, total) for g in self.groups), default=0)
+
+    def can_reserve(self, req, total: int, headroom: int = 0) -> bool:
+        start = self.tokens.get(req, 0)
+        return all(g.blocks_needed(req, start, total) + headroom <= g.pool.num_free for g in self.groups)
+
+    def reserve(self, req, total: int) -> None:
+        """Make sure `req` has pages for positions < total in every group. All or nothing: on
+        ResourceExhausted the pages this call took are given back."""
+        if req not in self.slots:
+            raise InvalidArgument(f"request {req!r} is not live")
+        if total > self.context:
+            raise InvalidArgument(f"request {req!r} would hold {total} tokens, the context is {self.context}")
+        start = self.tokens[req]
+        taken = []
+        try:
+            for g in self.groups:
+                t = g.tables[req]
+                want_len = -(-total // self.page_size)
+                lo = max(t.length, g.first_needed_block(start))
+                if lo > t.length:            # blocks a window has already passed are never allocated
+                    if t.length == t.first:
+                        t.first = lo
+                    t.length = lo
+                for b in range(lo, want_len):
+                    page = g.pool.allocate()
+                    taken.append((g, t, b, page))
+                    t.pages[b] = page
+                t.length = max(t.length, want_len)
+        except ResourceExhausted:
+            for g, t, b, page in reversed(taken):
+                g.pool.release(page)
+                t.pages[b] = -1
+                t.length = min(t.length, b)
+            raise
+        self.tokens[req] = max(self.tokens[req], total)
+
+    def advance(self, req, computed: int) -> int:
+        """`req` has now computed `computed` tokens; give back pages that every window has passed.
+        Returns the number of pages given back."""
+        n = 0
+        for g in self.groups:
+            if g.spec.window <= 0:
+                continue
+            t = g.tables[req]
+            keep_from = min(g.first_needed_block(computed), t.length)
+            for b in range(t.first, keep_from):
+                if t.pages[b] >= 0:
+                    g.pool.release(int(t.pages[b]))
+                    t.pages[b] = -1
+                    n += 1
+            t.first = max(t.first, keep_from)
+        return n
+
+    def free_request(self, req) -> None:
+        """Give back every page and the slot of `req`."""
+        slot = self.slots.pop(req, None)
+        if slot is None:
+            raise InvalidArgument(f"request {req!r} is not live (freed twice?)")
+        for g in self.groups:
+            t = g.tables.pop(req)
+            for b in range(t.first, t.length):
+                if t.pages[b] >= 0:
+                    g.pool.release(int(t.pages[b]))
+        self.tokens.pop(req)
+        self._free_slots.append(slot)
+
+    # ---- what the step function reads ---------------------------------------------------------------
+    def slot_of(self, req) -> int:
+        return self.slots[req]
+
+    def table_row(self, group: PageGroup, req) -> np.ndarray:
+        return group.tables[req].pages
+
+    def view(self, entry: int, block_tables: Dict[int, torch.Tensor]) -> Optional[CacheView]:
+        g = self.entry_group.get(entry)
+        if g is not None:
+            return CacheView("pages", g.arrays[entry], self.page_size, block_tables[g.gid])
+        if entry in self.state_arrays:
+            return CacheView("state", [self.state_arrays[entry]])
+        return None
+
+    # ---- accounting -----------------------------------------------------------------------------------
+    @property
+    def free_pages(self) -> int:
+        return min((g.pool.num_free for g in self.groups), default=self.num_pages)
+
+    @property
+    def free_slots(self) -> int:
+        return len(self._free_slots)
+
+    def bytes(self) -> int:
+        n = 0
+        for g in self.groups:
+            for arrs in g.arrays.values():
+                n += sum(a.numel() * a.element_size() for a in arrs)
+        n += sum(a.numel() * a.element_size() for a in self.state_arrays.values())
+        return n
+
+    def check(self) -> None:
+        """No page lost, held twice or freed twice; no slot held twice."""
+        for g in self.groups:
+            g.pool.check()
+            owners: Dict[int, Hashable] = {}
+            for req, t in g.tables.items():
+                for b in range(g.max_blocks):
+                    p = int(t.pages[b])
+                    inside = t.first <= b < t.length
+                    if p >= 0:
+                        if not inside:
+                            raise AssertionError(f"request {req!r} keeps page {p} outside its table range")
+                        if p in owners:
+                            raise AssertionError(f"page {p} is held by {owners[p]!r} and {req!r}")
+                        if not g.pool.is_held(p):
+                            raise AssertionError(f"page {p} of {req!r} is on the free list")
+                        owners[p] = req
+                    elif inside and g.spec.window <= 0:
+                        raise AssertionError(f"request {req!r} lacks a page for block {b}")
+            if len(owners) != g.pool.num_held:
+                raise AssertionError(f"{g.pool.num_held} pages are held but tables name {len(owners)}")
+        used = sorted(self.slots.values())
+        if len(set(used)) != len(used) or set(used) & set(self._free_slots):
+            raise AssertionError("a state slot is held twice")
+        if len(used) + len(self._free_slots) != self.max_requests:
+            raise AssertionError("a state slot is lost")

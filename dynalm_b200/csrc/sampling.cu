@@ -1,0 +1,125 @@
+// Token selection on the device: greedy argmax and temperature sampling over fp32 logits rows.
+//
+// Greedy: the index of the largest logit, ties to the lowest id (sample_greedy,
+// dynalm/src/sampling/sampler.cpp:31-38). Temperature: p_i = exp((l_i - max) / T), the total summed in
+// double, u * total walked down the ids in order until it goes negative, the last id on rounding
+// (Sampler::distribution and ::draw, :120-137,209-220). The uniform u comes from the host, where the
+// per-request xoshiro256** generator lives. The reference samples on the host from downloaded logits;
+// here only the chosen ids leave the device.
+#include "common.cuh"
+
+namespace dl {
+
+constexpr int SAMPLE_THREADS = 1024;
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restrict__ out) {
+  __shared__ float bv[32];
+  __shared__ int bi[32];
+  const float* row = logits + static_cast<size_t>(blockIdx.x) * ld;
+  float best = -INFINITY;
+  int idx = 0x7fffffff;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float v = row[i];
+    if (v > best) { best = v; idx = i; }   // ascending i per thread: the first maximum is kept
+  }
+  auto better = [](float v, int i, float bv_, int bi_) { return v > bv_ || (v == bv_ && i < bi_); };
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (better(ov, oi, best, idx)) { best = ov; idx = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { bv[warp] = best; bi[warp] = idx; }
+  __syncthreads();
+  if (warp == 0) {
+    best = lane < (blockDim.x >> 5) ? bv[lane] : -INFINITY;
+    idx = lane < (blockDim.x >> 5) ? bi[lane] : 0x7fffffff;
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+      if (better(ov, oi, best, idx)) { best = ov; idx = oi; }
+    }
+    if (lane == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;   // NaN-only rows give 0, as the reference
+  }
+}
+
+// One block per row. Each thread owns a contiguous run of ids so that the walk is in id order.
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_temperature_kernel(const float* __restrict__ logits, int ld, int vocab,
+                          const float* __restrict__ temperature, const double* __restrict__ uniform,
+                          int* __restrict__ out) {
+  __shared__ float red[33];
+  __shared__ double seg[SAMPLE_THREADS];
+  __shared__ int chosen;
+  const int r = blockIdx.x;
+  const float* row = logits + static_cast<size_t>(r) * ld;
+  const float inv_t = 1.0f / temperature[r];
+  float m = -INFINITY;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) m = fmaxf(m, row[i]);
+  m = block_max(m, red);
+
+  const int per = (vocab + blockDim.x - 1) / blockDim.x;
+  const int b = min(vocab, static_cast<int>(threadIdx.x) * per), e = min(vocab, b + per);
+  double s = 0.0;
+  for (int i = b; i < e; ++i) s += static_cast<double>(expf((row[i] - m) * inv_t));
+  seg[threadIdx.x] = s;
+  if (threadIdx.x == 0) chosen = -1;
+  __syncthreads();
+  // thread 0 finds the segment: a serial scan of 1024 doubles keeps the order of the reference's walk
+  __shared__ int seg_idx;
+  __shared__ double seg_rest;
+  if (threadIdx.x == 0) {
+    double total = 0.0;
+    for (int i = 0; i < blockDim.x; ++i) total += seg[i];
+    double u = uniform[r] * total;
+    int k = 0;
+    for (; k < blockDim.x - 1; ++k) {
+      if (u - seg[k] < 0.0) break;
+      u -= seg[k];
+    }
+    seg_idx = k;
+    seg_rest = u;
+  }
+  __syncthreads();
+  if (threadIdx.x == seg_idx) {
+    double u = seg_rest;
+    int pick = -1;
+    for (int i = b; i < e; ++i) {
+      u -= static_cast<double>(expf((row[i] - m) * inv_t));
+      if (u < 0.0) { pick = i; break; }
+    }
+    chosen = pick;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int pick = chosen;
+    if (pick < 0) {
+      // rounding left u >= 0 at the end of the segment: the next id with any mass, else the last id
+      pick = vocab - 1;
+      const int e_idx = min(vocab, (seg_idx + 1) * per);
+      for (int i = e_idx; i < vocab; ++i) {
+        if (expf((row[i] - m) * inv_t) > 0.0f) { pick = i; break; }
+      }
+    }
+    out[r] = pick;
+  }
+}
+
+}  // namespace dl
+
+DL_EXPORT int dl_argmax(const float* logits, int ld, int rows, int vocab, int* out, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (vocab <= 0) return DL_ERR_UNSUPPORTED;
+  dl::argmax_kernel<<<rows, dl::SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, out);
+  return dl::launch_status();
+}
+
+// temperature: fp32 [rows] (> 0); uniform: double [rows] in [0, 1).
+DL_EXPORT int dl_sample_temperature(const float* logits, int ld, int rows, int vocab, const float* temperature,
+                                    const double* uniform, int* out, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (vocab <= 0) return DL_ERR_UNSUPPORTED;
+  dl::sample_temperature_kernel<<<rows, dl::SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, temperature, uniform, out);
+  return dl::launch_status();
+}

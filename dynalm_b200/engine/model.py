@@ -1,0 +1,69 @@
+"""The model built from a plan: embedding, blocks run in the plan's order, final norm, head.
+
+This is the one generic decoder the registry's architectures build (the counterpart of the
+reference's `Transformer`, dynalm/src/model/transformer.h:51-179). It resolves weights once and
+allocates its scratch through the runtime's workspace; `forward` looks nothing up.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..config.plan import ModelPlan
+from ..parts import BLOCKS, NORMS
+from ..parts.base import CacheSpec, pick_tensors
+from ..parts.block import ResidualStream
+from ..parts.embedding import LogitsHead, TokenEmbedding
+
+
+class Decoder:
+    def __init__(self, plan: ModelPlan, store: Dict[str, torch.Tensor], runtime):
+        plan.validate()
+        self.plan = plan
+        self.rt = runtime
+        self.embedding = TokenEmbedding(plan.embedding, store, runtime)
+        self.blocks = [BLOCKS.get(b.kind)(b, store, runtime) for b in plan.layers]
+        self.order = list(plan.order)
+        self.final_norm = NORMS.get(plan.final_norm.kind)(plan.final_norm, pick_tensors(plan.final_norm, store, NORMS),
+                                                          runtime)
+        self.head = LogitsHead(plan.head, store, runtime, self.embedding)
+        self.vocab = plan.head.vocab
+        self.width = plan.embedding.width
+
+    def cache_specs(self) -> List[Optional[CacheSpec]]:
+        """Per run-order entry: the cache it owns, or None when it owns none."""
+        return [None if run.cache_of is not None else self.blocks[run.layer].cache_spec() for run in self.order]
+
+    def weight_bytes(self) -> int:
+        seen, n = set(), 0
+        for obj in [self.embedding, self.head, self.final_norm] + [p for b in self.blocks for p in vars(b).values()]:
+            for v in vars(obj).values() if hasattr(obj, "__dict__") else ():
+                if isinstance(v, torch.Tensor) and v.data_ptr() not in seen:
+                    seen.add(v.data_ptr())
+                    n += v.numel() * v.element_size()
+        return n
+
+    def hidden(self, ctx, caches) -> ResidualStream:
+        """Run embedding and all blocks; `caches[i]` is the CacheView of run-order entry i (or None)."""
+        x = self.embedding.forward(ctx.token_ids, ctx.num_tokens)
+        stream = ResidualStream(x)
+        for i, run in enumerate(self.order):
+            owner = i if run.cache_of is None else run.cache_of
+            stream = self.blocks[run.layer].forward(stream, ctx, caches[owner], run.cache_of is None)
+        return stream
+
+    def logits(self, stream: ResidualStream, ctx, out: torch.Tensor) -> torch.Tensor:
+        """Final norm and head on the wanted rows only (dynalm/src/model/transformer.cpp:701-718)."""
+        n = ctx.num_logit_rows
+        normed = self.rt.buffer("final_normed", (n, self.width))
+        self.final_norm.forward(stream.x, normed, delta=stream.pending, delta_scale=stream.pending_scale,
+                                rows=ctx.logit_rows)
+        return self.head.forward(normed, out[:n])
+
+    def forward(self, ctx, caches, out: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        stream = self.hidden(ctx, caches)
+        if ctx.num_logit_rows == 0 or out is None:
+            return None
+        return self.logits(stream, ctx, out)

@@ -1,0 +1,219 @@
+"""The step function: run one batch of (request, its next tokens) from the cache.
+
+Contract (the reference's `Transformer::forward_batch`, dynalm/src/model/transformer.h:55-75,
+preconditions at transformer.cpp:502-535): a step holds any number of requests, each a run of
+consecutive positions continuing where that request stopped: a portion of a prompt, or one decoded
+token. Portions sit beside single tokens in one batch. The step runs only the tokens it is given,
+writes their keys and values into the cache as a side effect, and returns float32 logits for the
+wanted rows only, in batch order.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import CacheManager
+from ..errors import InvalidArgument
+from .context import StepContext
+from .model import Decoder
+from .runtime import Runtime
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens and the places among them (0-based) whose
+    logits are wanted."""
+
+    request: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class _StepBuffers:
+    """Per-step integers, packed: one pinned host array per ring slot, one device array with fixed
+    addresses (kernels captured in a CUDA graph keep reading the same pointers). A step fills a host
+    slot and issues one host-to-device copy; a slot is reused only after its copy has completed."""
+
+    RING = 4
+
+    def __init__(self, device, max_tokens: int, max_requests: int, group_blocks: Dict[int, int]):
+        self.max_tokens, self.max_requests = max_tokens, max_requests
+        off = 0
+        self.off: Dict[str, slice] = {}
+
+        def take(name, n):
+            nonlocal off
+            self.off[name] = slice(off, off + n)
+            off += (n + 3) // 4 * 4       # 16-byte aligned sections
+
+        for name in ("token_ids", "positions", "row_request", "logit_rows"):
+            take(name, max_tokens)
+        take("q_start", max_requests + 1)
+        for name in ("pos_start", "kv_len", "state_slots"):
+            take(name, max_requests)
+        self.group_blocks = dict(group_blocks)
+        for gid, mb in group_blocks.items():
+            take(f"table{gid}", max_requests * mb)
+        self.size = off
+        self.host = [torch.zeros(self.size, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+        self.host_np = [h.numpy() for h in self.host]
+        self.events = [None] * self.RING
+        self.dev = torch.zeros(self.size, dtype=torch.int32, device=device)
+        self.turn = 0
+
+    def next_host(self) -> int:
+        i = self.turn
+        self.turn = (self.turn + 1) % self.RING
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        return i
+
+    def upload(self, i: int) -> None:
+        self.dev.copy_(self.host[i], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+
+    def dev_view(self, name: str) -> torch.Tensor:
+        return self.dev[self.off[name]]
+
+
+class StepFunction:
+    """Model + cache + the step. `step(entries)` is the whole forward path; generation, the
+    scheduler and trace replay all go through it."""
+
+    def __init__(self, model: Decoder, cache: CacheManager, runtime: Runtime, max_requests: int):
+        self.model = model
+        self.cache = cache
+        self.rt = runtime
+        self.max_tokens = runtime.max_tokens
+        self.max_requests = int(max_requests)
+        self.vocab = model.vocab
+        self.buffers = _StepBuffers(runtime.device, self.max_tokens, self.max_requests,
+                                    {g.gid: g.max_blocks for g in cache.groups})
+        self.computed: Dict[Hashable, int] = {}       # tokens each live request has in the cache
+        self._logits: Optional[torch.Tensor] = None
+        self._dev = {name: self.buffers.dev_view(name) for name in self.buffers.off}
+        self._tables = {g.gid: self._dev[f"table{g.gid}"].view(self.max_requests, g.max_blocks) for g in cache.groups}
+        self._caches = None
+
+    # ---- request lifetime ----------------------------------------------------------------------
+    def begin(self, request) -> None:
+        self.cache.add_request(request)
+        self.computed[request] = 0
+
+    def end(self, request) -> None:
+        """The request is finished (or dropped for recompute): its pages and slot are given back."""
+        self.cache.free_request(request)
+        del self.computed[request]
+
+    def live(self) -> List[Hashable]:
+        return list(self.computed)
+
+    # ---- the step ----------------------------------------------------------------------------------
+    def _logits_buffer(self, rows: int) -> torch.Tensor:
+        if self._logits is None or self._logits.shape[0] < rows:
+            cap = max(rows, 8)
+            cap = 1 << (cap - 1).bit_length()
+            self._logits = torch.empty((min(cap, max(self.max_tokens, rows)), self.vocab), dtype=torch.float32,
+                                       device=self.rt.device)
+        return self._logits
+
+    def build_context(self, entries: Sequence[StepEntry], reserve: bool = True) -> StepContext:
+        """Check the batch, reserve pages (unless the caller already has), flatten it and upload it."""
+        if not entries:
+            raise InvalidArgument("a step needs at least one entry")
+        if len(entries) > self.max_requests:
+            raise InvalidArgument(f"{len(entries)} requests in one step, the engine was made for {self.max_requests}")
+        total = sum(len(e.tokens) for e in entries)
+        if total > self.max_tokens:
+            raise InvalidArgument(f"{total} tokens in one step, the engine was made for {self.max_tokens}")
+        seen = set()
+        for e in entries:
+            if len(e.tokens) == 0:
+                raise InvalidArgument(f"request {e.request!r} brings no tokens")
+            if e.request in seen:
+                raise InvalidArgument(f"request {e.request!r} appears twice in one step")
+            seen.add(e.request)
+            for w in e.want:
+                if not 0 <= w < len(e.tokens):
+                    raise InvalidArgument(f"request {e.request!r} wants place {w} of {len(e.tokens)} tokens")
+            if min(e.tokens) < 0 or max(e.tokens) >= self.vocab:
+                raise InvalidArgument(f"request {e.request!r} has a token id outside [0, {self.vocab})")
+        for e in entries:
+            if e.request not in self.computed:
+                if not reserve:
+                    raise InvalidArgument(f"request {e.request!r} is not live")
+                self.begin(e.request)
+            if reserve:
+                self.cache.reserve(e.request, self.computed[e.request] + len(e.tokens))
+            elif self.cache.tokens[e.request] < self.computed[e.request] + len(e.tokens):
+                raise InvalidArgument(f"request {e.request!r} has no pages reserved for its tokens")
+
+        b = self.buffers
+        i = b.next_host()
+        h = b.host_np[i]
+        off = b.off
+        tok = h[off["token_ids"]]
+        pos = h[off["positions"]]
+        rreq = h[off["row_request"]]
+        lrows = h[off["logit_rows"]]
+        q_start = h[off["q_start"]]
+        pos_start = h[off["pos_start"]]
+        kv_len = h[off["kv_len"]]
+        slots = h[off["state_slots"]]
+        r0 = 0
+        n_logit = 0
+        h_q_len, h_pos_start, h_slots = [], [], []
+        for r, e in enumerate(entries):
+            n = len(e.tokens)
+            start = self.computed[e.request]
+            tok[r0:r0 + n] = e.tokens
+            pos[r0:r0 + n] = np.arange(start, start + n, dtype=np.int32)
+            rreq[r0:r0 + n] = r
+            for w in e.want:
+                lrows[n_logit] = r0 + w
+                n_logit += 1
+            q_start[r] = r0
+            pos_start[r] = start
+            kv_len[r] = start + n
+            slot = self.cache.slot_of(e.request)
+            slots[r] = slot
+            h_q_len.append(n)
+            h_pos_start.append(start)
+            h_slots.append(slot)
+            for g in self.cache.groups:
+                mb = g.max_blocks
+                sec = off[f"table{g.gid}"]
+                h[sec.start + r * mb: sec.start + (r + 1) * mb] = self.cache.table_row(g, e.request)
+            r0 += n
+        q_start[len(entries)] = r0
+        b.upload(i)
+        d = self._dev
+        return StepContext(
+            num_tokens=total, num_requests=len(entries), token_ids=d["token_ids"], positions=d["positions"],
+            row_request=d["row_request"], q_start=d["q_start"], pos_start=d["pos_start"], kv_len=d["kv_len"],
+            state_slots=d["state_slots"], logit_rows=d["logit_rows"], num_logit_rows=n_logit,
+            h_q_len=h_q_len, h_pos_start=h_pos_start, h_state_slots=h_slots, block_tables=self._tables,
+            decode_only=all(n == 1 for n in h_q_len), max_q_len=max(h_q_len),
+            max_kv_len=max(s + n for s, n in zip(h_pos_start, h_q_len)))
+
+    def caches(self):
+        if self._caches is None:
+            self._caches = [self.cache.view(i, self._tables) for i in range(len(self.model.order))]
+        return self._caches
+
+    def step(self, entries: Sequence[StepEntry], reserve: bool = True) -> Optional[torch.Tensor]:
+        """Run the batch. Returns float32 logits [wanted rows, vocab] on the device (a view of a
+        buffer that the next step overwrites), or None when nothing was wanted."""
+        ctx = self.build_context(entries, reserve)
+        out = self._logits_buffer(ctx.num_logit_rows) if ctx.num_logit_rows else None
+        logits = self.model.forward(ctx, self.caches(), out)
+        for e in entries:
+            self.computed[e.request] += len(e.tokens)
+            self.cache.advance(e.request, self.computed[e.request])
+        return logits

@@ -1,0 +1,239 @@
+"""Python faces of the CUDA kernels: check sizes, pass pointers, launch on torch's current stream.
+
+Every function refuses what its kernel cannot take with `Unsupported` (never a wrong result) and
+raises `EngineError` when a launch fails. Tensors must live on the CUDA device; there is no CPU path.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_double, c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from ..errors import EngineError, InvalidArgument, Unsupported
+from . import lib as _lib
+
+DL_ERR_UNSUPPORTED = 10001
+
+_P, _I, _F, _L = c_void_p, c_int, c_float, c_longlong
+
+# library -> function -> argument types
+_SIGNATURES = {
+    "embedding": {"dl_embed": [_I, _P, _P, _P, _I, _I, _I, _F, _P]},
+    "norm": {
+        "dl_rmsnorm": [_I, _I, _P, _P, _F, _P, _F, _P, _P, _I, _I, _I, _P],
+        "dl_residual_add": [_I, _P, _P, _F, _L, _P],
+    },
+    "activation": {"dl_silu_mul": [_I, _P, _P, _I, _I, _P]},
+    "rope_cache": {"dl_rope_cache_write": [_I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _F, _I, _I, _I, _I, _I, _I, _P]},
+    "attention_generic": {
+        "dl_paged_attention_generic": [_I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P]},
+    "gemm_simt": {"dl_gemm_simt": [_I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _P]},
+    "sampling": {
+        "dl_argmax": [_P, _I, _I, _I, _P, _P],
+        "dl_sample_temperature": [_P, _I, _I, _I, _P, _P, _P, _P],
+    },
+}
+
+_funcs = {}
+
+
+def _fn(library: str, name: str):
+    f = _funcs.get(name)
+    if f is None:
+        f = getattr(_lib.load(library), name)
+        f.argtypes = _SIGNATURES[library][name]
+        f.restype = c_int
+        _funcs[name] = f
+    return f
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code == DL_ERR_UNSUPPORTED:
+        raise Unsupported(f"{what}: the kernel refuses these sizes")
+    raise EngineError(f"{what}: CUDA error {code}")
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return 0
+    if dtype == torch.bfloat16:
+        return 1
+    raise Unsupported(f"dtype {dtype} has no kernels (float32 and bfloat16 do)")
+
+
+def _cuda(*tensors: Optional[torch.Tensor]) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise InvalidArgument("kernels take CUDA tensors only; there is no CPU path")
+
+
+def _rows_contiguous(t: torch.Tensor, what: str) -> None:
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise InvalidArgument(f"{what} must be 2-D with unit stride along its rows")
+
+
+# ---------------------------------------------------------------------------------------------
+
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[i, :] = table[ids[i], :] * scale; out is the float32 residual stream [rows, width]."""
+    _cuda(table, ids, out)
+    rows, width = out.shape
+    if out.dtype != torch.float32 or not out.is_contiguous() or ids.dtype != torch.int32 or not table.is_contiguous():
+        raise InvalidArgument("embed: out float32 contiguous, ids int32, table contiguous")
+    if table.shape[1] != width or ids.numel() < rows:
+        raise InvalidArgument("embed: shapes disagree")
+    _check(_fn("embedding", "dl_embed")(dtype_code(table.dtype), _p(table), _p(ids), _p(out), rows, width,
+                                         table.shape[0], scale, _stream()), "embed")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, delta: Optional[torch.Tensor] = None,
+            delta_scale: float = 1.0, rows: Optional[torch.Tensor] = None, write_residual: bool = True) -> None:
+    """out[r] = rmsnorm(x[src] + delta_scale * delta[src]) * weight, src = rows[r] or r.
+
+    x: float32 [n, width] residual stream, updated in place with the sum when `delta` is given and
+    `write_residual`; delta: [n, width] of either dtype; weight: float32 [width]; out: [n_out, width]."""
+    _cuda(x, weight, out, delta, rows)
+    width = x.shape[1]
+    if x.dtype != torch.float32 or weight.dtype != torch.float32 or not x.is_contiguous() or not out.is_contiguous():
+        raise InvalidArgument("rmsnorm: x and weight float32, x and out contiguous")
+    if out.shape[1] != width or weight.numel() != width:
+        raise InvalidArgument("rmsnorm: widths disagree")
+    n_rows = out.shape[0]
+    if rows is not None:
+        if rows.dtype != torch.int32 or rows.numel() < n_rows:
+            raise InvalidArgument("rmsnorm: rows must be int32 with one entry per output row")
+        write_residual = False
+    elif x.shape[0] < n_rows:
+        raise InvalidArgument("rmsnorm: fewer input rows than output rows")
+    if delta is not None and (not delta.is_contiguous() or delta.shape[1] != width):
+        raise InvalidArgument("rmsnorm: delta must be contiguous [n, width]")
+    dd = dtype_code(delta.dtype) if delta is not None else dtype_code(out.dtype)
+    _check(_fn("norm", "dl_rmsnorm")(dtype_code(out.dtype), dd, _p(x), _p(delta), delta_scale, _p(weight), eps,
+                                      _p(out), _p(rows), n_rows, width, 1 if write_residual else 0, _stream()),
+           "rmsnorm")
+
+
+def residual_add(x: torch.Tensor, delta: torch.Tensor, scale: float = 1.0) -> None:
+    """x += scale * delta over the first delta.shape[0] rows (x float32)."""
+    _cuda(x, delta)
+    if x.dtype != torch.float32 or not x.is_contiguous() or not delta.is_contiguous() or x.shape[1] != delta.shape[1]:
+        raise InvalidArgument("residual_add: x float32, both contiguous, same width")
+    _check(_fn("norm", "dl_residual_add")(dtype_code(delta.dtype), _p(x), _p(delta), scale, delta.numel(), _stream()),
+           "residual_add")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, j] = silu(gate_up[t, j]) * gate_up[t, inner + j]."""
+    _cuda(gate_up, out)
+    rows, inner = out.shape
+    if gate_up.shape != (rows, 2 * inner) or not gate_up.is_contiguous() or not out.is_contiguous() \
+            or gate_up.dtype != out.dtype:
+        raise InvalidArgument("silu_mul: gate_up [rows, 2*inner] and out [rows, inner], contiguous, one dtype")
+    _check(_fn("activation", "dl_silu_mul")(dtype_code(out.dtype), _p(gate_up), _p(out), rows, inner, _stream()),
+           "silu_mul")
+
+
+def rope_cache_write(qkv: torch.Tensor, positions: torch.Tensor, row_request: torch.Tensor,
+                     block_table: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+                     v_cache: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor], rotary_dim: int,
+                     pos_scale: float, n_heads: int, n_kv_heads: int, head_dim: int, page_size: int,
+                     write_cache: bool = True) -> None:
+    """Rotate the q heads of `qkv` in place; rotate the k heads and copy the v heads into the paged
+    cache at each row's position. qkv: [rows, >= (n_heads + 2 n_kv_heads) head_dim]."""
+    _cuda(qkv, positions, row_request, block_table, k_cache, v_cache, inv_freq)
+    _rows_contiguous(qkv, "qkv")
+    rows = qkv.shape[0]
+    need = (n_heads + (2 * n_kv_heads if write_cache else 0)) * head_dim
+    if qkv.shape[1] < need:
+        raise InvalidArgument("rope_cache_write: qkv is narrower than its heads")
+    if write_cache:
+        if k_cache is None or v_cache is None or block_table is None:
+            raise InvalidArgument("rope_cache_write: a cache write needs k_cache, v_cache and a block table")
+        if k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+            raise InvalidArgument("rope_cache_write: cache arrays must be contiguous and of qkv's dtype")
+        if tuple(k_cache.shape[1:]) != (page_size, n_kv_heads, head_dim):
+            raise InvalidArgument("rope_cache_write: cache shape is not [pages, page_size, kv_heads, head_dim]")
+        if block_table.dtype != torch.int32 or block_table.stride(-1) != 1:
+            raise InvalidArgument("rope_cache_write: block_table must be int32 rows")
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() * 2 != rotary_dim):
+        raise InvalidArgument("rope_cache_write: inv_freq must be float32 [rotary_dim / 2]")
+    if rotary_dim > head_dim or rotary_dim % 2:
+        raise Unsupported(f"rotary_dim {rotary_dim} does not fit head_dim {head_dim}")
+    max_blocks = block_table.stride(0) if block_table is not None else 0
+    _check(_fn("rope_cache", "dl_rope_cache_write")(
+        dtype_code(qkv.dtype), _p(qkv), qkv.stride(0), _p(positions), _p(row_request), _p(block_table), max_blocks,
+        _p(k_cache), _p(v_cache), _p(inv_freq), rotary_dim if inv_freq is not None else 0, pos_scale, rows, n_heads,
+        n_kv_heads, head_dim, page_size, 1 if write_cache else 0, _stream()), "rope_cache_write")
+
+
+def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                            positions: torch.Tensor, row_request: torch.Tensor, out: torch.Tensor, n_heads: int,
+                            n_kv_heads: int, head_dim: int, page_size: int, scale: float, window: int = 0) -> None:
+    """Causal attention of every row over its request's cached keys; see csrc/attention_generic.cu.
+    q, out: [rows, >= n_heads * head_dim] views with unit column stride."""
+    _cuda(q, k_cache, v_cache, block_table, positions, row_request, out)
+    _rows_contiguous(q, "q")
+    _rows_contiguous(out, "out")
+    if head_dim % 16 or head_dim > 256:
+        raise Unsupported(f"attention: head_dim {head_dim} must be a multiple of 16, at most 256")
+    if n_heads % n_kv_heads:
+        raise Unsupported(f"attention: {n_heads} heads do not divide into {n_kv_heads} KV heads")
+    if q.dtype != out.dtype or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        raise InvalidArgument("attention: q, out and the cache must share one dtype")
+    if tuple(k_cache.shape[1:]) != (page_size, n_kv_heads, head_dim) or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+        raise InvalidArgument("attention: cache shape is not [pages, page_size, kv_heads, head_dim]")
+    _check(_fn("attention_generic", "dl_paged_attention_generic")(
+        dtype_code(q.dtype), _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), block_table.stride(0),
+        _p(positions), _p(row_request), _p(out), out.stride(0), q.shape[0], n_heads, n_kv_heads, head_dim, page_size,
+        scale, window, _stream()), "paged_attention_generic")
+
+
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+              out_scale: float = 1.0) -> None:
+    """out = (x @ w.T + bias) * out_scale with fp32 accumulation in a fixed order; see csrc/gemm_simt.cu."""
+    _cuda(x, w, out, bias)
+    _rows_contiguous(x, "x")
+    _rows_contiguous(out, "out")
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or not w.is_contiguous() or out.shape != (M, N) or x.dtype != w.dtype:
+        raise InvalidArgument("gemm: x [M, K], w [N, K] contiguous and of x's dtype, out [M, N]")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
+        raise InvalidArgument("gemm: bias must be float32 [N]")
+    _check(_fn("gemm_simt", "dl_gemm_simt")(dtype_code(x.dtype), dtype_code(out.dtype), _p(x), x.stride(0), _p(w),
+                                             _p(bias), _p(out), out.stride(0), M, N, K, out_scale, _stream()), "gemm_simt")
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = lowest index of the largest value of logits[r, :] (float32 rows, int32 out)."""
+    _cuda(logits, out)
+    _rows_contiguous(logits, "logits")
+    if logits.dtype != torch.float32 or out.dtype != torch.int32 or out.numel() < logits.shape[0]:
+        raise InvalidArgument("argmax: logits float32, out int32 with one entry per row")
+    _check(_fn("sampling", "dl_argmax")(_p(logits), logits.stride(0), logits.shape[0], logits.shape[1], _p(out),
+                                         _stream()), "argmax")
+
+
+def sample_temperature(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor) -> None:
+    """Draw out[r] from softmax(logits[r] / temperature[r]) by walking the ids in order with uniform[r]."""
+    _cuda(logits, temperature, uniform, out)
+    _rows_contiguous(logits, "logits")
+    rows = logits.shape[0]
+    if (logits.dtype != torch.float32 or temperature.dtype != torch.float32 or uniform.dtype != torch.float64
+            or out.dtype != torch.int32 or min(temperature.numel(), uniform.numel(), out.numel()) < rows):
+        raise InvalidArgument("sample_temperature: logits/temperature float32, uniform float64, out int32, one per row")
+    _check(_fn("sampling", "dl_sample_temperature")(_p(logits), logits.stride(0), rows, logits.shape[1], _p(temperature),
+                                                     _p(uniform), _p(out), _stream()), "sample_temperature")

@@ -1,0 +1,96 @@
+"""Causal grouped-query attention over the paged cache: the "attention" mixer.
+
+Order of work as the reference's layer body (dynalm/src/model/transformer.cpp:607-654): q, k, v
+projections (here one product against the row-wise concatenation [Wq; Wk; Wv], which changes no
+result), position encoding of q and k, write of k and v into the cache, attention of every row over
+its request's keys, output projection. The mixer keeps sizes and constants from its spec only.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..errors import Unsupported
+from ..kernels import linear, ops
+from .base import POSITIONS, CacheSpec, TensorDecl, register_mixer
+
+
+@register_mixer("attention")
+class PagedAttention:
+    @staticmethod
+    def declare(spec) -> Dict[str, TensorDecl]:
+        qw, kw = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
+        return {
+            "q": TensorDecl((qw, spec.width)),
+            "k": TensorDecl((kw, spec.width)),
+            "v": TensorDecl((kw, spec.width)),
+            "o": TensorDecl((spec.width, qw)),
+            "q_bias": TensorDecl((qw,), role="vector", required=False),
+            "k_bias": TensorDecl((kw,), role="vector", required=False),
+            "v_bias": TensorDecl((kw,), role="vector", required=False),
+            "o_bias": TensorDecl((spec.width,), role="vector", required=False),
+        }
+
+    def __init__(self, spec, tensors: Dict[str, torch.Tensor], runtime):
+        if spec.head_dim % 16 or not 0 < spec.head_dim <= 256:
+            raise Unsupported(f"attention: head_dim {spec.head_dim} must be a multiple of 16, at most 256")
+        if spec.num_heads % spec.num_kv_heads:
+            raise Unsupported(f"attention: {spec.num_heads} heads do not divide into {spec.num_kv_heads} KV heads")
+        self.spec = spec
+        self.rt = runtime
+        self.q_width = spec.num_heads * spec.head_dim
+        self.kv_width = spec.num_kv_heads * spec.head_dim
+        self.w_qkv = torch.cat([tensors["q"], tensors["k"], tensors["v"]], dim=0).contiguous()
+        biases = [tensors.get("q_bias"), tensors.get("k_bias"), tensors.get("v_bias")]
+        if any(b is not None for b in biases):
+            widths = (self.q_width, self.kv_width, self.kv_width)
+            self.b_qkv = torch.cat([b if b is not None else torch.zeros(w, dtype=torch.float32, device=runtime.device)
+                                    for b, w in zip(biases, widths)]).contiguous()
+        else:
+            self.b_qkv = None
+        self.w_o = tensors["o"]
+        self.b_o = tensors.get("o_bias")
+        pos = spec.position
+        self.position = POSITIONS.get(pos.kind)(pos, runtime) if pos is not None else None
+
+    def cache_spec(self) -> Optional[CacheSpec]:
+        return CacheSpec(kind="pages", entry_shape=(self.spec.num_kv_heads, self.spec.head_dim), tensors=2,
+                         window=self.spec.window)
+
+    def forward(self, x: torch.Tensor, ctx, cache, owns_cache: bool = True) -> torch.Tensor:
+        """x: [rows, width] normed input in the compute dtype -> [rows, width]."""
+        s, rt = self.spec, self.rt
+        rows = x.shape[0]
+        k_cache, v_cache = cache.arrays
+        if owns_cache:
+            qkv = rt.buffer("attn_qkv", (rows, self.q_width + 2 * self.kv_width))
+            linear(x, self.w_qkv, qkv, self.b_qkv)
+        else:
+            # a layer that reads another entry's cache makes queries only
+            qkv = rt.buffer("attn_qkv", (rows, self.q_width + 2 * self.kv_width))[:, :self.q_width]
+            linear(x, self.w_qkv[:self.q_width], qkv, self.b_qkv[:self.q_width] if self.b_qkv is not None else None)
+        table = self.position.table() if self.position is not None else None
+        if self.position is not None and table is None:
+            q = qkv[:, :self.q_width].unflatten(1, (s.num_heads, s.head_dim))
+            k = qkv[:, self.q_width:self.q_width + self.kv_width].unflatten(1, (s.num_kv_heads, s.head_dim)) \
+                if owns_cache else None
+            self.position.apply(q, k, ctx.positions[:rows])
+        inv_freq, rot, pos_scale = table if table is not None else (None, 0, 1.0)
+        ops.rope_cache_write(qkv, ctx.positions, ctx.row_request, cache.block_table, k_cache, v_cache, inv_freq, rot,
+                             pos_scale, s.num_heads, s.num_kv_heads, s.head_dim, cache.page_size, write_cache=owns_cache)
+        attn = rt.buffer("attn_out", (rows, self.q_width))
+        self.attend(qkv, cache, ctx, attn)
+        out = rt.buffer("mixer_out", (rows, s.width))
+        linear(attn, self.w_o, out, self.b_o)
+        return out
+
+    def attend(self, qkv: torch.Tensor, cache, ctx, out: torch.Tensor) -> None:
+        s = self.spec
+        k_cache, v_cache = cache.arrays
+        from ..kernels import attention as fast
+        if fast.paged_attention(qkv, cache, ctx, out, s):
+            return
+        ops.paged_attention_generic(qkv, k_cache, v_cache, cache.block_table, ctx.positions, ctx.row_request, out,
+                                    s.num_heads, s.num_kv_heads, s.head_dim, cache.page_size, float(s.scale), s.window)

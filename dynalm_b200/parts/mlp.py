@@ -1,0 +1,42 @@
+"""Gated feed-forward: down(act(gate x) * up x), the "gated_mlp" kind
+(dynalm/src/model/transformer.cpp:671-693). Gate and up run as one product against [Wg; Wu]."""
+
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..errors import Unsupported
+from ..kernels import linear, ops
+from .base import TensorDecl, register_feed_forward
+
+
+@register_feed_forward("gated_mlp")
+class GatedMLP:
+    @staticmethod
+    def declare(spec) -> Dict[str, TensorDecl]:
+        return {
+            "gate": TensorDecl((spec.inner, spec.width)),
+            "up": TensorDecl((spec.inner, spec.width)),
+            "down": TensorDecl((spec.width, spec.inner)),
+        }
+
+    def __init__(self, spec, tensors: Dict[str, torch.Tensor], runtime):
+        if spec.activation != "silu":
+            raise Unsupported(f"gated_mlp: activation '{spec.activation}' has no kernel (silu does)")
+        self.spec = spec
+        self.rt = runtime
+        self.w_gate_up = torch.cat([tensors["gate"], tensors["up"]], dim=0).contiguous()
+        self.w_down = tensors["down"]
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        s, rt = self.spec, self.rt
+        rows = x.shape[0]
+        gate_up = rt.buffer("ffn_gate_up", (rows, 2 * s.inner))
+        linear(x, self.w_gate_up, gate_up)
+        act = rt.buffer("ffn_act", (rows, s.inner))
+        ops.silu_mul(gate_up, act)
+        out = rt.buffer("ffn_out", (rows, s.width))
+        linear(act, self.w_down, out)
+        return out

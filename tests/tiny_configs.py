@@ -1,0 +1,33 @@
+"""Tiny Llama configurations for tests: config.json dicts that differ in every size and option."""
+
+# 2 layers, head_dim = hidden / heads, tied embeddings, plain RoPE.
+TINY_A = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "vocab_size": 256, "hidden_size": 64, "intermediate_size": 192, "num_hidden_layers": 2,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "max_position_embeddings": 128,
+    "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "tie_word_embeddings": True,
+}
+
+# 3 layers, explicit head_dim (heads * head_dim != hidden), 3:1 groups, llama3 RoPE scaling, untied head.
+TINY_B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "vocab_size": 384, "hidden_size": 96, "intermediate_size": 160, "num_hidden_layers": 3,
+    "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 32, "max_position_embeddings": 256,
+    "rms_norm_eps": 1e-6, "rope_theta": 500000.0, "tie_word_embeddings": False,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 32},
+}
+
+# 1 KV head, head_dim 48, a vocabulary that is no multiple of 8, partial rotary, linear scaling and the
+# four multipliers the reference reads for every model_type.
+TINY_C = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "vocab_size": 499, "hidden_size": 80, "intermediate_size": 112, "num_hidden_layers": 2,
+    "num_attention_heads": 5, "num_key_value_heads": 1, "head_dim": 48, "max_position_embeddings": 512,
+    "rms_norm_eps": 3e-5, "rope_theta": 25000.0, "tie_word_embeddings": True,
+    "partial_rotary_factor": 0.5,
+    "rope_scaling": {"type": "linear", "factor": 2.0},
+    "embedding_multiplier": 3.0, "residual_multiplier": 0.5, "attention_multiplier": 0.2, "logits_scaling": 4.0,
+}
+
+TINY = {"a": (TINY_A, 0), "b": (TINY_B, 2), "c": (TINY_C, 9)}   # name -> (config, weight seed)
