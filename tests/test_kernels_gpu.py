@@ -1,0 +1,273 @@
+"""Each kernel alone against a plain PyTorch fp32 reference of the same op, at sizes that are not
+the engine's: widths and vocabularies that are no power of two, head sizes in steps of 16, odd
+numbers of heads and groups, windows, pages entered in the middle."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype, scale=1.0):
+    return (2e-5 if dtype == torch.float32 else 2e-2) * scale
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from dynalm_b200.kernels import ops as o
+    return o
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width,vocab", [(80, 499), (2048, 1000), (24, 7)])
+def test_embed(ops, dtype, width, vocab):
+    g = torch.Generator(device="cpu").manual_seed(1)
+    table = torch.randn(vocab, width, generator=g).to(DEV, dtype)
+    ids = torch.randint(0, vocab, (37,), generator=g, dtype=torch.int32).to(DEV)
+    out = torch.empty(37, width, dtype=torch.float32, device=DEV)
+    ops.embed(table, ids, out, 3.0)
+    ref = table.float()[ids.long()] * 3.0
+    assert torch.equal(out, ref)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [96, 1000, 2048, 5120])
+def test_rmsnorm_with_residual_and_rows(ops, dtype, width):
+    g = torch.Generator(device="cpu").manual_seed(2)
+    n = 19
+    x = (torch.randn(n, width, generator=g) * 3).to(DEV)
+    delta = torch.randn(n, width, generator=g).to(DEV, dtype)
+    w = (1 + 0.1 * torch.randn(width, generator=g)).to(DEV)
+    eps = 3e-5
+
+    def ref_norm(v):
+        v = v.double()
+        return (v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * w.double()).float()
+
+    # plain
+    out = torch.empty(n, width, dtype=dtype, device=DEV)
+    ops.rmsnorm(x.clone(), w, eps, out)
+    assert (out.float() - ref_norm(x)).abs().max() <= tol(dtype, 4)
+    # fused residual add, written back
+    x2 = x.clone()
+    ops.rmsnorm(x2, w, eps, out, delta=delta, delta_scale=0.5)
+    summed = x + 0.5 * delta.float()
+    assert (x2 - summed).abs().max() <= 1e-6
+    assert (out.float() - ref_norm(summed)).abs().max() <= tol(dtype, 4)
+    # gathered rows: nothing written back
+    rows = torch.tensor([18, 0, 7], dtype=torch.int32, device=DEV)
+    x3 = x.clone()
+    out3 = torch.empty(3, width, dtype=dtype, device=DEV)
+    ops.rmsnorm(x3, w, eps, out3, delta=delta, delta_scale=0.5, rows=rows)
+    assert torch.equal(x3, x)
+    assert (out3.float() - ref_norm(summed[rows.long()])).abs().max() <= tol(dtype, 4)
+    # pending add alone
+    x4 = x.clone()
+    ops.residual_add(x4, delta, 0.5)
+    assert (x4 - summed).abs().max() <= 1e-6
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(ops, dtype):
+    g = torch.Generator(device="cpu").manual_seed(3)
+    gu = (torch.randn(13, 2 * 112, generator=g) * 4).to(DEV, dtype)
+    out = torch.empty(13, 112, dtype=dtype, device=DEV)
+    ops.silu_mul(gu, out)
+    a, b = gu.float()[:, :112], gu.float()[:, 112:]
+    ref = a * torch.sigmoid(a) * b
+    assert (out.float() - ref).abs().max() <= tol(dtype, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 499, 80), (37, 130, 200), (64, 64, 16), (200, 96, 1000), (5, 3, 7)])
+def test_gemm_simt(ops, dtype, M, N, K):
+    g = torch.Generator(device="cpu").manual_seed(4)
+    x = torch.randn(M, K, generator=g).to(DEV, dtype)
+    w = torch.randn(N, K, generator=g).to(DEV, dtype)
+    bias = torch.randn(N, generator=g).to(DEV)
+    ref = (x.double() @ w.double().T + bias.double()) * 0.25
+    for out_dtype in ({torch.float32} | {dtype}):
+        out = torch.empty(M, N, dtype=out_dtype, device=DEV)
+        ops.gemm_simt(x, w, out, bias, 0.25)
+        scale = ref.abs().max().item()
+        assert (out.double() - ref).abs().max() <= (1e-5 if out_dtype == torch.float32 else 1e-2) * scale
+    # a row's result does not depend on how many rows share the call
+    if M > 1:
+        one = torch.empty(1, N, dtype=torch.float32, device=DEV)
+        full = torch.empty(M, N, dtype=torch.float32, device=DEV)
+        ops.gemm_simt(x, w, full)
+        ops.gemm_simt(x[M - 1:M], w, one)
+        assert torch.equal(one[0], full[M - 1])
+
+
+def _rope_ref(x, pos, inv_freq, rot, pos_scale):
+    """x [n, heads, hd] fp64; half-split rotation of the first `rot` dims."""
+    half = rot // 2
+    theta = (pos.float() * pos_scale)[:, None] * inv_freq[None, :]          # fp32 product, as the kernel
+    c, s = torch.cos(theta.double())[:, None, :], torch.sin(theta.double())[:, None, :]
+    out = x.clone()
+    a, b = x[..., :half], x[..., half:rot]
+    out[..., :half] = a * c - b * s
+    out[..., half:rot] = a * s + b * c
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kvh,hd,rot,page", [(5, 1, 48, 24, 16), (6, 2, 32, 32, 16), (3, 3, 80, 80, 32),
+                                                     (8, 2, 128, 128, 16)])
+def test_rope_cache_write(ops, dtype, heads, kvh, hd, rot, page):
+    g = torch.Generator(device="cpu").manual_seed(5)
+    n_req, max_blocks, pages = 3, 8, 40
+    # three requests with rows at scattered positions; pages handed out in a shuffled order
+    perm = torch.randperm(pages, generator=g)[: n_req * max_blocks].reshape(n_req, max_blocks).to(torch.int32)
+    req = torch.tensor([0, 0, 0, 1, 2, 2, 1, 0], dtype=torch.int32)
+    pos = torch.tensor([14, 15, 16, 0, 100, 101, 47, 127 if page * max_blocks > 127 else 17], dtype=torch.int32)
+    n = len(req)
+    width = (heads + 2 * kvh) * hd
+    qkv = torch.randn(n, width, generator=g).to(DEV, dtype)
+    inv = (10000.0 ** (-torch.arange(rot // 2).float() * 2 / rot)).to(DEV)
+    kc = torch.zeros(pages, page, kvh, hd, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    before = qkv.clone()
+    ops.rope_cache_write(qkv, pos.to(DEV), req.to(DEV), perm.to(DEV), kc, vc, inv, rot, 0.5, heads, kvh, hd, page)
+    src = before.double().cpu()
+    q = src[:, :heads * hd].reshape(n, heads, hd)
+    k = src[:, heads * hd:(heads + kvh) * hd].reshape(n, kvh, hd)
+    v = src[:, (heads + kvh) * hd:].reshape(n, kvh, hd)
+    q_ref = _rope_ref(q, pos, inv.cpu(), rot, 0.5)
+    k_ref = _rope_ref(k, pos, inv.cpu(), rot, 0.5)
+    t = tol(dtype, 4)
+    assert (qkv[:, :heads * hd].double().cpu().reshape(n, heads, hd) - q_ref).abs().max() <= t
+    for i in range(n):
+        p = perm[req[i], pos[i] // page].item()
+        s = pos[i].item() % page
+        assert (kc[p, s].double().cpu() - k_ref[i]).abs().max() <= t, f"key of row {i}"
+        assert torch.equal(vc[p, s].cpu(), before[i, (heads + kvh) * hd:].reshape(kvh, hd).cpu()), f"value of row {i}"
+    # nothing else was touched
+    written = torch.zeros(pages, page, dtype=torch.bool)
+    for i in range(n):
+        written[perm[req[i], pos[i] // page], pos[i] % page] = True
+    assert kc.cpu()[~written].abs().max() == 0 and vc.cpu()[~written].abs().max() == 0
+
+
+def _attention_ref(q, keys, vals, scale, window):
+    """One row: q [heads, hd], keys/vals [t, kvh, hd] (positions 0..t-1, the row is at t-1)."""
+    heads, hd = q.shape
+    kvh = keys.shape[1]
+    t = keys.shape[0]
+    lo = max(0, t - window) if window > 0 else 0
+    out = torch.zeros(heads, hd, dtype=torch.float64)
+    for h in range(heads):
+        kh = keys[lo:, h // (heads // kvh)]
+        vh = vals[lo:, h // (heads // kvh)]
+        s = scale * (kh @ q[h])
+        p = torch.softmax(s, 0)
+        out[h] = p @ vh
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kvh,hd,page,window", [(4, 2, 16, 16, 0), (6, 2, 32, 16, 0), (5, 1, 48, 16, 0),
+                                                        (3, 3, 80, 32, 0), (8, 2, 128, 16, 40), (2, 1, 256, 16, 0),
+                                                        (4, 4, 64, 16, 7)])
+def test_paged_attention_generic(ops, dtype, heads, kvh, hd, page, window):
+    """Three requests in scattered pages (60 / 700 / 130 tokens); a batch that mixes a decode row, a
+    portion that starts in the middle of a page, a short run and another decode row. One far key is
+    made to stand out so that a kernel that skips or repeats a page cannot pass."""
+    g = torch.Generator(device="cpu").manual_seed(6)
+    lens = [60, 700, 130]
+    max_blocks = -(-max(lens) // page)
+    pages = sum(-(-l // page) for l in lens) + 5
+    perm = torch.randperm(pages, generator=g)
+    table = torch.full((3, max_blocks), -1, dtype=torch.int32)
+    kc = torch.zeros(pages, page, kvh, hd, dtype=dtype)
+    vc = torch.zeros_like(kc)
+    keys, vals = [], []
+    nxt = 0
+    for r, l in enumerate(lens):
+        k = torch.randn(l, kvh, hd, generator=g).to(dtype)
+        v = torch.randn(l, kvh, hd, generator=g).to(dtype)
+        k[3] *= 4.0                               # a far key with a large score for matching queries
+        keys.append(k)
+        vals.append(v)
+        for b in range(-(-l // page)):
+            table[r, b] = perm[nxt]
+            nxt += 1
+            n = min(page, l - b * page)
+            kc[table[r, b], :n] = k[b * page:b * page + n]
+            vc[table[r, b], :n] = v[b * page:b * page + n]
+    # rows: (request, position)
+    rows = [(0, 59)] + [(1, p) for p in range(700 - 210, 700)] + [(2, p) for p in range(100, 105)] + [(2, 129)]
+    # one row of request 1 is taken out and put last, as a second decode-like row would be
+    req = torch.tensor([r for r, _ in rows], dtype=torch.int32)
+    pos = torch.tensor([p for _, p in rows], dtype=torch.int32)
+    n = len(rows)
+    q = torch.randn(n, heads, hd, generator=g).to(dtype)
+    for i, (r, p) in enumerate(rows):
+        if i % 3 == 0:
+            q[i, :, :] = (keys[r][3, 0].float() * 0.5).to(dtype)     # points at the far key
+    scale = 1.0 / math.sqrt(hd)
+    out = torch.zeros(n, heads * hd, dtype=dtype, device=DEV)
+    ops.paged_attention_generic(q.reshape(n, heads * hd).to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV),
+                                pos.to(DEV), req.to(DEV), out, heads, kvh, hd, page, scale, window)
+    got = out.double().cpu().reshape(n, heads, hd)
+    for i, (r, p) in enumerate(rows):
+        ref = _attention_ref(q[i].double(), keys[r][:p + 1].double(), vals[r][:p + 1].double(), scale, window)
+        err = (got[i] - ref).abs().max().item()
+        assert err <= tol(dtype, 2), f"row {i} (request {r}, position {p}): {err}"
+
+
+def test_argmax_ties_and_sizes(ops):
+    g = torch.Generator(device="cpu").manual_seed(7)
+    for vocab in (7, 499, 128256):
+        logits = torch.randn(5, vocab, generator=g)
+        logits[1, 3] = logits[1].max() + 1
+        logits[1, min(6, vocab - 1)] = logits[1, 3]              # a tie: the lowest id wins
+        logits[2, vocab - 1] = 50.0
+        logits[3, 0] = 50.0
+        d = logits.to(DEV)
+        out = torch.empty(5, dtype=torch.int32, device=DEV)
+        ops.argmax(d, out)
+        ref = [int(np.flatnonzero(row == row.max())[0]) for row in logits.numpy()]
+        assert out.cpu().tolist() == ref
+
+
+def test_sample_temperature_matches_walk(ops):
+    from plain_llama import sample_temperature
+    g = torch.Generator(device="cpu").manual_seed(8)
+    for vocab in (11, 499, 5000):
+        logits = torch.randn(64, vocab, generator=g) * 3
+        temps = torch.full((64,), 0.8)
+        u = torch.rand(64, generator=g, dtype=torch.float64)
+        out = torch.empty(64, dtype=torch.int32, device=DEV)
+        ops.sample_temperature(logits.to(DEV), temps.to(DEV), u.to(DEV), out)
+        got = out.cpu().tolist()
+        agree = 0
+        for r in range(64):
+            ref = sample_temperature(logits[r].numpy(), 0.8, float(u[r]))
+            # a draw that lands within rounding of a boundary may fall to the neighbour
+            agree += got[r] == ref
+            assert abs(got[r] - ref) <= 1, f"row {r}: {got[r]} vs {ref}"
+        assert agree >= 62
+
+
+def test_sample_temperature_frequencies(ops):
+    """20 000 draws: empirical frequencies within 0.015 of softmax(l / T)
+    (the reference's own check, dynalm/tests/test_engine.cpp:507-680)."""
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0, 0.5]])
+    T = 0.7
+    n = 20000
+    g = torch.Generator(device="cpu").manual_seed(9)
+    u = torch.rand(n, generator=g, dtype=torch.float64).to(DEV)
+    big = logits.repeat(n, 1).to(DEV)
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops.sample_temperature(big, torch.full((n,), T, device=DEV), u, out)
+    freq = torch.bincount(out.cpu().long(), minlength=5).double() / n
+    p = torch.softmax(logits[0].double() / T, 0)
+    assert (freq - p).abs().max() < 0.015

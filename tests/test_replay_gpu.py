@@ -1,0 +1,67 @@
+"""Replay on the GPU against the plain implementation: the same requests whole, with the last 32
+tokens one by one, in portions of changing size, and mixed with so few pages that they are reused;
+in 32-bit and in bfloat16, for every tiny configuration."""
+
+import numpy as np
+import pytest
+
+from plain_llama import PlainLlama
+from replay_util import (compare, plan_chunks, plan_mixed, plan_tail, plan_whole, random_requests,
+                         run_plan_in_process, run_plan_trace_run)
+from tiny_configs import TINY
+
+pytestmark = pytest.mark.gpu
+
+# (absolute, relative-to-row-scale) tolerance on logits per dtype
+TOL = {"float32": (2e-5, 2e-5), "bfloat16": (2e-2, 4e-2)}
+LENGTHS = {"a": [5, 17, 33, 70, 41, 64], "b": [1, 7, 40, 64, 100, 129], "c": [3, 48, 95, 33, 160, 16]}
+SIZES = [16, 7, 2, 5, 3, 2, 11, 32, 2, 9]
+
+
+@pytest.fixture(scope="module")
+def plain_logits(tiny_folders):
+    out = {}
+    for name, (cfg, _) in TINY.items():
+        reqs = random_requests(cfg["vocab_size"], LENGTHS[name], seed=11 + len(name))
+        model = PlainLlama(tiny_folders[name])
+        out[name] = (reqs, {r: model.logits(t) for r, t in reqs.items()})
+    return out
+
+
+def _built(folder, dtype, kv_tokens, max_batch):
+    from dynalm_b200.engine import build
+    return build(folder, dtype=dtype, kv_tokens=kv_tokens, max_batch_tokens=max_batch, max_requests=8,
+                 context=max(kv_tokens, 256))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+def test_replay_all_cuts(name, dtype, tiny_folders, plain_logits):
+    reqs, plain = plain_logits[name]
+    tol = TOL[dtype]
+    plans = {
+        "whole": plan_whole(reqs),
+        "tail32": plan_tail(reqs, 32),
+        "chunks": plan_chunks(reqs, SIZES),
+        "mixed": plan_mixed(reqs, seed=5),
+        "mixed2": plan_mixed(reqs, seed=6, max_live=3, decode_tail=20),
+    }
+    for what, plan in plans.items():
+        # the pool is just what the plan needs, so that finished requests' pages are reused
+        need = plan.max_live_tokens(64)
+        built = _built(tiny_folders[name], dtype, need, max(need, 64))
+        got = run_plan_in_process(built.step_fn, plan)
+        worst = compare(plan, got, plain, tol[0], tol[1], f"{name}/{dtype}/{what}")
+        assert built.cache.free_pages == built.cache.num_pages, "pages were lost"
+        print(f"{name} {dtype} {what}: steps {len(plan.steps)} pool {need} worst {worst:.3g}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(dtype, tiny_folders, plain_logits, tmp_path):
+    """The program itself, as a user runs it: stdin in, files out, `done` lines."""
+    name = "b"
+    reqs, plain = plain_logits[name]
+    plan = plan_mixed(reqs, seed=7)
+    vocab = TINY[name][0]["vocab_size"]
+    got = run_plan_trace_run(tiny_folders[name], dtype, plan, str(tmp_path / "out"), plan.max_live_tokens(64), vocab)
+    compare(plan, got, plain, *TOL[dtype], f"trace_run/{dtype}")
