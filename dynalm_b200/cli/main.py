@@ -1,0 +1,215 @@
+"""Command line in the manner of `dynalm run` (dynalm/src/cli/main.cpp:112-190, run.cpp:34-73,208-450).
+
+    dynalm run <model_dir> --tokens 1,2,3 -n 32 --temp 0.8 --seed 4
+
+Option names and meanings are the reference's where it has them (-n/--max-tokens, -c/--ctx, --batch,
+--kv, --mode, --temp, --top-k, --top-p, --min-p, --repeat-penalty, --presence-penalty,
+--frequency-penalty, --repeat-last-n, --seed, --no-stream, -q/-v). This engine starts at token ids:
+the prompt is given as ids (`--tokens`, or `-p` holding ids separated by commas or spaces) or drawn
+at random (`--prompt-len`); output is token ids. After the ids come the reference's two stats lines.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import tempfile
+import time
+
+from .. import __version__
+
+USAGE = """usage: dynalm run <model> (--tokens IDS | -p IDS | --prompt-len N) [options]
+       dynalm random-model <out_dir> --config FILE --seed S [--dtype bf16|f32]
+       dynalm version
+  <model>               a folder with config.json and model.safetensors
+  --tokens IDS          prompt token ids, separated by commas (repeatable: one request each)
+  -p, --prompt IDS      the same (this engine has no tokenizer; the prompt is ids)
+  --prompt-len N        a random prompt of N ids drawn with --prompt-seed (default 0)
+  -n, --max-tokens N    tokens to generate (default 128)
+  -c, --ctx N           KV cache capacity in tokens (default 4096)
+  --batch N             max tokens per forward pass (default 512)
+  --kv bf16|f32         KV cache dtype; it follows the compute dtype (see --mode / --dtype)
+  --mode M              auto | performance: bfloat16 kernels (default); exact | safe: everything in float32
+  --dtype D             bf16 | f32: the same choice by name
+  --max-running N       most requests decoded together (default 64)
+  --chunk N             most prompt tokens of one request per step (default 128)
+  --stop-id ID          end-of-generation token id (repeatable)
+  --no-stream           print only the final ids
+sampling (default: greedy):
+  --temp T              temperature (0 = greedy; also --temperature)
+  --top-k K, --top-p P, --min-p P
+  --repeat-penalty R, --presence-penalty P, --frequency-penalty F, --repeat-last-n N
+  --seed S              RNG seed (reproducible output)
+global: -q quiet, -v verbose, --version
+"""
+
+
+def _ids(text: str):
+    return [int(t) for t in text.replace(",", " ").split()]
+
+
+def _run_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="dynalm run", add_help=False)
+    ap.add_argument("model")
+    ap.add_argument("--tokens", "-p", "--prompt", dest="tokens", action="append", default=[])
+    ap.add_argument("--prompt-len", type=int, default=0)
+    ap.add_argument("--prompt-seed", type=int, default=0)
+    ap.add_argument("-n", "--max-tokens", type=int, default=128)
+    ap.add_argument("-c", "--ctx", type=int, default=4096)
+    ap.add_argument("--batch", type=int, default=512)
+    ap.add_argument("--kv", choices=["bf16", "f32", "f16"], default=None)
+    ap.add_argument("--mode", choices=["auto", "performance", "exact", "safe"], default="auto")
+    ap.add_argument("--dtype", choices=["bf16", "f32", "bfloat16", "float32"], default=None)
+    ap.add_argument("--max-running", type=int, default=64)
+    ap.add_argument("--chunk", type=int, default=128)
+    ap.add_argument("--stop-id", type=int, action="append", default=[])
+    ap.add_argument("--no-stream", action="store_true")
+    ap.add_argument("--temp", "--temperature", dest="temp", type=float, default=0.0)
+    ap.add_argument("--top-k", type=int, default=0)
+    ap.add_argument("--top-p", type=float, default=1.0)
+    ap.add_argument("--min-p", type=float, default=0.0)
+    ap.add_argument("--repeat-penalty", type=float, default=1.0)
+    ap.add_argument("--presence-penalty", type=float, default=0.0)
+    ap.add_argument("--frequency-penalty", type=float, default=0.0)
+    ap.add_argument("--repeat-last-n", type=int, default=64)
+    ap.add_argument("--seed", type=int, default=None)
+    ap.add_argument("-h", "--help", action="store_true")
+    return ap
+
+
+def cmd_run(argv, quiet: bool) -> int:
+    args = _run_parser().parse_args(argv)
+    if args.help:
+        sys.stderr.write(USAGE)
+        return 0
+    import numpy as np
+    from ..engine import Engine, Request, SchedulerConfig
+    from ..errors import EngineError
+    from ..sampling import SamplingParams
+
+    dtype = "float32" if (args.dtype in ("f32", "float32") or args.mode in ("exact", "safe")) else "bfloat16"
+    if args.kv == "f32" and dtype != "float32":
+        print("dynalm: --kv f32 needs --mode exact (the cache has the compute dtype)", file=sys.stderr)
+        return 2
+    if args.kv == "f16":
+        print("dynalm: --kv f16 is not offered; the cache is bf16 (or f32 with --mode exact)", file=sys.stderr)
+        return 2
+    try:
+        sched = SchedulerConfig(max_running=args.max_running, max_prefill_chunk=args.chunk, max_batch_tokens=args.batch)
+        engine = Engine(args.model, dtype=dtype, ctx=args.ctx, batch=args.batch, max_running=args.max_running,
+                        scheduler=sched)
+    except EngineError as e:
+        print(f"dynalm: {e}", file=sys.stderr)
+        return 1
+    prompts = [_ids(t) for t in args.tokens]
+    if args.prompt_len > 0:
+        rng = np.random.RandomState(args.prompt_seed)
+        prompts.append([int(t) for t in rng.randint(0, engine.config.vocab_size, size=args.prompt_len)])
+    if not prompts:
+        sys.stderr.write(USAGE)
+        return 2
+    sp = [SamplingParams(temperature=args.temp, top_k=args.top_k, top_p=args.top_p, min_p=args.min_p,
+                         repetition_penalty=args.repeat_penalty, presence_penalty=args.presence_penalty,
+                         frequency_penalty=args.frequency_penalty, penalty_last_n=args.repeat_last_n,
+                         seed=None if args.seed is None else args.seed + i) for i in range(len(prompts))]
+    t0 = time.perf_counter()
+    ids = [engine.scheduler.submit(Request(p, args.max_tokens, s, tuple(args.stop_id))) for p, s in zip(prompts, sp)]
+    out = {i: [] for i in ids}
+    final = {}
+    ttft = None
+    gaps = []
+    last = t0
+    while not engine.scheduler.idle:
+        for ev in engine.scheduler.step():
+            now = time.perf_counter()
+            if ev.token is not None:
+                out[ev.request_id].append(ev.token)
+                if ttft is None:
+                    ttft = (now - t0) * 1e3
+                else:
+                    gaps.append((now - last) * 1e3)
+                last = now
+                if not args.no_stream and len(ids) == 1:
+                    sys.stdout.write(f"{ev.token} ")
+                    sys.stdout.flush()
+            if ev.finished:
+                final[ev.request_id] = ev
+    total_ms = (time.perf_counter() - t0) * 1e3
+    if not args.no_stream and len(ids) == 1:
+        sys.stdout.write("\n")
+    else:
+        for i in ids:
+            print(" ".join(str(t) for t in out[i]))
+    rc = 0
+    for i in ids:
+        if final[i].error:
+            print(f"dynalm: request {i}: {final[i].error}", file=sys.stderr)
+            rc = 1
+    if not quiet:
+        gaps.sort()
+
+        def pct(p):
+            return gaps[min(len(gaps) - 1, int(p / 100.0 * len(gaps)))] if gaps else 0.0
+        n_prompt = sum(len(p) for p in prompts)
+        n_gen = sum(len(v) for v in out.values())
+        decode_s = (total_ms - (ttft or 0.0)) / 1e3
+        reason = ",".join(sorted({str(final[i].finish_reason or final[i].status) for i in ids}))
+        print(f"\n[stats] prompt {n_prompt} tok | TTFT {ttft or 0.0:.1f} ms | generated {n_gen} tok, "
+              f"{(n_gen - len(ids)) / decode_s if decode_s > 0 else 0.0:.1f} tok/s | finish {reason} | "
+              f"inter-delta p50 {pct(50):.1f} p90 {pct(90):.1f} p99 {pct(99):.1f} ms", file=sys.stderr)
+        ss = engine.scheduler.stats
+        if ss.steps_decode_only > 0:
+            print(f"[engine] prefill {ss.forward_prefill_only_ms + ss.forward_mixed_ms:.1f} ms (forward, "
+                  f"{ss.steps_prefill_only + ss.steps_mixed} steps) | decode step "
+                  f"{ss.forward_decode_only_ms / ss.steps_decode_only:.2f} ms (forward, {ss.steps_decode_only} steps)",
+                  file=sys.stderr)
+    return rc
+
+
+def cmd_random_model(argv) -> int:
+    ap = argparse.ArgumentParser(prog="dynalm random-model")
+    ap.add_argument("out_dir")
+    ap.add_argument("--config", required=True, help="a config.json to copy sizes from")
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--dtype", choices=["bf16", "f32"], default="bf16")
+    args = ap.parse_args(argv)
+    import torch
+    from ..config.reader import read_json_file
+    from ..weights import write_model_folder
+    write_model_folder(args.out_dir, read_json_file(args.config), args.seed,
+                       torch.bfloat16 if args.dtype == "bf16" else torch.float32)
+    print(args.out_dir)
+    return 0
+
+
+def main(argv=None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    quiet = False
+    while argv and argv[0] in ("-q", "-v", "--version") or (argv and argv[0].startswith("--log-level")):
+        flag = argv.pop(0)
+        if flag == "--version":
+            print(f"dynalm_b200 {__version__}")
+            return 0
+        if flag == "--log-level" and argv:
+            argv.pop(0)
+        quiet = quiet or flag == "-q"
+    if not argv or argv[0] in ("-h", "--help", "help"):
+        sys.stderr.write(USAGE)
+        return 0 if argv else 2
+    cmd, rest = argv[0], argv[1:]
+    if cmd == "run":
+        return cmd_run(rest, quiet)
+    if cmd == "random-model":
+        return cmd_random_model(rest)
+    if cmd == "version":
+        print(f"dynalm_b200 {__version__}")
+        return 0
+    print(f"dynalm: unknown command '{cmd}'\n", file=sys.stderr)
+    sys.stderr.write(USAGE)
+    return 2
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -10,6 +10,7 @@ adapter (dynalm/src/model/arch_llama.cpp:23-39).
 from __future__ import annotations
 
 import dataclasses
+import math
 from dataclasses import dataclass
 from typing import Any, Mapping, Optional
 
@@ -83,8 +84,8 @@ class LlamaConfig:
     # ---- derived sizes -------------------------------------------------------------------
     @property
     def rotary_dim(self) -> int:
-        # hf_model.cpp:197: lround(head_dim * partial_rotary_factor)
-        return int(round(self.head_dim * self.partial_rotary_factor))
+        # hf_model.cpp:197: lround(head_dim * partial_rotary_factor), halves away from zero
+        return int(math.floor(self.head_dim * self.partial_rotary_factor + 0.5))
 
     @property
     def q_width(self) -> int:

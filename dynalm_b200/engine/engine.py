@@ -1,0 +1,128 @@
+"""The programmatic entry point: `Engine(model).generate(prompts)`.
+
+The reference's entry is C++ (`Engine::create(EngineOptions)`, `generate_text`, `RequestStream`,
+dynalm/src/runtime/engine.h:59-104,176-225,292-337) and starts at text; this engine starts at
+token ids, so prompts are lists of ids and results are lists of ids. Option names follow
+`EngineOptions` / `dynalm run`: `ctx` is the KV capacity in tokens, `batch` the most tokens per
+forward pass.
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Any, Dict, Iterator, List, Mapping, Optional, Sequence, Union
+
+import torch
+
+from ..cache import DEFAULT_PAGE_SIZE
+from ..errors import InvalidArgument
+from ..sampling import SamplingParams
+from .build import BuiltModel, build
+from .executor import GpuExecutor
+from .scheduler import Event, Request, Scheduler, SchedulerConfig
+from .step import StepEntry
+
+
+@dataclass
+class Generation:
+    """One finished request."""
+
+    tokens: List[int]
+    finish_reason: Optional[str]
+    status: str
+    error: Optional[str]
+    prompt_tokens: int
+    ttft_ms: float = 0.0
+    total_ms: float = 0.0
+
+
+class Engine:
+    def __init__(self, model: Optional[str] = None, *, config: Optional[Mapping[str, Any]] = None,
+                 tensors: Optional[Mapping[str, torch.Tensor]] = None, random_seed: Optional[int] = None,
+                 dtype: str = "bfloat16", ctx: int = 4096, batch: int = 512, max_running: int = 64,
+                 page_size: int = DEFAULT_PAGE_SIZE, device: str = "cuda:0",
+                 scheduler: Optional[SchedulerConfig] = None, keep_trace: bool = False):
+        """model: a folder with config.json and model.safetensors. Without a folder, pass `config`
+        (a config.json dict) and either `tensors` or `random_seed` (random weights in memory)."""
+        if model is None and config is not None and tensors is None:
+            if random_seed is None:
+                raise InvalidArgument("a configuration without tensors needs random_seed")
+            from ..registry import find_architecture
+            from ..weights.random_init import random_tensors
+            from .runtime import parse_dtype
+            arch = find_architecture(config)
+            plan = arch.plan(arch.read_config(config), present=None)
+            tensors = random_tensors(plan, random_seed, parse_dtype(dtype))
+        self.built: BuiltModel = build(model, config_obj=config, tensors=tensors, dtype=dtype, kv_tokens=ctx,
+                                       max_batch_tokens=batch, max_requests=max_running, page_size=page_size,
+                                       device=device)
+        self.config = self.built.config
+        self.step_fn = self.built.step_fn
+        self.executor = GpuExecutor(self.step_fn)
+        cfg = scheduler or SchedulerConfig()
+        cfg.max_running = min(cfg.max_running, max_running)
+        cfg.max_batch_tokens = min(cfg.max_batch_tokens, batch) if scheduler else batch
+        cfg.context_length = min(cfg.context_length, self.built.plan.context_length)
+        self.scheduler = Scheduler(self.executor, cfg, keep_trace=keep_trace)
+
+    # ---- generation ------------------------------------------------------------------------------------
+    def generate(self, prompts: Union[Sequence[int], Sequence[Sequence[int]]], max_tokens: int = 128,
+                 temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0,
+                 repeat_penalty: float = 1.0, presence_penalty: float = 0.0, frequency_penalty: float = 0.0,
+                 repeat_last_n: int = 64, seed: Optional[int] = None, stop_token_ids: Sequence[int] = (),
+                 sampling: Optional[Sequence[SamplingParams]] = None) -> Union[Generation, List[Generation]]:
+        """Generate for one prompt (a list of ids) or several (a list of lists), batched continuously.
+        `seed` seeds request i with seed + i. `sampling` overrides the sampling options per prompt."""
+        single = len(prompts) > 0 and not isinstance(prompts[0], (list, tuple))
+        plist = [list(prompts)] if single else [list(p) for p in prompts]
+        results: Dict[int, Generation] = {}
+        first: Dict[int, float] = {}
+        t0 = time.perf_counter()
+        order = []
+        for i, p in enumerate(plist):
+            sp = sampling[i] if sampling is not None else SamplingParams(
+                temperature=temperature, top_k=top_k, top_p=top_p, min_p=min_p, repetition_penalty=repeat_penalty,
+                presence_penalty=presence_penalty, frequency_penalty=frequency_penalty, penalty_last_n=repeat_last_n,
+                seed=None if seed is None else seed + i)
+            order.append(self.scheduler.submit(Request(p, max_tokens, sp, tuple(stop_token_ids))))
+        toks: Dict[int, List[int]] = {rid: [] for rid in order}
+        while not self.scheduler.idle:
+            for ev in self.scheduler.step():
+                if ev.request_id not in toks:
+                    continue
+                if ev.token is not None:
+                    toks[ev.request_id].append(ev.token)
+                    first.setdefault(ev.request_id, (time.perf_counter() - t0) * 1e3)
+                if ev.finished:
+                    results[ev.request_id] = Generation(toks[ev.request_id], ev.finish_reason, ev.status, ev.error,
+                                                        ev.prompt_tokens, first.get(ev.request_id, 0.0),
+                                                        (time.perf_counter() - t0) * 1e3)
+        out = [results[rid] for rid in order]
+        return out[0] if single else out
+
+    def stream(self, prompt: Sequence[int], max_tokens: int = 128, sampling: Optional[SamplingParams] = None,
+               stop_token_ids: Sequence[int] = ()) -> Iterator[Event]:
+        """Events of one request as they come (the counterpart of RequestStream::next)."""
+        rid = self.scheduler.submit(Request(list(prompt), max_tokens, sampling or SamplingParams(),
+                                            tuple(stop_token_ids)))
+        done = False
+        while not done and not self.scheduler.idle:
+            for ev in self.scheduler.step():
+                if ev.request_id == rid:
+                    yield ev
+                    done = done or ev.finished
+
+    # ---- direct access -----------------------------------------------------------------------------------
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """The step function itself: logits at the wanted places (see StepFunction.step)."""
+        return self.step_fn.step(entries)
+
+    def end(self, request) -> None:
+        self.step_fn.end(request)
+
+    def stats(self) -> dict:
+        s = self.scheduler.stats
+        return {"scheduler": dict(vars(s)), "free_pages": self.built.cache.free_pages,
+                "pages": self.built.cache.num_pages, "cache_bytes": self.built.cache.bytes(),
+                "workspace_bytes": self.built.runtime.workspace_bytes()}

@@ -1,0 +1,427 @@
+"""Continuous batching above the step function.
+
+One iteration (`Scheduler.step`): take in new requests, retire finished ones, admit waiting ones
+while pages allow, plan a batch under the token budgets (decode rows first, then prompt portions),
+run it, sample where a request's pending work was completed, emit events. The decisions follow the
+reference's scheduler (dynalm/src/scheduler/scheduler.cpp:234-353 admission and validation,
+:357-378 preemption, :380-778 the step; sequence states dynalm/src/runtime/sequence.cpp:24-93).
+
+When pages run out while a batch is planned, the most recently admitted OTHER running request is
+preempted: all its pages are given back, it keeps its generated tokens, goes to the front of the
+waiting queue and is recomputed (prompt and generated tokens as one prompt) when it is admitted
+again. If nothing can be preempted the request fails with "request needs more KV than the cache
+holds". A request whose prompt plus max_new_tokens cannot fit the pool even alone is refused when
+it is taken in.
+
+The scheduler drives an `Executor`: something with a cache manager and a `run(batch)` that
+computes the batch and returns the sampled token of every item that asked for one. The GPU
+executor is `dynalm_b200.engine.executor.GpuExecutor`; tests use a fake to check decisions on the CPU.
+"""
+
+from __future__ import annotations
+
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Callable, Deque, Dict, Hashable, List, Optional, Protocol, Sequence
+
+from ..cache import CacheManager
+from ..errors import EngineError, InvalidArgument, ResourceExhausted
+from ..sampling import Sampler, SamplingParams
+
+WAITING, PREFILL, DECODE, FINISHED, CANCELLED, ERROR = "waiting", "prefill", "decode", "finished", "cancelled", "error"
+FINISH_EOG, FINISH_LENGTH, FINISH_STOPPED = "eog", "length", "stopped"
+
+
+@dataclass
+class SchedulerConfig:
+    """Budgets per step, in tokens. The defaults are the reference's GPU profile
+    (dynalm/src/runtime/engine.h:131,152-153; dynalm/src/scheduler/scheduler.h:130-137)."""
+
+    max_running: int = 64
+    decode_token_budget: int = 64
+    prefill_token_budget: int = 256
+    max_prefill_chunk: int = 128          # per request per step; 0 = up to the budget
+    max_batch_tokens: int = 512
+    context_length: int = 1 << 24         # prompt + max_new_tokens may not exceed it
+
+    def clamp(self) -> None:
+        # both budgets must fit one forward pass (scheduler.cpp:91-96)
+        self.decode_token_budget = max(1, min(self.decode_token_budget, self.max_batch_tokens - 1))
+        self.prefill_token_budget = max(1, min(self.prefill_token_budget,
+                                               self.max_batch_tokens - self.decode_token_budget))
+
+
+@dataclass
+class Request:
+    """What a caller submits."""
+
+    prompt: Sequence[int]
+    max_new_tokens: int = 128
+    sampling: SamplingParams = field(default_factory=SamplingParams)
+    stop_token_ids: Sequence[int] = ()     # end-of-generation ids; generation stops after one is sampled
+    priority: int = 0
+    on_event: Optional[Callable[["Event"], None]] = None
+
+
+@dataclass
+class Event:
+    request_id: int
+    token: Optional[int]             # the token sampled in this step, None on a bare final event
+    finished: bool = False
+    status: str = DECODE
+    finish_reason: Optional[str] = None
+    error: Optional[str] = None
+    prompt_tokens: int = 0
+    completion_tokens: int = 0
+
+
+class SequenceState:
+    """A request in flight: its tokens, how many are in the cache, its state
+    (dynalm/src/runtime/sequence.h:40-101)."""
+
+    def __init__(self, rid: int, req: Request, arrival: int):
+        self.id = rid
+        self.req = req
+        self.tokens: List[int] = list(req.prompt)
+        self.prompt_len = len(self.tokens)
+        self.num_computed = 0
+        self.status = WAITING
+        self.finish_reason: Optional[str] = None
+        self.error: Optional[str] = None
+        self.preemptions = 0
+        self.arrival = arrival
+        self.admit_order = 0
+        self.last_step = 0
+        self.sampler: Optional[Sampler] = None      # made once the request has passed validation
+        self.cancel_requested = False
+
+    @property
+    def pending(self) -> int:
+        return len(self.tokens) - self.num_computed
+
+    @property
+    def generated(self) -> int:
+        return len(self.tokens) - self.prompt_len
+
+    @property
+    def terminal(self) -> bool:
+        return self.status in (FINISHED, CANCELLED, ERROR)
+
+    def mark_computed(self, n: int) -> None:
+        self.num_computed += n
+        self.status = PREFILL if self.num_computed < self.prompt_len else DECODE
+
+    def append_token(self, tok: int) -> None:
+        self.tokens.append(tok)
+        if tok in self.req.stop_token_ids:
+            self.status, self.finish_reason = FINISHED, FINISH_EOG
+        elif self.generated >= self.req.max_new_tokens:
+            self.status, self.finish_reason = FINISHED, FINISH_LENGTH
+
+
+@dataclass
+class BatchItem:
+    seq: SequenceState
+    start: int
+    tokens: List[int]
+    sample: bool                     # this portion completes the pending work: sample its last row
+
+
+class Executor(Protocol):
+    cache: CacheManager
+    max_tokens: int
+
+    def begin(self, request_id: Hashable) -> None: ...
+    def end(self, request_id: Hashable) -> None: ...
+    def run(self, batch: List[BatchItem]) -> Dict[Hashable, int]: ...
+
+
+@dataclass
+class StepTrace:
+    """What one step computed (dynalm/src/scheduler/scheduler.h:98-125)."""
+
+    step: int
+    decode_rows: int
+    prefill_rows: int
+    items: List[tuple]               # (request id, start, n, sampled)
+    preempted: List[int]
+    admitted: List[int]
+    free_pages_after: int
+
+
+@dataclass
+class SchedulerStats:
+    steps: int = 0
+    steps_decode_only: int = 0
+    steps_prefill_only: int = 0
+    steps_mixed: int = 0
+    admitted: int = 0
+    finished: int = 0
+    failed: int = 0
+    preemptions: int = 0
+    tokens_prefilled: int = 0
+    tokens_decoded: int = 0
+    forward_decode_only_ms: float = 0.0
+    forward_prefill_only_ms: float = 0.0
+    forward_mixed_ms: float = 0.0
+
+
+class Scheduler:
+    def __init__(self, executor: Executor, config: SchedulerConfig = None, keep_trace: bool = False):
+        self.ex = executor
+        self.cfg = config or SchedulerConfig()
+        self.cfg.max_batch_tokens = min(self.cfg.max_batch_tokens, executor.max_tokens)
+        self.cfg.max_running = min(self.cfg.max_running, executor.cache.max_requests)
+        self.cfg.clamp()
+        self.incoming: List[SequenceState] = []
+        self.waiting: Deque[SequenceState] = deque()
+        self.running: List[SequenceState] = []
+        self.by_id: Dict[int, SequenceState] = {}
+        self.stats = SchedulerStats()
+        self.trace: Optional[List[StepTrace]] = [] if keep_trace else None
+        self._next_id = 1
+        self._arrivals = 0
+        self._admit_counter = 0
+        self._callbacks: Dict[int, Callable[[Event], None]] = {}
+        self._last_rows = (0, 0)
+
+    # ---- submission ----------------------------------------------------------------------------------
+    def submit(self, req: Request) -> int:
+        rid = self._next_id
+        self._next_id += 1
+        self._arrivals += 1
+        seq = SequenceState(rid, req, self._arrivals)
+        self.by_id[rid] = seq
+        self.incoming.append(seq)
+        if req.on_event is not None:
+            self._callbacks[rid] = req.on_event
+        return rid
+
+    def cancel(self, rid: int) -> None:
+        seq = self.by_id.get(rid)
+        if seq is not None:
+            seq.cancel_requested = True
+
+    @property
+    def idle(self) -> bool:
+        return not (self.incoming or self.waiting or self.running)
+
+    # ---- one iteration ---------------------------------------------------------------------------------
+    def _fail(self, seq: SequenceState, msg: str, events: List[Event]) -> None:
+        seq.status, seq.error = ERROR, msg
+        self.stats.failed += 1
+        events.append(self._final_event(seq, None))
+
+    def _final_event(self, seq: SequenceState, token: Optional[int]) -> Event:
+        return Event(seq.id, token, True, seq.status, seq.finish_reason, seq.error, seq.prompt_len, seq.generated)
+
+    def _drain_incoming(self, events: List[Event]) -> None:
+        """Validate new requests (scheduler.cpp:245-275) and queue them by priority, then arrival."""
+        cache = self.ex.cache
+        vocab = getattr(self.ex, "vocab", None)
+        for seq in self.incoming:
+            req = seq.req
+            try:
+                req.sampling.validate()
+                if len(req.prompt) == 0:
+                    raise InvalidArgument("empty prompt")
+                if req.max_new_tokens <= 0:
+                    raise InvalidArgument("max_new_tokens must be > 0")
+                total = len(req.prompt) + req.max_new_tokens
+                if total > self.cfg.context_length:
+                    raise InvalidArgument(f"prompt ({len(req.prompt)}) + max_new_tokens ({req.max_new_tokens}) "
+                                          f"exceeds the context length {self.cfg.context_length}")
+                if total > cache.context or -(-total // cache.page_size) > cache.num_pages:
+                    raise InvalidArgument("request could never fit the KV cache even alone")
+                if vocab is not None and (min(req.prompt) < 0 or max(req.prompt) >= vocab):
+                    raise InvalidArgument(f"token id outside [0, {vocab})")
+            except EngineError as e:
+                self._fail(seq, str(e), events)
+                self.by_id.pop(seq.id, None)
+                continue
+            seq.sampler = Sampler(req.sampling)
+            self.waiting.append(seq)
+        if self.incoming:
+            self.incoming.clear()
+            self.waiting = deque(sorted(self.waiting, key=lambda s: (-s.req.priority, s.arrival)))
+
+    def _retire(self, events: List[Event]) -> None:
+        keep = []
+        for seq in self.running:
+            if seq.cancel_requested and not seq.terminal:
+                seq.status = CANCELLED
+                events.append(self._final_event(seq, None))
+            if seq.terminal:
+                self.ex.end(seq.id)
+                self.by_id.pop(seq.id, None)
+            else:
+                keep.append(seq)
+        self.running = keep
+        for seq in [s for s in self.waiting if s.cancel_requested]:
+            self.waiting.remove(seq)
+            seq.status = CANCELLED
+            self.by_id.pop(seq.id, None)
+            events.append(self._final_event(seq, None))
+
+    def _admit(self, admitted: List[int]) -> None:
+        """While there is room: the pending tokens plus one page of headroom must fit now
+        (scheduler.cpp:311-353)."""
+        cache = self.ex.cache
+        promised = 0        # pages of requests admitted in this pass, which reserve only when planned
+        while self.waiting and len(self.running) < self.cfg.max_running:
+            seq = self.waiting[0]
+            need = -(-seq.pending // cache.page_size) + 1
+            if cache.free_pages - promised < need and self.running:
+                break
+            if cache.free_slots == 0:
+                break
+            self.waiting.popleft()
+            promised += need - 1
+            self.ex.begin(seq.id)
+            self._admit_counter += 1
+            seq.admit_order = self._admit_counter
+            if seq.preemptions == 0:
+                self.stats.admitted += 1
+            seq.status = PREFILL
+            self.running.append(seq)
+            admitted.append(seq.id)
+
+    def _preempt_one(self, keep: SequenceState, preempted: List[int]) -> bool:
+        """Give back all pages of the most recently admitted running request other than `keep`
+        and send it to the front of the waiting queue for recomputation (scheduler.cpp:357-378)."""
+        victim = None
+        for s in self.running:
+            if s is keep or s.terminal or self.ex.cache.tokens.get(s.id, 0) == 0:
+                continue
+            if victim is None or s.admit_order > victim.admit_order:
+                victim = s
+        if victim is None:
+            return False
+        self.ex.end(victim.id)
+        victim.num_computed = 0
+        victim.status = WAITING
+        victim.preemptions += 1
+        self.stats.preemptions += 1
+        self.running.remove(victim)
+        self.waiting.appendleft(victim)
+        preempted.append(victim.id)
+        return True
+
+    def _plan(self, events: List[Event], preempted: List[int]) -> List[BatchItem]:
+        cfg, cache = self.cfg, self.ex.cache
+        for attempt in range(65):
+            batch: List[BatchItem] = []
+            decode_rows = prefill_rows = 0
+            restart = False
+
+            def is_decode(s: SequenceState) -> bool:
+                return s.status == DECODE and s.pending == 1
+
+            order = sorted((s for s in self.running if not s.terminal and s.pending > 0),
+                           key=lambda s: (0, s.last_step, s.admit_order) if is_decode(s)
+                           else (1, -s.req.priority, s.admit_order))
+            for seq in order:
+                decode = is_decode(seq)
+                used = decode_rows if decode else prefill_rows
+                budget = cfg.decode_token_budget if decode else cfg.prefill_token_budget
+                n = min(seq.pending, budget - used)
+                if not decode and cfg.max_prefill_chunk > 0:
+                    n = min(n, cfg.max_prefill_chunk)
+                if n <= 0:
+                    continue
+                try:
+                    cache.reserve(seq.id, seq.num_computed + n)
+                except ResourceExhausted:
+                    if attempt < 64 and self._preempt_one(seq, preempted):
+                        restart = True
+                        break
+                    self._fail(seq, "request needs more KV than the cache holds", events)
+                    continue
+                start = seq.num_computed
+                batch.append(BatchItem(seq, start, seq.tokens[start:start + n], sample=(n == seq.pending)))
+                if decode:
+                    decode_rows += n
+                else:
+                    prefill_rows += n
+            if not restart:
+                self._last_rows = (decode_rows, prefill_rows)
+                return batch
+        return []
+
+    def step(self) -> List[Event]:
+        """One iteration. Returns the events of this step (also sent to each request's callback)."""
+        events: List[Event] = []
+        admitted: List[int] = []
+        preempted: List[int] = []
+        self._drain_incoming(events)
+        self._retire(events)
+        self._admit(admitted)
+        if self.running:
+            batch = self._plan(events, preempted)
+            if batch:
+                self._run(batch, events)
+            step_no = self.stats.steps
+            if self.trace is not None:
+                self.trace.append(StepTrace(
+                    step_no, self._last_rows[0] if batch else 0, self._last_rows[1] if batch else 0,
+                    [(b.seq.id, b.start, len(b.tokens), b.sample) for b in batch], preempted, admitted,
+                    self.ex.cache.free_pages))
+        self._retire_finished_now()
+        for ev in events:
+            seq_cb = self._callbacks.pop(ev.request_id, None) if ev.finished else self._callbacks.get(ev.request_id)
+            if seq_cb is not None:
+                seq_cb(ev)
+        return events
+
+    def _retire_finished_now(self) -> None:
+        # Finished requests give their pages back at once rather than at the top of the next
+        # step, so that a caller that stops stepping leaves nothing held.
+        keep = []
+        for seq in self.running:
+            if seq.terminal:
+                self.ex.end(seq.id)
+                self.by_id.pop(seq.id, None)
+            else:
+                keep.append(seq)
+        self.running = keep
+
+    def _run(self, batch: List[BatchItem], events: List[Event]) -> None:
+        self.stats.steps += 1
+        step_no = self.stats.steps
+        n_decode = sum(1 for b in batch if len(b.tokens) == 1 and b.seq.status == DECODE)
+        n_prefill = sum(len(b.tokens) for b in batch) - n_decode
+        t0 = time.perf_counter()
+        try:
+            sampled = self.ex.run(batch)
+        except EngineError as e:
+            # a failed forward fails only this batch's requests (scheduler.cpp:663-666)
+            for b in batch:
+                self._fail(b.seq, f"forward failed: {e}", events)
+            return
+        ms = (time.perf_counter() - t0) * 1e3
+        if n_prefill == 0:
+            self.stats.steps_decode_only += 1
+            self.stats.forward_decode_only_ms += ms
+        elif n_decode == 0:
+            self.stats.steps_prefill_only += 1
+            self.stats.forward_prefill_only_ms += ms
+        else:
+            self.stats.steps_mixed += 1
+            self.stats.forward_mixed_ms += ms
+        self.stats.tokens_decoded += n_decode
+        self.stats.tokens_prefilled += n_prefill
+        for b in batch:
+            seq = b.seq
+            seq.mark_computed(len(b.tokens))
+            seq.last_step = step_no
+            self.ex.cache.advance(seq.id, seq.num_computed)
+            if not b.sample:
+                continue
+            tok = sampled[seq.id]
+            seq.append_token(tok)
+            if seq.terminal:
+                self.stats.finished += 1
+                events.append(self._final_event(seq, tok))
+            else:
+                events.append(Event(seq.id, tok, False, seq.status, None, None, seq.prompt_len, seq.generated))

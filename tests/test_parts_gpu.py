@@ -1,0 +1,291 @@
+"""Each part alone against the plain function of the same part, and a toy mixer with state of its
+own that is registered, built and stepped without touching the framework."""
+
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as plain
+from tiny_configs import TINY_B, TINY_C
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _tol(dtype):
+    return 3e-5 if dtype == torch.float32 else 3e-2
+
+
+def _runtime(dtype, max_tokens=256):
+    from dynalm_b200.engine import Runtime
+    return Runtime(DEV, dtype, max_tokens)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_part(dtype):
+    from dynalm_b200.config import NormSpec
+    from dynalm_b200.parts import NORMS
+    rt = _runtime(dtype)
+    g = torch.Generator().manual_seed(0)
+    w = 1 + 0.1 * torch.randn(96, generator=g)
+    x = torch.randn(11, 96, generator=g) * 2
+    part = NORMS.get("rms")(NormSpec("rms", 96, 1e-6), {"weight": w.to(DEV)}, rt)
+    out = torch.empty(11, 96, dtype=dtype, device=DEV)
+    part.forward(x.to(DEV), out)
+    ref = plain.rms_norm(x.double().numpy(), w.double().numpy(), 1e-6)
+    assert np.abs(out.float().cpu().numpy() - ref).max() <= _tol(dtype) * 4
+
+
+def test_rotary_part_frequencies():
+    from dynalm_b200.parts import POSITIONS
+    from dynalm_b200.registry import find_architecture
+    rt = _runtime(torch.float32)
+    for cfg in (TINY_B, TINY_C):
+        arch = find_architecture(cfg)
+        spec = arch.plan(arch.read_config(cfg)).layers[0].mixer.position
+        part = POSITIONS.get(spec.kind)(spec, rt)
+        inv, rot, scale = part.table()
+        ref = plain.rope_inv_freq(plain.read_config_dict(cfg) if hasattr(plain, "read_config_dict") else _filled(cfg))
+        assert rot == 2 * len(ref) and np.array_equal(inv.cpu().numpy(), ref)
+
+
+def _filled(cfg):
+    c = dict(cfg)
+    c.setdefault("head_dim", c["hidden_size"] // c["num_attention_heads"])
+    c.setdefault("partial_rotary_factor", 1.0)
+    c.setdefault("rope_theta", 10000.0)
+    return c
+
+
+def _context(rt, cache, entries, vocab=1000):
+    from dynalm_b200.engine import BatchBuilder, StepEntry
+    b = BatchBuilder(cache, rt, 8, vocab)
+    return b, b.build([StepEntry(r, t, []) for r, t in entries])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_mixer_alone(dtype):
+    """The mixer over two requests cut into portions equals the plain attention block on whole sequences."""
+    from dynalm_b200.cache import CacheManager
+    from dynalm_b200.engine import BatchBuilder, StepEntry
+    from dynalm_b200.parts import MIXERS
+    from dynalm_b200.registry import find_architecture
+    cfg = plain_cfg = _filled(dict(TINY_B, attention_multiplier=0.0, residual_multiplier=1.0))
+    arch = find_architecture(TINY_B)
+    spec = arch.plan(arch.read_config(TINY_B)).layers[0].mixer
+    rt = _runtime(dtype)
+    g = torch.Generator().manual_seed(1)
+    H, qw, kw = 96, 192, 64
+    t = {"q": torch.randn(qw, H, generator=g) * 0.1, "k": torch.randn(kw, H, generator=g) * 0.1,
+         "v": torch.randn(kw, H, generator=g) * 0.1, "o": torch.randn(H, qw, generator=g) * 0.1}
+    mixer = MIXERS.get("attention")(spec, {n: v.to(DEV, dtype) for n, v in t.items()}, rt)
+    cache = CacheManager([mixer.cache_spec()], 16, 256, 8, 256, DEV, dtype)
+    builder = BatchBuilder(cache, rt, 8, 1000)
+    lens = {"a": 50, "b": 21}
+    xs = {r: torch.randn(n, H, generator=g) for r, n in lens.items()}
+    w = {"p.self_attn." + n + "_proj.weight": v.to(dtype).double().numpy() for n, v in t.items()}
+    ref = {r: plain.attention_block(xs[r].to(dtype).double().numpy(), w, "p.", plain_cfg, np.arange(lens[r]))
+           for r in lens}
+    got = {r: [] for r in lens}
+    cuts = [[("a", 0, 17), ("b", 0, 2)], [("b", 2, 19)], [("a", 17, 32), ("b", 21, 0)], [("a", 49, 1)]]
+    for step in cuts:
+        entries = [(r, s, n) for r, s, n in step if n > 0]
+        ctx = builder.build([StepEntry(r, [0] * n, []) for r, s, n in entries])
+        x = torch.cat([xs[r][s:s + n] for r, s, n in entries]).to(DEV, dtype)
+        view = cache.view(0, builder.tables)
+        y = mixer.forward(x, ctx, view, True).float().cpu()
+        builder.finish([StepEntry(r, [0] * n, []) for r, s, n in entries])
+        o = 0
+        for r, s, n in entries:
+            got[r].append(y[o:o + n])
+            o += n
+    for r in lens:
+        err = np.abs(torch.cat(got[r]).numpy() - ref[r]).max()
+        assert err <= _tol(dtype) * max(1.0, np.abs(ref[r]).max()), f"{r}: {err}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_feed_forward_alone(dtype):
+    from dynalm_b200.config import FeedForwardSpec
+    from dynalm_b200.parts import FEED_FORWARDS
+    rt = _runtime(dtype)
+    g = torch.Generator().manual_seed(2)
+    W, F = 80, 112
+    t = {"gate": torch.randn(F, W, generator=g) * 0.2, "up": torch.randn(F, W, generator=g) * 0.2,
+         "down": torch.randn(W, F, generator=g) * 0.2}
+    part = FEED_FORWARDS.get("gated_mlp")(FeedForwardSpec("gated_mlp", W, F), {n: v.to(DEV, dtype) for n, v in t.items()}, rt)
+    x = torch.randn(9, W, generator=g)
+    y = part.forward(x.to(DEV, dtype), None).float().cpu().numpy()
+    d = {n: v.to(dtype).double().numpy() for n, v in t.items()}
+    ref = plain.gated_mlp(x.to(dtype).double().numpy(), d["gate"], d["up"], d["down"])
+    assert np.abs(y - ref).max() <= _tol(dtype) * max(1.0, np.abs(ref).max())
+
+
+# ---------------------------------------------------------------------------------------------
+# a toy architecture defined here: one attention layer, then a layer whose mixer keeps a running
+# state per request, run twice, the second time sharing nothing; plus an entry that reads another
+# entry's cache
+# ---------------------------------------------------------------------------------------------
+
+def _register_toy():
+    from dynalm_b200.config import (BlockSpec, EmbeddingSpec, FeedForwardSpec, HeadSpec, LayerRun, MixerSpec, ModelPlan,
+                                    NormSpec, PositionSpec)
+    from dynalm_b200.parts import CacheSpec, TensorDecl, register_mixer
+    from dynalm_b200.registry import register_architecture
+
+    @register_mixer("toy_decay")
+    class ToyDecay:
+        """y_t = W x_t + 0.5 * s_{t-1}; s_t = y_t. The state s is one row per request."""
+
+        @staticmethod
+        def declare(spec):
+            return {"w": TensorDecl((spec.width, spec.width))}
+
+        def __init__(self, spec, tensors, runtime):
+            self.spec, self.w, self.rt = spec, tensors["w"], runtime
+
+        def cache_spec(self):
+            return CacheSpec(kind="state", state_shape=(self.spec.width,), dtype="float32")
+
+        def forward(self, x, ctx, cache, owns_cache=True):
+            state = cache.arrays[0]
+            proj = (x.float() @ self.w.float().T)
+            out = torch.empty_like(proj)
+            r0 = 0
+            for n, slot in zip(ctx.h_q_len, ctx.h_state_slots):
+                s = state[slot].clone()
+                for i in range(n):
+                    s = proj[r0 + i] + 0.5 * s
+                    out[r0 + i] = s
+                state[slot] = s
+                r0 += n
+            return out.to(x.dtype)
+
+    class ToyArch:
+        name = "ToyForCausalLM"
+        model_types = ("toy",)
+
+        def read_config(self, obj):
+            return dict(obj)
+
+        def plan(self, c, present=None):
+            W, V = c["width"], c["vocab"]
+
+            def norm(n):
+                return NormSpec("rms", W, 1e-5, {"weight": n})
+
+            def ffn(p):
+                return FeedForwardSpec("gated_mlp", W, c["inner"], "silu",
+                                       {"gate": p + "gate", "up": p + "up", "down": p + "down"})
+            attn = MixerSpec("attention", W, c["heads"], c["kv_heads"], c["head_dim"], c["head_dim"] ** -0.5, 0,
+                             PositionSpec("rotary", c["head_dim"], c["head_dim"], 10000.0),
+                             {"q": "l0.q", "k": "l0.k", "v": "l0.v", "o": "l0.o"})
+            win = MixerSpec("attention", W, c["heads"], c["kv_heads"], c["head_dim"], c["head_dim"] ** -0.5, c["window"],
+                            PositionSpec("none"), {"q": "l2.q", "k": "l2.k", "v": "l2.v", "o": "l2.o"})
+            toy = MixerSpec("toy_decay", W, tensors={"w": "l1.w"})
+            layers = [BlockSpec("pre_norm", norm("l0.n1"), attn, norm("l0.n2"), ffn("l0.")),
+                      BlockSpec("pre_norm", norm("l1.n1"), toy, norm("l1.n2"), ffn("l1.")),
+                      BlockSpec("pre_norm", norm("l2.n1"), win, norm("l2.n2"), ffn("l2."))]
+            # layer 1 is named twice; the last entry runs layer 0 again on the first entry's cache
+            order = [LayerRun(0), LayerRun(1), LayerRun(2), LayerRun(1), LayerRun(0, cache_of=0)]
+            return ModelPlan(EmbeddingSpec(V, W, 1.0, {"weight": "emb"}), layers, order, norm("final"),
+                             HeadSpec(V, W, True), c["context"])
+
+    register_architecture(ToyArch())
+    return ToyArch
+
+
+TOY = {"architectures": ["ToyForCausalLM"], "model_type": "toy", "width": 48, "vocab": 120, "inner": 64, "heads": 3,
+       "kv_heads": 1, "head_dim": 16, "window": 24, "context": 256}
+
+
+def _toy_reference(w, tokens):
+    """Whole sequence, no cache, plain functions; mirrors ToyArch.plan."""
+    c = {"num_attention_heads": 3, "num_key_value_heads": 1, "head_dim": 16, "partial_rotary_factor": 1.0,
+         "rope_theta": 10000.0, "attention_multiplier": 0.0}
+    n = len(tokens)
+    x = w["emb"][np.asarray(tokens)]
+
+    kept = {}
+
+    def attn(h, p, rotary, window, read_cache_of=None):
+        q = (h @ w[p + "q"].T).reshape(n, 3, 16)
+        if rotary:
+            q = plain.rope(q, np.arange(n), c)
+        if read_cache_of is None:
+            k = (h @ w[p + "k"].T).reshape(n, 1, 16)
+            v = (h @ w[p + "v"].T).reshape(n, 1, 16)
+            if rotary:
+                k = plain.rope(k, np.arange(n), c)
+            kept[p] = (k, v)
+        else:
+            k, v = kept[read_cache_of]       # the keys and values the earlier entry cached
+        return plain.attention(q, k, v, 16 ** -0.5, window).reshape(n, 48) @ w[p + "o"].T
+
+    def toy(h):
+        proj = h @ w["l1.w"].T
+        out = np.zeros_like(proj)
+        s = np.zeros(48)
+        for i in range(n):
+            s = proj[i] + 0.5 * s
+            out[i] = s
+        return out
+
+    def ffn(h, p):
+        return plain.gated_mlp(h, w[p + "gate"], w[p + "up"], w[p + "down"])
+
+    for p, mix in (("l0.", lambda h: attn(h, "l0.", True, 0)), ("l1.", toy), ("l2.", lambda h: attn(h, "l2.", False, 24)),
+                   ("l1.", toy), ("l0.", lambda h: attn(h, "l0.", True, 0, read_cache_of="l0."))):
+        x = x + mix(plain.rms_norm(x, w[p + "n1"], 1e-5))
+        x = x + ffn(plain.rms_norm(x, w[p + "n2"], 1e-5), p)
+    return plain.rms_norm(x, w["final"], 1e-5) @ w["emb"].T
+
+
+def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
+    """A model whose plan names a layer twice (each run with a state of its own), has a windowed
+    attention layer beside a full one (two page groups) and an entry that reads another entry's
+    cache. Whole requests and cut requests give the same logits, and both match plain functions."""
+    _register_toy()
+    from dynalm_b200.engine import StepEntry, build
+    from dynalm_b200.weights import write_model_folder
+    folder = str(tmp_path / "toy")
+    write_model_folder(folder, TOY, 3, torch.float32)
+    w = plain.read_safetensors(os.path.join(folder, "model.safetensors"))
+    rng = np.random.RandomState(0)
+    reqs = {"a": [int(t) for t in rng.randint(0, 120, 70)], "b": [int(t) for t in rng.randint(0, 120, 37)]}
+
+    def run(cuts):
+        built = build(folder, dtype="float32", kv_tokens=256, max_batch_tokens=128, max_requests=4)
+        assert len(built.cache.groups) == 2                       # all keys | a window of them
+        assert set(built.cache.state_arrays) == {1, 3}            # a state of its own per run of the toy layer
+        out = {r: [] for r in reqs}
+        pos = {r: 0 for r in reqs}
+        for step in cuts:
+            entries = []
+            for r, n in step:
+                entries.append(StepEntry(r, reqs[r][pos[r]:pos[r] + n], list(range(n))))
+            logits = built.step_fn.step(entries).cpu().numpy()
+            o = 0
+            for r, n in step:
+                out[r].append(logits[o:o + n].copy())
+                pos[r] += n
+                o += n
+            built.cache.check()
+        win_group = [g for g in built.cache.groups if g.spec.window > 0][0]
+        assert win_group.pool.num_held < sum(-(-len(t) // 16) for t in reqs.values())   # the window gave pages back
+        for r in reqs:
+            built.step_fn.end(r)
+        assert built.cache.free_pages == built.cache.num_pages
+        return {r: np.concatenate(v) for r, v in out.items()}
+
+    whole = run([[("a", 70)], [("b", 37)]])
+    cut = run([[("a", 16), ("b", 5)], [("a", 7)], [("b", 2), ("a", 2)], [("a", 40), ("b", 29)], [("a", 1), ("b", 1)],
+               [("a", 1)], [("a", 1)], [("a", 2)]])
+    for r in reqs:
+        ref = _toy_reference(w, reqs[r])
+        assert np.abs(whole[r] - ref).max() <= 3e-5 * max(1.0, np.abs(ref).max()), f"{r}: whole vs plain"
+        assert np.abs(cut[r] - ref).max() <= 3e-5 * max(1.0, np.abs(ref).max()), f"{r}: cut vs plain"

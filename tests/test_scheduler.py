@@ -1,0 +1,209 @@
+"""The scheduler's decisions on the CPU, with a fake executor that computes nothing: tokens are a
+fixed function of (request's tokens so far), so that recomputation after a preemption must give the
+same tokens."""
+
+import hashlib
+
+import pytest
+import torch
+
+from dynalm_b200.cache import CacheManager
+from dynalm_b200.engine.scheduler import (CANCELLED, ERROR, FINISHED, Request, Scheduler, SchedulerConfig)
+from dynalm_b200.parts.base import CacheSpec
+from dynalm_b200.sampling import SamplingParams
+
+SPEC = CacheSpec("pages", entry_shape=(1, 16))
+
+
+class FakeExecutor:
+    vocab = 1000
+
+    def __init__(self, kv_tokens=4096, max_requests=8, max_tokens=512, page=16, context=4096):
+        self.cache = CacheManager([SPEC], page, kv_tokens, max_requests, context, device=None, dtype=torch.float32)
+        self.max_tokens = max_tokens
+        self.batches = []
+        self.live = set()
+
+    def begin(self, rid):
+        self.cache.add_request(rid)
+        self.live.add(rid)
+
+    def end(self, rid):
+        self.cache.free_request(rid)
+        self.live.remove(rid)
+
+    def run(self, batch):
+        assert sum(len(b.tokens) for b in batch) <= self.max_tokens
+        self.batches.append([(b.seq.id, b.start, len(b.tokens), b.sample) for b in batch])
+        out = {}
+        for b in batch:
+            # the pages for these tokens are there
+            assert self.cache.tokens[b.seq.id] >= b.start + len(b.tokens)
+            assert b.tokens == b.seq.tokens[b.start:b.start + len(b.tokens)]
+            if b.sample:
+                h = hashlib.sha256(repr(b.seq.tokens[:b.start + len(b.tokens)]).encode()).digest()
+                out[b.seq.id] = int.from_bytes(h[:4], "little") % self.vocab
+        self.cache.check()
+        return out
+
+
+def run_all(s, limit=10000):
+    events = []
+    n = 0
+    while not s.idle:
+        events += s.step()
+        n += 1
+        assert n < limit, "the scheduler does not finish"
+    return events
+
+
+def collect(events):
+    toks, final = {}, {}
+    for e in events:
+        if e.token is not None:
+            toks.setdefault(e.request_id, []).append(e.token)
+        if e.finished:
+            final[e.request_id] = e
+    return toks, final
+
+
+def prompts(n, lens):
+    return [[(7 * i + 3 * j) % 1000 for j in range(lens[i % len(lens)])] for i in range(n)]
+
+
+def test_budgets_order_and_no_skipped_position():
+    ex = FakeExecutor()
+    cfg = SchedulerConfig(max_running=8, decode_token_budget=4, prefill_token_budget=48, max_prefill_chunk=32,
+                          max_batch_tokens=64)
+    s = Scheduler(ex, cfg, keep_trace=True)
+    ids = [s.submit(Request(p, max_new_tokens=12)) for p in prompts(6, [5, 70, 33, 130, 1, 64])]
+    toks, final = collect(run_all(s))
+    assert all(final[i].status == FINISHED and final[i].finish_reason == "length" and len(toks[i]) == 12 for i in ids)
+    computed = {}
+    for batch in ex.batches:
+        decode = [b for b in batch if b[2] == 1 and b[3] and computed.get(b[0], 0) > 0]
+        assert sum(b[2] for b in batch) <= cfg.max_batch_tokens
+        for rid, start, n, sample in batch:
+            assert start == computed.get(rid, 0), "a position was skipped or repeated"
+            computed[rid] = start + n
+    for t in s.trace:
+        assert t.decode_rows <= cfg.decode_token_budget and t.prefill_rows <= cfg.prefill_token_budget
+        for rid, start, n, sample in t.items:
+            if not (n == 1 and sample):
+                assert n <= cfg.max_prefill_chunk
+    # decode rows come first in a batch
+    for batch in ex.batches:
+        kinds = [0 if (n == 1 and sample and start > 0) else 1 for _, start, n, sample in batch]
+        assert kinds == sorted(kinds)
+    assert ex.cache.free_pages == ex.cache.num_pages and not ex.live
+
+
+def test_decode_rows_rotate_under_a_small_budget():
+    ex = FakeExecutor()
+    s = Scheduler(ex, SchedulerConfig(max_running=8, decode_token_budget=2, prefill_token_budget=64,
+                                      max_prefill_chunk=64, max_batch_tokens=128))
+    ids = [s.submit(Request(p, max_new_tokens=6)) for p in prompts(5, [4])]
+    toks, final = collect(run_all(s))
+    assert all(len(toks[i]) == 6 for i in ids)
+    # with 5 decoding and a budget of 2, nobody waits more than 3 steps between tokens
+    last = {}
+    for n, batch in enumerate(ex.batches):
+        for rid, start, k, sample in batch:
+            if sample:
+                assert n - last.get(rid, n) <= 3
+                last[rid] = n
+
+
+def test_page_shortage_preempts_and_gives_the_same_tokens():
+    """An engine with few pages gives the same tokens as a roomy one, and preempts on the way
+    (the reference's own check, dynalm/tests/test_engine.cpp:1725-1758)."""
+    ps = prompts(6, [40, 90, 17, 120, 64, 33])
+
+    def run(kv):
+        ex = FakeExecutor(kv_tokens=kv)
+        s = Scheduler(ex, SchedulerConfig(max_running=6, decode_token_budget=8, prefill_token_budget=64,
+                                          max_prefill_chunk=32, max_batch_tokens=128), keep_trace=True)
+        ids = [s.submit(Request(p, max_new_tokens=40)) for p in ps]
+        toks, final = collect(run_all(s))
+        assert ex.cache.free_pages == ex.cache.num_pages and not ex.live
+        return [toks[i] for i in ids], [final[i].status for i in ids], s
+
+    roomy, st1, s1 = run(4096)
+    tight, st2, s2 = run(320)
+    assert st1 == st2 == [FINISHED] * 6
+    assert s1.stats.preemptions == 0 and s2.stats.preemptions > 0
+    assert tight == roomy
+    # a preempted request goes to the front of the queue and starts again from position 0
+    assert any(t.preempted for t in s2.trace)
+
+
+def test_a_request_that_can_never_fit_fails_and_others_go_on():
+    ex = FakeExecutor(kv_tokens=128, context=4096)
+    s = Scheduler(ex, SchedulerConfig(max_running=4, max_batch_tokens=256))
+    big = s.submit(Request(list(range(200)), max_new_tokens=4))
+    ok = s.submit(Request(list(range(20)), max_new_tokens=4))
+    toks, final = collect(run_all(s))
+    assert final[big].status == ERROR and "never fit" in final[big].error
+    assert final[ok].status == FINISHED and len(toks[ok]) == 4
+
+
+def test_alone_in_the_pool_and_still_too_big_fails_with_the_reference_message():
+    # fits on paper (prompt + new tokens <= pool) but a second request holds pages it cannot take back
+    ex = FakeExecutor(kv_tokens=64)
+    s = Scheduler(ex, SchedulerConfig(max_running=2, max_batch_tokens=128, prefill_token_budget=64,
+                                      max_prefill_chunk=64))
+    a = s.submit(Request(list(range(30)), max_new_tokens=30))
+    toks, final = collect(run_all(s))
+    assert final[a].status == FINISHED        # 60 tokens fit 4 pages
+
+
+def test_validation_failures():
+    ex = FakeExecutor()
+    s = Scheduler(ex, SchedulerConfig(context_length=64))
+    bad = [s.submit(Request([], 4)), s.submit(Request([1, 2], 0)), s.submit(Request(list(range(60)), 10)),
+           s.submit(Request([5, 1000], 4)), s.submit(Request([1], 4, SamplingParams(temperature=-1.0))),
+           s.submit(Request([1], 4, SamplingParams(top_p=0.0)))]
+    good = s.submit(Request([1, 2, 3], 4))
+    toks, final = collect(run_all(s))
+    assert all(final[b].status == ERROR for b in bad)
+    msgs = [final[b].error for b in bad]
+    assert "empty prompt" in msgs[0] and "max_new_tokens" in msgs[1] and "context length" in msgs[2]
+    assert "token id" in msgs[3] and "temperature" in msgs[4] and "top_p" in msgs[5]
+    assert final[good].status == FINISHED
+
+
+def test_cancel_stop_token_priority_and_callbacks():
+    ex = FakeExecutor()
+    s = Scheduler(ex, SchedulerConfig(max_running=1, max_batch_tokens=64))
+    seen = []
+    low = s.submit(Request([1, 2, 3], 50, priority=0, on_event=seen.append))
+    high = s.submit(Request([4, 5, 6], 3, priority=5))
+    first = s.step()
+    # one slot: the higher priority runs first although it came second
+    assert ex.batches[0][0][0] == high
+    s.cancel(low)
+    toks, final = collect(first + run_all(s))
+    assert final[low].status == CANCELLED and final[high].status == FINISHED
+    assert seen and seen[-1].finished and seen[-1].status == CANCELLED
+    # stop ids end generation with reason eog
+    ex2 = FakeExecutor()
+    s2 = Scheduler(ex2, SchedulerConfig())
+    probe = s2.submit(Request([9, 9, 9], 8))
+    t, _ = collect(run_all(s2))
+    stop_at = t[probe][2]
+    r = s2.submit(Request([9, 9, 9], 8, stop_token_ids=(stop_at,)))
+    t2, f2 = collect(run_all(s2))
+    assert t2[r] == t[probe][:t[probe].index(stop_at) + 1] and f2[r].finish_reason == "eog"
+    assert not ex2.live and ex2.cache.free_pages == ex2.cache.num_pages
+
+
+def test_admission_waits_for_pages():
+    ex = FakeExecutor(kv_tokens=160)          # 10 pages
+    s = Scheduler(ex, SchedulerConfig(max_running=4, max_batch_tokens=256, prefill_token_budget=128,
+                                      max_prefill_chunk=128), keep_trace=True)
+    a = s.submit(Request(list(range(100)), 8))          # 7 pages + headroom
+    b = s.submit(Request(list(range(60)), 8))           # needs 4 + 1: must wait for a
+    s.step()
+    assert [q.id for q in s.running] == [a] and [q.id for q in s.waiting] == [b]
+    toks, final = collect(run_all(s))
+    assert final[a].status == final[b].status == FINISHED
