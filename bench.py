@@ -1,0 +1,266 @@
+"""Decode and prefill throughput of dynalm_b200 on one B200, Llama 3.2 1B shape, random bf16 weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one decode step of a batch of 8 requests that each hold 2,048 tokens of context. `value` is
+decoded tokens per second over exactly K steps, timed with CUDA events on the launching stream (the
+token ids fed are fixed, nothing is read back inside the timed region); `e2e` is the same through the
+Python entry point's scheduler: host token ids in, sampled token ids out, every step. Beside them: a
+2,048-token prefill with its fraction of the bf16 matrix peak, the decode step's fraction of the HBM
+roofline (every weight read once plus the cache of the live requests), and decode at batch 1 and 64.
+Prints one JSON line.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: the Llama 3.2 1B shape.
+LLAMA_1B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "vocab_size": 128256, "hidden_size": 2048,
+    "intermediate_size": 8192, "num_hidden_layers": 16, "num_attention_heads": 32, "num_key_value_heads": 8,
+    "head_dim": 64, "max_position_embeddings": 131072, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "tie_word_embeddings": True,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+}
+FULL_LAYERS = 16
+CONTEXT = 8192          # benchmark context length: the longest a request may grow
+HELD = 2048             # tokens each sequence holds when decoding
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(p):
+        try:
+            d = json.load(open(p))
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+        except (KeyError, ValueError, TypeError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """nvidia-smi in the background during the timed region: SM clocks and throttle reasons."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        self.result = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out = ""
+        mhz, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                mhz.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if mhz:
+            self.result = {"sm_mhz": statistics.median(mhz), "sm_max_mhz": max(mx), "reasons": sorted(reasons)}
+
+
+def weight_bytes(cfg, layers):
+    H, F, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    qw = cfg["num_attention_heads"] * cfg["head_dim"]
+    kw = cfg["num_key_value_heads"] * cfg["head_dim"]
+    per_layer = (qw + 2 * kw) * H + H * qw + 3 * F * H
+    return 2 * (layers * per_layer + V * H) + 4 * H * (2 * layers + 1)      # bf16 matrices, fp32 norm weights
+
+
+def kv_bytes_per_token(cfg, layers):
+    return 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * layers * 2
+
+
+def prefill_flops(cfg, layers, T):
+    H, F, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, hd = cfg["num_attention_heads"], cfg["head_dim"]
+    qw, kw = nh * hd, cfg["num_key_value_heads"] * hd
+    per_layer = (qw + 2 * kw) * H + H * qw + 3 * F * H
+    return 2.0 * layers * per_layer * T + 4.0 * nh * hd * layers * T * (T + 1) / 2 + 2.0 * V * H
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration (named in config)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "dynalm-project/dynalm is a C++/CMake project with no Python package (pip: neither setup.py nor "
+                          "pyproject.toml found) and no CUDA code of its own; its GPU path needs ggml fetched from the "
+                          "network at configure time, so only its CPU build exists offline"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    W = max(3, args.warmup)
+    K = max(1, args.steps)
+
+    import numpy as np
+    import torch
+    from dynalm_b200 import Engine, Request, SchedulerConfig, StepEntry
+    from dynalm_b200.kernels import gemm, ops
+
+    peaks = load_peaks()
+    cfg = dict(LLAMA_1B)
+    cfg["num_hidden_layers"] = args.layers
+    batches = [args.batch] if args.no_points else sorted({1, args.batch, 64})
+    max_b = max(batches)
+    held_max = HELD + W + K + 16
+    t_build = time.time()
+    eng = Engine(config=cfg, random_seed=0, dtype="bfloat16", ctx=max_b * (-(-held_max // 16) * 16) + 4096,
+                 batch=PREFILL_TOKENS, max_running=max_b,
+                 scheduler=SchedulerConfig(max_running=max_b, decode_token_budget=max_b,
+                                           prefill_token_budget=PREFILL_TOKENS - max_b,
+                                           max_prefill_chunk=PREFILL_TOKENS - max_b, max_batch_tokens=PREFILL_TOKENS))
+    step_fn = eng.step_fn
+    rng = np.random.RandomState(0)
+    vocab = cfg["vocab_size"]
+    print(f"[bench] engine built in {time.time() - t_build:.1f} s ({args.layers} layers)", file=sys.stderr)
+
+    def timed(fn, n):
+        """n calls of fn between two CUDA events on the current stream -> milliseconds."""
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b)
+
+    # ---- prefill of one 2,048-token prompt -----------------------------------------------------------
+    prompt = [int(t) for t in rng.randint(0, vocab, PREFILL_TOKENS)]
+
+    def prefill_once():
+        step_fn.step([StepEntry("p", prompt, [PREFILL_TOKENS - 1])])
+        step_fn.end("p")
+    for _ in range(3):
+        prefill_once()
+    pre_ms = timed(prefill_once, 5) / 5
+    flops = prefill_flops(cfg, args.layers, PREFILL_TOKENS)
+    prefill = {"value": round(PREFILL_TOKENS / pre_ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
+               "frac": round(flops / (pre_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
+
+    # ---- decode: device-timed ------------------------------------------------------------------------------
+    def fill(B):
+        for r in range(B):
+            step_fn.step([StepEntry(("d", r), [int(t) for t in rng.randint(0, vocab, HELD)], [])])
+
+    def drop(B):
+        for r in range(B):
+            step_fn.end(("d", r))
+
+    ids_out = torch.zeros(max_b, dtype=torch.int32, device="cuda:0")
+    results = {}
+    launches = 0
+    clocks = None
+    for B in batches:
+        fill(B)
+        toks = [[int(rng.randint(0, vocab))] for _ in range(B)]
+
+        def decode_once():
+            logits = step_fn.step([StepEntry(("d", r), toks[r], [0]) for r in range(B)])
+            ops.argmax(logits, ids_out[:B])
+        for _ in range(W):
+            decode_once()
+        if B == args.batch:
+            l0, g0 = ops.LAUNCHES, gemm.LIBRARY_CALLS
+            with ClockSampler() as cs:
+                ms = timed(decode_once, K)
+            clocks = cs.result
+            launches = ops.LAUNCHES - l0 + getattr(step_fn, "graph_kernel_launches", 0)
+            lib_calls = gemm.LIBRARY_CALLS - g0
+        else:
+            ms = timed(decode_once, K)
+        results[B] = ms / K
+        drop(B)
+
+    ms_step = results[args.batch]
+    value = args.batch / ms_step * 1e3
+    bytes_step = weight_bytes(cfg, args.layers) + args.batch * (HELD + W + K / 2) * kv_bytes_per_token(cfg, args.layers)
+    achieved = bytes_step / (ms_step * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / peaks["hbm_gbs"], 4), "of": peaks["source"]}
+
+    # ---- decode end to end through the scheduler: host ids in, host ids out, every step ----------------------
+    B = args.batch
+    for r in range(B):
+        eng.scheduler.submit(Request([int(t) for t in rng.randint(0, vocab, HELD)], max_new_tokens=W + K + 4))
+    while any(s.status != "decode" or s.pending != 1 for s in eng.scheduler.running) or eng.scheduler.waiting \
+            or eng.scheduler.incoming:
+        eng.scheduler.step()
+    for _ in range(W):
+        eng.scheduler.step()
+    h0, d0 = eng.executor.h2d_bytes, eng.executor.d2h_bytes
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    n_tok = 0
+    for _ in range(K):
+        n_tok += sum(1 for ev in eng.scheduler.step() if ev.token is not None)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    e2e = {"value": round(n_tok / e2e_s, 1), "unit": "tokens/s",
+           "h2d_bytes_per_step": (eng.executor.h2d_bytes - h0) // K, "d2h_bytes_per_step": (eng.executor.d2h_bytes - d0) // K}
+    while not eng.scheduler.idle:
+        eng.scheduler.step()
+
+    out = {
+        "metric": "decode tokens/s, Llama 3.2 1B shape, batch 8, 2048 tokens of context per sequence",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights N(0, 0.02) seed 0, random token ids",
+        "config": {"model": "llama-3.2-1b-shape", "layers": args.layers, "layers_full": FULL_LAYERS, "hidden": 2048,
+                   "heads": 32, "kv_heads": 8, "head_dim": 64, "intermediate": 8192, "vocab": 128256,
+                   "global_batch": args.batch, "seq_len": HELD, "context": CONTEXT, "kv_block": 16, "parallelism": "none",
+                   "l2": "inputs larger than L2 (weights + cache >= 2.5 GB per step)", "tied_embeddings": True},
+        "e2e": e2e, "gpu_launches": launches, "library_gemm_calls": lib_calls, "prefill": prefill,
+        "roofline": roofline,
+        "points": {f"decode_b{b}": round(b / results[b] * 1e3, 1) for b in batches if b != args.batch},
+        "clocks": clocks, "impl": "ours",
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
