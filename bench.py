@@ -26,7 +26,7 @@ sys.path.insert(0, ROOT)
 LLAMA_1B = {
     "architectures": ["LlamaForCausalLM"], "model_type": "llama", "vocab_size": 128256, "hidden_size": 2048,
     "intermediate_size": 8192, "num_hidden_layers": 16, "num_attention_heads": 32, "num_key_value_heads": 8,
-    "head_dim": 64, "max_position_embeddings": 131072, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "head_dim": 64, "max_position_embeddings": 8192, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
     "tie_word_embeddings": True,
     "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
                      "original_max_position_embeddings": 8192},
@@ -121,6 +121,9 @@ def main():
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel (for profiling)")
+    ap.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
+                    help="profiling aid: run only the device-timed decode loop, or only the prefill")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -153,6 +156,8 @@ def main():
                                            prefill_token_budget=PREFILL_TOKENS - max_b,
                                            max_prefill_chunk=PREFILL_TOKENS - max_b, max_batch_tokens=PREFILL_TOKENS))
     step_fn = eng.step_fn
+    if args.no_graphs:
+        step_fn.use_graphs = False
     rng = np.random.RandomState(0)
     vocab = cfg["vocab_size"]
     print(f"[bench] engine built in {time.time() - t_build:.1f} s ({args.layers} layers)", file=sys.stderr)
@@ -174,9 +179,15 @@ def main():
     def prefill_once():
         step_fn.step([StepEntry("p", prompt, [PREFILL_TOKENS - 1])])
         step_fn.end("p")
-    for _ in range(3):
-        prefill_once()
-    pre_ms = timed(prefill_once, 5) / 5
+    if args.only == "decode":
+        pre_ms = float("nan")
+    else:
+        for _ in range(3):
+            prefill_once()
+        pre_ms = timed(prefill_once, 5) / 5
+    if args.only == "prefill":
+        print(json.dumps({"prefill_ms": pre_ms}))
+        return 0
     flops = prefill_flops(cfg, args.layers, PREFILL_TOKENS)
     prefill = {"value": round(PREFILL_TOKENS / pre_ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
                "frac": round(flops / (pre_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
@@ -221,6 +232,10 @@ def main():
     achieved = bytes_step / (ms_step * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": round(achieved / peaks["hbm_gbs"], 4), "of": peaks["source"]}
+
+    if args.only == "decode":
+        print(json.dumps({"decode_ms_per_step": ms_step, "roofline": roofline}))
+        return 0
 
     # ---- decode end to end through the scheduler: host ids in, host ids out, every step ----------------------
     B = args.batch

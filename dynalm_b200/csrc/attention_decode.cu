@@ -1,0 +1,308 @@
+// Split-KV paged attention for rows that bring few tokens (decode): bandwidth-bound, CUDA cores.
+//
+// One thread block per (key split, KV head, row). The block streams its share of the row's keys and
+// values once and serves every query head of the KV head's group from them (the reference's
+// GQA-grouped pass, dynacore/cpu/cpu_device.cpp:1297-1308,1347-1352). Inside a warp, LPK lanes share
+// one key: each lane holds one 16-byte vector of the head dimension, so a warp instruction reads
+// 32 / LPK whole key rows, fully coalesced. Scores are reduced over those lanes by shuffles; the
+// running (max, sum, acc) of the online softmax is kept per lane in fp32 and merged at the end over
+// the warp's key slots, then over the block's warps in shared memory. With more than one split the
+// block writes its unnormalised (acc, max, sum) to scratch and `attention_combine_kernel` merges the
+// splits by the log-sum-exp rule of the reference's split-K variant (:1782-1845).
+//
+// Scratch layout: part[((row * n_heads + head) * n_split + split) * (head_dim + 2)] = acc[head_dim], max, sum.
+#include "common.cuh"
+
+namespace dl {
+
+constexpr int DEC_THREADS = 128;
+constexpr int DEC_WARPS = DEC_THREADS / 32;
+constexpr int DEC_G = 4;   // query heads of one group served per block
+constexpr int DEC_U = 4;   // keys in flight per lane group
+
+template <typename T, int LPK>
+__global__ void __launch_bounds__(DEC_THREADS)
+decode_attention_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ k_cache,
+                        const T* __restrict__ v_cache, const int* __restrict__ block_table, int max_blocks,
+                        const int* __restrict__ positions, const int* __restrict__ row_request,
+                        T* __restrict__ out, int out_stride, float* __restrict__ part, int n_heads, int n_kv_heads,
+                        int head_dim, int page_shift, float scale_log2, int window, int n_split) {
+  constexpr int V = PerVec<T>::n;
+  constexpr int KPW = 32 / LPK;
+  extern __shared__ float sm[];   // [DEC_WARPS][DEC_G][head_dim + 2]
+  const int split = blockIdx.x, row = blockIdx.z;
+  const int group = n_heads / n_kv_heads;
+  const int chunks = (group + DEC_G - 1) / DEC_G;
+  const int kvh = blockIdx.y / chunks, h0 = (blockIdx.y % chunks) * DEC_G;
+  const int ng = min(DEC_G, group - h0);
+  const int head0 = kvh * group + h0;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int kg = lane / LPK, dl_ = lane % LPK;
+  const bool dim_ok = dl_ * V < head_dim;
+  const int page_mask = (1 << page_shift) - 1;
+
+  const int pos = positions[row];
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int n = pos + 1 - lo;
+  int len = (n + n_split - 1) / n_split;
+  len = (len + 15) & ~15;
+  const int k_begin = lo + split * len;
+  const int k_end = min(pos + 1, k_begin + len);
+  const int* table = block_table + static_cast<size_t>(row_request[row]) * max_blocks;
+  const size_t kv_row = static_cast<size_t>(n_kv_heads) * head_dim;
+  const size_t head_off = static_cast<size_t>(kvh) * head_dim + dl_ * V;
+
+  float qv[DEC_G][V];
+  float acc[DEC_G][V];
+  float m[DEC_G], l[DEC_G];
+#pragma unroll
+  for (int g = 0; g < DEC_G; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.0f;
+#pragma unroll
+    for (int j = 0; j < V; ++j) { acc[g][j] = 0.0f; qv[g][j] = 0.0f; }
+    if (g < ng && dim_ok) {
+      const T* qp = q + static_cast<size_t>(row) * q_stride + static_cast<size_t>(head0 + g) * head_dim + dl_ * V;
+      float f[V];
+      unpack<T>(*reinterpret_cast<const Vec16*>(qp), f);
+#pragma unroll
+      for (int j = 0; j < V; ++j) qv[g][j] = f[j] * scale_log2;
+    }
+  }
+
+  constexpr int STRIDE = DEC_WARPS * KPW;   // keys between a lane group's consecutive keys
+  // The loop bound is the same for every lane of a warp (the shuffles below name all 32 lanes);
+  // a lane group whose key lies past the end computes on zeros and discards the score.
+  for (int base = k_begin + warp * KPW; base < k_end; base += STRIDE * DEC_U) {
+    const int t0 = base + kg;
+    Vec16 kr[DEC_U], vr[DEC_U];
+    bool ok[DEC_U];
+#pragma unroll
+    for (int u = 0; u < DEC_U; ++u) {
+      const int t = t0 + u * STRIDE;
+      ok[u] = t < k_end;
+      kr[u].raw = make_uint4(0, 0, 0, 0);
+      vr[u].raw = make_uint4(0, 0, 0, 0);
+      if (ok[u] && dim_ok) {
+        const size_t slot = (static_cast<size_t>(table[t >> page_shift]) << page_shift) + (t & page_mask);
+        kr[u] = *reinterpret_cast<const Vec16*>(k_cache + slot * kv_row + head_off);
+        vr[u] = *reinterpret_cast<const Vec16*>(v_cache + slot * kv_row + head_off);
+      }
+    }
+    float s[DEC_G][DEC_U];
+#pragma unroll
+    for (int u = 0; u < DEC_U; ++u) {
+      float kf[V];
+      unpack<T>(kr[u], kf);
+#pragma unroll
+      for (int g = 0; g < DEC_G; ++g) {
+        float d = 0.0f;
+        if (g < ng) {
+#pragma unroll
+          for (int j = 0; j < V; ++j) d = fmaf(qv[g][j], kf[j], d);
+        }
+        s[g][u] = d;
+      }
+    }
+#pragma unroll
+    for (int o = 1; o < LPK; o <<= 1) {
+#pragma unroll
+      for (int g = 0; g < DEC_G; ++g) {
+        if (g < ng) {
+#pragma unroll
+          for (int u = 0; u < DEC_U; ++u) s[g][u] += __shfl_xor_sync(0xffffffffu, s[g][u], o);
+        }
+      }
+    }
+    float vf[DEC_U][V];
+#pragma unroll
+    for (int u = 0; u < DEC_U; ++u) unpack<T>(vr[u], vf[u]);
+#pragma unroll
+    for (int g = 0; g < DEC_G; ++g) {
+      if (g < ng) {
+        float bm = -INFINITY;
+#pragma unroll
+        for (int u = 0; u < DEC_U; ++u) {
+          if (!ok[u]) s[g][u] = -INFINITY;
+          bm = fmaxf(bm, s[g][u]);
+        }
+        if (bm > -INFINITY) {                      // this lane group had at least one key in range
+          const float m_new = fmaxf(m[g], bm);
+          const float corr = exp2f(m[g] - m_new);  // 0 the first time
+          float p[DEC_U], ps = 0.0f;
+#pragma unroll
+          for (int u = 0; u < DEC_U; ++u) {
+            p[u] = exp2f(s[g][u] - m_new);
+            ps += p[u];
+          }
+          l[g] = l[g] * corr + ps;
+          m[g] = m_new;
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            float a = acc[g][j] * corr;
+#pragma unroll
+            for (int u = 0; u < DEC_U; ++u) a = fmaf(p[u], vf[u][j], a);
+            acc[g][j] = a;
+          }
+        }
+      }
+    }
+  }
+
+  // merge the warp's key slots (lanes that differ in kg)
+#pragma unroll
+  for (int o = LPK; o < 32; o <<= 1) {
+#pragma unroll
+    for (int g = 0; g < DEC_G; ++g) {
+      if (g < ng) {
+        const float om = __shfl_xor_sync(0xffffffffu, m[g], o);
+        const float ol = __shfl_xor_sync(0xffffffffu, l[g], o);
+        const float m_new = fmaxf(m[g], om);
+        const float ca = m_new == -INFINITY ? 0.0f : exp2f(m[g] - m_new);
+        const float cb = m_new == -INFINITY ? 0.0f : exp2f(om - m_new);
+        l[g] = l[g] * ca + ol * cb;
+        m[g] = m_new;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float oa = __shfl_xor_sync(0xffffffffu, acc[g][j], o);
+          acc[g][j] = acc[g][j] * ca + oa * cb;
+        }
+      }
+    }
+  }
+  const int rec = head_dim + 2;
+  if (kg == 0) {
+#pragma unroll
+    for (int g = 0; g < DEC_G; ++g) {
+      if (g < ng) {
+        float* dst = sm + (static_cast<size_t>(warp) * DEC_G + g) * rec;
+        if (dim_ok) {
+#pragma unroll
+          for (int j = 0; j < V; ++j) dst[dl_ * V + j] = acc[g][j];
+        }
+        if (dl_ == 0) {
+          dst[head_dim] = m[g];
+          dst[head_dim + 1] = l[g];
+        }
+      }
+    }
+  }
+  __syncthreads();
+  // merge the block's warps: one thread per (head, dim)
+  for (int idx = threadIdx.x; idx < ng * head_dim; idx += DEC_THREADS) {
+    const int g = idx / head_dim, d = idx % head_dim;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) mm = fmaxf(mm, sm[(w * DEC_G + g) * rec + head_dim]);
+    float a = 0.0f, ll = 0.0f;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      const float* src = sm + (w * DEC_G + g) * rec;
+      const float c = mm == -INFINITY ? 0.0f : exp2f(src[head_dim] - mm);
+      a += src[d] * c;
+      ll += src[head_dim + 1] * c;
+    }
+    const int head = head0 + g;
+    if (n_split == 1) {
+      out[static_cast<size_t>(row) * out_stride + static_cast<size_t>(head) * head_dim + d] = from_float<T>(a / ll);
+    } else {
+      float* dst = part + ((static_cast<size_t>(row) * n_heads + head) * n_split + split) * rec;
+      dst[d] = a;
+      if (d == 0) {
+        dst[head_dim] = mm;
+        dst[head_dim + 1] = ll;
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void attention_combine_kernel(const float* __restrict__ part, T* __restrict__ out, int out_stride,
+                                         int n_heads, int head_dim, int n_split) {
+  const int head = blockIdx.x, row = blockIdx.y;
+  const int rec = head_dim + 2;
+  const float* base = part + (static_cast<size_t>(row) * n_heads + head) * n_split * rec;
+  float mm = -INFINITY;
+  for (int s = 0; s < n_split; ++s) mm = fmaxf(mm, base[s * rec + head_dim]);
+  for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+    float a = 0.0f, ll = 0.0f;
+    for (int s = 0; s < n_split; ++s) {
+      const float ms = base[s * rec + head_dim];
+      const float c = ms == -INFINITY ? 0.0f : exp2f(ms - mm);
+      a += base[s * rec + d] * c;
+      ll += base[s * rec + head_dim + 1] * c;
+    }
+    out[static_cast<size_t>(row) * out_stride + static_cast<size_t>(head) * head_dim + d] = from_float<T>(a / ll);
+  }
+}
+
+template <typename T>
+int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, const int* block_table,
+                  int max_blocks, const int* positions, const int* row_request, void* out, int out_stride,
+                  float* part, int rows, int n_heads, int n_kv_heads, int head_dim, int page_size, float scale,
+                  int window, int n_split, cudaStream_t stream) {
+  constexpr int V = PerVec<T>::n;
+  int page_shift = 0;
+  while ((1 << page_shift) < page_size) ++page_shift;
+  if ((1 << page_shift) != page_size) return DL_ERR_UNSUPPORTED;
+  if (head_dim % 16 != 0 || head_dim <= 0 || head_dim > 32 * V || n_heads % n_kv_heads != 0 || n_split < 1 ||
+      rows > 65535 || (n_split > 1 && part == nullptr))
+    return DL_ERR_UNSUPPORTED;
+  const int vecs = head_dim / V + (head_dim % V ? 1 : 0);
+  int lpk = 1;
+  while (lpk < vecs) lpk <<= 1;
+  const int group = n_heads / n_kv_heads;
+  const int chunks = (group + DEC_G - 1) / DEC_G;
+  dim3 grid(n_split, n_kv_heads * chunks, rows);
+  const size_t smem = static_cast<size_t>(DEC_WARPS) * DEC_G * (head_dim + 2) * sizeof(float);
+  const float scale_log2 = scale * 1.4426950408889634f;
+#define DL_LAUNCH(L)                                                                                            \
+  decode_attention_kernel<T, L><<<grid, DEC_THREADS, smem, stream>>>(                                           \
+      static_cast<const T*>(q), q_stride, static_cast<const T*>(kc), static_cast<const T*>(vc), block_table,    \
+      max_blocks, positions, row_request, static_cast<T*>(out), out_stride, part, n_heads, n_kv_heads, head_dim, \
+      page_shift, scale_log2, window, n_split)
+  switch (lpk) {
+    case 1: DL_LAUNCH(1); break;
+    case 2: DL_LAUNCH(2); break;
+    case 4: DL_LAUNCH(4); break;
+    case 8: DL_LAUNCH(8); break;
+    case 16: DL_LAUNCH(16); break;
+    case 32: DL_LAUNCH(32); break;
+    default: return DL_ERR_UNSUPPORTED;
+  }
+#undef DL_LAUNCH
+  int rc = launch_status();
+  if (rc != 0 || n_split == 1) return rc;
+  dim3 cgrid(n_heads, rows);
+  const int cthreads = head_dim <= 32 ? 32 : (head_dim <= 64 ? 64 : 128);
+  attention_combine_kernel<T><<<cgrid, cthreads, 0, stream>>>(part, static_cast<T*>(out), out_stride, n_heads,
+                                                             head_dim, n_split);
+  return launch_status();
+}
+
+}  // namespace dl
+
+// Floats of scratch that `dl_paged_attention_decode` needs for n_split > 1.
+DL_EXPORT long long dl_paged_attention_decode_scratch(int rows, int n_heads, int head_dim, int n_split) {
+  return n_split <= 1 ? 0 : static_cast<long long>(rows) * n_heads * n_split * (head_dim + 2);
+}
+
+// q/out: rows with head h at column h * head_dim. k_cache, v_cache: [pages, page_size, kv_heads, head_dim],
+// page_size a power of two. part: fp32 scratch of dl_paged_attention_decode_scratch floats (may be null when
+// n_split == 1). Every row attends keys [lo, positions[row]] of its request.
+DL_EXPORT int dl_paged_attention_decode(int dtype, const void* q, int q_stride, const void* k_cache,
+                                        const void* v_cache, const int* block_table, int max_blocks,
+                                        const int* positions, const int* row_request, void* out, int out_stride,
+                                        float* part, int rows, int n_heads, int n_kv_heads, int head_dim,
+                                        int page_size, float scale, int window, int n_split, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (dtype == 0)
+    return dl::launch_decode<float>(q, q_stride, k_cache, v_cache, block_table, max_blocks, positions, row_request, out,
+                                    out_stride, part, rows, n_heads, n_kv_heads, head_dim, page_size, scale, window,
+                                    n_split, stream);
+  if (dtype == 1)
+    return dl::launch_decode<dl::bf16>(q, q_stride, k_cache, v_cache, block_table, max_blocks, positions, row_request,
+                                       out, out_stride, part, rows, n_heads, n_kv_heads, head_dim, page_size, scale,
+                                       window, n_split, stream);
+  return DL_ERR_UNSUPPORTED;
+}

@@ -41,7 +41,7 @@ def build(model_dir: Optional[str] = None, *, config_obj: Optional[Mapping[str, 
     context            the longest one request may grow (default: max_position_embeddings)
     """
     compute = parse_dtype(dtype)
-    runtime = Runtime(device, compute, max_tokens=max_batch_tokens)
+    runtime = Runtime(device, compute, max_tokens=max_batch_tokens, max_requests=max_requests)
     if model_dir is not None:
         folder = open_model_folder(model_dir)
         config, plan = folder.config, folder.plan

@@ -46,6 +46,10 @@ class StepContext:
     state_slots: torch.Tensor
     logit_rows: torch.Tensor
     num_logit_rows: int
+    # every request cut into tiles of at most 64 consecutive rows: int32 [num_q_tiles, 4] =
+    # (request, first row of the step, rows, first position)
+    q_tiles: Optional[torch.Tensor] = None
+    num_q_tiles: int = 0
     h_q_len: List[int] = field(default_factory=list)
     h_pos_start: List[int] = field(default_factory=list)
     h_state_slots: List[int] = field(default_factory=list)

@@ -32,6 +32,21 @@ class Decoder:
         self.vocab = plan.head.vocab
         self.width = plan.embedding.width
 
+    @property
+    def graph_safe(self) -> bool:
+        """True when every mixer and feed-forward says its launches depend only on what
+        `graph_key` covers, so that a decode step can be captured once and replayed."""
+        return all(getattr(b.mixer, "graph_safe", False) and getattr(b.ffn, "graph_safe", False) for b in self.blocks)
+
+    def graph_key(self, ctx) -> tuple:
+        """What, beyond the numbers of rows, the parts' launch shapes depend on for this step."""
+        key = ()
+        for b in self.blocks:
+            f = getattr(b.mixer, "graph_key", None)
+            if f is not None:
+                key += tuple(f(ctx))
+        return tuple(sorted(set(key)))
+
     def cache_specs(self) -> List[Optional[CacheSpec]]:
         """Per run-order entry: the cache it owns, or None when it owns none."""
         return [None if run.cache_of is not None else self.blocks[run.layer].cache_spec() for run in self.order]

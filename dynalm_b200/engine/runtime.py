@@ -32,7 +32,7 @@ class Runtime:
     filled it, except where a name says otherwise.
     """
 
-    def __init__(self, device="cuda:0", dtype="bfloat16", max_tokens: int = 2048):
+    def __init__(self, device="cuda:0", dtype="bfloat16", max_tokens: int = 2048, max_requests: int = 64):
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise ExtensionMissing("dynalm_b200 runs on a CUDA device only; there is no CPU path")
@@ -40,6 +40,7 @@ class Runtime:
             raise ExtensionMissing("no CUDA device is available; dynalm_b200 has no CPU path")
         self.dtype = parse_dtype(dtype)
         self.max_tokens = int(max_tokens)
+        self.max_requests = int(max_requests)      # the most rows a decode-only step can bring
         self._buffers: Dict[Tuple, torch.Tensor] = {}
 
     def buffer(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype = None) -> torch.Tensor:
@@ -53,6 +54,18 @@ class Runtime:
             buf = torch.zeros((self.max_tokens,) + tail, dtype=dtype, device=self.device)
             self._buffers[key] = buf
         return buf[:rows]
+
+    def flat(self, name: str, numel: int, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        """A persistent 1-D scratch array of `numel` elements, allocated once at the size first asked
+        for (callers ask for their maximum), so that its address never changes."""
+        key = (name, "flat", dtype)
+        buf = self._buffers.get(key)
+        if buf is None:
+            buf = torch.zeros(int(numel), dtype=dtype, device=self.device)
+            self._buffers[key] = buf
+        if buf.numel() < numel:
+            raise InvalidArgument(f"scratch '{name}' was made for {buf.numel()} elements, {numel} are asked for")
+        return buf
 
     def workspace_bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._buffers.values())

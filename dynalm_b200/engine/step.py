@@ -33,6 +33,9 @@ class StepEntry:
     want: Sequence[int] = ()
 
 
+Q_TILE = 64     # rows of one request per query tile (see StepContext.q_tiles)
+
+
 class _StepBuffers:
     """Per-step integers, packed: one pinned host array per ring slot, one device array with fixed
     addresses (kernels captured in a CUDA graph keep reading the same pointers). A step fills a host
@@ -55,6 +58,8 @@ class _StepBuffers:
         take("q_start", max_requests + 1)
         for name in ("pos_start", "kv_len", "state_slots"):
             take(name, max_requests)
+        self.max_q_tiles = max_tokens // Q_TILE + max_requests
+        take("q_tiles", 4 * self.max_q_tiles)
         self.group_blocks = dict(group_blocks)
         for gid, mb in group_blocks.items():
             take(f"table{gid}", max_requests * mb)
@@ -149,6 +154,8 @@ class BatchBuilder:
         pos_start = h[off["pos_start"]]
         kv_len = h[off["kv_len"]]
         slots = h[off["state_slots"]]
+        tiles = h[off["q_tiles"]]
+        n_tiles = 0
         r0 = 0
         n_logit = 0
         h_q_len, h_pos_start, h_slots = [], [], []
@@ -169,6 +176,9 @@ class BatchBuilder:
             h_q_len.append(n)
             h_pos_start.append(start)
             h_slots.append(slot)
+            for t0 in range(0, n, Q_TILE):
+                tiles[4 * n_tiles: 4 * n_tiles + 4] = (r, r0 + t0, min(Q_TILE, n - t0), start + t0)
+                n_tiles += 1
             for g in self.cache.groups:
                 mb = g.max_blocks
                 sec = off[f"table{g.gid}"]
@@ -181,6 +191,7 @@ class BatchBuilder:
             num_tokens=total, num_requests=len(entries), token_ids=d["token_ids"], positions=d["positions"],
             row_request=d["row_request"], q_start=d["q_start"], pos_start=d["pos_start"], kv_len=d["kv_len"],
             state_slots=d["state_slots"], logit_rows=d["logit_rows"], num_logit_rows=n_logit,
+            q_tiles=d["q_tiles"], num_q_tiles=n_tiles,
             h_q_len=h_q_len, h_pos_start=h_pos_start, h_state_slots=h_slots, block_tables=self.tables,
             decode_only=all(n == 1 for n in h_q_len), max_q_len=max(h_q_len),
             max_kv_len=max(s + n for s, n in zip(h_pos_start, h_q_len)))
@@ -196,7 +207,8 @@ class StepFunction:
     """Model + cache + the step. `step(entries)` is the whole forward path; generation, the
     scheduler and trace replay all go through it."""
 
-    def __init__(self, model: Decoder, cache: CacheManager, runtime: Runtime, max_requests: int):
+    def __init__(self, model: Decoder, cache: CacheManager, runtime: Runtime, max_requests: int,
+                 use_graphs: bool = True):
         self.model = model
         self.cache = cache
         self.rt = runtime
@@ -208,6 +220,16 @@ class StepFunction:
         self.computed = self.batcher.computed
         self._logits: Optional[torch.Tensor] = None
         self._caches = None
+        # Decode-only steps (one token per request) are captured once per (requests, wanted rows,
+        # span bucket) as a CUDA graph and replayed: the kernels read the step's integers from the
+        # packed device buffer, whose addresses never change. The reference's GPU path keeps one
+        # prepared graph per step structure in the same way, at most 64 of them
+        # (dynacore/include/dynacore/gpu/ggml_device.h:8-13,39-48).
+        self.use_graphs = bool(use_graphs) and model.graph_safe
+        self._graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}
+        self._decode_logits: Optional[torch.Tensor] = None
+        self.graph_kernel_launches = 0     # kernels replayed through graphs so far
+        self._graph_nodes: Dict[tuple, int] = {}
 
     # ---- request lifetime ----------------------------------------------------------------------
     def begin(self, request) -> None:
@@ -238,7 +260,41 @@ class StepFunction:
         """Run the batch. Returns float32 logits [wanted rows, vocab] on the device (a view of a
         buffer that the next step overwrites), or None when nothing was wanted."""
         ctx = self.batcher.build(entries, reserve)
-        out = self._logits_buffer(ctx.num_logit_rows) if ctx.num_logit_rows else None
-        logits = self.model.forward(ctx, self.caches(), out)
+        if self.use_graphs and ctx.decode_only:
+            logits = self._replay(ctx)
+        else:
+            out = self._logits_buffer(ctx.num_logit_rows) if ctx.num_logit_rows else None
+            logits = self.model.forward(ctx, self.caches(), out)
         self.batcher.finish(entries)
         return logits
+
+    MAX_GRAPHS = 64
+
+    def _replay(self, ctx: StepContext) -> Optional[torch.Tensor]:
+        from ..kernels import ops
+        if self._decode_logits is None:
+            self._decode_logits = torch.empty((self.max_requests, self.vocab), dtype=torch.float32,
+                                              device=self.rt.device)
+        key = (ctx.num_requests, ctx.num_logit_rows) + self.model.graph_key(ctx)
+        out = self._decode_logits if ctx.num_logit_rows else None
+        graph = self._graphs.get(key)
+        if graph is None:
+            # once eagerly (allocates workspaces, loads kernels), then capture the same calls
+            self.model.forward(ctx, self.caches(), out)
+            torch.cuda.current_stream().synchronize()
+            if len(self._graphs) >= self.MAX_GRAPHS:
+                old = next(iter(self._graphs))
+                del self._graphs[old]
+                self._graph_nodes.pop(old, None)
+            graph = torch.cuda.CUDAGraph()
+            before = ops.LAUNCHES
+            with torch.cuda.graph(graph):
+                self.model.forward(ctx, self.caches(), out)
+            from ..kernels import gemm
+            self._graph_nodes[key] = ops.LAUNCHES - before
+            self._graphs[key] = graph
+            # the eager run above already produced this step's result
+            return out[:ctx.num_logit_rows] if out is not None else None
+        graph.replay()
+        self.graph_kernel_launches += self._graph_nodes[key]
+        return out[:ctx.num_logit_rows] if out is not None else None

@@ -1,10 +1,68 @@
-"""Chooses the attention kernel for a step. Returns False when only the plain kernel applies
-(float32, or a shape the tensor-core kernels refuse), and the caller runs that one."""
+"""Chooses the attention kernel for a step.
+
+float32 always runs the plain kernel (csrc/attention_generic.cu), whose arithmetic for a row is
+fixed by the row alone. bfloat16 steps in which every request brings one token run the split-KV
+kernel (csrc/attention_decode.cu); other bfloat16 steps (prompt portions, alone or beside decode
+rows) run the tensor-core flash kernel (csrc/attention_prefill.cu). Every shape the faster kernels
+refuse falls to the plain kernel.
+"""
 
 from __future__ import annotations
 
 import torch
 
+from . import ops
 
-def paged_attention(qkv: torch.Tensor, cache, ctx, out: torch.Tensor, spec) -> bool:
-    return False
+SM_COUNT = 148            # B200
+MAX_SPLITS = 32
+
+
+def decode_splits(rows: int, n_heads: int, n_kv_heads: int, max_kv_len: int) -> int:
+    """Key splits per row so that the grid fills the GPU about twice, each split at least 256 keys."""
+    group = n_heads // n_kv_heads
+    blocks = rows * n_kv_heads * (-(-group // 4))
+    want = -(-2 * SM_COUNT // max(blocks, 1))
+    return max(1, min(want, max(1, max_kv_len // 256), MAX_SPLITS))
+
+
+def decode_plan(ctx, spec) -> int:
+    """The number of key splits for this step (also part of the CUDA-graph key)."""
+    span = ctx.max_kv_len if spec.window <= 0 else min(ctx.max_kv_len, spec.window)
+    # bucket the span so that a growing context changes the launch shape only now and then
+    bucket = 256
+    while bucket < span:
+        bucket *= 2
+    return decode_splits(ctx.num_tokens, spec.num_heads, spec.num_kv_heads, bucket)
+
+
+def use_decode_kernel(ctx, spec, dtype: torch.dtype, page_size: int) -> bool:
+    return (dtype == torch.bfloat16 and ctx.decode_only and page_size & (page_size - 1) == 0
+            and spec.head_dim % 16 == 0 and spec.head_dim <= 256)
+
+
+def use_prefill_kernel(ctx, spec, qkv: torch.Tensor, page_size: int) -> bool:
+    return (qkv.dtype == torch.bfloat16 and ctx.q_tiles is not None and page_size & (page_size - 1) == 0
+            and spec.head_dim % 16 == 0 and spec.head_dim <= 128 and qkv.stride(0) % 8 == 0)
+
+
+def paged_attention(qkv: torch.Tensor, cache, ctx, out: torch.Tensor, spec, runtime) -> bool:
+    """Run the fast kernel for this step if one applies; False means the caller runs the plain one."""
+    k_cache, v_cache = cache.arrays
+    if not use_decode_kernel(ctx, spec, qkv.dtype, cache.page_size):
+        if not use_prefill_kernel(ctx, spec, qkv, cache.page_size):
+            return False
+        ops.paged_attention_prefill(qkv, k_cache, v_cache, cache.block_table, ctx.q_tiles, ctx.num_q_tiles, out,
+                                    spec.num_heads, spec.num_kv_heads, spec.head_dim, cache.page_size,
+                                    float(spec.scale), spec.window)
+        return True
+    rows = qkv.shape[0]
+    n_split = decode_plan(ctx, spec)
+    scratch = None
+    if n_split > 1:
+        most_rows = max(runtime.max_requests, rows)
+        scratch = runtime.flat(f"attn_split_scratch_{spec.num_heads}x{spec.head_dim}",
+                               ops.decode_scratch_floats(most_rows, spec.num_heads, spec.head_dim, MAX_SPLITS))
+    ops.paged_attention_decode(qkv, k_cache, v_cache, cache.block_table, ctx.positions, ctx.row_request, out, scratch,
+                               spec.num_heads, spec.num_kv_heads, spec.head_dim, cache.page_size, float(spec.scale),
+                               spec.window, n_split)
+    return True

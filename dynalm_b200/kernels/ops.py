@@ -30,6 +30,10 @@ _SIGNATURES = {
     "rope_cache": {"dl_rope_cache_write": [_I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _F, _I, _I, _I, _I, _I, _I, _P]},
     "attention_generic": {
         "dl_paged_attention_generic": [_I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P]},
+    "attention_decode": {
+        "dl_paged_attention_decode": [_I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P]},
+    "attention_prefill": {
+        "dl_paged_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P]},
     "gemm_simt": {"dl_gemm_simt": [_I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _P]},
     "sampling": {
         "dl_argmax": [_P, _I, _I, _I, _P, _P],
@@ -204,6 +208,63 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
         dtype_code(q.dtype), _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), block_table.stride(0),
         _p(positions), _p(row_request), _p(out), out.stride(0), q.shape[0], n_heads, n_kv_heads, head_dim, page_size,
         scale, window, _stream()), "paged_attention_generic")
+
+
+def decode_scratch_floats(rows: int, n_heads: int, head_dim: int, n_split: int) -> int:
+    """Floats of scratch `paged_attention_decode` needs."""
+    return 0 if n_split <= 1 else rows * n_heads * n_split * (head_dim + 2)
+
+
+def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                           positions: torch.Tensor, row_request: torch.Tensor, out: torch.Tensor,
+                           scratch: Optional[torch.Tensor], n_heads: int, n_kv_heads: int, head_dim: int,
+                           page_size: int, scale: float, window: int, n_split: int) -> None:
+    """Split-KV attention for rows that bring few tokens; see csrc/attention_decode.cu. `scratch`:
+    float32 with at least decode_scratch_floats(...) elements when n_split > 1."""
+    _cuda(q, k_cache, v_cache, block_table, positions, row_request, out, scratch)
+    _rows_contiguous(q, "q")
+    _rows_contiguous(out, "out")
+    rows = q.shape[0]
+    if page_size & (page_size - 1):
+        raise Unsupported(f"decode attention: page size {page_size} is not a power of two")
+    if head_dim % 16 or head_dim > 256 or n_heads % n_kv_heads:
+        raise Unsupported(f"decode attention: head_dim {head_dim} / heads {n_heads}:{n_kv_heads} not supported")
+    if q.dtype != out.dtype or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        raise InvalidArgument("decode attention: q, out and the cache must share one dtype")
+    if tuple(k_cache.shape[1:]) != (page_size, n_kv_heads, head_dim) or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+        raise InvalidArgument("decode attention: cache shape is not [pages, page_size, kv_heads, head_dim]")
+    need = decode_scratch_floats(rows, n_heads, head_dim, n_split)
+    if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
+        raise InvalidArgument(f"decode attention: scratch must be float32 with at least {need} elements")
+    _check(_fn("attention_decode", "dl_paged_attention_decode")(
+        dtype_code(q.dtype), _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), block_table.stride(0),
+        _p(positions), _p(row_request), _p(out), out.stride(0), _p(scratch), rows, n_heads, n_kv_heads, head_dim,
+        page_size, scale, window, n_split, _stream()), "paged_attention_decode")
+
+
+def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                            q_tiles: torch.Tensor, n_tiles: int, out: torch.Tensor, n_heads: int, n_kv_heads: int,
+                            head_dim: int, page_size: int, scale: float, window: int = 0) -> None:
+    """Flash attention of query tiles over the paged cache, bfloat16; see csrc/attention_prefill.cu.
+    q_tiles: int32 [n_tiles, 4] = (request, first row, rows <= 64, first position)."""
+    _cuda(q, k_cache, v_cache, block_table, q_tiles, out)
+    _rows_contiguous(q, "q")
+    _rows_contiguous(out, "out")
+    if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or v_cache.dtype != torch.bfloat16:
+        raise Unsupported("prefill attention: bfloat16 only")
+    if head_dim % 16 or head_dim > 128 or page_size & (page_size - 1) or n_heads % n_kv_heads:
+        raise Unsupported(f"prefill attention: head_dim {head_dim} (multiple of 16 up to 128), page size {page_size} "
+                          f"(a power of two), heads {n_heads}:{n_kv_heads}")
+    if q.stride(0) % 8 or out.stride(0) % 2 or q.data_ptr() % 16 or out.data_ptr() % 4 or q_tiles.data_ptr() % 16:
+        raise Unsupported("prefill attention: q rows must be 16-byte aligned, out rows 4-byte aligned")
+    if tuple(k_cache.shape[1:]) != (page_size, n_kv_heads, head_dim) or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+        raise InvalidArgument("prefill attention: cache shape is not [pages, page_size, kv_heads, head_dim]")
+    if q_tiles.dtype != torch.int32 or q_tiles.numel() < 4 * n_tiles:
+        raise InvalidArgument("prefill attention: q_tiles must be int32 [n_tiles, 4]")
+    _check(_fn("attention_prefill", "dl_paged_attention_prefill")(
+        _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), block_table.stride(0), _p(q_tiles), n_tiles,
+        _p(out), out.stride(0), n_heads, n_kv_heads, head_dim, page_size, scale, window, _stream()),
+        "paged_attention_prefill")
 
 
 def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,

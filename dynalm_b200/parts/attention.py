@@ -19,6 +19,8 @@ from .base import POSITIONS, CacheSpec, TensorDecl, register_mixer
 
 @register_mixer("attention")
 class PagedAttention:
+    graph_safe = True      # launches depend on row counts (and graph_key) only
+
     @staticmethod
     def declare(spec) -> Dict[str, TensorDecl]:
         qw, kw = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
@@ -86,11 +88,15 @@ class PagedAttention:
         linear(attn, self.w_o, out, self.b_o)
         return out
 
+    def graph_key(self, ctx) -> tuple:
+        from ..kernels import attention as fast
+        return (("attn_splits", fast.decode_plan(ctx, self.spec)),)
+
     def attend(self, qkv: torch.Tensor, cache, ctx, out: torch.Tensor) -> None:
         s = self.spec
         k_cache, v_cache = cache.arrays
         from ..kernels import attention as fast
-        if fast.paged_attention(qkv, cache, ctx, out, s):
+        if fast.paged_attention(qkv, cache, ctx, out, s, self.rt):
             return
         ops.paged_attention_generic(qkv, k_cache, v_cache, cache.block_table, ctx.positions, ctx.row_request, out,
                                     s.num_heads, s.num_kv_heads, s.head_dim, cache.page_size, float(s.scale), s.window)

@@ -14,6 +14,8 @@ from .base import TensorDecl, register_feed_forward
 
 @register_feed_forward("gated_mlp")
 class GatedMLP:
+    graph_safe = True      # launches depend on row counts (and graph_key) only
+
     @staticmethod
     def declare(spec) -> Dict[str, TensorDecl]:
         return {

@@ -271,3 +271,127 @@ def test_sample_temperature_frequencies(ops):
     freq = torch.bincount(out.cpu().long(), minlength=5).double() / n
     p = torch.softmax(logits[0].double() / T, 0)
     assert (freq - p).abs().max() < 0.015
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kvh,hd,page,window,splits", [(4, 2, 16, 16, 0, 1), (6, 2, 32, 16, 0, 3), (5, 1, 48, 16, 0, 4),
+                                                               (3, 3, 80, 32, 0, 2), (8, 2, 128, 16, 40, 2),
+                                                               (16, 2, 64, 16, 0, 5), (32, 8, 64, 16, 0, 8),
+                                                               (4, 4, 256, 16, 0, 2), (4, 4, 64, 16, 7, 1)])
+def test_paged_attention_decode(ops, dtype, heads, kvh, hd, page, window, splits):
+    """The split-KV kernel against the same reference as the plain kernel: requests of 1, 60, 700 and
+    130 tokens in scattered pages, one row each at its last position, a far key that stands out,
+    any number of splits (more splits than the short requests have keys)."""
+    if dtype == torch.float32 and hd > 128:
+        pytest.skip("the float32 instantiation holds head sizes up to 128")
+    g = torch.Generator(device="cpu").manual_seed(10)
+    lens = [1, 60, 700, 130]
+    max_blocks = -(-max(lens) // page)
+    pages = sum(-(-l // page) for l in lens) + 5
+    perm = torch.randperm(pages, generator=g)
+    table = torch.full((len(lens), max_blocks), -1, dtype=torch.int32)
+    kc = torch.zeros(pages, page, kvh, hd, dtype=dtype)
+    vc = torch.zeros_like(kc)
+    keys, vals = [], []
+    nxt = 0
+    for r, l in enumerate(lens):
+        k = torch.randn(l, kvh, hd, generator=g).to(dtype)
+        v = torch.randn(l, kvh, hd, generator=g).to(dtype)
+        k[min(3, l - 1)] *= 4.0
+        keys.append(k)
+        vals.append(v)
+        for b in range(-(-l // page)):
+            table[r, b] = perm[nxt]
+            nxt += 1
+            n = min(page, l - b * page)
+            kc[table[r, b], :n] = k[b * page:b * page + n]
+            vc[table[r, b], :n] = v[b * page:b * page + n]
+    order = [2, 0, 3, 1]
+    req = torch.tensor(order, dtype=torch.int32)
+    pos = torch.tensor([lens[r] - 1 for r in order], dtype=torch.int32)
+    n = len(order)
+    q = torch.randn(n, heads, hd, generator=g).to(dtype)
+    q[0] = (keys[2][3, 0].float() * 0.5).to(dtype)
+    scale = 1.0 / math.sqrt(hd)
+    out = torch.zeros(n, heads * hd, dtype=dtype, device=DEV)
+    scratch = torch.zeros(max(1, ops.decode_scratch_floats(n, heads, hd, splits)), dtype=torch.float32, device=DEV)
+    ops.paged_attention_decode(q.reshape(n, heads * hd).to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV), pos.to(DEV),
+                               req.to(DEV), out, scratch, heads, kvh, hd, page, scale, window, splits)
+    got = out.double().cpu().reshape(n, heads, hd)
+    for i, r in enumerate(order):
+        ref = _attention_ref(q[i].double(), keys[r].double(), vals[r].double(), scale, window)
+        err = (got[i] - ref).abs().max().item()
+        assert err <= tol(dtype, 2), f"row {i} (request {r}): {err}"
+
+
+@pytest.mark.parametrize("heads,kvh,hd,page,window", [(4, 2, 16, 16, 0), (6, 2, 32, 16, 0), (5, 1, 48, 16, 0),
+                                                        (3, 3, 80, 32, 0), (8, 2, 128, 16, 40), (32, 8, 64, 16, 0),
+                                                        (4, 4, 64, 16, 7), (2, 1, 112, 16, 100), (4, 2, 96, 64, 0)])
+def test_paged_attention_prefill(ops, heads, kvh, hd, page, window):
+    """The tensor-core flash kernel on a mixed batch: a decode row, a 210-row portion that starts in
+    the middle of a page and of a key tile, a 5-row run, another decode row and a 64-row portion from
+    position 0; a far key stands out; queries padded inside a wider row (as q inside qkv)."""
+    dtype = torch.bfloat16
+    g = torch.Generator(device="cpu").manual_seed(12)
+    lens = [60, 700, 130, 64]
+    max_blocks = -(-max(lens) // page)
+    pages = sum(-(-l // page) for l in lens) + 5
+    perm = torch.randperm(pages, generator=g)
+    table = torch.full((len(lens), max_blocks), -1, dtype=torch.int32)
+    kc = torch.zeros(pages, page, kvh, hd, dtype=dtype)
+    vc = torch.zeros_like(kc)
+    keys, vals = [], []
+    nxt = 0
+    for r, l in enumerate(lens):
+        k = torch.randn(l, kvh, hd, generator=g).to(dtype)
+        v = torch.randn(l, kvh, hd, generator=g).to(dtype)
+        k[3] *= 4.0
+        keys.append(k)
+        vals.append(v)
+        for b in range(-(-l // page)):
+            table[r, b] = perm[nxt]
+            nxt += 1
+            n = min(page, l - b * page)
+            kc[table[r, b], :n] = k[b * page:b * page + n]
+            vc[table[r, b], :n] = v[b * page:b * page + n]
+    if window > 0:
+        # pages wholly behind the window of the first row of each run are not there any more
+        pass
+    runs = [(0, 59, 1), (1, 700 - 210, 210), (2, 100, 5), (2, 129, 1), (3, 0, 64)]      # (request, first position, rows)
+    rows = [(r, p0 + i) for r, p0, n in runs for i in range(n)]
+    tiles = []
+    row0 = 0
+    for r, p0, n in runs:
+        for t0 in range(0, n, 64):
+            tiles.append((r, row0 + t0, min(64, n - t0), p0 + t0))
+        row0 += n
+    n = len(rows)
+    q = torch.randn(n, heads, hd, generator=g).to(dtype)
+    for i, (r, p) in enumerate(rows):
+        if i % 3 == 0:
+            q[i, :, :] = (keys[r][3, 0].float() * 0.5).to(dtype)
+    wide = torch.zeros(n, heads * hd + 2 * kvh * hd, dtype=dtype)
+    wide[:, :heads * hd] = q.reshape(n, heads * hd)
+    wide = wide.to(DEV)
+    scale = 1.0 / math.sqrt(hd)
+    out = torch.zeros(n, heads * hd, dtype=dtype, device=DEV)
+    ops.paged_attention_prefill(wide[:, :heads * hd], kc.to(DEV), vc.to(DEV), table.to(DEV),
+                                torch.tensor(tiles, dtype=torch.int32).to(DEV), len(tiles), out, heads, kvh, hd, page,
+                                scale, window)
+    got = out.double().cpu().reshape(n, heads, hd)
+    for i, (r, p) in enumerate(rows):
+        ref = _attention_ref(q[i].double(), keys[r][:p + 1].double(), vals[r][:p + 1].double(), scale, window)
+        err = (got[i] - ref).abs().max().item()
+        assert err <= 2.5e-2, f"row {i} (request {r}, position {p}): {err}"
+    # a row's result does not depend on where its portion was cut: the 210-row run again as 7 + 203 rows
+    runs2 = [(1, 700 - 210, 7), (1, 700 - 203, 203)]
+    tiles2, row0 = [], 1
+    for r, p0, m in runs2:
+        for t0 in range(0, m, 64):
+            tiles2.append((r, row0 + t0, min(64, m - t0), p0 + t0))
+        row0 += m
+    out2 = torch.zeros_like(out)
+    ops.paged_attention_prefill(wide[:, :heads * hd], kc.to(DEV), vc.to(DEV), table.to(DEV),
+                                torch.tensor(tiles2, dtype=torch.int32).to(DEV), len(tiles2), out2, heads, kvh, hd, page,
+                                scale, window)
+    assert torch.equal(out2[1:211], out[1:211])
