@@ -280,6 +280,289 @@ int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, c
   return launch_status();
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// The tensor-core variant (bf16): the same split-KV scheme, but the group's query heads form the
+// rows of an m16n8k16 tile, and each warp streams its own key tiles through a private multi-stage
+// cp.async pipeline in shared memory, so that many kilobytes stay in flight per warp whatever the
+// register budget. Warp w of a block takes key tiles w, w + 4, ... of the block's key range; tiles are
+// 32 keys. Scores, softmax and the merge are fp32; P is rounded to bf16 for the P V product.
+// ------------------------------------------------------------------------------------------------
+
+constexpr int DT_WARPS = 4;
+constexpr int DT_THREADS = DT_WARPS * 32;
+constexpr int DT_KT = 32;     // keys per tile
+
+__device__ __forceinline__ void dt_cp_async16(void* smem, const void* gmem, bool valid) {
+  const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void dt_ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+  const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void dt_ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
+  const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void dt_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t dt_pack(float lo, float hi) {
+  __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&p);
+}
+
+template <int HD, int STAGES>
+__global__ void __launch_bounds__(DT_THREADS)
+decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k_cache,
+                           const bf16* __restrict__ v_cache, const int* __restrict__ block_table, int max_blocks,
+                           const int* __restrict__ positions, const int* __restrict__ row_request,
+                           bf16* __restrict__ out, int out_stride, float* __restrict__ part, int n_heads,
+                           int n_kv_heads, int page_shift, float scale_log2, int window, int n_split) {
+  constexpr int LD = HD + 8;
+  constexpr int CH = HD / 8;
+  constexpr int KS = HD / 16;
+  constexpr int TILE_ELEMS = DT_KT * LD;                 // one of K or V of one stage
+  extern __shared__ __align__(16) unsigned char dt_smem[];
+  bf16* Qs = reinterpret_cast<bf16*>(dt_smem);           // [16][LD]
+  bf16* KV = Qs + 16 * LD;                               // [warp][stage][K | V][DT_KT][LD]
+  float* merge = reinterpret_cast<float*>(dt_smem);      // reused after the loop: [warp][16][HD + 2]
+
+  const int split = blockIdx.x, row = blockIdx.z;
+  const int group = n_heads / n_kv_heads;
+  const int chunks = (group + 15) / 16;
+  const int kvh = blockIdx.y / chunks, h0 = (blockIdx.y % chunks) * 16;
+  const int ng = min(16, group - h0);
+  const int head0 = kvh * group + h0;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int page_mask = (1 << page_shift) - 1;
+
+  const int pos = positions[row];
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int n = pos + 1 - lo;
+  int len = (n + n_split - 1) / n_split;
+  len = (len + DT_KT - 1) / DT_KT * DT_KT;
+  const int k_begin = lo + split * len;
+  const int k_end = min(pos + 1, k_begin + len);
+  const int n_tiles = k_end > k_begin ? (k_end - k_begin + DT_KT - 1) / DT_KT : 0;
+  const int* table = block_table + static_cast<size_t>(row_request[row]) * max_blocks;
+  const size_t kv_row = static_cast<size_t>(n_kv_heads) * HD;
+
+  // the group's query heads as the rows of one 16-row tile (rows past the group are zero)
+  for (int c = tid; c < 16 * CH; c += DT_THREADS) {
+    const int r = c / CH, ch = c % CH;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < ng)
+      v = *reinterpret_cast<const uint4*>(q + static_cast<size_t>(row) * q_stride + static_cast<size_t>(head0 + r) * HD + ch * 8);
+    *reinterpret_cast<uint4*>(Qs + r * LD + ch * 8) = v;
+  }
+  __syncthreads();
+  uint32_t qf[KS][4];
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+    const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
+    const int c = ks * 16 + (lane >> 4) * 8;
+    dt_ldmatrix_x4(qf[ks], Qs + r * LD + c);
+  }
+
+  bf16* my = KV + static_cast<size_t>(warp) * STAGES * 2 * TILE_ELEMS;
+  auto load_tile = [&](int i, int stage) {          // this warp's i-th tile: block tile i * DT_WARPS + warp
+    const int key0 = k_begin + (i * DT_WARPS + warp) * DT_KT;
+    bf16* kd = my + static_cast<size_t>(stage) * 2 * TILE_ELEMS;
+    bf16* vd = kd + TILE_ELEMS;
+#pragma unroll
+    for (int c = lane; c < DT_KT * CH; c += 32) {
+      const int r = c / CH, ch = c % CH;
+      const int key = key0 + r;
+      const bool ok = key < k_end;
+      size_t off = 0;
+      if (ok) {
+        const size_t slot = (static_cast<size_t>(table[key >> page_shift]) << page_shift) + (key & page_mask);
+        off = slot * kv_row + static_cast<size_t>(kvh) * HD + ch * 8;
+      }
+      dt_cp_async16(kd + r * LD + ch * 8, k_cache + off, ok);
+      dt_cp_async16(vd + r * LD + ch * 8, v_cache + off, ok);
+    }
+  };
+  const int my_tiles = n_tiles > warp ? (n_tiles - warp + DT_WARPS - 1) / DT_WARPS : 0;
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < my_tiles) load_tile(s, s);
+    asm volatile("cp.async.commit_group;\n" ::);
+  }
+
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+
+  for (int i = 0; i < my_tiles; ++i) {
+    const int stage = i % STAGES;
+    if (i + STAGES - 1 < my_tiles) load_tile(i + STAGES - 1, (i + STAGES - 1) % STAGES);
+    asm volatile("cp.async.commit_group;\n" ::);
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(STAGES - 1));
+    __syncwarp();
+    const bf16* kt = my + static_cast<size_t>(stage) * 2 * TILE_ELEMS;
+    const bf16* vt = kt + TILE_ELEMS;
+    const int key0 = k_begin + (i * DT_WARPS + warp) * DT_KT;
+
+    float s[DT_KT / 8][4];
+#pragma unroll
+    for (int j = 0; j < DT_KT / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f; }
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+      for (int np = 0; np < DT_KT / 16; ++np) {
+        uint32_t kb[4];
+        const int key = np * 16 + (lane & 7) + (lane >> 4) * 8;
+        const int c = ks * 16 + ((lane >> 3) & 1) * 8;
+        dt_ldmatrix_x4(kb, kt + key * LD + c);
+        dt_mma(s[2 * np], qf[ks], kb[0], kb[1]);
+        dt_mma(s[2 * np + 1], qf[ks], kb[2], kb[3]);
+      }
+    }
+    const bool edge = key0 + DT_KT > k_end;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < DT_KT / 8; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float v = s[j][e] * scale_log2;
+        if (edge && key0 + j * 8 + 2 * t + (e & 1) >= k_end) v = -INFINITY;
+        s[j][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    }
+    float corr[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      const float m_new = fmaxf(m_run[h], mx[h]);       // finite: the first key of every tile is in range
+      corr[h] = exp2f(m_run[h] - m_new);
+      m_run[h] = m_new;
+      mx[h] = m_new;
+    }
+    float ls[2] = {0.0f, 0.0f};
+    uint32_t pf[DT_KT / 16][4];
+#pragma unroll
+    for (int j = 0; j < DT_KT / 8; ++j) {
+      const float p0 = exp2f(s[j][0] - mx[0]), p1 = exp2f(s[j][1] - mx[0]);
+      const float p2 = exp2f(s[j][2] - mx[1]), p3 = exp2f(s[j][3] - mx[1]);
+      ls[0] += p0 + p1;
+      ls[1] += p2 + p3;
+      pf[j >> 1][(j & 1) * 2] = dt_pack(p0, p1);
+      pf[j >> 1][(j & 1) * 2 + 1] = dt_pack(p2, p3);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      ls[h] += __shfl_xor_sync(0xffffffffu, ls[h], 1);
+      ls[h] += __shfl_xor_sync(0xffffffffu, ls[h], 2);
+      l_run[h] = l_run[h] * corr[h] + ls[h];
+    }
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j) {
+      o[j][0] *= corr[0]; o[j][1] *= corr[0];
+      o[j][2] *= corr[1]; o[j][3] *= corr[1];
+    }
+#pragma unroll
+    for (int kk = 0; kk < DT_KT / 16; ++kk) {
+#pragma unroll
+      for (int dp = 0; dp < HD / 16; ++dp) {
+        uint32_t vb[4];
+        const int key = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int c = dp * 16 + (lane >> 4) * 8;
+        dt_ldmatrix_x4_trans(vb, vt + key * LD + c);
+        dt_mma(o[2 * dp], pf[kk], vb[0], vb[1]);
+        dt_mma(o[2 * dp + 1], pf[kk], vb[2], vb[3]);
+      }
+    }
+    __syncwarp();        // the warp is done with this stage before a later prefetch overwrites it
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::);
+  __syncthreads();       // every warp has left the pipeline buffers: they become the merge area
+
+  constexpr int REC = HD + 2;
+  float* mine = merge + static_cast<size_t>(warp) * 16 * REC;
+#pragma unroll
+  for (int j = 0; j < HD / 8; ++j) {
+    const int d = j * 8 + 2 * t;
+    mine[g * REC + d] = o[j][0];
+    mine[g * REC + d + 1] = o[j][1];
+    mine[(g + 8) * REC + d] = o[j][2];
+    mine[(g + 8) * REC + d + 1] = o[j][3];
+  }
+  if (t == 0) {
+    mine[g * REC + HD] = m_run[0];
+    mine[g * REC + HD + 1] = l_run[0];
+    mine[(g + 8) * REC + HD] = m_run[1];
+    mine[(g + 8) * REC + HD + 1] = l_run[1];
+  }
+  __syncthreads();
+  for (int idx = tid; idx < ng * HD; idx += DT_THREADS) {
+    const int r = idx / HD, d = idx % HD;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DT_WARPS; ++w) mm = fmaxf(mm, merge[(w * 16 + r) * REC + HD]);
+    float a = 0.0f, ll = 0.0f;
+#pragma unroll
+    for (int w = 0; w < DT_WARPS; ++w) {
+      const float* src = merge + (w * 16 + r) * REC;
+      const float c = mm == -INFINITY ? 0.0f : exp2f(src[HD] - mm);
+      a += src[d] * c;
+      ll += src[HD + 1] * c;
+    }
+    const int head = head0 + r;
+    if (n_split == 1) {
+      out[static_cast<size_t>(row) * out_stride + static_cast<size_t>(head) * HD + d] = __float2bfloat16_rn(a / ll);
+    } else {
+      float* dst = part + ((static_cast<size_t>(row) * n_heads + head) * n_split + split) * REC;
+      dst[d] = a;
+      if (d == 0) {
+        dst[HD] = mm;
+        dst[HD + 1] = ll;
+      }
+    }
+  }
+}
+
+template <int HD, int STAGES>
+int launch_decode_tc(const void* q, int q_stride, const void* kc, const void* vc, const int* block_table, int max_blocks,
+                     const int* positions, const int* row_request, void* out, int out_stride, float* part, int rows,
+                     int n_heads, int n_kv_heads, int page_shift, float scale, int window, int n_split,
+                     cudaStream_t stream) {
+  constexpr size_t pipe = static_cast<size_t>(16 + DT_WARPS * STAGES * 2 * DT_KT) * (HD + 8) * sizeof(bf16);
+  constexpr size_t mrg = static_cast<size_t>(DT_WARPS) * 16 * (HD + 2) * sizeof(float);
+  constexpr size_t smem = pipe > mrg ? pipe : mrg;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_tc_kernel<HD, STAGES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  const int group = n_heads / n_kv_heads;
+  dim3 grid(n_split, n_kv_heads * ((group + 15) / 16), rows);
+  decode_attention_tc_kernel<HD, STAGES><<<grid, DT_THREADS, smem, stream>>>(
+      static_cast<const bf16*>(q), q_stride, static_cast<const bf16*>(kc), static_cast<const bf16*>(vc), block_table,
+      max_blocks, positions, row_request, static_cast<bf16*>(out), out_stride, part, n_heads, n_kv_heads, page_shift,
+      scale * 1.4426950408889634f, window, n_split);
+  int rc = launch_status();
+  if (rc != 0 || n_split == 1) return rc;
+  dim3 cgrid(n_heads, rows);
+  const int cthreads = HD <= 32 ? 32 : (HD <= 64 ? 64 : 128);
+  attention_combine_kernel<bf16><<<cgrid, cthreads, 0, stream>>>(part, static_cast<bf16*>(out), out_stride, n_heads, HD,
+                                                                n_split);
+  return launch_status();
+}
+
 }  // namespace dl
 
 // Floats of scratch that `dl_paged_attention_decode` needs for n_split > 1.
@@ -305,4 +588,37 @@ DL_EXPORT int dl_paged_attention_decode(int dtype, const void* q, int q_stride, 
                                        out, out_stride, part, rows, n_heads, n_kv_heads, head_dim, page_size, scale,
                                        window, n_split, stream);
   return DL_ERR_UNSUPPORTED;
+}
+
+// The tensor-core variant: bfloat16, head_dim a multiple of 16 up to 128, q rows 16-byte aligned. Same
+// arguments and scratch as dl_paged_attention_decode.
+DL_EXPORT int dl_paged_attention_decode_tc(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                                           const int* block_table, int max_blocks, const int* positions,
+                                           const int* row_request, void* out, int out_stride, float* part, int rows,
+                                           int n_heads, int n_kv_heads, int head_dim, int page_size, float scale,
+                                           int window, int n_split, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  int page_shift = 0;
+  while ((1 << page_shift) < page_size) ++page_shift;
+  if ((1 << page_shift) != page_size || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || n_split < 1 || rows > 65535 ||
+      (q_stride & 7) || (n_split > 1 && part == nullptr))
+    return DL_ERR_UNSUPPORTED;
+#define DL_CASE(H, S)                                                                                                 \
+  case H:                                                                                                             \
+    return dl::launch_decode_tc<H, S>(q, q_stride, k_cache, v_cache, block_table, max_blocks, positions, row_request, \
+                                      out, out_stride, part, rows, n_heads, n_kv_heads, page_shift, scale, window,    \
+                                      n_split, stream)
+  switch (head_dim) {
+    DL_CASE(16, 4);
+    DL_CASE(32, 4);
+    DL_CASE(48, 3);
+    DL_CASE(64, 3);
+    DL_CASE(80, 3);
+    DL_CASE(96, 2);
+    DL_CASE(112, 2);
+    DL_CASE(128, 2);
+    default:
+      return DL_ERR_UNSUPPORTED;
+  }
+#undef DL_CASE
 }

@@ -1,0 +1,203 @@
+// y = x W^T for few rows (decode): a weight-streaming matrix product, bf16 operands, fp32 accumulation.
+//
+// With M <= 64 rows the product is bound by reading W once from HBM, so the kernel is built around
+// that stream. It computes y^T = W x^T on the tensor cores (mma.sync m16n8k16): the 16 rows of the
+// A operand are 16 output features (rows of W, contiguous in K), the 8 columns of the B operand are 8
+// batch rows. A block owns FT = 16 * MT features; its 8 warps split K between them in blocks of 64, each
+// lane reading whole 16-byte pieces of a weight row (the k order inside a 32-wide block is permuted
+// identically for W and x, which leaves the dot products unchanged), with no shared-memory staging. The
+// warps' partial sums are added in shared memory in a fixed order. Small N can also split K over
+// gridDim.y blocks, which then write fp32 partial results [split][M][N] that the consumer adds up in a
+// fixed order (the residual-add + RMSNorm kernel does), so results never depend on timing.
+//
+// Epilogues: bf16 or fp32 store, or SwiGLU: W = [Wg; Wu], a block takes 8 gate rows and the 8 matching up
+// rows and stores silu(g) * u (the reference's matmul_gated, dynacore/include/dynacore/device/device.h:188-199).
+#include "common.cuh"
+
+namespace dl {
+
+constexpr int SK_WARPS = 8;
+constexpr int SK_THREADS = SK_WARPS * 32;
+constexpr int SK_KB = 64;          // k per block: two 16-byte pieces per lane and row
+
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+enum { SK_OUT_BF16 = 0, SK_OUT_F32 = 1, SK_OUT_SWIGLU = 2 };
+
+// MT: m16 tiles (16 features each) per block; NT: n8 tiles (8 batch rows each).
+template <int MT, int NT>
+__global__ void __launch_bounds__(SK_THREADS)
+gemm_skinny_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w, void* __restrict__ y, int ldy,
+                   int M, int N, int K, int mode, float out_scale, long long split_stride) {
+  extern __shared__ float red[];     // [SK_WARPS][MT * 16][NT * 8]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int f0 = blockIdx.x * (MT * 16);
+  const int n_split = gridDim.y, split = blockIdx.y;
+  const int half = N / 2;            // SwiGLU: gate rows [0, half), up rows [half, N)
+
+  // the weight rows of this lane: features f0 + mt*16 + g and + 8
+  const bf16* wrow[MT][2];
+  bool wok[MT][2];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      int f;
+      if (mode == SK_OUT_SWIGLU) {
+        const int j = blockIdx.x * (MT * 8) + mt * 8 + g;   // gate row j, up row half + j
+        f = h == 0 ? j : half + j;
+        wok[mt][h] = j < half;
+      } else {
+        f = f0 + mt * 16 + g + h * 8;
+        wok[mt][h] = f < N;
+      }
+      wrow[mt][h] = w + static_cast<size_t>(wok[mt][h] ? f : 0) * K;
+    }
+  }
+  const bf16* xrow[NT];
+  bool xok[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const int b = nt * 8 + g;
+    xok[nt] = b < M;
+    xrow[nt] = x + static_cast<size_t>(xok[nt] ? b : 0) * ldx;
+  }
+
+  float acc[MT][NT][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) { acc[mt][nt][0] = acc[mt][nt][1] = acc[mt][nt][2] = acc[mt][nt][3] = 0.0f; }
+
+  // K range of this block, in blocks of 64; warps take blocks round-robin
+  const int nblk = (K + SK_KB - 1) / SK_KB;
+  const int per = (nblk + n_split - 1) / n_split;
+  const int blk_begin = split * per, blk_end = min(nblk, blk_begin + per);
+#pragma unroll 2
+  for (int blk = blk_begin + warp; blk < blk_end; blk += SK_WARPS) {
+    const int k0 = blk * SK_KB + 8 * t;
+    const bool ok0 = k0 + 8 <= K, ok1 = k0 + 32 + 8 <= K;
+    uint4 a[MT][2][2], bq[NT][2];
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        a[mt][h][0] = (wok[mt][h] && ok0) ? ld_stream16(wrow[mt][h] + k0) : zero;
+        a[mt][h][1] = (wok[mt][h] && ok1) ? ld_stream16(wrow[mt][h] + k0 + 32) : zero;
+      }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      bq[nt][0] = (xok[nt] && ok0) ? *reinterpret_cast<const uint4*>(xrow[nt] + k0) : zero;
+      bq[nt][1] = (xok[nt] && ok1) ? *reinterpret_cast<const uint4*>(xrow[nt] + k0 + 32) : zero;
+    }
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          // 16-byte piece = words (x, y, z, w) = k pairs; one mma takes (x, y), the next (z, w)
+          mma16816(acc[mt][nt], a[mt][0][c].x, a[mt][1][c].x, a[mt][0][c].y, a[mt][1][c].y, bq[nt][c].x, bq[nt][c].y);
+          mma16816(acc[mt][nt], a[mt][0][c].z, a[mt][1][c].z, a[mt][0][c].w, a[mt][1][c].w, bq[nt][c].z, bq[nt][c].w);
+        }
+      }
+    }
+  }
+
+  // warps -> shared; c0,c1: (feature g, batch 2t, 2t+1); c2,c3: (feature g + 8, same batch)
+  constexpr int FT = MT * 16, BT = NT * 8;
+  float* mine = red + static_cast<size_t>(warp) * FT * BT;
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int b = nt * 8 + 2 * t;
+      mine[(mt * 16 + g) * BT + b] = acc[mt][nt][0];
+      mine[(mt * 16 + g) * BT + b + 1] = acc[mt][nt][1];
+      mine[(mt * 16 + g + 8) * BT + b] = acc[mt][nt][2];
+      mine[(mt * 16 + g + 8) * BT + b + 1] = acc[mt][nt][3];
+    }
+  __syncthreads();
+  if (mode == SK_OUT_SWIGLU) {
+    // tile rows [mt*16 + i] = gate j, [mt*16 + 8 + i] = up j, j = blockIdx.x * MT*8 + mt*8 + i
+    for (int idx = threadIdx.x; idx < MT * 8 * BT; idx += SK_THREADS) {
+      const int b = idx / (MT * 8), jj = idx % (MT * 8);
+      const int mt = jj / 8, i = jj % 8;
+      const int j = blockIdx.x * (MT * 8) + jj;
+      if (b >= M || j >= half) continue;
+      float gate = 0.0f, up = 0.0f;
+#pragma unroll
+      for (int wv = 0; wv < SK_WARPS; ++wv) {
+        gate += red[(static_cast<size_t>(wv) * FT + mt * 16 + i) * BT + b];
+        up += red[(static_cast<size_t>(wv) * FT + mt * 16 + 8 + i) * BT + b];
+      }
+      const float s = gate / (1.0f + expf(-gate));
+      static_cast<bf16*>(y)[static_cast<size_t>(b) * ldy + j] = __float2bfloat16_rn(s * up);
+    }
+    return;
+  }
+  for (int idx = threadIdx.x; idx < FT * BT; idx += SK_THREADS) {
+    const int b = idx / FT, fi = idx % FT;      // consecutive threads -> consecutive features of one batch row
+    const int f = f0 + fi;
+    if (b >= M || f >= N) continue;
+    float v = 0.0f;
+#pragma unroll
+    for (int wv = 0; wv < SK_WARPS; ++wv) v += red[(static_cast<size_t>(wv) * FT + fi) * BT + b];
+    v *= out_scale;
+    if (mode == SK_OUT_F32)
+      static_cast<float*>(y)[static_cast<size_t>(split) * split_stride + static_cast<size_t>(b) * ldy + f] = v;
+    else
+      static_cast<bf16*>(y)[static_cast<size_t>(b) * ldy + f] = __float2bfloat16_rn(v);
+  }
+}
+
+template <int MT, int NT>
+int launch_skinny(const void* x, int ldx, const void* w, void* y, int ldy, int M, int N, int K, int mode,
+                  float out_scale, int n_split, long long split_stride, cudaStream_t stream) {
+  const int feats = mode == SK_OUT_SWIGLU ? N / 2 : N;
+  const int per_block = mode == SK_OUT_SWIGLU ? MT * 8 : MT * 16;
+  dim3 grid((feats + per_block - 1) / per_block, n_split);
+  const size_t smem = static_cast<size_t>(SK_WARPS) * MT * 16 * NT * 8 * sizeof(float);
+  static bool configured = false;
+  if (smem > 48 * 1024 && !configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  gemm_skinny_kernel<MT, NT><<<grid, SK_THREADS, smem, stream>>>(
+      static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), y, ldy, M, N, K, mode, out_scale, split_stride);
+  return launch_status();
+}
+
+}  // namespace dl
+
+// x: bf16 [M, K] rows of ldx elements (16-byte aligned rows), w: bf16 [N, K] contiguous, K a multiple of 8,
+// M <= 64. mode 0: y bf16 [M, N]; mode 1: y fp32, n_split partial results of [M, ldy] floats each,
+// split_stride floats apart; mode 2: w = [gate; up] (N even), y bf16 [M, N / 2] = silu(x Wg^T) * (x Wu^T).
+// n_split > 1 needs mode 1.
+DL_EXPORT int dl_gemm_skinny(const void* x, int ldx, const void* w, void* y, int ldy, int M, int N, int K, int mode,
+                             float out_scale, int n_split, long long split_stride, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 64 || K <= 0 || (K & 7) || (ldx & 7) || n_split < 1 || n_split > 64 || (n_split > 1 && mode != dl::SK_OUT_F32) ||
+      (mode == dl::SK_OUT_SWIGLU && (N & 1)) || mode < 0 || mode > 2)
+    return DL_ERR_UNSUPPORTED;
+  if (M <= 8) return dl::launch_skinny<1, 1>(x, ldx, w, y, ldy, M, N, K, mode, out_scale, n_split, split_stride, stream);
+  if (M <= 16) return dl::launch_skinny<1, 2>(x, ldx, w, y, ldy, M, N, K, mode, out_scale, n_split, split_stride, stream);
+  if (M <= 32) return dl::launch_skinny<2, 4>(x, ldx, w, y, ldy, M, N, K, mode, out_scale, n_split, split_stride, stream);
+  return dl::launch_skinny<2, 8>(x, ldx, w, y, ldy, M, N, K, mode, out_scale, n_split, split_stride, stream);
+}

@@ -12,10 +12,20 @@
 
 namespace dl {
 
+// delta may come in `parts` partial sums, `part_stride` elements apart (a split-K matrix product
+// leaves them so); they are added in index order, so the result does not depend on timing.
+template <typename TD>
+__device__ __forceinline__ float delta_at(const TD* dr, int i, int parts, size_t part_stride) {
+  float d = to_float(dr[i]);
+  for (int p = 1; p < parts; ++p) d += to_float(dr[p * part_stride + i]);
+  return d;
+}
+
 template <typename TO, typename TD>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, float delta_scale,
                                const float* __restrict__ w, float eps, TO* __restrict__ out,
-                               const int* __restrict__ rows, int width, int write_residual) {
+                               const int* __restrict__ rows, int width, int write_residual, int parts,
+                               size_t part_stride) {
   __shared__ float red[33];
   const int r = blockIdx.x;
   const size_t src = rows ? static_cast<size_t>(rows[r]) : static_cast<size_t>(r);
@@ -25,7 +35,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ del
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     float v = xr[i];
     if (dr) {
-      v = fmaf(delta_scale, to_float(dr[i]), v);
+      v = fmaf(delta_scale, delta_at(dr, i, parts, part_stride), v);
       if (write_residual) xr[i] = v;
     }
     ss = fmaf(v, v, ss);
@@ -35,29 +45,36 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ del
   TO* orow = out + static_cast<size_t>(r) * width;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     float v = xr[i];
-    if (dr && !write_residual) v = fmaf(delta_scale, to_float(dr[i]), v);
+    if (dr && !write_residual) v = fmaf(delta_scale, delta_at(dr, i, parts, part_stride), v);
     orow[i] = from_float<TO>(v * inv * w[i]);
   }
 }
 
 // x += scale * delta, for a pending residual that no norm follows.
 template <typename TD>
-__global__ void residual_add_kernel(float* __restrict__ x, const TD* __restrict__ delta, float scale, size_t n) {
+__global__ void residual_add_kernel(float* __restrict__ x, const TD* __restrict__ delta, float scale, size_t n,
+                                    int parts, size_t part_stride) {
   const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i < n) x[i] = fmaf(scale, to_float(delta[i]), x[i]);
+  if (i < n) {
+    float d = to_float(delta[i]);
+    for (int p = 1; p < parts; ++p) d += to_float(delta[p * part_stride + i]);
+    x[i] = fmaf(scale, d, x[i]);
+  }
 }
 
 }  // namespace dl
 
-// out_dtype / delta_dtype: 0 = float32, 1 = bfloat16. delta and rows may be null.
+// out_dtype / delta_dtype: 0 = float32, 1 = bfloat16. delta and rows may be null. delta_parts >= 1 partial
+// sums of delta lie delta_part_stride elements apart.
 DL_EXPORT int dl_rmsnorm(int out_dtype, int delta_dtype, float* x, const void* delta, float delta_scale,
                          const float* w, float eps, void* out, const int* rows, int n_rows, int width,
-                         int write_residual, cudaStream_t stream) {
+                         int write_residual, int delta_parts, long long delta_part_stride, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
 #define DL_LAUNCH(TO, TD)                                                                            \
   dl::rmsnorm_kernel<TO, TD><<<n_rows, threads, 0, stream>>>(x, static_cast<const TD*>(delta), delta_scale, w, eps, \
-                                                             static_cast<TO*>(out), rows, width, write_residual)
+                                                             static_cast<TO*>(out), rows, width, write_residual, \
+                                                             delta_parts, static_cast<size_t>(delta_part_stride))
   if (out_dtype == 0 && delta_dtype == 0) DL_LAUNCH(float, float);
   else if (out_dtype == 1 && delta_dtype == 1) DL_LAUNCH(dl::bf16, dl::bf16);
   else if (out_dtype == 1 && delta_dtype == 0) DL_LAUNCH(dl::bf16, float);
@@ -68,12 +85,12 @@ DL_EXPORT int dl_rmsnorm(int out_dtype, int delta_dtype, float* x, const void* d
 }
 
 DL_EXPORT int dl_residual_add(int delta_dtype, float* x, const void* delta, float scale, long long n,
-                              cudaStream_t stream) {
+                              int delta_parts, long long delta_part_stride, cudaStream_t stream) {
   if (n <= 0) return 0;
   const int threads = 256;
   const unsigned blocks = static_cast<unsigned>((n + threads - 1) / threads);
-  if (delta_dtype == 0) dl::residual_add_kernel<float><<<blocks, threads, 0, stream>>>(x, static_cast<const float*>(delta), scale, static_cast<size_t>(n));
-  else if (delta_dtype == 1) dl::residual_add_kernel<dl::bf16><<<blocks, threads, 0, stream>>>(x, static_cast<const dl::bf16*>(delta), scale, static_cast<size_t>(n));
+  if (delta_dtype == 0) dl::residual_add_kernel<float><<<blocks, threads, 0, stream>>>(x, static_cast<const float*>(delta), scale, static_cast<size_t>(n), delta_parts, static_cast<size_t>(delta_part_stride));
+  else if (delta_dtype == 1) dl::residual_add_kernel<dl::bf16><<<blocks, threads, 0, stream>>>(x, static_cast<const dl::bf16*>(delta), scale, static_cast<size_t>(n), delta_parts, static_cast<size_t>(delta_part_stride));
   else return DL_ERR_UNSUPPORTED;
   return dl::launch_status();
 }

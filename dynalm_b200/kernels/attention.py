@@ -17,12 +17,17 @@ SM_COUNT = 148            # B200
 MAX_SPLITS = 32
 
 
-def decode_splits(rows: int, n_heads: int, n_kv_heads: int, max_kv_len: int) -> int:
-    """Key splits per row so that the grid fills the GPU about twice, each split at least 256 keys."""
+def decode_splits(rows: int, n_heads: int, n_kv_heads: int, max_kv_len: int, tensor_cores: bool = True) -> int:
+    """Key splits per row so that the grid fills the GPU about twice, each split at least 128 keys
+    (one 32-key tile for each of a block's four warps)."""
     group = n_heads // n_kv_heads
-    blocks = rows * n_kv_heads * (-(-group // 4))
+    blocks = rows * n_kv_heads * (-(-group // (16 if tensor_cores else 4)))
     want = -(-2 * SM_COUNT // max(blocks, 1))
-    return max(1, min(want, max(1, max_kv_len // 256), MAX_SPLITS))
+    return max(1, min(want, max(1, max_kv_len // 128), MAX_SPLITS))
+
+
+def decode_uses_tensor_cores(spec) -> bool:
+    return spec.head_dim <= 128
 
 
 def decode_plan(ctx, spec) -> int:
@@ -32,7 +37,7 @@ def decode_plan(ctx, spec) -> int:
     bucket = 256
     while bucket < span:
         bucket *= 2
-    return decode_splits(ctx.num_tokens, spec.num_heads, spec.num_kv_heads, bucket)
+    return decode_splits(ctx.num_tokens, spec.num_heads, spec.num_kv_heads, bucket, decode_uses_tensor_cores(spec))
 
 
 def use_decode_kernel(ctx, spec, dtype: torch.dtype, page_size: int) -> bool:
@@ -64,5 +69,5 @@ def paged_attention(qkv: torch.Tensor, cache, ctx, out: torch.Tensor, spec, runt
                                ops.decode_scratch_floats(most_rows, spec.num_heads, spec.head_dim, MAX_SPLITS))
     ops.paged_attention_decode(qkv, k_cache, v_cache, cache.block_table, ctx.positions, ctx.row_request, out, scratch,
                                spec.num_heads, spec.num_kv_heads, spec.head_dim, cache.page_size, float(spec.scale),
-                               spec.window, n_split)
+                               spec.window, n_split, tensor_cores=decode_uses_tensor_cores(spec) and qkv.stride(0) % 8 == 0)
     return True

@@ -1,10 +1,12 @@
 """y = x W^T (+ bias): picks the matrix-product kernel for a dtype and shape.
 
 float32 always runs the plain fixed-order kernel (csrc/gemm_simt.cu): the true 32-bit path uses no
-tensor cores and no reduced-precision mode. bfloat16 runs the library product (cuBLAS through torch),
-which is where the reference's GPU path calls a library too (ggml_mul_mat,
-dynacore/src/gpu/ggml_graph.cpp:278-292), with fp32 accumulation; shapes the library call cannot
-express (a bias, a float32 output from bfloat16 operands on an older torch) run the plain kernel.
+tensor cores and no reduced-precision mode. bfloat16 with at most 64 rows (decode) runs the
+weight-streaming kernel (csrc/gemm_skinny.cu), which can also apply SwiGLU on the way out or leave
+split-K partial sums for the consumer to add. bfloat16 with more rows runs the library product (cuBLAS
+through torch), which is where the reference's GPU path calls a library too (ggml_mul_mat,
+dynacore/src/gpu/ggml_graph.cpp:278-292), with fp32 accumulation. Shapes these cannot express (a bias,
+a K that is no multiple of 8) run the plain kernel.
 """
 
 from __future__ import annotations
@@ -15,6 +17,7 @@ import torch
 
 from . import ops
 
+SM_COUNT = 148
 _mm_out_dtype_ok: Optional[bool] = None
 LIBRARY_CALLS = 0    # matrix products handed to the library so far
 
@@ -35,15 +38,33 @@ def _mm_f32_out(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
         raise
 
 
+def skinny_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and x.shape[0] <= ops.SKINNY_MAX_ROWS and x.shape[1] % 8 == 0
+            and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.is_contiguous())
+
+
+def split_count(n_features: int, k: int, rows: int) -> int:
+    """How many blocks split K for a small N, so that the grid covers the GPU about twice and every
+    warp of a block still gets at least one 64-wide piece of K."""
+    tiles = -(-n_features // (16 if rows <= 16 else 32))
+    want = -(-2 * SM_COUNT // tiles)
+    return max(1, min(want, 8, k // 512))
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
            out_scale: float = 1.0) -> torch.Tensor:
     """out[M, N] = (x[M, K] @ w[N, K].T + bias[N]) * out_scale. x and w share a dtype; out may be
     float32 for bfloat16 operands (logits)."""
-    if x.dtype == torch.float32 or bias is not None or out_scale != 1.0 or not x.is_contiguous() \
-            or not out.is_contiguous():
+    global LIBRARY_CALLS
+    if x.dtype == torch.float32 or bias is not None:
         ops.gemm_simt(x, w, out, bias, out_scale)
         return out
-    global LIBRARY_CALLS
+    if skinny_ok(x, w) and out.stride(1) == 1:
+        ops.gemm_skinny(x, w, out, "store", out_scale)
+        return out
+    if out_scale != 1.0 or not x.is_contiguous() or not out.is_contiguous():
+        ops.gemm_simt(x, w, out, bias, out_scale)
+        return out
     if out.dtype == x.dtype:
         torch.mm(x, w.t(), out=out)
         LIBRARY_CALLS += 1
@@ -53,3 +74,33 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[t
     else:
         ops.gemm_simt(x, w, out, None, 1.0)
     return out
+
+
+def linear_partial(x: torch.Tensor, w: torch.Tensor, runtime, name: str) -> torch.Tensor:
+    """x W^T whose consumer adds it into the residual stream: for few rows the product may split K
+    and come back as float32 partial sums [parts, M, N] (see ops.rmsnorm's `delta`); otherwise a
+    plain [M, N] tensor in the compute dtype."""
+    M, N = x.shape[0], w.shape[0]
+    if x.dtype == torch.bfloat16 and skinny_ok(x, w):
+        parts = split_count(N, x.shape[1], M)
+        if parts > 1:
+            flat = runtime.flat(f"{name}_parts_{N}", 8 * ops.SKINNY_MAX_ROWS * N, torch.float32)
+            out = flat[:parts * M * N].view(parts, M, N)
+            ops.gemm_skinny(x, w, out, "store", 1.0)
+            return out
+    out = runtime.buffer(name, (M, N))
+    return linear(x, w, out)
+
+
+def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, runtime, inner: int) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) with w_gate_up = [Wg; Wu]: fused in the product's epilogue for few
+    bfloat16 rows, else the product followed by the activation kernel."""
+    rows = x.shape[0]
+    act = runtime.buffer("ffn_act", (rows, inner))
+    if x.dtype == torch.bfloat16 and skinny_ok(x, w_gate_up):
+        ops.gemm_skinny(x, w_gate_up, act, "swiglu")
+        return act
+    gate_up = runtime.buffer("ffn_gate_up", (rows, 2 * inner))
+    linear(x, w_gate_up, gate_up)
+    ops.silu_mul(gate_up, act)
+    return act

@@ -23,17 +23,19 @@ _P, _I, _F, _L = c_void_p, c_int, c_float, c_longlong
 _SIGNATURES = {
     "embedding": {"dl_embed": [_I, _P, _P, _P, _I, _I, _I, _F, _P]},
     "norm": {
-        "dl_rmsnorm": [_I, _I, _P, _P, _F, _P, _F, _P, _P, _I, _I, _I, _P],
-        "dl_residual_add": [_I, _P, _P, _F, _L, _P],
+        "dl_rmsnorm": [_I, _I, _P, _P, _F, _P, _F, _P, _P, _I, _I, _I, _I, _L, _P],
+        "dl_residual_add": [_I, _P, _P, _F, _L, _I, _L, _P],
     },
     "activation": {"dl_silu_mul": [_I, _P, _P, _I, _I, _P]},
     "rope_cache": {"dl_rope_cache_write": [_I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _F, _I, _I, _I, _I, _I, _I, _P]},
     "attention_generic": {
         "dl_paged_attention_generic": [_I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P]},
     "attention_decode": {
-        "dl_paged_attention_decode": [_I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P]},
+        "dl_paged_attention_decode": [_I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+        "dl_paged_attention_decode_tc": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P]},
     "attention_prefill": {
         "dl_paged_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P]},
+    "gemm_skinny": {"dl_gemm_skinny": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _L, _P]},
     "gemm_simt": {"dl_gemm_simt": [_I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _P]},
     "sampling": {
         "dl_argmax": [_P, _I, _I, _I, _P, _P],
@@ -113,7 +115,8 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
     """out[r] = rmsnorm(x[src] + delta_scale * delta[src]) * weight, src = rows[r] or r.
 
     x: float32 [n, width] residual stream, updated in place with the sum when `delta` is given and
-    `write_residual`; delta: [n, width] of either dtype; weight: float32 [width]; out: [n_out, width]."""
+    `write_residual`; delta: [n, width] of either dtype, or [parts, n, width] partial sums that are
+    added in order; weight: float32 [width]; out: [n_out, width]."""
     _cuda(x, weight, out, delta, rows)
     width = x.shape[1]
     if x.dtype != torch.float32 or weight.dtype != torch.float32 or not x.is_contiguous() or not out.is_contiguous():
@@ -127,21 +130,32 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
         write_residual = False
     elif x.shape[0] < n_rows:
         raise InvalidArgument("rmsnorm: fewer input rows than output rows")
-    if delta is not None and (not delta.is_contiguous() or delta.shape[1] != width):
-        raise InvalidArgument("rmsnorm: delta must be contiguous [n, width]")
+    parts, part_stride = _delta_parts(delta, width, "rmsnorm")
     dd = dtype_code(delta.dtype) if delta is not None else dtype_code(out.dtype)
     _check(_fn("norm", "dl_rmsnorm")(dtype_code(out.dtype), dd, _p(x), _p(delta), delta_scale, _p(weight), eps,
-                                      _p(out), _p(rows), n_rows, width, 1 if write_residual else 0, _stream()),
-           "rmsnorm")
+                                      _p(out), _p(rows), n_rows, width, 1 if write_residual else 0, parts, part_stride,
+                                      _stream()), "rmsnorm")
+
+
+def _delta_parts(delta: Optional[torch.Tensor], width: int, what: str):
+    """(number of partial sums, elements between them) of a delta that is [n, width] or [parts, n, width]."""
+    if delta is None:
+        return 1, 0
+    if not delta.is_contiguous() or delta.shape[-1] != width or delta.dim() not in (2, 3):
+        raise InvalidArgument(f"{what}: delta must be contiguous [n, width] or [parts, n, width]")
+    if delta.dim() == 3:
+        return delta.shape[0], delta.stride(0)
+    return 1, 0
 
 
 def residual_add(x: torch.Tensor, delta: torch.Tensor, scale: float = 1.0) -> None:
-    """x += scale * delta over the first delta.shape[0] rows (x float32)."""
+    """x += scale * delta over delta's rows (x float32); delta may be [parts, n, width] partial sums."""
     _cuda(x, delta)
-    if x.dtype != torch.float32 or not x.is_contiguous() or not delta.is_contiguous() or x.shape[1] != delta.shape[1]:
-        raise InvalidArgument("residual_add: x float32, both contiguous, same width")
-    _check(_fn("norm", "dl_residual_add")(dtype_code(delta.dtype), _p(x), _p(delta), scale, delta.numel(), _stream()),
-           "residual_add")
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise InvalidArgument("residual_add: x float32 and contiguous")
+    parts, part_stride = _delta_parts(delta, x.shape[1], "residual_add")
+    _check(_fn("norm", "dl_residual_add")(dtype_code(delta.dtype), _p(x), _p(delta), scale, delta.numel() // parts,
+                                           parts, part_stride, _stream()), "residual_add")
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
@@ -218,9 +232,10 @@ def decode_scratch_floats(rows: int, n_heads: int, head_dim: int, n_split: int) 
 def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                            positions: torch.Tensor, row_request: torch.Tensor, out: torch.Tensor,
                            scratch: Optional[torch.Tensor], n_heads: int, n_kv_heads: int, head_dim: int,
-                           page_size: int, scale: float, window: int, n_split: int) -> None:
+                           page_size: int, scale: float, window: int, n_split: int, tensor_cores: bool = False) -> None:
     """Split-KV attention for rows that bring few tokens; see csrc/attention_decode.cu. `scratch`:
-    float32 with at least decode_scratch_floats(...) elements when n_split > 1."""
+    float32 with at least decode_scratch_floats(...) elements when n_split > 1. `tensor_cores`
+    picks the mma variant (bfloat16, head_dim up to 128)."""
     _cuda(q, k_cache, v_cache, block_table, positions, row_request, out, scratch)
     _rows_contiguous(q, "q")
     _rows_contiguous(out, "out")
@@ -236,6 +251,14 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
     need = decode_scratch_floats(rows, n_heads, head_dim, n_split)
     if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
         raise InvalidArgument(f"decode attention: scratch must be float32 with at least {need} elements")
+    if tensor_cores:
+        if q.dtype != torch.bfloat16 or head_dim > 128 or q.stride(0) % 8 or q.data_ptr() % 16:
+            raise Unsupported("decode attention (tensor cores): bfloat16, head_dim up to 128, 16-byte aligned q rows")
+        _check(_fn("attention_decode", "dl_paged_attention_decode_tc")(
+            _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), block_table.stride(0), _p(positions),
+            _p(row_request), _p(out), out.stride(0), _p(scratch), rows, n_heads, n_kv_heads, head_dim, page_size, scale,
+            window, n_split, _stream()), "paged_attention_decode_tc")
+        return
     _check(_fn("attention_decode", "dl_paged_attention_decode")(
         dtype_code(q.dtype), _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), block_table.stride(0),
         _p(positions), _p(row_request), _p(out), out.stride(0), _p(scratch), rows, n_heads, n_kv_heads, head_dim,
@@ -281,6 +304,39 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optiona
         raise InvalidArgument("gemm: bias must be float32 [N]")
     _check(_fn("gemm_simt", "dl_gemm_simt")(dtype_code(x.dtype), dtype_code(out.dtype), _p(x), x.stride(0), _p(w),
                                              _p(bias), _p(out), out.stride(0), M, N, K, out_scale, _stream()), "gemm_simt")
+
+
+SKINNY_MAX_ROWS = 64
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str = "store", out_scale: float = 1.0) -> None:
+    """Weight-streaming product for at most 64 rows, bfloat16 operands; see csrc/gemm_skinny.cu.
+
+    mode "store": out [M, N] bfloat16 or float32, or float32 [parts, M, N] to split K over `parts`
+    blocks (the consumer adds the parts); mode "swiglu": w = [gate; up], out [M, N/2] bfloat16."""
+    _cuda(x, w, out)
+    _rows_contiguous(x, "x")
+    M, K = x.shape
+    N = w.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not w.is_contiguous() or w.shape[1] != K:
+        raise InvalidArgument("gemm_skinny: x and w bfloat16, w [N, K] contiguous")
+    if M > SKINNY_MAX_ROWS or K % 8 or x.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16:
+        raise Unsupported(f"gemm_skinny: at most {SKINNY_MAX_ROWS} rows, K a multiple of 8, 16-byte aligned rows")
+    n_split, split_stride = 1, 0
+    if mode == "swiglu":
+        if N % 2 or out.shape != (M, N // 2) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
+            raise InvalidArgument("gemm_skinny: swiglu needs out [M, N/2] bfloat16")
+        code, ldy = 2, out.stride(0)
+    elif out.dim() == 3:
+        if out.dtype != torch.float32 or out.shape[1:] != (M, N) or not out.is_contiguous():
+            raise InvalidArgument("gemm_skinny: split output must be contiguous float32 [parts, M, N]")
+        code, ldy, n_split, split_stride = 1, N, out.shape[0], out.stride(0)
+    else:
+        if out.shape != (M, N) or out.stride(1) != 1 or out.dtype not in (torch.bfloat16, torch.float32):
+            raise InvalidArgument("gemm_skinny: out [M, N] bfloat16 or float32")
+        code, ldy = (0 if out.dtype == torch.bfloat16 else 1), out.stride(0)
+    _check(_fn("gemm_skinny", "dl_gemm_skinny")(_p(x), x.stride(0), _p(w), _p(out), ldy, M, N, K, code, out_scale,
+                                                 n_split, split_stride, _stream()), "gemm_skinny")
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

@@ -14,6 +14,7 @@ import torch
 
 from ..errors import Unsupported
 from ..kernels import linear, ops
+from ..kernels.gemm import linear_partial
 from .base import POSITIONS, CacheSpec, TensorDecl, register_mixer
 
 
@@ -84,6 +85,8 @@ class PagedAttention:
                              pos_scale, s.num_heads, s.num_kv_heads, s.head_dim, cache.page_size, write_cache=owns_cache)
         attn = rt.buffer("attn_out", (rows, self.q_width))
         self.attend(qkv, cache, ctx, attn)
+        if self.b_o is None:
+            return linear_partial(attn, self.w_o, rt, "mixer_out")
         out = rt.buffer("mixer_out", (rows, s.width))
         linear(attn, self.w_o, out, self.b_o)
         return out

@@ -8,7 +8,7 @@ from typing import Dict
 import torch
 
 from ..errors import Unsupported
-from ..kernels import linear, ops
+from ..kernels.gemm import linear_partial, linear_swiglu
 from .base import TensorDecl, register_feed_forward
 
 
@@ -34,11 +34,5 @@ class GatedMLP:
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         s, rt = self.spec, self.rt
-        rows = x.shape[0]
-        gate_up = rt.buffer("ffn_gate_up", (rows, 2 * s.inner))
-        linear(x, self.w_gate_up, gate_up)
-        act = rt.buffer("ffn_act", (rows, s.inner))
-        ops.silu_mul(gate_up, act)
-        out = rt.buffer("ffn_out", (rows, s.width))
-        linear(act, self.w_down, out)
-        return out
+        act = linear_swiglu(x, self.w_gate_up, rt, s.inner)
+        return linear_partial(act, self.w_down, rt, "ffn_out")

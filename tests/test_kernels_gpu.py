@@ -273,15 +273,21 @@ def test_sample_temperature_frequencies(ops):
     assert (freq - p).abs().max() < 0.015
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("dtype", DTYPES + ["tensor_cores"])
 @pytest.mark.parametrize("heads,kvh,hd,page,window,splits", [(4, 2, 16, 16, 0, 1), (6, 2, 32, 16, 0, 3), (5, 1, 48, 16, 0, 4),
                                                                (3, 3, 80, 32, 0, 2), (8, 2, 128, 16, 40, 2),
                                                                (16, 2, 64, 16, 0, 5), (32, 8, 64, 16, 0, 8),
-                                                               (4, 4, 256, 16, 0, 2), (4, 4, 64, 16, 7, 1)])
+                                                               (4, 4, 256, 16, 0, 2), (4, 4, 64, 16, 7, 1),
+                                                               (40, 2, 64, 16, 0, 3), (2, 1, 112, 64, 300, 6)])
 def test_paged_attention_decode(ops, dtype, heads, kvh, hd, page, window, splits):
     """The split-KV kernel against the same reference as the plain kernel: requests of 1, 60, 700 and
     130 tokens in scattered pages, one row each at its last position, a far key that stands out,
     any number of splits (more splits than the short requests have keys)."""
+    tc = dtype == "tensor_cores"
+    if tc:
+        dtype = torch.bfloat16
+        if hd > 128:
+            pytest.skip("the tensor-core variant holds head sizes up to 128")
     if dtype == torch.float32 and hd > 128:
         pytest.skip("the float32 instantiation holds head sizes up to 128")
     g = torch.Generator(device="cpu").manual_seed(10)
@@ -316,7 +322,7 @@ def test_paged_attention_decode(ops, dtype, heads, kvh, hd, page, window, splits
     out = torch.zeros(n, heads * hd, dtype=dtype, device=DEV)
     scratch = torch.zeros(max(1, ops.decode_scratch_floats(n, heads, hd, splits)), dtype=torch.float32, device=DEV)
     ops.paged_attention_decode(q.reshape(n, heads * hd).to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV), pos.to(DEV),
-                               req.to(DEV), out, scratch, heads, kvh, hd, page, scale, window, splits)
+                               req.to(DEV), out, scratch, heads, kvh, hd, page, scale, window, splits, tensor_cores=tc)
     got = out.double().cpu().reshape(n, heads, hd)
     for i, r in enumerate(order):
         ref = _attention_ref(q[i].double(), keys[r].double(), vals[r].double(), scale, window)
@@ -395,3 +401,39 @@ def test_paged_attention_prefill(ops, heads, kvh, hd, page, window):
                                 torch.tensor(tiles2, dtype=torch.int32).to(DEV), len(tiles2), out2, heads, kvh, hd, page,
                                 scale, window)
     assert torch.equal(out2[1:211], out[1:211])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 3072, 2048), (8, 499, 80), (7, 130, 200), (16, 96, 1000), (9, 48, 64), (33, 250, 264),
+                                   (64, 160, 96), (3, 17, 8)])
+def test_gemm_skinny(ops, M, N, K):
+    g = torch.Generator(device="cpu").manual_seed(13)
+    x = torch.randn(M, K, generator=g).to(DEV, torch.bfloat16)
+    w = torch.randn(N, K, generator=g).to(DEV, torch.bfloat16)
+    ref = x.double() @ w.double().T
+    scale = ref.abs().max().item()
+    out32 = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ops.gemm_skinny(x, w, out32, "store", 0.5)
+    assert (out32.double() - 0.5 * ref).abs().max() <= 1e-5 * scale
+    out16 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_skinny(x, w, out16)
+    assert (out16.double() - ref).abs().max() <= 1e-2 * scale
+    # x as a view with a wider row (q inside qkv), K split over 3 blocks, parts added by the consumer
+    wide = torch.zeros(M, K + 24, dtype=torch.bfloat16, device=DEV)
+    wide[:, :K] = x
+    parts = torch.empty(3, M, N, dtype=torch.float32, device=DEV)
+    ops.gemm_skinny(wide[:, :K], w, parts)
+    assert (parts.sum(0).double() - ref).abs().max() <= 1e-5 * scale
+    # fused SwiGLU: w = [gate; up]
+    if N % 2 == 0:
+        act = torch.empty(M, N // 2, dtype=torch.bfloat16, device=DEV)
+        ops.gemm_skinny(x, w, act, "swiglu")
+        gate, up = ref[:, :N // 2], ref[:, N // 2:]
+        want = gate * torch.sigmoid(gate) * up
+        assert (act.double() - want).abs().max() <= 1e-2 * max(1.0, want.abs().max().item())
+    # the consumer adds the parts in order
+    resid = torch.randn(M, N, generator=g).to(DEV)
+    wn = torch.ones(N, device=DEV)
+    normed = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    r2 = resid.clone()
+    ops.rmsnorm(r2, wn, 1e-5, normed, delta=parts, delta_scale=1.0)
+    assert (r2.double() - (resid.double() + ref)).abs().max() <= 2e-5 * max(1.0, scale)
