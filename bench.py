@@ -148,7 +148,7 @@ def main():
     cfg["num_hidden_layers"] = args.layers
     batches = [args.batch] if args.no_points else sorted({1, args.batch, 64})
     max_b = max(batches)
-    held_max = HELD + W + K + 16
+    held_max = HELD + W + K + 4 * args.batch + 96
     t_build = time.time()
     eng = Engine(config=cfg, random_seed=0, dtype="bfloat16", ctx=max_b * (-(-held_max // 16) * 16) + 4096,
                  batch=PREFILL_TOKENS, max_running=max_b,
@@ -240,7 +240,7 @@ def main():
     # ---- decode end to end through the scheduler: host ids in, host ids out, every step ----------------------
     B = args.batch
     for r in range(B):
-        eng.scheduler.submit(Request([int(t) for t in rng.randint(0, vocab, HELD)], max_new_tokens=W + K + 4))
+        eng.scheduler.submit(Request([int(t) for t in rng.randint(0, vocab, HELD)], max_new_tokens=W + K + 4 * B + 64))
     while any(s.status != "decode" or s.pending != 1 for s in eng.scheduler.running) or eng.scheduler.waiting \
             or eng.scheduler.incoming:
         eng.scheduler.step()
@@ -256,6 +256,8 @@ def main():
     e2e_s = time.perf_counter() - t0
     e2e = {"value": round(n_tok / e2e_s, 1), "unit": "tokens/s",
            "h2d_bytes_per_step": (eng.executor.h2d_bytes - h0) // K, "d2h_bytes_per_step": (eng.executor.d2h_bytes - d0) // K}
+    for s_ in list(eng.scheduler.running):
+        eng.scheduler.cancel(s_.id)
     while not eng.scheduler.idle:
         eng.scheduler.step()
 
