@@ -622,3 +622,72 @@ DL_EXPORT int dl_paged_attention_decode_tc(const void* q, int q_stride, const vo
   }
 #undef DL_CASE
 }
+
+// ------------------------------------------------------------------------------------------------
+// The entry point that allocates nothing (see dynalm_noalloc.h for who needs it and its rules).
+// ------------------------------------------------------------------------------------------------
+#include "dynalm_noalloc.h"
+
+#include <mutex>
+
+// Partial results of the split-KV kernel, for callers that have no scratch to give. In host code this
+// name is only a handle for cudaGetSymbolAddress: it is not a device address and must never be passed
+// to a kernel as one.
+static __device__ __align__(256) float dl_noalloc_scratch[DL_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {};
+std::mutex g_noalloc_mutex;
+
+// The device address of the array on the current device, looked up once per device.
+int noalloc_scratch(float** ptr) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= kMaxDevices) return DL_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), dl_noalloc_scratch);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    g_noalloc_ptr[dev] = p;
+  }
+  *ptr = g_noalloc_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+DL_EXPORT int dl_paged_attention_decode_noalloc(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                                                const int* block_table, int max_blocks, const int* positions,
+                                                const int* row_request, void* out, int out_stride, int rows,
+                                                int n_heads, int n_kv_heads, int head_dim, int page_size, float scale,
+                                                int window, int n_split, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (n_split < 1 || n_heads <= 0 || head_dim <= 0) return DL_ERR_UNSUPPORTED;
+  const long long need = dl_paged_attention_decode_scratch(rows, n_heads, head_dim, n_split);
+  if (need > DL_NOALLOC_SCRATCH_FLOATS) return DL_ERR_NOALLOC_TOO_LARGE;
+  float* part = nullptr;
+  if (need > 0) {
+    const int rc = noalloc_scratch(&part);
+    if (rc != 0) return rc;
+  }
+  return dl_paged_attention_decode_tc(q, q_stride, k_cache, v_cache, block_table, max_blocks, positions, row_request,
+                                      out, out_stride, part, rows, n_heads, n_kv_heads, head_dim, page_size, scale,
+                                      window, n_split, stream);
+}
+
+DL_EXPORT const char* dl_noalloc_strerror(int code) {
+  switch (code) {
+    case 0:
+      return "ok";
+    case DL_ERR_NOALLOC_TOO_LARGE:
+      return "the call needs more scratch than the library's built-in array holds (rows * n_heads * n_split * "
+             "(head_dim + 2) floats, at most 1048576): lower n_split or pass fewer rows per call";
+    case DL_ERR_UNSUPPORTED:
+      return "the kernel does not take these sizes (bfloat16, head_dim a multiple of 16 up to 128, page size a "
+             "power of two, 16-byte aligned q rows)";
+    default:
+      return cudaGetErrorString(static_cast<cudaError_t>(code));
+  }
+}
