@@ -71,6 +71,66 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const int
   for (int idx = threadIdx.x; idx < kv_width; idx += blockDim.x) vdst[idx] = base[q_width + kv_width + idx];
 }
 
+// The same with 16-byte accesses: rot / 2, head_dim and row_stride are multiples of the vector length.
+template <typename T>
+__global__ void rope_cache_vec_kernel(T* __restrict__ qkv, int row_stride, const int* __restrict__ positions,
+                                      const int* __restrict__ row_request, const int* __restrict__ block_table,
+                                      int max_blocks, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                      const float* __restrict__ inv_freq, int rot, float pos_scale, int n_heads,
+                                      int n_kv_heads, int head_dim, int page_size, int write_cache) {
+  constexpr int V = PerVec<T>::n;
+  extern __shared__ float cs[];  // cos[rot/2], sin[rot/2]
+  const int row = blockIdx.x;
+  const int pos = positions[row];
+  const int half = inv_freq ? rot / 2 : 0;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const float theta = static_cast<float>(pos) * pos_scale * inv_freq[i];
+    float s, c;
+    sincosf(theta, &s, &c);
+    cs[i] = c;
+    cs[half + i] = s;
+  }
+  __syncthreads();
+  T* base = qkv + static_cast<size_t>(row) * row_stride;
+  T* kdst = nullptr;
+  T* vdst = nullptr;
+  if (write_cache) {
+    const int req = row_request[row];
+    const int page = block_table[static_cast<size_t>(req) * max_blocks + pos / page_size];
+    const size_t slot = static_cast<size_t>(page) * page_size + pos % page_size;
+    kdst = k_cache + slot * n_kv_heads * head_dim;
+    vdst = v_cache + slot * n_kv_heads * head_dim;
+  }
+  const int q_width = n_heads * head_dim, kv_width = n_kv_heads * head_dim;
+  const int hc = half / V;                        // vector pairs per head
+  const int rot_heads = write_cache ? n_heads + n_kv_heads : n_heads;
+  for (int idx = threadIdx.x; idx < rot_heads * hc; idx += blockDim.x) {
+    const int h = idx / hc, ci = idx % hc;
+    T* hx = base + static_cast<size_t>(h) * head_dim + ci * V;
+    float a[V], b[V], ra[V], rb[V];
+    unpack<T>(*reinterpret_cast<const Vec16*>(hx), a);
+    unpack<T>(*reinterpret_cast<const Vec16*>(hx + half), b);
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      const float c = cs[ci * V + j], sn = cs[half + ci * V + j];
+      ra[j] = a[j] * c - b[j] * sn;
+      rb[j] = a[j] * sn + b[j] * c;
+    }
+    T* dst = h < n_heads ? hx : kdst + static_cast<size_t>(h - n_heads) * head_dim + ci * V;
+    *reinterpret_cast<Vec16*>(dst) = pack<T>(ra);
+    *reinterpret_cast<Vec16*>(dst + half) = pack<T>(rb);
+  }
+  if (!write_cache) return;
+  const int tail = (head_dim - 2 * half) / V;     // unrotated vectors of each key head
+  for (int idx = threadIdx.x; idx < n_kv_heads * tail; idx += blockDim.x) {
+    const int h = idx / tail, d = 2 * half + (idx % tail) * V;
+    *reinterpret_cast<Vec16*>(kdst + static_cast<size_t>(h) * head_dim + d) =
+        *reinterpret_cast<const Vec16*>(base + q_width + static_cast<size_t>(h) * head_dim + d);
+  }
+  for (int idx = threadIdx.x; idx < kv_width / V; idx += blockDim.x)
+    *reinterpret_cast<Vec16*>(vdst + idx * V) = *reinterpret_cast<const Vec16*>(base + q_width + kv_width + idx * V);
+}
+
 }  // namespace dl
 
 // qkv: [rows, row_stride] with q | k | v side by side; q is rotated in place, k is rotated on its way
@@ -86,6 +146,21 @@ DL_EXPORT int dl_rope_cache_write(int dtype, void* qkv, int row_stride, const in
   const int threads = 256;
   const size_t smem = static_cast<size_t>(rot) * sizeof(float);
   if (smem > 48 * 1024) return DL_ERR_UNSUPPORTED;
+  const int vec = dtype == 0 ? 4 : 8;
+  const int half = inv_freq ? rot / 2 : 0;
+  if ((dtype == 0 || dtype == 1) && half % vec == 0 && head_dim % vec == 0 && row_stride % vec == 0 &&
+      (reinterpret_cast<uintptr_t>(qkv) & 15) == 0) {
+#define DL_LAUNCH_VEC(T)                                                                                            \
+  dl::rope_cache_vec_kernel<T><<<rows, threads, smem, stream>>>(static_cast<T*>(qkv), row_stride, positions,        \
+                                                                row_request, block_table, max_blocks,               \
+                                                                static_cast<T*>(k_cache), static_cast<T*>(v_cache), \
+                                                                inv_freq, rot, pos_scale, n_heads, n_kv_heads,      \
+                                                                head_dim, page_size, write_cache)
+    if (dtype == 0) DL_LAUNCH_VEC(float);
+    else DL_LAUNCH_VEC(dl::bf16);
+#undef DL_LAUNCH_VEC
+    return dl::launch_status();
+  }
 #define DL_LAUNCH(T)                                                                                              \
   dl::rope_cache_kernel<T><<<rows, threads, smem, stream>>>(static_cast<T*>(qkv), row_stride, positions, row_request, \
                                                             block_table, max_blocks, static_cast<T*>(k_cache),    \

@@ -44,6 +44,54 @@ argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restri
   }
 }
 
+// Large vocabularies: ARGMAX_PARTS blocks per row each scan a contiguous slice and leave (value, index);
+// a second small kernel picks among them. Ties still go to the lowest index: slices are in index
+// order and the comparison prefers the lower index on equal values.
+constexpr int ARGMAX_PARTS = 32;
+
+__global__ void __launch_bounds__(256)
+argmax_part_kernel(const float* __restrict__ logits, int ld, int vocab, float* __restrict__ pv, int* __restrict__ pi) {
+  __shared__ float bv[8];
+  __shared__ int bi[8];
+  const int r = blockIdx.y, part = blockIdx.x;
+  const int per = (vocab + ARGMAX_PARTS - 1) / ARGMAX_PARTS;
+  const int b = min(vocab, part * per), e = min(vocab, b + per);
+  const float* row = logits + static_cast<size_t>(r) * ld;
+  float best = -INFINITY;
+  int idx = 0x7fffffff;
+  for (int i = b + threadIdx.x; i < e; i += blockDim.x) {
+    const float v = row[i];
+    if (v > best) { best = v; idx = i; }
+  }
+  auto better = [](float v, int i, float bv_, int bi_) { return v > bv_ || (v == bv_ && i < bi_); };
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (better(ov, oi, best, idx)) { best = ov; idx = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { bv[warp] = best; bi[warp] = idx; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w)
+      if (better(bv[w], bi[w], best, idx)) { best = bv[w]; idx = bi[w]; }
+    pv[r * ARGMAX_PARTS + part] = best;
+    pi[r * ARGMAX_PARTS + part] = idx;
+  }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int* __restrict__ out) {
+  const int r = blockIdx.x, lane = threadIdx.x;     // 32 threads
+  float best = pv[r * ARGMAX_PARTS + lane];
+  int idx = pi[r * ARGMAX_PARTS + lane];
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+  }
+  if (lane == 0) out[r] = idx == 0x7fffffff ? 0 : idx;
+}
+
 // One block per row. Each thread owns a contiguous run of ids so that the walk is in id order.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_temperature_kernel(const float* __restrict__ logits, int ld, int vocab,
@@ -108,9 +156,19 @@ sample_temperature_kernel(const float* __restrict__ logits, int ld, int vocab,
 
 }  // namespace dl
 
-DL_EXPORT int dl_argmax(const float* logits, int ld, int rows, int vocab, int* out, cudaStream_t stream) {
+// scratch: room for rows * 32 floats and rows * 32 ints (rows * 256 bytes), or null to use one block per row.
+DL_EXPORT int dl_argmax(const float* logits, int ld, int rows, int vocab, int* out, void* scratch,
+                        cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0) return DL_ERR_UNSUPPORTED;
+  if (scratch != nullptr && vocab >= 8192 && rows <= 65535) {
+    float* pv = static_cast<float*>(scratch);
+    int* pi = reinterpret_cast<int*>(pv + static_cast<size_t>(rows) * dl::ARGMAX_PARTS);
+    dim3 grid(dl::ARGMAX_PARTS, rows);
+    dl::argmax_part_kernel<<<grid, 256, 0, stream>>>(logits, ld, vocab, pv, pi);
+    dl::argmax_final_kernel<<<rows, 32, 0, stream>>>(pv, pi, out);
+    return dl::launch_status();
+  }
   dl::argmax_kernel<<<rows, dl::SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, out);
   return dl::launch_status();
 }

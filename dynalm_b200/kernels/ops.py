@@ -38,7 +38,7 @@ _SIGNATURES = {
     "gemm_skinny": {"dl_gemm_skinny": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _L, _P]},
     "gemm_simt": {"dl_gemm_simt": [_I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _P]},
     "sampling": {
-        "dl_argmax": [_P, _I, _I, _I, _P, _P],
+        "dl_argmax": [_P, _I, _I, _I, _P, _P, _P],
         "dl_sample_temperature": [_P, _I, _I, _I, _P, _P, _P, _P],
     },
 }
@@ -339,13 +339,23 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str =
                                                  n_split, split_stride, _stream()), "gemm_skinny")
 
 
+_argmax_scratch = {}
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     """out[r] = lowest index of the largest value of logits[r, :] (float32 rows, int32 out)."""
     _cuda(logits, out)
     _rows_contiguous(logits, "logits")
-    if logits.dtype != torch.float32 or out.dtype != torch.int32 or out.numel() < logits.shape[0]:
+    rows = logits.shape[0]
+    if logits.dtype != torch.float32 or out.dtype != torch.int32 or out.numel() < rows:
         raise InvalidArgument("argmax: logits float32, out int32 with one entry per row")
-    _check(_fn("sampling", "dl_argmax")(_p(logits), logits.stride(0), logits.shape[0], logits.shape[1], _p(out),
+    # partial (value, index) pairs of the two-stage kernel; grown in powers of two, kept per device
+    key = logits.device
+    scratch = _argmax_scratch.get(key)
+    if scratch is None or scratch.numel() < rows * 64:
+        scratch = torch.empty(max(64, 1 << (rows * 64 - 1).bit_length()), dtype=torch.float32, device=logits.device)
+        _argmax_scratch[key] = scratch
+    _check(_fn("sampling", "dl_argmax")(_p(logits), logits.stride(0), rows, logits.shape[1], _p(out), _p(scratch),
                                          _stream()), "argmax")
 
 
