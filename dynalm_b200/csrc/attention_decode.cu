@@ -219,6 +219,8 @@ decode_attention_kernel(const T* __restrict__ q, int q_stride, const T* __restri
 template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ part, T* __restrict__ out, int out_stride,
                                          int n_heads, int head_dim, int n_split) {
+  pdl_trigger();
+  pdl_wait();
   const int head = blockIdx.x, row = blockIdx.y;
   const int rec = head_dim + 2;
   const float* base = part + (static_cast<size_t>(row) * n_heads + head) * n_split * rec;
@@ -334,6 +336,8 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
   bf16* KV = Qs + 16 * LD;                               // [warp][stage][K | V][DT_KT][LD]
   float* merge = reinterpret_cast<float*>(dt_smem);      // reused after the loop: [warp][16][HD + 2]
 
+  pdl_trigger();
+  pdl_wait();
   const int split = blockIdx.x, row = blockIdx.z;
   const int group = n_heads / n_kv_heads;
   const int chunks = (group + 15) / 16;
@@ -550,17 +554,15 @@ int launch_decode_tc(const void* q, int q_stride, const void* kc, const void* vc
   }
   const int group = n_heads / n_kv_heads;
   dim3 grid(n_split, n_kv_heads * ((group + 15) / 16), rows);
-  decode_attention_tc_kernel<HD, STAGES><<<grid, DT_THREADS, smem, stream>>>(
-      static_cast<const bf16*>(q), q_stride, static_cast<const bf16*>(kc), static_cast<const bf16*>(vc), block_table,
-      max_blocks, positions, row_request, static_cast<bf16*>(out), out_stride, part, n_heads, n_kv_heads, page_shift,
-      scale * 1.4426950408889634f, window, n_split);
-  int rc = launch_status();
+  int rc = launch(decode_attention_tc_kernel<HD, STAGES>, grid, dim3(DT_THREADS), smem, stream,
+                  static_cast<const bf16*>(q), q_stride, static_cast<const bf16*>(kc), static_cast<const bf16*>(vc),
+                  block_table, max_blocks, positions, row_request, static_cast<bf16*>(out), out_stride, part, n_heads,
+                  n_kv_heads, page_shift, scale * 1.4426950408889634f, window, n_split);
   if (rc != 0 || n_split == 1) return rc;
   dim3 cgrid(n_heads, rows);
   const int cthreads = HD <= 32 ? 32 : (HD <= 64 ? 64 : 128);
-  attention_combine_kernel<bf16><<<cgrid, cthreads, 0, stream>>>(part, static_cast<bf16*>(out), out_stride, n_heads, HD,
-                                                                n_split);
-  return launch_status();
+  return launch(attention_combine_kernel<bf16>, cgrid, dim3(cthreads), 0, stream, static_cast<const float*>(part),
+                static_cast<bf16*>(out), out_stride, n_heads, HD, n_split);
 }
 
 }  // namespace dl

@@ -8,6 +8,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define DL_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -119,5 +120,37 @@ __device__ __forceinline__ Vec16 pack<bf16>(const float* in) {
 }
 
 inline int launch_status() { return static_cast<int>(cudaGetLastError()); }
+
+// Programmatic dependent launch. A kernel launched through `launch` may begin while the kernel before
+// it on the stream is still running; it must call pdl_wait() before it reads anything an earlier kernel
+// wrote and before it writes anything at all. pdl_trigger() lets the kernel after it begin likewise.
+// Kernels launched the ordinary way treat both as no-ops. The early start is off unless DYNALM_PDL=1:
+// measured on B200 inside the decode graph it made the step slower (1.50 ms against 1.24 ms at batch 8).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("DYNALM_PDL");
+    v = (e != nullptr && e[0] == '1') ? 1 : 0;
+  }
+  return v == 1;
+}
+
+template <typename... KArgs, typename... Args>
+inline int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return static_cast<int>(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
+}
 
 }  // namespace dl

@@ -8,6 +8,8 @@ namespace dl {
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
                              int width, int vocab, float scale) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   int id = ids[row];
   // The step function has already refused ids outside [0, vocab); clamping keeps a stray id
@@ -40,9 +42,9 @@ DL_EXPORT int dl_embed(int dtype, const void* table, const int* ids, float* out,
   if (rows <= 0) return 0;
   const int threads = width >= 1024 ? 256 : 128;
   if (dtype == 0) {
-    dl::embed_kernel<float><<<rows, threads, 0, stream>>>(static_cast<const float*>(table), ids, out, width, vocab, scale);
+    return dl::launch(dl::embed_kernel<float>, dim3(rows), dim3(threads), 0, stream, static_cast<const float*>(table), ids, out, width, vocab, scale);
   } else if (dtype == 1) {
-    dl::embed_kernel<dl::bf16><<<rows, threads, 0, stream>>>(static_cast<const dl::bf16*>(table), ids, out, width, vocab, scale);
+    return dl::launch(dl::embed_kernel<dl::bf16>, dim3(rows), dim3(threads), 0, stream, static_cast<const dl::bf16*>(table), ids, out, width, vocab, scale);
   } else {
     return DL_ERR_UNSUPPORTED;
   }

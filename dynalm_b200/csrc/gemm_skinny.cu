@@ -86,6 +86,8 @@ gemm_skinny_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
   const int nblk = (K + SK_KB - 1) / SK_KB;
   const int per = (nblk + n_split - 1) / n_split;
   const int blk_begin = split * per, blk_end = min(nblk, blk_begin + per);
+  pdl_trigger();
+  pdl_wait();
 #pragma unroll 2
   for (int blk = blk_begin + warp; blk < blk_end; blk += SK_WARPS) {
     const int k0 = blk * SK_KB + 8 * t;
@@ -179,9 +181,8 @@ int launch_skinny(const void* x, int ldx, const void* w, void* y, int ldy, int M
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  gemm_skinny_kernel<MT, NT><<<grid, SK_THREADS, smem, stream>>>(
-      static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), y, ldy, M, N, K, mode, out_scale, split_stride);
-  return launch_status();
+  return launch(gemm_skinny_kernel<MT, NT>, grid, dim3(SK_THREADS), smem, stream, static_cast<const bf16*>(x), ldx,
+                static_cast<const bf16*>(w), y, ldy, M, N, K, mode, out_scale, split_stride);
 }
 
 }  // namespace dl

@@ -78,6 +78,8 @@ rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, float de
                    const float* __restrict__ w, float eps, TO* __restrict__ out, const int* __restrict__ rows,
                    int width, int write_residual, int parts, size_t part_stride) {
   __shared__ float red[33];
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const size_t src = rows ? static_cast<size_t>(rows[r]) : static_cast<size_t>(r);
   float* xr = x + src * width;
@@ -156,10 +158,11 @@ DL_EXPORT int dl_rmsnorm(int out_dtype, int delta_dtype, float* x, const void* d
   if (width % 4 == 0 && width <= 8 * 4 * dl::NORM_VEC_THREADS &&
       (delta_part_stride % 4 == 0)) {
     const int nv = (width + 4 * dl::NORM_VEC_THREADS - 1) / (4 * dl::NORM_VEC_THREADS);
+    int rc = 0;
 #define DL_VEC(TO, TD, NV)                                                                                         \
-  dl::rmsnorm_vec_kernel<TO, TD, NV><<<n_rows, dl::NORM_VEC_THREADS, 0, stream>>>(                                 \
-      x, static_cast<const TD*>(delta), delta_scale, w, eps, static_cast<TO*>(out), rows, width, write_residual,   \
-      delta_parts, static_cast<size_t>(delta_part_stride))
+  rc = dl::launch(dl::rmsnorm_vec_kernel<TO, TD, NV>, dim3(n_rows), dim3(dl::NORM_VEC_THREADS), 0, stream, x,      \
+                  static_cast<const TD*>(delta), delta_scale, w, eps, static_cast<TO*>(out), rows, width,          \
+                  write_residual, delta_parts, static_cast<size_t>(delta_part_stride))
 #define DL_VEC_NV(TO, TD)                                   \
   do {                                                      \
     if (nv <= 1) DL_VEC(TO, TD, 1);                         \
@@ -174,7 +177,7 @@ DL_EXPORT int dl_rmsnorm(int out_dtype, int delta_dtype, float* x, const void* d
     else return DL_ERR_UNSUPPORTED;
 #undef DL_VEC_NV
 #undef DL_VEC
-    return dl::launch_status();
+    return rc;
   }
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
 #define DL_LAUNCH(TO, TD)                                                                            \

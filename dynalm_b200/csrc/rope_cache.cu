@@ -80,6 +80,8 @@ __global__ void rope_cache_vec_kernel(T* __restrict__ qkv, int row_stride, const
                                       int n_kv_heads, int head_dim, int page_size, int write_cache) {
   constexpr int V = PerVec<T>::n;
   extern __shared__ float cs[];  // cos[rot/2], sin[rot/2]
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   const int pos = positions[row];
   const int half = inv_freq ? rot / 2 : 0;
@@ -151,15 +153,12 @@ DL_EXPORT int dl_rope_cache_write(int dtype, void* qkv, int row_stride, const in
   if ((dtype == 0 || dtype == 1) && half % vec == 0 && head_dim % vec == 0 && row_stride % vec == 0 &&
       (reinterpret_cast<uintptr_t>(qkv) & 15) == 0) {
 #define DL_LAUNCH_VEC(T)                                                                                            \
-  dl::rope_cache_vec_kernel<T><<<rows, threads, smem, stream>>>(static_cast<T*>(qkv), row_stride, positions,        \
-                                                                row_request, block_table, max_blocks,               \
-                                                                static_cast<T*>(k_cache), static_cast<T*>(v_cache), \
-                                                                inv_freq, rot, pos_scale, n_heads, n_kv_heads,      \
-                                                                head_dim, page_size, write_cache)
-    if (dtype == 0) DL_LAUNCH_VEC(float);
-    else DL_LAUNCH_VEC(dl::bf16);
+  dl::launch(dl::rope_cache_vec_kernel<T>, dim3(rows), dim3(threads), smem, stream, static_cast<T*>(qkv), row_stride, \
+             positions, row_request, block_table, max_blocks, static_cast<T*>(k_cache), static_cast<T*>(v_cache),   \
+             inv_freq, rot, pos_scale, n_heads, n_kv_heads, head_dim, page_size, write_cache)
+    if (dtype == 0) return DL_LAUNCH_VEC(float);
+    return DL_LAUNCH_VEC(dl::bf16);
 #undef DL_LAUNCH_VEC
-    return dl::launch_status();
   }
 #define DL_LAUNCH(T)                                                                                              \
   dl::rope_cache_kernel<T><<<rows, threads, smem, stream>>>(static_cast<T*>(qkv), row_stride, positions, row_request, \
