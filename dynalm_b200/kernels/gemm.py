@@ -1,7 +1,7 @@
 """y = x W^T (+ bias): picks the matrix-product kernel for a dtype and shape.
 
 float32 always runs the plain fixed-order kernel (csrc/gemm_simt.cu): the true 32-bit path uses no
-tensor cores and no reduced-precision mode. bfloat16 with at most 64 rows (decode) runs the
+tensor cores and no reduced-precision mode. bfloat16 with at most 16 rows (decode) runs the
 weight-streaming kernel (csrc/gemm_skinny.cu), which can also apply SwiGLU on the way out or leave
 split-K partial sums for the consumer to add. bfloat16 with more rows runs the library product (cuBLAS
 through torch), which is where the reference's GPU path calls a library too (ggml_mul_mat,
@@ -39,7 +39,7 @@ def _mm_f32_out(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
 
 
 def skinny_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
-    return (x.dtype == torch.bfloat16 and x.shape[0] <= ops.SKINNY_MAX_ROWS and x.shape[1] % 8 == 0
+    return (x.dtype == torch.bfloat16 and x.shape[0] <= ops.SKINNY_FAST_ROWS and x.shape[1] % 8 == 0
             and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.is_contiguous())
 
 

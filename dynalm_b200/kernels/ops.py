@@ -36,6 +36,7 @@ _SIGNATURES = {
     "attention_prefill": {
         "dl_paged_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P]},
     "gemm_skinny": {"dl_gemm_skinny": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _L, _P]},
+    "gemm_tcgen05": {"dl_gemm_tcgen05": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P]},
     "gemm_simt": {"dl_gemm_simt": [_I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _P]},
     "sampling": {
         "dl_argmax": [_P, _I, _I, _I, _P, _P, _P],
@@ -306,7 +307,8 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optiona
                                              _p(bias), _p(out), out.stride(0), M, N, K, out_scale, _stream()), "gemm_simt")
 
 
-SKINNY_MAX_ROWS = 64
+SKINNY_MAX_ROWS = 64      # what the kernel takes
+SKINNY_FAST_ROWS = 16     # up to here it beats the library product (measured on B200); dispatchers use this
 
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str = "store", out_scale: float = 1.0) -> None:
@@ -337,6 +339,55 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str =
         code, ldy = (0 if out.dtype == torch.bfloat16 else 1), out.stride(0)
     _check(_fn("gemm_skinny", "dl_gemm_skinny")(_p(x), x.stride(0), _p(w), _p(out), ldy, M, N, K, code, out_scale,
                                                  n_split, split_stride, _stream()), "gemm_skinny")
+
+
+_tcgen05_status = {}
+
+
+def gemm_tcgen05_status(device=None) -> int:
+    """The timeout code the tcgen05 kernels left on `device` (0: none). Reading it synchronises."""
+    if device is None:
+        return max((int(t.item()) for t in _tcgen05_status.values()), default=0)
+    t = _tcgen05_status.get(torch.device(device))
+    return 0 if t is None else int(t.item())
+
+
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str = "store", out_scale: float = 1.0) -> None:
+    """x W^T on tcgen05 tensor cores with TMA-fed operands; see csrc/gemm_tcgen05.cu.
+
+    x [M, K] and w [N, K] bfloat16; out [M, N] bfloat16 or float32, or with mode "swiglu"
+    (w = [gate; up]) out [M, N/2] bfloat16."""
+    _cuda(x, w, out)
+    _rows_contiguous(x, "x")
+    M, K = x.shape
+    N = w.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not w.is_contiguous() or w.shape[1] != K:
+        raise InvalidArgument("gemm_tcgen05: x and w bfloat16, w [N, K] contiguous")
+    if K % 8 or x.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16 or out.data_ptr() % 16 or out.stride(1) != 1:
+        raise Unsupported("gemm_tcgen05: K and row pitches must be multiples of 8 elements, bases 16-byte aligned")
+    if mode == "swiglu":
+        if N % 16 or out.shape != (M, N // 2) or out.dtype != torch.bfloat16 or out.stride(0) % 8:
+            raise Unsupported("gemm_tcgen05: swiglu needs out [M, N/2] bfloat16 with N/2 a multiple of 8")
+        code = 2
+    else:
+        if out.shape != (M, N):
+            raise InvalidArgument("gemm_tcgen05: out [M, N]")
+        if out.dtype == torch.bfloat16:
+            if N % 8 or out.stride(0) % 8:
+                raise Unsupported("gemm_tcgen05: bfloat16 output needs N and its row pitch to be multiples of 8")
+            code = 0
+        elif out.dtype == torch.float32:
+            if N % 4 or out.stride(0) % 4:
+                raise Unsupported("gemm_tcgen05: float32 output needs N and its row pitch to be multiples of 4")
+            code = 1
+        else:
+            raise InvalidArgument("gemm_tcgen05: out bfloat16 or float32")
+    status = _tcgen05_status.get(x.device)
+    if status is None:
+        status = torch.zeros(1, dtype=torch.int32, device=x.device)
+        _tcgen05_status[x.device] = status
+    _check(_fn("gemm_tcgen05", "dl_gemm_tcgen05")(_p(x), x.stride(0), _p(w), _p(out), out.stride(0), M, N, K, code,
+                                                   out_scale, _p(status), _stream()), "gemm_tcgen05")
 
 
 _argmax_scratch = {}

@@ -437,3 +437,34 @@ def test_gemm_skinny(ops, M, N, K):
     r2 = resid.clone()
     ops.rmsnorm(r2, wn, 1e-5, normed, delta=parts, delta_scale=1.0)
     assert (r2.double() - (resid.double() + ref)).abs().max() <= 2e-5 * max(1.0, scale)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 256), (100, 264, 200), (300, 1000, 136), (17, 48, 8),
+                                   (2048, 3072, 2048), (513, 4096, 1024)])
+def test_gemm_tcgen05(ops, M, N, K):
+    """The tcgen05 / TMEM / TMA matrix product against an fp64 reference: tiles that end inside M, N
+    and K, all three epilogues, and an operand that is a view with a wider row."""
+    g = torch.Generator(device="cpu").manual_seed(14)
+    x = torch.randn(M, K, generator=g).to(DEV, torch.bfloat16)
+    w = torch.randn(N, K, generator=g).to(DEV, torch.bfloat16)
+    ref = x.double() @ w.double().T
+    scale = ref.abs().max().item()
+    out16 = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tcgen05(x, w, out16)
+    assert ops.gemm_tcgen05_status() == 0, "a wait inside the kernel timed out"
+    assert (out16.double() - ref).abs().max() <= 1e-2 * scale
+    out32 = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ops.gemm_tcgen05(x, w, out32, "store", 0.5)
+    assert (out32.double() - 0.5 * ref).abs().max() <= 2e-5 * scale
+    wide = torch.zeros(M, K + 40, dtype=torch.bfloat16, device=DEV)
+    wide[:, :K] = x
+    out32b = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ops.gemm_tcgen05(wide[:, :K], w, out32b)
+    assert (out32b.double() - ref).abs().max() <= 2e-5 * scale
+    if N % 16 == 0:
+        act = torch.empty(M, N // 2, dtype=torch.bfloat16, device=DEV)
+        ops.gemm_tcgen05(x, w, act, "swiglu")
+        gate, up = ref[:, :N // 2], ref[:, N // 2:]
+        want = gate * torch.sigmoid(gate) * up
+        assert (act.double() - want).abs().max() <= 1e-2 * max(1.0, want.abs().max().item())
+    assert ops.gemm_tcgen05_status() == 0
