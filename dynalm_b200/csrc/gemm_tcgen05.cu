@@ -1,13 +1,13 @@
 // y = x W^T on the 5th-generation tensor cores: tcgen05.mma with the accumulator in tensor memory,
 // operands brought to shared memory by TMA. bf16 operands, fp32 accumulation.
 //
-// One thread block computes a 128 x BN tile of y (BN = 256, or 2 x 128 for SwiGLU). Roles:
+// A thread block computes 128 x BN tiles of y (BN = 256, or 2 x 128 for SwiGLU), one after another. Roles:
 //   warp 0, one lane   TMA producer: for each 64-wide slice of K, waits for a free stage, arms the stage's
 //                      mbarrier with the byte count and issues the tile loads (x: 128 rows, W: BN rows), both
 //                      K-major with the 128-byte swizzle that the tensor core reads directly
 //   warp 1, one lane   issues four tcgen05.mma (M 128, N BN, K 16) per stage into the TMEM accumulator and
-//                      commits them to the stage's "empty" barrier; after the last slice commits to the
-//                      "accumulator ready" barrier. Warp 1 also allocates and frees the TMEM columns.
+//                      commits them to the stage's "empty" barrier; after a tile's last slice commits to that
+//                      accumulator's "full" barrier. Warp 1 also allocates and frees the TMEM columns.
 //   warps 2..5         epilogue: each warp reads its quarter of the 128 TMEM lanes (one output row per thread),
 //                      converts and stores: bf16, fp32 (optionally scaled), or SwiGLU, where the tile's first
 //                      128 columns are gate features and the last 128 the matching up features of W = [Wg; Wu].
@@ -29,15 +29,20 @@
 namespace dl {
 
 constexpr int T5_BM = 128;
-constexpr int T5_BN = 256;
 constexpr int T5_BK = 64;                 // 64 bf16 = 128 bytes: one swizzle row
-constexpr int T5_STAGES = 4;
 constexpr int T5_THREADS = 192;           // 6 warps
 constexpr uint32_t T5_A_BYTES = T5_BM * T5_BK * 2;    // 16 KiB
-constexpr uint32_t T5_B_BYTES = T5_BN * T5_BK * 2;    // 32 KiB
-constexpr uint32_t T5_STAGE_BYTES = T5_A_BYTES + T5_B_BYTES;
-constexpr uint32_t T5_TMEM_COLS = 256;
-constexpr size_t T5_SMEM = static_cast<size_t>(T5_STAGES) * T5_STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+constexpr uint32_t T5_STORE_BYTES = 4 * 32 * 128;     // per epilogue warp: 32 rows x 128 bytes of output, staged for coalesced stores
+
+// Tile width BN is 256 (4 stages of 48 KiB) or 128 (6 stages of 32 KiB, for shapes whose tile count
+// fits the SMs badly at 256).
+template <int BN> struct T5 {
+  static constexpr int STAGES = BN == 256 ? 4 : 6;
+  static constexpr uint32_t B_BYTES = BN * T5_BK * 2;
+  static constexpr uint32_t STAGE_BYTES = T5_A_BYTES + B_BYTES;
+  static constexpr uint32_t TMEM_COLS = 2 * BN;      // two accumulators
+  static constexpr size_t SMEM = static_cast<size_t>(STAGES) * STAGE_BYTES + T5_STORE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+};
 
 enum { T5_OUT_BF16 = 0, T5_OUT_F32 = 1, T5_OUT_SWIGLU = 2 };
 enum { T5_ERR_PRODUCER = 1, T5_ERR_MMA = 2, T5_ERR_EPILOGUE = 3 };
@@ -50,8 +55,9 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-// Bounded wait for the phase with the given parity. False (and *status set) after about a second.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+// Bounded wait for the phase with the given parity. False after about a second (then *status and the
+// block's abort flag are set), or as soon as another role of the block has given up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code, volatile int* abort_flag) {
   const uint32_t addr = smem_u32(bar);
   const long long start = clock64();
   for (uint32_t spins = 0;; ++spins) {
@@ -62,9 +68,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(done) : "r"(addr), "r"(parity) : "memory");
     if (done) return true;
-    if ((spins & 1023u) == 1023u && clock64() - start > 2000000000ll) {
-      atomicExch(status, code);
-      return false;
+    if ((spins & 255u) == 255u) {
+      if (*abort_flag) return false;
+      if (clock64() - start > 2000000000ll) {
+        atomicExch(status, code);
+        *abort_flag = 1;
+        return false;
+      }
     }
   }
 }
@@ -107,32 +117,63 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// The registers of tmem_ld32 are valid only after this.
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
   __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&p);
 }
 
+// Writes this warp's 32 rows x 64 bf16 columns (one row per lane, `w` = the lane's 8 x 16 bytes) through a
+// swizzled shared staging area, so that each store instruction covers four whole 128-byte row pieces.
+// `col0` is the first of the 64 columns, `n_valid` the number of valid output columns overall.
+__device__ __forceinline__ void store_rows_bf16(const uint4 (&w)[8], unsigned char* stage, int lane, bf16* out, int ldy,
+                                                int row0, int M, int col0, int n_valid) {
+  uint4* st = reinterpret_cast<uint4*>(stage);
+#pragma unroll
+  for (int ch = 0; ch < 8; ++ch) st[lane * 8 + (ch ^ (lane & 7))] = w[ch];
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = i * 4 + (lane >> 3), ch = lane & 7;
+    const uint4 v = st[r * 8 + (ch ^ (r & 7))];
+    const int col = col0 + ch * 8;
+    if (row0 + r < M && col < n_valid) *reinterpret_cast<uint4*>(out + static_cast<size_t>(row0 + r) * ldy + col) = v;
+  }
+  __syncwarp();
+}
+
 // gate_rows: for SwiGLU the number of gate features F (W has 2F rows); the tile's W rows are
 // [n0, n0 + 128) and [F + n0, F + n0 + 128). Otherwise unused.
+//
+// The kernel is persistent: gridDim.x blocks (at most one per SM) walk the output tiles in the order
+// tile = blockIdx.x, blockIdx.x + gridDim.x, ...; tiles with consecutive numbers share their rows of x
+// (tile -> row block tile / tiles_n, column block tile % tiles_n), so x stays in L2 while W streams.
+// The accumulator is double-buffered in tensor memory (2 x 256 columns): the epilogue warps drain
+// one tile while the MMA warp fills the next.
+template <int T5_BN>
 __global__ void __launch_bounds__(T5_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     void* __restrict__ y, int ldy, int M, int N, int K, int mode, float out_scale, int gate_rows,
-                    int* __restrict__ status) {
+                    int tiles_n, int num_tiles, int* __restrict__ status) {
+  constexpr int T5_STAGES = T5<T5_BN>::STAGES;
+  constexpr uint32_t T5_B_BYTES = T5<T5_BN>::B_BYTES, T5_STAGE_BYTES = T5<T5_BN>::STAGE_BYTES, T5_TMEM_COLS = T5<T5_BN>::TMEM_COLS;
   extern __shared__ unsigned char t5_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(t5_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + static_cast<size_t>(T5_STAGES) * T5_STAGE_BYTES);
-  uint64_t* full_bar = bars;                        // [T5_STAGES]
-  uint64_t* empty_bar = bars + T5_STAGES;           // [T5_STAGES]
-  uint64_t* acc_bar = bars + 2 * T5_STAGES;         // accumulator ready
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * T5_STAGES + 1);
+  unsigned char* store_stage = tiles + static_cast<size_t>(T5_STAGES) * T5_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(store_stage + T5_STORE_BYTES);
+  uint64_t* full_bar = bars;                        // [T5_STAGES] stage loaded
+  uint64_t* empty_bar = bars + T5_STAGES;           // [T5_STAGES] stage consumed
+  uint64_t* acc_full = bars + 2 * T5_STAGES;        // [2] accumulator complete
+  uint64_t* acc_empty = bars + 2 * T5_STAGES + 2;   // [2] accumulator drained
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * T5_STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool swiglu = mode == T5_OUT_SWIGLU;
   const int n_per_tile = swiglu ? T5_BN / 2 : T5_BN;      // output features per tile
-  const int n0 = blockIdx.x * n_per_tile, m0 = blockIdx.y * T5_BM;
   const int k_tiles = (K + T5_BK - 1) / T5_BK;
 
   if (threadIdx.x == 0) {
@@ -140,7 +181,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(acc_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);                  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -154,108 +199,140 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kt = 0; kt < k_tiles; ++kt) {
-        const int s = kt % T5_STAGES;
-        if (kt >= T5_STAGES && !mbar_wait(&empty_bar[s], ((kt / T5_STAGES) & 1) ^ 1, status, T5_ERR_PRODUCER)) break;
-        unsigned char* a_dst = tiles + static_cast<size_t>(s) * T5_STAGE_BYTES;
-        unsigned char* b_dst = a_dst + T5_A_BYTES;
-        mbar_expect_tx(&full_bar[s], T5_STAGE_BYTES);
-        tma_load_2d(a_dst, &map_x, kt * T5_BK, m0, &full_bar[s]);
-        if (swiglu) {
+      uint32_t it = 0;                               // k-slices issued so far, over all tiles
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / tiles_n) * T5_BM, n0 = (tile % tiles_n) * n_per_tile;
+        for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+          const int s = it % T5_STAGES;
+          if (it >= T5_STAGES && !mbar_wait(&empty_bar[s], ((it / T5_STAGES) & 1) ^ 1, status, T5_ERR_PRODUCER, abort_flag)) {
+            ok = false;
+            break;
+          }
+          unsigned char* a_dst = tiles + static_cast<size_t>(s) * T5_STAGE_BYTES;
+          unsigned char* b_dst = a_dst + T5_A_BYTES;
+          mbar_expect_tx(&full_bar[s], T5_STAGE_BYTES);
+          tma_load_2d(a_dst, &map_x, kt * T5_BK, m0, &full_bar[s]);
           tma_load_2d(b_dst, &map_w, kt * T5_BK, n0, &full_bar[s]);
-          tma_load_2d(b_dst + T5_B_BYTES / 2, &map_w, kt * T5_BK, gate_rows + n0, &full_bar[s]);
-        } else {
-          tma_load_2d(b_dst, &map_w, kt * T5_BK, n0, &full_bar[s]);
-          tma_load_2d(b_dst + T5_B_BYTES / 2, &map_w, kt * T5_BK, n0 + T5_BN / 2, &full_bar[s]);
+          tma_load_2d(b_dst + T5_B_BYTES / 2, &map_w, kt * T5_BK, swiglu ? gate_rows + n0 : n0 + T5_BN / 2, &full_bar[s]);
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc(T5_BM, T5_BN);
+      uint32_t it = 0, local = 0;                    // k-slices consumed; tiles done by this block
       bool ok = true;
-      for (int kt = 0; kt < k_tiles && ok; ++kt) {
-        const int s = kt % T5_STAGES;
-        ok = mbar_wait(&full_bar[s], (kt / T5_STAGES) & 1, status, T5_ERR_MMA);
-        if (!ok) break;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const uint32_t buf = local & 1;
+        // the epilogue must have drained this buffer (its previous use was tile local - 2)
+        if (local >= 2 && !mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, status, T5_ERR_MMA, abort_flag)) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = smem_u32(tiles + static_cast<size_t>(s) * T5_STAGE_BYTES);
-        const uint32_t b_addr = a_addr + T5_A_BYTES;
+        const uint32_t acc = tmem_base + buf * T5_BN;
+        for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+          const int s = it % T5_STAGES;
+          if (!mbar_wait(&full_bar[s], (it / T5_STAGES) & 1, status, T5_ERR_MMA, abort_flag)) {
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = smem_u32(tiles + static_cast<size_t>(s) * T5_STAGE_BYTES);
+          const uint32_t b_addr = a_addr + T5_A_BYTES;
 #pragma unroll
-        for (int k = 0; k < T5_BK / 16; ++k) {
-          // 16 elements of K = 32 bytes further along the swizzled row
-          umma_bf16(tmem_base, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32), idesc,
-                    (kt > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < T5_BK / 16; ++k) {
+            // 16 elements of K = 32 bytes further along the swizzled row
+            umma_bf16(acc, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32), idesc,
+                      (kt > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);                // arrives when these MMAs have finished reading the stage
         }
-        umma_commit(&empty_bar[s]);      // arrives when these MMAs have finished reading the stage
+        umma_commit(&acc_full[buf]);                 // arrives when every MMA issued so far has completed
       }
-      umma_commit(acc_bar);              // arrives when every MMA issued so far has completed
     }
   } else {
     // epilogue: warp w may touch TMEM lanes 32 * (w % 4) .. + 31
     const int quarter = warp & 3;
-    const int row = m0 + quarter * 32 + lane;
-    // one lane polls; the whole warp then takes the same branch (tcgen05.ld is warp-wide)
-    int ready = 0;
-    if (lane == 0) ready = mbar_wait(acc_bar, 0, status, T5_ERR_EPILOGUE) ? 1 : 0;
-    ready = __shfl_sync(0xffffffffu, ready, 0);
-    if (ready) {
+    uint32_t local = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      const uint32_t buf = local & 1;
+      const int m0 = (tile / tiles_n) * T5_BM, n0 = (tile % tiles_n) * n_per_tile;
+      const int row = m0 + quarter * 32 + lane;
+      // one lane polls; the whole warp then takes the same branch (tcgen05.ld is warp-wide)
+      int ready = 0;
+      if (lane == 0) ready = mbar_wait(&acc_full[buf], (local >> 1) & 1, status, T5_ERR_EPILOGUE, abort_flag) ? 1 : 0;
+      ready = __shfl_sync(0xffffffffu, ready, 0);
+      if (!ready) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+      const uint32_t lane_addr = tmem_base + buf * T5_BN + (static_cast<uint32_t>(quarter * 32) << 16);
+      unsigned char* my_stage = store_stage + (warp - 2) * (T5_STORE_BYTES / 4);
+      const int row0 = m0 + quarter * 32;
       if (swiglu) {
         bf16* out = static_cast<bf16*>(y);
-        for (int c = 0; c < T5_BN / 2; c += 32) {
-          uint32_t g[32], u[32];
-          tmem_ld32(lane_addr + c, g);
-          tmem_ld32(lane_addr + T5_BN / 2 + c, u);
-          if (row < M) {
+        for (int c0 = 0; c0 < T5_BN / 2; c0 += 64) {
+          uint4 w[8];
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            uint32_t g[32], u[32];
+            tmem_ld32(lane_addr + c0 + hh * 32, g);
+            tmem_ld32(lane_addr + T5_BN / 2 + c0 + hh * 32, u);
+            tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
-              const int col = n0 + c + j;
-              if (col < gate_rows) {           // gate_rows is a multiple of 8
-                uint32_t w4[4];
+              uint32_t w4[4];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const float g0 = __uint_as_float(g[j + 2 * e]), g1 = __uint_as_float(g[j + 2 * e + 1]);
-                  const float u0 = __uint_as_float(u[j + 2 * e]), u1 = __uint_as_float(u[j + 2 * e + 1]);
-                  w4[e] = pack2_bf16(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
-                }
-                *reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * ldy + col) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+              for (int e = 0; e < 4; ++e) {
+                const float g0 = __uint_as_float(g[j + 2 * e]), g1 = __uint_as_float(g[j + 2 * e + 1]);
+                const float u0 = __uint_as_float(u[j + 2 * e]), u1 = __uint_as_float(u[j + 2 * e + 1]);
+                w4[e] = pack2_bf16(__fdividef(g0, 1.0f + __expf(-g0)) * u0, __fdividef(g1, 1.0f + __expf(-g1)) * u1);
               }
+              w[hh * 4 + j / 8] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
             }
           }
+          store_rows_bf16(w, my_stage, lane, out, ldy, row0, M, n0 + c0, gate_rows);   // gate_rows is a multiple of 8
         }
       } else {
-        for (int c = 0; c < T5_BN; c += 32) {
-          uint32_t v[32];
-          tmem_ld32(lane_addr + c, v);
-          if (row < M) {
-            if (mode == T5_OUT_F32) {
+        for (int c0 = 0; c0 < T5_BN; c0 += 64) {
+          uint32_t va[32], vb[32];
+          tmem_ld32(lane_addr + c0, va);
+          tmem_ld32(lane_addr + c0 + 32, vb);
+          tmem_ld_wait();
+          if (mode == T5_OUT_F32) {
+            if (row < M) {
               float* out = static_cast<float*>(y) + static_cast<size_t>(row) * ldy;
 #pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                const int col = n0 + c + j;
-                if (col < N)                    // N is a multiple of 4 in this mode
-                  *reinterpret_cast<float4*>(out + col) =
-                      make_float4(__uint_as_float(v[j]) * out_scale, __uint_as_float(v[j + 1]) * out_scale,
-                                  __uint_as_float(v[j + 2]) * out_scale, __uint_as_float(v[j + 3]) * out_scale);
-              }
-            } else {
-              bf16* out = static_cast<bf16*>(y) + static_cast<size_t>(row) * ldy;
+              for (int hh = 0; hh < 2; ++hh) {
+                const uint32_t* v = hh == 0 ? va : vb;
 #pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                const int col = n0 + c + j;
-                if (col < N)                    // N is a multiple of 8 in this mode
-                  *reinterpret_cast<uint4*>(out + col) = make_uint4(
-                      pack2_bf16(__uint_as_float(v[j]) * out_scale, __uint_as_float(v[j + 1]) * out_scale),
-                      pack2_bf16(__uint_as_float(v[j + 2]) * out_scale, __uint_as_float(v[j + 3]) * out_scale),
-                      pack2_bf16(__uint_as_float(v[j + 4]) * out_scale, __uint_as_float(v[j + 5]) * out_scale),
-                      pack2_bf16(__uint_as_float(v[j + 6]) * out_scale, __uint_as_float(v[j + 7]) * out_scale));
+                for (int j = 0; j < 32; j += 4) {
+                  const int col = n0 + c0 + hh * 32 + j;
+                  if (col < N)                    // N is a multiple of 4 in this mode
+                    *reinterpret_cast<float4*>(out + col) =
+                        make_float4(__uint_as_float(v[j]) * out_scale, __uint_as_float(v[j + 1]) * out_scale,
+                                    __uint_as_float(v[j + 2]) * out_scale, __uint_as_float(v[j + 3]) * out_scale);
+                }
               }
             }
+          } else {
+            uint4 w[8];
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+              const uint32_t* v = hh == 0 ? va : vb;
+#pragma unroll
+              for (int j = 0; j < 32; j += 8)
+                w[hh * 4 + j / 8] = make_uint4(
+                    pack2_bf16(__uint_as_float(v[j]) * out_scale, __uint_as_float(v[j + 1]) * out_scale),
+                    pack2_bf16(__uint_as_float(v[j + 2]) * out_scale, __uint_as_float(v[j + 3]) * out_scale),
+                    pack2_bf16(__uint_as_float(v[j + 4]) * out_scale, __uint_as_float(v[j + 5]) * out_scale),
+                    pack2_bf16(__uint_as_float(v[j + 6]) * out_scale, __uint_as_float(v[j + 7]) * out_scale));
+            }
+            store_rows_bf16(w, my_stage, lane, static_cast<bf16*>(y), ldy, row0, M, n0 + c0, N);   // N is a multiple of 8
           }
         }
       }
+      // this warp has read its part of the buffer: let the MMA warp reuse it
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
     }
   }
   // common exit: every role arrives here, with or without a timeout
@@ -315,22 +392,52 @@ DL_EXPORT int dl_gemm_tcgen05(const void* x, int ldx, const void* w, void* y, in
   if ((mode == dl::T5_OUT_SWIGLU && (N & 1)) || (mode == dl::T5_OUT_F32 ? (feats & 3) || (ldy & 3) : (feats & 7) || (ldy & 7)) ||
       (reinterpret_cast<uintptr_t>(y) & 15))
     return DL_ERR_UNSUPPORTED;
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
+  }
+  const long long m_tiles = (M + dl::T5_BM - 1) / dl::T5_BM;
+  // Tile width: 256 unless 128 wastes far fewer SM-rounds (a round of 128-wide tiles costs somewhat more than
+  // half a round of 256-wide ones, measured).
+  auto rounds = [&](int bn) {
+    const int per = mode == dl::T5_OUT_SWIGLU ? bn / 2 : bn;
+    const long long t = m_tiles * ((feats + per - 1) / per);
+    return static_cast<double>((t + sm_count - 1) / sm_count) * (bn / 256.0);
+  };
+  const int bn = rounds(128) < 0.7 * rounds(256) ? 128 : 256;
+  const int per_tile = mode == dl::T5_OUT_SWIGLU ? bn / 2 : bn;
+  const int tiles_n = (feats + per_tile - 1) / per_tile;
+  const long long tiles = m_tiles * tiles_n;
+  if (tiles > (1ll << 30)) return DL_ERR_UNSUPPORTED;
   CUtensorMap map_x, map_w;
   int rc = dl::make_map(&map_x, x, M, K, ldx, dl::T5_BM);
   if (rc != 0) return rc;
-  rc = dl::make_map(&map_w, w, N, K, K, dl::T5_BN / 2);
+  rc = dl::make_map(&map_w, w, N, K, K, bn / 2);
   if (rc != 0) return rc;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(dl::gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(dl::T5_SMEM));
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
+  const int blocks = static_cast<int>(tiles < sm_count ? tiles : sm_count);
+  const int gate_rows = mode == dl::T5_OUT_SWIGLU ? N / 2 : 0;
+  if (bn == 256) {
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(dl::gemm_tcgen05_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(dl::T5<256>::SMEM));
+      if (e != cudaSuccess) return static_cast<int>(e);
+      configured = true;
+    }
+    dl::gemm_tcgen05_kernel<256><<<blocks, dl::T5_THREADS, dl::T5<256>::SMEM, stream>>>(
+        map_x, map_w, y, ldy, M, N, K, mode, out_scale, gate_rows, tiles_n, static_cast<int>(tiles), status);
+  } else {
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(dl::gemm_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(dl::T5<128>::SMEM));
+      if (e != cudaSuccess) return static_cast<int>(e);
+      configured = true;
+    }
+    dl::gemm_tcgen05_kernel<128><<<blocks, dl::T5_THREADS, dl::T5<128>::SMEM, stream>>>(
+        map_x, map_w, y, ldy, M, N, K, mode, out_scale, gate_rows, tiles_n, static_cast<int>(tiles), status);
   }
-  const int per_tile = mode == dl::T5_OUT_SWIGLU ? dl::T5_BN / 2 : dl::T5_BN;
-  dim3 grid((feats + per_tile - 1) / per_tile, (M + dl::T5_BM - 1) / dl::T5_BM);
-  if (grid.y > 65535) return DL_ERR_UNSUPPORTED;
-  dl::gemm_tcgen05_kernel<<<grid, dl::T5_THREADS, dl::T5_SMEM, stream>>>(map_x, map_w, y, ldy, M, N, K, mode, out_scale,
-                                                                        mode == dl::T5_OUT_SWIGLU ? N / 2 : 0, status);
   return dl::launch_status();
 }

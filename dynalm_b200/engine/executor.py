@@ -7,6 +7,7 @@ from typing import Dict, Hashable, List
 import numpy as np
 import torch
 
+from ..errors import EngineError
 from ..kernels import ops
 from .scheduler import BatchItem
 from .step import StepEntry, StepFunction
@@ -32,6 +33,7 @@ class GpuExecutor:
         self._temp = torch.ones(n, dtype=torch.float32, device=dev)
         self._u = torch.zeros(n, dtype=torch.float64, device=dev)
         self.h2d_bytes = 0
+        self.steps = 0
         self.d2h_bytes = 0
 
     def begin(self, request_id: Hashable) -> None:
@@ -70,6 +72,9 @@ class GpuExecutor:
             self.d2h_bytes += rows.nbytes
         torch.cuda.current_stream().synchronize()
         self.d2h_bytes += self._ids_host.numel() * 4
+        self.steps += 1
+        if self.steps % 64 == 1 and ops.gemm_tcgen05_status() != 0:
+            raise EngineError("a tcgen05 matrix product gave up waiting on a barrier; its results are not valid")
         ids = self._ids_host.numpy()
         out: Dict[Hashable, int] = {}
         for i, b in enumerate(want):

@@ -42,6 +42,7 @@ def main(argv=None) -> int:
     from ..errors import EngineError
     from .build import build
     from .step import StepEntry
+    from ..kernels import ops
 
     page = args.page_size or DEFAULT_PAGE_SIZE
     pool_tokens = -(-args.max_tokens // page) * page
@@ -69,6 +70,8 @@ def main(argv=None) -> int:
                     host.tofile(os.path.join(args.out, f"{step}.f32"))
                 else:
                     torch.cuda.current_stream().synchronize()
+            if ops.gemm_tcgen05_status() != 0:
+                raise EngineError("a tcgen05 matrix product gave up waiting on a barrier; its results are not valid")
             for req in obj.get("end", []):
                 step_fn.end(req)
         except (EngineError, KeyError, ValueError, TypeError) as e:

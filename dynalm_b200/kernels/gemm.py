@@ -3,10 +3,12 @@
 float32 always runs the plain fixed-order kernel (csrc/gemm_simt.cu): the true 32-bit path uses no
 tensor cores and no reduced-precision mode. bfloat16 with at most 16 rows (decode) runs the
 weight-streaming kernel (csrc/gemm_skinny.cu), which can also apply SwiGLU on the way out or leave
-split-K partial sums for the consumer to add. bfloat16 with more rows runs the library product (cuBLAS
-through torch), which is where the reference's GPU path calls a library too (ggml_mul_mat,
-dynacore/src/gpu/ggml_graph.cpp:278-292), with fp32 accumulation. Shapes these cannot express (a bias,
-a K that is no multiple of 8) run the plain kernel.
+split-K partial sums for the consumer to add. bfloat16 with more rows runs the tcgen05 / TMEM / TMA
+kernel (csrc/gemm_tcgen05.cu, plain or with the SwiGLU epilogue) whenever the product has enough
+128 x 256 tiles to fill the GPU; the few shapes in between (17..127 rows with a narrow output, where
+split-K wins) run the library product (cuBLAS through torch), which is where the reference's GPU path
+calls a library too (ggml_mul_mat, dynacore/src/gpu/ggml_graph.cpp:278-292). Shapes none of these can
+express (a bias, a K that is no multiple of 8) run the plain kernel.
 """
 
 from __future__ import annotations
@@ -51,6 +53,20 @@ def split_count(n_features: int, k: int, rows: int) -> int:
     return max(1, min(want, 8, k // 512))
 
 
+def tcgen05_ok(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, features: int) -> bool:
+    """Whether the tcgen05 kernel takes this product and has enough tiles to fill the GPU: with few
+    tiles (few rows and a narrow output) a split-K library kernel does better."""
+    if x.dtype != torch.bfloat16 or x.shape[1] % 8 or x.stride(1) != 1 or x.stride(0) % 8 or not w.is_contiguous():
+        return False
+    if x.data_ptr() % 16 or w.data_ptr() % 16 or out.data_ptr() % 16 or out.stride(1) != 1:
+        return False
+    align = 4 if out.dtype == torch.float32 else 8
+    if features % align or out.stride(0) % align:
+        return False
+    tiles = -(-x.shape[0] // 128) * -(-features // 256)
+    return tiles >= 96
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
            out_scale: float = 1.0) -> torch.Tensor:
     """out[M, N] = (x[M, K] @ w[N, K].T + bias[N]) * out_scale. x and w share a dtype; out may be
@@ -61,6 +77,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[t
         return out
     if skinny_ok(x, w) and out.stride(1) == 1:
         ops.gemm_skinny(x, w, out, "store", out_scale)
+        return out
+    if tcgen05_ok(x, w, out, w.shape[0]):
+        ops.gemm_tcgen05(x, w, out, "store", out_scale)
         return out
     if out_scale != 1.0 or not x.is_contiguous() or not out.is_contiguous():
         ops.gemm_simt(x, w, out, bias, out_scale)
@@ -99,6 +118,9 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, runtime, inner: int)
     act = runtime.buffer("ffn_act", (rows, inner))
     if x.dtype == torch.bfloat16 and skinny_ok(x, w_gate_up):
         ops.gemm_skinny(x, w_gate_up, act, "swiglu")
+        return act
+    if x.dtype == torch.bfloat16 and inner % 8 == 0 and w_gate_up.shape[0] == 2 * inner and tcgen05_ok(x, w_gate_up, act, 2 * inner):
+        ops.gemm_tcgen05(x, w_gate_up, act, "swiglu")
         return act
     gate_up = runtime.buffer("ffn_gate_up", (rows, 2 * inner))
     linear(x, w_gate_up, gate_up)
