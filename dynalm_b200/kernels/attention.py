@@ -15,6 +15,7 @@ from . import ops
 
 SM_COUNT = 148            # B200
 MAX_SPLITS = 32
+DECODE_FILL = int(__import__('os').environ.get('DYNALM_DECODE_FILL', '1'))   # blocks per SM the split count aims for
 
 
 def decode_splits(rows: int, n_heads: int, n_kv_heads: int, max_kv_len: int, tensor_cores: bool = True) -> int:
@@ -22,7 +23,7 @@ def decode_splits(rows: int, n_heads: int, n_kv_heads: int, max_kv_len: int, ten
     (one 32-key tile for each of a block's four warps)."""
     group = n_heads // n_kv_heads
     blocks = rows * n_kv_heads * (-(-group // (16 if tensor_cores else 4)))
-    want = -(-2 * SM_COUNT // max(blocks, 1))
+    want = -(-DECODE_FILL * SM_COUNT // max(blocks, 1))
     return max(1, min(want, max(1, max_kv_len // 128), MAX_SPLITS))
 
 
