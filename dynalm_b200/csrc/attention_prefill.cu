@@ -1,6 +1,6 @@
 // Paged flash attention for prompt portions: bf16 tensor cores (mma.sync m16n8k16), fp32 softmax.
 //
-// One thread block per (query tile, head). A query tile is up to 64 consecutive rows of ONE request
+// One thread block per (query tile, head). A query tile is up to 128 consecutive rows of ONE request
 // (the host cuts every request of the step into such tiles; a single decoded token is a tile of one
 // row), so portions of several prompts and decode rows share a launch. Keys and values are read in
 // place through the request's block table, 64 keys at a time, double-buffered with cp.async; the
@@ -17,7 +17,7 @@
 
 namespace dl {
 
-constexpr int PF_BM = 64;       // query rows per block (4 warps x 16)
+constexpr int PF_TILE = 128;    // rows of a query tile as the host cuts them
 constexpr int PF_BN = 64;       // keys per tile
 constexpr int PF_THREADS = 128;
 
@@ -58,6 +58,11 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
                          const bf16* __restrict__ v_cache, const int* __restrict__ block_table, int max_blocks,
                          const int4* __restrict__ tiles, bf16* __restrict__ out, int out_stride, int n_heads,
                          int n_kv_heads, int page_shift, float scale_log2, int window) {
+  // A warp owns PF_MT tiles of 16 query rows and reuses every K and V fragment for all of them. Two tiles per
+  // warp were measured slower on B200 at head_dim 64 (235 registers, half as many blocks): one it is.
+  constexpr int PF_MT = 1;
+  constexpr int PF_BM = 64 * PF_MT;       // query rows per block (4 warps)
+  constexpr int SUB = PF_TILE / PF_BM;    // blocks per query tile
   constexpr int LD = HD + 8;              // row stride in elements: 16 bytes of padding keep ldmatrix conflict-free
   constexpr int CH = HD / 8;              // 16-byte chunks per row
   constexpr int KS = HD / 16;             // k-steps of the Q K^T product
@@ -66,8 +71,10 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
   bf16* Ks = Qs + PF_BM * LD;             // [2][PF_BN][LD]
   bf16* Vs = Ks + 2 * PF_BN * LD;         // [2][PF_BN][LD]
 
-  const int4 tile = tiles[blockIdx.x];
-  const int req = tile.x, row0 = tile.y, nrows = tile.z, pos0 = tile.w;
+  const int4 tile = tiles[blockIdx.x / SUB];
+  const int sub = blockIdx.x % SUB;
+  const int req = tile.x, row0 = tile.y + sub * PF_BM, nrows = min(PF_BM, tile.z - sub * PF_BM), pos0 = tile.w + sub * PF_BM;
+  if (nrows <= 0) return;
   const int head = blockIdx.y;
   const int kvh = head / (n_heads / n_kv_heads);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -106,15 +113,23 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
   load_kv(j_begin, 0);
   cp_async_commit();
 
-  float o[HD / 8][4];
+  float o[PF_MT][HD / 8][4];
 #pragma unroll
-  for (int i = 0; i < HD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
-  uint32_t qf[KS][4];
-  const int r_a = warp * 16 + g, r_b = r_a + 8;                 // the two rows this lane owns
-  const int pos_a = pos0 + r_a, pos_b = pos0 + r_b;
-  const int lo_a = window > 0 ? max(0, pos_a - window + 1) : 0;
-  const int lo_b = window > 0 ? max(0, pos_b - window + 1) : 0;
+  for (int mt = 0; mt < PF_MT; ++mt)
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) { o[mt][i][0] = o[mt][i][1] = o[mt][i][2] = o[mt][i][3] = 0.0f; }
+  float m_run[PF_MT][2], l_run[PF_MT][2];
+  int pos_r[PF_MT][2], lo_r[PF_MT][2];            // position and first visible key of the lane's rows
+#pragma unroll
+  for (int mt = 0; mt < PF_MT; ++mt)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      m_run[mt][h] = -INFINITY;
+      l_run[mt][h] = 0.0f;
+      pos_r[mt][h] = pos0 + warp * (16 * PF_MT) + mt * 16 + g + h * 8;
+      lo_r[mt][h] = window > 0 ? max(0, pos_r[mt][h] - window + 1) : 0;
+    }
+  uint32_t qf[PF_MT][KS][4];
 
   for (int j = j_begin; j <= j_end; ++j) {
     const int stage = (j - j_begin) & 1;
@@ -123,20 +138,24 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
     cp_async_wait<1>();
     __syncthreads();
     if (j == j_begin) {
-      // Q fragments once: the warp's 16 rows, all k-steps
+      // Q fragments once: the warp's 32 rows, all k-steps
 #pragma unroll
-      for (int ks = 0; ks < KS; ++ks) {
-        const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-        const int c = ks * 16 + (lane >> 4) * 8;
-        ldmatrix_x4(qf[ks], Qs + r * LD + c);
-      }
+      for (int mt = 0; mt < PF_MT; ++mt)
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+          const int r = warp * (16 * PF_MT) + mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+          const int c = ks * 16 + (lane >> 4) * 8;
+          ldmatrix_x4(qf[mt][ks], Qs + r * LD + c);
+        }
     }
     const bf16* kt = Ks + stage * PF_BN * LD;
     const bf16* vt = Vs + stage * PF_BN * LD;
 
-    float s[PF_BN / 8][4];
+    float s[PF_MT][PF_BN / 8][4];
 #pragma unroll
-    for (int i = 0; i < PF_BN / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f; }
+    for (int mt = 0; mt < PF_MT; ++mt)
+#pragma unroll
+      for (int i = 0; i < PF_BN / 8; ++i) { s[mt][i][0] = s[mt][i][1] = s[mt][i][2] = s[mt][i][3] = 0.0f; }
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks) {
 #pragma unroll
@@ -145,62 +164,67 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
         const int key = np * 16 + (lane & 7) + (lane >> 4) * 8;
         const int c = ks * 16 + ((lane >> 3) & 1) * 8;
         ldmatrix_x4(kb, kt + key * LD + c);
-        mma_bf16(s[2 * np], qf[ks], kb[0], kb[1]);
-        mma_bf16(s[2 * np + 1], qf[ks], kb[2], kb[3]);
-      }
-    }
-    // scale, mask by position, row maxima
-    const int key0 = j * PF_BN;
-    const bool edge = key0 + PF_BN - 1 > pos0 + warp * 16 || (window > 0 && key0 < max(lo_a, lo_b));
-    float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int i = 0; i < PF_BN / 8; ++i) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float v = s[i][e] * scale_log2;
-        if (edge) {
-          const int key = key0 + i * 8 + 2 * t + (e & 1);
-          const bool second = e >= 2;
-          const int p = second ? pos_b : pos_a, lo = second ? lo_b : lo_a;
-          if (key > p || key < lo) v = -INFINITY;
+        for (int mt = 0; mt < PF_MT; ++mt) {
+          mma_bf16(s[mt][2 * np], qf[mt][ks], kb[0], kb[1]);
+          mma_bf16(s[mt][2 * np + 1], qf[mt][ks], kb[2], kb[3]);
         }
-        s[i][e] = v;
-        mx[e >> 1] = fmaxf(mx[e >> 1], v);
       }
     }
-    float corr[2];
+    // scale, mask by position, online softmax; P as bf16 A fragments
+    const int key0 = j * PF_BN;
+    uint32_t pf[PF_MT][PF_BN / 16][4];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
-      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-      const float m_new = fmaxf(m_run[h], mx[h]);
-      // a row with no visible key so far (rows past the end of the tile, or a window that starts
-      // later) keeps max = -inf; its probabilities are exact zeros
-      corr[h] = m_new == -INFINITY ? 1.0f : exp2f(m_run[h] - m_new);
-      m_run[h] = m_new;
-      mx[h] = m_new == -INFINITY ? 0.0f : m_new;
-    }
-    float ls[2] = {0.0f, 0.0f};
-    uint32_t pf[PF_BN / 16][4];
+    for (int mt = 0; mt < PF_MT; ++mt) {
+      const bool edge = key0 + PF_BN - 1 > pos0 + warp * (16 * PF_MT) + mt * 16 ||
+                        (window > 0 && key0 < max(lo_r[mt][0], lo_r[mt][1]));
+      float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int i = 0; i < PF_BN / 8; ++i) {
-      const float p0 = exp2f(s[i][0] - mx[0]), p1 = exp2f(s[i][1] - mx[0]);
-      const float p2 = exp2f(s[i][2] - mx[1]), p3 = exp2f(s[i][3] - mx[1]);
-      ls[0] += p0 + p1;
-      ls[1] += p2 + p3;
-      pf[i >> 1][(i & 1) * 2] = pack_bf16(p0, p1);
-      pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p2, p3);
-    }
+      for (int i = 0; i < PF_BN / 8; ++i) {
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      ls[h] += __shfl_xor_sync(0xffffffffu, ls[h], 1);
-      ls[h] += __shfl_xor_sync(0xffffffffu, ls[h], 2);
-      l_run[h] = l_run[h] * corr[h] + ls[h];
-    }
+        for (int e = 0; e < 4; ++e) {
+          float v = s[mt][i][e] * scale_log2;
+          if (edge) {
+            const int key = key0 + i * 8 + 2 * t + (e & 1);
+            if (key > pos_r[mt][e >> 1] || key < lo_r[mt][e >> 1]) v = -INFINITY;
+          }
+          s[mt][i][e] = v;
+          mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        }
+      }
+      float corr[2];
 #pragma unroll
-    for (int i = 0; i < HD / 8; ++i) {
-      o[i][0] *= corr[0]; o[i][1] *= corr[0];
-      o[i][2] *= corr[1]; o[i][3] *= corr[1];
+      for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        const float m_new = fmaxf(m_run[mt][h], mx[h]);
+        // a row with no visible key so far (rows past the end of the tile, or a window that starts
+        // later) keeps max = -inf; its probabilities are exact zeros
+        corr[h] = m_new == -INFINITY ? 1.0f : exp2f(m_run[mt][h] - m_new);
+        m_run[mt][h] = m_new;
+        mx[h] = m_new == -INFINITY ? 0.0f : m_new;
+      }
+      float ls[2] = {0.0f, 0.0f};
+#pragma unroll
+      for (int i = 0; i < PF_BN / 8; ++i) {
+        const float p0 = exp2f(s[mt][i][0] - mx[0]), p1 = exp2f(s[mt][i][1] - mx[0]);
+        const float p2 = exp2f(s[mt][i][2] - mx[1]), p3 = exp2f(s[mt][i][3] - mx[1]);
+        ls[0] += p0 + p1;
+        ls[1] += p2 + p3;
+        pf[mt][i >> 1][(i & 1) * 2] = pack_bf16(p0, p1);
+        pf[mt][i >> 1][(i & 1) * 2 + 1] = pack_bf16(p2, p3);
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        ls[h] += __shfl_xor_sync(0xffffffffu, ls[h], 1);
+        ls[h] += __shfl_xor_sync(0xffffffffu, ls[h], 2);
+        l_run[mt][h] = l_run[mt][h] * corr[h] + ls[h];
+      }
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i) {
+        o[mt][i][0] *= corr[0]; o[mt][i][1] *= corr[0];
+        o[mt][i][2] *= corr[1]; o[mt][i][3] *= corr[1];
+      }
     }
     // O += P V
 #pragma unroll
@@ -211,25 +235,32 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
         const int key = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
         const int c = dp * 16 + (lane >> 4) * 8;
         ldmatrix_x4_trans(vb, vt + key * LD + c);
-        mma_bf16(o[2 * dp], pf[kk], vb[0], vb[1]);
-        mma_bf16(o[2 * dp + 1], pf[kk], vb[2], vb[3]);
+#pragma unroll
+        for (int mt = 0; mt < PF_MT; ++mt) {
+          mma_bf16(o[mt][2 * dp], pf[mt][kk], vb[0], vb[1]);
+          mma_bf16(o[mt][2 * dp + 1], pf[mt][kk], vb[2], vb[3]);
+        }
       }
     }
     __syncthreads();     // every warp is done with this stage before the next prefetch overwrites it
   }
   cp_async_wait<0>();
 
-  const float inv_a = l_run[0] > 0.0f ? 1.0f / l_run[0] : 0.0f;
-  const float inv_b = l_run[1] > 0.0f ? 1.0f / l_run[1] : 0.0f;
 #pragma unroll
-  for (int i = 0; i < HD / 8; ++i) {
-    const int col = head * HD + i * 8 + 2 * t;
-    if (r_a < nrows)
-      *reinterpret_cast<uint32_t*>(out + static_cast<size_t>(row0 + r_a) * out_stride + col) =
-          pack_bf16(o[i][0] * inv_a, o[i][1] * inv_a);
-    if (r_b < nrows)
-      *reinterpret_cast<uint32_t*>(out + static_cast<size_t>(row0 + r_b) * out_stride + col) =
-          pack_bf16(o[i][2] * inv_b, o[i][3] * inv_b);
+  for (int mt = 0; mt < PF_MT; ++mt) {
+    const int r_a = warp * (16 * PF_MT) + mt * 16 + g, r_b = r_a + 8;
+    const float inv_a = l_run[mt][0] > 0.0f ? 1.0f / l_run[mt][0] : 0.0f;
+    const float inv_b = l_run[mt][1] > 0.0f ? 1.0f / l_run[mt][1] : 0.0f;
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+      const int col = head * HD + i * 8 + 2 * t;
+      if (r_a < nrows)
+        *reinterpret_cast<uint32_t*>(out + static_cast<size_t>(row0 + r_a) * out_stride + col) =
+            pack_bf16(o[mt][i][0] * inv_a, o[mt][i][1] * inv_a);
+      if (r_b < nrows)
+        *reinterpret_cast<uint32_t*>(out + static_cast<size_t>(row0 + r_b) * out_stride + col) =
+            pack_bf16(o[mt][i][2] * inv_b, o[mt][i][3] * inv_b);
+    }
   }
 }
 
@@ -237,7 +268,8 @@ template <int HD>
 int launch_prefill(const void* q, int q_stride, const void* kc, const void* vc, const int* block_table, int max_blocks,
                    const int* tiles, int n_tiles, void* out, int out_stride, int n_heads, int n_kv_heads, int page_shift,
                    float scale, int window, cudaStream_t stream) {
-  constexpr size_t smem = static_cast<size_t>(PF_BM + 4 * PF_BN) * (HD + 8) * sizeof(bf16);
+  constexpr int BM = 64;
+  constexpr size_t smem = static_cast<size_t>(BM + 4 * PF_BN) * (HD + 8) * sizeof(bf16);
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -245,7 +277,7 @@ int launch_prefill(const void* q, int q_stride, const void* kc, const void* vc, 
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  dim3 grid(n_tiles, n_heads);
+  dim3 grid(n_tiles * (PF_TILE / BM), n_heads);
   prefill_attention_kernel<HD><<<grid, PF_THREADS, smem, stream>>>(
       static_cast<const bf16*>(q), q_stride, static_cast<const bf16*>(kc), static_cast<const bf16*>(vc), block_table,
       max_blocks, reinterpret_cast<const int4*>(tiles), static_cast<bf16*>(out), out_stride, n_heads, n_kv_heads,
@@ -255,7 +287,7 @@ int launch_prefill(const void* q, int q_stride, const void* kc, const void* vc, 
 
 }  // namespace dl
 
-// bfloat16 only. tiles: int32 [n_tiles, 4] = (request, first row, rows <= 64, first position), 16-byte aligned.
+// bfloat16 only. tiles: int32 [n_tiles, 4] = (request, first row, rows <= 128, first position), 16-byte aligned.
 // q/out rows have head h at column h * head_dim; both strides and head_dim keep rows 4-byte aligned for the
 // packed stores (head_dim is a multiple of 16, at most 128; larger heads take the plain kernel).
 DL_EXPORT int dl_paged_attention_prefill(const void* q, int q_stride, const void* k_cache, const void* v_cache,

@@ -46,7 +46,7 @@ class StepContext:
     state_slots: torch.Tensor
     logit_rows: torch.Tensor
     num_logit_rows: int
-    # every request cut into tiles of at most 64 consecutive rows: int32 [num_q_tiles, 4] =
+    # every request cut into tiles of at most 128 consecutive rows: int32 [num_q_tiles, 4] =
     # (request, first row of the step, rows, first position)
     q_tiles: Optional[torch.Tensor] = None
     num_q_tiles: int = 0

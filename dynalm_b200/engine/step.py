@@ -33,7 +33,7 @@ class StepEntry:
     want: Sequence[int] = ()
 
 
-Q_TILE = 64     # rows of one request per query tile (see StepContext.q_tiles)
+Q_TILE = 128    # rows of one request per query tile (see StepContext.q_tiles)
 
 
 class _StepBuffers:

@@ -270,7 +270,7 @@ def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
                             q_tiles: torch.Tensor, n_tiles: int, out: torch.Tensor, n_heads: int, n_kv_heads: int,
                             head_dim: int, page_size: int, scale: float, window: int = 0) -> None:
     """Flash attention of query tiles over the paged cache, bfloat16; see csrc/attention_prefill.cu.
-    q_tiles: int32 [n_tiles, 4] = (request, first row, rows <= 64, first position)."""
+    q_tiles: int32 [n_tiles, 4] = (request, first row, rows <= 128, first position)."""
     _cuda(q, k_cache, v_cache, block_table, q_tiles, out)
     _rows_contiguous(q, "q")
     _rows_contiguous(out, "out")

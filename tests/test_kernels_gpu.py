@@ -368,8 +368,8 @@ def test_paged_attention_prefill(ops, heads, kvh, hd, page, window):
     tiles = []
     row0 = 0
     for r, p0, n in runs:
-        for t0 in range(0, n, 64):
-            tiles.append((r, row0 + t0, min(64, n - t0), p0 + t0))
+        for t0 in range(0, n, 128):
+            tiles.append((r, row0 + t0, min(128, n - t0), p0 + t0))
         row0 += n
     n = len(rows)
     q = torch.randn(n, heads, hd, generator=g).to(dtype)
