@@ -65,3 +65,31 @@ def test_trace_run_program(dtype, tiny_folders, plain_logits, tmp_path):
     vocab = TINY[name][0]["vocab_size"]
     got = run_plan_trace_run(tiny_folders[name], dtype, plan, str(tmp_path / "out"), plan.max_live_tokens(64), vocab)
     compare(plan, got, plain, *TOL[dtype], f"trace_run/{dtype}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(dtype, tiny_folders):
+    """A short prompt and 380 tokens decoded one by one (pages fill and new ones are taken every 16
+    steps; in bfloat16 the decode steps replay a CUDA graph whose key changes as the context grows)."""
+    name = "c"
+    cfg = TINY[name][0]
+    toks = random_requests(cfg["vocab_size"], [400], seed=21)["r0"]
+    plain = {"r0": PlainLlama(tiny_folders[name]).logits(toks)}
+    plan = plan_tail({"r0": toks}, tail=380)
+    built = _built(tiny_folders[name], dtype, 448, 64)
+    got = run_plan_in_process(built.step_fn, plan)
+    compare(plan, got, plain, *TOL[dtype], f"long/{dtype}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+def test_first_tokens_of_a_sequence(name, dtype, tiny_folders):
+    """Requests of one, two and three tokens: position 0 alone, and the first steps from it."""
+    cfg = TINY[name][0]
+    reqs = random_requests(cfg["vocab_size"], [1, 2, 3, 2], seed=22)
+    model = PlainLlama(tiny_folders[name])
+    plain = {r: model.logits(t) for r, t in reqs.items()}
+    for what, plan in (("whole", plan_whole(reqs)), ("one by one", plan_tail(reqs, 32)),
+                       ("together", plan_mixed(reqs, seed=1, decode_tail=1, sizes=(2, 3)))):
+        built = _built(tiny_folders[name], dtype, 256, 64)
+        compare(plan, run_plan_in_process(built.step_fn, plan), plain, *TOL[dtype], f"first/{name}/{dtype}/{what}")
