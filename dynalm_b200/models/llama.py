@@ -110,6 +110,8 @@ class LlamaArchitecture:
             head=HeadSpec(cfg.vocab_size, cfg.hidden_size, tied, cfg.logits_scaling,
                           {} if tied else {"weight": "lm_head.weight"}),
             context_length=cfg.max_position_embeddings,
+            # buffers that older Hugging Face checkpoints carry and nothing reads
+            ignorable=tuple(f"model.layers.{l}.self_attn.rotary_emb.inv_freq" for l in range(cfg.num_hidden_layers)),
         )
         plan.validate()
         return plan

@@ -289,3 +289,133 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
         ref = _toy_reference(w, reqs[r])
         assert np.abs(whole[r] - ref).max() <= 3e-5 * max(1.0, np.abs(ref).max()), f"{r}: whole vs plain"
         assert np.abs(cut[r] - ref).max() <= 3e-5 * max(1.0, np.abs(ref).max()), f"{r}: cut vs plain"
+
+
+# ---------------------------------------------------------------------------------------------
+# another position encoding and a feed-forward with routing, both defined here
+# ---------------------------------------------------------------------------------------------
+
+def _register_toy_parts():
+    from dynalm_b200.parts import TensorDecl, register_feed_forward, register_position
+
+    @register_position("toy_adjacent")
+    class AdjacentPairs:
+        """Rotates ADJACENT pairs (2i, 2i+1) by pos * theta^(-2i/d): no table for the fused kernel, so
+        the attention mixer calls apply() before its cache write."""
+
+        def __init__(self, spec, runtime):
+            d = spec.head_dim
+            self.inv = (spec.theta ** (-torch.arange(0, d, 2, dtype=torch.float64) / d)).to(runtime.device)
+
+        def table(self):
+            return None
+
+        def apply(self, q, k, positions):
+            ang = positions.double()[:, None] * self.inv[None, :]
+            c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+            for x in (q, k):
+                if x is None:
+                    continue
+                a, b = x[..., 0::2].double(), x[..., 1::2].double()
+                x[..., 0::2] = (a * c - b * s).to(x.dtype)
+                x[..., 1::2] = (a * s + b * c).to(x.dtype)
+
+    @register_feed_forward("toy_routed")
+    class TopOneExperts:
+        """Two experts, each a plain matrix; a token goes to the expert with the larger router logit
+        (computed in float32) and is scaled by that logit's sigmoid."""
+
+        @staticmethod
+        def declare(spec):
+            return {"router": TensorDecl((2, spec.width)), "e0": TensorDecl((spec.width, spec.width)),
+                    "e1": TensorDecl((spec.width, spec.width))}
+
+        def __init__(self, spec, tensors, runtime):
+            self.t = tensors
+
+        def forward(self, x, ctx):
+            logits = x.float() @ self.t["router"].float().T
+            pick = logits.argmax(-1)
+            gate = torch.sigmoid(logits.gather(1, pick[:, None]))
+            y0, y1 = x.float() @ self.t["e0"].float().T, x.float() @ self.t["e1"].float().T
+            return (torch.where(pick[:, None] == 0, y0, y1) * gate).to(x.dtype)
+
+
+def test_toy_position_encoding_and_routed_feed_forward(tmp_path):
+    """A position encoding without a table (the mixer's apply() path) and a feed-forward with routing are
+    registered from here, built into a model through a toy architecture, and stepped whole and cut."""
+    _register_toy_parts()
+    from dynalm_b200.config import (BlockSpec, EmbeddingSpec, FeedForwardSpec, HeadSpec, LayerRun, MixerSpec, ModelPlan,
+                                    NormSpec, PositionSpec)
+    from dynalm_b200.engine import StepEntry, build
+    from dynalm_b200.registry import register_architecture
+    from dynalm_b200.weights import write_model_folder
+
+    W, V, HD = 64, 90, 32
+
+    class Arch:
+        name = "Toy2ForCausalLM"
+        model_types = ("toy2",)
+
+        def read_config(self, obj):
+            return dict(obj)
+
+        def plan(self, c, present=None):
+            def norm(n):
+                return NormSpec("rms", W, 1e-6, {"weight": n})
+            layers = []
+            for l in range(2):
+                p = f"l{l}."
+                layers.append(BlockSpec(
+                    "pre_norm", norm(p + "n1"),
+                    MixerSpec("attention", W, 2, 1, HD, HD ** -0.5, 0, PositionSpec("toy_adjacent", HD, HD, 100.0),
+                              {"q": p + "q", "k": p + "k", "v": p + "v", "o": p + "o"}),
+                    norm(p + "n2"),
+                    FeedForwardSpec("toy_routed", W, tensors={"router": p + "r", "e0": p + "e0", "e1": p + "e1"})))
+            return ModelPlan(EmbeddingSpec(V, W, 1.0, {"weight": "emb"}), layers, [LayerRun(0), LayerRun(1)], norm("final"),
+                             HeadSpec(V, W, True), 128)
+
+    register_architecture(Arch())
+    folder = str(tmp_path / "toy2")
+    write_model_folder(folder, {"architectures": ["Toy2ForCausalLM"], "model_type": "toy2"}, 6, torch.float32)
+    w = plain.read_safetensors(os.path.join(folder, "model.safetensors"))
+    toks = [int(t) for t in np.random.RandomState(3).randint(0, V, 45)]
+
+    # plain reference
+    n = len(toks)
+    x = w["emb"][np.asarray(toks)]
+    pos = np.arange(n)
+    inv = 100.0 ** (-np.arange(0, HD, 2) / HD)
+    ang = pos[:, None] * inv[None, :]
+
+    def rot(t):
+        a, b = t[..., 0::2], t[..., 1::2]
+        out = np.empty_like(t)
+        out[..., 0::2] = a * np.cos(ang)[:, None, :] - b * np.sin(ang)[:, None, :]
+        out[..., 1::2] = a * np.sin(ang)[:, None, :] + b * np.cos(ang)[:, None, :]
+        return out
+
+    for l in range(2):
+        p = f"l{l}."
+        h = plain.rms_norm(x, w[p + "n1"], 1e-6)
+        q = rot((h @ w[p + "q"].T).reshape(n, 2, HD))
+        k = rot((h @ w[p + "k"].T).reshape(n, 1, HD))
+        v = (h @ w[p + "v"].T).reshape(n, 1, HD)
+        x = x + plain.attention(q, k, v, HD ** -0.5).reshape(n, 2 * HD) @ w[p + "o"].T
+        h = plain.rms_norm(x, w[p + "n2"], 1e-6)
+        logits = h @ w[p + "r"].T
+        pick = logits.argmax(-1)
+        gate = 1.0 / (1.0 + np.exp(-logits[np.arange(n), pick]))
+        y = np.where(pick[:, None] == 0, h @ w[p + "e0"].T, h @ w[p + "e1"].T) * gate[:, None]
+        x = x + y
+    ref = plain.rms_norm(x, w["final"], 1e-6) @ w["emb"].T
+
+    for cuts in ([45], [16, 7, 2, 5, 3, 2, 1, 1, 8]):
+        built = build(folder, dtype="float32", kv_tokens=128, max_batch_tokens=64, max_requests=2)
+        assert not built.model.graph_safe          # the toy feed-forward does not claim it, so nothing is captured
+        got, p0 = [], 0
+        for c in cuts:
+            got.append(built.step_fn.step([StepEntry("r", toks[p0:p0 + c], list(range(c)))]).cpu().numpy().copy())
+            p0 += c
+        got = np.concatenate(got)
+        assert np.abs(got - ref).max() <= 5e-5 * max(1.0, np.abs(ref).max()), f"cuts {cuts}"

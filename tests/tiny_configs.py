@@ -30,4 +30,13 @@ TINY_C = {
     "embedding_multiplier": 3.0, "residual_multiplier": 0.5, "attention_multiplier": 0.2, "logits_scaling": 4.0,
 }
 
-TINY = {"a": (TINY_A, 0), "b": (TINY_B, 2), "c": (TINY_C, 9)}   # name -> (config, weight seed)
+# Sizes that defeat every vector path: a width and an inner width that are no multiple of 8, an odd vocabulary,
+# one KV head for five heads, 4 layers, nothing optional given.
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "vocab_size": 301, "hidden_size": 100, "intermediate_size": 172, "num_hidden_layers": 4,
+    "num_attention_heads": 5, "num_key_value_heads": 1, "head_dim": 16, "max_position_embeddings": 300,
+    "rms_norm_eps": 1e-5,
+}
+
+TINY = {"a": (TINY_A, 0), "b": (TINY_B, 2), "c": (TINY_C, 9), "d": (TINY_D, 4)}   # name -> (config, weight seed)
