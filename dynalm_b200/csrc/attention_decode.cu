@@ -8,9 +8,13 @@
 // running (max, sum, acc) of the online softmax is kept per lane in fp32 and merged at the end over
 // the warp's key slots, then over the block's warps in shared memory. With more than one split the
 // block writes its unnormalised (acc, max, sum) to scratch and `attention_combine_kernel` merges the
-// splits by the log-sum-exp rule of the reference's split-K variant (:1782-1845).
+// splits by the log-sum-exp rule of the reference's split-K variant (:1782-1845); the tensor-core variant
+// instead launches the splits of a row as one thread-block cluster and merges them in the shared memory of
+// the cluster's first block.
 //
 // Scratch layout: part[((row * n_heads + head) * n_split + split) * (head_dim + 2)] = acc[head_dim], max, sum.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace dl {
@@ -326,7 +330,8 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
                            const bf16* __restrict__ v_cache, const int* __restrict__ block_table, int max_blocks,
                            const int* __restrict__ positions, const int* __restrict__ row_request,
                            bf16* __restrict__ out, int out_stride, float* __restrict__ part, int n_heads,
-                           int n_kv_heads, int page_shift, float scale_log2, int window, int n_split) {
+                           int n_kv_heads, int page_shift, float scale_log2, int window, int n_split,
+                           int cluster_merge, int xbuf_offset) {
   constexpr int LD = HD + 8;
   constexpr int CH = HD / 8;
   constexpr int KS = HD / 16;
@@ -526,12 +531,42 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
     const int head = head0 + r;
     if (n_split == 1) {
       out[static_cast<size_t>(row) * out_stride + static_cast<size_t>(head) * HD + d] = __float2bfloat16_rn(a / ll);
+    } else if (cluster_merge) {
+      // the splits of one (row, KV head) are the blocks of one cluster: every block leaves its record in the
+      // shared memory of the cluster's first block
+      namespace cg = cooperative_groups;
+      float* xbuf = reinterpret_cast<float*>(dt_smem + xbuf_offset);
+      float* dst = cg::this_cluster().map_shared_rank(xbuf, 0) + (static_cast<size_t>(split) * 16 + r) * REC;
+      dst[d] = a;
+      if (d == 0) {
+        dst[HD] = mm;
+        dst[HD + 1] = ll;
+      }
     } else {
       float* dst = part + ((static_cast<size_t>(row) * n_heads + head) * n_split + split) * REC;
       dst[d] = a;
       if (d == 0) {
         dst[HD] = mm;
         dst[HD + 1] = ll;
+      }
+    }
+  }
+  if (n_split > 1 && cluster_merge) {
+    cooperative_groups::this_cluster().sync();       // every record has arrived (and is visible) in block 0
+    if (split == 0) {
+      const float* xbuf = reinterpret_cast<const float*>(dt_smem + xbuf_offset);
+      for (int idx = tid; idx < ng * HD; idx += DT_THREADS) {
+        const int r = idx / HD, d = idx % HD;
+        float mm = -INFINITY;
+        for (int sp = 0; sp < n_split; ++sp) mm = fmaxf(mm, xbuf[(sp * 16 + r) * REC + HD]);
+        float a = 0.0f, ll = 0.0f;
+        for (int sp = 0; sp < n_split; ++sp) {          // in split order, as attention_combine_kernel
+          const float* src = xbuf + (sp * 16 + r) * REC;
+          const float c = src[HD] == -INFINITY ? 0.0f : exp2f(src[HD] - mm);
+          a += src[d] * c;
+          ll += src[HD + 1] * c;
+        }
+        out[static_cast<size_t>(row) * out_stride + static_cast<size_t>(head0 + r) * HD + d] = __float2bfloat16_rn(a / ll);
       }
     }
   }
@@ -544,21 +579,40 @@ int launch_decode_tc(const void* q, int q_stride, const void* kc, const void* vc
                      cudaStream_t stream) {
   constexpr size_t pipe = static_cast<size_t>(16 + DT_WARPS * STAGES * 2 * DT_KT) * (HD + 8) * sizeof(bf16);
   constexpr size_t mrg = static_cast<size_t>(DT_WARPS) * 16 * (HD + 2) * sizeof(float);
-  constexpr size_t smem = pipe > mrg ? pipe : mrg;
-  static bool configured = false;
-  if (!configured) {
+  constexpr size_t base = ((pipe > mrg ? pipe : mrg) + 15) & ~static_cast<size_t>(15);
+  // Up to 8 splits can merge through the shared memory of a cluster's first block. Measured on B200: that wins
+  // for a handful of rows (batch 1: 1063 against 1010 tokens/s) and loses once the grid is a few dozen clusters
+  // (batch 8: 1.24 ms against 1.13 ms per step), where global scratch and the merge kernel do better.
+  const int group_blocks = n_kv_heads * ((n_heads / n_kv_heads + 15) / 16);
+  const bool cluster = n_split > 1 && n_split <= 8 && (part == nullptr || rows * group_blocks <= 32);
+  const size_t smem = base + (cluster ? static_cast<size_t>(n_split) * 16 * (HD + 2) * sizeof(float) : 0);
+  static size_t configured = 0;
+  if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(decode_attention_tc_kernel<HD, STAGES>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
+    configured = smem;
   }
   const int group = n_heads / n_kv_heads;
   dim3 grid(n_split, n_kv_heads * ((group + 15) / 16), rows);
-  int rc = launch(decode_attention_tc_kernel<HD, STAGES>, grid, dim3(DT_THREADS), smem, stream,
-                  static_cast<const bf16*>(q), q_stride, static_cast<const bf16*>(kc), static_cast<const bf16*>(vc),
-                  block_table, max_blocks, positions, row_request, static_cast<bf16*>(out), out_stride, part, n_heads,
-                  n_kv_heads, page_shift, scale * 1.4426950408889634f, window, n_split);
-  if (rc != 0 || n_split == 1) return rc;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(DT_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(n_split);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = cluster ? 1 : 0;
+  int rc = static_cast<int>(cudaLaunchKernelEx(
+      &cfg, decode_attention_tc_kernel<HD, STAGES>, static_cast<const bf16*>(q), q_stride, static_cast<const bf16*>(kc),
+      static_cast<const bf16*>(vc), block_table, max_blocks, positions, row_request, static_cast<bf16*>(out), out_stride,
+      part, n_heads, n_kv_heads, page_shift, scale * 1.4426950408889634f, window, n_split, cluster ? 1 : 0,
+      static_cast<int>(base)));
+  if (rc != 0 || n_split == 1 || cluster) return rc;
   dim3 cgrid(n_heads, rows);
   const int cthreads = HD <= 32 ? 32 : (HD <= 64 ? 64 : 128);
   return launch(attention_combine_kernel<bf16>, cgrid, dim3(cthreads), 0, stream, static_cast<const float*>(part),
@@ -593,7 +647,8 @@ DL_EXPORT int dl_paged_attention_decode(int dtype, const void* q, int q_stride, 
 }
 
 // The tensor-core variant: bfloat16, head_dim a multiple of 16 up to 128, q rows 16-byte aligned. Same
-// arguments and scratch as dl_paged_attention_decode.
+// arguments as dl_paged_attention_decode. Up to 8 splits are the blocks of a thread-block cluster and merge through
+// distributed shared memory (no scratch is touched); more splits use the scratch and the merge kernel.
 DL_EXPORT int dl_paged_attention_decode_tc(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                            const int* block_table, int max_blocks, const int* positions,
                                            const int* row_request, void* out, int out_stride, float* part, int rows,
@@ -603,7 +658,7 @@ DL_EXPORT int dl_paged_attention_decode_tc(const void* q, int q_stride, const vo
   int page_shift = 0;
   while ((1 << page_shift) < page_size) ++page_shift;
   if ((1 << page_shift) != page_size || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || n_split < 1 || rows > 65535 ||
-      (q_stride & 7) || (n_split > 1 && part == nullptr))
+      (q_stride & 7) || (n_split > 8 && part == nullptr))   // without scratch, up to 8 splits merge in a cluster
     return DL_ERR_UNSUPPORTED;
 #define DL_CASE(H, S)                                                                                                 \
   case H:                                                                                                             \

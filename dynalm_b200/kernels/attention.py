@@ -15,6 +15,7 @@ from . import ops
 
 SM_COUNT = 148            # B200
 MAX_SPLITS = 32
+CLUSTER_SPLITS = 8          # up to here the tensor-core kernel merges splits inside a thread-block cluster
 DECODE_FILL = int(__import__('os').environ.get('DYNALM_DECODE_FILL', '1'))   # blocks per SM the split count aims for
 
 
@@ -24,7 +25,7 @@ def decode_splits(rows: int, n_heads: int, n_kv_heads: int, max_kv_len: int, ten
     group = n_heads // n_kv_heads
     blocks = rows * n_kv_heads * (-(-group // (16 if tensor_cores else 4)))
     want = -(-DECODE_FILL * SM_COUNT // max(blocks, 1))
-    return max(1, min(want, max(1, max_kv_len // 128), MAX_SPLITS))
+    return max(1, min(want, max(1, max_kv_len // 128), CLUSTER_SPLITS if tensor_cores else MAX_SPLITS))
 
 
 def decode_uses_tensor_cores(spec) -> bool:

@@ -278,7 +278,7 @@ def test_sample_temperature_frequencies(ops):
                                                                (3, 3, 80, 32, 0, 2), (8, 2, 128, 16, 40, 2),
                                                                (16, 2, 64, 16, 0, 5), (32, 8, 64, 16, 0, 8),
                                                                (4, 4, 256, 16, 0, 2), (4, 4, 64, 16, 7, 1),
-                                                               (40, 2, 64, 16, 0, 3), (2, 1, 112, 64, 300, 6)])
+                                                               (40, 2, 64, 16, 0, 3), (2, 1, 112, 64, 300, 6), (4, 2, 64, 16, 0, 12)])
 def test_paged_attention_decode(ops, dtype, heads, kvh, hd, page, window, splits):
     """The split-KV kernel against the same reference as the plain kernel: requests of 1, 60, 700 and
     130 tokens in scattered pages, one row each at its last position, a far key that stands out,
