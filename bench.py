@@ -31,6 +31,17 @@ LLAMA_1B = {
     "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
                      "original_max_position_embeddings": 8192},
 }
+# BASELINE.json configs[3] and [4]: the 3B and 8B shapes with their serving workloads.
+LLAMA_3B = dict(LLAMA_1B, hidden_size=3072, num_hidden_layers=28, num_attention_heads=24, num_key_value_heads=8,
+                head_dim=128, intermediate_size=8192)
+LLAMA_8B = dict(LLAMA_1B, hidden_size=4096, num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8,
+                head_dim=128, intermediate_size=14336, tie_word_embeddings=False,
+                rope_scaling=dict(LLAMA_1B["rope_scaling"], factor=8.0))
+SERVING = {
+    # name: (config, weight seed, requests, prompt lengths (lo, hi), prompt seed, decode tokens, prefill chunk)
+    "serve3b": (LLAMA_3B, 5, 32, (128, 4096), 6, 256, 512),
+    "serve8b": (LLAMA_8B, 7, 64, (1024, 1024), 8, 512, 512),
+}
 FULL_LAYERS = 16
 CONTEXT = 8192          # benchmark context length: the longest a request may grow
 HELD = 2048             # tokens each sequence holds when decoding
@@ -112,6 +123,64 @@ def prefill_flops(cfg, layers, T):
     return 2.0 * layers * per_layer * T + 4.0 * nh * hd * layers * T * (T + 1) / 2 + 2.0 * V * H
 
 
+def serving(name, layers=None):
+    """Continuous batching end to end through the Python entry point: all requests submitted at once, prompts
+    prefilled in chunks beside decode rows, every request decoding its full count. Prints one JSON line."""
+    import numpy as np
+    import torch
+    from dynalm_b200 import Engine, Request, SchedulerConfig
+
+    cfg, wseed, n_req, (lo, hi), pseed, n_decode, chunk = SERVING[name]
+    cfg = dict(cfg)
+    full_layers = cfg["num_hidden_layers"]
+    if layers:
+        cfg["num_hidden_layers"] = layers
+    rng = np.random.RandomState(pseed)
+    lens = [int(rng.randint(lo, hi + 1)) for _ in range(n_req)]
+    prompts = [[int(t) for t in rng.randint(0, cfg["vocab_size"], n)] for n in lens]
+    kv_tokens = sum(-(-(n + n_decode) // 16) * 16 for n in lens) + 1024
+    t0 = time.time()
+    eng = Engine(config=cfg, random_seed=wseed, dtype="bfloat16", ctx=kv_tokens, batch=chunk + n_req, max_running=n_req,
+                 scheduler=SchedulerConfig(max_running=n_req, decode_token_budget=n_req, prefill_token_budget=chunk,
+                                           max_prefill_chunk=chunk, max_batch_tokens=chunk + n_req))
+    print(f"[bench] {name}: engine built in {time.time() - t0:.1f} s", file=sys.stderr)
+    warm = eng.generate(prompts[0][:64], max_tokens=4)          # loads kernels, captures nothing of the timed run
+    assert len(warm.tokens) == 4
+    for p in prompts:
+        eng.scheduler.submit(Request(p, max_new_tokens=n_decode))
+    done, first, n_tok = 0, {}, 0
+    torch.cuda.synchronize()
+    with ClockSampler() as cs:
+        t0 = time.perf_counter()
+        while not eng.scheduler.idle:
+            for ev in eng.scheduler.step():
+                if ev.token is not None:
+                    n_tok += 1
+                    first.setdefault(ev.request_id, time.perf_counter() - t0)
+                done += ev.finished
+        torch.cuda.synchronize()
+        total = time.perf_counter() - t0
+    st = eng.scheduler.stats
+    ttft = sorted(first.values())
+    out = {
+        "metric": f"continuous batching, {name}: generated tokens/s over the whole run", "value": round(n_tok / total, 1),
+        "unit": "tokens/s", "n_gpus": 1, "impl": "ours", "dtype": "bf16", "seconds": round(total, 3),
+        "requests": n_req, "finished": done, "generated": n_tok, "prompt_tokens": sum(lens),
+        "prompt_tokens_per_s": round(sum(lens) / total, 1),
+        "ttft_ms": {"p50": round(ttft[len(ttft) // 2] * 1e3, 1), "max": round(ttft[-1] * 1e3, 1)},
+        "steps": {"decode_only": st.steps_decode_only, "prefill_only": st.steps_prefill_only, "mixed": st.steps_mixed},
+        "decode_step_ms": round(st.forward_decode_only_ms / max(1, st.steps_decode_only), 3),
+        "preemptions": st.preemptions,
+        "config": {"model": name, "layers": cfg["num_hidden_layers"], "layers_full": full_layers, "hidden": cfg["hidden_size"],
+                   "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "prefill_chunk": chunk,
+                   "decode_tokens": n_decode, "kv_tokens": kv_tokens},
+        "clocks": cs.result, "data": "synthetic: random weights, random token ids",
+    }
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -120,6 +189,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--workload", choices=["decode"] + sorted(SERVING), default="decode",
+                    help="decode: the default benchmark; serve3b / serve8b: continuous batching of the 3B / 8B workloads")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel (for profiling)")
     ap.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
@@ -135,6 +206,8 @@ def main():
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.workload != "decode":
+        return serving(args.workload, args.layers if args.layers != FULL_LAYERS else None)
     W = max(3, args.warmup)
     K = max(1, args.steps)
 

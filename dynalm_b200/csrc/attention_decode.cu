@@ -382,10 +382,30 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
   }
 
   bf16* my = KV + static_cast<size_t>(warp) * STAGES * 2 * TILE_ELEMS;
+  // When the block's key range starts on a multiple of 16 (always, unless a window moves it) and pages hold at
+  // least 16 keys, every 16 keys of a tile lie in one page: one table lookup serves 16 key rows.
+  const bool by_halves = (k_begin & 15) == 0 && page_shift >= 4;
   auto load_tile = [&](int i, int stage) {          // this warp's i-th tile: block tile i * DT_WARPS + warp
     const int key0 = k_begin + (i * DT_WARPS + warp) * DT_KT;
     bf16* kd = my + static_cast<size_t>(stage) * 2 * TILE_ELEMS;
     bf16* vd = kd + TILE_ELEMS;
+    if (by_halves) {
+#pragma unroll
+      for (int hf = 0; hf < DT_KT / 16; ++hf) {
+        const int kb = key0 + hf * 16;
+        size_t slot0 = 0;
+        if (kb < k_end) slot0 = (static_cast<size_t>(table[kb >> page_shift]) << page_shift) + (kb & page_mask);
+#pragma unroll
+        for (int c = lane; c < 16 * CH; c += 32) {
+          const int r = c / CH, ch = c % CH;
+          const bool ok = kb + r < k_end;
+          const size_t off = ok ? (slot0 + r) * kv_row + static_cast<size_t>(kvh) * HD + ch * 8 : 0;
+          dt_cp_async16(kd + (hf * 16 + r) * LD + ch * 8, k_cache + off, ok);
+          dt_cp_async16(vd + (hf * 16 + r) * LD + ch * 8, v_cache + off, ok);
+        }
+      }
+      return;
+    }
 #pragma unroll
     for (int c = lane; c < DT_KT * CH; c += 32) {
       const int r = c / CH, ch = c % CH;
