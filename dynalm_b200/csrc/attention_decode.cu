@@ -319,6 +319,11 @@ __device__ __forceinline__ void dt_mma(float (&d)[4], const uint32_t (&a)[4], ui
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ float dt_exp2(float x) {     // one special-function instruction; 2^-inf = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t dt_pack(float lo, float hi) {
   __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&p);
@@ -457,34 +462,33 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
         dt_mma(s[2 * np + 1], qf[ks], kb[2], kb[3]);
       }
     }
+    // raw scores stay in s; the maximum is kept in scaled (base-2) units and the scale is folded into the exponent
     const bool edge = key0 + DT_KT > k_end;
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int j = 0; j < DT_KT / 8; ++j) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        float v = s[j][e] * scale_log2;
-        if (edge && key0 + j * 8 + 2 * t + (e & 1) >= k_end) v = -INFINITY;
-        s[j][e] = v;
-        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        if (edge && key0 + j * 8 + 2 * t + (e & 1) >= k_end) s[j][e] = -INFINITY;
+        mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
       }
     }
-    float corr[2];
+    float corr[2], neg_m[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
       mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-      const float m_new = fmaxf(m_run[h], mx[h]);       // finite: the first key of every tile is in range
-      corr[h] = exp2f(m_run[h] - m_new);
+      const float m_new = fmaxf(m_run[h], mx[h] * scale_log2);       // finite: the first key of every tile is in range
+      corr[h] = dt_exp2(m_run[h] - m_new);
       m_run[h] = m_new;
-      mx[h] = m_new;
+      neg_m[h] = -m_new;
     }
     float ls[2] = {0.0f, 0.0f};
     uint32_t pf[DT_KT / 16][4];
 #pragma unroll
     for (int j = 0; j < DT_KT / 8; ++j) {
-      const float p0 = exp2f(s[j][0] - mx[0]), p1 = exp2f(s[j][1] - mx[0]);
-      const float p2 = exp2f(s[j][2] - mx[1]), p3 = exp2f(s[j][3] - mx[1]);
+      const float p0 = dt_exp2(fmaf(s[j][0], scale_log2, neg_m[0])), p1 = dt_exp2(fmaf(s[j][1], scale_log2, neg_m[0]));
+      const float p2 = dt_exp2(fmaf(s[j][2], scale_log2, neg_m[1])), p3 = dt_exp2(fmaf(s[j][3], scale_log2, neg_m[1]));
       ls[0] += p0 + p1;
       ls[1] += p2 + p3;
       pf[j >> 1][(j & 1) * 2] = dt_pack(p0, p1);
@@ -678,7 +682,7 @@ DL_EXPORT int dl_paged_attention_decode_tc(const void* q, int q_stride, const vo
   int page_shift = 0;
   while ((1 << page_shift) < page_size) ++page_shift;
   if ((1 << page_shift) != page_size || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || n_split < 1 || rows > 65535 ||
-      (q_stride & 7) || (n_split > 8 && part == nullptr))   // without scratch, up to 8 splits merge in a cluster
+      (q_stride & 7) || !(scale > 0.0f) || (n_split > 8 && part == nullptr))   // without scratch, up to 8 splits merge in a cluster
     return DL_ERR_UNSUPPORTED;
 #define DL_CASE(H, S)                                                                                                 \
   case H:                                                                                                             \

@@ -46,6 +46,12 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x by the special-function unit: one instruction; 2^-inf = 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&p);
@@ -94,20 +100,37 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
     const bf16* src = q + static_cast<size_t>(row0 + (ok ? r : 0)) * q_stride + static_cast<size_t>(head) * HD + ch * 8;
     cp_async16(Qs + r * LD + ch * 8, src, ok);
   }
+  // A thread copies the same (row, 16-byte piece) places of every key tile: what does not change from tile to
+  // tile is computed once.
+  constexpr int KV_ITERS = (PF_BN * CH + PF_THREADS - 1) / PF_THREADS;
+  int kv_r[KV_ITERS];                  // key row inside the tile, -1 past the tile
+  uint32_t kv_soff[KV_ITERS];          // byte offset inside a stage's K (or V) tile
+  size_t kv_goff[KV_ITERS];            // element offset inside a cache row
+#pragma unroll
+  for (int it = 0; it < KV_ITERS; ++it) {
+    const int c = tid + it * PF_THREADS;
+    const int r = c / CH, ch = c % CH;
+    kv_r[it] = c < PF_BN * CH ? r : -1;
+    kv_soff[it] = static_cast<uint32_t>((r * LD + ch * 8) * sizeof(bf16));
+    kv_goff[it] = static_cast<size_t>(kvh) * HD + ch * 8;
+  }
+  const uint32_t ks_base = static_cast<uint32_t>(__cvta_generic_to_shared(Ks));
+  const uint32_t vs_base = static_cast<uint32_t>(__cvta_generic_to_shared(Vs));
   auto load_kv = [&](int j, int stage) {
-    bf16* kd = Ks + stage * PF_BN * LD;
-    bf16* vd = Vs + stage * PF_BN * LD;
-    for (int c = tid; c < PF_BN * CH; c += PF_THREADS) {
-      const int r = c / CH, ch = c % CH;
-      const int key = j * PF_BN + r;
+    const uint32_t stage_off = static_cast<uint32_t>(stage * PF_BN * LD * sizeof(bf16));
+#pragma unroll
+    for (int it = 0; it < KV_ITERS; ++it) {
+      if (kv_r[it] < 0) continue;
+      const int key = j * PF_BN + kv_r[it];
       const bool ok = key >= lo_tile && key <= pos_last;
       size_t off = 0;
       if (ok) {
         const size_t slot = (static_cast<size_t>(table[key >> page_shift]) << page_shift) + (key & page_mask);
-        off = slot * kv_row + static_cast<size_t>(kvh) * HD + ch * 8;
+        off = slot * kv_row + kv_goff[it];
       }
-      cp_async16(kd + r * LD + ch * 8, k_cache + off, ok);
-      cp_async16(vd + r * LD + ch * 8, v_cache + off, ok);
+      const int bytes = ok ? 16 : 0;      // 0 source bytes: the 16 destination bytes are zero-filled
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(ks_base + stage_off + kv_soff[it]), "l"(k_cache + off), "r"(bytes));
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(vs_base + stage_off + kv_soff[it]), "l"(v_cache + off), "r"(bytes));
     }
   };
   load_kv(j_begin, 0);
@@ -178,37 +201,39 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
     for (int mt = 0; mt < PF_MT; ++mt) {
       const bool edge = key0 + PF_BN - 1 > pos0 + warp * (16 * PF_MT) + mt * 16 ||
                         (window > 0 && key0 < max(lo_r[mt][0], lo_r[mt][1]));
+      // Raw scores stay in s; the running maximum is kept in scaled (base-2) units, and the scale is folded
+      // into the exponent: p = 2^(s * scale - max).
       float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
       for (int i = 0; i < PF_BN / 8; ++i) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          float v = s[mt][i][e] * scale_log2;
+          float v = s[mt][i][e];
           if (edge) {
             const int key = key0 + i * 8 + 2 * t + (e & 1);
             if (key > pos_r[mt][e >> 1] || key < lo_r[mt][e >> 1]) v = -INFINITY;
+            s[mt][i][e] = v;
           }
-          s[mt][i][e] = v;
           mx[e >> 1] = fmaxf(mx[e >> 1], v);
         }
       }
-      float corr[2];
+      float corr[2], neg_m[2];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-        const float m_new = fmaxf(m_run[mt][h], mx[h]);
+        const float m_new = fmaxf(m_run[mt][h], mx[h] * scale_log2);     // the scale is positive
         // a row with no visible key so far (rows past the end of the tile, or a window that starts
         // later) keeps max = -inf; its probabilities are exact zeros
-        corr[h] = m_new == -INFINITY ? 1.0f : exp2f(m_run[mt][h] - m_new);
+        corr[h] = m_new == -INFINITY ? 1.0f : fast_exp2(m_run[mt][h] - m_new);
         m_run[mt][h] = m_new;
-        mx[h] = m_new == -INFINITY ? 0.0f : m_new;
+        neg_m[h] = m_new == -INFINITY ? 0.0f : -m_new;
       }
       float ls[2] = {0.0f, 0.0f};
 #pragma unroll
       for (int i = 0; i < PF_BN / 8; ++i) {
-        const float p0 = exp2f(s[mt][i][0] - mx[0]), p1 = exp2f(s[mt][i][1] - mx[0]);
-        const float p2 = exp2f(s[mt][i][2] - mx[1]), p3 = exp2f(s[mt][i][3] - mx[1]);
+        const float p0 = fast_exp2(fmaf(s[mt][i][0], scale_log2, neg_m[0])), p1 = fast_exp2(fmaf(s[mt][i][1], scale_log2, neg_m[0]));
+        const float p2 = fast_exp2(fmaf(s[mt][i][2], scale_log2, neg_m[1])), p3 = fast_exp2(fmaf(s[mt][i][3], scale_log2, neg_m[1]));
         ls[0] += p0 + p1;
         ls[1] += p2 + p3;
         pf[mt][i >> 1][(i & 1) * 2] = pack_bf16(p0, p1);
@@ -220,10 +245,13 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
         ls[h] += __shfl_xor_sync(0xffffffffu, ls[h], 2);
         l_run[mt][h] = l_run[mt][h] * corr[h] + ls[h];
       }
+      // once the maxima have settled the correction is exactly 1 for every row of the warp: skip the rescale
+      if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {
 #pragma unroll
-      for (int i = 0; i < HD / 8; ++i) {
-        o[mt][i][0] *= corr[0]; o[mt][i][1] *= corr[0];
-        o[mt][i][2] *= corr[1]; o[mt][i][3] *= corr[1];
+        for (int i = 0; i < HD / 8; ++i) {
+          o[mt][i][0] *= corr[0]; o[mt][i][1] *= corr[0];
+          o[mt][i][2] *= corr[1]; o[mt][i][3] *= corr[1];
+        }
       }
     }
     // O += P V
@@ -298,7 +326,7 @@ DL_EXPORT int dl_paged_attention_prefill(const void* q, int q_stride, const void
   int page_shift = 0;
   while ((1 << page_shift) < page_size) ++page_shift;
   if ((1 << page_shift) != page_size || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || n_heads > 65535 ||
-      (q_stride & 7) || (out_stride & 1))
+      (q_stride & 7) || (out_stride & 1) || !(scale > 0.0f))
     return DL_ERR_UNSUPPORTED;
 #define DL_CASE(H)                                                                                                  \
   case H:                                                                                                           \
