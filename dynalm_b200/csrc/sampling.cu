@@ -154,7 +154,21 @@ sample_temperature_kernel(const float* __restrict__ logits, int ld, int vocab,
   }
 }
 
+// Token feedback for a step launched before the previous step's tokens have reached the host: row r of the new
+// step takes the id that the previous step chose at place src[r] of its output (src[r] < 0: keep what the host wrote).
+__global__ void feedback_tokens_kernel(int* __restrict__ token_ids, const int* __restrict__ chosen,
+                                       const int* __restrict__ src, int n) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r < n && src[r] >= 0) token_ids[r] = chosen[src[r]];
+}
+
 }  // namespace dl
+
+DL_EXPORT int dl_feedback_tokens(int* token_ids, const int* chosen, const int* src, int n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  dl::feedback_tokens_kernel<<<(n + 127) / 128, 128, 0, stream>>>(token_ids, chosen, src, n);
+  return dl::launch_status();
+}
 
 // scratch: room for rows * 32 floats and rows * 32 ints (rows * 256 bytes), or null to use one block per row.
 DL_EXPORT int dl_argmax(const float* logits, int ld, int rows, int vocab, int* out, void* scratch,

@@ -6,6 +6,14 @@ run it, sample where a request's pending work was completed, emit events. The de
 reference's scheduler (dynalm/src/scheduler/scheduler.cpp:234-353 admission and validation,
 :357-378 preemption, :380-778 the step; sequence states dynalm/src/runtime/sequence.cpp:24-93).
 
+Decoding one step ahead: when the executor can `launch` a batch and `collect` it later (the GPU executor can,
+for decode batches sampled on the device), a decode batch is issued without waiting for its tokens, and the
+next call of `step` issues the following decode batch BEFORE collecting the first: the new batch takes its
+tokens on the device from what the previous one chose. The host's work for a step then overlaps the GPU's, and
+the events of a batch are returned one call later. This happens only in the steady state (nothing incoming or
+waiting, no cancellation, every running request in that batch); a request that ends on a stop token has one
+surplus token computed, whose result is dropped; a request that ends by length is never issued past its end.
+
 When pages run out while a batch is planned, the most recently admitted OTHER running request is
 preempted: all its pages are given back, it keeps its generated tokens, goes to the front of the
 waiting queue and is recomputed (prompt and generated tokens as one prompt) when it is admitted
@@ -185,6 +193,9 @@ class Scheduler:
         self._admit_counter = 0
         self._callbacks: Dict[int, Callable[[Event], None]] = {}
         self._last_rows = (0, 0)
+        self._inflight = None          # (batch, what executor.launch returned, launch time): issued, not yet collected
+        self._last_done = 0.0
+        self.lookahead = hasattr(executor, "launch") and hasattr(executor, "collect")
 
     # ---- submission ----------------------------------------------------------------------------------
     def submit(self, req: Request) -> int:
@@ -205,7 +216,7 @@ class Scheduler:
 
     @property
     def idle(self) -> bool:
-        return not (self.incoming or self.waiting or self.running)
+        return not (self.incoming or self.waiting or self.running or self._inflight)
 
     # ---- one iteration ---------------------------------------------------------------------------------
     def _fail(self, seq: SequenceState, msg: str, events: List[Event]) -> None:
@@ -349,17 +360,80 @@ class Scheduler:
                 return batch
         return []
 
+    def _plan_ahead(self, prev: List[BatchItem]) -> Optional[List[BatchItem]]:
+        """The decode batch that follows `prev` (issued, not yet collected), or None when the steady state does
+        not hold. Tokens are placeholders: the executor feeds them on the device from what `prev` chose."""
+        if self.incoming or self.waiting or len(prev) != len(self.running):
+            return None
+        if any(s.cancel_requested or s.terminal for s in self.running):
+            return None
+        if sum(1 for b in prev if b.seq.generated + 1 < b.seq.req.max_new_tokens) > self.cfg.decode_token_budget:
+            return None
+        nxt: List[BatchItem] = []
+        try:
+            for b in prev:
+                seq = b.seq
+                if seq.generated + 1 >= seq.req.max_new_tokens:
+                    continue                                  # `prev` gives it its last token
+                start = b.start + len(b.tokens)
+                self.ex.cache.reserve(seq.id, start + 1)
+                nxt.append(BatchItem(seq, start, [0], sample=True))
+        except ResourceExhausted:
+            return None                                       # the ordinary path will preempt
+        return nxt or None
+
+    def _dispatch(self, events: List[Event]) -> List[Event]:
+        for ev in events:
+            seq_cb = self._callbacks.pop(ev.request_id, None) if ev.finished else self._callbacks.get(ev.request_id)
+            if seq_cb is not None:
+                seq_cb(ev)
+        return events
+
     def step(self) -> List[Event]:
         """One iteration. Returns the events of this step (also sent to each request's callback)."""
         events: List[Event] = []
         admitted: List[int] = []
         preempted: List[int] = []
+        if self._inflight is not None:
+            prev, launched, t_launch = self._inflight
+            nxt = self._plan_ahead(prev)
+            nxt_launched = None
+            t_next = time.perf_counter()
+            if nxt is not None:
+                try:
+                    nxt_launched = self.ex.launch(nxt, after=launched)
+                except EngineError:
+                    nxt = None
+            try:
+                sampled = self.ex.collect(launched)
+            except EngineError as e:
+                for b in prev:
+                    self._fail(b.seq, f"forward failed: {e}", events)
+                sampled = None
+            # a batch's time: from its launch, or from the moment the batch before it was done, to its collection
+            now = time.perf_counter()
+            self._account(prev, (now - max(t_launch, self._last_done)) * 1e3)
+            self._last_done = now
+            if sampled is not None:
+                self._finish_batch(prev, sampled, events)
+            self._inflight = (nxt, nxt_launched, t_next) if nxt is not None else None
+            self._retire_finished_now()
+            if self._inflight is not None or sampled is None:
+                return self._dispatch(events)
+            # nothing was issued ahead: go on with an ordinary iteration in this same call
         self._drain_incoming(events)
         self._retire(events)
         self._admit(admitted)
         if self.running:
             batch = self._plan(events, preempted)
-            if batch:
+            if batch and self.lookahead and self.ex.can_launch(batch):
+                try:
+                    t_launch = time.perf_counter()
+                    self._inflight = (batch, self.ex.launch(batch), t_launch)
+                except EngineError as e:
+                    for b in batch:
+                        self._fail(b.seq, f"forward failed: {e}", events)
+            elif batch:
                 self._run(batch, events)
             step_no = self.stats.steps
             if self.trace is not None:
@@ -368,11 +442,7 @@ class Scheduler:
                     [(b.seq.id, b.start, len(b.tokens), b.sample) for b in batch], preempted, admitted,
                     self.ex.cache.free_pages))
         self._retire_finished_now()
-        for ev in events:
-            seq_cb = self._callbacks.pop(ev.request_id, None) if ev.finished else self._callbacks.get(ev.request_id)
-            if seq_cb is not None:
-                seq_cb(ev)
-        return events
+        return self._dispatch(events)
 
     def _retire_finished_now(self) -> None:
         # Finished requests give their pages back at once rather than at the top of the next
@@ -386,20 +456,10 @@ class Scheduler:
                 keep.append(seq)
         self.running = keep
 
-    def _run(self, batch: List[BatchItem], events: List[Event]) -> None:
+    def _account(self, batch: List[BatchItem], ms: float) -> None:
         self.stats.steps += 1
-        step_no = self.stats.steps
         n_decode = sum(1 for b in batch if len(b.tokens) == 1 and b.seq.status == DECODE)
         n_prefill = sum(len(b.tokens) for b in batch) - n_decode
-        t0 = time.perf_counter()
-        try:
-            sampled = self.ex.run(batch)
-        except EngineError as e:
-            # a failed forward fails only this batch's requests (scheduler.cpp:663-666)
-            for b in batch:
-                self._fail(b.seq, f"forward failed: {e}", events)
-            return
-        ms = (time.perf_counter() - t0) * 1e3
         if n_prefill == 0:
             self.stats.steps_decode_only += 1
             self.stats.forward_decode_only_ms += ms
@@ -411,8 +471,13 @@ class Scheduler:
             self.stats.forward_mixed_ms += ms
         self.stats.tokens_decoded += n_decode
         self.stats.tokens_prefilled += n_prefill
+
+    def _finish_batch(self, batch: List[BatchItem], sampled: Dict[Hashable, int], events: List[Event]) -> None:
+        step_no = self.stats.steps
         for b in batch:
             seq = b.seq
+            if seq.terminal:
+                continue            # ended (stop token, failure) while this batch was already on its way
             seq.mark_computed(len(b.tokens))
             seq.last_step = step_no
             self.ex.cache.advance(seq.id, seq.num_computed)
@@ -425,3 +490,16 @@ class Scheduler:
                 events.append(self._final_event(seq, tok))
             else:
                 events.append(Event(seq.id, tok, False, seq.status, None, None, seq.prompt_len, seq.generated))
+
+    def _run(self, batch: List[BatchItem], events: List[Event]) -> None:
+        t0 = time.perf_counter()
+        try:
+            sampled = self.ex.run(batch)
+        except EngineError as e:
+            # a failed forward fails only this batch's requests (scheduler.cpp:663-666)
+            self.stats.steps += 1
+            for b in batch:
+                self._fail(b.seq, f"forward failed: {e}", events)
+            return
+        self._account(batch, (time.perf_counter() - t0) * 1e3)
+        self._finish_batch(batch, sampled, events)

@@ -56,7 +56,7 @@ class _StepBuffers:
         for name in ("token_ids", "positions", "row_request", "logit_rows"):
             take(name, max_tokens)
         take("q_start", max_requests + 1)
-        for name in ("pos_start", "kv_len", "state_slots"):
+        for name in ("pos_start", "kv_len", "state_slots", "feedback_src"):
             take(name, max_requests)
         self.max_q_tiles = max_tokens // Q_TILE + max_requests
         take("q_tiles", 4 * self.max_q_tiles)
@@ -111,8 +111,11 @@ class BatchBuilder:
         self.cache.free_request(request)
         del self.computed[request]
 
-    def build(self, entries: Sequence[StepEntry], reserve: bool = True) -> StepContext:
-        """Check the batch, reserve pages (unless the caller already has), flatten it and upload it."""
+    def build(self, entries: Sequence[StepEntry], reserve: bool = True,
+              feedback_src: Optional[Sequence[int]] = None) -> StepContext:
+        """Check the batch, reserve pages (unless the caller already has), flatten it and upload it.
+        `feedback_src[r]` (one-token entries only): the place in the previous step's chosen ids that row r's
+        token comes from on the device, or -1 to keep the token given here."""
         if not entries:
             raise InvalidArgument("a step needs at least one entry")
         if len(entries) > self.max_requests:
@@ -185,6 +188,10 @@ class BatchBuilder:
                 h[sec.start + r * mb: sec.start + (r + 1) * mb] = self.cache.table_row(g, e.request)
             r0 += n
         q_start[len(entries)] = r0
+        if feedback_src is not None:
+            if total != len(entries) or len(feedback_src) != len(entries):
+                raise InvalidArgument("token feedback needs one token per entry and one source per entry")
+            h[off["feedback_src"]][:len(entries)] = feedback_src
         b.upload(i)
         d = self._dev
         return StepContext(
@@ -256,10 +263,20 @@ class StepFunction:
             self._caches = [self.cache.view(i, self.batcher.tables) for i in range(len(self.model.order))]
         return self._caches
 
-    def step(self, entries: Sequence[StepEntry], reserve: bool = True) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], reserve: bool = True, token_feedback=None) -> Optional[torch.Tensor]:
         """Run the batch. Returns float32 logits [wanted rows, vocab] on the device (a view of a
-        buffer that the next step overwrites), or None when nothing was wanted."""
-        ctx = self.batcher.build(entries, reserve)
+        buffer that the next step overwrites), or None when nothing was wanted.
+
+        token_feedback = (chosen ids on the device, [source place per entry]): the tokens of this step's
+        one-token entries are taken on the device from the ids a previous step chose, so the step can be
+        issued before those ids have reached the host."""
+        if token_feedback is None:
+            ctx = self.batcher.build(entries, reserve)
+        else:
+            from ..kernels import ops
+            chosen, src = token_feedback
+            ctx = self.batcher.build(entries, reserve, feedback_src=src)
+            ops.feedback_tokens(ctx.token_ids, chosen, self.batcher._dev["feedback_src"], len(entries))
         if self.use_graphs and ctx.decode_only:
             logits = self._replay(ctx)
         else:

@@ -41,6 +41,7 @@ _SIGNATURES = {
     "sampling": {
         "dl_argmax": [_P, _I, _I, _I, _P, _P, _P],
         "dl_sample_temperature": [_P, _I, _I, _I, _P, _P, _P, _P],
+        "dl_feedback_tokens": [_P, _P, _P, _I, _P],
     },
 }
 
@@ -408,6 +409,14 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
         _argmax_scratch[key] = scratch
     _check(_fn("sampling", "dl_argmax")(_p(logits), logits.stride(0), rows, logits.shape[1], _p(out), _p(scratch),
                                          _stream()), "argmax")
+
+
+def feedback_tokens(token_ids: torch.Tensor, chosen: torch.Tensor, src: torch.Tensor, n: int) -> None:
+    """token_ids[r] = chosen[src[r]] for r < n where src[r] >= 0 (all int32, on the device)."""
+    _cuda(token_ids, chosen, src)
+    if token_ids.dtype != torch.int32 or chosen.dtype != torch.int32 or src.dtype != torch.int32 or min(token_ids.numel(), src.numel()) < n:
+        raise InvalidArgument("feedback_tokens: int32 tensors with at least n entries")
+    _check(_fn("sampling", "dl_feedback_tokens")(_p(token_ids), _p(chosen), _p(src), n, _stream()), "feedback_tokens")
 
 
 def sample_temperature(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor) -> None:

@@ -207,3 +207,96 @@ def test_admission_waits_for_pages():
     assert [q.id for q in s.running] == [a] and [q.id for q in s.waiting] == [b]
     toks, final = collect(run_all(s))
     assert final[a].status == final[b].status == FINISHED
+
+
+class FakeAsyncExecutor(FakeExecutor):
+    """The fake with `launch` / `collect`, as the GPU executor has them: a decode batch is issued without its
+    tokens being known, and the batch after it may be issued before the first is collected."""
+
+    def __init__(self, *a, **k):
+        super().__init__(*a, **k)
+        self.launched = 0
+        self.ahead = 0
+
+    @staticmethod
+    def can_launch(batch):
+        return bool(batch) and all(b.sample and len(b.tokens) == 1 for b in batch)
+
+    def launch(self, batch, after=None):
+        assert self.can_launch(batch)
+        self.launched += 1
+        self.ahead += after is not None
+        self.batches.append([(b.seq.id, b.start, 1, True) for b in batch])
+        for b in batch:
+            assert self.cache.tokens[b.seq.id] >= b.start + 1
+        return [(b.seq, b.start) for b in batch]
+
+    def collect(self, handle):
+        out = {}
+        for seq, start in handle:
+            assert len(seq.tokens) == start + 1, "the token before this one has not been resolved"
+            h = hashlib.sha256(repr(seq.tokens[:start + 1]).encode()).digest()
+            out[seq.id] = int.from_bytes(h[:4], "little") % self.vocab
+        return out
+
+
+def test_decoding_one_step_ahead_gives_the_same_tokens():
+    ps = prompts(5, [12, 40, 7, 33, 20])
+
+    def run(ex, stop=()):
+        s = Scheduler(ex, SchedulerConfig(max_running=8, decode_token_budget=8, prefill_token_budget=64,
+                                          max_prefill_chunk=32, max_batch_tokens=128))
+        ids = [s.submit(Request(p, max_new_tokens=10 + 3 * i, stop_token_ids=stop)) for i, p in enumerate(ps)]
+        toks, final = collect(run_all(s))
+        assert not ex.live and ex.cache.free_pages == ex.cache.num_pages
+        return [toks[i] for i in ids], [final[i].finish_reason for i in ids]
+
+    plain_toks, plain_reasons = run(FakeExecutor())
+    ex = FakeAsyncExecutor()
+    ahead_toks, ahead_reasons = run(ex)
+    assert ahead_toks == plain_toks and ahead_reasons == plain_reasons == ["length"] * 5
+    assert ex.ahead > 10                                  # most decode batches were issued before the previous one was collected
+    # no request is ever issued past its last token
+    per_req = {}
+    for batch in ex.batches:
+        for rid, start, n, _ in batch:
+            per_req[rid] = max(per_req.get(rid, 0), start + n)
+    for i, p in enumerate(ps):
+        assert per_req[i + 1] == len(p) + 10 + 3 * i - 1
+    # a stop token ends a request although the batch after it is already on its way; the others go on unharmed
+    stop = (plain_toks[1][4],)
+    want_toks, want_reasons = run(FakeExecutor(), stop)
+    got_toks, got_reasons = run(FakeAsyncExecutor(), stop)
+    assert got_toks == want_toks and got_reasons == want_reasons and "eog" in got_reasons
+
+
+def test_one_step_ahead_with_arrivals_cancels_and_few_pages():
+    """Requests arriving, being cancelled and being preempted while batches are in flight: the scheduler falls
+    back to the ordinary iteration whenever the steady state does not hold, and the tokens stay the same."""
+    ps = prompts(6, [40, 90, 17, 120, 64, 33])
+
+    def run(ex):
+        s = Scheduler(ex, SchedulerConfig(max_running=6, decode_token_budget=8, prefill_token_budget=64,
+                                          max_prefill_chunk=32, max_batch_tokens=128))
+        ids = [s.submit(Request(p, max_new_tokens=40)) for p in ps[:3]]
+        events = []
+        for n in range(10000):
+            if s.idle:
+                break
+            events += s.step()
+            if n == 6:
+                ids += [s.submit(Request(p, max_new_tokens=40)) for p in ps[3:]]
+            if n == 30:
+                s.cancel(ids[2])
+        toks, final = collect(events)
+        assert not ex.live and ex.cache.free_pages == ex.cache.num_pages
+        return [toks.get(i, []) for i in ids], [final[i].status for i in ids], s.stats.preemptions
+
+    roomy = run(FakeExecutor(kv_tokens=4096))
+    ahead_roomy = run(FakeAsyncExecutor(kv_tokens=4096))
+    ahead_tight = run(FakeAsyncExecutor(kv_tokens=320))
+    for got in (ahead_roomy, ahead_tight):
+        for i in (0, 1, 3, 4, 5):
+            assert got[0][i] == roomy[0][i] and got[1][i] == FINISHED
+        assert got[1][2] == CANCELLED and got[0][2] == roomy[0][2][:len(got[0][2])]
+    assert ahead_tight[2] > 0
