@@ -1,0 +1,441 @@
+// Paged flash attention for prompt portions on the 5th-generation tensor cores (tcgen05, sm_100a).
+//
+// One thread block per (query tile, head). A query tile is up to 128 consecutive rows of ONE request, as the
+// host cuts them. Keys and values are read in place from the paged cache by TMA, 16 keys (one page, or a
+// piece of a larger page) per copy, in tiles of BN keys whose boundaries are multiples of BN in absolute
+// position, so the arithmetic of a row does not depend on where its portion was cut.
+//
+//   S = Q K^T      tcgen05.mma, M 128, N BN, both operands K-major from shared memory, S in tensor memory
+//   softmax        128 threads, one row each: S from tensor memory, mask by position, running maximum and
+//                  sum in fp32 with base-2 exponentials, P rounded to bf16 into shared memory
+//   O += P V       tcgen05.mma, M 128, N head_dim, P K-major, V read as it lies in the cache (head
+//                  dimension contiguous: an MN-major operand), O in tensor memory
+//
+// Roles: warps 0..3 softmax and the final store, warp 4 (one lane) TMA producer, warp 5 (one lane) issues
+// the MMAs and owns the tensor-memory allocation. The MMA warp issues S of tile i+1 as soon as the softmax
+// warps have read S of tile i, so the tensor core works under the softmax. O is rescaled only when a row's
+// maximum has grown by more than 2^8 since the reference point of its exponentials was set; the result is
+// the same function of the scores, with probabilities kept below 2^8.
+//
+// Two blocks fit an SM (112 KiB of shared memory and 256 tensor-memory columns each).
+//
+// Every wait on an mbarrier is bounded (tcgen05.cuh); on a timeout all roles fall through to the common
+// exit, where tensor memory is freed, and *status tells the host.
+//
+// Formula and masking as the reference's attention (dynacore/cpu/cpu_device.cpp:1309-1412, 1717-1776);
+// its GPU path calls ggml_flash_attn_ext here (dynacore/src/gpu/ggml_graph.cpp:465-484).
+#include <limits.h>
+
+#include "tcgen05.cuh"
+
+namespace dl {
+
+constexpr int FA_BM = 128;             // query rows per block
+constexpr int FA_THREADS = 192;
+constexpr int FA_BOX_KEYS = 16;        // keys per TMA copy
+constexpr uint32_t FA_O_COL = 128;     // first tensor-memory column of O (S starts at 0)
+constexpr uint32_t FA_TMEM_COLS = 256;
+enum { FA_ERR_PRODUCER = 11, FA_ERR_MMA = 12, FA_ERR_SOFTMAX = 13, FA_ERR_ALIGN = 14 };
+
+template <int HD> struct FA {
+  static constexpr int BN = HD == 64 ? 128 : 64;       // keys per tile
+  static constexpr int DB = HD / 64;                   // 64-wide blocks of the head dimension (128 bytes: one swizzle row)
+  static constexpr uint32_t Q_BYTES = FA_BM * HD * 2;
+  static constexpr uint32_t KV_BYTES = BN * HD * 2;    // one K or one V tile
+  static constexpr uint32_t P_BYTES = FA_BM * BN * 2;
+  static constexpr uint32_t BAR_BYTES = 128;
+  static constexpr uint32_t SMEM = Q_BYTES + 4 * KV_BYTES + P_BYTES + BAR_BYTES;
+};
+
+// 2^x on the special-function unit; 2^-inf = 0.
+__device__ __forceinline__ float fa_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// One lane polls, the whole warp takes the same branch (the tensor-memory loads that follow are warp-wide).
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, int lane, int* status, int code, volatile int* abort_flag) {
+  int ready = 0;
+  if (lane == 0) ready = mbar_wait(bar, parity, status, code, abort_flag) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ready, 0) != 0;
+}
+
+// tiles[i] = (request, first row of the step, rows <= 128, first position)
+template <int HD>
+__global__ void __launch_bounds__(FA_THREADS, 2)
+prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                              const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table, int max_blocks,
+                              const int4* __restrict__ tiles, bf16* __restrict__ out, int out_stride, int n_heads,
+                              int n_kv_heads, int page_shift, float scale_log2, int window, int* __restrict__ status) {
+  constexpr int BN = FA<HD>::BN, DB = FA<HD>::DB;
+  constexpr uint32_t Q_BYTES = FA<HD>::Q_BYTES, KV_BYTES = FA<HD>::KV_BYTES, P_BYTES = FA<HD>::P_BYTES;
+  constexpr uint32_t Q_BLOCK = FA_BM * 128;       // bytes of one 64-wide block of Q (128 rows of 128 bytes)
+  constexpr uint32_t KV_BLOCK = BN * 128;         // likewise for a K or V tile
+  extern __shared__ __align__(1024) unsigned char fa_raw[];
+  unsigned char* q_s = fa_raw;
+  unsigned char* k_s = q_s + Q_BYTES;             // [2][KV_BYTES]
+  unsigned char* v_s = k_s + 2 * KV_BYTES;        // [2][KV_BYTES]
+  unsigned char* p_s = v_s + 2 * KV_BYTES;        // [BN / 64][128 rows][128 bytes]; the output staging at the end
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + P_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;                    // [2]
+  uint64_t* v_full = bars + 3;                    // [2]
+  uint64_t* k_empty = bars + 5;                   // [2] S of the tile has been computed
+  uint64_t* v_empty = bars + 7;                   // [2] P V of the tile has been computed
+  uint64_t* s_full = bars + 9;                    // S is in tensor memory
+  uint64_t* s_empty = bars + 10;                  // the softmax threads hold S in registers
+  uint64_t* p_full = bars + 11;                   // P is in shared memory and O has been rescaled
+  uint64_t* pv_done = bars + 12;                  // O includes the tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  if (smem_u32(fa_raw) & 1023u) {                 // the swizzled tiles need 1024-byte alignment
+    if (threadIdx.x == 0) atomicExch(status, FA_ERR_ALIGN);
+    return;
+  }
+
+  const int4 tile = tiles[blockIdx.y];      // heads of one tile are neighbours in launch order: the tiles with most keys start first
+  const int req = tile.x, row0 = tile.y, nrows = tile.z, pos0 = tile.w;
+  const int head = blockIdx.x;
+  const int kvh = head / (n_heads / n_kv_heads);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pos_last = pos0 + nrows - 1;
+  const int lo_tile = window > 0 ? max(0, pos0 - window + 1) : 0;      // the first key any row of the tile reads
+  const int j_begin = lo_tile / BN, n_kt = pos_last / BN - j_begin + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(s_empty, 128);
+    mbar_init(p_full, 128);
+    mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(FA_TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_before_sync();
+  __syncthreads();
+  tcgen05_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    // TMA producer: the whole warp runs the loop, one elected lane issues the copies
+    const int* table = block_table + static_cast<size_t>(req) * max_blocks;
+    const int page_mask = (1 << page_shift) - 1;
+    if (elect_one()) {
+      mbar_expect_tx(q_full, Q_BYTES);
+#pragma unroll
+      for (int db = 0; db < DB; ++db) tma_load_2d(q_s + db * Q_BLOCK, &map_q, head * HD + db * 64, row0, q_full);
+    }
+    // a piece of 16 keys wholly outside [lo_tile, pos_last] is masked anyway: it is read from the nearest
+    // piece inside, so that every copy reads pages this request holds (finite values)
+    const int first_piece = lo_tile & ~(FA_BOX_KEYS - 1), last_piece = pos_last & ~(FA_BOX_KEYS - 1);
+    for (int i = 0; i < n_kt; ++i) {
+      const int s = i & 1;
+      // lane b looks up the page of piece b
+      int my_slot = 0;
+      if (lane < BN / FA_BOX_KEYS) {
+        const int key = min(max((j_begin + i) * BN + lane * FA_BOX_KEYS, first_piece), last_piece);
+        my_slot = (table[key >> page_shift] << page_shift) + (key & page_mask);
+      }
+      if (i >= 2 && !warp_wait(&k_empty[s], ((i >> 1) & 1) ^ 1, lane, status, FA_ERR_PRODUCER, abort_flag)) break;
+      if (elect_one()) mbar_expect_tx(&k_full[s], KV_BYTES);
+#pragma unroll
+      for (int b = 0; b < BN / FA_BOX_KEYS; ++b) {
+        const int slot = __shfl_sync(0xffffffffu, my_slot, b);
+        if (elect_one()) {
+#pragma unroll
+          for (int db = 0; db < DB; ++db)
+            tma_load_3d(k_s + s * KV_BYTES + db * KV_BLOCK + b * (FA_BOX_KEYS * 128), &map_k, db * 64, kvh, slot, &k_full[s]);
+        }
+      }
+      if (i >= 2 && !warp_wait(&v_empty[s], ((i >> 1) & 1) ^ 1, lane, status, FA_ERR_PRODUCER, abort_flag)) break;
+      if (elect_one()) mbar_expect_tx(&v_full[s], KV_BYTES);
+#pragma unroll
+      for (int b = 0; b < BN / FA_BOX_KEYS; ++b) {
+        const int slot = __shfl_sync(0xffffffffu, my_slot, b);
+        if (elect_one()) {
+#pragma unroll
+          for (int db = 0; db < DB; ++db)
+            tma_load_3d(v_s + s * KV_BYTES + db * KV_BLOCK + b * (FA_BOX_KEYS * 128), &map_v, db * 64, kvh, slot, &v_full[s]);
+        }
+      }
+    }
+    if (*abort_flag) {
+      // Another role gave up: before the block ends, give the copies in flight time to land (bounded).
+      for (int spin = 0; spin < (1 << 16); ++spin) __nanosleep(64);
+    }
+  } else if (warp == 5) {
+    // MMA issue: the whole warp runs the loop, one elected lane issues the instructions
+    constexpr uint32_t idesc_s = umma_idesc(FA_BM, BN);
+    constexpr uint32_t idesc_o = umma_idesc_b_mn(FA_BM, HD);
+    // descriptors of the first pieces; a step along the tile adds (bytes >> 4) to the address field
+    const uint64_t q_desc = umma_desc_sw128(smem_u32(q_s)), k_desc = umma_desc_sw128(smem_u32(k_s));
+    const uint64_t p_desc = umma_desc_sw128(smem_u32(p_s)), v_desc = umma_desc_mn_sw128(smem_u32(v_s), KV_BLOCK, 1024);
+    // S of tile i: waits for K, issues HD / 16 MMAs, frees the K stage and signals the softmax warps
+    auto issue_s = [&](int i) -> bool {
+      const int s = i & 1;
+      if (!warp_wait(&k_full[s], (i >> 1) & 1, lane, status, FA_ERR_MMA, abort_flag)) return false;
+      tcgen05_after_sync();
+      if (elect_one()) {
+#pragma unroll
+        for (int db = 0; db < DB; ++db)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_bf16(tmem_base, q_desc + ((db * Q_BLOCK + k * 32) >> 4), k_desc + ((s * KV_BYTES + db * KV_BLOCK + k * 32) >> 4),
+                      idesc_s, (db > 0 || k > 0) ? 1u : 0u);
+        umma_commit(&k_empty[s]);
+        umma_commit(s_full);
+      }
+      __syncwarp();
+      return true;
+    };
+    bool ok = warp_wait(q_full, 0, lane, status, FA_ERR_MMA, abort_flag);
+    ok = ok && issue_s(0);
+    for (int i = 0; i < n_kt && ok; ++i) {
+      const int s = i & 1;
+      if (i + 1 < n_kt) {
+        // S of the next tile overwrites S of this one: the softmax threads must hold it in registers
+        if (!warp_wait(s_empty, i & 1, lane, status, FA_ERR_MMA, abort_flag) || !issue_s(i + 1)) break;
+      }
+      if (!warp_wait(&v_full[s], (i >> 1) & 1, lane, status, FA_ERR_MMA, abort_flag)) break;
+      if (!warp_wait(p_full, i & 1, lane, status, FA_ERR_MMA, abort_flag)) break;
+      tcgen05_after_sync();
+      if (elect_one()) {
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          // P: 16 keys = 32 bytes along a swizzled row, 64 keys per block of 128 rows. V: 16 keys = 16 rows of
+          // 128 bytes; groups of 8 keys 1024 bytes apart, blocks of 64 head dimensions KV_BLOCK apart.
+          umma_bf16(tmem_base + FA_O_COL, p_desc + (((kk >> 2) * (FA_BM * 128) + (kk & 3) * 32) >> 4),
+                    v_desc + ((s * KV_BYTES + kk * (16 * 128)) >> 4), idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&v_empty[s]);
+        umma_commit(pv_done);
+      }
+      __syncwarp();
+    }
+  } else {
+    // softmax: thread r owns query row r = tensor-memory lane r
+    const int r = threadIdx.x;
+    const uint32_t taddr_s = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    const uint32_t taddr_o = taddr_s + FA_O_COL;
+    const int pos_r = pos0 + r;
+    const int lo_r = window > 0 ? max(0, pos_r - window + 1) : 0;
+    float m_ref = -INFINITY;      // the reference point of this row's exponentials, in base-2 units
+    float l_run = 0.0f;
+    bool ok = true;
+    for (int i = 0; i < n_kt; ++i) {
+      if (!warp_wait(s_full, i & 1, lane, status, FA_ERR_SOFTMAX, abort_flag)) { ok = false; break; }
+      tcgen05_after_sync();
+      uint32_t sv[BN];
+#pragma unroll
+      for (int c0 = 0; c0 < BN; c0 += 32) tmem_ld32(taddr_s + c0, *reinterpret_cast<uint32_t(*)[32]>(&sv[c0]));
+      tmem_ld_wait();
+      tcgen05_before_sync();
+      mbar_arrive(s_empty);
+
+      const int key0 = (j_begin + i) * BN;
+      const bool edge = key0 + BN - 1 > pos0 + warp * 32 || (window > 0 && key0 < max(0, pos0 + warp * 32 + 31 - window + 1));
+      if (edge) {
+#pragma unroll
+        for (int c = 0; c < BN; ++c) {
+          const int key = key0 + c;
+          if (key > pos_r || key < lo_r) sv[c] = 0xff800000u;      // -inf
+        }
+      }
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < BN; c += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(sv[c]));
+        mx1 = fmaxf(mx1, __uint_as_float(sv[c + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(sv[c + 2]));
+        mx3 = fmaxf(mx3, __uint_as_float(sv[c + 3]));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;      // the scale is positive
+      float corr = 1.0f;
+      bool rescale = false;
+      if (m_ref == -INFINITY) {
+        m_ref = mx;                 // nothing accumulated so far (may stay -inf: no visible key yet)
+      } else if (mx > m_ref + 8.0f) {
+        corr = fa_exp2(m_ref - mx);
+        m_ref = mx;
+        rescale = true;
+      }
+      const float neg_m = m_ref == -INFINITY ? 0.0f : -m_ref;
+      float sum0 = 0.0f, sum1 = 0.0f;
+      // 8 probabilities -> one 16-byte piece of P
+      auto exp8 = [&](int c0, uint32_t (&w)[4]) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float p0 = fa_exp2(fmaf(__uint_as_float(sv[c0 + 2 * e]), scale_log2, neg_m));
+          const float p1 = fa_exp2(fmaf(__uint_as_float(sv[c0 + 2 * e + 1]), scale_log2, neg_m));
+          sum0 += p0;
+          sum1 += p1;
+          w[e] = pack2_bf16(p0, p1);
+        }
+      };
+      // P is K-major with the 128-byte swizzle: row r, 16-byte piece ch of a 64-key block at ch ^ (r & 7)
+      auto store8 = [&](int c0, const uint32_t (&w)[4]) {
+        unsigned char* row = p_s + (c0 >> 6) * (FA_BM * 128) + r * 128;
+        *reinterpret_cast<uint4*>(row + ((((c0 >> 3) & 7) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      };
+      // the first 64 keys go to registers while P V of the previous tile may still be reading the P buffer
+      uint32_t first[8][4];
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) exp8(ch * 8, first[ch]);
+      if (i > 0) {
+        // P V of the previous tile: O is complete up to it and the P buffer is free
+        if (!warp_wait(pv_done, (i - 1) & 1, lane, status, FA_ERR_SOFTMAX, abort_flag)) { ok = false; break; }
+        tcgen05_after_sync();
+        if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+          for (int c0 = 0; c0 < HD; c0 += 32) {
+            uint32_t o[32];
+            tmem_ld32(taddr_o + c0, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * corr);
+            tmem_st32(taddr_o + c0, o);
+          }
+          tmem_st_wait();
+        }
+      }
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) store8(ch * 8, first[ch]);
+#pragma unroll
+      for (int c0 = 64; c0 < BN; c0 += 8) {
+        uint32_t w[4];
+        exp8(c0, w);
+        store8(c0, w);
+      }
+      l_run = l_run * corr + (sum0 + sum1);
+      fence_proxy_async_smem();
+      tcgen05_before_sync();
+      mbar_arrive(p_full);
+    }
+    if (ok && warp_wait(pv_done, (n_kt - 1) & 1, lane, status, FA_ERR_SOFTMAX, abort_flag)) {
+      tcgen05_after_sync();
+      const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+      unsigned char* my_stage = p_s + warp * 4096;
+#pragma unroll
+      for (int c0 = 0; c0 < HD; c0 += 64) {
+        uint32_t va[32], vb[32];
+        tmem_ld32(taddr_o + c0, va);
+        tmem_ld32(taddr_o + c0 + 32, vb);
+        tmem_ld_wait();
+        uint4 w[8];
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const uint32_t* v = hh == 0 ? va : vb;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8)
+            w[hh * 4 + j / 8] = make_uint4(pack2_bf16(__uint_as_float(v[j]) * inv, __uint_as_float(v[j + 1]) * inv),
+                                           pack2_bf16(__uint_as_float(v[j + 2]) * inv, __uint_as_float(v[j + 3]) * inv),
+                                           pack2_bf16(__uint_as_float(v[j + 4]) * inv, __uint_as_float(v[j + 5]) * inv),
+                                           pack2_bf16(__uint_as_float(v[j + 6]) * inv, __uint_as_float(v[j + 7]) * inv));
+        }
+        store_rows_bf16(w, my_stage, lane, out, out_stride, row0 + warp * 32, row0 + nrows, head * HD + c0, INT_MAX);
+      }
+    }
+  }
+  // common exit: every role arrives here, with or without a timeout
+  tcgen05_before_sync();
+  __syncthreads();
+  if (warp == 5) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(FA_TMEM_COLS) : "memory");
+  }
+}
+
+// ---- host side -------------------------------------------------------------------------------------
+
+// q: [n_rows, cols] bf16 with a row pitch of `ld` elements; box = 128 rows x 64 columns.
+static int make_q_map(CUtensorMap* map, const void* base, int n_rows, int cols, int ld) {
+  EncodeTiledFn fn = tensor_map_encoder();
+  if (fn == nullptr) return DL_ERR_UNSUPPORTED;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(n_rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  const cuuint32_t box[2] = {64, FA_BM};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 700000 + static_cast<int>(r);
+}
+
+// cache: [n_slots, n_kv_heads, head_dim] bf16, contiguous; box = 16 slots x 1 head x 64 columns.
+static int make_cache_map(CUtensorMap* map, const void* base, long long n_slots, int n_kv_heads, int head_dim) {
+  EncodeTiledFn fn = tensor_map_encoder();
+  if (fn == nullptr) return DL_ERR_UNSUPPORTED;
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(n_kv_heads), static_cast<cuuint64_t>(n_slots)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(head_dim) * 2, static_cast<cuuint64_t>(n_kv_heads) * head_dim * 2};
+  const cuuint32_t box[3] = {64, 1, FA_BOX_KEYS};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 700000 + static_cast<int>(r);
+}
+
+template <int HD>
+int launch_prefill_tc05(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const int* block_table,
+                        int max_blocks, const int* tiles, int n_tiles, void* out, int out_stride, int n_heads, int n_kv_heads,
+                        int page_shift, float scale, int window, int* status, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(FA<HD>::SMEM));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  dim3 grid(n_heads, n_tiles);
+  prefill_attention_tc05_kernel<HD><<<grid, FA_THREADS, FA<HD>::SMEM, stream>>>(
+      mq, mk, mv, block_table, max_blocks, reinterpret_cast<const int4*>(tiles), static_cast<bf16*>(out), out_stride, n_heads,
+      n_kv_heads, page_shift, scale * 1.4426950408889634f, window, status);
+  return launch_status();
+}
+
+}  // namespace dl
+
+// bfloat16, head_dim 64 or 128, pages of 16 keys or a larger power of two. q: [n_rows, q_stride] with head h at
+// column h * head_dim; caches: [n_pages, page_size, n_kv_heads, head_dim] contiguous and free of NaN/Inf bit
+// patterns (a fresh cache is zero-filled); tiles: int32 [n_tiles, 4] = (request, first row, rows <= 128, first
+// position), 16-byte aligned. status: one device int, set to a nonzero code if a wait inside the kernel timed
+// out (left untouched otherwise). Other shapes return "unsupported": the caller has the mma.sync kernel.
+DL_EXPORT int dl_paged_attention_prefill_tcgen05(const void* q, int q_stride, int n_rows, const void* k_cache,
+                                                 const void* v_cache, long long n_pages, const int* block_table,
+                                                 int max_blocks, const int* tiles, int n_tiles, void* out, int out_stride,
+                                                 int n_heads, int n_kv_heads, int head_dim, int page_size, float scale,
+                                                 int window, int* status, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  int page_shift = 0;
+  while ((1 << page_shift) < page_size) ++page_shift;
+  if ((1 << page_shift) != page_size || page_size < dl::FA_BOX_KEYS || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 ||
+      n_tiles > 65535 || (head_dim != 64 && head_dim != 128) || (q_stride & 7) || (out_stride & 7) || !(scale > 0.0f) ||
+      (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) ||
+      (reinterpret_cast<uintptr_t>(k_cache) & 15) || (reinterpret_cast<uintptr_t>(v_cache) & 15) ||
+      (reinterpret_cast<uintptr_t>(tiles) & 15) || status == nullptr || n_rows <= 0 || n_pages <= 0 ||
+      n_pages * page_size > 0x7fffffffll)
+    return DL_ERR_UNSUPPORTED;
+  CUtensorMap mq, mk, mv;
+  int rc = dl::make_q_map(&mq, q, n_rows, n_heads * head_dim, q_stride);
+  if (rc != 0) return rc;
+  rc = dl::make_cache_map(&mk, k_cache, n_pages * page_size, n_kv_heads, head_dim);
+  if (rc != 0) return rc;
+  rc = dl::make_cache_map(&mv, v_cache, n_pages * page_size, n_kv_heads, head_dim);
+  if (rc != 0) return rc;
+  if (head_dim == 64)
+    return dl::launch_prefill_tc05<64>(mq, mk, mv, block_table, max_blocks, tiles, n_tiles, out, out_stride, n_heads,
+                                       n_kv_heads, page_shift, scale, window, status, stream);
+  return dl::launch_prefill_tc05<128>(mq, mk, mv, block_table, max_blocks, tiles, n_tiles, out, out_stride, n_heads,
+                                      n_kv_heads, page_shift, scale, window, status, stream);
+}

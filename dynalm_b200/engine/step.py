@@ -157,8 +157,7 @@ class BatchBuilder:
         pos_start = h[off["pos_start"]]
         kv_len = h[off["kv_len"]]
         slots = h[off["state_slots"]]
-        tiles = h[off["q_tiles"]]
-        n_tiles = 0
+        tiles = []
         r0 = 0
         n_logit = 0
         h_q_len, h_pos_start, h_slots = [], [], []
@@ -180,14 +179,17 @@ class BatchBuilder:
             h_pos_start.append(start)
             h_slots.append(slot)
             for t0 in range(0, n, Q_TILE):
-                tiles[4 * n_tiles: 4 * n_tiles + 4] = (r, r0 + t0, min(Q_TILE, n - t0), start + t0)
-                n_tiles += 1
+                tiles.append((r, r0 + t0, min(Q_TILE, n - t0), start + t0))
             for g in self.cache.groups:
                 mb = g.max_blocks
                 sec = off[f"table{g.gid}"]
                 h[sec.start + r * mb: sec.start + (r + 1) * mb] = self.cache.table_row(g, e.request)
             r0 += n
         q_start[len(entries)] = r0
+        # the tiles that read the most keys first: the attention grid then ends evenly
+        tiles.sort(key=lambda t: -(t[3] + t[2]))
+        n_tiles = len(tiles)
+        h[off["q_tiles"]][:4 * n_tiles] = np.asarray(tiles, dtype=np.int32).reshape(-1)
         if feedback_src is not None:
             if total != len(entries) or len(feedback_src) != len(entries):
                 raise InvalidArgument("token feedback needs one token per entry and one source per entry")

@@ -3,11 +3,14 @@
 float32 always runs the plain kernel (csrc/attention_generic.cu), whose arithmetic for a row is
 fixed by the row alone. bfloat16 steps in which every request brings one token run the split-KV
 kernel (csrc/attention_decode.cu); other bfloat16 steps (prompt portions, alone or beside decode
-rows) run the tensor-core flash kernel (csrc/attention_prefill.cu). Every shape the faster kernels
-refuse falls to the plain kernel.
+rows) run a flash kernel: the tcgen05 one (csrc/attention_prefill_tcgen05.cu) for head sizes 64 and
+128 with pages of at least 16 keys, else the mma.sync one (csrc/attention_prefill.cu). Every shape
+the faster kernels refuse falls to the plain kernel.
 """
 
 from __future__ import annotations
+
+import os
 
 import torch
 
@@ -16,7 +19,7 @@ from . import ops
 SM_COUNT = 148            # B200
 MAX_SPLITS = 32
 CLUSTER_SPLITS = 8          # up to here the tensor-core kernel merges splits inside a thread-block cluster
-DECODE_FILL = int(__import__('os').environ.get('DYNALM_DECODE_FILL', '1'))   # blocks per SM the split count aims for
+DECODE_FILL = int(os.environ.get('DYNALM_DECODE_FILL', '1'))   # blocks per SM the split count aims for
 
 
 def decode_splits(rows: int, n_heads: int, n_kv_heads: int, max_kv_len: int, tensor_cores: bool = True) -> int:
@@ -52,15 +55,24 @@ def use_prefill_kernel(ctx, spec, qkv: torch.Tensor, page_size: int) -> bool:
             and spec.head_dim % 16 == 0 and spec.head_dim <= 128 and qkv.stride(0) % 8 == 0)
 
 
+PREFILL_TCGEN05 = os.environ.get("DYNALM_PREFILL_TCGEN05", "1") != "0"     # 0: the mma.sync kernel for every head size
+
+
+def use_prefill_tcgen05(spec, qkv: torch.Tensor, out: torch.Tensor, page_size: int) -> bool:
+    return (PREFILL_TCGEN05 and spec.head_dim in ops.PREFILL_TCGEN05_HEAD_DIMS and page_size >= 16
+            and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0 and qkv.data_ptr() % 16 == 0)
+
+
 def paged_attention(qkv: torch.Tensor, cache, ctx, out: torch.Tensor, spec, runtime) -> bool:
     """Run the fast kernel for this step if one applies; False means the caller runs the plain one."""
     k_cache, v_cache = cache.arrays
     if not use_decode_kernel(ctx, spec, qkv.dtype, cache.page_size):
         if not use_prefill_kernel(ctx, spec, qkv, cache.page_size):
             return False
-        ops.paged_attention_prefill(qkv, k_cache, v_cache, cache.block_table, ctx.q_tiles, ctx.num_q_tiles, out,
-                                    spec.num_heads, spec.num_kv_heads, spec.head_dim, cache.page_size,
-                                    float(spec.scale), spec.window)
+        kernel = (ops.paged_attention_prefill_tcgen05 if use_prefill_tcgen05(spec, qkv, out, cache.page_size)
+                  else ops.paged_attention_prefill)
+        kernel(qkv, k_cache, v_cache, cache.block_table, ctx.q_tiles, ctx.num_q_tiles, out, spec.num_heads,
+               spec.num_kv_heads, spec.head_dim, cache.page_size, float(spec.scale), spec.window)
         return True
     rows = qkv.shape[0]
     n_split = decode_plan(ctx, spec)

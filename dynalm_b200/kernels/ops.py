@@ -35,6 +35,8 @@ _SIGNATURES = {
         "dl_paged_attention_decode_tc": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P]},
     "attention_prefill": {
         "dl_paged_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P]},
+    "attention_prefill_tcgen05": {
+        "dl_paged_attention_prefill_tcgen05": [_P, _I, _I, _P, _P, _L, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P]},
     "gemm_skinny": {"dl_gemm_skinny": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _L, _P]},
     "gemm_tcgen05": {"dl_gemm_tcgen05": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P]},
     "gemm_simt": {"dl_gemm_simt": [_I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _P]},
@@ -267,6 +269,57 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
         page_size, scale, window, n_split, _stream()), "paged_attention_decode")
 
 
+_tcgen05_status = {}
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    """One int32 per device that the tcgen05 kernels write a code into when a wait inside them times out."""
+    status = _tcgen05_status.get(device)
+    if status is None:
+        status = torch.zeros(1, dtype=torch.int32, device=device)
+        _tcgen05_status[device] = status
+    return status
+
+
+def gemm_tcgen05_status(device=None) -> int:
+    """The timeout code the tcgen05 kernels (matrix product, prompt attention) left on `device` (0: none).
+    Reading it synchronises."""
+    if device is None:
+        return max((int(t.item()) for t in _tcgen05_status.values()), default=0)
+    t = _tcgen05_status.get(torch.device(device))
+    return 0 if t is None else int(t.item())
+
+
+PREFILL_TCGEN05_HEAD_DIMS = (64, 128)
+
+
+def paged_attention_prefill_tcgen05(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                                    q_tiles: torch.Tensor, n_tiles: int, out: torch.Tensor, n_heads: int, n_kv_heads: int,
+                                    head_dim: int, page_size: int, scale: float, window: int = 0) -> None:
+    """Flash attention of query tiles over the paged cache on tcgen05 tensor cores, bfloat16, head_dim 64 or
+    128, pages of at least 16 keys; see csrc/attention_prefill_tcgen05.cu. Arguments as paged_attention_prefill."""
+    _cuda(q, k_cache, v_cache, block_table, q_tiles, out)
+    _rows_contiguous(q, "q")
+    _rows_contiguous(out, "out")
+    if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or v_cache.dtype != torch.bfloat16:
+        raise Unsupported("prefill attention (tcgen05): bfloat16 only")
+    if head_dim not in PREFILL_TCGEN05_HEAD_DIMS or page_size < 16 or page_size & (page_size - 1) or n_heads % n_kv_heads:
+        raise Unsupported(f"prefill attention (tcgen05): head_dim {head_dim} (64 or 128), page size {page_size} "
+                          f"(a power of two from 16), heads {n_heads}:{n_kv_heads}")
+    if (q.stride(0) % 8 or out.stride(0) % 8 or q.data_ptr() % 16 or out.data_ptr() % 16 or q_tiles.data_ptr() % 16
+            or k_cache.data_ptr() % 16 or v_cache.data_ptr() % 16):
+        raise Unsupported("prefill attention (tcgen05): q, out and cache rows must be 16-byte aligned")
+    if tuple(k_cache.shape[1:]) != (page_size, n_kv_heads, head_dim) or not k_cache.is_contiguous() or not v_cache.is_contiguous() \
+            or v_cache.shape != k_cache.shape:
+        raise InvalidArgument("prefill attention (tcgen05): cache shape is not [pages, page_size, kv_heads, head_dim]")
+    if q_tiles.dtype != torch.int32 or q_tiles.numel() < 4 * n_tiles:
+        raise InvalidArgument("prefill attention (tcgen05): q_tiles must be int32 [n_tiles, 4]")
+    _check(_fn("attention_prefill_tcgen05", "dl_paged_attention_prefill_tcgen05")(
+        _p(q), q.stride(0), q.shape[0], _p(k_cache), _p(v_cache), k_cache.shape[0], _p(block_table), block_table.stride(0),
+        _p(q_tiles), n_tiles, _p(out), out.stride(0), n_heads, n_kv_heads, head_dim, page_size, scale, window,
+        _p(_status_word(q.device)), _stream()), "paged_attention_prefill_tcgen05")
+
+
 def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                             q_tiles: torch.Tensor, n_tiles: int, out: torch.Tensor, n_heads: int, n_kv_heads: int,
                             head_dim: int, page_size: int, scale: float, window: int = 0) -> None:
@@ -342,17 +395,6 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str =
                                                  n_split, split_stride, _stream()), "gemm_skinny")
 
 
-_tcgen05_status = {}
-
-
-def gemm_tcgen05_status(device=None) -> int:
-    """The timeout code the tcgen05 kernels left on `device` (0: none). Reading it synchronises."""
-    if device is None:
-        return max((int(t.item()) for t in _tcgen05_status.values()), default=0)
-    t = _tcgen05_status.get(torch.device(device))
-    return 0 if t is None else int(t.item())
-
-
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str = "store", out_scale: float = 1.0) -> None:
     """x W^T on tcgen05 tensor cores with TMA-fed operands; see csrc/gemm_tcgen05.cu.
 
@@ -383,10 +425,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str 
             code = 1
         else:
             raise InvalidArgument("gemm_tcgen05: out bfloat16 or float32")
-    status = _tcgen05_status.get(x.device)
-    if status is None:
-        status = torch.zeros(1, dtype=torch.int32, device=x.device)
-        _tcgen05_status[x.device] = status
+    status = _status_word(x.device)
     _check(_fn("gemm_tcgen05", "dl_gemm_tcgen05")(_p(x), x.stride(0), _p(w), _p(out), out.stride(0), M, N, K, code,
                                                    out_scale, _p(status), _stream()), "gemm_tcgen05")
 

@@ -334,9 +334,38 @@ def test_paged_attention_decode(ops, dtype, heads, kvh, hd, page, window, splits
                                                         (3, 3, 80, 32, 0), (8, 2, 128, 16, 40), (32, 8, 64, 16, 0),
                                                         (4, 4, 64, 16, 7), (2, 1, 112, 16, 100), (4, 2, 96, 64, 0)])
 def test_paged_attention_prefill(ops, heads, kvh, hd, page, window):
-    """The tensor-core flash kernel on a mixed batch: a decode row, a 210-row portion that starts in
-    the middle of a page and of a key tile, a 5-row run, another decode row and a 64-row portion from
-    position 0; a far key stands out; queries padded inside a wider row (as q inside qkv)."""
+    """The mma.sync flash kernel; see _check_prefill_kernel."""
+    _check_prefill_kernel(ops.paged_attention_prefill, heads, kvh, hd, page, window)
+
+
+@pytest.mark.parametrize("heads,kvh,hd,page,window", [(32, 8, 64, 16, 0), (4, 4, 64, 16, 7), (8, 2, 128, 16, 40),
+                                                        (6, 2, 128, 32, 0), (3, 1, 64, 64, 300), (2, 2, 128, 16, 129)])
+def test_paged_attention_prefill_tcgen05(ops, heads, kvh, hd, page, window):
+    """The tcgen05 flash kernel (head sizes 64 and 128) on the same mixed batch, twice in a row (tensor memory
+    is freed and taken again), with no timeout recorded."""
+    for _ in range(2):
+        _check_prefill_kernel(ops.paged_attention_prefill_tcgen05, heads, kvh, hd, page, window)
+    assert ops.gemm_tcgen05_status() == 0
+
+
+def test_paged_attention_prefill_tcgen05_refuses_other_shapes(ops):
+    q = torch.zeros(4, 2 * 48, dtype=torch.bfloat16, device=DEV)
+    kc = torch.zeros(3, 16, 1, 48, dtype=torch.bfloat16, device=DEV)
+    tiles = torch.tensor([[0, 0, 4, 0]], dtype=torch.int32, device=DEV)
+    table = torch.zeros(1, 2, dtype=torch.int32, device=DEV)
+    with pytest.raises(Exception, match="head_dim 48"):
+        ops.paged_attention_prefill_tcgen05(q, kc, kc.clone(), table, tiles, 1, torch.zeros_like(q), 2, 1, 48, 16, 0.1, 0)
+    q = torch.zeros(4, 2 * 64, dtype=torch.bfloat16, device=DEV)
+    kc = torch.zeros(6, 8, 1, 64, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(Exception, match="page size 8"):
+        ops.paged_attention_prefill_tcgen05(q, kc, kc.clone(), table, tiles, 1, torch.zeros_like(q), 2, 1, 64, 8, 0.1, 0)
+
+
+def _check_prefill_kernel(run, heads, kvh, hd, page, window):
+    """A flash kernel on a mixed batch: a decode row, a 210-row portion that starts in the middle of a
+    page and of a key tile, a 5-row run, another decode row and a 64-row portion from position 0; an
+    early key stands out for some rows and a late one (far above the running maximum) for others;
+    queries padded inside a wider row (as q inside qkv)."""
     dtype = torch.bfloat16
     g = torch.Generator(device="cpu").manual_seed(12)
     lens = [60, 700, 130, 64]
@@ -352,6 +381,7 @@ def test_paged_attention_prefill(ops, heads, kvh, hd, page, window):
         k = torch.randn(l, kvh, hd, generator=g).to(dtype)
         v = torch.randn(l, kvh, hd, generator=g).to(dtype)
         k[3] *= 4.0
+        k[l - 12] *= 5.0
         keys.append(k)
         vals.append(v)
         for b in range(-(-l // page)):
@@ -376,14 +406,15 @@ def test_paged_attention_prefill(ops, heads, kvh, hd, page, window):
     for i, (r, p) in enumerate(rows):
         if i % 3 == 0:
             q[i, :, :] = (keys[r][3, 0].float() * 0.5).to(dtype)
+        if i % 3 == 1:
+            q[i, :, :] = (keys[r][lens[r] - 12, 0].float() * 0.2).to(dtype)
     wide = torch.zeros(n, heads * hd + 2 * kvh * hd, dtype=dtype)
     wide[:, :heads * hd] = q.reshape(n, heads * hd)
     wide = wide.to(DEV)
     scale = 1.0 / math.sqrt(hd)
     out = torch.zeros(n, heads * hd, dtype=dtype, device=DEV)
-    ops.paged_attention_prefill(wide[:, :heads * hd], kc.to(DEV), vc.to(DEV), table.to(DEV),
-                                torch.tensor(tiles, dtype=torch.int32).to(DEV), len(tiles), out, heads, kvh, hd, page,
-                                scale, window)
+    run(wide[:, :heads * hd], kc.to(DEV), vc.to(DEV), table.to(DEV),
+        torch.tensor(tiles, dtype=torch.int32).to(DEV), len(tiles), out, heads, kvh, hd, page, scale, window)
     got = out.double().cpu().reshape(n, heads, hd)
     for i, (r, p) in enumerate(rows):
         ref = _attention_ref(q[i].double(), keys[r][:p + 1].double(), vals[r][:p + 1].double(), scale, window)
@@ -397,9 +428,8 @@ def test_paged_attention_prefill(ops, heads, kvh, hd, page, window):
             tiles2.append((r, row0 + t0, min(64, m - t0), p0 + t0))
         row0 += m
     out2 = torch.zeros_like(out)
-    ops.paged_attention_prefill(wide[:, :heads * hd], kc.to(DEV), vc.to(DEV), table.to(DEV),
-                                torch.tensor(tiles2, dtype=torch.int32).to(DEV), len(tiles2), out2, heads, kvh, hd, page,
-                                scale, window)
+    run(wide[:, :heads * hd], kc.to(DEV), vc.to(DEV), table.to(DEV),
+        torch.tensor(tiles2, dtype=torch.int32).to(DEV), len(tiles2), out2, heads, kvh, hd, page, scale, window)
     assert torch.equal(out2[1:211], out[1:211])
 
 
