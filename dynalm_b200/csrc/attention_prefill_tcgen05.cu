@@ -54,13 +54,6 @@ __device__ __forceinline__ float fa_exp2(float x) {
   return y;
 }
 
-// One lane polls, the whole warp takes the same branch (the tensor-memory loads that follow are warp-wide).
-__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, int lane, int* status, int code, volatile int* abort_flag) {
-  int ready = 0;
-  if (lane == 0) ready = mbar_wait(bar, parity, status, code, abort_flag) ? 1 : 0;
-  return __shfl_sync(0xffffffffu, ready, 0) != 0;
-}
-
 // tiles[i] = (request, first row of the step, rows <= 128, first position)
 template <int HD>
 __global__ void __launch_bounds__(FA_THREADS, 2)
@@ -148,7 +141,7 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
         const int key = min(max((j_begin + i) * BN + lane * FA_BOX_KEYS, first_piece), last_piece);
         my_slot = (table[key >> page_shift] << page_shift) + (key & page_mask);
       }
-      if (i >= 2 && !warp_wait(&k_empty[s], ((i >> 1) & 1) ^ 1, lane, status, FA_ERR_PRODUCER, abort_flag)) break;
+      if (i >= 2 && !warp_wait(&k_empty[s], ((i >> 1) & 1) ^ 1, status, FA_ERR_PRODUCER, abort_flag)) break;
       if (elect_one()) mbar_expect_tx(&k_full[s], KV_BYTES);
 #pragma unroll
       for (int b = 0; b < BN / FA_BOX_KEYS; ++b) {
@@ -159,7 +152,7 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
             tma_load_3d(k_s + s * KV_BYTES + db * KV_BLOCK + b * (FA_BOX_KEYS * 128), &map_k, db * 64, kvh, slot, &k_full[s]);
         }
       }
-      if (i >= 2 && !warp_wait(&v_empty[s], ((i >> 1) & 1) ^ 1, lane, status, FA_ERR_PRODUCER, abort_flag)) break;
+      if (i >= 2 && !warp_wait(&v_empty[s], ((i >> 1) & 1) ^ 1, status, FA_ERR_PRODUCER, abort_flag)) break;
       if (elect_one()) mbar_expect_tx(&v_full[s], KV_BYTES);
 #pragma unroll
       for (int b = 0; b < BN / FA_BOX_KEYS; ++b) {
@@ -185,7 +178,7 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
     // S of tile i: waits for K, issues HD / 16 MMAs, frees the K stage and signals the softmax warps
     auto issue_s = [&](int i) -> bool {
       const int s = i & 1;
-      if (!warp_wait(&k_full[s], (i >> 1) & 1, lane, status, FA_ERR_MMA, abort_flag)) return false;
+      if (!warp_wait(&k_full[s], (i >> 1) & 1, status, FA_ERR_MMA, abort_flag)) return false;
       tcgen05_after_sync();
       if (elect_one()) {
 #pragma unroll
@@ -200,16 +193,16 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
       __syncwarp();
       return true;
     };
-    bool ok = warp_wait(q_full, 0, lane, status, FA_ERR_MMA, abort_flag);
+    bool ok = warp_wait(q_full, 0, status, FA_ERR_MMA, abort_flag);
     ok = ok && issue_s(0);
     for (int i = 0; i < n_kt && ok; ++i) {
       const int s = i & 1;
       if (i + 1 < n_kt) {
         // S of the next tile overwrites S of this one: the softmax threads must hold it in registers
-        if (!warp_wait(s_empty, i & 1, lane, status, FA_ERR_MMA, abort_flag) || !issue_s(i + 1)) break;
+        if (!warp_wait(s_empty, i & 1, status, FA_ERR_MMA, abort_flag) || !issue_s(i + 1)) break;
       }
-      if (!warp_wait(&v_full[s], (i >> 1) & 1, lane, status, FA_ERR_MMA, abort_flag)) break;
-      if (!warp_wait(p_full, i & 1, lane, status, FA_ERR_MMA, abort_flag)) break;
+      if (!warp_wait(&v_full[s], (i >> 1) & 1, status, FA_ERR_MMA, abort_flag)) break;
+      if (!warp_wait(p_full, i & 1, status, FA_ERR_MMA, abort_flag)) break;
       tcgen05_after_sync();
       if (elect_one()) {
 #pragma unroll
@@ -235,7 +228,7 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
     float l_run = 0.0f;
     bool ok = true;
     for (int i = 0; i < n_kt; ++i) {
-      if (!warp_wait(s_full, i & 1, lane, status, FA_ERR_SOFTMAX, abort_flag)) { ok = false; break; }
+      if (!warp_wait(s_full, i & 1, status, FA_ERR_SOFTMAX, abort_flag)) { ok = false; break; }
       tcgen05_after_sync();
       uint32_t sv[BN];
 #pragma unroll
@@ -295,7 +288,7 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
       for (int ch = 0; ch < 8; ++ch) exp8(ch * 8, first[ch]);
       if (i > 0) {
         // P V of the previous tile: O is complete up to it and the P buffer is free
-        if (!warp_wait(pv_done, (i - 1) & 1, lane, status, FA_ERR_SOFTMAX, abort_flag)) { ok = false; break; }
+        if (!warp_wait(pv_done, (i - 1) & 1, status, FA_ERR_SOFTMAX, abort_flag)) { ok = false; break; }
         tcgen05_after_sync();
         if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll
@@ -323,7 +316,7 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
       tcgen05_before_sync();
       mbar_arrive(p_full);
     }
-    if (ok && warp_wait(pv_done, (n_kt - 1) & 1, lane, status, FA_ERR_SOFTMAX, abort_flag)) {
+    if (ok && warp_wait(pv_done, (n_kt - 1) & 1, status, FA_ERR_SOFTMAX, abort_flag)) {
       tcgen05_after_sync();
       const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
       unsigned char* my_stage = p_s + warp * 4096;

@@ -96,17 +96,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    if (lane == 0) {
-      uint32_t it = 0;                               // k-slices issued so far, over all tiles
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile / tiles_n) * T5_BM, n0 = (tile % tiles_n) * n_per_tile;
-        for (int kt = 0; kt < k_tiles; ++kt, ++it) {
-          const int s = it % T5_STAGES;
-          if (it >= T5_STAGES && !mbar_wait(&empty_bar[s], ((it / T5_STAGES) & 1) ^ 1, status, T5_ERR_PRODUCER, abort_flag)) {
-            ok = false;
-            break;
-          }
+    // TMA producer: the whole warp runs the loop (every lane polls the barrier), one elected lane issues the copies
+    uint32_t it = 0;                               // k-slices issued so far, over all tiles
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m0 = (tile / tiles_n) * T5_BM, n0 = (tile % tiles_n) * n_per_tile;
+      for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+        const int s = it % T5_STAGES;
+        if (it >= T5_STAGES && !warp_wait(&empty_bar[s], ((it / T5_STAGES) & 1) ^ 1, status, T5_ERR_PRODUCER, abort_flag)) {
+          ok = false;
+          break;
+        }
+        if (elect_one()) {
           unsigned char* a_dst = tiles + static_cast<size_t>(s) * T5_STAGE_BYTES;
           unsigned char* b_dst = a_dst + T5_A_BYTES;
           mbar_expect_tx(&full_bar[s], T5_STAGE_BYTES);
@@ -114,38 +115,42 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           tma_load_2d(b_dst, &map_w, kt * T5_BK, n0, &full_bar[s]);
           tma_load_2d(b_dst + T5_B_BYTES / 2, &map_w, kt * T5_BK, swiglu ? gate_rows + n0 : n0 + T5_BN / 2, &full_bar[s]);
         }
+        __syncwarp();
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc(T5_BM, T5_BN);
-      uint32_t it = 0, local = 0;                    // k-slices consumed; tiles done by this block
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
-        const uint32_t buf = local & 1;
-        // the epilogue must have drained this buffer (its previous use was tile local - 2)
-        if (local >= 2 && !mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, status, T5_ERR_MMA, abort_flag)) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t acc = tmem_base + buf * T5_BN;
-        for (int kt = 0; kt < k_tiles; ++kt, ++it) {
-          const int s = it % T5_STAGES;
-          if (!mbar_wait(&full_bar[s], (it / T5_STAGES) & 1, status, T5_ERR_MMA, abort_flag)) {
-            ok = false;
-            break;
-          }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a_addr = smem_u32(tiles + static_cast<size_t>(s) * T5_STAGE_BYTES);
-          const uint32_t b_addr = a_addr + T5_A_BYTES;
+    // MMA issue: the whole warp runs the loop, one elected lane issues the instructions
+    constexpr uint32_t idesc = umma_idesc(T5_BM, T5_BN);
+    const uint64_t desc0 = umma_desc_sw128(smem_u32(tiles));      // a step along the tiles adds (bytes >> 4)
+    uint32_t it = 0, local = 0;                    // k-slices consumed; tiles done by this block
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      const uint32_t buf = local & 1;
+      // the epilogue must have drained this buffer (its previous use was tile local - 2)
+      if (local >= 2 && !warp_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, status, T5_ERR_MMA, abort_flag)) break;
+      tcgen05_after_sync();
+      const uint32_t acc = tmem_base + buf * T5_BN;
+      for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+        const int s = it % T5_STAGES;
+        if (!warp_wait(&full_bar[s], (it / T5_STAGES) & 1, status, T5_ERR_MMA, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tcgen05_after_sync();
+        if (elect_one()) {
+          const uint64_t a_desc = desc0 + ((static_cast<uint32_t>(s) * T5_STAGE_BYTES) >> 4);
+          const uint64_t b_desc = a_desc + (T5_A_BYTES >> 4);
 #pragma unroll
           for (int k = 0; k < T5_BK / 16; ++k) {
             // 16 elements of K = 32 bytes further along the swizzled row
-            umma_bf16(acc, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32), idesc,
-                      (kt > 0 || k > 0) ? 1u : 0u);
+            umma_bf16(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (kt > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[s]);                // arrives when these MMAs have finished reading the stage
         }
-        umma_commit(&acc_full[buf]);                 // arrives when every MMA issued so far has completed
+        __syncwarp();
       }
+      if (ok && elect_one()) umma_commit(&acc_full[buf]);    // arrives when every MMA issued so far has completed
+      __syncwarp();
     }
   } else {
     // epilogue: warp w may touch TMEM lanes 32 * (w % 4) .. + 31
@@ -155,12 +160,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       const uint32_t buf = local & 1;
       const int m0 = (tile / tiles_n) * T5_BM, n0 = (tile % tiles_n) * n_per_tile;
       const int row = m0 + quarter * 32 + lane;
-      // one lane polls; the whole warp then takes the same branch (tcgen05.ld is warp-wide)
-      int ready = 0;
-      if (lane == 0) ready = mbar_wait(&acc_full[buf], (local >> 1) & 1, status, T5_ERR_EPILOGUE, abort_flag) ? 1 : 0;
-      ready = __shfl_sync(0xffffffffu, ready, 0);
-      if (!ready) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (!warp_wait(&acc_full[buf], (local >> 1) & 1, status, T5_ERR_EPILOGUE, abort_flag)) break;
+      tcgen05_after_sync();
       const uint32_t lane_addr = tmem_base + buf * T5_BN + (static_cast<uint32_t>(quarter * 32) << 16);
       unsigned char* my_stage = store_stage + (warp - 2) * (T5_STORE_BYTES / 4);
       const int row0 = m0 + quarter * 32;
