@@ -223,8 +223,8 @@ decode_attention_kernel(const T* __restrict__ q, int q_stride, const T* __restri
 template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ part, T* __restrict__ out, int out_stride,
                                          int n_heads, int head_dim, int n_split) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int head = blockIdx.x, row = blockIdx.y;
   const int rec = head_dim + 2;
   const float* base = part + (static_cast<size_t>(row) * n_heads + head) * n_split * rec;
@@ -346,8 +346,8 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
   bf16* KV = Qs + 16 * LD;                               // [warp][stage][K | V][DT_KT][LD]
   float* merge = reinterpret_cast<float*>(dt_smem);      // reused after the loop: [warp][16][HD + 2]
 
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int split = blockIdx.x, row = blockIdx.z;
   const int group = n_heads / n_kv_heads;
   const int chunks = (group + 15) / 16;

@@ -8,8 +8,8 @@ namespace dl {
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
                              int width, int vocab, float scale) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int row = blockIdx.x;
   int id = ids[row];
   // The step function has already refused ids outside [0, vocab); clamping keeps a stray id

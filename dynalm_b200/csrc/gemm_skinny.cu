@@ -36,14 +36,104 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
 
 enum { SK_OUT_BF16 = 0, SK_OUT_F32 = 1, SK_OUT_SWIGLU = 2 };
 
+// The weight stream of one block: y^T tile = W rows (wrow, 16 * MT of them in MMA row order) times x^T, k-blocks
+// [blk_begin, blk_end) dealt to the warps round-robin. Leaves every warp's partial tile in `red`
+// ([SK_WARPS][MT * 16][NT * 8] floats, shared) and synchronises the block.
+template <int MT, int NT>
+__device__ __forceinline__ void skinny_accumulate(const bf16* __restrict__ x, int ldx, const bf16* const (&wrow)[MT][2],
+                                                  const bool (&wok)[MT][2], int M, int K, int blk_begin, int blk_end,
+                                                  float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const bf16* xrow[NT];
+  bool xok[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const int b = nt * 8 + g;
+    xok[nt] = b < M;
+    xrow[nt] = x + static_cast<size_t>(xok[nt] ? b : 0) * ldx;
+  }
+  float acc[MT][NT][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) { acc[mt][nt][0] = acc[mt][nt][1] = acc[mt][nt][2] = acc[mt][nt][3] = 0.0f; }
+
+  // The weight rows of a k-block: 16-byte pieces at k0 and k0 + 32 of each of the lane's rows.
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  auto load_w = [&](int blk, uint4 (&a)[MT][2][2]) {
+    const int k0 = blk * SK_KB + 8 * t;
+    const bool ok0 = k0 + 8 <= K, ok1 = k0 + 32 + 8 <= K;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        a[mt][h][0] = (wok[mt][h] && ok0) ? ld_stream16(wrow[mt][h] + k0) : zero;
+        a[mt][h][1] = (wok[mt][h] && ok1) ? ld_stream16(wrow[mt][h] + k0 + 32) : zero;
+      }
+  };
+  // The weights do not depend on the kernel before this one: the first pieces are on their way before the wait
+  // for it, and each k-block's pieces are requested one block ahead of their use.
+  uint4 a[MT][2][2];
+  int blk = blk_begin + warp;
+  if (blk < blk_end) load_w(blk, a);
+  pdl_wait();
+  pdl_trigger();
+  for (; blk < blk_end; blk += SK_WARPS) {
+    uint4 a_next[MT][2][2];
+    if (blk + SK_WARPS < blk_end) load_w(blk + SK_WARPS, a_next);
+    const int k0 = blk * SK_KB + 8 * t;
+    const bool ok0 = k0 + 8 <= K, ok1 = k0 + 32 + 8 <= K;
+    uint4 bq[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      bq[nt][0] = (xok[nt] && ok0) ? *reinterpret_cast<const uint4*>(xrow[nt] + k0) : zero;
+      bq[nt][1] = (xok[nt] && ok1) ? *reinterpret_cast<const uint4*>(xrow[nt] + k0 + 32) : zero;
+    }
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          // 16-byte piece = words (x, y, z, w) = k pairs; one mma takes (x, y), the next (z, w)
+          mma16816(acc[mt][nt], a[mt][0][c].x, a[mt][1][c].x, a[mt][0][c].y, a[mt][1][c].y, bq[nt][c].x, bq[nt][c].y);
+          mma16816(acc[mt][nt], a[mt][0][c].z, a[mt][1][c].z, a[mt][0][c].w, a[mt][1][c].w, bq[nt][c].z, bq[nt][c].w);
+        }
+      }
+    }
+    if (blk + SK_WARPS < blk_end) {
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) { a[mt][h][0] = a_next[mt][h][0]; a[mt][h][1] = a_next[mt][h][1]; }
+    }
+  }
+
+  // warps -> shared; c0,c1: (feature g, batch 2t, 2t+1); c2,c3: (feature g + 8, same batch)
+  constexpr int FT = MT * 16, BT = NT * 8;
+  float* mine = red + static_cast<size_t>(warp) * FT * BT;
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int b = nt * 8 + 2 * t;
+      mine[(mt * 16 + g) * BT + b] = acc[mt][nt][0];
+      mine[(mt * 16 + g) * BT + b + 1] = acc[mt][nt][1];
+      mine[(mt * 16 + g + 8) * BT + b] = acc[mt][nt][2];
+      mine[(mt * 16 + g + 8) * BT + b + 1] = acc[mt][nt][3];
+    }
+  __syncthreads();
+}
+
 // MT: m16 tiles (16 features each) per block; NT: n8 tiles (8 batch rows each).
 template <int MT, int NT>
 __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w, void* __restrict__ y, int ldy,
                    int M, int N, int K, int mode, float out_scale, long long split_stride) {
   extern __shared__ float red[];     // [SK_WARPS][MT * 16][NT * 8]
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int g = lane >> 2, t = lane & 3;
+  const int lane = threadIdx.x & 31;
+  const int g = lane >> 2;
   const int f0 = blockIdx.x * (MT * 16);
   const int n_split = gridDim.y, split = blockIdx.y;
   const int half = N / 2;            // SwiGLU: gate rows [0, half), up rows [half, N)
@@ -67,73 +157,13 @@ gemm_skinny_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
       wrow[mt][h] = w + static_cast<size_t>(wok[mt][h] ? f : 0) * K;
     }
   }
-  const bf16* xrow[NT];
-  bool xok[NT];
-#pragma unroll
-  for (int nt = 0; nt < NT; ++nt) {
-    const int b = nt * 8 + g;
-    xok[nt] = b < M;
-    xrow[nt] = x + static_cast<size_t>(xok[nt] ? b : 0) * ldx;
-  }
-
-  float acc[MT][NT][4];
-#pragma unroll
-  for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) { acc[mt][nt][0] = acc[mt][nt][1] = acc[mt][nt][2] = acc[mt][nt][3] = 0.0f; }
-
-  // K range of this block, in blocks of 64; warps take blocks round-robin
+  // K range of this block, in blocks of 64
   const int nblk = (K + SK_KB - 1) / SK_KB;
   const int per = (nblk + n_split - 1) / n_split;
   const int blk_begin = split * per, blk_end = min(nblk, blk_begin + per);
-  pdl_trigger();
-  pdl_wait();
-#pragma unroll 2
-  for (int blk = blk_begin + warp; blk < blk_end; blk += SK_WARPS) {
-    const int k0 = blk * SK_KB + 8 * t;
-    const bool ok0 = k0 + 8 <= K, ok1 = k0 + 32 + 8 <= K;
-    uint4 a[MT][2][2], bq[NT][2];
-    const uint4 zero = make_uint4(0, 0, 0, 0);
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        a[mt][h][0] = (wok[mt][h] && ok0) ? ld_stream16(wrow[mt][h] + k0) : zero;
-        a[mt][h][1] = (wok[mt][h] && ok1) ? ld_stream16(wrow[mt][h] + k0 + 32) : zero;
-      }
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      bq[nt][0] = (xok[nt] && ok0) ? *reinterpret_cast<const uint4*>(xrow[nt] + k0) : zero;
-      bq[nt][1] = (xok[nt] && ok1) ? *reinterpret_cast<const uint4*>(xrow[nt] + k0 + 32) : zero;
-    }
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          // 16-byte piece = words (x, y, z, w) = k pairs; one mma takes (x, y), the next (z, w)
-          mma16816(acc[mt][nt], a[mt][0][c].x, a[mt][1][c].x, a[mt][0][c].y, a[mt][1][c].y, bq[nt][c].x, bq[nt][c].y);
-          mma16816(acc[mt][nt], a[mt][0][c].z, a[mt][1][c].z, a[mt][0][c].w, a[mt][1][c].w, bq[nt][c].z, bq[nt][c].w);
-        }
-      }
-    }
-  }
+  skinny_accumulate<MT, NT>(x, ldx, wrow, wok, M, K, blk_begin, blk_end, red);
 
-  // warps -> shared; c0,c1: (feature g, batch 2t, 2t+1); c2,c3: (feature g + 8, same batch)
   constexpr int FT = MT * 16, BT = NT * 8;
-  float* mine = red + static_cast<size_t>(warp) * FT * BT;
-#pragma unroll
-  for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      const int b = nt * 8 + 2 * t;
-      mine[(mt * 16 + g) * BT + b] = acc[mt][nt][0];
-      mine[(mt * 16 + g) * BT + b + 1] = acc[mt][nt][1];
-      mine[(mt * 16 + g + 8) * BT + b] = acc[mt][nt][2];
-      mine[(mt * 16 + g + 8) * BT + b + 1] = acc[mt][nt][3];
-    }
-  __syncthreads();
   if (mode == SK_OUT_SWIGLU) {
     // tile rows [mt*16 + i] = gate j, [mt*16 + 8 + i] = up j, j = blockIdx.x * MT*8 + mt*8 + i
     for (int idx = threadIdx.x; idx < MT * 8 * BT; idx += SK_THREADS) {
@@ -164,6 +194,87 @@ gemm_skinny_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
       static_cast<float*>(y)[static_cast<size_t>(split) * split_stride + static_cast<size_t>(b) * ldy + f] = v;
     else
       static_cast<bf16*>(y)[static_cast<size_t>(b) * ldy + f] = __float2bfloat16_rn(v);
+  }
+}
+
+// The q | k | v projection of an attention layer with the rotary encoding and the cache write in its epilogue.
+// W = [Wq; Wk; Wv]. A block of a q or k head takes 8 rotary pairs: its 16 MMA rows are features p .. p + 7 and
+// p + half .. p + half + 7 of the head (half = head_dim / 2: the whole head is rotated), so both members of a
+// pair meet in one block. A block of a v head takes 16 consecutive features. The sums are rounded to bf16
+// before the rotation, as the unfused path rounds them into its q | k | v buffer; the rotation is the one of
+// rope_cache.cu (same angle formula, sincosf, fp32), so both paths give the same bits. Rotated q goes to
+// q_out [M, ldq], rotated k and plain v into the request's cache page.
+struct QkvRope {
+  const int* positions;       // [M]
+  const int* row_request;     // [M]
+  const int* block_table;     // [requests, max_blocks]
+  int max_blocks;
+  bf16* k_cache;
+  bf16* v_cache;
+  const float* inv_freq;      // [head_dim / 2]
+  float pos_scale;
+  int n_heads, n_kv_heads, head_dim, page_size;
+};
+
+template <int NT>
+__global__ void __launch_bounds__(SK_THREADS)
+gemm_skinny_qkv_rope_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w, bf16* __restrict__ q_out,
+                            int ldq, int M, int K, QkvRope p) {
+  extern __shared__ float red[];     // [SK_WARPS][16][NT * 8]
+  const int lane = threadIdx.x & 31;
+  const int g = lane >> 2;
+  const int hd = p.head_dim, half = hd / 2, per_head = hd / 16;
+  const int rot_blocks = (p.n_heads + p.n_kv_heads) * per_head;
+  const bool rotated = static_cast<int>(blockIdx.x) < rot_blocks;
+  int head, f_lo, f_hi;              // head counts q heads, then k heads, then v heads
+  if (rotated) {
+    head = blockIdx.x / per_head;
+    f_lo = head * hd + (blockIdx.x % per_head) * 8;
+    f_hi = f_lo + half;
+  } else {
+    const int vb = blockIdx.x - rot_blocks;
+    head = p.n_heads + p.n_kv_heads + vb / per_head;
+    f_lo = head * hd + (vb % per_head) * 16;
+    f_hi = f_lo + 8;
+  }
+  const bf16* wrow[1][2] = {{w + static_cast<size_t>(f_lo + g) * K, w + static_cast<size_t>(f_hi + g) * K}};
+  const bool wok[1][2] = {{true, true}};
+  skinny_accumulate<1, NT>(x, ldx, wrow, wok, M, K, 0, (K + SK_KB - 1) / SK_KB, red);
+
+  constexpr int BT = NT * 8;
+  for (int idx = threadIdx.x; idx < 8 * BT; idx += SK_THREADS) {
+    const int b = idx / 8, i = idx % 8;
+    if (b >= M) continue;
+    float lo = 0.0f, hi = 0.0f;
+#pragma unroll
+    for (int wv = 0; wv < SK_WARPS; ++wv) {
+      lo += red[(static_cast<size_t>(wv) * 16 + i) * BT + b];
+      hi += red[(static_cast<size_t>(wv) * 16 + 8 + i) * BT + b];
+    }
+    lo = __bfloat162float(__float2bfloat16_rn(lo));
+    hi = __bfloat162float(__float2bfloat16_rn(hi));
+    const int pos = p.positions[b];
+    bf16* dst;                       // where feature f_lo + i of row b goes; f_hi + i lies (f_hi - f_lo) further
+    if (rotated) {
+      const float theta = static_cast<float>(pos) * p.pos_scale * p.inv_freq[f_lo - head * hd + i];
+      float sn, c;
+      sincosf(theta, &sn, &c);
+      const float ra = lo * c - hi * sn, rb = lo * sn + hi * c;
+      lo = ra;
+      hi = rb;
+    }
+    if (head < p.n_heads) {
+      dst = q_out + static_cast<size_t>(b) * ldq + f_lo + i;
+    } else {
+      const int req = p.row_request[b];
+      const int page = p.block_table[static_cast<size_t>(req) * p.max_blocks + pos / p.page_size];
+      const size_t slot = static_cast<size_t>(page) * p.page_size + pos % p.page_size;
+      const bool is_k = head < p.n_heads + p.n_kv_heads;
+      const int kvh = head - p.n_heads - (is_k ? 0 : p.n_kv_heads);
+      dst = (is_k ? p.k_cache : p.v_cache) + (slot * p.n_kv_heads + kvh) * hd + (f_lo - head * hd) + i;
+    }
+    dst[0] = __float2bfloat16_rn(lo);
+    dst[f_hi - f_lo] = __float2bfloat16_rn(hi);
   }
 }
 
@@ -201,4 +312,41 @@ DL_EXPORT int dl_gemm_skinny(const void* x, int ldx, const void* w, void* y, int
   if (M <= 16) return dl::launch_skinny<1, 2>(x, ldx, w, y, ldy, M, N, K, mode, out_scale, n_split, split_stride, stream);
   if (M <= 32) return dl::launch_skinny<2, 4>(x, ldx, w, y, ldy, M, N, K, mode, out_scale, n_split, split_stride, stream);
   return dl::launch_skinny<2, 8>(x, ldx, w, y, ldy, M, N, K, mode, out_scale, n_split, split_stride, stream);
+}
+
+// The fused q | k | v projection (see gemm_skinny_qkv_rope_kernel): x bf16 [M, K], M <= 16; w bf16 [(n_heads +
+// 2 n_kv_heads) * head_dim, K]; q_out bf16 [M, ldq]; caches [pages, page_size, n_kv_heads, head_dim]; the whole
+// head is rotated (rotary width = head_dim), head_dim a multiple of 16.
+DL_EXPORT int dl_gemm_skinny_qkv_rope(const void* x, int ldx, const void* w, void* q_out, int ldq, int M, int K,
+                                      const int* positions, const int* row_request, const int* block_table, int max_blocks,
+                                      void* k_cache, void* v_cache, const float* inv_freq, float pos_scale, int n_heads,
+                                      int n_kv_heads, int head_dim, int page_size, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (M > 16 || K <= 0 || (K & 7) || (ldx & 7) || head_dim <= 0 || (head_dim & 15) || n_heads <= 0 || n_kv_heads <= 0 ||
+      page_size <= 0 || inv_freq == nullptr)
+    return DL_ERR_UNSUPPORTED;
+  dl::QkvRope p;
+  p.positions = positions;
+  p.row_request = row_request;
+  p.block_table = block_table;
+  p.max_blocks = max_blocks;
+  p.k_cache = static_cast<dl::bf16*>(k_cache);
+  p.v_cache = static_cast<dl::bf16*>(v_cache);
+  p.inv_freq = inv_freq;
+  p.pos_scale = pos_scale;
+  p.n_heads = n_heads;
+  p.n_kv_heads = n_kv_heads;
+  p.head_dim = head_dim;
+  p.page_size = page_size;
+  const dim3 grid((n_heads + 2 * n_kv_heads) * (head_dim / 16));
+  if (M <= 8) {
+    const size_t smem = static_cast<size_t>(dl::SK_WARPS) * 16 * 8 * sizeof(float);
+    return dl::launch(dl::gemm_skinny_qkv_rope_kernel<1>, grid, dim3(dl::SK_THREADS), smem, stream,
+                      static_cast<const dl::bf16*>(x), ldx, static_cast<const dl::bf16*>(w), static_cast<dl::bf16*>(q_out), ldq,
+                      M, K, p);
+  }
+  const size_t smem = static_cast<size_t>(dl::SK_WARPS) * 16 * 16 * sizeof(float);
+  return dl::launch(dl::gemm_skinny_qkv_rope_kernel<2>, grid, dim3(dl::SK_THREADS), smem, stream,
+                    static_cast<const dl::bf16*>(x), ldx, static_cast<const dl::bf16*>(w), static_cast<dl::bf16*>(q_out), ldq,
+                    M, K, p);
 }

@@ -78,8 +78,8 @@ rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, float de
                    const float* __restrict__ w, float eps, TO* __restrict__ out, const int* __restrict__ rows,
                    int width, int write_residual, int parts, size_t part_stride) {
   __shared__ float red[33];
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x;
   const size_t src = rows ? static_cast<size_t>(rows[r]) : static_cast<size_t>(r);
   float* xr = x + src * width;

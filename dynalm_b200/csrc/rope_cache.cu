@@ -80,8 +80,8 @@ __global__ void rope_cache_vec_kernel(T* __restrict__ qkv, int row_stride, const
                                       int n_kv_heads, int head_dim, int page_size, int write_cache) {
   constexpr int V = PerVec<T>::n;
   extern __shared__ float cs[];  // cos[rot/2], sin[rot/2]
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int row = blockIdx.x;
   const int pos = positions[row];
   const int half = inv_freq ? rot / 2 : 0;

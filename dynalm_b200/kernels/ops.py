@@ -37,7 +37,9 @@ _SIGNATURES = {
         "dl_paged_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P]},
     "attention_prefill_tcgen05": {
         "dl_paged_attention_prefill_tcgen05": [_P, _I, _I, _P, _P, _L, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P]},
-    "gemm_skinny": {"dl_gemm_skinny": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _L, _P]},
+    "gemm_skinny": {
+        "dl_gemm_skinny": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _L, _P],
+        "dl_gemm_skinny_qkv_rope": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P, _F, _I, _I, _I, _I, _P]},
     "gemm_tcgen05": {"dl_gemm_tcgen05": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P]},
     "gemm_simt": {"dl_gemm_simt": [_I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _P]},
     "sampling": {
@@ -267,6 +269,39 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
         dtype_code(q.dtype), _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), block_table.stride(0),
         _p(positions), _p(row_request), _p(out), out.stride(0), _p(scratch), rows, n_heads, n_kv_heads, head_dim,
         page_size, scale, window, n_split, _stream()), "paged_attention_decode")
+
+
+def gemm_skinny_qkv_rope(x: torch.Tensor, w_qkv: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor,
+                         row_request: torch.Tensor, block_table: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                         inv_freq: torch.Tensor, pos_scale: float, n_heads: int, n_kv_heads: int, head_dim: int,
+                         page_size: int) -> None:
+    """The q | k | v projection of up to 16 rows with rotary encoding and cache write in its epilogue: rotated q
+    into q_out [rows, >= n_heads * head_dim], rotated k and plain v into the paged cache. The whole head is
+    rotated (inv_freq has head_dim / 2 entries). bfloat16; see csrc/gemm_skinny.cu."""
+    _cuda(x, w_qkv, q_out, positions, row_request, block_table, k_cache, v_cache, inv_freq)
+    _rows_contiguous(x, "x")
+    _rows_contiguous(q_out, "q_out")
+    M, K = x.shape
+    if any(t.dtype != torch.bfloat16 for t in (x, w_qkv, q_out, k_cache, v_cache)):
+        raise Unsupported("gemm_skinny_qkv_rope: bfloat16 only")
+    if M > SKINNY_FAST_ROWS or K % 8 or x.stride(0) % 8 or head_dim % 16:
+        raise Unsupported(f"gemm_skinny_qkv_rope: {M} rows (at most {SKINNY_FAST_ROWS}), K {K} and head_dim {head_dim}")
+    if tuple(w_qkv.shape) != ((n_heads + 2 * n_kv_heads) * head_dim, K) or not w_qkv.is_contiguous():
+        raise InvalidArgument("gemm_skinny_qkv_rope: w must be contiguous [(heads + 2 kv_heads) * head_dim, K]")
+    if inv_freq.dtype != torch.float32 or inv_freq.numel() * 2 != head_dim:
+        raise Unsupported("gemm_skinny_qkv_rope: the rotary width must be the whole head (inv_freq float32 [head_dim / 2])")
+    if q_out.shape[0] < M or q_out.shape[1] < n_heads * head_dim:
+        raise InvalidArgument("gemm_skinny_qkv_rope: q_out is smaller than [rows, heads * head_dim]")
+    if tuple(k_cache.shape[1:]) != (page_size, n_kv_heads, head_dim) or k_cache.shape != v_cache.shape \
+            or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+        raise InvalidArgument("gemm_skinny_qkv_rope: cache shape is not [pages, page_size, kv_heads, head_dim]")
+    if block_table.dtype != torch.int32 or block_table.stride(-1) != 1 or positions.dtype != torch.int32 \
+            or row_request.dtype != torch.int32:
+        raise InvalidArgument("gemm_skinny_qkv_rope: positions, row_request and block_table must be int32")
+    _check(_fn("gemm_skinny", "dl_gemm_skinny_qkv_rope")(
+        _p(x), x.stride(0), _p(w_qkv), _p(q_out), q_out.stride(0), M, K, _p(positions), _p(row_request), _p(block_table),
+        block_table.stride(0), _p(k_cache), _p(v_cache), _p(inv_freq), pos_scale, n_heads, n_kv_heads, head_dim, page_size,
+        _stream()), "gemm_skinny_qkv_rope")
 
 
 _tcgen05_status = {}

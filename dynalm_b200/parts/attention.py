@@ -67,6 +67,13 @@ class PagedAttention:
         s, rt = self.spec, self.rt
         rows = x.shape[0]
         k_cache, v_cache = cache.arrays
+        table = self.position.table() if self.position is not None else None
+        if owns_cache and self._fused_projection_applies(x, table):
+            # few rows: one weight-streaming kernel projects, rotates and writes the cache
+            qkv = rt.buffer("attn_qkv", (rows, self.q_width + 2 * self.kv_width))
+            ops.gemm_skinny_qkv_rope(x, self.w_qkv, qkv, ctx.positions, ctx.row_request, cache.block_table, k_cache, v_cache,
+                                     table[0], table[2], s.num_heads, s.num_kv_heads, s.head_dim, cache.page_size)
+            return self._attend_and_project(qkv, cache, ctx, rows)
         if owns_cache:
             qkv = rt.buffer("attn_qkv", (rows, self.q_width + 2 * self.kv_width))
             linear(x, self.w_qkv, qkv, self.b_qkv)
@@ -74,7 +81,6 @@ class PagedAttention:
             # a layer that reads another entry's cache makes queries only
             qkv = rt.buffer("attn_qkv", (rows, self.q_width + 2 * self.kv_width))[:, :self.q_width]
             linear(x, self.w_qkv[:self.q_width], qkv, self.b_qkv[:self.q_width] if self.b_qkv is not None else None)
-        table = self.position.table() if self.position is not None else None
         if self.position is not None and table is None:
             q = qkv[:, :self.q_width].unflatten(1, (s.num_heads, s.head_dim))
             k = qkv[:, self.q_width:self.q_width + self.kv_width].unflatten(1, (s.num_kv_heads, s.head_dim)) \
@@ -83,6 +89,16 @@ class PagedAttention:
         inv_freq, rot, pos_scale = table if table is not None else (None, 0, 1.0)
         ops.rope_cache_write(qkv, ctx.positions, ctx.row_request, cache.block_table, k_cache, v_cache, inv_freq, rot,
                              pos_scale, s.num_heads, s.num_kv_heads, s.head_dim, cache.page_size, write_cache=owns_cache)
+        return self._attend_and_project(qkv, cache, ctx, rows)
+
+    def _fused_projection_applies(self, x: torch.Tensor, table) -> bool:
+        """bfloat16, at most 16 rows, no bias, and the rotation covers the whole head."""
+        return (table is not None and table[0] is not None and table[1] == self.spec.head_dim and self.b_qkv is None
+                and x.dtype == torch.bfloat16 and x.shape[0] <= ops.SKINNY_FAST_ROWS and x.shape[1] % 8 == 0
+                and x.stride(0) % 8 == 0)
+
+    def _attend_and_project(self, qkv: torch.Tensor, cache, ctx, rows: int) -> torch.Tensor:
+        s, rt = self.spec, self.rt
         attn = rt.buffer("attn_out", (rows, self.q_width))
         self.attend(qkv, cache, ctx, attn)
         if self.b_o is None:
