@@ -121,27 +121,29 @@ __device__ __forceinline__ Vec16 pack<bf16>(const float* in) {
 
 inline int launch_status() { return static_cast<int>(cudaGetLastError()); }
 
-// Programmatic dependent launch. A kernel launched through `launch` may begin while the kernel before
-// it on the stream is still running; it must call pdl_wait() before it reads anything an earlier kernel
-// wrote and before it writes anything at all. pdl_trigger() lets the kernel after it begin likewise; the
-// kernels here call it after their own wait, so that at most two kernels share the SMs (with the trigger first,
-// a whole chain of waiting kernels held slots that the running kernel's later blocks needed).
-// Kernels launched the ordinary way treat both as no-ops. The early start is off unless DYNALM_PDL=1:
-// measured on B200 inside the decode graph it made the step slower (1.50 ms against 1.24 ms at batch 8).
+// Programmatic dependent launch. A kernel launched with the attribute may begin while the kernel before it on
+// the stream is still running; it must call pdl_wait() before it reads anything an earlier kernel wrote and
+// before it writes anything at all. pdl_trigger() lets the kernel after it begin likewise; the kernels here call
+// it after their own wait, so that at most two kernels share the SMs (with the trigger first, a whole chain of
+// waiting kernels held slots that the running kernel's later blocks needed). Kernels launched the ordinary way
+// treat both as no-ops.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-inline bool pdl_enabled() {
+// DYNALM_PDL: 2 or unset = only the weight-streaming kernels (`launch_streaming`), which request their first
+// weights before they wait; 1 = every kernel launched through `launch` too; 0 = none. Measured on B200, decode
+// step at batch 8 inside the CUDA graph: 0.99 ms with 0, 1.00 ms with 1, 0.95 ms with 2.
+inline int pdl_mode() {
   static int v = -1;
   if (v < 0) {
     const char* e = getenv("DYNALM_PDL");
-    v = (e != nullptr && e[0] == '1') ? 1 : 0;
+    v = (e != nullptr && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 2;
   }
-  return v == 1;
+  return v;
 }
 
 template <typename... KArgs, typename... Args>
-inline int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+inline int launch_impl(bool early, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -151,8 +153,19 @@ inline int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, 
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cfg.numAttrs = early ? 1 : 0;
   return static_cast<int>(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
+}
+
+template <typename... KArgs, typename... Args>
+inline int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  return launch_impl(pdl_mode() == 1, kernel, grid, block, smem, stream, args...);
+}
+
+// For kernels that have work to do before their wait (weights to request).
+template <typename... KArgs, typename... Args>
+inline int launch_streaming(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  return launch_impl(pdl_mode() >= 1, kernel, grid, block, smem, stream, args...);
 }
 
 }  // namespace dl

@@ -292,7 +292,7 @@ int launch_skinny(const void* x, int ldx, const void* w, void* y, int ldy, int M
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  return launch(gemm_skinny_kernel<MT, NT>, grid, dim3(SK_THREADS), smem, stream, static_cast<const bf16*>(x), ldx,
+  return launch_streaming(gemm_skinny_kernel<MT, NT>, grid, dim3(SK_THREADS), smem, stream, static_cast<const bf16*>(x), ldx,
                 static_cast<const bf16*>(w), y, ldy, M, N, K, mode, out_scale, split_stride);
 }
 
@@ -341,12 +341,12 @@ DL_EXPORT int dl_gemm_skinny_qkv_rope(const void* x, int ldx, const void* w, voi
   const dim3 grid((n_heads + 2 * n_kv_heads) * (head_dim / 16));
   if (M <= 8) {
     const size_t smem = static_cast<size_t>(dl::SK_WARPS) * 16 * 8 * sizeof(float);
-    return dl::launch(dl::gemm_skinny_qkv_rope_kernel<1>, grid, dim3(dl::SK_THREADS), smem, stream,
+    return dl::launch_streaming(dl::gemm_skinny_qkv_rope_kernel<1>, grid, dim3(dl::SK_THREADS), smem, stream,
                       static_cast<const dl::bf16*>(x), ldx, static_cast<const dl::bf16*>(w), static_cast<dl::bf16*>(q_out), ldq,
                       M, K, p);
   }
   const size_t smem = static_cast<size_t>(dl::SK_WARPS) * 16 * 16 * sizeof(float);
-  return dl::launch(dl::gemm_skinny_qkv_rope_kernel<2>, grid, dim3(dl::SK_THREADS), smem, stream,
+  return dl::launch_streaming(dl::gemm_skinny_qkv_rope_kernel<2>, grid, dim3(dl::SK_THREADS), smem, stream,
                     static_cast<const dl::bf16*>(x), ldx, static_cast<const dl::bf16*>(w), static_cast<dl::bf16*>(q_out), ldq,
                     M, K, p);
 }
