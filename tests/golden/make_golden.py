@@ -30,11 +30,11 @@ from tiny_configs import TINY  # noqa: E402
 import dynalm_b200  # noqa: E402,F401
 from dynalm_b200.weights import write_model_folder  # noqa: E402
 
-PROMPT_LEN = {"a": 33, "b": 40, "c": 24, "d": 21}
+PROMPT_LEN = {"a": 33, "b": 40, "c": 24, "d": 21, "e": 37, "f": 19}
 
 
 def prompt_for(name: str, vocab: int):
-    rng = np.random.RandomState({"a": 1, "b": 3, "c": 5, "d": 7}[name])
+    rng = np.random.RandomState({"a": 1, "b": 3, "c": 5, "d": 7, "e": 9, "f": 11}[name])
     return [int(t) for t in rng.randint(0, vocab, size=PROMPT_LEN[name])]
 
 

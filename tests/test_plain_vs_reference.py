@@ -16,7 +16,7 @@ from plain_llama import PlainLlama
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
 
-@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d", "e", "f"])
 def test_plain_matches_reference(name, tiny_folders):
     meta = json.load(open(os.path.join(GOLDEN, f"{name}.json")))
     folder = tiny_folders[name]

@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 # (absolute, relative-to-row-scale) tolerance on logits per dtype
 TOL = {"float32": (2e-5, 2e-5), "bfloat16": (2e-2, 4e-2)}
 LENGTHS = {"a": [5, 17, 33, 70, 41, 64], "b": [1, 7, 40, 64, 100, 129], "c": [3, 48, 95, 33, 160, 16],
-           "d": [2, 65, 130, 31, 16]}
+           "d": [2, 65, 130, 31, 16], "e": [4, 150, 33, 260, 71, 129], "f": [2, 140, 66, 17, 200]}
 SIZES = [16, 7, 2, 5, 3, 2, 11, 32, 2, 9]
 
 
@@ -36,7 +36,7 @@ def _built(folder, dtype, kv_tokens, max_batch):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d", "e", "f"])
 def test_replay_all_cuts(name, dtype, tiny_folders, plain_logits):
     reqs, plain = plain_logits[name]
     tol = TOL[dtype]

@@ -39,4 +39,23 @@ TINY_D = {
     "rms_norm_eps": 1e-5,
 }
 
-TINY = {"a": (TINY_A, 0), "b": (TINY_B, 2), "c": (TINY_C, 9), "d": (TINY_D, 4)}   # name -> (config, weight seed)
+# The head sizes that the tcgen05 prompt attention takes: 64 with 2:1 groups and llama3 scaling ...
+TINY_E = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "vocab_size": 320, "hidden_size": 128, "intermediate_size": 208, "num_hidden_layers": 2,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "max_position_embeddings": 512,
+    "rms_norm_eps": 1e-5, "rope_theta": 500000.0, "tie_word_embeddings": True,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 64},
+}
+
+# ... and 128 with three heads on one KV head, untied.
+TINY_F = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "vocab_size": 272, "hidden_size": 72, "intermediate_size": 136, "num_hidden_layers": 2,
+    "num_attention_heads": 3, "num_key_value_heads": 1, "head_dim": 128, "max_position_embeddings": 512,
+    "rms_norm_eps": 2e-6, "rope_theta": 10000.0, "tie_word_embeddings": False,
+}
+
+# name -> (config, weight seed)
+TINY = {"a": (TINY_A, 0), "b": (TINY_B, 2), "c": (TINY_C, 9), "d": (TINY_D, 4), "e": (TINY_E, 6), "f": (TINY_F, 8)}
