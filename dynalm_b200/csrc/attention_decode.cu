@@ -346,8 +346,6 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
   bf16* KV = Qs + 16 * LD;                               // [warp][stage][K | V][DT_KT][LD]
   float* merge = reinterpret_cast<float*>(dt_smem);      // reused after the loop: [warp][16][HD + 2]
 
-  pdl_wait();
-  pdl_trigger();
   const int split = blockIdx.x, row = blockIdx.z;
   const int group = n_heads / n_kv_heads;
   const int chunks = (group + 15) / 16;
@@ -368,23 +366,6 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
   const int n_tiles = k_end > k_begin ? (k_end - k_begin + DT_KT - 1) / DT_KT : 0;
   const int* table = block_table + static_cast<size_t>(row_request[row]) * max_blocks;
   const size_t kv_row = static_cast<size_t>(n_kv_heads) * HD;
-
-  // the group's query heads as the rows of one 16-row tile (rows past the group are zero)
-  for (int c = tid; c < 16 * CH; c += DT_THREADS) {
-    const int r = c / CH, ch = c % CH;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < ng)
-      v = *reinterpret_cast<const uint4*>(q + static_cast<size_t>(row) * q_stride + static_cast<size_t>(head0 + r) * HD + ch * 8);
-    *reinterpret_cast<uint4*>(Qs + r * LD + ch * 8) = v;
-  }
-  __syncthreads();
-  uint32_t qf[KS][4];
-#pragma unroll
-  for (int ks = 0; ks < KS; ++ks) {
-    const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
-    const int c = ks * 16 + (lane >> 4) * 8;
-    dt_ldmatrix_x4(qf[ks], Qs + r * LD + c);
-  }
 
   bf16* my = KV + static_cast<size_t>(warp) * STAGES * 2 * TILE_ELEMS;
   // When the block's key range starts on a multiple of 16 (always, unless a window moves it) and pages hold at
@@ -426,11 +407,44 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
     }
   };
   const int my_tiles = n_tiles > warp ? (n_tiles - warp + DT_WARPS - 1) / DT_WARPS : 0;
+  // Keys and values of earlier steps do not depend on the kernel before this one (the step's positions and block
+  // tables were uploaded before the step): their first tiles are requested before the wait for that kernel. Only
+  // the tile that holds the newest key, which that kernel has just written, waits.
+  unsigned deferred = 0;
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
-    if (s < my_tiles) load_tile(s, s);
+    if (s < my_tiles) {
+      if (k_begin + (s * DT_WARPS + warp + 1) * DT_KT <= pos) load_tile(s, s);
+      else deferred |= 1u << s;
+    }
     asm volatile("cp.async.commit_group;\n" ::);
   }
+  pdl_wait();
+  pdl_trigger();
+  if (deferred) {
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s)
+      if (deferred & (1u << s)) load_tile(s, s);
+    asm volatile("cp.async.commit_group;\n" ::);
+    asm volatile("cp.async.wait_group 0;\n" ::);      // the groups of the loop below count from here
+  }
+  // the group's query heads as the rows of one 16-row tile (rows past the group are zero)
+  for (int c = tid; c < 16 * CH; c += DT_THREADS) {
+    const int r = c / CH, ch = c % CH;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < ng)
+      v = *reinterpret_cast<const uint4*>(q + static_cast<size_t>(row) * q_stride + static_cast<size_t>(head0 + r) * HD + ch * 8);
+    *reinterpret_cast<uint4*>(Qs + r * LD + ch * 8) = v;
+  }
+  __syncthreads();
+  uint32_t qf[KS][4];
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+    const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
+    const int c = ks * 16 + (lane >> 4) * 8;
+    dt_ldmatrix_x4(qf[ks], Qs + r * LD + c);
+  }
+
 
   float o[HD / 8][4];
 #pragma unroll
@@ -624,13 +638,22 @@ int launch_decode_tc(const void* q, int q_stride, const void* kc, const void* vc
   cfg.blockDim = dim3(DT_THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = static_cast<unsigned>(n_split);
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
+  cudaLaunchAttribute attr[2];
+  int n_attr = 0;
+  if (cluster) {
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = static_cast<unsigned>(n_split);
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = 1;
+    ++n_attr;
+  }
+  if (pdl_mode() >= 1) {          // the kernel requests its first tiles of old keys before it waits
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = cluster ? 1 : 0;
+  cfg.numAttrs = n_attr;
   int rc = static_cast<int>(cudaLaunchKernelEx(
       &cfg, decode_attention_tc_kernel<HD, STAGES>, static_cast<const bf16*>(q), q_stride, static_cast<const bf16*>(kc),
       static_cast<const bf16*>(vc), block_table, max_blocks, positions, row_request, static_cast<bf16*>(out), out_stride,

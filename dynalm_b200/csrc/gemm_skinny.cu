@@ -72,23 +72,29 @@ __device__ __forceinline__ void skinny_accumulate(const bf16* __restrict__ x, in
         a[mt][h][1] = (wok[mt][h] && ok1) ? ld_stream16(wrow[mt][h] + k0 + 32) : zero;
       }
   };
-  // The weights do not depend on the kernel before this one: the first pieces are on their way before the wait
-  // for it, and each k-block's pieces are requested one block ahead of their use.
-  uint4 a[MT][2][2];
-  int blk = blk_begin + warp;
-  if (blk < blk_end) load_w(blk, a);
-  pdl_wait();
-  pdl_trigger();
-  for (; blk < blk_end; blk += SK_WARPS) {
-    uint4 a_next[MT][2][2];
-    if (blk + SK_WARPS < blk_end) load_w(blk + SK_WARPS, a_next);
+  auto load_x = [&](int blk, uint4 (&bq)[NT][2]) {
     const int k0 = blk * SK_KB + 8 * t;
     const bool ok0 = k0 + 8 <= K, ok1 = k0 + 32 + 8 <= K;
-    uint4 bq[NT][2];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       bq[nt][0] = (xok[nt] && ok0) ? *reinterpret_cast<const uint4*>(xrow[nt] + k0) : zero;
       bq[nt][1] = (xok[nt] && ok1) ? *reinterpret_cast<const uint4*>(xrow[nt] + k0 + 32) : zero;
+    }
+  };
+  // The weights do not depend on the kernel before this one: the first pieces are on their way before the wait
+  // for it, and each k-block's pieces (weights and x) are requested one block ahead of their use.
+  uint4 a[MT][2][2], bq[NT][2];
+  int blk = blk_begin + warp;
+  if (blk < blk_end) load_w(blk, a);
+  pdl_wait();
+  pdl_trigger();
+  if (blk < blk_end) load_x(blk, bq);
+  for (; blk < blk_end; blk += SK_WARPS) {
+    uint4 a_next[MT][2][2], bq_next[NT][2];
+    const bool more = blk + SK_WARPS < blk_end;
+    if (more) {
+      load_w(blk + SK_WARPS, a_next);
+      load_x(blk + SK_WARPS, bq_next);
     }
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
@@ -102,11 +108,13 @@ __device__ __forceinline__ void skinny_accumulate(const bf16* __restrict__ x, in
         }
       }
     }
-    if (blk + SK_WARPS < blk_end) {
+    if (more) {
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int h = 0; h < 2; ++h) { a[mt][h][0] = a_next[mt][h][0]; a[mt][h][1] = a_next[mt][h][1]; }
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) { bq[nt][0] = bq_next[nt][0]; bq[nt][1] = bq_next[nt][1]; }
     }
   }
 
@@ -128,7 +136,7 @@ __device__ __forceinline__ void skinny_accumulate(const bf16* __restrict__ x, in
 
 // MT: m16 tiles (16 features each) per block; NT: n8 tiles (8 batch rows each).
 template <int MT, int NT>
-__global__ void __launch_bounds__(SK_THREADS)
+__global__ void __launch_bounds__(SK_THREADS, (MT == 1 && NT == 1) ? 4 : 1)
 gemm_skinny_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w, void* __restrict__ y, int ldy,
                    int M, int N, int K, int mode, float out_scale, long long split_stride) {
   extern __shared__ float red[];     // [SK_WARPS][MT * 16][NT * 8]
@@ -217,7 +225,7 @@ struct QkvRope {
 };
 
 template <int NT>
-__global__ void __launch_bounds__(SK_THREADS)
+__global__ void __launch_bounds__(SK_THREADS, NT == 1 ? 4 : 1)
 gemm_skinny_qkv_rope_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w, bf16* __restrict__ q_out,
                             int ldq, int M, int K, QkvRope p) {
   extern __shared__ float red[];     // [SK_WARPS][16][NT * 8]

@@ -7,6 +7,7 @@ raises `EngineError` when a launch fails. Tensors must live on the CUDA device; 
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_double, c_float, c_int, c_longlong, c_void_p
 from typing import Optional
 
@@ -397,7 +398,7 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optiona
 
 
 SKINNY_MAX_ROWS = 64      # what the kernel takes
-SKINNY_FAST_ROWS = 16     # up to here it beats the library product (measured on B200); dispatchers use this
+SKINNY_FAST_ROWS = int(os.environ.get("DYNALM_SKINNY_ROWS", "16"))     # up to here the dispatchers use it (measured on B200)
 
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str = "store", out_scale: float = 1.0) -> None:
