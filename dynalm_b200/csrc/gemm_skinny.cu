@@ -12,7 +12,7 @@
 //
 // Epilogues: bf16 or fp32 store, or SwiGLU: W = [Wg; Wu], a block takes 8 gate rows and the 8 matching up
 // rows and stores silu(g) * u (the reference's matmul_gated, dynacore/include/dynacore/device/device.h:188-199).
-#include "common.cuh"
+#include "qkv_rope.cuh"
 
 namespace dl {
 
@@ -83,19 +83,22 @@ __device__ __forceinline__ void skinny_accumulate(const bf16* __restrict__ x, in
   };
   // The weights do not depend on the kernel before this one: the first pieces are on their way before the wait
   // for it, and each k-block's pieces (weights and x) are requested one block ahead of their use.
+  // (x is requested ahead only in the variants for up to 16 rows: more would cost registers.)
+  constexpr bool X_AHEAD = NT <= 2;
   uint4 a[MT][2][2], bq[NT][2];
   int blk = blk_begin + warp;
   if (blk < blk_end) load_w(blk, a);
   pdl_wait();
   pdl_trigger();
-  if (blk < blk_end) load_x(blk, bq);
+  if (X_AHEAD && blk < blk_end) load_x(blk, bq);
   for (; blk < blk_end; blk += SK_WARPS) {
-    uint4 a_next[MT][2][2], bq_next[NT][2];
+    uint4 a_next[MT][2][2], bq_next[X_AHEAD ? NT : 1][2];
     const bool more = blk + SK_WARPS < blk_end;
     if (more) {
       load_w(blk + SK_WARPS, a_next);
-      load_x(blk + SK_WARPS, bq_next);
+      if constexpr (X_AHEAD) load_x(blk + SK_WARPS, bq_next);
     }
+    if constexpr (!X_AHEAD) load_x(blk, bq);
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
 #pragma unroll
@@ -113,8 +116,10 @@ __device__ __forceinline__ void skinny_accumulate(const bf16* __restrict__ x, in
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int h = 0; h < 2; ++h) { a[mt][h][0] = a_next[mt][h][0]; a[mt][h][1] = a_next[mt][h][1]; }
+      if constexpr (X_AHEAD) {
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) { bq[nt][0] = bq_next[nt][0]; bq[nt][1] = bq_next[nt][1]; }
+        for (int nt = 0; nt < NT; ++nt) { bq[nt][0] = bq_next[nt][0]; bq[nt][1] = bq_next[nt][1]; }
+      }
     }
   }
 
@@ -212,18 +217,6 @@ gemm_skinny_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
 // before the rotation, as the unfused path rounds them into its q | k | v buffer; the rotation is the one of
 // rope_cache.cu (same angle formula, sincosf, fp32), so both paths give the same bits. Rotated q goes to
 // q_out [M, ldq], rotated k and plain v into the request's cache page.
-struct QkvRope {
-  const int* positions;       // [M]
-  const int* row_request;     // [M]
-  const int* block_table;     // [requests, max_blocks]
-  int max_blocks;
-  bf16* k_cache;
-  bf16* v_cache;
-  const float* inv_freq;      // [head_dim / 2]
-  float pos_scale;
-  int n_heads, n_kv_heads, head_dim, page_size;
-};
-
 template <int NT>
 __global__ void __launch_bounds__(SK_THREADS, NT == 1 ? 4 : 1)
 gemm_skinny_qkv_rope_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w, bf16* __restrict__ q_out,
@@ -274,9 +267,7 @@ gemm_skinny_qkv_rope_kernel(const bf16* __restrict__ x, int ldx, const bf16* __r
     if (head < p.n_heads) {
       dst = q_out + static_cast<size_t>(b) * ldq + f_lo + i;
     } else {
-      const int req = p.row_request[b];
-      const int page = p.block_table[static_cast<size_t>(req) * p.max_blocks + pos / p.page_size];
-      const size_t slot = static_cast<size_t>(page) * p.page_size + pos % p.page_size;
+      const size_t slot = qkv_rope_slot(p, b, pos);
       const bool is_k = head < p.n_heads + p.n_kv_heads;
       const int kvh = head - p.n_heads - (is_k ? 0 : p.n_kv_heads);
       dst = (is_k ? p.k_cache : p.v_cache) + (slot * p.n_kv_heads + kvh) * hd + (f_lo - head * hd) + i;
@@ -341,6 +332,7 @@ DL_EXPORT int dl_gemm_skinny_qkv_rope(const void* x, int ldx, const void* w, voi
   p.k_cache = static_cast<dl::bf16*>(k_cache);
   p.v_cache = static_cast<dl::bf16*>(v_cache);
   p.inv_freq = inv_freq;
+  p.angles = nullptr;
   p.pos_scale = pos_scale;
   p.n_heads = n_heads;
   p.n_kv_heads = n_kv_heads;

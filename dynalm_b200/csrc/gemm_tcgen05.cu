@@ -20,6 +20,7 @@
 // The reference reaches its GPU matrix products through a library (ggml_mul_mat,
 // dynacore/src/gpu/ggml_graph.cpp:278-292) and fuses the gated activation only on its CPU path
 // (matmul_gated, dynacore/include/dynacore/device/device.h:188-199).
+#include "qkv_rope.cuh"
 #include "tcgen05.cuh"
 
 namespace dl {
@@ -40,7 +41,7 @@ template <int BN> struct T5 {
   static constexpr size_t SMEM = static_cast<size_t>(STAGES) * STAGE_BYTES + T5_STORE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
 };
 
-enum { T5_OUT_BF16 = 0, T5_OUT_F32 = 1, T5_OUT_SWIGLU = 2 };
+enum { T5_OUT_BF16 = 0, T5_OUT_F32 = 1, T5_OUT_SWIGLU = 2, T5_OUT_QKV_ROPE = 3 };
 enum { T5_ERR_PRODUCER = 1, T5_ERR_MMA = 2, T5_ERR_EPILOGUE = 3 };
 
 // gate_rows: for SwiGLU the number of gate features F (W has 2F rows); the tile's W rows are
@@ -55,7 +56,7 @@ template <int T5_BN>
 __global__ void __launch_bounds__(T5_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     void* __restrict__ y, int ldy, int M, int N, int K, int mode, float out_scale, int gate_rows,
-                    int tiles_n, int num_tiles, int* __restrict__ status) {
+                    int tiles_n, int num_tiles, int* __restrict__ status, const QkvRope rope) {
   constexpr int T5_STAGES = T5<T5_BN>::STAGES;
   constexpr uint32_t T5_B_BYTES = T5<T5_BN>::B_BYTES, T5_STAGE_BYTES = T5<T5_BN>::STAGE_BYTES, T5_TMEM_COLS = T5<T5_BN>::TMEM_COLS;
   extern __shared__ unsigned char t5_raw[];
@@ -189,6 +190,72 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           }
           store_rows_bf16(w, my_stage, lane, out, ldy, row0, M, n0 + c0, gate_rows);   // gate_rows is a multiple of 8
         }
+      } else if (mode == T5_OUT_QKV_ROPE) {
+        // W = [Wq; Wk; Wv]: a tile holds whole heads (head_dim 64 or 128 divides the tile width). Thread = row:
+        // the two members of rotary pair i of a head are columns i and i + head_dim / 2 of the same thread.
+        const bool live = row < M;
+        const int pos = live ? rope.positions[row] : 0;
+        const size_t slot = live ? qkv_rope_slot(rope, row, pos) : 0;
+        const float fpos = static_cast<float>(pos) * rope.pos_scale;
+        const int hd = rope.head_dim;
+        const float4* my_angles = rope.angles != nullptr && live
+                                      ? reinterpret_cast<const float4*>(rope.angles + static_cast<size_t>(row) * (hd / 2))
+                                      : nullptr;       // two (cos, sin) pairs per 16-byte load
+        for (int h0 = 0; h0 < T5_BN && n0 + h0 < N; h0 += hd) {
+          const int head = (n0 + h0) / hd;                // q heads, then k heads, then v heads
+          const bool rotated = head < rope.n_heads + rope.n_kv_heads;
+          bf16* dst = nullptr;
+          if (live) {
+            if (head < rope.n_heads) {
+              dst = static_cast<bf16*>(y) + static_cast<size_t>(row) * ldy + static_cast<size_t>(head) * hd;
+            } else {
+              const bool is_k = head < rope.n_heads + rope.n_kv_heads;
+              const int kvh = head - rope.n_heads - (is_k ? 0 : rope.n_kv_heads);
+              dst = (is_k ? rope.k_cache : rope.v_cache) + (slot * rope.n_kv_heads + kvh) * hd;
+            }
+          }
+          for (int piece = 0; piece < hd / 64; ++piece) {     // 32 pairs at a time
+            uint32_t lo[32], hi[32];
+            tmem_ld32(lane_addr + h0 + piece * 32, lo);
+            tmem_ld32(lane_addr + h0 + hd / 2 + piece * 32, hi);
+            tmem_ld_wait();
+            // (cos, sin) of the piece's 32 pairs, two pairs per float4: all requested before any is used
+            float4 cs[16];
+            if (rotated) {
+              if (my_angles != nullptr) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) cs[i] = my_angles[piece * 16 + i];
+              } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                  sincosf(fpos * rope.inv_freq[piece * 32 + 2 * i], &cs[i].y, &cs[i].x);
+                  sincosf(fpos * rope.inv_freq[piece * 32 + 2 * i + 1], &cs[i].w, &cs[i].z);
+                }
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) cs[i] = make_float4(1.0f, 0.0f, 1.0f, 0.0f);     // v heads: no rotation
+            }
+            uint4 wlo[4], whi[4];
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint32_t pl[4], ph[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float a0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(lo[j + 2 * e])));
+                const float a1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(lo[j + 2 * e + 1])));
+                const float b0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(hi[j + 2 * e])));
+                const float b1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(hi[j + 2 * e + 1])));
+                const float4 t4 = cs[j / 2 + e];
+                pl[e] = pack2_bf16(a0 * t4.x - b0 * t4.y, a1 * t4.z - b1 * t4.w);
+                ph[e] = pack2_bf16(a0 * t4.y + b0 * t4.x, a1 * t4.w + b1 * t4.z);
+              }
+              wlo[j / 8] = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+              whi[j / 8] = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+            }
+            store_rows_pieces(wlo, whi, my_stage, lane, dst, piece * 32, hd / 2 + piece * 32);
+          }
+        }
       } else {
         for (int c0 = 0; c0 < T5_BN; c0 += 64) {
           uint32_t va[32], vb[32];
@@ -264,11 +331,11 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int 
 // mode 0: y bf16 [M, N] (N % 8 == 0); mode 1: y fp32 [M, N] (N % 4 == 0); mode 2: w = [gate; up] with N = 2F rows,
 // y bf16 [M, F] = silu(x Wg^T) * (x Wu^T) (F % 8 == 0). status: one device int, set to a nonzero code if a wait
 // inside the kernel timed out (left untouched otherwise).
-DL_EXPORT int dl_gemm_tcgen05(const void* x, int ldx, const void* w, void* y, int ldy, int M, int N, int K, int mode,
-                              float out_scale, int* status, cudaStream_t stream) {
+static int t5_launch(const void* x, int ldx, const void* w, void* y, int ldy, int M, int N, int K, int mode, float out_scale,
+                     int* status, const dl::QkvRope& rope, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K & 7) || (ldx & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) ||
-      status == nullptr || mode < 0 || mode > 2)
+      status == nullptr || mode < 0 || mode > 3)
     return DL_ERR_UNSUPPORTED;
   const int feats = mode == dl::T5_OUT_SWIGLU ? N / 2 : N;
   if ((mode == dl::T5_OUT_SWIGLU && (N & 1)) || (mode == dl::T5_OUT_F32 ? (feats & 3) || (ldy & 3) : (feats & 7) || (ldy & 7)) ||
@@ -309,7 +376,7 @@ DL_EXPORT int dl_gemm_tcgen05(const void* x, int ldx, const void* w, void* y, in
       configured = true;
     }
     dl::gemm_tcgen05_kernel<256><<<blocks, dl::T5_THREADS, dl::T5<256>::SMEM, stream>>>(
-        map_x, map_w, y, ldy, M, N, K, mode, out_scale, gate_rows, tiles_n, static_cast<int>(tiles), status);
+        map_x, map_w, y, ldy, M, N, K, mode, out_scale, gate_rows, tiles_n, static_cast<int>(tiles), status, rope);
   } else {
     static bool configured = false;
     if (!configured) {
@@ -319,7 +386,45 @@ DL_EXPORT int dl_gemm_tcgen05(const void* x, int ldx, const void* w, void* y, in
       configured = true;
     }
     dl::gemm_tcgen05_kernel<128><<<blocks, dl::T5_THREADS, dl::T5<128>::SMEM, stream>>>(
-        map_x, map_w, y, ldy, M, N, K, mode, out_scale, gate_rows, tiles_n, static_cast<int>(tiles), status);
+        map_x, map_w, y, ldy, M, N, K, mode, out_scale, gate_rows, tiles_n, static_cast<int>(tiles), status, rope);
   }
   return dl::launch_status();
+}
+
+DL_EXPORT int dl_gemm_tcgen05(const void* x, int ldx, const void* w, void* y, int ldy, int M, int N, int K, int mode,
+                              float out_scale, int* status, cudaStream_t stream) {
+  if (mode < 0 || mode > 2) return DL_ERR_UNSUPPORTED;
+  const dl::QkvRope none = {};
+  return t5_launch(x, ldx, w, y, ldy, M, N, K, mode, out_scale, status, none, stream);
+}
+
+// The q | k | v projection with the rotary encoding and the cache write in the epilogue: w bf16 [(n_heads + 2
+// n_kv_heads) * head_dim, K], head_dim 64 or 128 with the whole head rotated; rotated q goes to q_out [M, ldq]
+// (16-byte aligned rows), rotated k and plain v to the caches [pages, page_size, n_kv_heads, head_dim]. angles:
+// [M, head_dim / 2] (cos, sin) pairs from dl_rope_angles, or null (the epilogue then computes them, head by head).
+DL_EXPORT int dl_gemm_tcgen05_qkv_rope(const void* x, int ldx, const void* w, void* q_out, int ldq, int M, int K,
+                                       const int* positions, const int* row_request, const int* block_table, int max_blocks,
+                                       void* k_cache, void* v_cache, const float* inv_freq, const void* angles,
+                                       float pos_scale, int n_heads, int n_kv_heads, int head_dim, int page_size,
+                                       int* status, cudaStream_t stream) {
+  if ((head_dim != 64 && head_dim != 128) || n_heads <= 0 || n_kv_heads <= 0 || page_size <= 0 || inv_freq == nullptr ||
+      (reinterpret_cast<uintptr_t>(k_cache) & 15) || (reinterpret_cast<uintptr_t>(v_cache) & 15) ||
+      (reinterpret_cast<uintptr_t>(angles) & 15))
+    return DL_ERR_UNSUPPORTED;
+  dl::QkvRope p;
+  p.positions = positions;
+  p.row_request = row_request;
+  p.block_table = block_table;
+  p.max_blocks = max_blocks;
+  p.k_cache = static_cast<dl::bf16*>(k_cache);
+  p.v_cache = static_cast<dl::bf16*>(v_cache);
+  p.inv_freq = inv_freq;
+  p.angles = static_cast<const float2*>(angles);
+  p.pos_scale = pos_scale;
+  p.n_heads = n_heads;
+  p.n_kv_heads = n_kv_heads;
+  p.head_dim = head_dim;
+  p.page_size = page_size;
+  return t5_launch(x, ldx, w, q_out, ldq, M, (n_heads + 2 * n_kv_heads) * head_dim, K, dl::T5_OUT_QKV_ROPE, 1.0f, status, p,
+                   stream);
 }

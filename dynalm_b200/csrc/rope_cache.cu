@@ -133,7 +133,31 @@ __global__ void rope_cache_vec_kernel(T* __restrict__ qkv, int row_stride, const
     *reinterpret_cast<Vec16*>(vdst + idx * V) = *reinterpret_cast<const Vec16*>(base + q_width + kv_width + idx * V);
 }
 
+// (cos, sin) of every rotary pair of every row of a step: out[row * half + i] = sincos(float(pos) * pos_scale *
+// inv_freq[i]), the values the kernels above compute for themselves. A step computes them once for all layers
+// whose projection kernel rotates in its epilogue (gemm_tcgen05.cu).
+__global__ void rope_angles_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, int half,
+                                   float pos_scale, int rows, float2* __restrict__ out) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * half) return;
+  const int row = idx / half, i = idx % half;
+  const float theta = static_cast<float>(positions[row]) * pos_scale * inv_freq[i];
+  float s, c;
+  sincosf(theta, &s, &c);
+  out[idx] = make_float2(c, s);
+}
+
 }  // namespace dl
+
+DL_EXPORT int dl_rope_angles(const int* positions, const float* inv_freq, int half, float pos_scale, int rows, void* out,
+                             cudaStream_t stream) {
+  if (rows <= 0 || half <= 0) return 0;
+  const long long n = static_cast<long long>(rows) * half;
+  if (n > (1ll << 30)) return DL_ERR_UNSUPPORTED;
+  dl::rope_angles_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(positions, inv_freq, half, pos_scale,
+                                                                                     rows, static_cast<float2*>(out));
+  return dl::launch_status();
+}
 
 // qkv: [rows, row_stride] with q | k | v side by side; q is rotated in place, k is rotated on its way
 // into the cache (the k columns of qkv are left unrotated), v is copied. inv_freq may be null (no

@@ -182,6 +182,29 @@ __device__ __forceinline__ void store_rows_bf16(const uint4 (&w)[8], unsigned ch
   __syncwarp();
 }
 
+// As store_rows_bf16 for rows that lie anywhere: lane r holds two pieces of 32 bf16 (`lo`, `hi`: 4 x 16 bytes each)
+// of its row and the row's base pointer `dst` (null: nothing is written); the pieces go to dst + off_lo and
+// dst + off_hi (elements, multiples of 8). Each store instruction covers four rows' pieces of 64 bytes.
+__device__ __forceinline__ void store_rows_pieces(const uint4 (&lo)[4], const uint4 (&hi)[4], unsigned char* stage, int lane,
+                                                  bf16* dst, int off_lo, int off_hi) {
+  uint4* st = reinterpret_cast<uint4*>(stage);
+#pragma unroll
+  for (int ch = 0; ch < 4; ++ch) {
+    st[lane * 8 + (ch ^ (lane & 7))] = lo[ch];
+    st[lane * 8 + ((ch + 4) ^ (lane & 7))] = hi[ch];
+  }
+  __syncwarp();
+  const unsigned long long mine = reinterpret_cast<unsigned long long>(dst);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = i * 4 + (lane >> 3), ch = lane & 7;
+    const uint4 v = st[r * 8 + (ch ^ (r & 7))];
+    bf16* base = reinterpret_cast<bf16*>(__shfl_sync(0xffffffffu, mine, r));
+    if (base != nullptr) *reinterpret_cast<uint4*>(base + (ch < 4 ? off_lo + ch * 8 : off_hi + (ch - 4) * 8)) = v;
+  }
+  __syncwarp();
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);

@@ -28,7 +28,9 @@ _SIGNATURES = {
         "dl_residual_add": [_I, _P, _P, _F, _L, _I, _L, _P],
     },
     "activation": {"dl_silu_mul": [_I, _P, _P, _I, _I, _P]},
-    "rope_cache": {"dl_rope_cache_write": [_I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _F, _I, _I, _I, _I, _I, _I, _P]},
+    "rope_cache": {
+        "dl_rope_cache_write": [_I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _F, _I, _I, _I, _I, _I, _I, _P],
+        "dl_rope_angles": [_P, _P, _I, _F, _I, _P, _P]},
     "attention_generic": {
         "dl_paged_attention_generic": [_I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P]},
     "attention_decode": {
@@ -41,7 +43,9 @@ _SIGNATURES = {
     "gemm_skinny": {
         "dl_gemm_skinny": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _L, _P],
         "dl_gemm_skinny_qkv_rope": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P, _F, _I, _I, _I, _I, _P]},
-    "gemm_tcgen05": {"dl_gemm_tcgen05": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P]},
+    "gemm_tcgen05": {
+        "dl_gemm_tcgen05": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
+        "dl_gemm_tcgen05_qkv_rope": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P, _F, _I, _I, _I, _I, _P, _P]},
     "gemm_simt": {"dl_gemm_simt": [_I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _P]},
     "sampling": {
         "dl_argmax": [_P, _I, _I, _I, _P, _P, _P],
@@ -272,33 +276,60 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
         page_size, scale, window, n_split, _stream()), "paged_attention_decode")
 
 
-def gemm_skinny_qkv_rope(x: torch.Tensor, w_qkv: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor,
-                         row_request: torch.Tensor, block_table: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
-                         inv_freq: torch.Tensor, pos_scale: float, n_heads: int, n_kv_heads: int, head_dim: int,
-                         page_size: int) -> None:
-    """The q | k | v projection of up to 16 rows with rotary encoding and cache write in its epilogue: rotated q
-    into q_out [rows, >= n_heads * head_dim], rotated k and plain v into the paged cache. The whole head is
-    rotated (inv_freq has head_dim / 2 entries). bfloat16; see csrc/gemm_skinny.cu."""
+QKV_ROPE_TCGEN05_HEAD_DIMS = (64, 128)
+
+
+def rope_angles(positions: torch.Tensor, inv_freq: torch.Tensor, pos_scale: float, rows: int, out: torch.Tensor) -> None:
+    """out[r, i] = (cos, sin)(float(positions[r]) * pos_scale * inv_freq[i]): float32 [rows, len(inv_freq), 2]."""
+    _cuda(positions, inv_freq, out)
+    half = inv_freq.numel()
+    if positions.dtype != torch.int32 or inv_freq.dtype != torch.float32 or out.dtype != torch.float32 \
+            or out.numel() < rows * half * 2 or not out.is_contiguous() or out.data_ptr() % 16:
+        raise InvalidArgument("rope_angles: int32 positions, float32 inv_freq, contiguous float32 out [rows, half, 2]")
+    _check(_fn("rope_cache", "dl_rope_angles")(_p(positions), _p(inv_freq), half, pos_scale, rows, _p(out), _stream()),
+           "rope_angles")
+
+
+def gemm_qkv_rope(x: torch.Tensor, w_qkv: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor,
+                  row_request: torch.Tensor, block_table: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                  inv_freq: torch.Tensor, pos_scale: float, n_heads: int, n_kv_heads: int, head_dim: int,
+                  page_size: int, angles: Optional[torch.Tensor] = None) -> None:
+    """The q | k | v projection with rotary encoding and cache write in its epilogue: rotated q into
+    q_out [rows, >= n_heads * head_dim], rotated k and plain v into the paged cache. The whole head is rotated
+    (inv_freq has head_dim / 2 entries). bfloat16. Up to 16 rows: the weight-streaming kernel
+    (csrc/gemm_skinny.cu, head_dim a multiple of 16); more rows: the tcgen05 kernel (csrc/gemm_tcgen05.cu,
+    head_dim 64 or 128), which reads the step's (cos, sin) pairs from `angles` (see rope_angles) when given."""
     _cuda(x, w_qkv, q_out, positions, row_request, block_table, k_cache, v_cache, inv_freq)
     _rows_contiguous(x, "x")
     _rows_contiguous(q_out, "q_out")
     M, K = x.shape
     if any(t.dtype != torch.bfloat16 for t in (x, w_qkv, q_out, k_cache, v_cache)):
-        raise Unsupported("gemm_skinny_qkv_rope: bfloat16 only")
-    if M > SKINNY_FAST_ROWS or K % 8 or x.stride(0) % 8 or head_dim % 16:
-        raise Unsupported(f"gemm_skinny_qkv_rope: {M} rows (at most {SKINNY_FAST_ROWS}), K {K} and head_dim {head_dim}")
+        raise Unsupported("gemm_qkv_rope: bfloat16 only")
+    few = M <= SKINNY_FAST_ROWS
+    if K % 8 or x.stride(0) % 8 or (head_dim % 16 if few else head_dim not in QKV_ROPE_TCGEN05_HEAD_DIMS):
+        raise Unsupported(f"gemm_qkv_rope: {M} rows, K {K} and head_dim {head_dim}")
+    if angles is not None and (angles.dtype != torch.float32 or angles.numel() < M * head_dim or not angles.is_contiguous()):
+        raise InvalidArgument("gemm_qkv_rope: angles must be contiguous float32 [rows, head_dim / 2, 2]")
+    if not few and (x.data_ptr() % 16 or w_qkv.data_ptr() % 16 or q_out.data_ptr() % 16 or q_out.stride(0) % 8):
+        raise Unsupported("gemm_qkv_rope: x, w and q_out rows must be 16-byte aligned")
     if tuple(w_qkv.shape) != ((n_heads + 2 * n_kv_heads) * head_dim, K) or not w_qkv.is_contiguous():
-        raise InvalidArgument("gemm_skinny_qkv_rope: w must be contiguous [(heads + 2 kv_heads) * head_dim, K]")
+        raise InvalidArgument("gemm_qkv_rope: w must be contiguous [(heads + 2 kv_heads) * head_dim, K]")
     if inv_freq.dtype != torch.float32 or inv_freq.numel() * 2 != head_dim:
-        raise Unsupported("gemm_skinny_qkv_rope: the rotary width must be the whole head (inv_freq float32 [head_dim / 2])")
+        raise Unsupported("gemm_qkv_rope: the rotary width must be the whole head (inv_freq float32 [head_dim / 2])")
     if q_out.shape[0] < M or q_out.shape[1] < n_heads * head_dim:
-        raise InvalidArgument("gemm_skinny_qkv_rope: q_out is smaller than [rows, heads * head_dim]")
+        raise InvalidArgument("gemm_qkv_rope: q_out is smaller than [rows, heads * head_dim]")
     if tuple(k_cache.shape[1:]) != (page_size, n_kv_heads, head_dim) or k_cache.shape != v_cache.shape \
             or not k_cache.is_contiguous() or not v_cache.is_contiguous():
-        raise InvalidArgument("gemm_skinny_qkv_rope: cache shape is not [pages, page_size, kv_heads, head_dim]")
+        raise InvalidArgument("gemm_qkv_rope: cache shape is not [pages, page_size, kv_heads, head_dim]")
     if block_table.dtype != torch.int32 or block_table.stride(-1) != 1 or positions.dtype != torch.int32 \
             or row_request.dtype != torch.int32:
-        raise InvalidArgument("gemm_skinny_qkv_rope: positions, row_request and block_table must be int32")
+        raise InvalidArgument("gemm_qkv_rope: positions, row_request and block_table must be int32")
+    if not few:
+        _check(_fn("gemm_tcgen05", "dl_gemm_tcgen05_qkv_rope")(
+            _p(x), x.stride(0), _p(w_qkv), _p(q_out), q_out.stride(0), M, K, _p(positions), _p(row_request),
+            _p(block_table), block_table.stride(0), _p(k_cache), _p(v_cache), _p(inv_freq), _p(angles), pos_scale, n_heads,
+            n_kv_heads, head_dim, page_size, _p(_status_word(x.device)), _stream()), "gemm_tcgen05_qkv_rope")
+        return
     _check(_fn("gemm_skinny", "dl_gemm_skinny_qkv_rope")(
         _p(x), x.stride(0), _p(w_qkv), _p(q_out), q_out.stride(0), M, K, _p(positions), _p(row_request), _p(block_table),
         block_table.stride(0), _p(k_cache), _p(v_cache), _p(inv_freq), pos_scale, n_heads, n_kv_heads, head_dim, page_size,

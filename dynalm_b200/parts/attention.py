@@ -69,10 +69,12 @@ class PagedAttention:
         k_cache, v_cache = cache.arrays
         table = self.position.table() if self.position is not None else None
         if owns_cache and self._fused_projection_applies(x, table):
-            # few rows: one weight-streaming kernel projects, rotates and writes the cache
+            # one kernel projects, rotates and writes the cache
             qkv = rt.buffer("attn_qkv", (rows, self.q_width + 2 * self.kv_width))
-            ops.gemm_skinny_qkv_rope(x, self.w_qkv, qkv, ctx.positions, ctx.row_request, cache.block_table, k_cache, v_cache,
-                                     table[0], table[2], s.num_heads, s.num_kv_heads, s.head_dim, cache.page_size)
+            step_angles = getattr(self.position, "step_angles", None)
+            angles = step_angles(ctx, rt) if rows > ops.SKINNY_FAST_ROWS and step_angles is not None else None
+            ops.gemm_qkv_rope(x, self.w_qkv, qkv, ctx.positions, ctx.row_request, cache.block_table, k_cache, v_cache,
+                              table[0], table[2], s.num_heads, s.num_kv_heads, s.head_dim, cache.page_size, angles)
             return self._attend_and_project(qkv, cache, ctx, rows)
         if owns_cache:
             qkv = rt.buffer("attn_qkv", (rows, self.q_width + 2 * self.kv_width))
@@ -92,10 +94,16 @@ class PagedAttention:
         return self._attend_and_project(qkv, cache, ctx, rows)
 
     def _fused_projection_applies(self, x: torch.Tensor, table) -> bool:
-        """bfloat16, at most 16 rows, no bias, and the rotation covers the whole head."""
-        return (table is not None and table[0] is not None and table[1] == self.spec.head_dim and self.b_qkv is None
-                and x.dtype == torch.bfloat16 and x.shape[0] <= ops.SKINNY_FAST_ROWS and x.shape[1] % 8 == 0
-                and x.stride(0) % 8 == 0)
+        """bfloat16, no bias, the rotation covers the whole head, and either few rows (the weight-streaming
+        kernel) or enough tiles for the tcgen05 kernel with a head size it takes."""
+        if not (table is not None and table[0] is not None and table[1] == self.spec.head_dim and self.b_qkv is None
+                and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0):
+            return False
+        if x.shape[0] <= ops.SKINNY_FAST_ROWS:
+            return True
+        from ..kernels.gemm import tcgen05_ok
+        qkv = self.rt.buffer("attn_qkv", (x.shape[0], self.q_width + 2 * self.kv_width))
+        return self.spec.head_dim in ops.QKV_ROPE_TCGEN05_HEAD_DIMS and tcgen05_ok(x, self.w_qkv, qkv, self.w_qkv.shape[0])
 
     def _attend_and_project(self, qkv: torch.Tensor, cache, ctx, rows: int) -> torch.Tensor:
         s, rt = self.spec, self.rt

@@ -44,6 +44,20 @@ class RotaryEncoding:
         """(inverse frequencies float32 [rotary_dim / 2], rotary_dim, position scale) for the fused kernel."""
         return self.inv_freq, self.rotary_dim, self.pos_scale
 
+    def step_angles(self, ctx, runtime) -> torch.Tensor:
+        """(cos, sin) of every pair for every row of the step, float32 [rows, rotary_dim / 2, 2]: computed once per
+        step and shared by all layers with the same encoding."""
+        key = ("rope_angles", self.rotary_dim, self.pos_scale, float(self.spec.theta), self.spec.factors)
+        got = ctx.extras.get(key)
+        if got is None:
+            from ..kernels import ops
+            half = self.rotary_dim // 2
+            flat = runtime.flat(f"rope_angles_{abs(hash(key)) % (1 << 32):08x}", runtime.max_tokens * half * 2)
+            got = flat[:ctx.num_tokens * half * 2].view(ctx.num_tokens, half, 2)
+            ops.rope_angles(ctx.positions, self.inv_freq, self.pos_scale, ctx.num_tokens, got)
+            ctx.extras[key] = got
+        return got
+
     def apply(self, q, k, positions) -> None:  # the fused kernel does it
         raise NotImplementedError
 

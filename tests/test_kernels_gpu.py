@@ -501,33 +501,53 @@ def test_gemm_tcgen05(ops, M, N, K):
 
 
 @pytest.mark.parametrize("rows,heads,kvh,hd,K,page", [(8, 32, 8, 64, 2048, 16), (1, 4, 4, 16, 80, 16), (13, 6, 2, 128, 264, 32),
-                                                      (16, 5, 1, 48, 1000, 16)])
-def test_gemm_skinny_qkv_rope_matches_the_separate_kernels(ops, rows, heads, kvh, hd, K, page):
-    """Projection + rotation + cache write in one kernel against gemm_skinny followed by rope_cache_write:
+                                                      (16, 5, 1, 48, 1000, 16), (300, 32, 8, 64, 512, 16),
+                                                      (133, 5, 1, 128, 200, 32), (1000, 6, 3, 64, 72, 16)])
+def test_gemm_qkv_rope_matches_the_separate_kernels(ops, rows, heads, kvh, hd, K, page):
+    """Projection + rotation + cache write in one kernel (weight-streaming up to 16 rows, tcgen05 beyond) against
+    the plain product followed by rope_cache_write:
     the same q and the same cache pages (positions in the middle of pages, requests in shuffled rows)."""
     g = torch.Generator(device="cpu").manual_seed(5)
     width = (heads + 2 * kvh) * hd
     x = (torch.randn(rows, K, generator=g) * 0.5).bfloat16().to(DEV)
     w = (torch.randn(width, K, generator=g) / math.sqrt(K)).bfloat16().to(DEV)
     inv_freq = (10000.0 ** (-torch.arange(0, hd, 2, dtype=torch.float32) / hd)).to(DEV)
-    positions = torch.tensor([(37 * r + 5) % 90 for r in range(rows)], dtype=torch.int32, device=DEV)
-    row_request = torch.tensor([(r * 7) % rows for r in range(rows)], dtype=torch.int32, device=DEV)
-    max_blocks = -(-90 // page)
-    table = torch.randperm(rows * max_blocks, generator=g).to(torch.int32).view(rows, max_blocks).to(DEV)
-    pages = rows * max_blocks
+    n_req = min(rows, 16)                      # row r belongs to request r % n_req, at a position of its own
+    span = 90 * -(-rows // n_req)
+    positions = torch.tensor([(37 * (r % n_req) + 5) % 90 + 90 * (r // n_req) for r in range(rows)], dtype=torch.int32,
+                             device=DEV)
+    row_request = torch.tensor([(r * 7) % n_req if rows <= 16 else r % n_req for r in range(rows)], dtype=torch.int32,
+                               device=DEV)
+    if rows <= 16:
+        positions = torch.tensor([(37 * r + 5) % 90 for r in range(rows)], dtype=torch.int32, device=DEV)
+    max_blocks = -(-span // page)
+    table = torch.randperm(n_req * max_blocks, generator=g).to(torch.int32).view(n_req, max_blocks).to(DEV)
+    pages = n_req * max_blocks
 
     def caches():
         return (torch.zeros(pages, page, kvh, hd, dtype=torch.bfloat16, device=DEV),
                 torch.zeros(pages, page, kvh, hd, dtype=torch.bfloat16, device=DEV))
     k_ref, v_ref = caches()
     qkv_ref = torch.zeros(rows, width, dtype=torch.bfloat16, device=DEV)
-    ops.gemm_skinny(x, w, qkv_ref)
+    if rows <= 16:
+        ops.gemm_skinny(x, w, qkv_ref)
+    else:
+        ops.gemm_tcgen05(x, w, qkv_ref)
     ops.rope_cache_write(qkv_ref, positions, row_request, table, k_ref, v_ref, inv_freq, hd, 0.5, heads, kvh, hd, page)
     k_got, v_got = caches()
     qkv_got = torch.zeros(rows, width, dtype=torch.bfloat16, device=DEV)
-    ops.gemm_skinny_qkv_rope(x, w, qkv_got, positions, row_request, table, k_got, v_got, inv_freq, 0.5, heads, kvh, hd, page)
+    ops.gemm_qkv_rope(x, w, qkv_got, positions, row_request, table, k_got, v_got, inv_freq, 0.5, heads, kvh, hd, page)
     q_ref, q_got = qkv_ref[:, :heads * hd].float(), qkv_got[:, :heads * hd].float()
     assert (q_ref - q_got).abs().max().item() <= 1e-2 * q_ref.abs().max().item()
     assert (k_ref.float() - k_got.float()).abs().max().item() <= 1e-2 * k_ref.float().abs().max().item()
     assert torch.equal(v_ref, v_got)
     assert k_got.abs().sum().item() > 0 and (k_got != 0).sum().item() == rows * kvh * hd
+    if rows > 16:
+        # the same with the step's (cos, sin) pairs computed once beforehand: the same bits
+        angles = torch.zeros(rows, hd // 2, 2, dtype=torch.float32, device=DEV)
+        ops.rope_angles(positions, inv_freq, 0.5, rows, angles)
+        k2, v2 = caches()
+        qkv2 = torch.zeros_like(qkv_got)
+        ops.gemm_qkv_rope(x, w, qkv2, positions, row_request, table, k2, v2, inv_freq, 0.5, heads, kvh, hd, page, angles)
+        assert torch.equal(qkv2[:, :heads * hd], qkv_got[:, :heads * hd]) and torch.equal(k2, k_got) and torch.equal(v2, v_got)
+    assert ops.gemm_tcgen05_status() == 0
