@@ -7,9 +7,9 @@
 //
 //   S = Q K^T      tcgen05.mma, M 128, N BN, both operands K-major from shared memory, S in tensor memory
 //   softmax        128 threads, one row each: S from tensor memory, mask by position, running maximum and
-//                  sum in fp32 with base-2 exponentials, P rounded to bf16 into shared memory
-//   O += P V       tcgen05.mma, M 128, N head_dim, P K-major, V read as it lies in the cache (head
-//                  dimension contiguous: an MN-major operand), O in tensor memory
+//                  sum in fp32 with base-2 exponentials, P rounded to bf16 back into tensor memory
+//   O += P V       tcgen05.mma, M 128, N head_dim, P from tensor memory, V read as it lies in the cache
+//                  (head dimension contiguous: an MN-major operand), O in tensor memory
 //
 // Roles: warps 0..3 softmax and the final store, warp 4 (one lane) TMA producer, warp 5 (one lane) issues
 // the MMAs and owns the tensor-memory allocation. The MMA warp issues S of tile i+1 as soon as the softmax
@@ -17,7 +17,8 @@
 // maximum has grown by more than 2^8 since the reference point of its exponentials was set; the result is
 // the same function of the scores, with probabilities kept below 2^8.
 //
-// Two blocks fit an SM (112 KiB of shared memory and 256 tensor-memory columns each).
+// Two blocks fit an SM (112 KiB of shared memory: Q and three stages of K and V; 256 tensor-memory columns:
+// S, O and P).
 //
 // Every wait on an mbarrier is bounded (tcgen05.cuh); on a timeout all roles fall through to the common
 // exit, where tensor memory is freed, and *status tells the host.
@@ -42,9 +43,10 @@ template <int HD> struct FA {
   static constexpr int DB = HD / 64;                   // 64-wide blocks of the head dimension (128 bytes: one swizzle row)
   static constexpr uint32_t Q_BYTES = FA_BM * HD * 2;
   static constexpr uint32_t KV_BYTES = BN * HD * 2;    // one K or one V tile
-  static constexpr uint32_t P_BYTES = FA_BM * BN * 2;
-  static constexpr uint32_t BAR_BYTES = 128;
-  static constexpr uint32_t SMEM = Q_BYTES + 4 * KV_BYTES + P_BYTES + BAR_BYTES;
+  static constexpr int STAGES = 3;                     // of K and of V
+  static constexpr uint32_t P_COL = HD == 64 ? 192 : 64;   // tensor-memory columns: S from 0, O from 128, P (BN / 2 columns) here
+  static constexpr uint32_t BAR_BYTES = 192;
+  static constexpr uint32_t SMEM = Q_BYTES + 2 * STAGES * KV_BYTES + BAR_BYTES;
 };
 
 // 2^x on the special-function unit; 2^-inf = 0.
@@ -62,25 +64,25 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
                               const int4* __restrict__ tiles, bf16* __restrict__ out, int out_stride, int n_heads,
                               int n_kv_heads, int page_shift, float scale_log2, int window, int* __restrict__ status) {
   constexpr int BN = FA<HD>::BN, DB = FA<HD>::DB;
-  constexpr uint32_t Q_BYTES = FA<HD>::Q_BYTES, KV_BYTES = FA<HD>::KV_BYTES, P_BYTES = FA<HD>::P_BYTES;
+  constexpr int ST = FA<HD>::STAGES;
+  constexpr uint32_t Q_BYTES = FA<HD>::Q_BYTES, KV_BYTES = FA<HD>::KV_BYTES, P_COL = FA<HD>::P_COL;
   constexpr uint32_t Q_BLOCK = FA_BM * 128;       // bytes of one 64-wide block of Q (128 rows of 128 bytes)
   constexpr uint32_t KV_BLOCK = BN * 128;         // likewise for a K or V tile
   extern __shared__ __align__(1024) unsigned char fa_raw[];
   unsigned char* q_s = fa_raw;
-  unsigned char* k_s = q_s + Q_BYTES;             // [2][KV_BYTES]
-  unsigned char* v_s = k_s + 2 * KV_BYTES;        // [2][KV_BYTES]
-  unsigned char* p_s = v_s + 2 * KV_BYTES;        // [BN / 64][128 rows][128 bytes]; the output staging at the end
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + P_BYTES);
+  unsigned char* k_s = q_s + Q_BYTES;             // [ST][KV_BYTES]; the output staging at the end
+  unsigned char* v_s = k_s + ST * KV_BYTES;       // [ST][KV_BYTES]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + ST * KV_BYTES);
   uint64_t* q_full = bars;
-  uint64_t* k_full = bars + 1;                    // [2]
-  uint64_t* v_full = bars + 3;                    // [2]
-  uint64_t* k_empty = bars + 5;                   // [2] S of the tile has been computed
-  uint64_t* v_empty = bars + 7;                   // [2] P V of the tile has been computed
-  uint64_t* s_full = bars + 9;                    // S is in tensor memory
-  uint64_t* s_empty = bars + 10;                  // the softmax threads hold S in registers
-  uint64_t* p_full = bars + 11;                   // P is in shared memory and O has been rescaled
-  uint64_t* pv_done = bars + 12;                  // O includes the tile
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* k_full = bars + 1;                    // [ST]
+  uint64_t* v_full = k_full + ST;                 // [ST]
+  uint64_t* k_empty = v_full + ST;                // [ST] S of the tile has been computed
+  uint64_t* v_empty = k_empty + ST;               // [ST] P V of the tile has been computed
+  uint64_t* s_full = v_empty + ST;                // S is in tensor memory
+  uint64_t* s_empty = s_full + 1;                 // the softmax threads hold S in registers
+  uint64_t* p_full = s_full + 2;                  // P is in tensor memory and O has been rescaled
+  uint64_t* pv_done = s_full + 3;                 // O includes the tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   if (smem_u32(fa_raw) & 1023u) {                 // the swizzled tiles need 1024-byte alignment
@@ -99,7 +101,7 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < ST; ++s) {
       mbar_init(&k_full[s], 1);
       mbar_init(&v_full[s], 1);
       mbar_init(&k_empty[s], 1);
@@ -134,14 +136,15 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
     // piece inside, so that every copy reads pages this request holds (finite values)
     const int first_piece = lo_tile & ~(FA_BOX_KEYS - 1), last_piece = pos_last & ~(FA_BOX_KEYS - 1);
     for (int i = 0; i < n_kt; ++i) {
-      const int s = i & 1;
+      const int s = i % ST;
+      const uint32_t round = static_cast<uint32_t>(i / ST);
       // lane b looks up the page of piece b
       int my_slot = 0;
       if (lane < BN / FA_BOX_KEYS) {
         const int key = min(max((j_begin + i) * BN + lane * FA_BOX_KEYS, first_piece), last_piece);
         my_slot = (table[key >> page_shift] << page_shift) + (key & page_mask);
       }
-      if (i >= 2 && !warp_wait(&k_empty[s], ((i >> 1) & 1) ^ 1, status, FA_ERR_PRODUCER, abort_flag)) break;
+      if (i >= ST && !warp_wait(&k_empty[s], (round & 1) ^ 1, status, FA_ERR_PRODUCER, abort_flag)) break;
       if (elect_one()) mbar_expect_tx(&k_full[s], KV_BYTES);
 #pragma unroll
       for (int b = 0; b < BN / FA_BOX_KEYS; ++b) {
@@ -152,7 +155,7 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
             tma_load_3d(k_s + s * KV_BYTES + db * KV_BLOCK + b * (FA_BOX_KEYS * 128), &map_k, db * 64, kvh, slot, &k_full[s]);
         }
       }
-      if (i >= 2 && !warp_wait(&v_empty[s], ((i >> 1) & 1) ^ 1, status, FA_ERR_PRODUCER, abort_flag)) break;
+      if (i >= ST && !warp_wait(&v_empty[s], (round & 1) ^ 1, status, FA_ERR_PRODUCER, abort_flag)) break;
       if (elect_one()) mbar_expect_tx(&v_full[s], KV_BYTES);
 #pragma unroll
       for (int b = 0; b < BN / FA_BOX_KEYS; ++b) {
@@ -174,11 +177,11 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
     constexpr uint32_t idesc_o = umma_idesc_b_mn(FA_BM, HD);
     // descriptors of the first pieces; a step along the tile adds (bytes >> 4) to the address field
     const uint64_t q_desc = umma_desc_sw128(smem_u32(q_s)), k_desc = umma_desc_sw128(smem_u32(k_s));
-    const uint64_t p_desc = umma_desc_sw128(smem_u32(p_s)), v_desc = umma_desc_mn_sw128(smem_u32(v_s), KV_BLOCK, 1024);
+    const uint64_t v_desc = umma_desc_mn_sw128(smem_u32(v_s), KV_BLOCK, 1024);
     // S of tile i: waits for K, issues HD / 16 MMAs, frees the K stage and signals the softmax warps
     auto issue_s = [&](int i) -> bool {
-      const int s = i & 1;
-      if (!warp_wait(&k_full[s], (i >> 1) & 1, status, FA_ERR_MMA, abort_flag)) return false;
+      const int s = i % ST;
+      if (!warp_wait(&k_full[s], (i / ST) & 1, status, FA_ERR_MMA, abort_flag)) return false;
       tcgen05_after_sync();
       if (elect_one()) {
 #pragma unroll
@@ -196,21 +199,21 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
     bool ok = warp_wait(q_full, 0, status, FA_ERR_MMA, abort_flag);
     ok = ok && issue_s(0);
     for (int i = 0; i < n_kt && ok; ++i) {
-      const int s = i & 1;
+      const int s = i % ST;
       if (i + 1 < n_kt) {
         // S of the next tile overwrites S of this one: the softmax threads must hold it in registers
         if (!warp_wait(s_empty, i & 1, status, FA_ERR_MMA, abort_flag) || !issue_s(i + 1)) break;
       }
-      if (!warp_wait(&v_full[s], (i >> 1) & 1, status, FA_ERR_MMA, abort_flag)) break;
+      if (!warp_wait(&v_full[s], (i / ST) & 1, status, FA_ERR_MMA, abort_flag)) break;
       if (!warp_wait(p_full, i & 1, status, FA_ERR_MMA, abort_flag)) break;
       tcgen05_after_sync();
       if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
-          // P: 16 keys = 32 bytes along a swizzled row, 64 keys per block of 128 rows. V: 16 keys = 16 rows of
-          // 128 bytes; groups of 8 keys 1024 bytes apart, blocks of 64 head dimensions KV_BLOCK apart.
-          umma_bf16(tmem_base + FA_O_COL, p_desc + (((kk >> 2) * (FA_BM * 128) + (kk & 3) * 32) >> 4),
-                    v_desc + ((s * KV_BYTES + kk * (16 * 128)) >> 4), idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+          // P: 16 keys = 8 tensor-memory columns (two bf16 each). V: 16 keys = 16 rows of 128 bytes; groups of 8
+          // keys 1024 bytes apart, blocks of 64 head dimensions KV_BLOCK apart.
+          umma_bf16_ts(tmem_base + FA_O_COL, tmem_base + P_COL + kk * 8, v_desc + ((s * KV_BYTES + kk * (16 * 128)) >> 4),
+                       idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(&v_empty[s]);
         umma_commit(pv_done);
@@ -277,17 +280,12 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
           w[e] = pack2_bf16(p0, p1);
         }
       };
-      // P is K-major with the 128-byte swizzle: row r, 16-byte piece ch of a 64-key block at ch ^ (r & 7)
-      auto store8 = [&](int c0, const uint32_t (&w)[4]) {
-        unsigned char* row = p_s + (c0 >> 6) * (FA_BM * 128) + r * 128;
-        *reinterpret_cast<uint4*>(row + ((((c0 >> 3) & 7) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-      };
-      // the first 64 keys go to registers while P V of the previous tile may still be reading the P buffer
+      // the first 64 keys go to registers while P V of the previous tile may still be reading P
       uint32_t first[8][4];
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) exp8(ch * 8, first[ch]);
       if (i > 0) {
-        // P V of the previous tile: O is complete up to it and the P buffer is free
+        // P V of the previous tile: O is complete up to it and P may be overwritten
         if (!warp_wait(pv_done, (i - 1) & 1, status, FA_ERR_SOFTMAX, abort_flag)) { ok = false; break; }
         tcgen05_after_sync();
         if (__any_sync(0xffffffffu, rescale)) {
@@ -303,23 +301,24 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
           tmem_st_wait();
         }
       }
+      // P in tensor memory: this thread's lane, column j = keys 2j and 2j + 1
+      const uint32_t taddr_p = taddr_s + P_COL;
+      tmem_st32(taddr_p, *reinterpret_cast<const uint32_t(*)[32]>(&first[0][0]));
+      if constexpr (BN > 64) {
+        uint32_t second[8][4];
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) store8(ch * 8, first[ch]);
-#pragma unroll
-      for (int c0 = 64; c0 < BN; c0 += 8) {
-        uint32_t w[4];
-        exp8(c0, w);
-        store8(c0, w);
+        for (int ch = 0; ch < 8; ++ch) exp8(64 + ch * 8, second[ch]);
+        tmem_st32(taddr_p + 32, *reinterpret_cast<const uint32_t(*)[32]>(&second[0][0]));
       }
+      tmem_st_wait();
       l_run = l_run * corr + (sum0 + sum1);
-      fence_proxy_async_smem();
       tcgen05_before_sync();
       mbar_arrive(p_full);
     }
     if (ok && warp_wait(pv_done, (n_kt - 1) & 1, status, FA_ERR_SOFTMAX, abort_flag)) {
       tcgen05_after_sync();
       const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-      unsigned char* my_stage = p_s + warp * 4096;
+      unsigned char* my_stage = k_s + warp * 4096;      // every K and V stage has been consumed
 #pragma unroll
       for (int c0 = 0; c0 < HD; c0 += 64) {
         uint32_t va[32], vb[32];
