@@ -297,7 +297,8 @@ int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, c
 
 constexpr int DT_WARPS = 4;
 constexpr int DT_THREADS = DT_WARPS * 32;
-constexpr int DT_KT = 32;     // keys per tile
+// Keys per tile of a warp (KT): 32, or 16 for the large head sizes, where 32 would leave room for only one block
+// per SM (shared memory) and too few warps to cover the latency of the key and value stream.
 
 __device__ __forceinline__ void dt_cp_async16(void* smem, const void* gmem, bool valid) {
   const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
@@ -329,7 +330,7 @@ __device__ __forceinline__ uint32_t dt_pack(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&p);
 }
 
-template <int HD, int STAGES>
+template <int HD, int STAGES, int KT>
 __global__ void __launch_bounds__(DT_THREADS)
 decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k_cache,
                            const bf16* __restrict__ v_cache, const int* __restrict__ block_table, int max_blocks,
@@ -340,10 +341,10 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
   constexpr int LD = HD + 8;
   constexpr int CH = HD / 8;
   constexpr int KS = HD / 16;
-  constexpr int TILE_ELEMS = DT_KT * LD;                 // one of K or V of one stage
+  constexpr int TILE_ELEMS = KT * LD;                 // one of K or V of one stage
   extern __shared__ __align__(16) unsigned char dt_smem[];
   bf16* Qs = reinterpret_cast<bf16*>(dt_smem);           // [16][LD]
-  bf16* KV = Qs + 16 * LD;                               // [warp][stage][K | V][DT_KT][LD]
+  bf16* KV = Qs + 16 * LD;                               // [warp][stage][K | V][KT][LD]
   float* merge = reinterpret_cast<float*>(dt_smem);      // reused after the loop: [warp][16][HD + 2]
 
   const int split = blockIdx.x, row = blockIdx.z;
@@ -360,10 +361,10 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
   const int n = pos + 1 - lo;
   int len = (n + n_split - 1) / n_split;
-  len = (len + DT_KT - 1) / DT_KT * DT_KT;
+  len = (len + KT - 1) / KT * KT;
   const int k_begin = lo + split * len;
   const int k_end = min(pos + 1, k_begin + len);
-  const int n_tiles = k_end > k_begin ? (k_end - k_begin + DT_KT - 1) / DT_KT : 0;
+  const int n_tiles = k_end > k_begin ? (k_end - k_begin + KT - 1) / KT : 0;
   const int* table = block_table + static_cast<size_t>(row_request[row]) * max_blocks;
   const size_t kv_row = static_cast<size_t>(n_kv_heads) * HD;
 
@@ -372,12 +373,12 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
   // least 16 keys, every 16 keys of a tile lie in one page: one table lookup serves 16 key rows.
   const bool by_halves = (k_begin & 15) == 0 && page_shift >= 4;
   auto load_tile = [&](int i, int stage) {          // this warp's i-th tile: block tile i * DT_WARPS + warp
-    const int key0 = k_begin + (i * DT_WARPS + warp) * DT_KT;
+    const int key0 = k_begin + (i * DT_WARPS + warp) * KT;
     bf16* kd = my + static_cast<size_t>(stage) * 2 * TILE_ELEMS;
     bf16* vd = kd + TILE_ELEMS;
     if (by_halves) {
 #pragma unroll
-      for (int hf = 0; hf < DT_KT / 16; ++hf) {
+      for (int hf = 0; hf < KT / 16; ++hf) {
         const int kb = key0 + hf * 16;
         size_t slot0 = 0;
         if (kb < k_end) slot0 = (static_cast<size_t>(table[kb >> page_shift]) << page_shift) + (kb & page_mask);
@@ -393,7 +394,7 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
       return;
     }
 #pragma unroll
-    for (int c = lane; c < DT_KT * CH; c += 32) {
+    for (int c = lane; c < KT * CH; c += 32) {
       const int r = c / CH, ch = c % CH;
       const int key = key0 + r;
       const bool ok = key < k_end;
@@ -414,7 +415,7 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
     if (s < my_tiles) {
-      if (k_begin + (s * DT_WARPS + warp + 1) * DT_KT <= pos) load_tile(s, s);
+      if (k_begin + (s * DT_WARPS + warp + 1) * KT <= pos) load_tile(s, s);
       else deferred |= 1u << s;
     }
     asm volatile("cp.async.commit_group;\n" ::);
@@ -459,15 +460,15 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
     __syncwarp();
     const bf16* kt = my + static_cast<size_t>(stage) * 2 * TILE_ELEMS;
     const bf16* vt = kt + TILE_ELEMS;
-    const int key0 = k_begin + (i * DT_WARPS + warp) * DT_KT;
+    const int key0 = k_begin + (i * DT_WARPS + warp) * KT;
 
-    float s[DT_KT / 8][4];
+    float s[KT / 8][4];
 #pragma unroll
-    for (int j = 0; j < DT_KT / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f; }
+    for (int j = 0; j < KT / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f; }
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks) {
 #pragma unroll
-      for (int np = 0; np < DT_KT / 16; ++np) {
+      for (int np = 0; np < KT / 16; ++np) {
         uint32_t kb[4];
         const int key = np * 16 + (lane & 7) + (lane >> 4) * 8;
         const int c = ks * 16 + ((lane >> 3) & 1) * 8;
@@ -477,10 +478,10 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
       }
     }
     // raw scores stay in s; the maximum is kept in scaled (base-2) units and the scale is folded into the exponent
-    const bool edge = key0 + DT_KT > k_end;
+    const bool edge = key0 + KT > k_end;
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int j = 0; j < DT_KT / 8; ++j) {
+    for (int j = 0; j < KT / 8; ++j) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         if (edge && key0 + j * 8 + 2 * t + (e & 1) >= k_end) s[j][e] = -INFINITY;
@@ -498,9 +499,9 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
       neg_m[h] = -m_new;
     }
     float ls[2] = {0.0f, 0.0f};
-    uint32_t pf[DT_KT / 16][4];
+    uint32_t pf[KT / 16][4];
 #pragma unroll
-    for (int j = 0; j < DT_KT / 8; ++j) {
+    for (int j = 0; j < KT / 8; ++j) {
       const float p0 = dt_exp2(fmaf(s[j][0], scale_log2, neg_m[0])), p1 = dt_exp2(fmaf(s[j][1], scale_log2, neg_m[0]));
       const float p2 = dt_exp2(fmaf(s[j][2], scale_log2, neg_m[1])), p3 = dt_exp2(fmaf(s[j][3], scale_log2, neg_m[1]));
       ls[0] += p0 + p1;
@@ -520,7 +521,7 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
       o[j][2] *= corr[1]; o[j][3] *= corr[1];
     }
 #pragma unroll
-    for (int kk = 0; kk < DT_KT / 16; ++kk) {
+    for (int kk = 0; kk < KT / 16; ++kk) {
 #pragma unroll
       for (int dp = 0; dp < HD / 16; ++dp) {
         uint32_t vb[4];
@@ -610,12 +611,12 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
   }
 }
 
-template <int HD, int STAGES>
+template <int HD, int STAGES, int KT>
 int launch_decode_tc(const void* q, int q_stride, const void* kc, const void* vc, const int* block_table, int max_blocks,
                      const int* positions, const int* row_request, void* out, int out_stride, float* part, int rows,
                      int n_heads, int n_kv_heads, int page_shift, float scale, int window, int n_split,
                      cudaStream_t stream) {
-  constexpr size_t pipe = static_cast<size_t>(16 + DT_WARPS * STAGES * 2 * DT_KT) * (HD + 8) * sizeof(bf16);
+  constexpr size_t pipe = static_cast<size_t>(16 + DT_WARPS * STAGES * 2 * KT) * (HD + 8) * sizeof(bf16);
   constexpr size_t mrg = static_cast<size_t>(DT_WARPS) * 16 * (HD + 2) * sizeof(float);
   constexpr size_t base = ((pipe > mrg ? pipe : mrg) + 15) & ~static_cast<size_t>(15);
   // Up to 8 splits can merge through the shared memory of a cluster's first block. Measured on B200: that wins
@@ -626,7 +627,7 @@ int launch_decode_tc(const void* q, int q_stride, const void* kc, const void* vc
   const size_t smem = base + (cluster ? static_cast<size_t>(n_split) * 16 * (HD + 2) * sizeof(float) : 0);
   static size_t configured = 0;
   if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(decode_attention_tc_kernel<HD, STAGES>,
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_tc_kernel<HD, STAGES, KT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = smem;
@@ -655,7 +656,7 @@ int launch_decode_tc(const void* q, int q_stride, const void* kc, const void* vc
   cfg.attrs = attr;
   cfg.numAttrs = n_attr;
   int rc = static_cast<int>(cudaLaunchKernelEx(
-      &cfg, decode_attention_tc_kernel<HD, STAGES>, static_cast<const bf16*>(q), q_stride, static_cast<const bf16*>(kc),
+      &cfg, decode_attention_tc_kernel<HD, STAGES, KT>, static_cast<const bf16*>(q), q_stride, static_cast<const bf16*>(kc),
       static_cast<const bf16*>(vc), block_table, max_blocks, positions, row_request, static_cast<bf16*>(out), out_stride,
       part, n_heads, n_kv_heads, page_shift, scale * 1.4426950408889634f, window, n_split, cluster ? 1 : 0,
       static_cast<int>(base)));
@@ -707,20 +708,20 @@ DL_EXPORT int dl_paged_attention_decode_tc(const void* q, int q_stride, const vo
   if ((1 << page_shift) != page_size || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || n_split < 1 || rows > 65535 ||
       (q_stride & 7) || !(scale > 0.0f) || (n_split > 8 && part == nullptr))   // without scratch, up to 8 splits merge in a cluster
     return DL_ERR_UNSUPPORTED;
-#define DL_CASE(H, S)                                                                                                 \
+#define DL_CASE(H, S, T)                                                                                               \
   case H:                                                                                                             \
-    return dl::launch_decode_tc<H, S>(q, q_stride, k_cache, v_cache, block_table, max_blocks, positions, row_request, \
+    return dl::launch_decode_tc<H, S, T>(q, q_stride, k_cache, v_cache, block_table, max_blocks, positions, row_request, \
                                       out, out_stride, part, rows, n_heads, n_kv_heads, page_shift, scale, window,    \
                                       n_split, stream)
   switch (head_dim) {
-    DL_CASE(16, 4);
-    DL_CASE(32, 4);
-    DL_CASE(48, 3);
-    DL_CASE(64, 3);
-    DL_CASE(80, 3);
-    DL_CASE(96, 2);
-    DL_CASE(112, 2);
-    DL_CASE(128, 2);
+    DL_CASE(16, 4, 32);
+    DL_CASE(32, 4, 32);
+    DL_CASE(48, 3, 32);
+    DL_CASE(64, 3, 32);
+    DL_CASE(80, 3, 32);
+    DL_CASE(96, 3, 16);
+    DL_CASE(112, 3, 16);
+    DL_CASE(128, 3, 16);
     default:
       return DL_ERR_UNSUPPORTED;
   }
