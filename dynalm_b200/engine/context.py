@@ -48,8 +48,14 @@ class StepContext:
     num_logit_rows: int
     # every request cut into tiles of at most 128 consecutive rows: int32 [num_q_tiles, 4] =
     # (request, first row of the step, rows, first position)
+    # The tiles of prompt portions come first (those that read the most keys first), then the one-row tiles of
+    # the requests at the head of the step that bring a single token each (`leading_decode_rows` of them, rows
+    # 0 .. leading_decode_rows - 1): a mixer may hand those rows to its decode kernel and only the first
+    # `num_prompt_q_tiles` tiles to its prompt kernel.
     q_tiles: Optional[torch.Tensor] = None
     num_q_tiles: int = 0
+    num_prompt_q_tiles: int = 0
+    leading_decode_rows: int = 0
     h_q_len: List[int] = field(default_factory=list)
     h_pos_start: List[int] = field(default_factory=list)
     h_state_slots: List[int] = field(default_factory=list)

@@ -186,8 +186,13 @@ class BatchBuilder:
                 h[sec.start + r * mb: sec.start + (r + 1) * mb] = self.cache.table_row(g, e.request)
             r0 += n
         q_start[len(entries)] = r0
-        # the tiles that read the most keys first: the attention grid then ends evenly
-        tiles.sort(key=lambda t: -(t[3] + t[2]))
+        # single-token requests at the head of the step (the scheduler puts decode rows first)
+        lead = 0
+        while lead < len(entries) and len(entries[lead].tokens) == 1:
+            lead += 1
+        # prompt tiles first, those that read the most keys first (the attention grid then ends evenly); then the
+        # one-row tiles of the leading decode rows
+        tiles.sort(key=lambda t: (t[0] < lead, -(t[3] + t[2])))
         n_tiles = len(tiles)
         h[off["q_tiles"]][:4 * n_tiles] = np.asarray(tiles, dtype=np.int32).reshape(-1)
         if feedback_src is not None:
@@ -200,7 +205,7 @@ class BatchBuilder:
             num_tokens=total, num_requests=len(entries), token_ids=d["token_ids"], positions=d["positions"],
             row_request=d["row_request"], q_start=d["q_start"], pos_start=d["pos_start"], kv_len=d["kv_len"],
             state_slots=d["state_slots"], logit_rows=d["logit_rows"], num_logit_rows=n_logit,
-            q_tiles=d["q_tiles"], num_q_tiles=n_tiles,
+            q_tiles=d["q_tiles"], num_q_tiles=n_tiles, num_prompt_q_tiles=n_tiles - lead, leading_decode_rows=lead,
             h_q_len=h_q_len, h_pos_start=h_pos_start, h_state_slots=h_slots, block_tables=self.tables,
             decode_only=all(n == 1 for n in h_q_len), max_q_len=max(h_q_len),
             max_kv_len=max(s + n for s, n in zip(h_pos_start, h_q_len)))

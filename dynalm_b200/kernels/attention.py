@@ -35,19 +35,26 @@ def decode_uses_tensor_cores(spec) -> bool:
     return spec.head_dim <= 128
 
 
-def decode_plan(ctx, spec) -> int:
-    """The number of key splits for this step (also part of the CUDA-graph key)."""
+def decode_plan(ctx, spec, rows: int = 0) -> int:
+    """The number of key splits for the step's decode rows (all rows unless `rows` says how many); also part
+    of the CUDA-graph key."""
     span = ctx.max_kv_len if spec.window <= 0 else min(ctx.max_kv_len, spec.window)
     # bucket the span so that a growing context changes the launch shape only now and then
     bucket = 256
     while bucket < span:
         bucket *= 2
-    return decode_splits(ctx.num_tokens, spec.num_heads, spec.num_kv_heads, bucket, decode_uses_tensor_cores(spec))
+    return decode_splits(rows or ctx.num_tokens, spec.num_heads, spec.num_kv_heads, bucket, decode_uses_tensor_cores(spec))
+
+
+MIXED_DECODE_ROWS = 1      # from this many leading decode rows on, a mixed step runs them through the decode kernel
+
+
+def decode_kernel_takes(spec, dtype: torch.dtype, page_size: int) -> bool:
+    return dtype == torch.bfloat16 and page_size & (page_size - 1) == 0 and spec.head_dim % 16 == 0 and spec.head_dim <= 256
 
 
 def use_decode_kernel(ctx, spec, dtype: torch.dtype, page_size: int) -> bool:
-    return (dtype == torch.bfloat16 and ctx.decode_only and page_size & (page_size - 1) == 0
-            and spec.head_dim % 16 == 0 and spec.head_dim <= 256)
+    return ctx.decode_only and decode_kernel_takes(spec, dtype, page_size)
 
 
 def use_prefill_kernel(ctx, spec, qkv: torch.Tensor, page_size: int) -> bool:
@@ -63,25 +70,38 @@ def use_prefill_tcgen05(spec, qkv: torch.Tensor, out: torch.Tensor, page_size: i
             and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0 and qkv.data_ptr() % 16 == 0)
 
 
-def paged_attention(qkv: torch.Tensor, cache, ctx, out: torch.Tensor, spec, runtime) -> bool:
-    """Run the fast kernel for this step if one applies; False means the caller runs the plain one."""
+def _decode_rows(qkv: torch.Tensor, cache, ctx, out: torch.Tensor, spec, runtime, rows: int) -> None:
+    """The split-KV kernel on rows 0 .. rows - 1 (each the newest token of its request)."""
     k_cache, v_cache = cache.arrays
-    if not use_decode_kernel(ctx, spec, qkv.dtype, cache.page_size):
-        if not use_prefill_kernel(ctx, spec, qkv, cache.page_size):
-            return False
-        kernel = (ops.paged_attention_prefill_tcgen05 if use_prefill_tcgen05(spec, qkv, out, cache.page_size)
-                  else ops.paged_attention_prefill)
-        kernel(qkv, k_cache, v_cache, cache.block_table, ctx.q_tiles, ctx.num_q_tiles, out, spec.num_heads,
-               spec.num_kv_heads, spec.head_dim, cache.page_size, float(spec.scale), spec.window)
-        return True
-    rows = qkv.shape[0]
-    n_split = decode_plan(ctx, spec)
+    n_split = decode_plan(ctx, spec, rows)
     scratch = None
     if n_split > 1:
         most_rows = max(runtime.max_requests, rows)
         scratch = runtime.flat(f"attn_split_scratch_{spec.num_heads}x{spec.head_dim}",
                                ops.decode_scratch_floats(most_rows, spec.num_heads, spec.head_dim, MAX_SPLITS))
-    ops.paged_attention_decode(qkv, k_cache, v_cache, cache.block_table, ctx.positions, ctx.row_request, out, scratch,
-                               spec.num_heads, spec.num_kv_heads, spec.head_dim, cache.page_size, float(spec.scale),
-                               spec.window, n_split, tensor_cores=decode_uses_tensor_cores(spec) and qkv.stride(0) % 8 == 0)
+    ops.paged_attention_decode(qkv[:rows], k_cache, v_cache, cache.block_table, ctx.positions[:rows], ctx.row_request[:rows],
+                               out[:rows], scratch, spec.num_heads, spec.num_kv_heads, spec.head_dim, cache.page_size,
+                               float(spec.scale), spec.window, n_split,
+                               tensor_cores=decode_uses_tensor_cores(spec) and qkv.stride(0) % 8 == 0)
+
+
+def paged_attention(qkv: torch.Tensor, cache, ctx, out: torch.Tensor, spec, runtime) -> bool:
+    """Run the fast kernel(s) for this step if they apply; False means the caller runs the plain one."""
+    k_cache, v_cache = cache.arrays
+    if use_decode_kernel(ctx, spec, qkv.dtype, cache.page_size):
+        _decode_rows(qkv, cache, ctx, out, spec, runtime, qkv.shape[0])
+        return True
+    if not use_prefill_kernel(ctx, spec, qkv, cache.page_size):
+        return False
+    n_tiles = ctx.num_q_tiles
+    if ctx.leading_decode_rows >= MIXED_DECODE_ROWS and decode_kernel_takes(spec, qkv.dtype, cache.page_size):
+        # a mixed step: the decode rows at its head go through the split-KV kernel (as a one-row query tile each
+        # of them would occupy a whole block of the prompt kernel), the prompt portions through the flash kernel
+        _decode_rows(qkv, cache, ctx, out, spec, runtime, ctx.leading_decode_rows)
+        n_tiles = ctx.num_prompt_q_tiles
+    if n_tiles > 0:
+        kernel = (ops.paged_attention_prefill_tcgen05 if use_prefill_tcgen05(spec, qkv, out, cache.page_size)
+                  else ops.paged_attention_prefill)
+        kernel(qkv, k_cache, v_cache, cache.block_table, ctx.q_tiles, n_tiles, out, spec.num_heads,
+               spec.num_kv_heads, spec.head_dim, cache.page_size, float(spec.scale), spec.window)
     return True
