@@ -11,7 +11,14 @@ handed out; every request takes a slot whether or not the model has such entries
 
 What is given back when: all pages and the slot when a request is freed (finished, cancelled,
 failed, or preempted for recompute: dynalm/src/runtime/sequence.cpp:44-63); windowed pages after
-`advance`.
+`advance`; pages past a shorter length after `truncate`.
+
+Requests can share pages: `fork` gives a new request the block tables of a live one (every page
+retained once more, as `KvBlockTable::clone`, dynalm/src/kv_cache/kv_cache.cpp:146-151), and
+`reserve` copies a shared page before the request writes into it (copy-on-write, as
+`make_writable`, kv_cache.cpp:153-168; the copy covers every member entry of the group, as
+`copy_block` covers all layers, kv_cache.cpp:77-86). A page goes back to the pool when its last
+holder lets go of it.
 """
 
 from __future__ import annotations
@@ -60,13 +67,29 @@ class PageGroup:
             return 0
         return max(0, next_pos - self.spec.window + 1) // self.page_size
 
+    def shared_blocks(self, req, begin: int, end: int) -> List[int]:
+        """Blocks of `req` that hold positions in [begin, end) on pages other requests hold too."""
+        t = self.tables.get(req)
+        if t is None or end <= begin:
+            return []
+        lo = max(t.first, begin // self.page_size)
+        hi = min(t.length, -(-end // self.page_size))
+        return [b for b in range(lo, hi) if t.pages[b] >= 0 and self.pool.refcount(int(t.pages[b])) > 1]
+
     def blocks_needed(self, req, start_pos: int, total: int) -> int:
-        """New pages that holding `total` tokens needs, the next query being at `start_pos`."""
+        """New pages that holding `total` tokens needs, the next query (and the first position written) being
+        at `start_pos`: pages for new blocks, and copies of shared pages the request is about to write into."""
         t = self.tables.get(req)
         have_first, have_len = (t.first, t.length) if t is not None else (0, 0)
         want_len = -(-total // self.page_size)
         lo = max(have_len, self.first_needed_block(start_pos), have_first)
-        return max(0, want_len - lo)
+        return max(0, want_len - lo) + len(self.shared_blocks(req, start_pos, total))
+
+    def copy_page(self, src: int, dst: int) -> None:
+        """The content of page `src` into page `dst`, for every member entry (layer) of the group."""
+        for arrs in self.arrays.values():
+            for a in arrs:
+                a[dst].copy_(a[src])
 
 
 class CacheManager:
@@ -151,16 +174,23 @@ class CacheManager:
         start = self.tokens.get(req, 0)
         return all(g.blocks_needed(req, start, total) + headroom <= g.pool.num_free for g in self.groups)
 
-    def reserve(self, req, total: int) -> None:
-        """Make sure `req` has pages for positions < total in every group. All or nothing: on
-        ResourceExhausted the pages this call took are given back."""
+    def reserve(self, req, total: int, write_from: Optional[int] = None) -> None:
+        """Make sure `req` has pages of its own for the positions it is about to write, [write_from, total)
+        (`write_from` defaults to the tokens reserved so far), in every group: new pages for new blocks, and a
+        private copy of every page in that range that it shares with another request. All or nothing: on
+        ResourceExhausted the pages this call took are given back and no table has changed."""
         if req not in self.slots:
             raise InvalidArgument(f"request {req!r} is not live")
         if total > self.context:
             raise InvalidArgument(f"request {req!r} would hold {total} tokens, the context is {self.context}")
-        start = self.tokens[req]
+        start = self.tokens[req] if write_from is None else min(int(write_from), self.tokens[req])
         taken = []
+        copies = []      # (group, table, block, shared page, private page)
         try:
+            for g in self.groups:
+                t = g.tables[req]
+                for b in g.shared_blocks(req, start, total):
+                    copies.append((g, t, b, int(t.pages[b]), g.pool.allocate()))
             for g in self.groups:
                 t = g.tables[req]
                 want_len = -(-total // self.page_size)
@@ -179,8 +209,57 @@ class CacheManager:
                 g.pool.release(page)
                 t.pages[b] = -1
                 t.length = min(t.length, b)
+            for g, t, b, shared, private in copies:
+                g.pool.release(private)
             raise
+        for g, t, b, shared, private in copies:
+            g.copy_page(shared, private)
+            t.pages[b] = private
+            g.pool.release(shared)
         self.tokens[req] = max(self.tokens[req], total)
+
+    def fork(self, parent, child, tokens: Optional[int] = None) -> int:
+        """A new request `child` that holds what `parent` holds: the same pages in every group (each held once
+        more; a later write copies first, see `reserve`) and a copy of the parent's state rows in a slot of its
+        own. `tokens`: how many of the parent's tokens the child starts from (the parent may have pages reserved
+        beyond what it has computed); default all. Returns the child's slot."""
+        if parent not in self.slots:
+            raise InvalidArgument(f"request {parent!r} is not live")
+        slot = self.add_request(child)
+        for g in self.groups:
+            src, dst = g.tables[parent], g.tables[child]
+            dst.pages[:] = src.pages
+            dst.first, dst.length = src.first, src.length
+            for b in range(src.first, src.length):
+                if src.pages[b] >= 0:
+                    g.pool.retain(int(src.pages[b]))
+        self.tokens[child] = self.tokens[parent]
+        for arr in self.state_arrays.values():
+            arr[slot].copy_(arr[self.slots[parent]])
+        if tokens is not None and tokens < self.tokens[child]:
+            self.truncate(child, tokens)
+        return slot
+
+    def truncate(self, req, total: int) -> int:
+        """`req` keeps its first `total` tokens only: pages wholly past them are given back
+        (`KvBlockTable::truncate`, dynalm/src/kv_cache/kv_cache.cpp:137-144). Returns the pages let go."""
+        if req not in self.slots:
+            raise InvalidArgument(f"request {req!r} is not live")
+        if total < 0 or total > self.tokens[req]:
+            raise InvalidArgument(f"request {req!r} holds {self.tokens[req]} tokens, it cannot be cut to {total}")
+        n = 0
+        keep = -(-total // self.page_size)
+        for g in self.groups:
+            t = g.tables[req]
+            for b in range(max(keep, t.first), t.length):
+                if t.pages[b] >= 0:
+                    g.pool.release(int(t.pages[b]))
+                    t.pages[b] = -1
+                    n += 1
+            t.length = max(min(t.length, keep), min(t.first, keep))
+            t.first = min(t.first, t.length)
+        self.tokens[req] = total
+        return n
 
     def advance(self, req, computed: int) -> int:
         """`req` has now computed `computed` tokens; give back pages that every window has passed.
@@ -245,10 +324,10 @@ class CacheManager:
         return n
 
     def check(self) -> None:
-        """No page lost, held twice or freed twice; no slot held twice."""
+        """No page lost or freed twice, every page counted once per table that names it; no slot held twice."""
         for g in self.groups:
             g.pool.check()
-            owners: Dict[int, Hashable] = {}
+            holders: Dict[int, int] = {}
             for req, t in g.tables.items():
                 for b in range(g.max_blocks):
                     p = int(t.pages[b])
@@ -256,15 +335,16 @@ class CacheManager:
                     if p >= 0:
                         if not inside:
                             raise AssertionError(f"request {req!r} keeps page {p} outside its table range")
-                        if p in owners:
-                            raise AssertionError(f"page {p} is held by {owners[p]!r} and {req!r}")
                         if not g.pool.is_held(p):
                             raise AssertionError(f"page {p} of {req!r} is on the free list")
-                        owners[p] = req
+                        holders[p] = holders.get(p, 0) + 1
                     elif inside and g.spec.window <= 0:
                         raise AssertionError(f"request {req!r} lacks a page for block {b}")
-            if len(owners) != g.pool.num_held:
-                raise AssertionError(f"{g.pool.num_held} pages are held but tables name {len(owners)}")
+            for p, n in holders.items():
+                if g.pool.refcount(p) != n:
+                    raise AssertionError(f"page {p} is named by {n} tables but counted {g.pool.refcount(p)} times")
+            if len(holders) != g.pool.num_held:
+                raise AssertionError(f"{g.pool.num_held} pages are held but tables name {len(holders)}")
         used = sorted(self.slots.values())
         if len(set(used)) != len(used) or set(used) & set(self._free_slots):
             raise AssertionError("a state slot is held twice")

@@ -1,9 +1,11 @@
-"""A pool of cache pages: a LIFO free list with an owner check.
+"""A pool of cache pages: a LIFO free list with reference counts.
 
 The reference's `KvBlockPool` (dynalm/src/kv_cache/kv_cache.cpp:13-86) hands out the lowest ids
-first and reuses the most recently freed block first; so does this one. It is owned by one thread
-(the scheduler's), so it takes no lock. Holding the state of every page lets a double free or a
-free of a page that was never handed out fail at once instead of corrupting the list.
+first, reuses the most recently freed block first, and counts references so that block tables can
+share blocks (`retain` / `release`, a block is free again at count 0: kv_cache.cpp:62-75); so does
+this one. It is owned by one thread (the scheduler's), so it takes no lock and its counts are
+plain integers. Knowing the count of every page lets a double free or a free of a page that was
+never handed out fail at once instead of corrupting the list.
 """
 
 from __future__ import annotations
@@ -19,7 +21,7 @@ class PagePool:
             raise InvalidArgument("a page pool needs at least one page")
         self.num_pages = int(num_pages)
         self._free: List[int] = list(range(self.num_pages - 1, -1, -1))   # pop() gives the lowest id first
-        self._held = [False] * self.num_pages
+        self._refs = [0] * self.num_pages
 
     @property
     def num_free(self) -> int:
@@ -30,22 +32,39 @@ class PagePool:
         return self.num_pages - len(self._free)
 
     def allocate(self) -> int:
+        """A free page, held once."""
         if not self._free:
             raise ResourceExhausted("KV cache is full")
         page = self._free.pop()
-        self._held[page] = True
+        self._refs[page] = 1
         return page
 
-    def release(self, page: int) -> None:
+    def _known(self, page: int) -> None:
         if not 0 <= page < self.num_pages:
             raise InvalidArgument(f"page {page} is not of this pool")
-        if not self._held[page]:
+
+    def retain(self, page: int) -> None:
+        """One more holder of a page that is held already."""
+        self._known(page)
+        if self._refs[page] <= 0:
+            raise InvalidArgument(f"page {page} is not held: it cannot be shared")
+        self._refs[page] += 1
+
+    def release(self, page: int) -> None:
+        """One holder less; the page is free again when nobody holds it."""
+        self._known(page)
+        if self._refs[page] <= 0:
             raise InvalidArgument(f"page {page} is freed twice")
-        self._held[page] = False
-        self._free.append(page)
+        self._refs[page] -= 1
+        if self._refs[page] == 0:
+            self._free.append(page)
+
+    def refcount(self, page: int) -> int:
+        self._known(page)
+        return self._refs[page]
 
     def is_held(self, page: int) -> bool:
-        return self._held[page]
+        return self._refs[page] > 0
 
     def check(self) -> None:
         """Every page is either on the free list once or held, never both."""
@@ -53,9 +72,9 @@ class PagePool:
         for p in self._free:
             if seen[p]:
                 raise AssertionError(f"page {p} is on the free list twice")
-            if self._held[p]:
+            if self._refs[p] != 0:
                 raise AssertionError(f"page {p} is free and held")
             seen[p] = True
         for p in range(self.num_pages):
-            if not seen[p] and not self._held[p]:
+            if not seen[p] and self._refs[p] <= 0:
                 raise AssertionError(f"page {p} is lost: neither free nor held")

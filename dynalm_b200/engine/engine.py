@@ -121,6 +121,10 @@ class Engine:
     def end(self, request) -> None:
         self.step_fn.end(request)
 
+    def fork(self, parent, child) -> None:
+        """A new request that goes on from where `parent` stands, sharing its cache pages (see StepFunction.fork)."""
+        self.step_fn.fork(parent, child)
+
     def stats(self) -> dict:
         s = self.scheduler.stats
         return {"scheduler": dict(vars(s)), "free_pages": self.built.cache.free_pages,

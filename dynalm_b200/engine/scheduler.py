@@ -342,7 +342,7 @@ class Scheduler:
                 if n <= 0:
                     continue
                 try:
-                    cache.reserve(seq.id, seq.num_computed + n)
+                    cache.reserve(seq.id, seq.num_computed + n, write_from=seq.num_computed)
                 except ResourceExhausted:
                     if attempt < 64 and self._preempt_one(seq, preempted):
                         restart = True
@@ -376,7 +376,7 @@ class Scheduler:
                 if seq.generated + 1 >= seq.req.max_new_tokens:
                     continue                                  # `prev` gives it its last token
                 start = b.start + len(b.tokens)
-                self.ex.cache.reserve(seq.id, start + 1)
+                self.ex.cache.reserve(seq.id, start + 1, write_from=start)
                 nxt.append(BatchItem(seq, start, [0], sample=True))
         except ResourceExhausted:
             return None                                       # the ordinary path will preempt

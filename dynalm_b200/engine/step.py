@@ -111,6 +111,14 @@ class BatchBuilder:
         self.cache.free_request(request)
         del self.computed[request]
 
+    def fork(self, parent, child) -> None:
+        """`child` starts as a copy of `parent`: it shares the parent's pages (copied when either writes into one)
+        and goes on from the parent's computed tokens."""
+        if parent not in self.computed:
+            raise InvalidArgument(f"request {parent!r} is not live")
+        self.cache.fork(parent, child, tokens=self.computed[parent])
+        self.computed[child] = self.computed[parent]
+
     def build(self, entries: Sequence[StepEntry], reserve: bool = True,
               feedback_src: Optional[Sequence[int]] = None) -> StepContext:
         """Check the batch, reserve pages (unless the caller already has), flatten it and upload it.
@@ -141,7 +149,7 @@ class BatchBuilder:
                     raise InvalidArgument(f"request {e.request!r} is not live")
                 self.begin(e.request)
             if reserve:
-                self.cache.reserve(e.request, self.computed[e.request] + len(e.tokens))
+                self.cache.reserve(e.request, self.computed[e.request] + len(e.tokens), write_from=self.computed[e.request])
             elif self.cache.tokens[e.request] < self.computed[e.request] + len(e.tokens):
                 raise InvalidArgument(f"request {e.request!r} has no pages reserved for its tokens")
 
@@ -252,6 +260,12 @@ class StepFunction:
     def end(self, request) -> None:
         """The request is finished (or dropped for recompute): its pages and slot are given back."""
         self.batcher.end(request)
+
+    def fork(self, parent, child) -> None:
+        """A new request that continues from where `parent` stands now, sharing the parent's cache pages; whichever
+        of the two writes into a shared page first gets a copy of it (the reference's fork and copy-on-write,
+        dynalm/src/kv_cache/kv_cache.cpp:146-168)."""
+        self.batcher.fork(parent, child)
 
     def live(self) -> List[Hashable]:
         return list(self.computed)

@@ -153,3 +153,148 @@ def test_random_orders(seed):
         m.free_request(r)
     m.check()
     assert all(g.pool.num_free == g.pool.num_pages for g in m.groups) and m.free_slots == 5
+
+
+def test_pool_reference_counts():
+    p = PagePool(3)
+    a = p.allocate()
+    p.retain(a)
+    assert p.refcount(a) == 2
+    p.release(a)
+    assert p.is_held(a) and p.num_free == 2          # one holder is left
+    p.release(a)
+    assert not p.is_held(a) and p.num_free == 3
+    with pytest.raises(InvalidArgument, match="freed twice"):
+        p.release(a)
+    with pytest.raises(InvalidArgument, match="not held"):
+        p.retain(a)
+    p.check()
+
+
+def test_fork_shares_pages_and_a_write_copies_first():
+    """A forked request holds its parent's pages; whoever writes into a shared page gets a copy with the same
+    content in every member entry, the other keeps the original; full pages stay shared until both are gone."""
+    m = CacheManager([FULL, FULL, STATE], 16, 256, 4, 256, device="cpu", dtype=torch.float32)
+    g = m.groups[0]
+    m.add_request("a")
+    m.reserve("a", 40)                                   # blocks 0, 1 full, block 2 half full
+    pages_a = m.table_row(g, "a")[:3].tolist()
+    for entry in g.members:
+        for t, arr in enumerate(g.arrays[entry]):
+            for b, p in enumerate(pages_a):
+                arr[p] = 100 * entry + 10 * t + b
+    m.state_arrays[2][m.slot_of("a")] = 7.0
+    free = m.free_pages
+    m.fork("a", "b")
+    assert m.free_pages == free and m.table_row(g, "b")[:3].tolist() == pages_a
+    assert all(g.pool.refcount(p) == 2 for p in pages_a)
+    assert torch.all(m.state_arrays[2][m.slot_of("b")] == 7.0) and m.slot_of("b") != m.slot_of("a")
+    m.check()
+    # b goes on from token 40: block 2 is shared and about to be written -> copied; block 3 is new
+    assert m.pages_needed("b", 50, start_pos=40) == 2
+    m.reserve("b", 50, write_from=40)
+    pages_b = m.table_row(g, "b")[:4].tolist()
+    assert pages_b[:2] == pages_a[:2] and pages_b[2] != pages_a[2] and pages_b[3] >= 0
+    assert g.pool.refcount(pages_a[2]) == 1 and g.pool.refcount(pages_b[2]) == 1 and g.pool.refcount(pages_a[0]) == 2
+    for entry in g.members:
+        for t, arr in enumerate(g.arrays[entry]):
+            assert torch.all(arr[pages_b[2]] == 100 * entry + 10 * t + 2)     # the copy carries the content
+    # a writes too: its block 2 is its own again, nothing is copied
+    free = m.free_pages
+    m.reserve("a", 41, write_from=40)
+    assert m.free_pages == free and m.table_row(g, "a")[:3].tolist() == pages_a
+    m.check()
+    m.free_request("a")
+    assert g.pool.refcount(pages_a[0]) == 1 and g.pool.is_held(pages_a[0]) and not g.pool.is_held(pages_a[2])
+    m.free_request("b")
+    m.check()
+    assert m.free_pages == m.num_pages
+
+
+def test_copy_on_write_is_all_or_nothing_when_pages_run_out():
+    m = manager([FULL], tokens=64, requests=3, context=64)          # 4 pages
+    m.add_request("a")
+    m.reserve("a", 40)                                              # 3 pages
+    m.fork("a", "b")
+    m.add_request("c")
+    m.reserve("c", 16)                                              # the last page
+    before = m.table_row(m.groups[0], "b").copy()
+    with pytest.raises(ResourceExhausted):
+        m.reserve("b", 41, write_from=40)                           # needs a copy of block 2: no page left
+    assert (m.table_row(m.groups[0], "b") == before).all() and m.free_pages == 0
+    m.check()
+
+
+def test_fork_from_fewer_tokens_and_truncate():
+    m = manager([FULL, WIN])
+    m.add_request("a")
+    m.reserve("a", 100)                                             # the parent has reserved ahead of what it computed
+    m.fork("a", "b", tokens=70)
+    assert m.tokens["b"] == 70 and m.groups[0].tables["b"].length == 5
+    m.check()
+    assert m.truncate("a", 33) > 0
+    assert m.tokens["a"] == 33 and m.groups[0].tables["a"].length == 3
+    with pytest.raises(InvalidArgument, match="cannot be cut"):
+        m.truncate("a", 34)
+    m.reserve("a", 48, write_from=33)                               # block 2 is shared with b: copied
+    m.check()
+    m.free_request("a")
+    m.free_request("b")
+    m.check()
+    assert m.free_pages == m.num_pages
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders_with_forks(seed):
+    """As test_random_orders, with forks and truncations among the operations: every page is counted once per
+    table that names it after every operation, and everything is free at the end."""
+    rng = random.Random(100 + seed)
+    specs = [FULL, WIN, None, FULL] if seed % 2 else [FULL, FULL]
+    m = manager(specs, page=16, tokens=rng.choice([96, 160, 512]), requests=6, context=400)
+    live = {}
+    nxt = 0
+    for _ in range(800):
+        op = rng.random()
+        if op < 0.10 and len(live) < 6:
+            m.add_request(nxt)
+            live[nxt] = 0
+            nxt += 1
+        elif op < 0.20 and live and len(live) < 6:
+            parent = rng.choice(list(live))
+            m.fork(parent, nxt, tokens=live[parent])
+            live[nxt] = live[parent]
+            nxt += 1
+        elif op < 0.27 and live:
+            r = rng.choice(list(live))
+            # a windowed group has given early pages back: only cut where every group still has its pages
+            if all(g.spec.window <= 0 for g in m.groups):
+                live[r] = rng.randint(0, live[r])
+                m.truncate(r, live[r])
+        elif op < 0.88 and live:
+            r = rng.choice(list(live))
+            n = rng.choice([1, 1, 1, 2, 5, 16, 33])
+            if live[r] + n > 400:
+                continue
+            free_before = [g.pool.num_free for g in m.groups]
+            tables_before = [g.tables[r].pages.copy() for g in m.groups]
+            try:
+                m.reserve(r, live[r] + n, write_from=live[r])
+                for g in m.groups:                     # what it is about to write is its own
+                    assert not g.shared_blocks(r, live[r], live[r] + n)
+                live[r] += n
+                m.advance(r, live[r])
+            except ResourceExhausted:
+                assert [g.pool.num_free for g in m.groups] == free_before
+                assert all((g.tables[r].pages == t).all() for g, t in zip(m.groups, tables_before))
+                victim = rng.choice(list(live))
+                m.free_request(victim)
+                del live[victim]
+        elif live:
+            r = rng.choice(list(live))
+            m.free_request(r)
+            del live[r]
+        m.check()
+    for r in list(live):
+        m.free_request(r)
+    m.check()
+    assert all(g.pool.num_free == g.pool.num_pages for g in m.groups) and m.free_slots == 6

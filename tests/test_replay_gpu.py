@@ -94,3 +94,57 @@ def test_first_tokens_of_a_sequence(name, dtype, tiny_folders):
                        ("together", plan_mixed(reqs, seed=1, decode_tail=1, sizes=(2, 3)))):
         built = _built(tiny_folders[name], dtype, 256, 64)
         compare(plan, run_plan_in_process(built.step_fn, plan), plain, *TOL[dtype], f"first/{name}/{dtype}/{what}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["b", "e"])
+def test_fork_and_copy_on_write_match_from_scratch(name, dtype, tiny_folders):
+    """A prompt that ends in the middle of a page is forked twice; the three requests go on with different tokens
+    (one by one, in portions of three, and in one piece) in the same steps. Each must give the logits of its own
+    whole sequence computed from scratch: the shared half page is copied before the first write into it."""
+    from dynalm_b200.engine import StepEntry
+    cfg = TINY[name][0]
+    rng = np.random.RandomState(31)
+    base = [int(t) for t in rng.randint(0, cfg["vocab_size"], 41)]
+    tails = {"p": [int(t) for t in rng.randint(0, cfg["vocab_size"], 30)],
+             "q": [int(t) for t in rng.randint(0, cfg["vocab_size"], 27)],
+             "r": [int(t) for t in rng.randint(0, cfg["vocab_size"], 12)]}
+    model = PlainLlama(tiny_folders[name])
+    plain = {r: model.logits(base + t) for r, t in tails.items()}
+    built = _built(tiny_folders[name], dtype, 256, 64)
+    fn = built.step_fn
+    tol = TOL[dtype]
+
+    def close(got, want, what):
+        err = np.abs(got - want).max()
+        assert err <= tol[0] + tol[1] * np.abs(want).max(), f"{what}: {err}"
+
+    got = fn.step([StepEntry("p", base, [40])]).float().cpu().numpy()
+    close(got[0], plain["p"][40], "prompt")
+    free_before = built.cache.free_pages
+    fn.fork("p", "q")
+    fn.fork("p", "r")
+    assert built.cache.free_pages == free_before            # a fork takes no page
+    built.cache.check()
+    done = {"p": 0, "q": 0, "r": 0}
+    portion = {"p": 1, "q": 3, "r": 12}
+    while any(done[r] < len(tails[r]) for r in tails):
+        entries, places = [], []
+        for r in ("q", "p", "r"):
+            n = min(portion[r], len(tails[r]) - done[r])
+            if n <= 0:
+                continue
+            entries.append(StepEntry(r, tails[r][done[r]:done[r] + n], list(range(n))))
+            places.append((r, done[r], n))
+            done[r] += n
+        got = fn.step(entries).float().cpu().numpy()
+        row = 0
+        for r, start, n in places:
+            for i in range(n):
+                close(got[row], plain[r][41 + start + i], f"{r} token {start + i}")
+                row += 1
+        built.cache.check()
+    for r in tails:
+        fn.end(r)
+    built.cache.check()
+    assert built.cache.free_pages == built.cache.num_pages
