@@ -102,10 +102,11 @@ class Engine:
         return out[0] if single else out
 
     def stream(self, prompt: Sequence[int], max_tokens: int = 128, sampling: Optional[SamplingParams] = None,
-               stop_token_ids: Sequence[int] = ()) -> Iterator[Event]:
-        """Events of one request as they come (the counterpart of RequestStream::next)."""
+               stop_token_ids: Sequence[int] = (), priority: int = 0, timeout_ms: float = 0.0) -> Iterator[Event]:
+        """Events of one request as they come (the counterpart of RequestStream::next; priority and timeout_ms
+        as GenerateParams, dynalm/src/runtime/engine.h:176-225)."""
         rid = self.scheduler.submit(Request(list(prompt), max_tokens, sampling or SamplingParams(),
-                                            tuple(stop_token_ids)))
+                                            tuple(stop_token_ids), priority=priority, timeout_ms=timeout_ms))
         done = False
         while not done and not self.scheduler.idle:
             for ev in self.scheduler.step():

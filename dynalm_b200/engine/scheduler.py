@@ -52,6 +52,13 @@ class SchedulerConfig:
     max_prefill_chunk: int = 128          # per request per step; 0 = up to the budget
     max_batch_tokens: int = 512
     context_length: int = 1 << 24         # prompt + max_new_tokens may not exceed it
+    # Decode-protected prefill (dynalm/src/scheduler/scheduler.h:138-150): in steps that also carry decode rows the
+    # prompt rows are capped by a budget that halves (down to protected_prefill_min) after a mixed step that took
+    # longer than decode_latency_target x the recent decode-only step time, and doubles (up to prefill_token_budget)
+    # after one that took less than half of that. Steps without decode rows keep the full budget.
+    decode_protect: bool = True
+    protected_prefill_min: int = 32
+    decode_latency_target: float = 6.0
 
     def clamp(self) -> None:
         # both budgets must fit one forward pass (scheduler.cpp:91-96)
@@ -69,6 +76,7 @@ class Request:
     sampling: SamplingParams = field(default_factory=SamplingParams)
     stop_token_ids: Sequence[int] = ()     # end-of-generation ids; generation stops after one is sampled
     priority: int = 0
+    timeout_ms: float = 0.0                # > 0: the request fails once it has been in the scheduler this long
     on_event: Optional[Callable[["Event"], None]] = None
 
 
@@ -103,6 +111,7 @@ class SequenceState:
         self.last_step = 0
         self.sampler: Optional[Sampler] = None      # made once the request has passed validation
         self.cancel_requested = False
+        self.deadline: float = 0.0                  # on the scheduler's clock; 0 = none
 
     @property
     def pending(self) -> int:
@@ -173,11 +182,15 @@ class SchedulerStats:
     forward_decode_only_ms: float = 0.0
     forward_prefill_only_ms: float = 0.0
     forward_mixed_ms: float = 0.0
+    timed_out: int = 0
+    mixed_prefill_budget: int = 0         # the prompt rows a step with decode rows may carry now
 
 
 class Scheduler:
-    def __init__(self, executor: Executor, config: SchedulerConfig = None, keep_trace: bool = False):
+    def __init__(self, executor: Executor, config: SchedulerConfig = None, keep_trace: bool = False,
+                 clock: Callable[[], float] = time.monotonic):
         self.ex = executor
+        self.clock = clock                 # seconds; deadlines are measured on it
         self.cfg = config or SchedulerConfig()
         self.cfg.max_batch_tokens = min(self.cfg.max_batch_tokens, executor.max_tokens)
         self.cfg.max_running = min(self.cfg.max_running, executor.cache.max_requests)
@@ -195,6 +208,9 @@ class Scheduler:
         self._last_rows = (0, 0)
         self._inflight = None          # (batch, what executor.launch returned, launch time): issued, not yet collected
         self._last_done = 0.0
+        self._decode_step_ema_ms = 0.0     # recent decode-only step time (0.8 old + 0.2 new, scheduler.cpp:601)
+        self._mixed_prefill_budget = self.cfg.prefill_token_budget
+        self.stats.mixed_prefill_budget = self._mixed_prefill_budget
         self.lookahead = hasattr(executor, "launch") and hasattr(executor, "collect")
 
     # ---- submission ----------------------------------------------------------------------------------
@@ -203,6 +219,8 @@ class Scheduler:
         self._next_id += 1
         self._arrivals += 1
         seq = SequenceState(rid, req, self._arrivals)
+        if req.timeout_ms > 0:
+            seq.deadline = self.clock() + req.timeout_ms / 1000.0
         self.by_id[rid] = seq
         self.incoming.append(seq)
         if req.on_event is not None:
@@ -256,6 +274,27 @@ class Scheduler:
         if self.incoming:
             self.incoming.clear()
             self.waiting = deque(sorted(self.waiting, key=lambda s: (-s.req.priority, s.arrival)))
+
+    def _expire_deadlines(self, events: List[Event]) -> None:
+        """Requests past their deadline fail (dynalm/src/scheduler/scheduler.cpp:293-309): running ones are retired
+        with the others of this step, waiting ones leave the queue here."""
+        now = self.clock()
+        for seq in self.running:
+            if not seq.terminal and seq.deadline and now > seq.deadline:
+                seq.status, seq.error = ERROR, "request timed out"
+                self.stats.failed += 1
+                self.stats.timed_out += 1
+                events.append(self._final_event(seq, None))
+        if any(seq.deadline and now > seq.deadline for seq in self.waiting):
+            keep = deque()
+            for seq in self.waiting:
+                if seq.deadline and now > seq.deadline:
+                    self._fail(seq, "request timed out while queued", events)
+                    self.stats.timed_out += 1
+                    self.by_id.pop(seq.id, None)
+                else:
+                    keep.append(seq)
+            self.waiting = keep
 
     def _retire(self, events: List[Event]) -> None:
         keep = []
@@ -332,10 +371,14 @@ class Scheduler:
             order = sorted((s for s in self.running if not s.terminal and s.pending > 0),
                            key=lambda s: (0, s.last_step, s.admit_order) if is_decode(s)
                            else (1, -s.req.priority, s.admit_order))
+            # beside decode rows the prompt rows are capped by the adaptive budget
+            any_decode = any(is_decode(s) for s in order)
+            prefill_budget = (min(cfg.prefill_token_budget, self._mixed_prefill_budget)
+                              if cfg.decode_protect and any_decode else cfg.prefill_token_budget)
             for seq in order:
                 decode = is_decode(seq)
                 used = decode_rows if decode else prefill_rows
-                budget = cfg.decode_token_budget if decode else cfg.prefill_token_budget
+                budget = cfg.decode_token_budget if decode else prefill_budget
                 n = min(seq.pending, budget - used)
                 if not decode and cfg.max_prefill_chunk > 0:
                     n = min(n, cfg.max_prefill_chunk)
@@ -366,6 +409,8 @@ class Scheduler:
         if self.incoming or self.waiting or len(prev) != len(self.running):
             return None
         if any(s.cancel_requested or s.terminal for s in self.running):
+            return None
+        if any(s.deadline for s in self.running) and any(s.deadline and self.clock() > s.deadline for s in self.running):
             return None
         if sum(1 for b in prev if b.seq.generated + 1 < b.seq.req.max_new_tokens) > self.cfg.decode_token_budget:
             return None
@@ -422,6 +467,7 @@ class Scheduler:
                 return self._dispatch(events)
             # nothing was issued ahead: go on with an ordinary iteration in this same call
         self._drain_incoming(events)
+        self._expire_deadlines(events)
         self._retire(events)
         self._admit(admitted)
         if self.running:
@@ -463,12 +509,22 @@ class Scheduler:
         if n_prefill == 0:
             self.stats.steps_decode_only += 1
             self.stats.forward_decode_only_ms += ms
+            self._decode_step_ema_ms = ms if self._decode_step_ema_ms == 0 else 0.8 * self._decode_step_ema_ms + 0.2 * ms
         elif n_decode == 0:
             self.stats.steps_prefill_only += 1
             self.stats.forward_prefill_only_ms += ms
         else:
             self.stats.steps_mixed += 1
             self.stats.forward_mixed_ms += ms
+            if self.cfg.decode_protect and self._decode_step_ema_ms > 0:
+                # steer the next mixed step's share of prompt rows toward the target multiple of a decode-only step
+                target = self.cfg.decode_latency_target * self._decode_step_ema_ms
+                if ms > target:
+                    self._mixed_prefill_budget = max(min(self.cfg.protected_prefill_min, self.cfg.prefill_token_budget),
+                                                     self._mixed_prefill_budget // 2)
+                elif ms < 0.5 * target:
+                    self._mixed_prefill_budget = min(self.cfg.prefill_token_budget, self._mixed_prefill_budget * 2)
+                self.stats.mixed_prefill_budget = self._mixed_prefill_budget
         self.stats.tokens_decoded += n_decode
         self.stats.tokens_prefilled += n_prefill
 
@@ -501,5 +557,7 @@ class Scheduler:
             for b in batch:
                 self._fail(b.seq, f"forward failed: {e}", events)
             return
-        self._account(batch, (time.perf_counter() - t0) * 1e3)
+        # an executor may say how long its step took (a simulated one in tests); else the wall clock does
+        ms = getattr(self.ex, "last_step_ms", None)
+        self._account(batch, (time.perf_counter() - t0) * 1e3 if ms is None else ms)
         self._finish_batch(batch, sampled, events)

@@ -300,3 +300,69 @@ def test_one_step_ahead_with_arrivals_cancels_and_few_pages():
             assert got[0][i] == roomy[0][i] and got[1][i] == FINISHED
         assert got[1][2] == CANCELLED and got[0][2] == roomy[0][2][:len(got[0][2])]
     assert ahead_tight[2] > 0
+
+
+def test_deadlines_fail_running_and_queued_requests():
+    """A request past its timeout fails with the reference's messages, whether it is running or still queued
+    (dynalm/src/scheduler/scheduler.cpp:293-309); its pages come back; the others go on."""
+    now = [0.0]
+    ex = FakeExecutor(kv_tokens=64, max_requests=4)                      # room for one 40-token request at a time
+    s = Scheduler(ex, SchedulerConfig(max_running=4, prefill_token_budget=16, max_prefill_chunk=16, max_batch_tokens=64),
+                  clock=lambda: now[0])
+    a = s.submit(Request(list(range(40)), max_new_tokens=8, timeout_ms=50))
+    b = s.submit(Request(list(range(40)), max_new_tokens=8, timeout_ms=20))   # waits behind a: no pages for both
+    c = s.submit(Request(list(range(40)), max_new_tokens=2))
+    events = s.step()
+    assert [q.id for q in s.running] == [a] and len(s.waiting) == 2
+    now[0] = 0.030                                                        # b's deadline passes in the queue
+    events = s.step()
+    failed = [e for e in events if e.finished]
+    assert [(e.request_id, e.status, e.error) for e in failed] == [(b, "error", "request timed out while queued")]
+    now[0] = 0.060                                                        # a's passes while it runs
+    events = s.step()
+    failed = [e for e in events if e.finished]
+    assert [(e.request_id, e.status, e.error) for e in failed] == [(a, "error", "request timed out")]
+    assert a not in ex.live
+    events = run_all(s)
+    done = [e for e in events if e.finished]
+    assert [(e.request_id, e.status, e.completion_tokens) for e in done] == [(c, "finished", 2)]
+    assert s.stats.timed_out == 2 and ex.cache.free_pages == ex.cache.num_pages
+
+
+def test_decode_protected_prefill_budget_halves_and_doubles():
+    """Beside decode rows the prompt rows follow the adaptive budget: it halves after a mixed step that took more than
+    decode_latency_target x a decode-only step, down to protected_prefill_min, and doubles again after fast ones;
+    steps without decode rows keep the whole budget (dynalm/src/scheduler/scheduler.h:138-150)."""
+    ex = FakeExecutor(kv_tokens=8192, max_requests=8, max_tokens=512, context=8192)
+    ms_per_prompt_row = [1.0]
+
+    real_run = ex.run
+
+    def run(batch):
+        rows = sum(len(b.tokens) for b in batch if len(b.tokens) > 1)
+        ex.last_step_ms = 1.0 + ms_per_prompt_row[0] * rows            # a decode-only step costs 1 ms
+        return real_run(batch)
+    ex.run = run
+    cfg = SchedulerConfig(max_running=8, decode_token_budget=8, prefill_token_budget=256, max_prefill_chunk=0,
+                          max_batch_tokens=512, protected_prefill_min=32, decode_latency_target=6.0)
+    s = Scheduler(ex, cfg)
+    s.submit(Request(list(range(10)), max_new_tokens=400))
+    for _ in range(4):
+        s.step()                                                         # prompt, then decode-only steps: 1 ms each
+    assert s.stats.steps_decode_only >= 2
+    s.submit(Request([t % 1000 for t in range(3000)], max_new_tokens=4))
+    budgets, prompt_rows = [], []
+    for _ in range(6):
+        s.step()
+        prompt_rows.append(sum(n for _, _, n, _ in ex.batches[-1] if n > 1))
+        budgets.append(s.stats.mixed_prefill_budget)
+    # 256 prompt rows cost 257 ms > 6 ms: the budget halves step after step down to its floor
+    assert prompt_rows[:5] == [256, 128, 64, 32, 32] and budgets[:4] == [128, 64, 32, 32]
+    ms_per_prompt_row[0] = 0.01                                          # prompt rows become cheap: 1.32 ms < 3 ms
+    for _ in range(4):
+        s.step()
+        budgets.append(s.stats.mixed_prefill_budget)
+    assert budgets[-4:] == [64, 128, 256, 256]
+    cfg.decode_protect = False
+    s.step()
+    assert sum(n for _, _, n, _ in ex.batches[-1] if n > 1) == 256
