@@ -46,6 +46,9 @@ _SIGNATURES = {
     "gemm_tcgen05": {
         "dl_gemm_tcgen05": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
         "dl_gemm_tcgen05_qkv_rope": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P, _F, _I, _I, _I, _I, _P, _P]},
+    "gemm_tcgen05_cluster": {
+        "dl_gemm_tcgen05_cluster": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
+        "dl_gemm_tcgen05_cluster_qkv_rope": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P, _F, _I, _I, _I, _I, _P, _P]},
     "gemm_simt": {"dl_gemm_simt": [_I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _P]},
     "sampling": {
         "dl_argmax": [_P, _I, _I, _I, _P, _P, _P],
@@ -325,7 +328,9 @@ def gemm_qkv_rope(x: torch.Tensor, w_qkv: torch.Tensor, q_out: torch.Tensor, pos
             or row_request.dtype != torch.int32:
         raise InvalidArgument("gemm_qkv_rope: positions, row_request and block_table must be int32")
     if not few:
-        _check(_fn("gemm_tcgen05", "dl_gemm_tcgen05_qkv_rope")(
+        library, name = (("gemm_tcgen05_cluster", "dl_gemm_tcgen05_cluster_qkv_rope") if tcgen05_pairs(M, w_qkv.shape[0])
+                         else ("gemm_tcgen05", "dl_gemm_tcgen05_qkv_rope"))
+        _check(_fn(library, name)(
             _p(x), x.stride(0), _p(w_qkv), _p(q_out), q_out.stride(0), M, K, _p(positions), _p(row_request),
             _p(block_table), block_table.stride(0), _p(k_cache), _p(v_cache), _p(inv_freq), _p(angles), pos_scale, n_heads,
             n_kv_heads, head_dim, page_size, _p(_status_word(x.device)), _stream()), "gemm_tcgen05_qkv_rope")
@@ -337,6 +342,22 @@ def gemm_qkv_rope(x: torch.Tensor, w_qkv: torch.Tensor, q_out: torch.Tensor, pos
 
 
 _tcgen05_status = {}
+_pairs: Optional[bool] = None      # whether the variant with pairs of blocks sharing W tiles can be used
+
+
+PAIRS_MIN_TILES = 4 * 148     # 128 x 256 tiles from which sharing W tiles between two blocks pays (measured on B200)
+
+
+def tcgen05_pairs(rows: int, features: int) -> bool:
+    """Large products run the tcgen05 kernel in which two thread blocks share each tile of W
+    (csrc/gemm_tcgen05_cluster.cu: 108 us against 119 us for 2048 x 16384 x 2048, 423 against 454 for 8192 rows),
+    unless DYNALM_GEMM_PAIRS=0 or that source file is not there; smaller ones, where the pairing only couples the
+    blocks' pipelines (54 us against 52 us for 2048 x 2048 x 8192), run csrc/gemm_tcgen05.cu."""
+    global _pairs
+    if _pairs is None:
+        _pairs = os.environ.get("DYNALM_GEMM_PAIRS", "1") != "0" and \
+            os.path.isfile(os.path.join(_lib.CSRC, "gemm_tcgen05_cluster.cu"))
+    return _pairs and -(-rows // 128) * -(-features // 256) >= PAIRS_MIN_TILES
 
 
 def _status_word(device: torch.device) -> torch.Tensor:
@@ -493,8 +514,10 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str 
         else:
             raise InvalidArgument("gemm_tcgen05: out bfloat16 or float32")
     status = _status_word(x.device)
-    _check(_fn("gemm_tcgen05", "dl_gemm_tcgen05")(_p(x), x.stride(0), _p(w), _p(out), out.stride(0), M, N, K, code,
-                                                   out_scale, _p(status), _stream()), "gemm_tcgen05")
+    library, name = (("gemm_tcgen05_cluster", "dl_gemm_tcgen05_cluster") if tcgen05_pairs(M, N)
+                     else ("gemm_tcgen05", "dl_gemm_tcgen05"))
+    _check(_fn(library, name)(_p(x), x.stride(0), _p(w), _p(out), out.stride(0), M, N, K, code, out_scale, _p(status),
+                              _stream()), "gemm_tcgen05")
 
 
 _argmax_scratch = {}

@@ -469,11 +469,20 @@ def test_gemm_skinny(ops, M, N, K):
     assert (r2.double() - (resid.double() + ref)).abs().max() <= 2e-5 * max(1.0, scale)
 
 
+@pytest.fixture(params=["alone", "pairs"])
+def tile_sharing(request, ops, monkeypatch):
+    """Runs a test with the tcgen05 product in which every block loads its own operands, and with the one in which
+    two blocks share each tile of W (forced for every size, also those for which the dispatcher would not use it)."""
+    monkeypatch.setattr(ops, "PAIRS_MIN_TILES", 1 if request.param == "pairs" else 1 << 40)
+    return request.param
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 256), (100, 264, 200), (300, 1000, 136), (17, 48, 8),
                                    (2048, 3072, 2048), (513, 4096, 1024)])
-def test_gemm_tcgen05(ops, M, N, K):
+def test_gemm_tcgen05(ops, tile_sharing, M, N, K):
     """The tcgen05 / TMEM / TMA matrix product against an fp64 reference: tiles that end inside M, N
-    and K, all three epilogues, and an operand that is a view with a wider row."""
+    and K (an odd number of row blocks leaves a pair's second block without rows), all three epilogues, and an
+    operand that is a view with a wider row."""
     g = torch.Generator(device="cpu").manual_seed(14)
     x = torch.randn(M, K, generator=g).to(DEV, torch.bfloat16)
     w = torch.randn(N, K, generator=g).to(DEV, torch.bfloat16)
@@ -503,7 +512,7 @@ def test_gemm_tcgen05(ops, M, N, K):
 @pytest.mark.parametrize("rows,heads,kvh,hd,K,page", [(8, 32, 8, 64, 2048, 16), (1, 4, 4, 16, 80, 16), (13, 6, 2, 128, 264, 32),
                                                       (16, 5, 1, 48, 1000, 16), (300, 32, 8, 64, 512, 16),
                                                       (133, 5, 1, 128, 200, 32), (1000, 6, 3, 64, 72, 16)])
-def test_gemm_qkv_rope_matches_the_separate_kernels(ops, rows, heads, kvh, hd, K, page):
+def test_gemm_qkv_rope_matches_the_separate_kernels(ops, tile_sharing, rows, heads, kvh, hd, K, page):
     """Projection + rotation + cache write in one kernel (weight-streaming up to 16 rows, tcgen05 beyond) against
     the plain product followed by rope_cache_write:
     the same q and the same cache pages (positions in the middle of pages, requests in shuffled rows)."""
