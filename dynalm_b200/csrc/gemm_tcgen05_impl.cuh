@@ -13,13 +13,13 @@ constexpr int T5_THREADS = 192;           // 6 warps
 constexpr uint32_t T5_A_BYTES = T5_BM * T5_BK * 2;    // 16 KiB
 constexpr uint32_t T5_STORE_BYTES = 4 * 32 * 128;     // per epilogue warp: 32 rows x 128 bytes of output, staged for coalesced stores
 
-// Tile width BN is 256 (4 stages of 48 KiB) or 128 (6 stages of 32 KiB, for shapes whose tile count
-// fits the SMs badly at 256).
+// Tile width BN is 256 (4 stages of 48 KiB), 192 (5 stages of 40 KiB) or 128 (6 stages of 32 KiB); the narrower
+// ones are for shapes whose tile count fits the SMs badly at 256. SwiGLU takes 256 or 128 only.
 template <int BN> struct T5 {
-  static constexpr int STAGES = BN == 256 ? 4 : 6;
+  static constexpr int STAGES = BN == 256 ? 4 : (BN == 192 ? 5 : 6);
   static constexpr uint32_t B_BYTES = BN * T5_BK * 2;
   static constexpr uint32_t STAGE_BYTES = T5_A_BYTES + B_BYTES;
-  static constexpr uint32_t TMEM_COLS = 2 * BN;      // two accumulators
+  static constexpr uint32_t TMEM_COLS = BN == 128 ? 256 : 512;      // two accumulators (a power of two)
   static constexpr size_t SMEM = static_cast<size_t>(STAGES) * STAGE_BYTES + T5_STORE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
 };
 
@@ -351,15 +351,26 @@ static int t5_launch(const void* x, int ldx, const void* w, void* y, int ldy, in
   }
   const long long m_blocks = (M + dl::T5_BM - 1) / dl::T5_BM;
   const long long m_tiles = (m_blocks + P::CLUSTER - 1) / P::CLUSTER;      // pairs of row blocks in a cluster
-  // Tile width: 256 unless 128 wastes far fewer SM-rounds (a round of 128-wide tiles costs somewhat more than
-  // half a round of 256-wide ones, measured).
+  // Tile width: the one whose rounds over the SMs cost least, a round of 192- or 128-wide tiles taking about 0.78
+  // or 0.7 of a round of 256-wide ones (measured). SwiGLU pairs gate and up columns in halves of 64: 256 or 128. The
+  // q | k | v epilogue needs whole heads in a tile.
   const int units = sm_count / P::CLUSTER;                                  // blocks, or clusters of two
-  auto rounds = [&](int bn) {
+  auto cost = [&](int bn, double per_round) {
     const int per = mode == dl::T5_OUT_SWIGLU ? bn / 2 : bn;
     const long long t = m_tiles * ((feats + per - 1) / per);
-    return static_cast<double>((t + units - 1) / units) * (bn / 256.0);
+    return static_cast<double>((t + units - 1) / units) * per_round;
   };
-  const int bn = rounds(128) < 0.7 * rounds(256) ? 128 : 256;
+  static int forced = -1;
+  if (forced < 0) { const char* e = getenv("T5_BN"); forced = e ? atoi(e) : 0; }
+  int bn = 256;
+  double best = cost(256, 1.0);
+  const bool can192 = mode != dl::T5_OUT_SWIGLU && (mode != dl::T5_OUT_QKV_ROPE || 192 % rope.head_dim == 0);
+  if (can192 && cost(192, 0.78) < best) {
+    bn = 192;
+    best = cost(192, 0.78);
+  }
+  if (cost(128, 0.7) < best) bn = 128;
+  if (forced == 128 || forced == 256 || (forced == 192 && can192)) bn = forced;
   const int per_tile = mode == dl::T5_OUT_SWIGLU ? bn / 2 : bn;
   const int tiles_n = (feats + per_tile - 1) / per_tile;
   const long long tiles = m_tiles * tiles_n;
@@ -392,6 +403,17 @@ static int t5_launch(const void* x, int ldx, const void* w, void* y, int ldy, in
     }
     cfg.dynamicSmemBytes = dl::T5<256>::SMEM;
     return static_cast<int>(cudaLaunchKernelEx(&cfg, dl::gemm_tcgen05_kernel<256, P>, map_x, map_w, y, ldy, M, N, K, mode,
+                                               out_scale, gate_rows, tiles_n, static_cast<int>(tiles), status, rope));
+  } else if (bn == 192) {
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(dl::gemm_tcgen05_kernel<192, P>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(dl::T5<192>::SMEM));
+      if (e != cudaSuccess) return static_cast<int>(e);
+      configured = true;
+    }
+    cfg.dynamicSmemBytes = dl::T5<192>::SMEM;
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, dl::gemm_tcgen05_kernel<192, P>, map_x, map_w, y, ldy, M, N, K, mode,
                                                out_scale, gate_rows, tiles_n, static_cast<int>(tiles), status, rope));
   } else {
     static bool configured = false;
