@@ -11,8 +11,8 @@
 //   O += P V       tcgen05.mma, M 128, N head_dim, P from tensor memory, V read as it lies in the cache
 //                  (head dimension contiguous: an MN-major operand), O in tensor memory
 //
-// Roles: warps 0..3 softmax and the final store, warp 4 (one lane) TMA producer, warp 5 (one lane) issues
-// the MMAs and owns the tensor-memory allocation. The MMA warp issues S of tile i+1 as soon as the softmax
+// Roles: warps 0..3 softmax and the final store, warp 4 TMA producer, warp 5 issues the MMAs and owns the
+// tensor-memory allocation (both run their loops as whole warps; one elected lane issues). The MMA warp issues S of tile i+1 as soon as the softmax
 // warps have read S of tile i, so the tensor core works under the softmax. O is rescaled only when a row's
 // maximum has grown by more than 2^8 since the reference point of its exponentials was set; the result is
 // the same function of the scores, with probabilities kept below 2^8.

@@ -1,16 +1,21 @@
 // y = x W^T on the 5th-generation tensor cores: tcgen05.mma with the accumulator in tensor memory,
 // operands brought to shared memory by TMA. bf16 operands, fp32 accumulation.
 //
-// A thread block computes 128 x BN tiles of y (BN = 256, or 2 x 128 for SwiGLU), one after another. Roles:
-//   warp 0, one lane   TMA producer: for each 64-wide slice of K, waits for a free stage, arms the stage's
+// The kernel and its launcher are in gemm_tcgen05_impl.cuh; this file instantiates them with every block loading
+// its own operands (gemm_tcgen05_cluster.cu: with pairs of blocks sharing W tiles).
+//
+// A thread block computes 128 x BN tiles of y (BN = 256, 192 or 128; for SwiGLU two halves of gate and up
+// columns), one after another. Roles (warps 0 and 1 run their loops as whole warps; one elected lane issues):
+//   warp 0             TMA producer: for each 64-wide slice of K, waits for a free stage, arms the stage's
 //                      mbarrier with the byte count and issues the tile loads (x: 128 rows, W: BN rows), both
 //                      K-major with the 128-byte swizzle that the tensor core reads directly
-//   warp 1, one lane   issues four tcgen05.mma (M 128, N BN, K 16) per stage into the TMEM accumulator and
+//   warp 1             issues four tcgen05.mma (M 128, N BN, K 16) per stage into the TMEM accumulator and
 //                      commits them to the stage's "empty" barrier; after a tile's last slice commits to that
 //                      accumulator's "full" barrier. Warp 1 also allocates and frees the TMEM columns.
 //   warps 2..5         epilogue: each warp reads its quarter of the 128 TMEM lanes (one output row per thread),
-//                      converts and stores: bf16, fp32 (optionally scaled), or SwiGLU, where the tile's first
-//                      128 columns are gate features and the last 128 the matching up features of W = [Wg; Wu].
+//                      converts and stores: bf16, fp32 (optionally scaled), SwiGLU, where the tile's first
+//                      half are gate features and the second the matching up features of W = [Wg; Wu], or the
+//                      q | k | v projection's rotary encoding and cache write (qkv_rope.cuh).
 // Rows, columns and K past the ends are zero-filled by TMA on the way in and masked on the way out.
 //
 // Every wait on an mbarrier is bounded: after about a second without progress the waiting role records a code
