@@ -360,8 +360,8 @@ static int t5_launch(const void* x, int ldx, const void* w, void* y, int ldy, in
     const long long t = m_tiles * ((feats + per - 1) / per);
     return static_cast<double>((t + units - 1) / units) * per_round;
   };
-  static int forced = -1;
-  if (forced < 0) { const char* e = getenv("T5_BN"); forced = e ? atoi(e) : 0; }
+  static int forced = -1;      // DYNALM_GEMM_TILE=128|192|256 overrides the choice where the width is allowed (for measurements)
+  if (forced < 0) { const char* e = getenv("DYNALM_GEMM_TILE"); forced = e ? atoi(e) : 0; }
   int bn = 256;
   double best = cost(256, 1.0);
   const bool can192 = mode != dl::T5_OUT_SWIGLU && (mode != dl::T5_OUT_QKV_ROPE || 192 % rope.head_dim == 0);
