@@ -19,16 +19,21 @@ from . import ops
 SM_COUNT = 148            # B200
 MAX_SPLITS = 32
 CLUSTER_SPLITS = 8          # up to here the tensor-core kernel merges splits inside a thread-block cluster
+LONG_SPLIT_KEYS = 1024      # keys per split from which more than CLUSTER_SPLITS splits pay
 DECODE_FILL = int(os.environ.get('DYNALM_DECODE_FILL', '1'))   # blocks per SM the split count aims for
 
 
 def decode_splits(rows: int, n_heads: int, n_kv_heads: int, max_kv_len: int, tensor_cores: bool = True) -> int:
-    """Key splits per row so that the grid fills the GPU about twice, each split at least 128 keys
-    (one 32-key tile for each of a block's four warps)."""
+    """Key splits per row so that the grid fills the GPU, each split at least 128 keys (one 32-key tile for each
+    of a block's four warps). The tensor-core kernel merges up to 8 splits inside a thread-block cluster, which
+    wins while a split is short; from 1,024 keys per split on, more splits (merged by a second kernel) win."""
     group = n_heads // n_kv_heads
     blocks = rows * n_kv_heads * (-(-group // (16 if tensor_cores else 4)))
     want = -(-DECODE_FILL * SM_COUNT // max(blocks, 1))
-    return max(1, min(want, max(1, max_kv_len // 128), CLUSTER_SPLITS if tensor_cores else MAX_SPLITS))
+    splits = max(1, min(want, max(1, max_kv_len // 128), MAX_SPLITS))
+    if tensor_cores and splits > CLUSTER_SPLITS and max_kv_len < CLUSTER_SPLITS * LONG_SPLIT_KEYS:
+        splits = CLUSTER_SPLITS
+    return splits
 
 
 def decode_uses_tensor_cores(spec) -> bool:
