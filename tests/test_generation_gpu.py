@@ -132,3 +132,59 @@ def test_step_function_refusals(tiny_folders):
         eng.step([StepEntry("x", list(range(10)), [0])])         # 70 tokens, the pool holds 64
     eng.end("x")
     assert eng.built.cache.free_pages == eng.built.cache.num_pages
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+def test_scheduler_under_random_load_gives_the_tokens_of_each_request_alone(seed, tiny_folders):
+    """Forty requests of random lengths, priorities and sampling (greedy or seeded temperature) arrive in bursts
+    between steps into an engine with few pages and six running slots; some are cancelled. In 32-bit a row's
+    arithmetic does not depend on the batch, so every request that ran to its end must have exactly the tokens it
+    gets alone in a roomy engine, whatever was preempted, recomputed or decoded one step ahead around it."""
+    from dynalm_b200 import Request, SamplingParams, SchedulerConfig
+    name = "b"
+    cfg = TINY[name][0]
+    rng = np.random.RandomState(40 + seed)
+    n = 40
+    prompts = [[int(t) for t in rng.randint(0, cfg["vocab_size"], rng.randint(1, 120))] for _ in range(n)]
+    new = [int(rng.randint(1, 60)) for _ in range(n)]
+    samp = [SamplingParams(temperature=0.8, seed=int(rng.randint(1, 1 << 30))) if rng.rand() < 0.4 else SamplingParams()
+            for _ in range(n)]
+    prio = [int(rng.randint(0, 3)) for _ in range(n)]
+
+    eng = _engine(tiny_folders[name], "float32", ctx=448, batch=96,
+                  scheduler=SchedulerConfig(max_running=6, decode_token_budget=6, prefill_token_budget=64,
+                                            max_prefill_chunk=48, max_batch_tokens=96))
+    got, ids, cancelled = {}, {}, set()
+    submitted = 0
+    steps = 0
+    while submitted < n or not eng.scheduler.idle:
+        if submitted < n and rng.rand() < 0.35:
+            for _ in range(int(rng.randint(1, 5))):
+                if submitted < n:
+                    i = submitted
+                    ids[eng.scheduler.submit(Request(prompts[i], new[i], samp[i], priority=prio[i]))] = i
+                    got[i] = []
+                    submitted += 1
+        if rng.rand() < 0.03 and ids:
+            rid = int(rng.choice(list(ids)))
+            eng.scheduler.cancel(rid)
+            cancelled.add(ids[rid])
+        for ev in eng.scheduler.step():
+            if ev.token is not None:
+                got[ids[ev.request_id]].append(ev.token)
+            if ev.finished and ev.status == "finished":
+                assert ev.completion_tokens == len(got[ids[ev.request_id]])
+        steps += 1
+        assert steps < 20000
+    assert eng.built.cache.free_pages == eng.built.cache.num_pages
+    assert eng.scheduler.stats.preemptions > 0, "the pool was meant to be too small"
+
+    alone = _engine(tiny_folders[name], "float32", ctx=4096, batch=128)
+    checked = 0
+    for i in range(n):
+        if i in cancelled:
+            continue
+        want = alone.generate(prompts[i], max_tokens=new[i], sampling=[samp[i]]).tokens
+        assert got[i] == want, f"request {i} (prompt {len(prompts[i])}, {new[i]} new, temperature {samp[i].temperature})"
+        checked += 1
+    assert checked >= n // 2
