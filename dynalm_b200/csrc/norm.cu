@@ -98,13 +98,24 @@ rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, float de
       const int c = (i * NORM_VEC_THREADS + threadIdx.x) * 4;
       d[i] = c < width ? load4<TD>(dr + c) : zero;
     }
-    for (int p = 1; p < parts; ++p) {       // parts are added in index order
+    // parts are added in index order; the loads of PC parts are issued together, so a product left in many
+    // parts costs few round trips
+    constexpr int PC = NV <= 2 ? 4 : (NV <= 4 ? 2 : 1);
+    for (int p = 1; p < parts; p += PC) {
+      float4 e[PC][NV];
 #pragma unroll
-      for (int i = 0; i < NV; ++i) {
-        const int c = (i * NORM_VEC_THREADS + threadIdx.x) * 4;
-        if (c < width) {
-          const float4 e = load4<TD>(dr + p * part_stride + c);
-          d[i].x += e.x; d[i].y += e.y; d[i].z += e.z; d[i].w += e.w;
+      for (int q = 0; q < PC; ++q) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          const int c = (i * NORM_VEC_THREADS + threadIdx.x) * 4;
+          e[q][i] = (p + q < parts && c < width) ? load4<TD>(dr + (p + q) * part_stride + c) : zero;
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < PC; ++q) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          d[i].x += e[q][i].x; d[i].y += e[q][i].y; d[i].z += e[q][i].z; d[i].w += e[q][i].w;
         }
       }
     }

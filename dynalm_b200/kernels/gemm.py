@@ -1,19 +1,22 @@
 """y = x W^T (+ bias): picks the matrix-product kernel for a dtype and shape.
 
 float32 always runs the plain fixed-order kernel (csrc/gemm_simt.cu): the true 32-bit path uses no
-tensor cores and no reduced-precision mode. bfloat16 with at most 16 rows (decode) runs the
-weight-streaming kernel (csrc/gemm_skinny.cu), which can also apply SwiGLU on the way out or leave
-split-K partial sums for the consumer to add. bfloat16 with more rows runs the tcgen05 / TMEM / TMA
-kernel (csrc/gemm_tcgen05.cu, plain or with the SwiGLU epilogue) whenever the product has enough
-128 x 256 tiles to fill the GPU; the few shapes in between (17..127 rows with a narrow output, where
-split-K wins) run the library product (cuBLAS through torch), which is where the reference's GPU path
-calls a library too (ggml_mul_mat, dynacore/src/gpu/ggml_graph.cpp:278-292). Shapes none of these can
-express (a bias, a K that is no multiple of 8) run the plain kernel.
+tensor cores and no reduced-precision mode. bfloat16 with at most 16 rows (decode) runs a
+weight-streaming kernel, which can also apply SwiGLU on the way out or leave split-K partial sums for
+the consumer to add: the mma.sync one (csrc/gemm_skinny.cu) up to 8 rows, the tcgen05 one
+(csrc/gemm_stream_tcgen05.cu), which computes the product transposed, from 9 to 16 rows. bfloat16 with
+more rows runs the tcgen05 / TMEM / TMA kernel (csrc/gemm_tcgen05.cu, plain or with the SwiGLU
+epilogue) whenever the product has enough 128 x 256 tiles to fill the GPU; the few shapes in between
+(17..127 rows with a narrow output, where split-K wins) run the library product (cuBLAS through torch), which is where the reference's GPU path calls a library too
+(ggml_mul_mat, dynacore/src/gpu/ggml_graph.cpp:278-292). Shapes none of these can express (a bias, a K
+that is no multiple of 8) run the plain kernel.
 """
 
 from __future__ import annotations
 
 from typing import Optional
+
+import os
 
 import torch
 
@@ -43,6 +46,27 @@ def _mm_f32_out(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
 def skinny_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
     return (x.dtype == torch.bfloat16 and x.shape[0] <= ops.SKINNY_FAST_ROWS and x.shape[1] % 8 == 0
             and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.is_contiguous())
+
+
+# Row counts (9 .. STREAM_ROWS) that the tcgen05 streaming kernel takes. Measured inside whole decode steps on B200
+# (1B shapes, 1,024 tokens of context): at 16 rows the step takes 1.01 ms with it against 1.09 ms with the mma.sync
+# kernel; at 8 rows 0.91 against 0.89 ms; at 32 and 64 rows the library's split-K kernels are as fast or faster,
+# because the consumer of the partial sums (one block per row) pays for them.
+STREAM_ROWS = min(int(os.environ.get("DYNALM_STREAM_ROWS", "16")), ops.STREAM_MAX_ROWS)
+
+
+def use_stream(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and 8 < x.shape[0] <= STREAM_ROWS and x.shape[1] % 8 == 0
+            and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.is_contiguous()
+            and w.data_ptr() % 16 == 0)
+
+
+def stream_split_count(n_features: int, k: int) -> int:
+    """K splits of the streaming kernel so that its blocks (one per 128 features and split) about fill the GPU, every
+    split with at least four 64-wide slices of K."""
+    tiles = -(-n_features // 128)
+    want = max(1, (SM_COUNT + tiles // 2) // tiles)
+    return max(1, min(want, 16, k // 256))
 
 
 def split_count(n_features: int, k: int, rows: int) -> int:
@@ -75,6 +99,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[t
     if x.dtype == torch.float32 or bias is not None:
         ops.gemm_simt(x, w, out, bias, out_scale)
         return out
+    if use_stream(x, w) and out.stride(1) == 1:
+        ops.gemm_stream(x, w, out, "store", out_scale)
+        return out
     if skinny_ok(x, w) and out.stride(1) == 1:
         ops.gemm_skinny(x, w, out, "store", out_scale)
         return out
@@ -100,12 +127,13 @@ def linear_partial(x: torch.Tensor, w: torch.Tensor, runtime, name: str) -> torc
     and come back as float32 partial sums [parts, M, N] (see ops.rmsnorm's `delta`); otherwise a
     plain [M, N] tensor in the compute dtype."""
     M, N = x.shape[0], w.shape[0]
-    if x.dtype == torch.bfloat16 and skinny_ok(x, w):
-        parts = split_count(N, x.shape[1], M)
+    if x.dtype == torch.bfloat16 and (use_stream(x, w) or skinny_ok(x, w)):
+        stream = use_stream(x, w)
+        parts = stream_split_count(N, x.shape[1]) if stream else split_count(N, x.shape[1], M)
         if parts > 1:
-            flat = runtime.flat(f"{name}_parts_{N}", 8 * ops.SKINNY_MAX_ROWS * N, torch.float32)
+            flat = runtime.flat(f"{name}_parts_{N}", 16 * ops.SKINNY_MAX_ROWS * N, torch.float32)
             out = flat[:parts * M * N].view(parts, M, N)
-            ops.gemm_skinny(x, w, out, "store", 1.0)
+            (ops.gemm_stream if stream else ops.gemm_skinny)(x, w, out, "store", 1.0)
             return out
     out = runtime.buffer(name, (M, N))
     return linear(x, w, out)
@@ -116,6 +144,9 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, runtime, inner: int)
     bfloat16 rows, else the product followed by the activation kernel."""
     rows = x.shape[0]
     act = runtime.buffer("ffn_act", (rows, inner))
+    if x.dtype == torch.bfloat16 and use_stream(x, w_gate_up):
+        ops.gemm_stream(x, w_gate_up, act, "swiglu")
+        return act
     if x.dtype == torch.bfloat16 and skinny_ok(x, w_gate_up):
         ops.gemm_skinny(x, w_gate_up, act, "swiglu")
         return act

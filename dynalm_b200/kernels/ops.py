@@ -49,6 +49,8 @@ _SIGNATURES = {
     "gemm_tcgen05_cluster": {
         "dl_gemm_tcgen05_cluster": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
         "dl_gemm_tcgen05_cluster_qkv_rope": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P, _F, _I, _I, _I, _I, _P, _P]},
+    "gemm_stream_tcgen05": {
+        "dl_gemm_stream": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _L, _P, _P]},
     "gemm_simt": {"dl_gemm_simt": [_I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _P]},
     "sampling": {
         "dl_argmax": [_P, _I, _I, _I, _P, _P, _P],
@@ -518,6 +520,40 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str 
                      else ("gemm_tcgen05", "dl_gemm_tcgen05"))
     _check(_fn(library, name)(_p(x), x.stride(0), _p(w), _p(out), out.stride(0), M, N, K, code, out_scale, _p(status),
                               _stream()), "gemm_tcgen05")
+
+
+STREAM_MAX_ROWS = 64       # what the tcgen05 weight-streaming product takes
+
+
+def gemm_stream(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str = "store", out_scale: float = 1.0) -> None:
+    """x W^T for up to 64 bfloat16 rows on tcgen05, built around the stream of W (csrc/gemm_stream_tcgen05.cu).
+
+    out [M, N] bfloat16 or float32; float32 [parts, M, N] (contiguous): K is split over `parts` blocks and each
+    leaves its partial sums; mode "swiglu" (w = [gate; up]): out [M, N/2] bfloat16."""
+    _cuda(x, w, out)
+    _rows_contiguous(x, "x")
+    M, K = x.shape
+    N = w.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not w.is_contiguous() or w.shape[1] != K:
+        raise InvalidArgument("gemm_stream: x and w bfloat16, w [N, K] contiguous")
+    if M > STREAM_MAX_ROWS or K % 8 or x.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16:
+        raise Unsupported(f"gemm_stream: at most {STREAM_MAX_ROWS} rows, K a multiple of 8, 16-byte aligned rows")
+    n_split, split_stride = 1, 0
+    if mode == "swiglu":
+        if N % 2 or out.shape != (M, N // 2) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
+            raise InvalidArgument("gemm_stream: swiglu needs out [M, N/2] bfloat16")
+        code, ldy = 2, out.stride(0)
+    elif out.dim() == 3:
+        if out.dtype != torch.float32 or out.shape[1:] != (M, N) or not out.is_contiguous():
+            raise InvalidArgument("gemm_stream: split output must be contiguous float32 [parts, M, N]")
+        code, ldy, n_split, split_stride = 1, N, out.shape[0], out.stride(0)
+    else:
+        if out.shape != (M, N) or out.stride(1) != 1 or out.dtype not in (torch.bfloat16, torch.float32):
+            raise InvalidArgument("gemm_stream: out [M, N] bfloat16 or float32")
+        code, ldy = (0 if out.dtype == torch.bfloat16 else 1), out.stride(0)
+    _check(_fn("gemm_stream_tcgen05", "dl_gemm_stream")(
+        _p(x), x.stride(0), _p(w), _p(out), ldy, M, N, K, code, out_scale, n_split, split_stride,
+        _p(_status_word(x.device)), _stream()), "gemm_stream")
 
 
 _argmax_scratch = {}

@@ -560,3 +560,37 @@ def test_gemm_qkv_rope_matches_the_separate_kernels(ops, tile_sharing, rows, hea
         ops.gemm_qkv_rope(x, w, qkv2, positions, row_request, table, k2, v2, inv_freq, 0.5, heads, kvh, hd, page, angles)
         assert torch.equal(qkv2[:, :heads * hd], qkv_got[:, :heads * hd]) and torch.equal(k2, k_got) and torch.equal(v2, v_got)
     assert ops.gemm_tcgen05_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 3072, 2048), (1, 499 * 2, 80), (16, 256, 64), (17, 130, 200), (33, 1000, 264),
+                                   (64, 2048, 1024), (40, 96, 8), (64, 640, 4096)])
+def test_gemm_stream(ops, M, N, K):
+    """The tcgen05 weight-streaming product (up to 64 rows, computed transposed) against an fp64 reference: tiles that
+    end inside N and K, every row count class, bf16 / fp32 / scaled output, K splits with an empty split, SwiGLU."""
+    g = torch.Generator(device="cpu").manual_seed(15)
+    x = torch.randn(M, K, generator=g).to(DEV, torch.bfloat16)
+    w = torch.randn(N, K, generator=g).to(DEV, torch.bfloat16)
+    ref = x.double() @ w.double().T
+    scale = ref.abs().max().item()
+    out16 = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_stream(x, w, out16)
+    assert ops.gemm_tcgen05_status() == 0, "a wait inside the kernel timed out"
+    assert (out16.double() - ref).abs().max() <= 1e-2 * scale
+    out32 = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ops.gemm_stream(x, w, out32, "store", 0.5)
+    assert (out32.double() - 0.5 * ref).abs().max() <= 2e-5 * scale
+    for parts in (2, 5, 7):
+        part = torch.full((parts, M, N), float("nan"), dtype=torch.float32, device=DEV)
+        ops.gemm_stream(x, w, part)
+        assert (part.double().sum(0) - ref).abs().max() <= 2e-5 * scale, parts
+    wide = torch.zeros(M, K + 24, dtype=torch.bfloat16, device=DEV)
+    wide[:, :K] = x
+    out32b = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ops.gemm_stream(wide[:, :K], w, out32b)
+    assert (out32b.double() - ref).abs().max() <= 2e-5 * scale
+    act = torch.full((M, N // 2), 7.0, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_stream(x, w, act, "swiglu")
+    gate, up = ref[:, :N // 2], ref[:, N // 2:]
+    want = gate * torch.sigmoid(gate) * up
+    assert (act.double() - want).abs().max() <= 1e-2 * max(1.0, want.abs().max().item())
+    assert ops.gemm_tcgen05_status() == 0
