@@ -49,9 +49,10 @@ def skinny_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 # Row counts (9 .. STREAM_ROWS) that the tcgen05 streaming kernel takes. Measured inside whole decode steps on B200
-# (1B shapes, 1,024 tokens of context): at 16 rows the step takes 1.01 ms with it against 1.09 ms with the mma.sync
-# kernel; at 8 rows 0.91 against 0.89 ms; at 32 and 64 rows the library's split-K kernels are as fast or faster,
-# because the consumer of the partial sums (one block per row) pays for them.
+# (1B shapes, 1,024 tokens of context): at 16 rows the step takes 0.98 ms with it against 1.09 ms with the mma.sync
+# kernel; at 8 rows 0.91 against 0.89 ms; at 24 rows 1.11 against 1.12 ms; at 32 and 64 rows the library's split-K
+# kernels are faster (1.15 against 1.18 ms, 1.41 against 1.49 ms): the consumer of the partial sums (one block per
+# row) pays for them.
 STREAM_ROWS = min(int(os.environ.get("DYNALM_STREAM_ROWS", "16")), ops.STREAM_MAX_ROWS)
 
 
@@ -61,12 +62,15 @@ def use_stream(x: torch.Tensor, w: torch.Tensor) -> bool:
             and w.data_ptr() % 16 == 0)
 
 
+STREAM_MAX_SPLITS = 6      # more partial sums cost the norm that adds them more than they save (0.98 against 1.00 ms)
+
+
 def stream_split_count(n_features: int, k: int) -> int:
     """K splits of the streaming kernel so that its blocks (one per 128 features and split) about fill the GPU, every
     split with at least four 64-wide slices of K."""
     tiles = -(-n_features // 128)
     want = max(1, (SM_COUNT + tiles // 2) // tiles)
-    return max(1, min(want, 16, k // 256))
+    return max(1, min(want, STREAM_MAX_SPLITS, k // 256))
 
 
 def split_count(n_features: int, k: int, rows: int) -> int:
