@@ -16,6 +16,7 @@ from ..parts import BLOCKS, NORMS
 from ..parts.base import CacheSpec, pick_tensors
 from ..parts.block import ResidualStream
 from ..parts.embedding import LogitsHead, TokenEmbedding
+from . import launch_memo
 
 
 class Decoder:
@@ -31,6 +32,11 @@ class Decoder:
         self.head = LogitsHead(plan.head, store, runtime, self.embedding)
         self.vocab = plan.head.vocab
         self.width = plan.embedding.width
+        # for launch_memo: blocks of equal class and spec share a number; the layouts of their tensors are filled on use
+        seen: Dict[tuple, int] = {}
+        self._run_kinds = [seen.setdefault((type(self.blocks[run.layer]), self.blocks[run.layer].spec), len(seen))
+                           for run in self.order]
+        self._run_layouts: Dict[int, tuple] = {}
 
     @property
     def graph_safe(self) -> bool:
@@ -64,9 +70,14 @@ class Decoder:
         """Run embedding and all blocks; `caches[i]` is the CacheView of run-order entry i (or None)."""
         x = self.embedding.forward(ctx.token_ids, ctx.num_tokens)
         stream = ResidualStream(x)
+        memo = launch_memo.LayerLaunchMemo(self._run_layouts, self._run_kinds) if launch_memo.ENABLED else None
         for i, run in enumerate(self.order):
             owner = i if run.cache_of is None else run.cache_of
-            stream = self.blocks[run.layer].forward(stream, ctx, caches[owner], run.cache_of is None)
+            block = self.blocks[run.layer]
+            if memo is None:
+                stream = block.forward(stream, ctx, caches[owner], run.cache_of is None)
+            else:
+                stream = memo.run(i, block, stream, ctx, caches[owner], run.cache_of is None)
         return stream
 
     def logits(self, stream: ResidualStream, ctx, out: torch.Tensor) -> torch.Tensor:

@@ -42,9 +42,13 @@ class Runtime:
         self.max_tokens = int(max_tokens)
         self.max_requests = int(max_requests)      # the most rows a decode-only step can bring
         self._buffers: Dict[Tuple, torch.Tensor] = {}
+        self._views: Dict[Tuple, torch.Tensor] = {}      # (name, shape, dtype) -> the first rows of a buffer
 
     def buffer(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype = None) -> torch.Tensor:
         dtype = dtype or self.dtype
+        view = self._views.get((name, shape, dtype))
+        if view is not None:
+            return view
         rows, tail = int(shape[0]), tuple(int(s) for s in shape[1:])
         if rows > self.max_tokens:
             raise InvalidArgument(f"{rows} rows asked of buffer '{name}', the runtime was made for {self.max_tokens}")
@@ -53,7 +57,10 @@ class Runtime:
         if buf is None:
             buf = torch.zeros((self.max_tokens,) + tail, dtype=dtype, device=self.device)
             self._buffers[key] = buf
-        return buf[:rows]
+        view = buf[:rows]
+        if isinstance(shape, tuple):
+            self._views[(name, shape, dtype)] = view
+        return view
 
     def flat(self, name: str, numel: int, dtype: torch.dtype = torch.float32) -> torch.Tensor:
         """A persistent 1-D scratch array of `numel` elements, allocated once at the size first asked

@@ -302,9 +302,14 @@ class StepFunction:
             logits = self._replay(ctx)
         else:
             out = self._logits_buffer(ctx.num_logit_rows) if ctx.num_logit_rows else None
-            logits = self.model.forward(ctx, self.caches(), out)
+            logits = self._forward(ctx, out)
         self.batcher.finish(entries)
         return logits
+
+    def _forward(self, ctx: StepContext, out: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        from ..kernels import ops
+        with ops.pinned_stream():
+            return self.model.forward(ctx, self.caches(), out)
 
     MAX_GRAPHS = 64
 
@@ -318,7 +323,7 @@ class StepFunction:
         graph = self._graphs.get(key)
         if graph is None:
             # once eagerly (allocates workspaces, loads kernels), then capture the same calls
-            self.model.forward(ctx, self.caches(), out)
+            self._forward(ctx, out)
             torch.cuda.current_stream().synchronize()
             if len(self._graphs) >= self.MAX_GRAPHS:
                 old = next(iter(self._graphs))
@@ -327,7 +332,7 @@ class StepFunction:
             graph = torch.cuda.CUDAGraph()
             before = ops.LAUNCHES
             with torch.cuda.graph(graph):
-                self.model.forward(ctx, self.caches(), out)
+                self._forward(ctx, out)
             from ..kernels import gemm
             self._graph_nodes[key] = ops.LAUNCHES - before
             self._graphs[key] = graph

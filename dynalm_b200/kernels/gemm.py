@@ -32,6 +32,7 @@ def _mm_f32_out(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
     global _mm_out_dtype_ok
     if _mm_out_dtype_ok is False:
         return False
+    ops.note_unrecorded_work()
     try:
         torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
         _mm_out_dtype_ok = True
@@ -116,7 +117,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[t
         ops.gemm_simt(x, w, out, bias, out_scale)
         return out
     if out.dtype == x.dtype:
-        torch.mm(x, w.t(), out=out)
+        ops.library_mm(x, w, out)
         LIBRARY_CALLS += 1
         return out
     if _mm_f32_out(x, w, out):

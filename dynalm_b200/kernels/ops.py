@@ -7,6 +7,7 @@ raises `EngineError` when a launch fails. Tensors must live on the CUDA device; 
 from __future__ import annotations
 
 import ctypes
+import contextlib
 import os
 from ctypes import c_double, c_float, c_int, c_longlong, c_void_p
 from typing import Optional
@@ -62,6 +63,9 @@ _SIGNATURES = {
 _funcs = {}
 
 
+_recording: Optional[list] = None
+
+
 def _fn(library: str, name: str):
     f = _funcs.get(name)
     if f is None:
@@ -69,11 +73,72 @@ def _fn(library: str, name: str):
         f.argtypes = _SIGNATURES[library][name]
         f.restype = c_int
         _funcs[name] = f
-    return f
+    if _recording is None:
+        return f
+    calls = _recording
+
+    def recorded(*args):
+        calls.append((f, args))
+        return f(*args)
+    return recorded
+
+
+def library_mm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x w^T by the library (cuBLAS through torch), written down like a launch of this module's when a
+    recording is on."""
+    torch.mm(x, w.t(), out=out)
+    if _recording is not None:
+        _recording.append((_library_mm_again, (x, w, out)))
+
+
+def note_unrecorded_work() -> None:
+    """For device work that is not written down while a recording is on: marks the recording as incomplete, so
+    that nobody repeats it."""
+    if _recording is not None:
+        _recording.append((None, ()))
+
+
+def _library_mm_again(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> int:
+    torch.mm(x, w.t(), out=out)
+    return 0
+
+
+class Recording:
+    """Inside the block every kernel launch of this module is also written down as (function, arguments), in
+    order: `calls`; a function returns 0 when its launch went well. Issuing the list again repeats the launches
+    (engine/launch_memo.py does, for the next layer)."""
+
+    def __enter__(self):
+        global _recording
+        self._outer = _recording
+        self.calls: list = []
+        _recording = self.calls
+        return self
+
+    def __exit__(self, *exc):
+        global _recording
+        _recording = self._outer
+        return False
+
+
+_pinned_stream: Optional[int] = None
 
 
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    return _pinned_stream if _pinned_stream is not None else torch.cuda.current_stream().cuda_stream
+
+
+@contextlib.contextmanager
+def pinned_stream():
+    """Inside the block every launch goes to the stream that is current on entry: one lookup for a whole forward
+    pass instead of one per launch (the lookup costs more than the launch)."""
+    global _pinned_stream
+    previous = _pinned_stream
+    _pinned_stream = torch.cuda.current_stream().cuda_stream
+    try:
+        yield
+    finally:
+        _pinned_stream = previous
 
 
 def _p(t: Optional[torch.Tensor]):

@@ -20,6 +20,7 @@ from .base import POSITIONS, CacheSpec, TensorDecl, register_mixer
 
 @register_mixer("attention")
 class PagedAttention:
+    replay_safe = True     # all device work goes through the recorded launches of kernels/ops.py (engine/launch_memo.py)
     graph_safe = True      # launches depend on row counts (and graph_key) only
 
     @staticmethod

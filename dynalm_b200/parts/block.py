@@ -41,9 +41,14 @@ class PreNormBlock:
         self.ffn_norm = NORMS.get(spec.ffn_norm.kind)(spec.ffn_norm, pick_tensors(spec.ffn_norm, store, NORMS), runtime)
         self.ffn = FEED_FORWARDS.get(spec.ffn.kind)(spec.ffn, pick_tensors(spec.ffn, store, FEED_FORWARDS), runtime)
         self.scale = float(spec.residual_scale)
+        # whether a later layer of the same kind may re-issue this block's launches by address (engine/launch_memo.py):
+        # only if every part says so of itself
+        parts = [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn, getattr(self.mixer, "position", None)]
+        self.replay_safe = all(getattr(p, "replay_safe", False) for p in parts if p is not None)
 
     def cache_spec(self):
         return self.mixer.cache_spec()
+
 
     def forward(self, stream: ResidualStream, ctx, cache, owns_cache: bool) -> ResidualStream:
         rows, width = stream.x.shape

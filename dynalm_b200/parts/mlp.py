@@ -14,6 +14,7 @@ from .base import TensorDecl, register_feed_forward
 
 @register_feed_forward("gated_mlp")
 class GatedMLP:
+    replay_safe = True     # all device work goes through the recorded launches of kernels/ops.py (engine/launch_memo.py)
     graph_safe = True      # launches depend on row counts (and graph_key) only
 
     @staticmethod

@@ -12,6 +12,8 @@ from .base import TensorDecl, register_norm
 
 @register_norm("rms")
 class RMSNorm:
+    replay_safe = True     # all device work goes through the recorded launches of kernels/ops.py (engine/launch_memo.py)
+
     @staticmethod
     def declare(spec) -> Dict[str, TensorDecl]:
         return {"weight": TensorDecl((spec.width,), role="vector", init="around_one")}

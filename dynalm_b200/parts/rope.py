@@ -24,6 +24,8 @@ from .base import register_position
 
 @register_position("rotary")
 class RotaryEncoding:
+    replay_safe = True     # all device work goes through the recorded launches of kernels/ops.py (engine/launch_memo.py)
+
     def __init__(self, spec, runtime):
         if spec.rotary_dim <= 0 or spec.rotary_dim > spec.head_dim or spec.rotary_dim % 2:
             raise Unsupported(f"rotary_dim {spec.rotary_dim} invalid for head_dim {spec.head_dim}")
@@ -64,6 +66,8 @@ class RotaryEncoding:
 
 @register_position("none")
 class NoPosition:
+    replay_safe = True     # all device work goes through the recorded launches of kernels/ops.py (engine/launch_memo.py)
+
     def __init__(self, spec, runtime):
         self.spec = spec
 

@@ -148,3 +148,28 @@ def test_fork_and_copy_on_write_match_from_scratch(name, dtype, tiny_folders):
         fn.end(r)
     built.cache.check()
     assert built.cache.free_pages == built.cache.num_pages
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["b", "d", "e"])
+def test_layers_issued_by_address_give_the_same_bits(name, dtype, tiny_folders, plain_logits, monkeypatch):
+    """From the third layer on, a step re-issues the second layer's launches with the layer's own addresses put in
+    (engine/launch_memo.py) instead of going through the parts' Python code: the logits are the same bits as with
+    every layer run through its parts, in whole prompts, portions and mixed steps; and the short way was taken
+    (also where a layer's products go to the library: config d in bfloat16, whose width is no multiple of 8)."""
+    from dynalm_b200.engine import launch_memo
+    reqs, _ = plain_logits[name]
+    for what, plan in (("chunks", plan_chunks(reqs, SIZES)), ("mixed", plan_mixed(reqs, seed=5))):
+        need = plan.max_live_tokens(64)
+        got = {}
+        for enabled in (True, False):
+            monkeypatch.setattr(launch_memo, "ENABLED", enabled)
+            before = launch_memo.REPLAYED_LAYERS
+            built = _built(tiny_folders[name], dtype, need, max(need, 64))
+            got[enabled] = run_plan_in_process(built.step_fn, plan)
+            replayed = launch_memo.REPLAYED_LAYERS - before
+            layers = TINY[name][0]["num_hidden_layers"]
+            assert (replayed > 0) == (enabled and layers > 2), (what, enabled, replayed)
+        assert got[True].keys() == got[False].keys()
+        for step in got[True]:
+            assert np.array_equal(got[True][step], got[False][step]), f"{name}/{dtype}/{what}: step {step} differs"
