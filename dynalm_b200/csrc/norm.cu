@@ -98,9 +98,9 @@ rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, float de
       const int c = (i * NORM_VEC_THREADS + threadIdx.x) * 4;
       d[i] = c < width ? load4<TD>(dr + c) : zero;
     }
-    // parts are added in index order; the loads of PC parts are issued together, so a product left in many
-    // parts costs few round trips
-    constexpr int PC = NV <= 2 ? 4 : (NV <= 4 ? 2 : 1);
+    // parts are added in index order; the loads of two parts are issued together, so a product left in many
+    // parts costs half the round trips (four at a time cost the three-part case 1 % of a decode step)
+    constexpr int PC = NV <= 4 ? 2 : 1;
     for (int p = 1; p < parts; p += PC) {
       float4 e[PC][NV];
 #pragma unroll
