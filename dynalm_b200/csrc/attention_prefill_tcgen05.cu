@@ -122,6 +122,10 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
   __syncthreads();
   tcgen05_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // up to here the block may have run beside the end of the kernel in front (programmatic dependent launch); q and the
+  // newest keys come from that kernel
+  pdl_wait();
+  pdl_trigger();
 
   if (warp == 4) {
     // TMA producer: the whole warp runs the loop, one elected lane issues the copies
@@ -390,10 +394,9 @@ int launch_prefill_tc05(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
     configured = true;
   }
   dim3 grid(n_heads, n_tiles);
-  prefill_attention_tc05_kernel<HD><<<grid, FA_THREADS, FA<HD>::SMEM, stream>>>(
-      mq, mk, mv, block_table, max_blocks, reinterpret_cast<const int4*>(tiles), static_cast<bf16*>(out), out_stride, n_heads,
-      n_kv_heads, page_shift, scale * 1.4426950408889634f, window, status);
-  return launch_status();
+  return launch_streaming(prefill_attention_tc05_kernel<HD>, grid, dim3(FA_THREADS), FA<HD>::SMEM, stream, mq, mk, mv, block_table,
+                          max_blocks, reinterpret_cast<const int4*>(tiles), static_cast<bf16*>(out), out_stride, n_heads,
+                          n_kv_heads, page_shift, scale * 1.4426950408889634f, window, status);
 }
 
 }  // namespace dl

@@ -92,34 +92,63 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 
   if (warp == 0) {
     // TMA producer: the whole warp runs the loop (every lane polls the barrier), one elected lane issues the copies
-    uint32_t it = 0;                               // k-slices issued so far, over all tiles
+    // The first stages' slices of W are requested before the wait on the kernel in front (programmatic dependent
+    // launch): W does not depend on it. x, which does, follows after the wait.
+    auto load_w = [&](int s, int kt, int n0) {
+      unsigned char* b_dst = tiles + static_cast<size_t>(s) * T5_STAGE_BYTES + T5_A_BYTES;
+      const int second_half = swiglu ? gate_rows + n0 : n0 + T5_BN / 2;      // W row of the tile's second half
+      if constexpr (P::CLUSTER == 2) {
+        // this block's half of the W tile, into both blocks (the partner sends the other half)
+        P::load_shared_half(b_dst + rank * (T5_B_BYTES / 2), &map_w, kt * T5_BK, rank == 0 ? n0 : second_half, &full_bar[s]);
+      } else {
+        tma_load_2d(b_dst, &map_w, kt * T5_BK, n0, &full_bar[s]);
+        tma_load_2d(b_dst + T5_B_BYTES / 2, &map_w, kt * T5_BK, second_half, &full_bar[s]);
+      }
+    };
+    auto load_x = [&](int s, int kt, int m0) {
+      tma_load_2d(tiles + static_cast<size_t>(s) * T5_STAGE_BYTES, &map_x, kt * T5_BK, m0, &full_bar[s]);
+    };
+    const int ahead = first_tile < num_tiles ? min(k_tiles, T5_STAGES) : 0;
+    if (ahead > 0) {
+      const int m0 = ((first_tile / tiles_n) * P::CLUSTER + rank) * T5_BM, n0 = (first_tile % tiles_n) * n_per_tile;
+      if (elect_one()) {
+        for (int kt = 0; kt < ahead; ++kt) {
+          mbar_expect_tx(&full_bar[kt], T5_STAGE_BYTES);
+          load_w(kt, kt, n0);
+        }
+      }
+      __syncwarp();
+      pdl_wait();
+      pdl_trigger();
+      if (elect_one()) {
+        for (int kt = 0; kt < ahead; ++kt) load_x(kt, kt, m0);
+      }
+      __syncwarp();
+    } else {
+      pdl_wait();
+      pdl_trigger();
+    }
+    uint32_t it = ahead;                           // k-slices issued so far, over all tiles
     bool ok = true;
     for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
       const int m0 = ((tile / tiles_n) * P::CLUSTER + rank) * T5_BM, n0 = (tile % tiles_n) * n_per_tile;
-      for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+      for (int kt = tile == first_tile ? ahead : 0; kt < k_tiles; ++kt, ++it) {
         const int s = it % T5_STAGES;
         if (it >= T5_STAGES && !warp_wait(&empty_bar[s], ((it / T5_STAGES) & 1) ^ 1, status, T5_ERR_PRODUCER, abort_flag)) {
           ok = false;
           break;
         }
         if (elect_one()) {
-          unsigned char* a_dst = tiles + static_cast<size_t>(s) * T5_STAGE_BYTES;
-          unsigned char* b_dst = a_dst + T5_A_BYTES;
           mbar_expect_tx(&full_bar[s], T5_STAGE_BYTES);
-          tma_load_2d(a_dst, &map_x, kt * T5_BK, m0, &full_bar[s]);
-          const int second_half = swiglu ? gate_rows + n0 : n0 + T5_BN / 2;      // W row of the tile's second half
-          if constexpr (P::CLUSTER == 2) {
-            // this block's half of the W tile, into both blocks (the partner sends the other half)
-            P::load_shared_half(b_dst + rank * (T5_B_BYTES / 2), &map_w, kt * T5_BK, rank == 0 ? n0 : second_half, &full_bar[s]);
-          } else {
-            tma_load_2d(b_dst, &map_w, kt * T5_BK, n0, &full_bar[s]);
-            tma_load_2d(b_dst + T5_B_BYTES / 2, &map_w, kt * T5_BK, second_half, &full_bar[s]);
-          }
+          load_x(s, kt, m0);
+          load_w(s, kt, n0);
         }
         __syncwarp();
       }
     }
   } else if (warp == 1) {
+    pdl_wait();
+    pdl_trigger();
     // MMA issue: the whole warp runs the loop, one elected lane issues the instructions
     constexpr uint32_t idesc = umma_idesc(T5_BM, T5_BN);
     const uint64_t desc0 = umma_desc_sw128(smem_u32(tiles));      // a step along the tiles adds (bytes >> 4)
@@ -154,6 +183,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       __syncwarp();
     }
   } else {
+    pdl_wait();
+    pdl_trigger();
     // epilogue: warp w may touch TMEM lanes 32 * (w % 4) .. + 31
     const int quarter = warp & 3;
     uint32_t local = 0;
@@ -385,13 +416,22 @@ static int t5_launch(const void* x, int ldx, const void* w, void* y, int ldy, in
   cfg.gridDim = dim3(blocks);
   cfg.blockDim = dim3(dl::T5_THREADS);
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = P::CLUSTER;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
+  cudaLaunchAttribute attr[2];
+  int n_attr = 0;
+  if (P::CLUSTER > 1) {
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = P::CLUSTER;
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = 1;
+    ++n_attr;
+  }
+  if (dl::pdl_mode() >= 1) {      // the kernel may start before the one in front has ended: it requests W before its wait
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = P::CLUSTER > 1 ? 1 : 0;
+  cfg.numAttrs = n_attr;
   const int gate_rows = mode == dl::T5_OUT_SWIGLU ? N / 2 : 0;
   if (bn == 256) {
     static bool configured = false;
