@@ -6,7 +6,7 @@ weight-streaming kernel, which can also apply SwiGLU on the way out or leave spl
 the consumer to add: the mma.sync one (csrc/gemm_skinny.cu) up to 8 rows, the tcgen05 one
 (csrc/gemm_stream_tcgen05.cu), which computes the product transposed, from 9 to 16 rows. bfloat16 with
 more rows runs the tcgen05 / TMEM / TMA kernel (csrc/gemm_tcgen05.cu, plain or with the SwiGLU
-epilogue) whenever the product has enough 128 x 256 tiles to fill the GPU; the few shapes in between
+epilogue) whenever the product has enough 128 x 128 tiles to fill the GPU; the few shapes in between
 (17..127 rows with a narrow output, where split-K wins) run the library product (cuBLAS through torch), which is where the reference's GPU path calls a library too
 (ggml_mul_mat, dynacore/src/gpu/ggml_graph.cpp:278-292). Shapes none of these can express (a bias, a K
 that is no multiple of 8) run the plain kernel.
@@ -92,7 +92,7 @@ def tcgen05_ok(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, features: in
     align = 4 if out.dtype == torch.float32 else 8
     if features % align or out.stride(0) % align:
         return False
-    tiles = -(-x.shape[0] // 128) * -(-features // 256)
+    tiles = -(-x.shape[0] // 128) * -(-features // 128)      # at the narrowest tile the kernel may choose
     return tiles >= 96
 
 
