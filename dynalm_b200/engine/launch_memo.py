@@ -71,7 +71,7 @@ class _Record:
     def __init__(self, calls, pending, pending_scale):
         # [(function, arguments, ((argument index, tensor index, offset or None for the tensor itself), ...))]
         self.calls = calls
-        self.library = sum(1 for f, _, _ in calls if f is ops._library_mm_again)
+        self.library = sum(1 for f, _, _ in calls if f is ops.library_mm_again)
         self.own = len(calls) - self.library
         self.pending = pending
         self.pending_scale = pending_scale

@@ -88,7 +88,7 @@ def library_mm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     recording is on."""
     torch.mm(x, w.t(), out=out)
     if _recording is not None:
-        _recording.append((_library_mm_again, (x, w, out)))
+        _recording.append((library_mm_again, (x, w, out)))
 
 
 def note_unrecorded_work() -> None:
@@ -98,7 +98,7 @@ def note_unrecorded_work() -> None:
         _recording.append((None, ()))
 
 
-def _library_mm_again(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> int:
+def library_mm_again(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> int:
     torch.mm(x, w.t(), out=out)
     return 0
 
