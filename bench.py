@@ -275,6 +275,9 @@ def main():
             step_fn.end(("d", r))
 
     ids_out = torch.zeros(max_b, dtype=torch.int32, device="cuda:0")
+    # the step function captures a decode-only launch shape as a CUDA graph when it has come GRAPH_AFTER times: that
+    # many steps of setup come before the warm-up, so that warm-up and timed steps are the steady state
+    PRIME = step_fn.GRAPH_AFTER if step_fn.use_graphs else 0
     results = {}
     launches = 0
     clocks = None
@@ -285,14 +288,14 @@ def main():
         def decode_once():
             logits = step_fn.step([StepEntry(("d", r), toks[r], [0]) for r in range(B)])
             ops.argmax(logits, ids_out[:B])
-        for _ in range(W):
+        for _ in range(PRIME + W):       # PRIME steps of setup (the launch shape becomes a CUDA graph), then W of warm-up
             decode_once()
         if B == args.batch:
-            l0, g0 = ops.LAUNCHES, gemm.LIBRARY_CALLS
+            l0, g0, r0 = ops.LAUNCHES, gemm.LIBRARY_CALLS, getattr(step_fn, "graph_kernel_launches", 0)
             with ClockSampler() as cs:
                 ms = timed(decode_once, K)
             clocks = cs.result
-            launches = ops.LAUNCHES - l0 + getattr(step_fn, "graph_kernel_launches", 0)
+            launches = ops.LAUNCHES - l0 + getattr(step_fn, "graph_kernel_launches", 0) - r0
             lib_calls = gemm.LIBRARY_CALLS - g0
         else:
             ms = timed(decode_once, K)
@@ -301,7 +304,7 @@ def main():
 
     ms_step = results[args.batch]
     value = args.batch / ms_step * 1e3
-    bytes_step = weight_bytes(cfg, args.layers) + args.batch * (HELD + W + K / 2) * kv_bytes_per_token(cfg, args.layers)
+    bytes_step = weight_bytes(cfg, args.layers) + args.batch * (HELD + PRIME + W + K / 2) * kv_bytes_per_token(cfg, args.layers)
     achieved = bytes_step / (ms_step * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": round(achieved / peaks["hbm_gbs"], 4), "of": peaks["source"]}
@@ -313,11 +316,11 @@ def main():
     # ---- decode end to end through the scheduler: host ids in, host ids out, every step ----------------------
     B = args.batch
     for r in range(B):
-        eng.scheduler.submit(Request([int(t) for t in rng.randint(0, vocab, HELD)], max_new_tokens=W + K + 4 * B + 64))
+        eng.scheduler.submit(Request([int(t) for t in rng.randint(0, vocab, HELD)], max_new_tokens=PRIME + W + K + 4 * B + 64))
     while any(s.status != "decode" or s.pending != 1 for s in eng.scheduler.running) or eng.scheduler.waiting \
             or eng.scheduler.incoming:
         eng.scheduler.step()
-    for _ in range(W):
+    for _ in range(PRIME + W):
         eng.scheduler.step()
     h0, d0 = eng.executor.h2d_bytes, eng.executor.d2h_bytes
     torch.cuda.synchronize()
