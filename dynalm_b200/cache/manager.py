@@ -23,7 +23,7 @@ holder lets go of it.
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence
 
 import numpy as np

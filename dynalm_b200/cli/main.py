@@ -12,10 +12,7 @@ at random (`--prompt-len`); output is token ids. After the ids come the referenc
 from __future__ import annotations
 
 import argparse
-import json
-import os
 import sys
-import tempfile
 import time
 
 from .. import __version__

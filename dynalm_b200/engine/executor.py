@@ -5,7 +5,6 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional
 
-import numpy as np
 import torch
 
 from ..errors import EngineError

@@ -22,7 +22,6 @@ import json
 import os
 import sys
 
-import numpy as np
 
 
 def main(argv=None) -> int:

@@ -10,7 +10,7 @@ wanted rows only, in batch order.
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 import os
 import time
 from typing import Dict, Hashable, List, Optional, Sequence

@@ -6,10 +6,9 @@ raises `EngineError` when a launch fails. Tensors must live on the CUDA device; 
 
 from __future__ import annotations
 
-import ctypes
 import contextlib
 import os
-from ctypes import c_double, c_float, c_int, c_longlong, c_void_p
+from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional
 
 import torch

@@ -19,7 +19,7 @@ here replace those flags.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, Optional, Tuple
+from typing import Any, Dict, Optional, Tuple
 
 from ..errors import InvalidArgument, Unsupported
 

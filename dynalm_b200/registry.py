@@ -8,7 +8,7 @@ config.json, with `model_type` as the fallback when that list is absent.
 
 from __future__ import annotations
 
-from typing import Any, Callable, Dict, Mapping, Optional, Protocol, Tuple
+from typing import Any, Dict, Mapping, Optional, Protocol, Tuple
 
 from .config.plan import ModelPlan
 from .errors import Corrupt, Unsupported

@@ -12,7 +12,7 @@ from __future__ import annotations
 import hashlib
 import json
 import os
-from typing import Any, Dict, Mapping, Optional
+from typing import Any, Dict, Mapping
 
 import torch
 

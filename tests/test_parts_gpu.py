@@ -1,8 +1,6 @@
 """Each part alone against the plain function of the same part, and a toy mixer with state of its
 own that is registered, built and stepped without touching the framework."""
 
-import json
-import math
 import os
 
 import numpy as np

@@ -4,7 +4,6 @@ same tokens."""
 
 import hashlib
 
-import pytest
 import torch
 
 from dynalm_b200.cache import CacheManager
