@@ -104,18 +104,18 @@ class LayerLaunchMemo:
     """One step's lists of launches, by kind of layer. `layouts` (run-order entry -> _Layout) and `kinds` outlive
     the step; the model keeps them."""
 
-    def __init__(self, layouts: Dict[int, Tuple[int, _Layout]], kinds: List[int]):
+    def __init__(self, layouts: Dict[int, Tuple[object, _Layout]], kinds: List[int]):
         self.layouts = layouts
         self.kinds = kinds                  # run-order entry -> a number that blocks of equal class and spec share
         self.records: Dict[tuple, Optional[_Record]] = {}
 
     def _layout(self, index: int, block, cache) -> _Layout:
         got = self.layouts.get(index)
-        if got is None or got[0] != id(cache):
+        if got is None or got[0] is not cache:             # the view is kept, so that no other object can take its place
             tensors = owned_tensors(block)
             if cache is not None:
                 tensors = tensors + list(cache.arrays) + ([cache.block_table] if cache.block_table is not None else [])
-            got = (id(cache), _Layout(tensors))
+            got = (cache, _Layout(tensors))
             self.layouts[index] = got
         return got[1]
 
