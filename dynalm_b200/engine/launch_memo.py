@@ -20,6 +20,10 @@ What makes this safe:
   layer's tensor (a library product is written down with its tensors, and the layer's own tensor among them is
   exchanged); all other arguments (shared scratch, the step's index arrays, sizes) stay.
 
+The addresses of a layer's tensors are read once, at the layer's first step, and kept by the model
+(`Decoder._run_layouts`): a part's tensors may be changed in place afterwards, but a part that gets another tensor
+object must be followed by `Decoder.forget_layouts()`.
+
 The reference has no counterpart: its layer loop is compiled C++ (dynalm/src/model/transformer.cpp:596-699).
 """
 

@@ -38,6 +38,11 @@ class Decoder:
                            for run in self.order]
         self._run_layouts: Dict[int, tuple] = {}
 
+    def forget_layouts(self) -> None:
+        """To be called when a part has been given another tensor object after the model has run a step: the
+        addresses that engine/launch_memo.py remembers for every layer are read again."""
+        self._run_layouts.clear()
+
     @property
     def graph_safe(self) -> bool:
         """True when every mixer and feed-forward says its launches depend only on what
