@@ -43,6 +43,15 @@ class Runtime:
         self.max_requests = int(max_requests)      # the most rows a decode-only step can bring
         self._buffers: Dict[Tuple, torch.Tensor] = {}
         self._views: Dict[Tuple, torch.Tensor] = {}      # (name, shape, dtype) -> the first rows of a buffer
+        self._side_stream = None
+
+    @property
+    def side_stream(self) -> int:
+        """The handle of a second stream, for a kernel that may run beside the kernels of the step's own stream
+        (ops.stream_fork / ops.stream_join put it in order)."""
+        if self._side_stream is None:
+            self._side_stream = torch.cuda.Stream(device=self.device)
+        return self._side_stream.cuda_stream
 
     def buffer(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype = None) -> torch.Tensor:
         dtype = dtype or self.dtype

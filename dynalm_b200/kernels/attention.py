@@ -51,6 +51,7 @@ def decode_plan(ctx, spec, rows: int = 0) -> int:
     return decode_splits(rows or ctx.num_tokens, spec.num_heads, spec.num_kv_heads, bucket, decode_uses_tensor_cores(spec))
 
 
+SIDE_BY_SIDE = os.environ.get("DYNALM_ATTENTION_SIDE_BY_SIDE", "1") != "0"    # 0: the two attention kernels of a mixed step one after the other
 MIXED_DECODE_ROWS = 1      # from this many leading decode rows on, a mixed step runs them through the decode kernel
 
 
@@ -99,14 +100,25 @@ def paged_attention(qkv: torch.Tensor, cache, ctx, out: torch.Tensor, spec, runt
     if not use_prefill_kernel(ctx, spec, qkv, cache.page_size):
         return False
     n_tiles = ctx.num_q_tiles
+    side = None
     if ctx.leading_decode_rows >= MIXED_DECODE_ROWS and decode_kernel_takes(spec, qkv.dtype, cache.page_size):
         # a mixed step: the decode rows at its head go through the split-KV kernel (as a one-row query tile each
-        # of them would occupy a whole block of the prompt kernel), the prompt portions through the flash kernel
-        _decode_rows(qkv, cache, ctx, out, spec, runtime, ctx.leading_decode_rows)
+        # of them would occupy a whole block of the prompt kernel), the prompt portions through the flash kernel.
+        # The two kernels read and write different rows and each fills a part of the GPU only: they run side by side,
+        # the decode rows on a second stream.
         n_tiles = ctx.num_prompt_q_tiles
+        if SIDE_BY_SIDE and n_tiles > 0:
+            side = runtime.side_stream
+            ops.stream_fork(side)
+            with ops.on_stream(side):
+                _decode_rows(qkv, cache, ctx, out, spec, runtime, ctx.leading_decode_rows)
+        else:
+            _decode_rows(qkv, cache, ctx, out, spec, runtime, ctx.leading_decode_rows)
     if n_tiles > 0:
         kernel = (ops.paged_attention_prefill_tcgen05 if use_prefill_tcgen05(spec, qkv, out, cache.page_size)
                   else ops.paged_attention_prefill)
         kernel(qkv, k_cache, v_cache, cache.block_table, ctx.q_tiles, n_tiles, out, spec.num_heads,
                spec.num_kv_heads, spec.head_dim, cache.page_size, float(spec.scale), spec.window)
+    if side is not None:
+        ops.stream_join(side)
     return True

@@ -57,6 +57,7 @@ _SIGNATURES = {
         "dl_sample_temperature": [_P, _I, _I, _I, _P, _P, _P, _P],
         "dl_feedback_tokens": [_P, _P, _P, _I, _P],
     },
+    "streams": {"dl_stream_fork": [_P, _P], "dl_stream_join": [_P, _P]},
 }
 
 _funcs = {}
@@ -80,6 +81,33 @@ def _fn(library: str, name: str):
         calls.append((f, args))
         return f(*args)
     return recorded
+
+
+@contextlib.contextmanager
+def on_stream(handle: int):
+    """Inside the block every launch of this module goes to the stream with this handle."""
+    global _pinned_stream
+    previous = _pinned_stream
+    _pinned_stream = int(handle)
+    try:
+        yield
+    finally:
+        _pinned_stream = previous
+
+
+def stream_fork(side: int) -> None:
+    """What the stream `side` is given from now on runs after everything the current stream has been given so far
+    (csrc/streams.cu)."""
+    code = _fn("streams", "dl_stream_fork")(_stream(), int(side))
+    if code != 0:
+        raise EngineError(f"stream_fork: CUDA error {code}")
+
+
+def stream_join(side: int) -> None:
+    """What the current stream is given from now on runs after everything `side` has been given so far."""
+    code = _fn("streams", "dl_stream_join")(_stream(), int(side))
+    if code != 0:
+        raise EngineError(f"stream_join: CUDA error {code}")
 
 
 def library_mm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
