@@ -76,7 +76,7 @@ class _Record:
         # [(function, arguments, ((argument index, tensor index, offset or None for the tensor itself), ...))]
         self.calls = calls
         self.library = sum(1 for f, _, _ in calls if f is ops.library_mm_again)
-        self.own = len(calls) - self.library
+        self.own = sum(1 for f, _, _ in calls if ops.counts_as_kernel(f))
         self.pending = pending
         self.pending_scale = pending_scale
 

@@ -95,6 +95,12 @@ def on_stream(handle: int):
         _pinned_stream = previous
 
 
+def counts_as_kernel(f) -> bool:
+    """Whether a recorded function launches a kernel of this package (a library product and the ordering of two
+    streams do not)."""
+    return f is not library_mm_again and f is not _funcs.get("dl_stream_fork") and f is not _funcs.get("dl_stream_join")
+
+
 def stream_fork(side: int) -> None:
     """What the stream `side` is given from now on runs after everything the current stream has been given so far
     (csrc/streams.cu)."""
