@@ -1,0 +1,59 @@
+"""Which kernel a matrix product and a decode attention go to, by shape: the decisions of kernels/gemm.py and
+kernels/attention.py on tensors that are never touched (no GPU needed)."""
+
+import torch
+
+from dynalm_b200.kernels import attention, gemm
+
+
+def _xw(rows, n, k, dtype=torch.bfloat16):
+    return torch.zeros(rows, k, dtype=dtype), torch.zeros(n, k, dtype=dtype)
+
+
+def test_few_rows_go_to_the_weight_streaming_products():
+    for rows in (1, 8):
+        x, w = _xw(rows, 2048, 2048)
+        assert gemm.skinny_ok(x, w) and not gemm.use_stream(x, w)          # mma.sync up to 8 rows
+    for rows in (9, 16):
+        x, w = _xw(rows, 2048, 2048)
+        assert gemm.use_stream(x, w)                                        # tcgen05, computed transposed, 9 to 16
+    x, w = _xw(17, 2048, 2048)
+    assert not gemm.use_stream(x, w) and not gemm.skinny_ok(x, w)
+    # a K that is no multiple of 8, or float32, takes neither
+    x, w = _xw(4, 256, 100)
+    assert not gemm.skinny_ok(x, w) and not gemm.use_stream(x, w)
+    x, w = _xw(12, 256, 128, torch.float32)
+    assert not gemm.skinny_ok(x, w) and not gemm.use_stream(x, w)
+
+
+def test_k_splits_fill_the_gpu_but_stay_few():
+    # o and down of the 1B shape at 9 to 16 rows: 16 feature tiles, at most 6 splits, each of at least 256 of K
+    assert gemm.stream_split_count(2048, 2048) == 6
+    assert gemm.stream_split_count(2048, 8192) == 6
+    assert gemm.stream_split_count(2048, 512) == 2
+    assert gemm.stream_split_count(128256, 2048) == 1
+    # the mma.sync kernel: up to 8 blocks along K, none for a wide output
+    assert gemm.split_count(2048, 2048, 8) == 3
+    assert gemm.split_count(16384, 2048, 8) == 1
+
+
+def test_the_tcgen05_product_needs_96_tiles_at_its_narrowest_width():
+    def ok(rows, n, k=2048):
+        x, w = _xw(rows, n, k)
+        return gemm.tcgen05_ok(x, w, torch.zeros(rows, n, dtype=torch.bfloat16), n)
+    assert ok(2048, 2048) and ok(2048, 16384)
+    assert ok(544, 3072)                    # 5 row blocks x 24 tiles of 128: a 512-token portion's O and down
+    assert not ok(64, 2048)                 # a decode batch of 64: the library's split-K kernel
+    assert ok(17, 128256)                   # the vocabulary product from 17 rows
+    assert not ok(2048, 2052)               # rows of the output must be 16-byte aligned
+
+
+def test_decode_attention_splits():
+    # batch 8 of the 1B shape at 2,048 keys: 64 blocks -> 3 splits; batch 64: enough blocks already
+    assert attention.decode_splits(8, 32, 8, 2048) == 3
+    assert attention.decode_splits(64, 32, 8, 2048) == 1
+    # one row: as many splits as the cluster merges, more only when a split still holds 1,024 keys
+    assert attention.decode_splits(1, 32, 8, 2048) == 8
+    assert attention.decode_splits(1, 32, 8, 65536) > 8
+    # never less than 128 keys per split
+    assert attention.decode_splits(1, 32, 8, 256) == 2
