@@ -226,6 +226,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     }
   }
   // common exit: every role arrives here, with or without a timeout
+  drain_after_abort(abort_flag);
   tcgen05_before_sync();
   __syncthreads();
   if (warp == 1) {

@@ -333,6 +333,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     }
   }
   // common exit: every role arrives here, with or without a timeout
+  drain_after_abort(abort_flag);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if constexpr (P::CLUSTER == 2) cluster_sync_all();      // nobody leaves while its partner may still send to it

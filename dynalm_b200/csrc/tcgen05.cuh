@@ -213,6 +213,13 @@ __device__ __forceinline__ void store_rows_pieces(const uint4 (&lo)[4], const ui
   __syncwarp();
 }
 
+// After a wait has timed out (abort_flag set by mbar_wait): before the block ends and its shared memory goes to
+// another block, its copies still in flight get time to land. Bounded: about 4 ms.
+__device__ __forceinline__ void drain_after_abort(volatile int* abort_flag) {
+  if (*abort_flag != 0)
+    for (int spin = 0; spin < (1 << 16); ++spin) __nanosleep(64);
+}
+
 // The rank of this block in its thread-block cluster, and a barrier over all threads of the cluster.
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
