@@ -13,6 +13,10 @@ Input, one JSON object per line on standard input:
 entries of a step run as one batch. `end`: requests that are finished after this step. For a step
 that wants something, `<out>/<step>.f32` receives the logits [wanted, vocab] as little-endian
 float32, in the order of the entries and of `want`. After every step a line `done <step>` is printed.
+
+`--summary FILE` adds a text line per wanted place, with what tools/ref_model.py of the reference reports of a
+logits row (:236-247): the id of the largest logit (ties: the lowest id), the 8 largest as id:logit, and the sum and
+the sum of squares of the row in float64. Nothing is sampled and nothing is fed back: it describes the file.
 """
 
 from __future__ import annotations
@@ -34,6 +38,7 @@ def main(argv=None) -> int:
                     help="most tokens live requests hold at any time (each request rounded up to a page)")
     ap.add_argument("--page-size", type=int, default=None, help="tokens per cache page (default: the engine's)")
     ap.add_argument("--max-requests", type=int, default=8, help="most requests alive at once")
+    ap.add_argument("--summary", default=None, help="also write a text line per wanted place to this file")
     args = ap.parse_args(argv)
 
     import torch
@@ -53,6 +58,21 @@ def main(argv=None) -> int:
         print(f"trace_run: {e}", file=sys.stderr)
         return 1
     step_fn = built.step_fn
+    summary = open(args.summary, "w", newline="\n") if args.summary else None
+
+    def describe(step, entries, rows):
+        import numpy as np
+        r = 0
+        for e in entries:
+            for place in e.want:
+                row = rows[r]
+                order = np.lexsort((np.arange(row.size), -row))[:8]        # largest first, ties by lowest id
+                wide = row.astype(np.float64)
+                summary.write(f"step {step} id {e.request} place {place} argmax {int(order[0])} top "
+                              + " ".join(f"{int(i)}:{row[i]:.6f}" for i in order)
+                              + f" stats {float(wide.sum()):.6f} {float((wide * wide).sum()):.6f}\n")
+                r += 1
+        summary.flush()
 
     for line in sys.stdin:
         line = line.strip()
@@ -67,6 +87,8 @@ def main(argv=None) -> int:
                 if logits is not None:
                     host = logits.to("cpu", torch.float32).numpy().astype("<f4", copy=False)
                     host.tofile(os.path.join(args.out, f"{step}.f32"))
+                    if summary is not None:
+                        describe(step, entries, host)
                 else:
                     torch.cuda.current_stream().synchronize()
             if ops.gemm_tcgen05_status() != 0:

@@ -130,12 +130,12 @@ def run_plan_in_process(step_fn, plan: Plan) -> Dict[int, np.ndarray]:
 
 
 def run_plan_trace_run(model_dir: str, dtype: str, plan: Plan, out_dir: str, max_tokens: int, vocab: int,
-                       env=None) -> Dict[int, np.ndarray]:
+                       env=None, summary: str = None) -> Dict[int, np.ndarray]:
     """Through bin/trace_run as a user would: one process, steps on stdin, files out."""
     text = "".join(json.dumps(s) + "\n" for s in plan.steps)
     proc = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype, "--out",
-                           out_dir, "--max-tokens", str(max_tokens)], input=text, capture_output=True, text=True,
-                          env=env, timeout=900)
+                           out_dir, "--max-tokens", str(max_tokens)] + (["--summary", summary] if summary else []),
+                          input=text, capture_output=True, text=True, env=env, timeout=900)
     assert proc.returncode == 0, f"trace_run failed:\n{proc.stdout[-2000:]}\n{proc.stderr[-4000:]}"
     done = [l for l in proc.stdout.splitlines() if l.startswith("done ")]
     assert [int(l.split()[1]) for l in done] == [s["step"] for s in plan.steps]

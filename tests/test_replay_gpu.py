@@ -64,8 +64,19 @@ def test_trace_run_program(dtype, tiny_folders, plain_logits, tmp_path):
     reqs, plain = plain_logits[name]
     plan = plan_mixed(reqs, seed=7)
     vocab = TINY[name][0]["vocab_size"]
-    got = run_plan_trace_run(tiny_folders[name], dtype, plan, str(tmp_path / "out"), plan.max_live_tokens(64), vocab)
+    summary = str(tmp_path / "summary.txt")
+    got = run_plan_trace_run(tiny_folders[name], dtype, plan, str(tmp_path / "out"), plan.max_live_tokens(64), vocab,
+                             summary=summary)
     compare(plan, got, plain, *TOL[dtype], f"trace_run/{dtype}")
+    # the text summary describes the files: one line per wanted place, the largest logit and the row's sums
+    lines = open(summary).read().splitlines()
+    assert len(lines) == sum(len(rows) for rows in plan.rows.values())
+    first_step = min(plan.rows)
+    words = lines[0].split()
+    assert words[:2] == ["step", str(first_step)] and words[6] == "argmax"
+    row = got[first_step][0]
+    assert int(words[7]) == int(np.argmax(row))
+    assert abs(float(words[-2]) - float(row.astype(np.float64).sum())) <= 1e-3 * max(1.0, abs(float(row.sum())))
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
