@@ -365,3 +365,37 @@ def test_decode_protected_prefill_budget_halves_and_doubles():
     cfg.decode_protect = False
     s.step()
     assert sum(n for _, _, n, _ in ex.batches[-1] if n > 1) == 256
+
+
+def test_a_failed_forward_fails_its_batch_only_and_gives_the_pages_back():
+    """The executor raises for one step (as a kernel that reports an error does): the requests of that batch end
+    with an error that names it, their pages are free again, and requests submitted afterwards run as usual
+    (dynalm/src/scheduler/scheduler.cpp:663-666)."""
+    from dynalm_b200.errors import EngineError
+
+    class FailsOnce(FakeExecutor):
+        fail_at = 3
+
+        def run(self, batch):
+            self.fail_at -= 1
+            if self.fail_at == 0:
+                raise EngineError("a product gave up waiting on a barrier")
+            return super().run(batch)
+
+    ex = FailsOnce(kv_tokens=1024)
+    s = Scheduler(ex, SchedulerConfig(max_running=4, max_batch_tokens=256))
+    first = [s.submit(Request(p, max_new_tokens=6)) for p in prompts(3, [20, 33, 7])]
+    events = run_all(s)
+    toks, final = collect(events)
+    failed = [r for r in first if final[r].status == ERROR]
+    assert failed, "the failing step held at least one request"
+    for r in failed:
+        assert "forward failed" in final[r].error and "barrier" in final[r].error
+    for r in first:
+        if r not in failed:
+            assert final[r].status == FINISHED and len(toks[r]) == 6
+    assert not ex.live and ex.cache.free_pages == ex.cache.num_pages
+    ex.cache.check()
+    later = s.submit(Request(list(range(40)), max_new_tokens=5))
+    toks, final = collect(run_all(s))
+    assert final[later].status == FINISHED and len(toks[later]) == 5
