@@ -12,6 +12,8 @@ at random (`--prompt-len`); output is token ids. After the ids come the referenc
 from __future__ import annotations
 
 import argparse
+import contextlib
+import os
 import sys
 import time
 
@@ -82,7 +84,7 @@ def cmd_run(argv, quiet: bool) -> int:
         sys.stderr.write(USAGE)
         return 0
     import numpy as np
-    from ..engine import Engine, Request, SchedulerConfig
+    from ..engine import Engine, SchedulerConfig
     from ..errors import EngineError
     from ..sampling import SamplingParams
 
@@ -111,6 +113,18 @@ def cmd_run(argv, quiet: bool) -> int:
                          repetition_penalty=args.repeat_penalty, presence_penalty=args.presence_penalty,
                          frequency_penalty=args.frequency_penalty, penalty_last_n=args.repeat_last_n,
                          seed=None if args.seed is None else args.seed + i) for i in range(len(prompts))]
+    from ..engine import profile
+    timing = (profile.kernel_times(engine.executor.step_fn) if os.environ.get("DYNALM_FORWARD_PROFILE", "0") != "0"
+              else contextlib.nullcontext())
+    with timing as kernel_times:
+        rc = _generate(args, engine, prompts, sp, quiet)
+    if kernel_times is not None:
+        print("[kernels]\n" + profile.table(kernel_times.totals()), file=sys.stderr)
+    return rc
+
+
+def _generate(args, engine, prompts, sp, quiet: bool) -> int:
+    from ..engine import Request
     t0 = time.perf_counter()
     ids = [engine.scheduler.submit(Request(p, args.max_tokens, s, tuple(args.stop_id))) for p, s in zip(prompts, sp)]
     out = {i: [] for i in ids}

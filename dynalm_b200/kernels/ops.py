@@ -73,6 +73,8 @@ def _fn(library: str, name: str):
         f.argtypes = _SIGNATURES[library][name]
         f.restype = c_int
         _funcs[name] = f
+    if _timing is not None:
+        return _timing.timed(name, f)
     if _recording is None:
         return f
     calls = _recording
@@ -119,6 +121,9 @@ def stream_join(side: int) -> None:
 def library_mm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """out = x w^T by the library (cuBLAS through torch), written down like a launch of this module's when a
     recording is on."""
+    if _timing is not None:
+        _timing.timed("library product (torch.mm)", library_mm_again)(x, w, out)
+        return
     torch.mm(x, w.t(), out=out)
     if _recording is not None:
         _recording.append((library_mm_again, (x, w, out)))
@@ -134,6 +139,47 @@ def note_unrecorded_work() -> None:
 def library_mm_again(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> int:
     torch.mm(x, w.t(), out=out)
     return 0
+
+
+_timing: Optional["KernelTimes"] = None
+
+
+class KernelTimes:
+    """Inside the block every kernel launch of this module stands between two CUDA events on its stream;
+    `totals()` then gives {C entry point: (launches, milliseconds)}. The counterpart of the reference's per-op marks
+    in its forward pass (`ForwardProfile`, dynalm/src/model/transformer.h:34-49): off unless asked for, and meant
+    for steps that run launch by launch (engine/profile.py sees to that)."""
+
+    def __enter__(self):
+        global _timing
+        self.marks: list = []
+        self._outer = _timing
+        _timing = self
+        return self
+
+    def __exit__(self, *exc):
+        global _timing
+        _timing = self._outer
+        return False
+
+    def timed(self, name: str, f):
+        def call(*args):
+            stream = torch.cuda.ExternalStream(_stream())
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record(stream)
+            code = f(*args)
+            end.record(stream)
+            self.marks.append((name, begin, end))
+            return code
+        return call
+
+    def totals(self) -> dict:
+        torch.cuda.synchronize()
+        out: dict = {}
+        for name, begin, end in self.marks:
+            n, ms = out.get(name, (0, 0.0))
+            out[name] = (n + 1, ms + begin.elapsed_time(end))
+        return out
 
 
 class Recording:

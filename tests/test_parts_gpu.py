@@ -417,3 +417,32 @@ def test_toy_position_encoding_and_routed_feed_forward(tmp_path):
             p0 += c
         got = np.concatenate(got)
         assert np.abs(got - ref).max() <= 5e-5 * max(1.0, np.abs(ref).max()), f"cuts {cuts}"
+
+
+def test_kernel_times_of_a_step(tiny_folders):
+    """engine/profile.py: inside `kernel_times` a step runs launch by launch with every launch between two events;
+    the table names the kernels with their counts, and the logits are those of the same step run as usual."""
+    import numpy as np
+    from tiny_configs import TINY
+    from dynalm_b200.engine import StepEntry, build, profile
+    cfg = TINY["b"][0]
+    layers = cfg["num_hidden_layers"]
+    rng = np.random.RandomState(3)
+    prompt = [int(t) for t in rng.randint(0, cfg["vocab_size"], 40)]
+    tail = [int(t) for t in rng.randint(0, cfg["vocab_size"], 5)]
+
+    def run(profiled):
+        built = build(tiny_folders["b"], dtype="bfloat16", kv_tokens=256, max_batch_tokens=64, max_requests=4)
+        fn = built.step_fn
+        fn.step([StepEntry("a", prompt, [])])
+        if not profiled:
+            return fn.step([StepEntry("a", tail[:1], [0]), StepEntry("b", tail, [4])]).float().cpu().numpy(), None
+        with profile.kernel_times(fn) as times:
+            logits = fn.step([StepEntry("a", tail[:1], [0]), StepEntry("b", tail, [4])]).float().cpu().numpy()
+        return logits, times.totals()
+    plain, _ = run(False)
+    got, totals = run(True)
+    assert np.array_equal(plain, got)
+    assert totals["dl_rmsnorm"][0] == 2 * layers + 1 and totals["dl_embed"][0] == 1
+    assert all(ms > 0.0 for _, ms in totals.values())
+    assert "dl_rmsnorm" in profile.table(totals)
