@@ -60,4 +60,9 @@ def build(model_dir: Optional[str] = None, *, config_obj: Optional[Mapping[str, 
     kv = int(kv_tokens or ctx_len)
     cache = CacheManager(model.cache_specs(), page_size, kv, max_requests, ctx_len, runtime.device, compute)
     step_fn = StepFunction(model, cache, runtime, max_requests)
+    if compute == torch.bfloat16:
+        # the library product that a few shapes still go to (kernels/gemm.py) sets itself up at its first call, which
+        # takes about 140 ms: here, not inside the first request
+        warm = torch.zeros(32, 64, dtype=compute, device=runtime.device)
+        torch.mm(warm, warm.t())
     return BuiltModel(config, plan, runtime, model, cache, step_fn)
