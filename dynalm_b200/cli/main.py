@@ -34,6 +34,7 @@ USAGE = """usage: dynalm run <model> (--tokens IDS | -p IDS | --prompt-len N) [o
   --dtype D             bf16 | f32: the same choice by name
   --max-running N       most requests decoded together (default 64)
   --chunk N             most prompt tokens of one request per step (default 128)
+  --solo-prefill-chunk N  the same for a lone prompt in a step without decode rows (default 256; 0 = off)
   --stop-id ID          end-of-generation token id (repeatable)
   --no-stream           print only the final ids
 sampling (default: greedy):
@@ -63,6 +64,7 @@ def _run_parser() -> argparse.ArgumentParser:
     ap.add_argument("--dtype", choices=["bf16", "f32", "bfloat16", "float32"], default=None)
     ap.add_argument("--max-running", type=int, default=64)
     ap.add_argument("--chunk", type=int, default=128)
+    ap.add_argument("--solo-prefill-chunk", type=int, default=256)
     ap.add_argument("--stop-id", type=int, action="append", default=[])
     ap.add_argument("--no-stream", action="store_true")
     ap.add_argument("--temp", "--temperature", dest="temp", type=float, default=0.0)
@@ -96,7 +98,8 @@ def cmd_run(argv, quiet: bool) -> int:
         print("dynalm: --kv f16 is not offered; the cache is bf16 (or f32 with --mode exact)", file=sys.stderr)
         return 2
     try:
-        sched = SchedulerConfig(max_running=args.max_running, max_prefill_chunk=args.chunk, max_batch_tokens=args.batch)
+        sched = SchedulerConfig(max_running=args.max_running, max_prefill_chunk=args.chunk, max_batch_tokens=args.batch,
+                                solo_prefill_chunk=args.solo_prefill_chunk)
         engine = Engine(args.model, dtype=dtype, ctx=args.ctx, batch=args.batch, max_running=args.max_running,
                         scheduler=sched)
     except EngineError as e:

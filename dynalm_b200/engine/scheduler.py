@@ -59,12 +59,20 @@ class SchedulerConfig:
     decode_protect: bool = True
     protected_prefill_min: int = 32
     decode_latency_target: float = 6.0
+    # Solo prefill (dynalm/src/scheduler/scheduler.h:165-187, scheduler.cpp:436-472): a step without decode rows in
+    # which exactly one request is prefilling gives it portions of solo_prefill_chunk rows under a budget of at least
+    # that many, instead of max_prefill_chunk and prefill_token_budget: fewer, larger products for a lone prompt.
+    # With several prompts prefilling the step is as ever, unless solo_prefill_split shares the solo budget among
+    # them (each up to max(max_prefill_chunk, solo_prefill_chunk / prompts)). 0 = off.
+    solo_prefill_chunk: int = 0
+    solo_prefill_split: bool = False
 
     def clamp(self) -> None:
         # both budgets must fit one forward pass (scheduler.cpp:91-96)
         self.decode_token_budget = max(1, min(self.decode_token_budget, self.max_batch_tokens - 1))
         self.prefill_token_budget = max(1, min(self.prefill_token_budget,
                                                self.max_batch_tokens - self.decode_token_budget))
+        self.solo_prefill_chunk = max(0, min(self.solo_prefill_chunk, self.max_batch_tokens))
 
 
 @dataclass
@@ -173,6 +181,7 @@ class SchedulerStats:
     steps_decode_only: int = 0
     steps_prefill_only: int = 0
     steps_mixed: int = 0
+    steps_solo_prefill: int = 0           # steps in which a lone prompt got the solo chunk
     admitted: int = 0
     finished: int = 0
     failed: int = 0
@@ -375,13 +384,22 @@ class Scheduler:
             any_decode = any(is_decode(s) for s in order)
             prefill_budget = (min(cfg.prefill_token_budget, self._mixed_prefill_budget)
                               if cfg.decode_protect and any_decode else cfg.prefill_token_budget)
+            prefill_chunk = cfg.max_prefill_chunk
+            prefilling = sum(1 for s in order if not is_decode(s))
+            solo = (cfg.solo_prefill_chunk > 0 and not any_decode and prefilling > 0
+                    and (prefilling == 1 or cfg.solo_prefill_split))
+            if solo:
+                prefill_budget = max(cfg.prefill_token_budget, cfg.solo_prefill_chunk)
+                prefill_chunk = cfg.solo_prefill_chunk
+                if prefilling > 1:
+                    prefill_chunk = max(cfg.max_prefill_chunk, cfg.solo_prefill_chunk // prefilling, 1)
             for seq in order:
                 decode = is_decode(seq)
                 used = decode_rows if decode else prefill_rows
                 budget = cfg.decode_token_budget if decode else prefill_budget
                 n = min(seq.pending, budget - used)
-                if not decode and cfg.max_prefill_chunk > 0:
-                    n = min(n, cfg.max_prefill_chunk)
+                if not decode and prefill_chunk > 0:
+                    n = min(n, prefill_chunk)
                 if n <= 0:
                     continue
                 try:
@@ -400,6 +418,8 @@ class Scheduler:
                     prefill_rows += n
             if not restart:
                 self._last_rows = (decode_rows, prefill_rows)
+                if solo and prefill_rows > 0:
+                    self.stats.steps_solo_prefill += 1
                 return batch
         return []
 

@@ -399,3 +399,50 @@ def test_a_failed_forward_fails_its_batch_only_and_gives_the_pages_back():
     later = s.submit(Request(list(range(40)), max_new_tokens=5))
     toks, final = collect(run_all(s))
     assert final[later].status == FINISHED and len(toks[later]) == 5
+
+
+def test_a_lone_prompt_gets_the_solo_chunk():
+    """solo_prefill_chunk (dynalm/src/scheduler/scheduler.cpp:436-472): a step without decode rows with exactly one
+    request prefilling gives it the larger portion; two prompts prefilling get the regular portions unless the solo
+    budget is split; steps with decode rows are as ever. The tokens are the same either way."""
+    def rows(ex):
+        return [[(n, sample) for _, _, n, sample in b] for b in ex.batches]
+
+    base = dict(max_running=4, max_batch_tokens=512, prefill_token_budget=64, max_prefill_chunk=32)
+    ex = FakeExecutor()
+    s = Scheduler(ex, SchedulerConfig(solo_prefill_chunk=200, **base))
+    a = s.submit(Request(list(range(450)), max_new_tokens=3))
+    toks_solo, _ = collect(run_all(s))
+    assert [b[0][0] for b in rows(ex)[:3]] == [200, 200, 50]          # 450 = 200 + 200 + 50, then decoding
+    assert s.stats.steps_solo_prefill == 3
+    ex0 = FakeExecutor()
+    s0 = Scheduler(ex0, SchedulerConfig(**base))
+    a0 = s0.submit(Request(list(range(450)), max_new_tokens=3))
+    toks_plain, _ = collect(run_all(s0))
+    assert toks_solo[a] == toks_plain[a0] and rows(ex0)[0] == [(32, False)] and s0.stats.steps_solo_prefill == 0
+
+    # two prompts prefilling: regular portions under the regular budget ...
+    ex2 = FakeExecutor()
+    s2 = Scheduler(ex2, SchedulerConfig(solo_prefill_chunk=200, **base))
+    s2.submit(Request(list(range(100)), max_new_tokens=2))
+    s2.submit(Request(list(range(100, 190)), max_new_tokens=2))
+    run_all(s2)
+    assert rows(ex2)[0] == [(32, False), (32, False)]
+    # ... or the solo budget shared among them
+    ex3 = FakeExecutor()
+    s3 = Scheduler(ex3, SchedulerConfig(solo_prefill_chunk=200, solo_prefill_split=True, **base))
+    s3.submit(Request(list(range(150)), max_new_tokens=2))
+    s3.submit(Request(list(range(100, 250)), max_new_tokens=2))
+    run_all(s3)
+    assert rows(ex3)[0] == [(100, False), (100, False)]
+
+    # beside a decoding request a new prompt gets the regular portion
+    ex4 = FakeExecutor()
+    s4 = Scheduler(ex4, SchedulerConfig(solo_prefill_chunk=200, **base))
+    s4.submit(Request(list(range(10)), max_new_tokens=30))
+    for _ in range(3):
+        s4.step()
+    s4.submit(Request(list(range(300)), max_new_tokens=2))
+    run_all(s4)
+    mixed = [b for b in rows(ex4) if len(b) == 2]
+    assert mixed and all(b[1][0] <= 32 for b in mixed if b[0] == (1, True))
