@@ -120,6 +120,7 @@ class SequenceState:
         self.sampler: Optional[Sampler] = None      # made once the request has passed validation
         self.cancel_requested = False
         self.deadline: float = 0.0                  # on the scheduler's clock; 0 = none
+        self.trace: Optional["RequestTrace"] = None  # filled along the way when the scheduler keeps traces
 
     @property
     def pending(self) -> int:
@@ -176,6 +177,25 @@ class StepTrace:
 
 
 @dataclass
+class RequestTrace:
+    """One request's life, kept when it ends if the scheduler keeps traces (dynalm/src/scheduler/scheduler.h:113-125).
+    Times are on the scheduler's clock, in seconds; 0 = never happened."""
+
+    id: int
+    prompt_tokens: int
+    generated: int = 0
+    submit_s: float = 0.0
+    admit_s: float = 0.0
+    first_scheduled_s: float = 0.0
+    first_token_s: float = 0.0
+    finish_s: float = 0.0
+    prefill_steps: int = 0               # steps in which it computed prompt rows (again after a preemption)
+    prefill_forward_ms: float = 0.0      # forward time of those steps
+    preemptions: int = 0
+    status: str = WAITING
+
+
+@dataclass
 class SchedulerStats:
     steps: int = 0
     steps_decode_only: int = 0
@@ -210,6 +230,8 @@ class Scheduler:
         self.by_id: Dict[int, SequenceState] = {}
         self.stats = SchedulerStats()
         self.trace: Optional[List[StepTrace]] = [] if keep_trace else None
+        self.request_traces: Optional[List[RequestTrace]] = [] if keep_trace else None      # in the order they end
+        self._last_forward_ms = 0.0
         self._next_id = 1
         self._arrivals = 0
         self._admit_counter = 0
@@ -230,6 +252,8 @@ class Scheduler:
         seq = SequenceState(rid, req, self._arrivals)
         if req.timeout_ms > 0:
             seq.deadline = self.clock() + req.timeout_ms / 1000.0
+        if self.request_traces is not None:
+            seq.trace = RequestTrace(rid, seq.prompt_len, submit_s=self.clock())
         self.by_id[rid] = seq
         self.incoming.append(seq)
         if req.on_event is not None:
@@ -252,6 +276,11 @@ class Scheduler:
         events.append(self._final_event(seq, None))
 
     def _final_event(self, seq: SequenceState, token: Optional[int]) -> Event:
+        if seq.trace is not None and self.request_traces is not None:
+            t = seq.trace
+            t.generated, t.preemptions, t.status, t.finish_s = seq.generated, seq.preemptions, seq.status, self.clock()
+            self.request_traces.append(t)
+            seq.trace = None
         return Event(seq.id, token, True, seq.status, seq.finish_reason, seq.error, seq.prompt_len, seq.generated)
 
     def _drain_incoming(self, events: List[Event]) -> None:
@@ -342,6 +371,8 @@ class Scheduler:
             seq.admit_order = self._admit_counter
             if seq.preemptions == 0:
                 self.stats.admitted += 1
+                if seq.trace is not None:
+                    seq.trace.admit_s = self.clock()
             seq.status = PREFILL
             self.running.append(seq)
             admitted.append(seq.id)
@@ -524,6 +555,7 @@ class Scheduler:
 
     def _account(self, batch: List[BatchItem], ms: float) -> None:
         self.stats.steps += 1
+        self._last_forward_ms = ms
         n_decode = sum(1 for b in batch if len(b.tokens) == 1 and b.seq.status == DECODE)
         n_prefill = sum(len(b.tokens) for b in batch) - n_decode
         if n_prefill == 0:
@@ -554,12 +586,20 @@ class Scheduler:
             seq = b.seq
             if seq.terminal:
                 continue            # ended (stop token, failure) while this batch was already on its way
+            if seq.trace is not None:
+                if seq.trace.first_scheduled_s == 0.0:
+                    seq.trace.first_scheduled_s = self.clock()
+                if b.start < seq.prompt_len:
+                    seq.trace.prefill_steps += 1
+                    seq.trace.prefill_forward_ms += self._last_forward_ms
             seq.mark_computed(len(b.tokens))
             seq.last_step = step_no
             self.ex.cache.advance(seq.id, seq.num_computed)
             if not b.sample:
                 continue
             tok = sampled[seq.id]
+            if seq.trace is not None and seq.trace.first_token_s == 0.0:
+                seq.trace.first_token_s = self.clock()
             seq.append_token(tok)
             if seq.terminal:
                 self.stats.finished += 1

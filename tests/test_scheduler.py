@@ -446,3 +446,39 @@ def test_a_lone_prompt_gets_the_solo_chunk():
     run_all(s4)
     mixed = [b for b in rows(ex4) if len(b) == 2]
     assert mixed and all(b[1][0] <= 32 for b in mixed if b[0] == (1, True))
+
+
+def test_request_traces_tell_each_request_s_life():
+    """With traces kept, every request leaves a record when it ends (dynalm/src/scheduler/scheduler.h:113-125):
+    its times in order, the steps that computed prompt rows (again after a preemption), how it ended."""
+    tick = [0.0]
+
+    def clock():
+        tick[0] += 0.001
+        return tick[0]
+
+    ps = prompts(6, [40, 90, 17, 120, 64, 33])
+    ex = FakeExecutor(kv_tokens=320)
+    s = Scheduler(ex, SchedulerConfig(max_running=6, decode_token_budget=8, prefill_token_budget=64,
+                                      max_prefill_chunk=32, max_batch_tokens=128), keep_trace=True, clock=clock)
+    ids = [s.submit(Request(p, max_new_tokens=40)) for p in ps]
+    bad = s.submit(Request([5, 6, 7], max_new_tokens=0))                   # refused at validation
+    run_all(s)
+    traces = {t.id: t for t in s.request_traces}
+    assert sorted(traces) == sorted(ids + [bad]) and len(s.request_traces) == 7
+    assert traces[bad].status == ERROR and traces[bad].first_token_s == 0.0 and traces[bad].admit_s == 0.0
+    assert traces[bad].submit_s < traces[bad].finish_s
+    assert s.stats.preemptions > 0 and sum(t.preemptions for t in traces.values()) == s.stats.preemptions
+    for rid, p in zip(ids, ps):
+        t = traces[rid]
+        assert t.status == FINISHED and t.prompt_tokens == len(p) and t.generated == 40
+        assert 0.0 < t.submit_s < t.admit_s < t.first_scheduled_s <= t.first_token_s < t.finish_s
+        least = -(-len(p) // 32)
+        assert t.prefill_steps >= least and (t.preemptions > 0 or t.prefill_steps == least)
+        assert t.prefill_forward_ms >= 0.0
+    assert any(t.preemptions > 0 and t.prefill_steps > -(-t.prompt_tokens // 32) for t in traces.values())
+    # without traces nothing is kept
+    s0 = Scheduler(FakeExecutor(), SchedulerConfig())
+    s0.submit(Request([1, 2, 3], max_new_tokens=2))
+    run_all(s0)
+    assert s0.request_traces is None and s0.trace is None
