@@ -128,6 +128,14 @@ class Engine:
 
     def stats(self) -> dict:
         s = self.scheduler.stats
+        from ..kernels import gemm, ops
+        from . import launch_memo
+        fn = self.step_fn
         return {"scheduler": dict(vars(s)), "free_pages": self.built.cache.free_pages,
                 "pages": self.built.cache.num_pages, "cache_bytes": self.built.cache.bytes(),
-                "workspace_bytes": self.built.runtime.workspace_bytes()}
+                "workspace_bytes": self.built.runtime.workspace_bytes(),
+                # how the steps were issued (counts since the process began, over all engines)
+                "kernel_launches": ops.LAUNCHES, "library_products": gemm.LIBRARY_CALLS,
+                "layers_issued_by_address": launch_memo.REPLAYED_LAYERS,
+                "graphs": {"captured": fn.graph_captures, "capture_ms": round(fn.graph_capture_ms, 3),
+                           "replayed_kernel_launches": fn.graph_kernel_launches}}

@@ -482,3 +482,20 @@ def test_request_traces_tell_each_request_s_life():
     s0.submit(Request([1, 2, 3], max_new_tokens=2))
     run_all(s0)
     assert s0.request_traces is None and s0.trace is None
+
+
+def test_engine_stats_snapshot_names_how_steps_were_issued():
+    """Engine.stats() on stand-ins (no GPU): the scheduler's counters, the cache's pages and how the steps were
+    issued (launches, library products, layers issued by address, graphs)."""
+    from types import SimpleNamespace
+    from dynalm_b200.engine.engine import Engine
+    from dynalm_b200.engine.scheduler import SchedulerStats
+    eng = Engine.__new__(Engine)
+    eng.scheduler = SimpleNamespace(stats=SchedulerStats(steps=3))
+    eng.built = SimpleNamespace(cache=SimpleNamespace(free_pages=5, num_pages=8, bytes=lambda: 1024),
+                                runtime=SimpleNamespace(workspace_bytes=lambda: 2048))
+    eng.step_fn = SimpleNamespace(graph_captures=2, graph_capture_ms=9.87654, graph_kernel_launches=232)
+    got = eng.stats()
+    assert got["scheduler"]["steps"] == 3 and got["free_pages"] == 5 and got["pages"] == 8
+    assert got["graphs"] == {"captured": 2, "capture_ms": 9.877, "replayed_kernel_launches": 232}
+    assert {"kernel_launches", "library_products", "layers_issued_by_address", "cache_bytes", "workspace_bytes"} <= set(got)
