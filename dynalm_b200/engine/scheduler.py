@@ -212,6 +212,8 @@ class SchedulerStats:
     forward_prefill_only_ms: float = 0.0
     forward_mixed_ms: float = 0.0
     timed_out: int = 0
+    plan_ms: float = 0.0                  # host time spent choosing batches and reserving their pages
+    emit_ms: float = 0.0                  # host time spent in the requests' callbacks
     mixed_prefill_budget: int = 0         # the prompt rows a step with decode rows may carry now
 
 
@@ -479,10 +481,13 @@ class Scheduler:
         return nxt or None
 
     def _dispatch(self, events: List[Event]) -> List[Event]:
-        for ev in events:
-            seq_cb = self._callbacks.pop(ev.request_id, None) if ev.finished else self._callbacks.get(ev.request_id)
-            if seq_cb is not None:
-                seq_cb(ev)
+        if self._callbacks and events:
+            t0 = time.perf_counter()
+            for ev in events:
+                seq_cb = self._callbacks.pop(ev.request_id, None) if ev.finished else self._callbacks.get(ev.request_id)
+                if seq_cb is not None:
+                    seq_cb(ev)
+            self.stats.emit_ms += (time.perf_counter() - t0) * 1e3
         return events
 
     def step(self) -> List[Event]:
@@ -492,9 +497,11 @@ class Scheduler:
         preempted: List[int] = []
         if self._inflight is not None:
             prev, launched, t_launch = self._inflight
+            t_plan = time.perf_counter()
             nxt = self._plan_ahead(prev)
             nxt_launched = None
             t_next = time.perf_counter()
+            self.stats.plan_ms += (t_next - t_plan) * 1e3
             if nxt is not None:
                 try:
                     nxt_launched = self.ex.launch(nxt, after=launched)
@@ -522,7 +529,9 @@ class Scheduler:
         self._retire(events)
         self._admit(admitted)
         if self.running:
+            t_plan = time.perf_counter()
             batch = self._plan(events, preempted)
+            self.stats.plan_ms += (time.perf_counter() - t_plan) * 1e3
             if batch and self.lookahead and self.ex.can_launch(batch):
                 try:
                     t_launch = time.perf_counter()

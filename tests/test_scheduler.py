@@ -399,6 +399,12 @@ def test_a_failed_forward_fails_its_batch_only_and_gives_the_pages_back():
     later = s.submit(Request(list(range(40)), max_new_tokens=5))
     toks, final = collect(run_all(s))
     assert final[later].status == FINISHED and len(toks[later]) == 5
+    # the time split of the reference's SchedulerStats (scheduler.h:260-313): planning and callbacks on the host
+    assert s.stats.plan_ms > 0.0 and s.stats.emit_ms == 0.0               # nobody asked for callbacks
+    seen = []
+    s.submit(Request(list(range(12)), max_new_tokens=3, on_event=seen.append))
+    run_all(s)
+    assert len(seen) == 3 and seen[-1].finished and s.stats.emit_ms > 0.0
 
 
 def test_a_lone_prompt_gets_the_solo_chunk():
