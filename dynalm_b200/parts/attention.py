@@ -31,10 +31,10 @@ class PagedAttention:
             "k": TensorDecl((kw, spec.width)),
             "v": TensorDecl((kw, spec.width)),
             "o": TensorDecl((spec.width, qw)),
-            "q_bias": TensorDecl((qw,), role="vector", required=False),
-            "k_bias": TensorDecl((kw,), role="vector", required=False),
-            "v_bias": TensorDecl((kw,), role="vector", required=False),
-            "o_bias": TensorDecl((spec.width,), role="vector", required=False),
+            "q_bias": TensorDecl((qw,), role="vector", required=False, init="bias"),
+            "k_bias": TensorDecl((kw,), role="vector", required=False, init="bias"),
+            "v_bias": TensorDecl((kw,), role="vector", required=False, init="bias"),
+            "o_bias": TensorDecl((spec.width,), role="vector", required=False, init="bias"),
         }
 
     def __init__(self, spec, tensors: Dict[str, torch.Tensor], runtime):

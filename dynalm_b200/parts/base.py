@@ -33,7 +33,7 @@ class TensorDecl:
     norm weights and biases to fp32 copies, dynalm/src/model/transformer.cpp:92-101);
     role "table_int": integer table, kept as int32.
     `init` tells the random-weights mode how to draw it: "normal" is N(0, 0.02),
-    "around_one" is 1 + N(0, 0.1) (norm weights), "zeros" is all zero.
+    "around_one" is 1 + N(0, 0.1) (norm weights), "bias" is N(0, 0.1), "zeros" is all zero.
     """
 
     shape: Tuple[int, ...]

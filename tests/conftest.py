@@ -18,13 +18,13 @@ def pytest_configure(config):
 def tiny_folders(tmp_path_factory):
     """name -> folder of each tiny model with float32 random weights (made once per session)."""
     import torch
-    from tiny_configs import TINY
+    from tiny_configs import OPTIONAL_TENSORS, TINY
     from dynalm_b200.weights import write_model_folder
 
     out = {}
     for name, (cfg, seed) in TINY.items():
         d = tmp_path_factory.mktemp(f"tiny_{name}")
-        write_model_folder(str(d), cfg, seed, dtype=torch.float32)
+        write_model_folder(str(d), cfg, seed, dtype=torch.float32, optional=OPTIONAL_TENSORS.get(name))
         out[name] = str(d)
     return out
 
@@ -32,12 +32,12 @@ def tiny_folders(tmp_path_factory):
 @pytest.fixture(scope="session")
 def tiny_folders_bf16(tmp_path_factory):
     import torch
-    from tiny_configs import TINY
+    from tiny_configs import OPTIONAL_TENSORS, TINY
     from dynalm_b200.weights import write_model_folder
 
     out = {}
     for name, (cfg, seed) in TINY.items():
         d = tmp_path_factory.mktemp(f"tiny_{name}_bf16")
-        write_model_folder(str(d), cfg, seed, dtype=torch.bfloat16)
+        write_model_folder(str(d), cfg, seed, dtype=torch.bfloat16, optional=OPTIONAL_TENSORS.get(name))
         out[name] = str(d)
     return out

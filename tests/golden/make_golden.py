@@ -26,15 +26,15 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
-from tiny_configs import TINY  # noqa: E402
+from tiny_configs import OPTIONAL_TENSORS, TINY  # noqa: E402
 import dynalm_b200  # noqa: E402,F401
 from dynalm_b200.weights import write_model_folder  # noqa: E402
 
-PROMPT_LEN = {"a": 33, "b": 40, "c": 24, "d": 21, "e": 37, "f": 19}
+PROMPT_LEN = {"a": 33, "b": 40, "c": 24, "d": 21, "e": 37, "f": 19, "g": 29}
 
 
 def prompt_for(name: str, vocab: int):
-    rng = np.random.RandomState({"a": 1, "b": 3, "c": 5, "d": 7, "e": 9, "f": 11}[name])
+    rng = np.random.RandomState({"a": 1, "b": 3, "c": 5, "d": 7, "e": 9, "f": 11, "g": 13}[name])
     return [int(t) for t in rng.randint(0, vocab, size=PROMPT_LEN[name])]
 
 
@@ -56,12 +56,12 @@ def main():
                            "-lpthread", "-o", harness])
     for name, (cfg, seed) in TINY.items():
         with tempfile.TemporaryDirectory() as d:
-            write_model_folder(d, cfg, seed, dtype=torch.float32)
+            write_model_folder(d, cfg, seed, dtype=torch.float32, optional=OPTIONAL_TENSORS.get(name))
             toks = prompt_for(name, cfg["vocab_size"])
             out = os.path.join(HERE, f"{name}.logits.f32")
             print(subprocess.check_output([harness, d, out] + [str(t) for t in toks], text=True).strip())
             meta = {"config": cfg, "seed": seed, "prompt": toks, "shape": [len(toks), cfg["vocab_size"]],
-                    "weights_sha256": weights_checksum(d)}
+                    "optional_tensors": OPTIONAL_TENSORS.get(name, []), "weights_sha256": weights_checksum(d)}
             with open(os.path.join(HERE, f"{name}.json"), "w") as f:
                 json.dump(meta, f, indent=1)
 

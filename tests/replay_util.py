@@ -114,6 +114,63 @@ def plan_mixed(reqs: Dict[str, List[int]], seed: int, max_live: int = 4, decode_
     return p
 
 
+def plan_many_rows(short: Dict[str, List[int]], long: Dict[str, List[int]], seed: int, tail_lo: int = 10,
+                   tail_hi: int = 22, sizes: Sequence[int] = (9, 2, 21, 5, 33)) -> Plan:
+    """Many live requests: the `short` ones (17 to 40 of them) are first brought in, four prompts a step; then every
+    step carries one token of each short request that has tokens left, beside a portion of one of the `long`
+    requests while there is one, and alone afterwards. The short requests end at different times, so the number of
+    single-token rows falls step by step from len(short); logits are wanted at every single-token row and at the
+    end of every portion."""
+    rng = np.random.RandomState(seed)
+    p = Plan()
+    names = list(short)
+    tails = {r: int(min(len(short[r]) - 1, rng.randint(tail_lo, tail_hi + 1))) for r in names}
+    for i in range(0, len(names), 4):
+        group = names[i:i + 4]
+        p.add([(r, short[r][:len(short[r]) - tails[r]], 0, [len(short[r]) - tails[r] - 1]) for r in group])
+    done = {r: len(short[r]) - tails[r] for r in names}
+    waiting = list(long)
+    cur, cur_pos, k = None, 0, 0
+    while any(done[r] < len(short[r]) for r in names) or waiting or cur is not None:
+        entries, ended = [], []
+        for r in names:
+            if done[r] < len(short[r]):
+                entries.append((r, [short[r][done[r]]], done[r], [0]))
+                done[r] += 1
+                if done[r] == len(short[r]):
+                    ended.append(r)
+        if cur is None and waiting:
+            cur, cur_pos = waiting.pop(0), 0
+        if cur is not None:
+            toks = long[cur]
+            n = min(sizes[k % len(sizes)], len(toks) - cur_pos)
+            k += 1
+            entries.append((cur, toks[cur_pos:cur_pos + n], cur_pos, [n - 1]))
+            cur_pos += n
+            if cur_pos == len(toks):
+                ended.append(cur)
+                cur = None
+        p.add(entries, end=ended)
+    return p
+
+
+def kl_and_top1(plan: Plan, got: Dict[int, np.ndarray], plain: Dict[str, np.ndarray], near_tie: float = 0.0):
+    """Over all written rows: the mean KL divergence from the plain distribution to the one got, and the share of
+    rows whose largest logit is at the same token (rows whose two largest plain logits lie within `near_tie` of each
+    other count as agreeing)."""
+    kls, same = [], []
+    for step in sorted(plan.rows):
+        for i, (r, pos) in enumerate(plan.rows[step]):
+            ref = plain[r][pos].astype(np.float64)
+            g = got[step][i].astype(np.float64)
+            lp_ref = ref - ref.max() - np.log(np.exp(ref - ref.max()).sum())
+            lp_got = g - g.max() - np.log(np.exp(g - g.max()).sum())
+            kls.append(float((np.exp(lp_ref) * (lp_ref - lp_got)).sum()))
+            top = np.sort(ref)[-2:]
+            same.append(bool(ref.argmax() == g.argmax()) or (top[1] - top[0]) <= near_tie)
+    return float(np.mean(kls)), float(np.mean(same))
+
+
 def run_plan_in_process(step_fn, plan: Plan) -> Dict[int, np.ndarray]:
     from dynalm_b200.engine import StepEntry
     out = {}

@@ -44,9 +44,17 @@ def test_greedy_generation(name, dtype, slack, tiny_folders):
         scale = np.abs(plain.logits(prompt)[-1]).max()
         _check_greedy_against_plain(plain, prompt, g.tokens, slack * max(1.0, scale))
     if dtype == "float32":
-        # in 32-bit the plain greedy continuation itself, unless the plain top two are within rounding
+        # in 32-bit the plain greedy continuation itself, token by token, up to the first place where the plain
+        # implementation's two largest logits are within rounding of each other
         for prompt, g in zip(reqs.values(), outs):
-            assert g.tokens[:4] == plain.greedy(prompt, 4) or True
+            seq = list(prompt)
+            for i, tok in enumerate(g.tokens[:8]):
+                row = plain.logits(seq)[-1]
+                top = np.sort(row)[-2:]
+                if top[1] - top[0] <= 1e-5:
+                    break
+                assert tok == int(np.argmax(row)), f"token {i} of the continuation: {tok}, plain {int(np.argmax(row))}"
+                seq.append(tok)
     # alone == batched: the logits of a request do not depend on what else is in the batch
     alone = [eng.generate(p, max_tokens=16).tokens for p in reqs.values()]
     if dtype == "float32":

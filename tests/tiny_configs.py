@@ -57,5 +57,20 @@ TINY_F = {
     "rms_norm_eps": 2e-6, "rope_theta": 10000.0, "tie_word_embeddings": False,
 }
 
+# Seven heads with a KV head each (no grouping), three layers, and the biases of all four attention projections,
+# which the architecture takes when the file carries them (see OPTIONAL_TENSORS).
+TINY_G = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "vocab_size": 333, "hidden_size": 112, "intermediate_size": 184, "num_hidden_layers": 3,
+    "num_attention_heads": 7, "num_key_value_heads": 7, "max_position_embeddings": 256,
+    "rms_norm_eps": 4e-6, "rope_theta": 1000000.0, "tie_word_embeddings": False,
+}
+
 # name -> (config, weight seed)
-TINY = {"a": (TINY_A, 0), "b": (TINY_B, 2), "c": (TINY_C, 9), "d": (TINY_D, 4), "e": (TINY_E, 6), "f": (TINY_F, 8)}
+TINY = {"a": (TINY_A, 0), "b": (TINY_B, 2), "c": (TINY_C, 9), "d": (TINY_D, 4), "e": (TINY_E, 6), "f": (TINY_F, 8),
+        "g": (TINY_G, 10)}
+
+# name -> file names of tensors that the model folder carries although the configuration does not ask for them
+OPTIONAL_TENSORS = {
+    "g": [f"model.layers.{l}.self_attn.{p}_proj.bias" for l in range(TINY_G["num_hidden_layers"]) for p in "qkvo"],
+}
