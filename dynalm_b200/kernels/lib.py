@@ -14,6 +14,7 @@ from __future__ import annotations
 import ctypes
 import hashlib
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -80,26 +81,51 @@ def sources() -> List[str]:
     return sorted(f[:-3] for f in os.listdir(CSRC) if f.endswith(".cu"))
 
 
+_INCLUDE = re.compile(r'^\s*#\s*include\s+"([^"]+)"', re.M)
+
+
+def _with_includes(name: str) -> List[str]:
+    """csrc/<name>.cu and every file of csrc/ that it includes, directly or through another."""
+    todo, found = [name + ".cu"], []
+    while todo:
+        f = todo.pop()
+        if f in found or not os.path.isfile(os.path.join(CSRC, f)):
+            continue
+        found.append(f)
+        with open(os.path.join(CSRC, f), "r", errors="replace") as fh:
+            todo.extend(_INCLUDE.findall(fh.read()))
+    return [found[0]] + sorted(found[1:])
+
+
 def _source_hash(name: str) -> str:
     h = hashlib.sha256()
-    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
-    files = [os.path.join(CSRC, name + ".cu")] + sorted(
-        os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h")))
-    for p in files:
-        with open(p, "rb") as f:
-            h.update(os.path.basename(p).encode())
-            h.update(f.read())
+    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + extra_flags()).encode())
+    for f in _with_includes(name):
+        with open(os.path.join(CSRC, f), "rb") as fh:
+            h.update(f.encode())
+            h.update(fh.read())
     return h.hexdigest()[:16]
 
 
+def extra_flags() -> List[str]:
+    """Flags that a switch of the environment adds to every kernel build (they are part of a library's hash, so the
+    builds with and without them lie side by side). DYNALM_CHECK=1: -DDL_CHECK, the kernels check every index that
+    they take from device data before they use it (see csrc/check.cuh)."""
+    return ["-DDL_CHECK=1"] if os.environ.get("DYNALM_CHECK", "0") not in ("", "0") else []
+
+
+def _file_name(name: str) -> str:
+    return f"libdl_{name}.{'check.' if extra_flags() else ''}{_source_hash(name)}.so"
+
+
 def library_path(name: str, directory: Optional[str] = None) -> str:
-    return os.path.join(directory or build_dir(), f"libdl_{name}.{_source_hash(name)}.so")
+    return os.path.join(directory or build_dir(), _file_name(name))
 
 
 def _find_built(name: str) -> Optional[str]:
     """A built library of the current sources, in any of the candidate folders (a read-only
     checkout may carry one that was built elsewhere)."""
-    fname = f"libdl_{name}.{_source_hash(name)}.so"
+    fname = _file_name(name)
     for d in (os.environ.get("DYNALM_BUILD_DIR"), os.path.join(os.path.dirname(CSRC), "_build"),
               os.path.join(tempfile.gettempdir(), f"dynalm_b200_build_{os.getuid()}")):
         if d and os.path.isfile(os.path.join(d, fname)):
@@ -118,7 +144,7 @@ def compile_library(name: str, verbose: bool = True) -> str:
     out = library_path(name)
     nvcc = find_nvcc()
     tmp = f"{out}.{os.getpid()}.tmp"
-    cmd = [nvcc] + ARCH_FLAGS + NVCC_FLAGS + ["-I", CSRC, "-o", tmp, src]
+    cmd = [nvcc] + ARCH_FLAGS + NVCC_FLAGS + extra_flags() + ["-I", CSRC, "-o", tmp, src]
     if verbose:
         _say(f"compiling {name}.cu for sm_100a ...")
     t0 = time.time()
@@ -144,9 +170,11 @@ def compile_library(name: str, verbose: bool = True) -> str:
     os.replace(tmp, out)
     if verbose:
         _say(f"built {os.path.basename(out)} in {time.time() - t0:.1f} s")
-    # older builds of the same source are of no use any more
+    # older builds of the same source and the same kind (plain or checked) are of no use any more
+    checked = bool(extra_flags())
     for f in os.listdir(os.path.dirname(out)):
-        if f.startswith(f"libdl_{name}.") and f.endswith(".so") and f != os.path.basename(out):
+        if f.startswith(f"libdl_{name}.") and f.endswith(".so") and f != os.path.basename(out) \
+                and f.startswith(f"libdl_{name}.check.") == checked:
             try:
                 os.unlink(os.path.join(os.path.dirname(out), f))
             except OSError:

@@ -217,8 +217,9 @@ def attention_block(x: np.ndarray, w: Dict[str, np.ndarray], p: str, c: dict, po
     return o + b if b is not None else o
 
 
-def forward(c: dict, w: Dict[str, np.ndarray], tokens: Sequence[int]) -> np.ndarray:
-    """Logits [n, vocab] of a whole sequence from position 0
+def forward(c: dict, w: Dict[str, np.ndarray], tokens: Sequence[int], rows: Optional[Sequence[int]] = None) -> np.ndarray:
+    """Logits [n, vocab] of a whole sequence from position 0 (with `rows`: at those positions only, as the
+    reference gathers the wanted rows before the final norm, dynalm/src/model/transformer.cpp:703-718)
     (dynalm/src/model/transformer.cpp:498-733): embed; per layer x += attn(norm(x)),
     x += mlp(norm(x)), each scaled by the residual multiplier when it is not 1 (:656,:696);
     final norm; lm_head (the embedding table when the file has no lm_head,
@@ -233,6 +234,8 @@ def forward(c: dict, w: Dict[str, np.ndarray], tokens: Sequence[int]) -> np.ndar
         h = rms_norm(x, w[p + "post_attention_layernorm.weight"], c["rms_norm_eps"])
         x = x + rscale * gated_mlp(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
                                    w[p + "mlp.down_proj.weight"])
+    if rows is not None:
+        x = x[np.asarray(rows, dtype=np.int64)]
     x = rms_norm(x, w["model.norm.weight"], c["rms_norm_eps"])
     head = w.get("lm_head.weight", w["model.embed_tokens.weight"])
     logits = x @ head.T
@@ -248,8 +251,8 @@ class PlainLlama:
         self.config = read_config(os.path.join(folder, "config.json"))
         self.weights = read_safetensors(os.path.join(folder, "model.safetensors"))
 
-    def logits(self, tokens: Sequence[int]) -> np.ndarray:
-        return forward(self.config, self.weights, tokens)
+    def logits(self, tokens: Sequence[int], rows: Optional[Sequence[int]] = None) -> np.ndarray:
+        return forward(self.config, self.weights, tokens, rows)
 
     def greedy(self, prompt: Sequence[int], steps: int) -> List[int]:
         """Whole-sequence recompute per new token; ties go to the lowest id

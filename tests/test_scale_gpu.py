@@ -1,68 +1,112 @@
-"""The Llama 3.2 1B layer sizes (4 of its 16 layers, the full vocabulary, tied embeddings, llama3 RoPE
-scaling) with random weights: the float32 engine gives equal logits however the prompt is cut, and the
-bfloat16 engine (tcgen05 products, flash attention, the decode kernels and graphs) agrees with it the
-way the reference asks of its own GPU path: mean KL at most 0.0025 and nearly all top-1 tokens equal
-(dynalm/benchmarks/bench_gpu_accuracy.cpp:91-92)."""
+"""The Llama 3.2 1B layer sizes (2 of its 16 layers, the full vocabulary, tied embeddings, llama3 RoPE scaling)
+with random weights, against the plain implementation: whole prompts, portions, and mixed steps of up to four
+live requests in a pool so small that pages are used again. At these sizes the bfloat16 engine runs what the tiny
+configurations cannot reach: the tcgen05 products (also the one in which two blocks share tiles of W, from 1,184
+rows), the tcgen05 prompt attention over many query tiles, and the library product for the row counts in between.
+
+32-bit: logits within 1e-4 of each row's largest logit. bfloat16: what the reference asks of its own GPU path
+against 32-bit, a mean KL divergence of at most 0.0025 and the same most likely token in at least 99 rows of 100
+(dynalm/benchmarks/bench_gpu_accuracy.cpp:91-92), here against the plain implementation on the same bfloat16
+weights."""
+
+import json
+import os
 
 import numpy as np
 import pytest
 import torch
 
+from plain_llama import PlainLlama
+from replay_util import Plan, compare, kl_and_top1, plan_mixed, random_requests, run_plan_in_process
+
 pytestmark = pytest.mark.gpu
 
 CFG = {
     "architectures": ["LlamaForCausalLM"], "model_type": "llama", "vocab_size": 128256, "hidden_size": 2048,
-    "intermediate_size": 8192, "num_hidden_layers": 4, "num_attention_heads": 32, "num_key_value_heads": 8,
+    "intermediate_size": 8192, "num_hidden_layers": 2, "num_attention_heads": 32, "num_key_value_heads": 8,
     "head_dim": 64, "max_position_embeddings": 8192, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
     "tie_word_embeddings": True,
     "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
                      "original_max_position_embeddings": 8192},
 }
+LENGTHS = [300, 170, 230, 129, 90, 200]
+LONG = 1300
+LONG_WANT = list(range(LONG - 6, LONG))
 
 
 @pytest.fixture(scope="module")
-def tensors():
+def folder(tmp_path_factory):
     from dynalm_b200.registry import find_architecture
-    from dynalm_b200.weights import random_tensors
+    from dynalm_b200.weights import random_tensors, write_safetensors
+    d = str(tmp_path_factory.mktemp("one_b_shape"))
     arch = find_architecture(CFG)
     t = random_tensors(arch.plan(arch.read_config(CFG)), 0, torch.bfloat16)
     # random N(0, 0.02) weights give nearly flat logits; a wider embedding makes the distribution peaked
-    # enough for top-1 and KL to mean something
+    # enough for the most likely token and the KL divergence to mean something
     t["model.embed_tokens.weight"] = (t["model.embed_tokens.weight"].float() * 8).to(torch.bfloat16)
-    return t
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(CFG, f)
+    write_safetensors(os.path.join(d, "model.safetensors"), t)
+    return d
 
 
-def _logits(tensors, dtype, cuts, tokens, want_from):
-    from dynalm_b200 import StepEntry
+def _plans():
+    reqs = random_requests(CFG["vocab_size"], LENGTHS, seed=3)
+    long = random_requests(CFG["vocab_size"], [LONG], seed=4)["r0"]
+    reqs["long"] = long
+    whole = Plan()
+    whole.add([("long", long, 0, LONG_WANT)], end=["long"])
+    cut = Plan()
+    pos = 0
+    for n in (700, 513, 2, 85):
+        cut.add([("long", long[pos:pos + n], pos, [w - pos for w in LONG_WANT if pos <= w < pos + n])],
+                end=["long"] if pos + n == LONG else [])
+        pos += n
+    short = {r: t for r, t in reqs.items() if r != "long"}
+    mixed = plan_mixed(short, seed=8, max_live=4, decode_tail=6, sizes=(2, 33, 130, 64, 257))
+    return reqs, {"whole": whole, "cut": cut, "mixed": mixed}
+
+
+@pytest.fixture(scope="module")
+def plain(folder):
+    """request -> {position: plain logits row}, for the positions that some plan wants."""
+    reqs, plans = _plans()
+    wanted = {r: set() for r in reqs}
+    for plan in plans.values():
+        for rows in plan.rows.values():
+            for r, pos in rows:
+                wanted[r].add(pos)
+    model = PlainLlama(folder)
+    out = {}
+    for r, toks in reqs.items():
+        places = sorted(wanted[r])
+        got = model.logits(toks, rows=places).astype(np.float32)
+        out[r] = {pos: got[i] for i, pos in enumerate(places)}
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_one_b_shape_against_plain(dtype, folder, plain):
     from dynalm_b200.engine import build
-    built = build(config_obj=CFG, tensors=tensors, dtype=dtype, kv_tokens=1024, max_batch_tokens=512, max_requests=4)
-    out, pos = [], 0
-    for c in cuts:
-        want = [i for i in range(c) if pos + i >= want_from]
-        got = built.step_fn.step([StepEntry("r", tokens[pos:pos + c], want)])
-        if got is not None:
-            out.append(got.float().cpu().numpy().copy())
-        pos += c
-    built.step_fn.end("r")
-    del built
-    torch.cuda.empty_cache()
-    return np.concatenate(out)
-
-
-def test_one_b_shape_parity(tensors):
-    rng = np.random.RandomState(0)
-    tokens = [int(t) for t in rng.randint(0, CFG["vocab_size"], 400)]
-    want_from = 336                                    # the last 64 positions
-    whole32 = _logits(tensors, "float32", [400], tokens, want_from)
-    cut32 = _logits(tensors, "float32", [300, 37, 2, 29] + [1] * 32, tokens, want_from)
-    assert np.abs(whole32 - cut32).max() <= 1e-4 * max(1.0, np.abs(whole32).max())
-    for cuts in ([400], [300, 37, 2, 29] + [1] * 32):
-        got = _logits(tensors, "bfloat16", cuts, tokens, want_from)
-        ref = whole32.astype(np.float64)
-        lp_ref = ref - np.log(np.exp(ref - ref.max(-1, keepdims=True)).sum(-1, keepdims=True)) - ref.max(-1, keepdims=True)
-        g = got.astype(np.float64)
-        lp_got = g - np.log(np.exp(g - g.max(-1, keepdims=True)).sum(-1, keepdims=True)) - g.max(-1, keepdims=True)
-        kl = (np.exp(lp_ref) * (lp_ref - lp_got)).sum(-1).mean()
-        top1 = (ref.argmax(-1) == g.argmax(-1)).mean()
-        print(f"cuts {len(cuts)}: mean KL {kl:.2e}, top-1 agreement {top1:.3f}")
-        assert kl <= 0.0025 and top1 >= 0.9
+    from dynalm_b200.kernels import gemm
+    _, plans = _plans()
+    for what, plan in plans.items():
+        need = plan.max_live_tokens(64)
+        library_before = gemm.LIBRARY_CALLS
+        built = build(folder, dtype=dtype, kv_tokens=need, max_batch_tokens=1408, max_requests=4, context=2048)
+        got = run_plan_in_process(built.step_fn, plan)
+        assert built.cache.free_pages == built.cache.num_pages
+        kl, top1 = kl_and_top1(plan, got, plain, near_tie=1e-4 if dtype == "float32" else 0.05)
+        if dtype == "float32":
+            worst = compare(plan, got, plain, 0.0, 1e-4, f"1B/{dtype}/{what}")
+            assert kl <= 1e-9 and top1 == 1.0
+        else:
+            worst = compare(plan, got, plain, 0.0, 5e-2, f"1B/{dtype}/{what}")
+            # (rows whose two largest plain logits lie within 0.05 of each other are not counted against it; of the
+            # others a few in a thousand still change places under bfloat16 rounding at this logit scale)
+            assert kl <= 0.0025 and top1 >= 0.99, f"1B/{dtype}/{what}: mean KL {kl:.3g}, top-1 agreement {top1:.4f}"
+            if what == "mixed":
+                assert gemm.LIBRARY_CALLS > library_before, "no product took the path of 17 to 127 rows"
+        print(f"1B {dtype} {what}: steps {len(plan.steps)} pool {need} worst {worst:.3g} KL {kl:.3g} top-1 {top1:.4f}")
+        del built
+        torch.cuda.empty_cache()
