@@ -52,7 +52,7 @@ decode_attention_kernel(const T* __restrict__ q, int q_stride, const T* __restri
   len = (len + 15) & ~15;
   const int k_begin = lo + split * len;
   const int k_end = min(pos + 1, k_begin + len);
-  const int* table = block_table + static_cast<size_t>(row_request[row]) * max_blocks;
+  const int* table = block_table + static_cast<size_t>(ck_request(row_request[row])) * max_blocks;
   const size_t kv_row = static_cast<size_t>(n_kv_heads) * head_dim;
   const size_t head_off = static_cast<size_t>(kvh) * head_dim + dl_ * V;
 
@@ -88,7 +88,7 @@ decode_attention_kernel(const T* __restrict__ q, int q_stride, const T* __restri
       kr[u].raw = make_uint4(0, 0, 0, 0);
       vr[u].raw = make_uint4(0, 0, 0, 0);
       if (ok[u] && dim_ok) {
-        const size_t slot = (static_cast<size_t>(table[t >> page_shift]) << page_shift) + (t & page_mask);
+        const size_t slot = (static_cast<size_t>(ck_page(table, t >> page_shift, max_blocks)) << page_shift) + (t & page_mask);
         kr[u] = *reinterpret_cast<const Vec16*>(k_cache + slot * kv_row + head_off);
         vr[u] = *reinterpret_cast<const Vec16*>(v_cache + slot * kv_row + head_off);
       }
@@ -365,7 +365,7 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
   const int k_begin = lo + split * len;
   const int k_end = min(pos + 1, k_begin + len);
   const int n_tiles = k_end > k_begin ? (k_end - k_begin + KT - 1) / KT : 0;
-  const int* table = block_table + static_cast<size_t>(row_request[row]) * max_blocks;
+  const int* table = block_table + static_cast<size_t>(ck_request(row_request[row])) * max_blocks;
   const size_t kv_row = static_cast<size_t>(n_kv_heads) * HD;
 
   bf16* my = KV + static_cast<size_t>(warp) * STAGES * 2 * TILE_ELEMS;
@@ -381,7 +381,7 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
       for (int hf = 0; hf < KT / 16; ++hf) {
         const int kb = key0 + hf * 16;
         size_t slot0 = 0;
-        if (kb < k_end) slot0 = (static_cast<size_t>(table[kb >> page_shift]) << page_shift) + (kb & page_mask);
+        if (kb < k_end) slot0 = (static_cast<size_t>(ck_page(table, kb >> page_shift, max_blocks)) << page_shift) + (kb & page_mask);
 #pragma unroll
         for (int c = lane; c < 16 * CH; c += 32) {
           const int r = c / CH, ch = c % CH;
@@ -400,7 +400,7 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
       const bool ok = key < k_end;
       size_t off = 0;
       if (ok) {
-        const size_t slot = (static_cast<size_t>(table[key >> page_shift]) << page_shift) + (key & page_mask);
+        const size_t slot = (static_cast<size_t>(ck_page(table, key >> page_shift, max_blocks)) << page_shift) + (key & page_mask);
         off = slot * kv_row + static_cast<size_t>(kvh) * HD + ch * 8;
       }
       dt_cp_async16(kd + r * LD + ch * 8, k_cache + off, ok);

@@ -32,7 +32,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* _
   const int kvh = head / (n_heads / n_kv_heads);
   const int pos = positions[row];
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-  const int* table = block_table + static_cast<size_t>(row_request[row]) * max_blocks;
+  const int* table = block_table + static_cast<size_t>(ck_request(row_request[row])) * max_blocks;
   const int tid = threadIdx.x;
 
   const T* qrow = q + static_cast<size_t>(row) * q_stride + static_cast<size_t>(head) * head_dim;
@@ -51,7 +51,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* _
     for (int t = c0 + tid; t < c1; t += ATT_THREADS) {
       float s = -INFINITY;
       if (t >= lo) {
-        const size_t slot = static_cast<size_t>(table[t / page_size]) * page_size + t % page_size;
+        const size_t slot = static_cast<size_t>(ck_page(table, t / page_size, max_blocks)) * page_size + t % page_size;
         const Vec16* kr = reinterpret_cast<const Vec16*>(k_cache + slot * kv_row + static_cast<size_t>(kvh) * head_dim);
         float dot = 0.0f;
         for (int i = 0; i < head_dim / V; ++i) {
@@ -82,7 +82,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* _
     if (g < groups) {
       const int t0 = max(c0, lo);
       for (int t = t0 + g; t < c1; t += groups) {
-        const size_t slot = static_cast<size_t>(table[t / page_size]) * page_size + t % page_size;
+        const size_t slot = static_cast<size_t>(ck_page(table, t / page_size, max_blocks)) * page_size + t % page_size;
         pv = fmaf(sp[t - c0], to_float(v_cache[slot * kv_row + static_cast<size_t>(kvh) * head_dim + d]), pv);
       }
     }

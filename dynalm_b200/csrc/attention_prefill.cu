@@ -77,7 +77,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
   bf16* Ks = Qs + PF_BM * LD;             // [2][PF_BN][LD]
   bf16* Vs = Ks + 2 * PF_BN * LD;         // [2][PF_BN][LD]
 
-  const int4 tile = tiles[blockIdx.x / SUB];
+  const int4 tile = ck_tile(tiles[blockIdx.x / SUB]);
   const int sub = blockIdx.x % SUB;
   const int req = tile.x, row0 = tile.y + sub * PF_BM, nrows = min(PF_BM, tile.z - sub * PF_BM), pos0 = tile.w + sub * PF_BM;
   if (nrows <= 0) return;
@@ -125,7 +125,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
       const bool ok = key >= lo_tile && key <= pos_last;
       size_t off = 0;
       if (ok) {
-        const size_t slot = (static_cast<size_t>(table[key >> page_shift]) << page_shift) + (key & page_mask);
+        const size_t slot = (static_cast<size_t>(ck_page(table, key >> page_shift, max_blocks)) << page_shift) + (key & page_mask);
         off = slot * kv_row + kv_goff[it];
       }
       const int bytes = ok ? 16 : 0;      // 0 source bytes: the 16 destination bytes are zero-filled

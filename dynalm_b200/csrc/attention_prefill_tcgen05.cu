@@ -90,8 +90,9 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
     return;
   }
 
-  const int4 tile = tiles[blockIdx.y];      // heads of one tile are neighbours in launch order: the tiles with most keys start first
+  const int4 tile = ck_tile(tiles[blockIdx.y]);      // heads of one tile are neighbours in launch order: the tiles with most keys start first
   const int req = tile.x, row0 = tile.y, nrows = tile.z, pos0 = tile.w;
+  if (nrows <= 0) return;                   // (a tile that a checked build has refused; nothing is set up yet)
   const int head = blockIdx.x;
   const int kvh = head / (n_heads / n_kv_heads);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -146,7 +147,7 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
       int my_slot = 0;
       if (lane < BN / FA_BOX_KEYS) {
         const int key = min(max((j_begin + i) * BN + lane * FA_BOX_KEYS, first_piece), last_piece);
-        my_slot = (table[key >> page_shift] << page_shift) + (key & page_mask);
+        my_slot = (ck_page(table, key >> page_shift, max_blocks) << page_shift) + (key & page_mask);
       }
       if (i >= ST && !warp_wait(&k_empty[s], (round & 1) ^ 1, status, FA_ERR_PRODUCER, abort_flag)) break;
       if (elect_one()) mbar_expect_tx(&k_full[s], KV_BYTES);

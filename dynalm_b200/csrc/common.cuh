@@ -169,3 +169,5 @@ inline int launch_streaming(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
 }
 
 }  // namespace dl
+
+#include "check.cuh"

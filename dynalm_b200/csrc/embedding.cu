@@ -11,7 +11,7 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
   pdl_wait();
   pdl_trigger();
   const int row = blockIdx.x;
-  int id = ids[row];
+  int id = ck_token(ids[row], vocab);
   // The step function has already refused ids outside [0, vocab); clamping keeps a stray id
   // from reading outside the table.
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);

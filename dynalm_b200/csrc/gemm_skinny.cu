@@ -272,6 +272,7 @@ gemm_skinny_qkv_rope_kernel(const bf16* __restrict__ x, int ldx, const bf16* __r
       dst = q_out + static_cast<size_t>(b) * ldq + f_lo + i;
     } else {
       const size_t slot = qkv_rope_slot(p, b, pos);
+      if (slot == QKV_NO_SLOT) continue;
       const bool is_k = head < p.n_heads + p.n_kv_heads;
       const int kvh = head - p.n_heads - (is_k ? 0 : p.n_kv_heads);
       dst = (is_k ? p.k_cache : p.v_cache) + (slot * p.n_kv_heads + kvh) * hd + (f_lo - head * hd) + i;

@@ -239,7 +239,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           if (live) {
             if (head < rope.n_heads) {
               dst = static_cast<bf16*>(y) + static_cast<size_t>(row) * ldy + static_cast<size_t>(head) * hd;
-            } else {
+            } else if (slot != QKV_NO_SLOT) {
               const bool is_k = head < rope.n_heads + rope.n_kv_heads;
               const int kvh = head - rope.n_heads - (is_k ? 0 : rope.n_kv_heads);
               dst = (is_k ? rope.k_cache : rope.v_cache) + (slot * rope.n_kv_heads + kvh) * hd;

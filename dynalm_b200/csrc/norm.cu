@@ -28,7 +28,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ del
                                size_t part_stride) {
   __shared__ float red[33];
   const int r = blockIdx.x;
-  const size_t src = rows ? static_cast<size_t>(rows[r]) : static_cast<size_t>(r);
+  const size_t src = rows ? static_cast<size_t>(ck_row(rows[r])) : static_cast<size_t>(r);
   float* xr = x + src * width;
   const TD* dr = delta ? delta + src * width : nullptr;
   float ss = 0.0f;
@@ -81,7 +81,7 @@ rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, float de
   pdl_wait();
   pdl_trigger();
   const int r = blockIdx.x;
-  const size_t src = rows ? static_cast<size_t>(rows[r]) : static_cast<size_t>(r);
+  const size_t src = rows ? static_cast<size_t>(ck_row(rows[r])) : static_cast<size_t>(r);
   float* xr = x + src * width;
   const TD* dr = delta ? delta + src * width : nullptr;
   const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);

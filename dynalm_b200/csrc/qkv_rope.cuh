@@ -22,10 +22,14 @@ struct QkvRope {
   int n_heads, n_kv_heads, head_dim, page_size;
 };
 
-// The cache slot (page * page_size + offset) of position `pos` of the request in `row`.
+constexpr size_t QKV_NO_SLOT = ~static_cast<size_t>(0);
+
+// The cache slot (page * page_size + offset) of position `pos` of the request in `row`; QKV_NO_SLOT when a
+// checked build has refused the request or the page, and the caller then stores neither key nor value.
 __device__ __forceinline__ size_t qkv_rope_slot(const QkvRope& p, int row, int pos) {
-  const int req = p.row_request[row];
-  const int page = p.block_table[static_cast<size_t>(req) * p.max_blocks + pos / p.page_size];
+  const int req = ck_request(p.row_request[row]);
+  const int page = ck_page_store(p.block_table + static_cast<size_t>(req) * p.max_blocks, pos / p.page_size, p.max_blocks);
+  if (page < 0) return QKV_NO_SLOT;
   return static_cast<size_t>(page) * p.page_size + pos % p.page_size;
 }
 

@@ -36,11 +36,15 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const int
   T* kdst = nullptr;
   T* vdst = nullptr;
   if (write_cache) {
-    const int req = row_request[row];
-    const int page = block_table[static_cast<size_t>(req) * max_blocks + pos / page_size];
-    const size_t slot = static_cast<size_t>(page) * page_size + pos % page_size;
-    kdst = k_cache + slot * n_kv_heads * head_dim;
-    vdst = v_cache + slot * n_kv_heads * head_dim;
+    const int req = ck_request(row_request[row]);
+    const int page = ck_page_store(block_table + static_cast<size_t>(req) * max_blocks, pos / page_size, max_blocks);
+    if (page < 0) {
+      write_cache = 0;          // only a checked build comes here: the row's keys and values are not stored
+    } else {
+      const size_t slot = static_cast<size_t>(page) * page_size + pos % page_size;
+      kdst = k_cache + slot * n_kv_heads * head_dim;
+      vdst = v_cache + slot * n_kv_heads * head_dim;
+    }
   }
   const int q_width = n_heads * head_dim, kv_width = n_kv_heads * head_dim;
 
@@ -97,11 +101,15 @@ __global__ void rope_cache_vec_kernel(T* __restrict__ qkv, int row_stride, const
   T* kdst = nullptr;
   T* vdst = nullptr;
   if (write_cache) {
-    const int req = row_request[row];
-    const int page = block_table[static_cast<size_t>(req) * max_blocks + pos / page_size];
-    const size_t slot = static_cast<size_t>(page) * page_size + pos % page_size;
-    kdst = k_cache + slot * n_kv_heads * head_dim;
-    vdst = v_cache + slot * n_kv_heads * head_dim;
+    const int req = ck_request(row_request[row]);
+    const int page = ck_page_store(block_table + static_cast<size_t>(req) * max_blocks, pos / page_size, max_blocks);
+    if (page < 0) {
+      write_cache = 0;          // only a checked build comes here: the row's keys and values are not stored
+    } else {
+      const size_t slot = static_cast<size_t>(page) * page_size + pos % page_size;
+      kdst = k_cache + slot * n_kv_heads * head_dim;
+      vdst = v_cache + slot * n_kv_heads * head_dim;
+    }
   }
   const int q_width = n_heads * head_dim, kv_width = n_kv_heads * head_dim;
   const int hc = half / V;                        // vector pairs per head

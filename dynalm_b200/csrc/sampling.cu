@@ -159,7 +159,7 @@ sample_temperature_kernel(const float* __restrict__ logits, int ld, int vocab,
 __global__ void feedback_tokens_kernel(int* __restrict__ token_ids, const int* __restrict__ chosen,
                                        const int* __restrict__ src, int n) {
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
-  if (r < n && src[r] >= 0) token_ids[r] = chosen[src[r]];
+  if (r < n && src[r] >= 0) token_ids[r] = chosen[ck_row(src[r])];   // checked against the length of `chosen`
 }
 
 }  // namespace dl

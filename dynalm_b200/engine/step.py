@@ -249,7 +249,8 @@ class StepFunction:
         # packed device buffer, whose addresses never change. The reference's GPU path keeps one
         # prepared graph per step structure in the same way, at most 64 of them
         # (dynacore/include/dynacore/gpu/ggml_device.h:8-13,39-48).
-        self.use_graphs = bool(use_graphs) and model.graph_safe
+        from ..kernels import ops as _ops
+        self.use_graphs = bool(use_graphs) and model.graph_safe and not _ops.CHECKED     # a checked build reads a record after every launch
         self._graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}
         self._decode_logits: Optional[torch.Tensor] = None
         self.graph_kernel_launches = 0     # kernels replayed through graphs so far

@@ -65,6 +65,67 @@ _funcs = {}
 
 _recording: Optional[list] = None
 
+# The checked build of the kernels (DYNALM_CHECK=1, csrc/check.cuh): every index a kernel takes from device memory
+# is compared with its range before use; after every launch the host reads the library's record of the first
+# violation and raises EngineError. Steps then run launch by launch (no CUDA graphs), each launch followed by a
+# wait for its stream: a build for finding faults, not for speed.
+CHECKED = bool(_lib.extra_flags())
+
+CHECK_CODES = {
+    1: "a token id outside the vocabulary",
+    2: "a gathered row outside the rows of the step",
+    3: "a request index outside the block table",
+    4: "a position whose block lies outside the request's row of the block table",
+    5: "a page id outside the pool",
+    6: "a place outside the array of chosen ids",
+    7: "a query tile whose rows lie outside the step",
+}
+
+
+def decode_check_record(record) -> str:
+    """The sentence for a record of csrc/check.cuh: (code, value, lowest allowed, one past the highest allowed,
+    blockIdx.x, blockIdx.y, blockIdx.z, threadIdx.x); '' when the code is 0."""
+    code, value, lo, hi, bx, by, bz, tx = (int(v) for v in record)
+    if code == 0:
+        return ""
+    what = CHECK_CODES.get(code, f"check code {code}")
+    return f"{what}: {value} is not in [{lo}, {hi}) (block {bx},{by},{bz}, thread {tx})"
+
+
+def _checked(library: str, name: str, f):
+    take = getattr(_lib.load(library), "dl_check_take")
+    take.argtypes = [c_void_p, c_void_p]
+    take.restype = c_int
+    record = (c_longlong * 8)()
+
+    def call(*args):
+        code = f(*args)
+        if code != 0:
+            return code
+        rc = take(record, _stream())
+        if rc != 0:
+            raise EngineError(f"{name}: CUDA error {rc} after the launch")
+        if record[0] != 0:
+            raise EngineError(f"{name} (checked build): {decode_check_record(record)}; the access was not made")
+        return 0
+    return call
+
+
+def check_limits(library: str, pages: int = 0, requests: int = 0, rows: int = 0, vocab: int = 0) -> None:
+    """In a checked build: the ranges that the kernels of `library` compare their indices with from now on (in
+    stream order); 0 = not known, not checked. Nothing otherwise."""
+    if not CHECKED:
+        return
+    f = _funcs.get(("limits", library))
+    if f is None:
+        f = getattr(_lib.load(library), "dl_check_limits")
+        f.argtypes = [_I, _I, _I, _I, _P]
+        f.restype = c_int
+        _funcs[("limits", library)] = f
+    code = f(int(pages), int(requests), int(rows), int(vocab), _stream())
+    if code != 0:
+        raise EngineError(f"dl_check_limits of {library}: CUDA error {code}")
+
 
 def _fn(library: str, name: str):
     f = _funcs.get(name)
@@ -72,6 +133,8 @@ def _fn(library: str, name: str):
         f = getattr(_lib.load(library), name)
         f.argtypes = _SIGNATURES[library][name]
         f.restype = c_int
+        if CHECKED and library != "streams":
+            f = _checked(library, name, f)
         _funcs[name] = f
     if _timing is not None:
         return _timing.timed(name, f)
@@ -292,6 +355,7 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
         raise InvalidArgument("rmsnorm: fewer input rows than output rows")
     parts, part_stride = _delta_parts(delta, width, "rmsnorm")
     dd = dtype_code(delta.dtype) if delta is not None else dtype_code(out.dtype)
+    check_limits("norm", rows=x.shape[0])
     _check(_fn("norm", "dl_rmsnorm")(dtype_code(out.dtype), dd, _p(x), _p(delta), delta_scale, _p(weight), eps,
                                       _p(out), _p(rows), n_rows, width, 1 if write_residual else 0, parts, part_stride,
                                       _stream()), "rmsnorm")
@@ -356,6 +420,8 @@ def rope_cache_write(qkv: torch.Tensor, positions: torch.Tensor, row_request: to
     if rotary_dim > head_dim or rotary_dim % 2:
         raise Unsupported(f"rotary_dim {rotary_dim} does not fit head_dim {head_dim}")
     max_blocks = block_table.stride(0) if block_table is not None else 0
+    if write_cache:
+        check_limits("rope_cache", pages=k_cache.shape[0], requests=block_table.shape[0], rows=rows)
     _check(_fn("rope_cache", "dl_rope_cache_write")(
         dtype_code(qkv.dtype), _p(qkv), qkv.stride(0), _p(positions), _p(row_request), _p(block_table), max_blocks,
         _p(k_cache), _p(v_cache), _p(inv_freq), rotary_dim if inv_freq is not None else 0, pos_scale, rows, n_heads,
@@ -378,6 +444,7 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
         raise InvalidArgument("attention: q, out and the cache must share one dtype")
     if tuple(k_cache.shape[1:]) != (page_size, n_kv_heads, head_dim) or not k_cache.is_contiguous() or not v_cache.is_contiguous():
         raise InvalidArgument("attention: cache shape is not [pages, page_size, kv_heads, head_dim]")
+    check_limits("attention_generic", pages=k_cache.shape[0], requests=block_table.shape[0], rows=q.shape[0])
     _check(_fn("attention_generic", "dl_paged_attention_generic")(
         dtype_code(q.dtype), _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), block_table.stride(0),
         _p(positions), _p(row_request), _p(out), out.stride(0), q.shape[0], n_heads, n_kv_heads, head_dim, page_size,
@@ -411,6 +478,7 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
     need = decode_scratch_floats(rows, n_heads, head_dim, n_split)
     if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
         raise InvalidArgument(f"decode attention: scratch must be float32 with at least {need} elements")
+    check_limits("attention_decode", pages=k_cache.shape[0], requests=block_table.shape[0], rows=rows)
     if tensor_cores:
         if q.dtype != torch.bfloat16 or head_dim > 128 or q.stride(0) % 8 or q.data_ptr() % 16:
             raise Unsupported("decode attention (tensor cores): bfloat16, head_dim up to 128, 16-byte aligned q rows")
@@ -476,11 +544,13 @@ def gemm_qkv_rope(x: torch.Tensor, w_qkv: torch.Tensor, q_out: torch.Tensor, pos
     if not few:
         library, name = (("gemm_tcgen05_cluster", "dl_gemm_tcgen05_cluster_qkv_rope") if tcgen05_pairs(M, w_qkv.shape[0])
                          else ("gemm_tcgen05", "dl_gemm_tcgen05_qkv_rope"))
+        check_limits(library, pages=k_cache.shape[0], requests=block_table.shape[0], rows=M)
         _check(_fn(library, name)(
             _p(x), x.stride(0), _p(w_qkv), _p(q_out), q_out.stride(0), M, K, _p(positions), _p(row_request),
             _p(block_table), block_table.stride(0), _p(k_cache), _p(v_cache), _p(inv_freq), _p(angles), pos_scale, n_heads,
             n_kv_heads, head_dim, page_size, _p(_status_word(x.device)), _stream()), "gemm_tcgen05_qkv_rope")
         return
+    check_limits("gemm_skinny", pages=k_cache.shape[0], requests=block_table.shape[0], rows=M)
     _check(_fn("gemm_skinny", "dl_gemm_skinny_qkv_rope")(
         _p(x), x.stride(0), _p(w_qkv), _p(q_out), q_out.stride(0), M, K, _p(positions), _p(row_request), _p(block_table),
         block_table.stride(0), _p(k_cache), _p(v_cache), _p(inv_freq), pos_scale, n_heads, n_kv_heads, head_dim, page_size,
@@ -548,6 +618,7 @@ def paged_attention_prefill_tcgen05(q: torch.Tensor, k_cache: torch.Tensor, v_ca
         raise InvalidArgument("prefill attention (tcgen05): cache shape is not [pages, page_size, kv_heads, head_dim]")
     if q_tiles.dtype != torch.int32 or q_tiles.numel() < 4 * n_tiles:
         raise InvalidArgument("prefill attention (tcgen05): q_tiles must be int32 [n_tiles, 4]")
+    check_limits("attention_prefill_tcgen05", pages=k_cache.shape[0], requests=block_table.shape[0], rows=q.shape[0])
     _check(_fn("attention_prefill_tcgen05", "dl_paged_attention_prefill_tcgen05")(
         _p(q), q.stride(0), q.shape[0], _p(k_cache), _p(v_cache), k_cache.shape[0], _p(block_table), block_table.stride(0),
         _p(q_tiles), n_tiles, _p(out), out.stride(0), n_heads, n_kv_heads, head_dim, page_size, scale, window,
@@ -573,6 +644,7 @@ def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
         raise InvalidArgument("prefill attention: cache shape is not [pages, page_size, kv_heads, head_dim]")
     if q_tiles.dtype != torch.int32 or q_tiles.numel() < 4 * n_tiles:
         raise InvalidArgument("prefill attention: q_tiles must be int32 [n_tiles, 4]")
+    check_limits("attention_prefill", pages=k_cache.shape[0], requests=block_table.shape[0], rows=q.shape[0])
     _check(_fn("attention_prefill", "dl_paged_attention_prefill")(
         _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), block_table.stride(0), _p(q_tiles), n_tiles,
         _p(out), out.stride(0), n_heads, n_kv_heads, head_dim, page_size, scale, window, _stream()),
@@ -725,6 +797,7 @@ def feedback_tokens(token_ids: torch.Tensor, chosen: torch.Tensor, src: torch.Te
     _cuda(token_ids, chosen, src)
     if token_ids.dtype != torch.int32 or chosen.dtype != torch.int32 or src.dtype != torch.int32 or min(token_ids.numel(), src.numel()) < n:
         raise InvalidArgument("feedback_tokens: int32 tensors with at least n entries")
+    check_limits("sampling", rows=chosen.numel())
     _check(_fn("sampling", "dl_feedback_tokens")(_p(token_ids), _p(chosen), _p(src), n, _stream()), "feedback_tokens")
 
 

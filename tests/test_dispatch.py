@@ -1,6 +1,8 @@
 """Which kernel a matrix product and a decode attention go to, by shape: the decisions of kernels/gemm.py and
 kernels/attention.py on tensors that are never touched (no GPU needed)."""
 
+import os
+
 import torch
 
 from dynalm_b200.kernels import attention, gemm
@@ -57,3 +59,16 @@ def test_decode_attention_splits():
     assert attention.decode_splits(1, 32, 8, 65536) > 8
     # never less than 128 keys per split
     assert attention.decode_splits(1, 32, 8, 256) == 2
+
+
+def test_check_records_are_decoded():
+    """Every code of the checked kernel build (csrc/check.cuh) has its sentence; 0 means nothing happened."""
+    from dynalm_b200.kernels import ops
+    assert ops.decode_check_record([0] * 8) == ""
+    for code, words in ops.CHECK_CODES.items():
+        text = ops.decode_check_record([code, -1, 0, 8, 3, 1, 0, 17])
+        assert words in text and "-1 is not in [0, 8)" in text and "block 3,1,0, thread 17" in text
+    assert "check code 99" in ops.decode_check_record([99, 1, 0, 1, 0, 0, 0, 0])
+    src = open(os.path.join(os.path.dirname(ops.__file__), "..", "csrc", "check.cuh")).read()
+    import re
+    assert sorted(int(m) for m in re.findall(r"#define DL_CK_\w+ (\d+)", src)) == sorted(ops.CHECK_CODES)
