@@ -123,6 +123,112 @@ def prefill_flops(cfg, layers, T):
     return 2.0 * layers * per_layer * T + 4.0 * nh * hd * layers * T * (T + 1) / 2 + 2.0 * V * H
 
 
+def write_random_llama(folder, cfg, seed):
+    """config.json and model.safetensors (bfloat16, N(0, 0.02) matrices, norm weights 1 + N(0, 0.1)) for the reference
+    arm, written with NumPy alone: that arm imports nothing of dynalm_b200."""
+    import numpy as np
+    H, F, V, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
+    qw, kw = cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"]
+    shapes = {"model.embed_tokens.weight": (V, H), "model.norm.weight": (H,)}
+    if not cfg.get("tie_word_embeddings", True):
+        shapes["lm_head.weight"] = (V, H)
+    for l in range(L):
+        p = f"model.layers.{l}."
+        shapes.update({p + "input_layernorm.weight": (H,), p + "post_attention_layernorm.weight": (H,),
+                       p + "self_attn.q_proj.weight": (qw, H), p + "self_attn.k_proj.weight": (kw, H),
+                       p + "self_attn.v_proj.weight": (kw, H), p + "self_attn.o_proj.weight": (H, qw),
+                       p + "mlp.gate_proj.weight": (F, H), p + "mlp.up_proj.weight": (F, H),
+                       p + "mlp.down_proj.weight": (H, F)})
+    header, off = {}, 0
+    for name, shape in shapes.items():
+        n = 2 * int(np.prod(shape))
+        header[name] = {"dtype": "BF16", "shape": list(shape), "data_offsets": [off, off + n]}
+        off += n
+    text = json.dumps(header, separators=(",", ":")).encode()
+    text += b" " * (-len(text) % 8)
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    from concurrent.futures import ThreadPoolExecutor
+    PIECE = 1 << 22
+
+    def piece(job):
+        index, m, vector = job
+        x = np.random.default_rng([seed, index]).standard_normal(m, dtype=np.float32)
+        x = x * np.float32(0.1) + np.float32(1.0) if vector else x * np.float32(0.02)
+        bits = x.view(np.uint32)
+        bits = (bits + np.uint32(0x7FFF) + ((bits >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)    # round to nearest even
+        return bits.astype("<u2").tobytes()
+
+    jobs = []
+    for name, shape in shapes.items():
+        n = int(np.prod(shape))
+        jobs += [(len(jobs) + k, min(PIECE, n - i), len(shape) == 1) for k, i in enumerate(range(0, n, PIECE))]
+    with open(os.path.join(folder, "model.safetensors"), "wb") as f, ThreadPoolExecutor(os.cpu_count() or 4) as pool:
+        f.write(len(text).to_bytes(8, "little"))
+        f.write(text)
+        for data in pool.map(piece, jobs):
+            f.write(data)
+
+
+def reference_arm(args):
+    """`--impl reference`: the same metric from dynalm-project/dynalm's own engine, unmodified, through its public C++
+    API on its CPU device (it has no CUDA code of its own; its GPU backends are ggml's and are fetched from the
+    network when the project is configured). baseline/build_reference.sh builds the program on a machine that has
+    the reference's source; here it is only run. Nothing of dynalm_b200 is imported on this path."""
+    import tempfile
+    exe = os.path.join(ROOT, "baseline", "_ref", "ref_bench")
+
+    def unavailable(why):
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+    if args.gpus != 1:
+        return unavailable("the reference arm is the reference's CPU engine: one process, no GPUs")
+    if not os.path.isfile(exe):
+        return unavailable("baseline/_ref/ref_bench is not built (sh baseline/build_reference.sh <reference source>); "
+                           "pip cannot install the reference: it is a C++/CMake project without setup.py or pyproject.toml")
+    W, K = max(3, args.warmup), max(1, args.steps)
+    cfg = dict(LLAMA_1B)
+    cfg["num_hidden_layers"] = args.layers
+    points = "-" if args.no_points else ",".join(str(b) for b in sorted({1, 64} - {args.batch}))
+    point_steps = min(K, 8)       # batch 64 takes about a second a step on a CPU
+    with tempfile.TemporaryDirectory(prefix="dynalm_ref_") as d:
+        t0 = time.time()
+        write_random_llama(d, cfg, 0)
+        print(f"[bench] reference arm: model folder written in {time.time() - t0:.1f} s", file=sys.stderr)
+        try:
+            proc = subprocess.run([exe, d, str(args.batch), str(HELD), str(K), str(W), str(PREFILL_TOKENS), points, str(point_steps), "0"],
+                                  capture_output=True, text=True, timeout=3000)
+        except (OSError, subprocess.TimeoutExpired) as e:
+            return unavailable(f"baseline/_ref/ref_bench could not be run: {e}")
+    if proc.returncode != 0:
+        return unavailable(f"baseline/_ref/ref_bench exited with {proc.returncode}: {proc.stderr.strip()[-300:]}")
+    r = json.loads(proc.stdout.strip().splitlines()[-1])
+    ms = r["decode_ms_per_step"]
+    out = {
+        "metric": "decode tokens/s, Llama 3.2 1B shape, batch 8, 2048 tokens of context per sequence",
+        "value": round(args.batch / ms * 1e3, 2), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 weights, fp32 activations, f16 cache (the reference's defaults)",
+        "data": "synthetic: random weights N(0, 0.02) seed 0, random token ids",
+        "config": {"model": "llama-3.2-1b-shape", "layers": args.layers, "layers_full": FULL_LAYERS, "hidden": 2048,
+                   "heads": 32, "kv_heads": 8, "head_dim": 64, "intermediate": 8192, "vocab": 128256,
+                   "global_batch": args.batch, "seq_len": HELD, "context": CONTEXT, "kv_block": 16, "parallelism": "none",
+                   "device": f"the reference's CPU device ({r['device']}, {r['threads']} threads): it has no CUDA code",
+                   "tied_embeddings": True},
+        "e2e": {"value": round(r["e2e_tokens_per_s"], 2), "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0, "through": "the reference's Scheduler: token ids in, token callbacks out"},
+        "gpu_launches": 0,
+        "prefill": {"value": round(PREFILL_TOKENS / r["prefill_ms"] * 1e3, 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(r["prefill_ms"], 1)},
+        "points": {f"decode_b{b}": round(int(b) / v * 1e3, 2) for b, v in r["points_ms_per_step"].items()
+                   if int(b) != args.batch},
+        "impl": "reference",
+    }
+    print(json.dumps(out))
+    return 0
+
+
 def serving(name, layers=None):
     """Continuous batching end to end through the Python entry point: all requests submitted at once, prompts
     prefilled in chunks beside decode rows, every request decoding its full count. Prints one JSON line."""
@@ -198,11 +304,7 @@ def main():
     args = ap.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "dynalm-project/dynalm is a C++/CMake project with no Python package (pip: neither setup.py nor "
-                          "pyproject.toml found) and no CUDA code of its own; its GPU path needs ggml fetched from the "
-                          "network at configure time, so only its CPU build exists offline"}))
-        return 0
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
