@@ -7,12 +7,12 @@ from . import models as _models  # noqa: F401  registers architectures
 from . import parts as _parts    # noqa: F401  registers part kinds
 from .registry import find_architecture, register_architecture, registered_architectures
 
-from .engine import Engine, Generation, Request, Scheduler, SchedulerConfig, StepEntry
+from .engine import Engine, Generation, Request, RequestStream, Scheduler, SchedulerConfig, StepEntry
 from .sampling import SamplingParams
 
 __version__ = "0.1.0"
 
 __all__ = ["errors", "Corrupt", "EngineError", "ExtensionMissing", "InvalidArgument", "NotFound",
            "ResourceExhausted", "Unsupported", "find_architecture", "register_architecture",
-           "registered_architectures", "Engine", "Generation", "Request", "Scheduler",
+           "registered_architectures", "Engine", "Generation", "Request", "RequestStream", "Scheduler",
            "SchedulerConfig", "StepEntry", "SamplingParams", "__version__"]

@@ -18,8 +18,10 @@ import sys
 import time
 
 from .. import __version__
+from ..utils import log
 
-USAGE = """usage: dynalm run <model> (--tokens IDS | -p IDS | --prompt-len N) [options]
+USAGE = """usage: dynalm [-q | -v | --log-level LEVEL] <command> [args]
+       dynalm run <model> (--tokens IDS | -p IDS | --prompt-len N) [options]
        dynalm random-model <out_dir> --config FILE --seed S [--dtype bf16|f32]
        dynalm version
   <model>               a folder with config.json and model.safetensors
@@ -27,7 +29,7 @@ USAGE = """usage: dynalm run <model> (--tokens IDS | -p IDS | --prompt-len N) [o
   -p, --prompt IDS      the same (this engine has no tokenizer; the prompt is ids)
   --prompt-len N        a random prompt of N ids drawn with --prompt-seed (default 0)
   -n, --max-tokens N    tokens to generate (default 128)
-  -c, --ctx N           KV cache capacity in tokens (default 4096)
+  -c, --ctx N           KV cache capacity in tokens (default 4096; auto = from the free device memory)
   --batch N             max tokens per forward pass (default 512)
   --kv bf16|f32         KV cache dtype; it follows the compute dtype (see --mode / --dtype)
   --mode M              auto | performance: bfloat16 kernels (default); exact | safe: everything in float32
@@ -42,7 +44,13 @@ sampling (default: greedy):
   --top-k K, --top-p P, --min-p P
   --repeat-penalty R, --presence-penalty P, --frequency-penalty F, --repeat-last-n N
   --seed S              RNG seed (reproducible output)
-global: -q quiet, -v verbose, --version
+  --config FILE         options from a file (else $DYNALM_CONFIG, else ~/.dynalm/config.yaml): the reference's YAML
+                        keys (runtime.context_length, runtime.batch_tokens, runtime.mode, kv_cache.dtype,
+                        sampling.temperature, sampling.max_tokens, model.path) or lines `option = value`;
+                        then DYNALM_CTX, DYNALM_BATCH, DYNALM_MODE, DYNALM_KV, DYNALM_TEMPERATURE,
+                        DYNALM_MAX_TOKENS, DYNALM_MODEL; then the command line: later sources win
+global: -q / --quiet (errors only), -v / --verbose, --log-level trace|debug|info|warn|error|off (default info, or
+        $DYNALM_LOG_LEVEL), --version
 """
 
 
@@ -52,12 +60,13 @@ def _ids(text: str):
 
 def _run_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="dynalm run", add_help=False)
-    ap.add_argument("model")
+    ap.add_argument("model", nargs="?", default=None)
+    ap.add_argument("--model", dest="model_option", default=None)
     ap.add_argument("--tokens", "-p", "--prompt", dest="tokens", action="append", default=[])
     ap.add_argument("--prompt-len", type=int, default=0)
     ap.add_argument("--prompt-seed", type=int, default=0)
     ap.add_argument("-n", "--max-tokens", type=int, default=128)
-    ap.add_argument("-c", "--ctx", type=int, default=4096)
+    ap.add_argument("-c", "--ctx", default="4096")
     ap.add_argument("--batch", type=int, default=512)
     ap.add_argument("--kv", choices=["bf16", "f32", "f16"], default=None)
     ap.add_argument("--mode", choices=["auto", "performance", "exact", "safe"], default="auto")
@@ -80,14 +89,40 @@ def _run_parser() -> argparse.ArgumentParser:
     return ap
 
 
-def cmd_run(argv, quiet: bool) -> int:
+# what `run` takes from the config file and from DYNALM_* (the reference's kRunConfigOptions,
+# dynalm/src/cli/run.cpp:202-207, as far as this engine has the option): name -> takes a value
+RUN_CONFIG_OPTIONS = {"model": True, "ctx": True, "batch": True, "kv": True, "mode": True, "temperature": True,
+                      "max-tokens": True}
+
+
+def cmd_run(argv, env=None) -> int:
+    from ..errors import EngineError
+    from .config import merge_config
+    try:
+        argv = merge_config(argv, RUN_CONFIG_OPTIONS, env)
+    except EngineError as e:
+        print(f"run: {e}", file=sys.stderr)
+        return 1
     args = _run_parser().parse_args(argv)
     if args.help:
         sys.stderr.write(USAGE)
         return 0
+    args.model = args.model or args.model_option
+    if args.model is None:
+        sys.stderr.write(USAGE)
+        return 2
+    if args.ctx == "auto":
+        args.ctx = None              # sized from the free device memory
+    else:
+        try:
+            args.ctx = int(args.ctx)
+            if args.ctx <= 0:
+                raise ValueError
+        except ValueError:
+            print(f"dynalm: --ctx takes a positive number of tokens or 'auto', not '{args.ctx}'", file=sys.stderr)
+            return 2
     import numpy as np
     from ..engine import Engine, SchedulerConfig
-    from ..errors import EngineError
     from ..sampling import SamplingParams
 
     dtype = "float32" if (args.dtype in ("f32", "float32") or args.mode in ("exact", "safe")) else "bfloat16"
@@ -120,13 +155,13 @@ def cmd_run(argv, quiet: bool) -> int:
     timing = (profile.kernel_times(engine.executor.step_fn) if os.environ.get("DYNALM_FORWARD_PROFILE", "0") != "0"
               else contextlib.nullcontext())
     with timing as kernel_times:
-        rc = _generate(args, engine, prompts, sp, quiet)
+        rc = _generate(args, engine, prompts, sp)
     if kernel_times is not None:
-        print("[kernels]\n" + profile.table(kernel_times.totals()), file=sys.stderr)
+        log.info("kernels", "\n" + profile.table(kernel_times.totals()))
     return rc
 
 
-def _generate(args, engine, prompts, sp, quiet: bool) -> int:
+def _generate(args, engine, prompts, sp) -> int:
     from ..engine import Request
     t0 = time.perf_counter()
     ids = [engine.scheduler.submit(Request(p, args.max_tokens, s, tuple(args.stop_id))) for p, s in zip(prompts, sp)]
@@ -161,7 +196,7 @@ def _generate(args, engine, prompts, sp, quiet: bool) -> int:
         if final[i].error:
             print(f"dynalm: request {i}: {final[i].error}", file=sys.stderr)
             rc = 1
-    if not quiet:
+    if log.enabled(log.INFO):
         gaps.sort()
 
         def pct(p):
@@ -170,15 +205,18 @@ def _generate(args, engine, prompts, sp, quiet: bool) -> int:
         n_gen = sum(len(v) for v in out.values())
         decode_s = (total_ms - (ttft or 0.0)) / 1e3
         reason = ",".join(sorted({str(final[i].finish_reason or final[i].status) for i in ids}))
-        print(f"\n[stats] prompt {n_prompt} tok | TTFT {ttft or 0.0:.1f} ms | generated {n_gen} tok, "
-              f"{(n_gen - len(ids)) / decode_s if decode_s > 0 else 0.0:.1f} tok/s | finish {reason} | "
-              f"inter-delta p50 {pct(50):.1f} p90 {pct(90):.1f} p99 {pct(99):.1f} ms", file=sys.stderr)
+        log.info("stats", f"prompt {n_prompt} tok | TTFT {ttft or 0.0:.1f} ms | generated {n_gen} tok, "
+                 f"{(n_gen - len(ids)) / decode_s if decode_s > 0 else 0.0:.1f} tok/s | finish {reason} | "
+                 f"inter-delta p50 {pct(50):.1f} p90 {pct(90):.1f} p99 {pct(99):.1f} ms")
         ss = engine.scheduler.stats
         if ss.steps_decode_only > 0:
-            print(f"[engine] prefill {ss.forward_prefill_only_ms + ss.forward_mixed_ms:.1f} ms (forward, "
-                  f"{ss.steps_prefill_only + ss.steps_mixed} steps) | decode step "
-                  f"{ss.forward_decode_only_ms / ss.steps_decode_only:.2f} ms (forward, {ss.steps_decode_only} steps)",
-                  file=sys.stderr)
+            log.info("engine", f"prefill {ss.forward_prefill_only_ms + ss.forward_mixed_ms:.1f} ms (forward, "
+                     f"{ss.steps_prefill_only + ss.steps_mixed} steps) | decode step "
+                     f"{ss.forward_decode_only_ms / ss.steps_decode_only:.2f} ms (forward, {ss.steps_decode_only} steps)")
+        st = engine.stats()
+        log.debug("engine", f"cache {st['pages']} pages ({st['cache_bytes'] / 2**20:.0f} MiB), workspace "
+                  f"{st['workspace_bytes'] / 2**20:.0f} MiB, {st['kernel_launches']} kernel launches, "
+                  f"{st['library_products']} library products, {st['graphs']['captured']} graphs captured")
     return rc
 
 
@@ -199,22 +237,38 @@ def cmd_random_model(argv) -> int:
 
 
 def main(argv=None) -> int:
+    """Global options come before the command (dynalm/src/cli/main.cpp:118-151): -q / --quiet (errors only),
+    -v / --verbose (debug), --log-level trace|debug|info|warn|error|off|quiet|normal|verbose; DYNALM_LOG_LEVEL sets
+    the default."""
     argv = list(sys.argv[1:] if argv is None else argv)
-    quiet = False
-    while argv and argv[0] in ("-q", "-v", "--version") or (argv and argv[0].startswith("--log-level")):
+    while argv and argv[0].startswith("-") and argv[0] not in ("-h", "--help"):
         flag = argv.pop(0)
         if flag == "--version":
             print(f"dynalm_b200 {__version__}")
             return 0
         if flag == "--log-level" and argv:
-            argv.pop(0)
-        quiet = quiet or flag == "-q"
+            name = argv.pop(0)
+            if not log.set_level(name):
+                print(f"dynalm: invalid log level '{name}' (quiet, normal, verbose, debug, trace)", file=sys.stderr)
+                return 1
+        elif flag.startswith("--log-level="):
+            if not log.set_level(flag.split("=", 1)[1]):
+                print(f"dynalm: invalid log level '{flag.split('=', 1)[1]}' (quiet, normal, verbose, debug, trace)",
+                      file=sys.stderr)
+                return 1
+        elif flag in ("-q", "--quiet"):
+            log.set_level("quiet")
+        elif flag in ("-v", "--verbose"):
+            log.set_level("verbose")
+        else:
+            print(f"dynalm: unknown option '{flag}'", file=sys.stderr)
+            return 1
     if not argv or argv[0] in ("-h", "--help", "help"):
         sys.stderr.write(USAGE)
         return 0 if argv else 2
     cmd, rest = argv[0], argv[1:]
     if cmd == "run":
-        return cmd_run(rest, quiet)
+        return cmd_run(rest)
     if cmd == "random-model":
         return cmd_random_model(rest)
     if cmd == "version":

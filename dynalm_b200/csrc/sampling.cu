@@ -13,9 +13,11 @@ namespace dl {
 constexpr int SAMPLE_THREADS = 1024;
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
-argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restrict__ out) {
+argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restrict__ out,
+              const int* __restrict__ status_src, int* __restrict__ status_dst) {
   __shared__ float bv[32];
   __shared__ int bi[32];
+  if (status_dst != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *status_dst = *status_src;
   const float* row = logits + static_cast<size_t>(blockIdx.x) * ld;
   float best = -INFINITY;
   int idx = 0x7fffffff;
@@ -80,8 +82,10 @@ argmax_part_kernel(const float* __restrict__ logits, int ld, int vocab, float* _
   }
 }
 
-__global__ void argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int* __restrict__ out) {
+__global__ void argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int* __restrict__ out,
+                                    const int* __restrict__ status_src, int* __restrict__ status_dst) {
   const int r = blockIdx.x, lane = threadIdx.x;     // 32 threads
+  if (status_dst != nullptr && r == 0 && lane == 0) *status_dst = *status_src;
   float best = pv[r * ARGMAX_PARTS + lane];
   int idx = pi[r * ARGMAX_PARTS + lane];
   for (int o = 16; o > 0; o >>= 1) {
@@ -171,8 +175,10 @@ DL_EXPORT int dl_feedback_tokens(int* token_ids, const int* chosen, const int* s
 }
 
 // scratch: room for rows * 32 floats and rows * 32 ints (rows * 256 bytes), or null to use one block per row.
+// status_dst (may be null): receives *status_src, so that a word some earlier kernel of the step may have written
+// travels to the host in the same copy as the chosen ids.
 DL_EXPORT int dl_argmax(const float* logits, int ld, int rows, int vocab, int* out, void* scratch,
-                        cudaStream_t stream) {
+                        const int* status_src, int* status_dst, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0) return DL_ERR_UNSUPPORTED;
   if (scratch != nullptr && vocab >= 8192 && rows <= 65535) {
@@ -180,10 +186,10 @@ DL_EXPORT int dl_argmax(const float* logits, int ld, int rows, int vocab, int* o
     int* pi = reinterpret_cast<int*>(pv + static_cast<size_t>(rows) * dl::ARGMAX_PARTS);
     dim3 grid(dl::ARGMAX_PARTS, rows);
     dl::argmax_part_kernel<<<grid, 256, 0, stream>>>(logits, ld, vocab, pv, pi);
-    dl::argmax_final_kernel<<<rows, 32, 0, stream>>>(pv, pi, out);
+    dl::argmax_final_kernel<<<rows, 32, 0, stream>>>(pv, pi, out, status_src, status_dst);
     return dl::launch_status();
   }
-  dl::argmax_kernel<<<rows, dl::SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, out);
+  dl::argmax_kernel<<<rows, dl::SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, out, status_src, status_dst);
   return dl::launch_status();
 }
 

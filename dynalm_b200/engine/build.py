@@ -13,6 +13,7 @@ from ..cache import DEFAULT_PAGE_SIZE, CacheManager
 from ..errors import InvalidArgument
 from ..registry import find_architecture
 from ..weights.loader import check_tensors, open_model_folder, place_tensors
+from . import memory
 from .model import Decoder
 from .runtime import Runtime, parse_dtype
 from .step import StepFunction
@@ -36,12 +37,15 @@ def build(model_dir: Optional[str] = None, *, config_obj: Optional[Mapping[str, 
 
     model_dir          a folder with config.json and model.safetensors, or
     config_obj+tensors a config.json dict and CPU tensors by file name (random-weights mode without a file)
-    kv_tokens          tokens the cache pool holds over all live requests (default: the context length)
+    kv_tokens          tokens the cache pool holds over all live requests (default: sized from the device memory that
+                       is free after the weights, engine/memory.py); a size that cannot fit is refused before
+                       anything is allocated, with the largest size that would fit
     max_batch_tokens   the most tokens one step may bring
     context            the longest one request may grow (default: max_position_embeddings)
     """
     compute = parse_dtype(dtype)
     runtime = Runtime(device, compute, max_tokens=max_batch_tokens, max_requests=max_requests)
+    free_before = torch.cuda.mem_get_info(runtime.device)[0]
     if model_dir is not None:
         folder = open_model_folder(model_dir)
         config, plan = folder.config, folder.plan
@@ -57,8 +61,13 @@ def build(model_dir: Optional[str] = None, *, config_obj: Optional[Mapping[str, 
         store = place_tensors(plan, tensors, runtime.device, compute)
     model = Decoder(plan, store, runtime)
     ctx_len = int(context or plan.context_length)
-    kv = int(kv_tokens or ctx_len)
-    cache = CacheManager(model.cache_specs(), page_size, kv, max_requests, ctx_len, runtime.device, compute)
+    specs = model.cache_specs()
+    per_token = memory.cache_bytes_per_token(specs, 2 if compute == torch.bfloat16 else 4)
+    weights = model.weight_bytes()
+    kv = int(kv_tokens) if kv_tokens else memory.auto_kv_tokens(ctx_len, per_token, weights, free_before)
+    pages = -(-kv // page_size)
+    memory.check_memory_fit(weights, pages * page_size * per_token, per_token, free_before)
+    cache = CacheManager(specs, page_size, kv, max_requests, ctx_len, runtime.device, compute)
     step_fn = StepFunction(model, cache, runtime, max_requests)
     if compute == torch.bfloat16:
         # the library product that a few shapes still go to (kernels/gemm.py) sets itself up at its first call, which

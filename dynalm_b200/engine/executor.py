@@ -40,9 +40,11 @@ class GpuExecutor:
         dev = step_fn.rt.device
         n = step_fn.max_requests
         self._n = n
-        self._ids = torch.zeros(2 * n, dtype=torch.int32, device=dev)            # greedy | drawn
+        # greedy | drawn | the device's status word as the step left it (a code when a bounded wait inside a kernel
+        # gave up): it reaches the host in the copy of the ids, so every step is checked without another wait
+        self._ids = torch.zeros(2 * n + 1, dtype=torch.int32, device=dev)
         # two host copies of everything a launch leaves behind: one launch may be in flight while the next is made
-        self._ids_host = [torch.zeros(2 * n, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._ids_host = [torch.zeros(2 * n + 1, dtype=torch.int32).pin_memory() for _ in range(2)]
         self._temp_host = [torch.ones(n, dtype=torch.float32).pin_memory() for _ in range(2)]
         self._u_host = [torch.zeros(n, dtype=torch.float64).pin_memory() for _ in range(2)]
         self._temp = torch.ones(n, dtype=torch.float32, device=dev)
@@ -65,7 +67,7 @@ class GpuExecutor:
 
     def _sample_on_device(self, logits: torch.Tensor, want: List[BatchItem], slot: int) -> None:
         n = len(want)
-        ops.argmax(logits, self._ids[:n])
+        ops.argmax(logits, self._ids[:n], status_to=self._ids[2 * self._n:])
         if any(not b.seq.sampler.params.greedy and b.seq.sampler.on_device for b in want):
             th, uh = self._temp_host[slot], self._u_host[slot]
             for i, b in enumerate(want):
@@ -99,14 +101,20 @@ class GpuExecutor:
 
     def collect(self, launched: Launched) -> Dict[Hashable, int]:
         launched.event.synchronize()
-        self._check_status()
         ids = self._ids_host[launched.slot].numpy()
+        self._check_status(ids)
         return {req: int(ids[place]) for req, place in launched.places.items()}
 
-    def _check_status(self) -> None:
+    def _check_status(self, ids) -> None:
+        """`ids`: the host copy of a step's chosen ids, whose last element is the status word as that step left it.
+        A code there means that a kernel of the step (or of a step launched since the last check) gave up a bounded
+        wait: nothing those steps computed is valid, keys and values they wrote included. The word is cleared, so
+        that the steps after the failed requests have been dropped start clean."""
         self.steps += 1
-        if self.steps % 64 == 1 and ops.gemm_tcgen05_status() != 0:
-            raise EngineError("a tcgen05 matrix product gave up waiting on a barrier; its results are not valid")
+        code = int(ids[2 * self._n])
+        if code != 0:
+            ops.clear_status(self.step_fn.rt.device)
+            raise EngineError(f"a kernel gave up waiting on a barrier (status {code}); the step's results are not valid")
 
     # ---- any batch, synchronously ------------------------------------------------------------------------
     def run(self, batch: List[BatchItem]) -> Dict[Hashable, int]:
@@ -129,8 +137,8 @@ class GpuExecutor:
             rows = logits[:n].index_select(0, idx).to("cpu", non_blocking=False).numpy()
             self.d2h_bytes += rows.nbytes
         torch.cuda.current_stream().synchronize()
-        self._check_status()
         ids = self._ids_host[slot].numpy()
+        self._check_status(ids)
         out: Dict[Hashable, int] = {}
         for i, b in enumerate(want):
             s = b.seq.sampler

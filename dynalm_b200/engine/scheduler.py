@@ -28,6 +28,7 @@ executor is `dynalm_b200.engine.executor.GpuExecutor`; tests use a fake to check
 
 from __future__ import annotations
 
+import threading
 import time
 from collections import deque
 from dataclasses import dataclass, field
@@ -245,31 +246,61 @@ class Scheduler:
         self._mixed_prefill_budget = self.cfg.prefill_token_budget
         self.stats.mixed_prefill_budget = self._mixed_prefill_budget
         self.lookahead = hasattr(executor, "launch") and hasattr(executor, "collect")
+        # `submit` and `cancel` may come from any thread (scheduler.cpp:167-190): they only touch what this lock
+        # guards (the hand-off list, the cancel list, the id counter, the table of callbacks); `step` takes both
+        # lists over at its top and everything else belongs to the thread that calls `step`.
+        self._handoff = threading.Lock()
+        self._cancels: List[int] = []
+        self.on_submit: Optional[Callable[[], None]] = None      # called after every submit and cancel (an engine's wake-up)
 
     # ---- submission ----------------------------------------------------------------------------------
     def submit(self, req: Request) -> int:
-        rid = self._next_id
-        self._next_id += 1
-        self._arrivals += 1
-        seq = SequenceState(rid, req, self._arrivals)
-        if req.timeout_ms > 0:
-            seq.deadline = self.clock() + req.timeout_ms / 1000.0
-        if self.request_traces is not None:
-            seq.trace = RequestTrace(rid, seq.prompt_len, submit_s=self.clock())
-        self.by_id[rid] = seq
-        self.incoming.append(seq)
-        if req.on_event is not None:
-            self._callbacks[rid] = req.on_event
+        """Thread-safe. The request is taken in at the top of the next `step`; an invalid one fails through its
+        callback then."""
+        with self._handoff:
+            rid = self._next_id
+            self._next_id += 1
+            self._arrivals += 1
+            seq = SequenceState(rid, req, self._arrivals)
+            if req.timeout_ms > 0:
+                seq.deadline = self.clock() + req.timeout_ms / 1000.0
+            if self.request_traces is not None:
+                seq.trace = RequestTrace(rid, seq.prompt_len, submit_s=self.clock())
+            self.incoming.append(seq)
+            if req.on_event is not None:
+                self._callbacks[rid] = req.on_event
+        if self.on_submit is not None:
+            self.on_submit()
         return rid
 
     def cancel(self, rid: int) -> None:
-        seq = self.by_id.get(rid)
-        if seq is not None:
-            seq.cancel_requested = True
+        """Thread-safe; takes effect at the next `step`. Unknown ids are ignored."""
+        with self._handoff:
+            self._cancels.append(rid)
+        if self.on_submit is not None:
+            self.on_submit()
+
+    def cancel_all(self) -> None:
+        """Thread-safe: every request known at the next `step` is cancelled."""
+        self.cancel(None)
 
     @property
     def idle(self) -> bool:
-        return not (self.incoming or self.waiting or self.running or self._inflight)
+        with self._handoff:
+            return not (self.incoming or self._cancels or self.waiting or self.running or self._inflight)
+
+    def _take_handoff(self) -> List[SequenceState]:
+        """What other threads have handed over since the last step: new requests (returned) and cancellations (marked)."""
+        with self._handoff:
+            new, self.incoming = self.incoming, []
+            cancels, self._cancels = self._cancels, []
+        for seq in new:
+            self.by_id[seq.id] = seq
+        for rid in cancels:
+            for seq in (list(self.by_id.values()) if rid is None else [self.by_id.get(rid)]):
+                if seq is not None:
+                    seq.cancel_requested = True
+        return new
 
     # ---- one iteration ---------------------------------------------------------------------------------
     def _fail(self, seq: SequenceState, msg: str, events: List[Event]) -> None:
@@ -289,7 +320,8 @@ class Scheduler:
         """Validate new requests (scheduler.cpp:245-275) and queue them by priority, then arrival."""
         cache = self.ex.cache
         vocab = getattr(self.ex, "vocab", None)
-        for seq in self.incoming:
+        incoming = self._take_handoff()
+        for seq in incoming:
             req = seq.req
             try:
                 req.sampling.validate()
@@ -311,8 +343,7 @@ class Scheduler:
                 continue
             seq.sampler = Sampler(req.sampling)
             self.waiting.append(seq)
-        if self.incoming:
-            self.incoming.clear()
+        if incoming:
             self.waiting = deque(sorted(self.waiting, key=lambda s: (-s.req.priority, s.arrival)))
 
     def _expire_deadlines(self, events: List[Event]) -> None:
@@ -459,7 +490,7 @@ class Scheduler:
     def _plan_ahead(self, prev: List[BatchItem]) -> Optional[List[BatchItem]]:
         """The decode batch that follows `prev` (issued, not yet collected), or None when the steady state does
         not hold. Tokens are placeholders: the executor feeds them on the device from what `prev` chose."""
-        if self.incoming or self.waiting or len(prev) != len(self.running):
+        if self.incoming or self._cancels or self.waiting or len(prev) != len(self.running):
             return None
         if any(s.cancel_requested or s.terminal for s in self.running):
             return None
@@ -484,7 +515,8 @@ class Scheduler:
         if self._callbacks and events:
             t0 = time.perf_counter()
             for ev in events:
-                seq_cb = self._callbacks.pop(ev.request_id, None) if ev.finished else self._callbacks.get(ev.request_id)
+                with self._handoff:
+                    seq_cb = self._callbacks.pop(ev.request_id, None) if ev.finished else self._callbacks.get(ev.request_id)
                 if seq_cb is not None:
                     seq_cb(ev)
             self.stats.emit_ms += (time.perf_counter() - t0) * 1e3
@@ -513,6 +545,16 @@ class Scheduler:
                 for b in prev:
                     self._fail(b.seq, f"forward failed: {e}", events)
                 sampled = None
+                if nxt_launched is not None:
+                    # the batch issued ahead took its tokens from the failed one: wait for it and drop what it made
+                    try:
+                        self.ex.collect(nxt_launched)
+                    except EngineError:
+                        pass
+                    for b in nxt:
+                        if not b.seq.terminal:
+                            self._fail(b.seq, f"forward failed: {e}", events)
+                    nxt = None
             # a batch's time: from its launch, or from the moment the batch before it was done, to its collection
             now = time.perf_counter()
             self._account(prev, (now - max(t_launch, self._last_done)) * 1e3)

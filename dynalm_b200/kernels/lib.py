@@ -24,6 +24,7 @@ import time
 from typing import Dict, List, Optional
 
 from ..errors import ExtensionMissing
+from ..utils import log as _log
 
 CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc")
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -35,7 +36,7 @@ _libs: Dict[str, ctypes.CDLL] = {}
 
 
 def _say(msg: str) -> None:
-    print(f"[dynalm_b200] {msg}", file=sys.stderr, flush=True)
+    _log.info("dynalm_b200", msg)
 
 
 def find_nvcc() -> str:

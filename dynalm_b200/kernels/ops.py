@@ -53,7 +53,7 @@ _SIGNATURES = {
         "dl_gemm_stream": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _L, _P, _P]},
     "gemm_simt": {"dl_gemm_simt": [_I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _P]},
     "sampling": {
-        "dl_argmax": [_P, _I, _I, _I, _P, _P, _P],
+        "dl_argmax": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
         "dl_sample_temperature": [_P, _I, _I, _I, _P, _P, _P, _P],
         "dl_feedback_tokens": [_P, _P, _P, _I, _P],
     },
@@ -775,8 +775,10 @@ def gemm_stream(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str =
 _argmax_scratch = {}
 
 
-def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
-    """out[r] = lowest index of the largest value of logits[r, :] (float32 rows, int32 out)."""
+def argmax(logits: torch.Tensor, out: torch.Tensor, status_to: Optional[torch.Tensor] = None) -> None:
+    """out[r] = lowest index of the largest value of logits[r, :] (float32 rows, int32 out). `status_to` (int32, one
+    element): also receives the device's status word (see gemm_tcgen05_status), so that it can travel to the host
+    in the copy that carries the chosen ids."""
     _cuda(logits, out)
     _rows_contiguous(logits, "logits")
     rows = logits.shape[0]
@@ -788,8 +790,16 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     if scratch is None or scratch.numel() < rows * 64:
         scratch = torch.empty(max(64, 1 << (rows * 64 - 1).bit_length()), dtype=torch.float32, device=logits.device)
         _argmax_scratch[key] = scratch
+    status = _status_word(logits.device) if status_to is not None else None
     _check(_fn("sampling", "dl_argmax")(_p(logits), logits.stride(0), rows, logits.shape[1], _p(out), _p(scratch),
-                                         _stream()), "argmax")
+                                         _p(status), _p(status_to), _stream()), "argmax")
+
+
+def clear_status(device) -> None:
+    """Zero the device's status word after its code has been reported."""
+    t = _tcgen05_status.get(torch.device(device))
+    if t is not None:
+        t.zero_()
 
 
 def feedback_tokens(token_ids: torch.Tensor, chosen: torch.Tensor, src: torch.Tensor, n: int) -> None:

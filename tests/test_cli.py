@@ -46,3 +46,60 @@ def test_random_model_writes_a_folder_the_loader_reads(tmp_path, capsys):
     assert folder.config.num_hidden_layers == TINY_B["num_hidden_layers"]
     assert len(folder.plan.layers) == TINY_B["num_hidden_layers"]
     folder.close()
+
+
+def test_config_file_environment_and_command_line_merge(tmp_path):
+    """config file < DYNALM_* < command line, both file formats, unknown keys with their line."""
+    import pytest
+    from dynalm_b200.cli.config import merge_config, parse_config_text
+    from dynalm_b200.cli.main import RUN_CONFIG_OPTIONS, _run_parser
+    from dynalm_b200.errors import InvalidArgument, NotFound
+    yaml = tmp_path / "config.yaml"
+    yaml.write_text("# a comment\nruntime:\n  context_length: 2048   # tokens\n  batch_tokens: \"256\"\n"
+                    "  threads: 8\nsampling:\n  temperature: 0.7\nserver:\n  port: 9000\nkv_cache:\n  dtype: bf16\n")
+    env = {"DYNALM_CONFIG": str(yaml), "DYNALM_BATCH": "384", "DYNALM_MAX_TOKENS": "9"}
+    merged = merge_config(["/m", "--tokens", "1,2", "--max-tokens", "5"], RUN_CONFIG_OPTIONS, env.get)
+    # the server's port and the thread count are documented keys that `run` here has no option for: skipped
+    assert merged == ["--ctx", "2048", "--batch", "256", "--temperature", "0.7", "--kv", "bf16", "--batch", "384",
+                      "--max-tokens", "9", "/m", "--tokens", "1,2", "--max-tokens", "5"]
+    args = _run_parser().parse_args(merged)
+    assert (args.ctx, args.batch, args.temp, args.max_tokens, args.model) == ("2048", 384, 0.7, 5, "/m")
+    # --config beats $DYNALM_CONFIG; the flat format; the model from the file
+    flat = tmp_path / "flat.conf"
+    flat.write_text("ctx = 512\nmodel = /from/file\nmode = exact\n")
+    merged = merge_config(["--config", str(flat), "--prompt-len", "4"], RUN_CONFIG_OPTIONS, env.get)
+    args = _run_parser().parse_args(merged)
+    assert args.ctx == "512" and args.model_option == "/from/file" and args.mode == "exact" and args.batch == 384
+    with pytest.raises(InvalidArgument, match=r"bad.yaml:2: unknown key 'runtime.speed'"):
+        parse_config_text("runtime:\n  speed: 3\n", RUN_CONFIG_OPTIONS, "bad.yaml")
+    with pytest.raises(InvalidArgument, match=r"f:1: unknown key 'port'"):
+        parse_config_text("port = 1\n", RUN_CONFIG_OPTIONS, "f")
+    with pytest.raises(InvalidArgument, match="lists"):
+        parse_config_text("runtime:\n  threads: [1, 2]\n", RUN_CONFIG_OPTIONS, "f")
+    with pytest.raises(NotFound):
+        merge_config(["--config", str(tmp_path / "none.yaml")], RUN_CONFIG_OPTIONS, {}.get)
+    with pytest.raises(InvalidArgument, match="--config needs"):
+        merge_config(["--config"], RUN_CONFIG_OPTIONS, {}.get)
+    # a file's error reaches the user as one line of `run`
+    bad = tmp_path / "bad.yaml"
+    bad.write_text("nonsense:\n  key: 1\n")
+    assert main(["run", "/m", "--config", str(bad), "--tokens", "1"]) == 1
+
+
+def test_log_levels_gate_the_package_lines(capsys):
+    from dynalm_b200.utils import log
+    before = log.level()
+    try:
+        assert main(["--log-level", "loud", "version"]) == 1
+        assert "invalid log level 'loud'" in capsys.readouterr().err
+        assert main(["--bogus", "version"]) == 1
+        assert "unknown option '--bogus'" in capsys.readouterr().err
+        for flags, shown in ((["-q"], {"error"}), ([], {"error", "warn", "info"}), (["-v"], {"error", "warn", "info", "debug"}),
+                             (["--log-level", "off"], set()), (["--log-level=warn"], {"error", "warn"})):
+            log.set_level("normal")
+            assert main(flags + ["version"]) == 0
+            capsys.readouterr()
+            log.error("t", "error"), log.warn("t", "warn"), log.info("t", "info"), log.debug("t", "debug")
+            assert set(capsys.readouterr().err.replace("[t] ", "").split()) == shown, flags
+    finally:
+        log.set_level(before)

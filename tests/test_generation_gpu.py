@@ -196,3 +196,70 @@ def test_scheduler_under_random_load_gives_the_tokens_of_each_request_alone(seed
         assert got[i] == want, f"request {i} (prompt {len(prompts[i])}, {new[i]} new, temperature {samp[i].temperature})"
         checked += 1
     assert checked >= n // 2
+
+
+def test_cache_size_is_admitted_before_it_is_allocated(tiny_folders):
+    """A --ctx that cannot fit the device is refused with the size that would fit, not by an out-of-memory error in
+    the middle of the allocation; without a size the cache is sized from the free memory."""
+    import torch
+    from dynalm_b200 import Engine
+    from dynalm_b200.errors import ResourceExhausted
+    free = torch.cuda.mem_get_info()[0]
+    per_token = 2 * 2 * 2 * 16 * 4             # config a in float32: 2 layers x (k, v) x 2 KV heads x 16 x 4 bytes
+    too_many = free // per_token * 2 // 16 * 16
+    with pytest.raises(ResourceExhausted, match=r"not enough GPU memory.*use --ctx \d+ or less"):
+        Engine(tiny_folders["a"], dtype="float32", ctx=too_many, batch=64, max_running=4)
+    assert torch.cuda.mem_get_info()[0] >= free - (256 << 20)          # nothing large was allocated on the way
+    eng = Engine(tiny_folders["a"], dtype="float32", batch=64, max_running=4)
+    assert eng.built.cache.num_pages * 16 == 65536                      # plenty of memory: the cap of the automatic size
+    assert eng.generate([1, 2, 3], max_tokens=4).status == "finished"
+
+
+def test_engine_thread_serves_submitters_on_other_threads(tiny_folders):
+    """The engine runs on its own thread; two threads submit requests while a third reads the streams. Every
+    request gets the tokens it gets alone (32-bit: the logits do not depend on what else is in a batch), a stream's
+    `next` times out instead of blocking when nothing has come, a cancelled stream ends as cancelled, and after
+    shutdown nothing is held."""
+    import threading
+    name = "b"
+    cfg = TINY[name][0]
+    reqs = list(random_requests(cfg["vocab_size"], [5, 17, 33, 9, 40, 12, 26, 3], seed=3).values())
+    alone_engine = _engine(tiny_folders[name], "float32")
+    alone = [alone_engine.generate(p, max_tokens=12).tokens for p in reqs]
+    eng = _engine(tiny_folders[name], "float32")
+    eng.start()
+    streams, lock = {}, threading.Lock()
+
+    def submitter(k):
+        for i in range(k, len(reqs), 2):
+            st = eng.submit(reqs[i], max_tokens=12)
+            with lock:
+                streams[i] = st
+    got = {}
+
+    def reader():
+        while len(got) < len(reqs):
+            with lock:
+                todo = [(i, st) for i, st in streams.items() if i not in got]
+            for i, st in todo:
+                got[i] = st.tokens()
+    threads = [threading.Thread(target=submitter, args=(k,)) for k in range(2)] + [threading.Thread(target=reader)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=120)
+        assert not t.is_alive()
+    assert [got[i] for i in range(len(reqs))] == alone
+    # nothing submitted: `next` gives up after its timeout; a long request is cancelled in the middle
+    long = eng.submit(reqs[2], max_tokens=200)
+    first = long.next(timeout=30.0)
+    assert first is not None and first.token is not None
+    long.cancel()
+    rest = list(long)
+    assert rest and rest[-1].finished and rest[-1].status == "cancelled" and long.next(timeout=0.01) is None
+    # generate() and stream() go through the thread while it runs
+    assert eng.generate(reqs[0], max_tokens=12).tokens == alone[0]
+    assert [ev.token for ev in eng.stream(reqs[1], max_tokens=12) if ev.token is not None] == alone[1]
+    eng.shutdown()
+    assert eng.loop_error is None and eng.scheduler.idle
+    assert eng.built.cache.free_pages == eng.built.cache.num_pages

@@ -6,6 +6,7 @@ import hashlib
 
 import torch
 
+from dynalm_b200.errors import EngineError
 from dynalm_b200.cache import CacheManager
 from dynalm_b200.engine.scheduler import (CANCELLED, ERROR, FINISHED, Request, Scheduler, SchedulerConfig)
 from dynalm_b200.parts.base import CacheSpec
@@ -269,6 +270,35 @@ def test_decoding_one_step_ahead_gives_the_same_tokens():
     assert got_toks == want_toks and got_reasons == want_reasons and "eog" in got_reasons
 
 
+def test_a_failed_step_with_a_batch_in_flight_fails_both_and_frees_everything():
+    """The GPU executor finds a step's status word in the copy of its chosen ids and raises when a kernel gave up a
+    wait. By then the next batch has been issued from the failed one's tokens: its requests fail too, nothing of it
+    is emitted, every page comes back, and requests submitted afterwards run normally."""
+    class Failing(FakeAsyncExecutor):
+        fail_at = 6
+
+        def collect(self, handle):
+            self.collected = getattr(self, "collected", 0) + 1
+            if self.collected == self.fail_at:
+                raise EngineError("a kernel gave up waiting on a barrier (status 3); the step's results are not valid")
+            if self.collected == self.fail_at + 1:
+                return {}            # the batch that was in flight behind the failed one: waited for, nothing kept
+            return super().collect(handle)
+
+    ex = Failing()
+    s = Scheduler(ex, SchedulerConfig(max_running=8, decode_token_budget=8, prefill_token_budget=64,
+                                      max_prefill_chunk=32, max_batch_tokens=128))
+    ids = [s.submit(Request(p, max_new_tokens=20)) for p in prompts(3, [12, 20, 7])]
+    toks, final = collect(run_all(s))
+    assert all(final[i].status == "error" and "gave up waiting" in final[i].error for i in ids)
+    assert all(len(toks[i]) < 20 for i in ids)
+    assert not ex.live and ex.cache.free_pages == ex.cache.num_pages and s.idle
+    ex.cache.check()
+    again = s.submit(Request(prompts(1, [9])[0], max_new_tokens=5))
+    toks, final = collect(run_all(s))
+    assert final[again].status == FINISHED and len(toks[again]) == 5
+
+
 def test_one_step_ahead_with_arrivals_cancels_and_few_pages():
     """Requests arriving, being cancelled and being preempted while batches are in flight: the scheduler falls
     back to the ordinary iteration whenever the steady state does not hold, and the tokens stay the same."""
@@ -505,3 +535,47 @@ def test_engine_stats_snapshot_names_how_steps_were_issued():
     assert got["scheduler"]["steps"] == 3 and got["free_pages"] == 5 and got["pages"] == 8
     assert got["graphs"] == {"captured": 2, "capture_ms": 9.877, "replayed_kernel_launches": 232}
     assert {"kernel_launches", "library_products", "layers_issued_by_address", "cache_bytes", "workspace_bytes"} <= set(got)
+
+
+def test_submit_and_cancel_from_other_threads():
+    """Four threads submit (and one of them cancels) while this thread steps: every request ends exactly once, the
+    ones that were not cancelled with the tokens they get alone, and nothing stays held."""
+    import threading
+    ps = prompts(24, [10 + 3 * (i % 7) for i in range(24)])
+    alone = {}
+    for i, p in enumerate(ps):
+        s1 = Scheduler(FakeExecutor(), SchedulerConfig(max_running=8, max_batch_tokens=128))
+        rid = s1.submit(Request(p, max_new_tokens=6))
+        alone[i] = collect(run_all(s1))[0][rid]
+    ex = FakeAsyncExecutor()
+    s = Scheduler(ex, SchedulerConfig(max_running=8, decode_token_budget=8, prefill_token_budget=64,
+                                      max_prefill_chunk=32, max_batch_tokens=128))
+    rid_of, cancelled, lock = {}, set(), threading.Lock()
+
+    def worker(k):
+        for i in range(k, len(ps), 4):
+            rid = s.submit(Request(ps[i], max_new_tokens=6))
+            with lock:
+                rid_of[i] = rid
+            if k == 3 and i % 8 == 3:
+                s.cancel(rid)
+                with lock:
+                    cancelled.add(i)
+    threads = [threading.Thread(target=worker, args=(k,)) for k in range(4)]
+    for t in threads:
+        t.start()
+    events = []
+    while any(t.is_alive() for t in threads) or not s.idle:
+        events += s.step()
+    for t in threads:
+        t.join()
+    toks, final = collect(events)
+    assert sorted(final) == sorted(rid_of.values())
+    assert sum(1 for e in events if e.finished) == len(ps)
+    for i, rid in rid_of.items():
+        if i in cancelled:
+            assert final[rid].status in (CANCELLED, FINISHED)
+        else:
+            assert final[rid].status == FINISHED and toks[rid] == alone[i]
+    assert not ex.live and ex.cache.free_pages == ex.cache.num_pages
+    ex.cache.check()
