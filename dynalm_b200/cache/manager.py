@@ -23,14 +23,14 @@ holder lets go of it.
 
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
 import numpy as np
 import torch
 
 from ..engine.context import CacheView
-from ..errors import InvalidArgument, ResourceExhausted
+from ..errors import InvalidArgument, ResourceExhausted, Unsupported
 from ..parts.base import CacheSpec
 from .pool import PagePool
 
@@ -48,6 +48,11 @@ class _Table:
     pages: np.ndarray            # int32 [max_blocks], -1 = no page
     first: int = 0               # blocks below `first` were given back (window)
     length: int = 0              # blocks [first, length) hold pages
+    dirty: List[int] = field(default_factory=list)     # blocks whose page has changed since the device copy was last brought up to date
+
+    def set(self, block: int, page: int) -> None:
+        self.pages[block] = page
+        self.dirty.append(block)
 
 
 class PageGroup:
@@ -145,6 +150,7 @@ class CacheManager:
         self._free_slots: List[int] = list(range(self.max_requests - 1, -1, -1))
         self.slots: Dict[Hashable, int] = {}
         self.tokens: Dict[Hashable, int] = {}     # tokens reserved so far per request
+        self._dirty: set = set()                  # (group id, request) whose table has changed since take_table_updates
 
     # ---- requests -----------------------------------------------------------------------------
     def has_request(self, req) -> bool:
@@ -184,8 +190,9 @@ class CacheManager:
         if total > self.context:
             raise InvalidArgument(f"request {req!r} would hold {total} tokens, the context is {self.context}")
         start = self.tokens[req] if write_from is None else min(int(write_from), self.tokens[req])
-        taken = []
+        taken = []       # (group, table, block, page)
         copies = []      # (group, table, block, shared page, private page)
+        moves = []       # (table, first block that gets a page): blocks a window has already passed are never allocated
         try:
             for g in self.groups:
                 t = g.tables[req]
@@ -195,27 +202,30 @@ class CacheManager:
                 t = g.tables[req]
                 want_len = -(-total // self.page_size)
                 lo = max(t.length, g.first_needed_block(start))
-                if lo > t.length:            # blocks a window has already passed are never allocated
-                    if t.length == t.first:
-                        t.first = lo
-                    t.length = lo
+                if lo > t.length:
+                    moves.append((t, lo))
                 for b in range(lo, want_len):
-                    page = g.pool.allocate()
-                    taken.append((g, t, b, page))
-                    t.pages[b] = page
-                t.length = max(t.length, want_len)
+                    taken.append((g, t, b, g.pool.allocate()))
         except ResourceExhausted:
+            # nothing has been written into a table yet: give the pages back and leave
             for g, t, b, page in reversed(taken):
                 g.pool.release(page)
-                t.pages[b] = -1
-                t.length = min(t.length, b)
             for g, t, b, shared, private in copies:
                 g.pool.release(private)
             raise
+        for t, lo in moves:
+            if t.length == t.first:
+                t.first = lo
+            t.length = lo
+        for g, t, b, page in taken:
+            t.set(b, page)
+            t.length = max(t.length, b + 1)
+            self._dirty.add((g.gid, req))
         for g, t, b, shared, private in copies:
             g.copy_page(shared, private)
-            t.pages[b] = private
+            t.set(b, private)
             g.pool.release(shared)
+            self._dirty.add((g.gid, req))
         self.tokens[req] = max(self.tokens[req], total)
 
     def fork(self, parent, child, tokens: Optional[int] = None) -> int:
@@ -233,20 +243,27 @@ class CacheManager:
             for b in range(src.first, src.length):
                 if src.pages[b] >= 0:
                     g.pool.retain(int(src.pages[b]))
+                    dst.dirty.append(b)
+            self._dirty.add((g.gid, child))
         self.tokens[child] = self.tokens[parent]
         for arr in self.state_arrays.values():
             arr[slot].copy_(arr[self.slots[parent]])
         if tokens is not None and tokens < self.tokens[child]:
-            self.truncate(child, tokens)
+            self.truncate(child, tokens, computed_beyond=False)      # the state rows copied above stand at `tokens`
         return slot
 
-    def truncate(self, req, total: int) -> int:
+    def truncate(self, req, total: int, computed_beyond: bool = True) -> int:
         """`req` keeps its first `total` tokens only: pages wholly past them are given back
-        (`KvBlockTable::truncate`, dynalm/src/kv_cache/kv_cache.cpp:137-144). Returns the pages let go."""
+        (`KvBlockTable::truncate`, dynalm/src/kv_cache/kv_cache.cpp:137-144). Returns the pages let go.
+        `computed_beyond` False says that nothing past `total` has been computed yet (pages were only reserved), so
+        that per-request state has nothing to take back."""
         if req not in self.slots:
             raise InvalidArgument(f"request {req!r} is not live")
         if total < 0 or total > self.tokens[req]:
             raise InvalidArgument(f"request {req!r} holds {self.tokens[req]} tokens, it cannot be cut to {total}")
+        if self.state_specs and computed_beyond and total < self.tokens[req]:
+            # state of fixed size has no history to go back to: such a request is recomputed, not cut
+            raise Unsupported(f"request {req!r} cannot be cut back: the model keeps per-request state that cannot be rewound")
         n = 0
         keep = -(-total // self.page_size)
         for g in self.groups:
@@ -254,7 +271,8 @@ class CacheManager:
             for b in range(max(keep, t.first), t.length):
                 if t.pages[b] >= 0:
                     g.pool.release(int(t.pages[b]))
-                    t.pages[b] = -1
+                    t.set(b, -1)
+                    self._dirty.add((g.gid, req))
                     n += 1
             t.length = max(min(t.length, keep), min(t.first, keep))
             t.first = min(t.first, t.length)
@@ -273,7 +291,8 @@ class CacheManager:
             for b in range(t.first, keep_from):
                 if t.pages[b] >= 0:
                     g.pool.release(int(t.pages[b]))
-                    t.pages[b] = -1
+                    t.set(b, -1)
+                    self._dirty.add((g.gid, req))
                     n += 1
             t.first = max(t.first, keep_from)
         return n
@@ -288,6 +307,7 @@ class CacheManager:
             for b in range(t.first, t.length):
                 if t.pages[b] >= 0:
                     g.pool.release(int(t.pages[b]))
+            self._dirty.discard((g.gid, req))
         self.tokens.pop(req)
         self._free_slots.append(slot)
 
@@ -297,6 +317,24 @@ class CacheManager:
 
     def table_row(self, group: PageGroup, req) -> np.ndarray:
         return group.tables[req].pages
+
+    def take_table_updates(self) -> List[tuple]:
+        """What has changed in the block tables since the last call, as (group id, slot, block, page): the device
+        keeps a copy of every live request's table in the row of its slot, and a step brings it up to date with
+        these alone, so a step's cost on the host and on the bus follows what changed, not how long the requests
+        are. A page of -1 marks a block that was given back."""
+        out = []
+        for gid, req in sorted(self._dirty, key=lambda k: (k[0], self.slots[k[1]])):
+            t = self.groups[gid].tables[req]
+            slot = self.slots[req]
+            seen = set()
+            for b in reversed(t.dirty):            # the last change of a block wins
+                if b not in seen:
+                    seen.add(b)
+                    out.append((gid, slot, b, int(t.pages[b])))
+            t.dirty.clear()
+        self._dirty.clear()
+        return out
 
     def view(self, entry: int, block_tables: Dict[int, torch.Tensor]) -> Optional[CacheView]:
         g = self.entry_group.get(entry)

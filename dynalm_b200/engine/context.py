@@ -13,8 +13,9 @@ class CacheView:
     """One run-order entry's share of the cache for the current step.
 
     kind "pages": `arrays` are [pages, page_size, *entry_shape] tensors (keys and values for
-    attention) and `block_table` is int32 [requests, max_blocks]: page of position p of the step's
-    request r = block_table[r, p // page_size] (-1 where a windowed group has given the page back).
+    attention) and `block_table` is int32 [request slots, max_blocks]: page of position p of the request in
+    slot s = block_table[s, p // page_size] (-1 where a windowed group has given the page back, and where the
+    request has no page yet). The table lives on the device; a step sends only what changed.
     kind "state": `arrays[0]` is [slots, *state_shape]; the step's request r owns row
     `ctx.state_slots[r]`.
     """
@@ -30,7 +31,8 @@ class StepContext:
     """One step: a batch of (request, its next tokens), flattened.
 
     Row i of the step is token `token_ids[i]` at position `positions[i]` of the step's request
-    `row_request[i]`; request r's rows are q_start[r] .. q_start[r+1]-1, consecutive positions from
+    `row_request[i]`, whose slot (the row of the block tables and of state arrays that it owns for as long as it
+    lives) is `row_slot[i]`; request r's rows are q_start[r] .. q_start[r+1]-1, consecutive positions from
     pos_start[r]; after the step it holds kv_len[r] = pos_start[r] + rows tokens. All tensors are
     int32 on the device; the `h_` lists are the same values on the host for parts that plan launches.
     """
@@ -40,27 +42,20 @@ class StepContext:
     token_ids: torch.Tensor
     positions: torch.Tensor
     row_request: torch.Tensor
+    row_slot: torch.Tensor
     q_start: torch.Tensor
     pos_start: torch.Tensor
     kv_len: torch.Tensor
     state_slots: torch.Tensor
     logit_rows: torch.Tensor
     num_logit_rows: int
-    # every request cut into tiles of at most 128 consecutive rows: int32 [num_q_tiles, 4] =
-    # (request, first row of the step, rows, first position)
-    # The tiles of prompt portions come first (those that read the most keys first), then the one-row tiles of
-    # the requests at the head of the step that bring a single token each (`leading_decode_rows` of them, rows
-    # 0 .. leading_decode_rows - 1): a mixer may hand those rows to its decode kernel and only the first
-    # `num_prompt_q_tiles` tiles to its prompt kernel.
-    q_tiles: Optional[torch.Tensor] = None
-    num_q_tiles: int = 0
-    num_prompt_q_tiles: int = 0
-    leading_decode_rows: int = 0
     h_q_len: List[int] = field(default_factory=list)
     h_pos_start: List[int] = field(default_factory=list)
     h_state_slots: List[int] = field(default_factory=list)
-    block_tables: Dict[int, torch.Tensor] = field(default_factory=dict)   # cache group -> [requests, max_blocks]
+    block_tables: Dict[int, torch.Tensor] = field(default_factory=dict)   # cache group -> [request slots, max_blocks]
     decode_only: bool = False        # every request brings exactly one token
     max_q_len: int = 0
     max_kv_len: int = 0
-    extras: Dict[str, object] = field(default_factory=dict)   # per-step scratch parts may share (launch plans)
+    # per-step scratch that parts share. A part's step plan (see StepShape in engine/step.py) is found under its name
+    # as (the plan's integers on the device, what its `fill` returned); parts may add entries of their own.
+    extras: Dict[str, object] = field(default_factory=dict)

@@ -43,13 +43,17 @@ REPLAYED_LAYERS = 0          # layers issued from a list so far
 
 
 def owned_tensors(obj, depth: int = 0) -> List[torch.Tensor]:
-    """The tensors a block and its parts hold, in the order of their attributes (the same for two objects built
-    by the same code)."""
+    """The tensors a block and its parts hold, in an order that is the same for two objects built by the same code.
+    A part may say so itself (`replay_tensors() -> list`); else its attributes are walked in order: tensors, and
+    objects that are parts in their own right (they say `replay_safe` of themselves, wherever their class lives)."""
+    own = getattr(obj, "replay_tensors", None)
+    if own is not None:
+        return list(own())
     found: List[torch.Tensor] = []
     for name, value in vars(obj).items():
         if isinstance(value, torch.Tensor):
             found.append(value)
-        elif depth < 3 and hasattr(value, "__dict__") and type(value).__module__.startswith("dynalm_b200.parts"):
+        elif depth < 3 and hasattr(value, "__dict__") and hasattr(value, "replay_safe"):
             found.extend(owned_tensors(value, depth + 1))
     return found
 

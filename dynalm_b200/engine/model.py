@@ -47,16 +47,27 @@ class Decoder:
     def graph_safe(self) -> bool:
         """True when every mixer and feed-forward says its launches depend only on what
         `graph_key` covers, so that a decode step can be captured once and replayed."""
-        return all(getattr(b.mixer, "graph_safe", False) and getattr(b.ffn, "graph_safe", False) for b in self.blocks)
+        return all(getattr(b, "graph_safe", False) for b in self.blocks)
 
     def graph_key(self, ctx) -> tuple:
         """What, beyond the numbers of rows, the parts' launch shapes depend on for this step."""
         key = ()
         for b in self.blocks:
-            f = getattr(b.mixer, "graph_key", None)
+            f = getattr(b, "graph_key", None)
             if f is not None:
                 key += tuple(f(ctx))
         return tuple(sorted(set(key)))
+
+    def step_plans(self) -> list:
+        """The step plans the layers' parts ask for, each once (by name): what a part wants computed on the host once
+        per step and sent along with the step's integers (engine/step.py)."""
+        plans, names = [], set()
+        for b in self.blocks:
+            for plan in (b.step_plans() if hasattr(b, "step_plans") else []):
+                if plan.name not in names:
+                    names.add(plan.name)
+                    plans.append(plan)
+        return plans
 
     def cache_specs(self) -> List[Optional[CacheSpec]]:
         """Per run-order entry: the cache it owns, or None when it owns none."""

@@ -35,17 +35,30 @@ class StepEntry:
     want: Sequence[int] = ()
 
 
-Q_TILE = 128    # rows of one request per query tile (see StepContext.q_tiles)
+class StepShape:
+    """What a step looks like on the host, for the parts' step plans: per entry of the batch its number of rows,
+    first row, first position and request slot."""
+
+    __slots__ = ("q_len", "q_start", "pos_start", "slots", "num_tokens")
+
+    def __init__(self, q_len, q_start, pos_start, slots, num_tokens):
+        self.q_len, self.q_start, self.pos_start, self.slots, self.num_tokens = q_len, q_start, pos_start, slots, num_tokens
 
 
 class _StepBuffers:
     """Per-step integers, packed: one pinned host array per ring slot, one device array with fixed
     addresses (kernels captured in a CUDA graph keep reading the same pointers). A step fills a host
-    slot and issues one host-to-device copy; a slot is reused only after its copy has completed."""
+    slot and issues one host-to-device copy; a slot is reused only after its copy has completed.
+
+    Beside the step's own arrays it has a section for every step plan a part asked for (`plans`: objects with
+    `name`, `ints(max_tokens, max_requests)` and `fill(host_section, shape) -> meta`), and one for the changes of
+    the block tables. The block tables themselves stay on the device: `tables` [groups, request slots, blocks per
+    request], one row per slot, brought up to date by the step that changes them."""
 
     RING = 4
 
-    def __init__(self, device, max_tokens: int, max_requests: int, group_blocks: Dict[int, int]):
+    def __init__(self, device, max_tokens: int, max_requests: int, n_groups: int, max_blocks: int, page_size: int,
+                 plans=()):
         self.max_tokens, self.max_requests = max_tokens, max_requests
         off = 0
         self.off: Dict[str, slice] = {}
@@ -55,21 +68,27 @@ class _StepBuffers:
             self.off[name] = slice(off, off + n)
             off += (n + 3) // 4 * 4       # 16-byte aligned sections
 
-        for name in ("token_ids", "positions", "row_request", "logit_rows"):
+        for name in ("token_ids", "positions", "row_request", "row_slot", "logit_rows"):
             take(name, max_tokens)
         take("q_start", max_requests + 1)
         for name in ("pos_start", "kv_len", "state_slots", "feedback_src"):
             take(name, max_requests)
-        self.max_q_tiles = max_tokens // Q_TILE + max_requests
-        take("q_tiles", 4 * self.max_q_tiles)
-        self.group_blocks = dict(group_blocks)
-        for gid, mb in group_blocks.items():
-            take(f"table{gid}", max_requests * mb)
+        self.plans = list(plans)
+        for plan in self.plans:
+            take(f"plan:{plan.name}", int(plan.ints(max_tokens, max_requests)))
+        # changed table entries of one step: new pages of the tokens it brings, pages windows gave back, a few copies
+        self.max_updates = max(1, n_groups) * (max_tokens // max(1, page_size) + 4 * max_requests) + 64
+        take("table_updates", 4 * self.max_updates)
         self.size = off
-        self.host = [torch.zeros(self.size, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+        self.device = torch.device(device)
+        on_gpu = self.device.type == "cuda"
+        self.host = [torch.zeros(self.size, dtype=torch.int32) for _ in range(self.RING)]
+        if on_gpu:
+            self.host = [h.pin_memory() for h in self.host]
         self.host_np = [h.numpy() for h in self.host]
         self.events = [None] * self.RING
-        self.dev = torch.zeros(self.size, dtype=torch.int32, device=device)
+        self.dev = torch.zeros(self.size, dtype=torch.int32, device=self.device)
+        self.tables = torch.full((max(1, n_groups), max_requests, max_blocks), -1, dtype=torch.int32, device=self.device)
         self.turn = 0
 
     def next_host(self) -> int:
@@ -79,11 +98,17 @@ class _StepBuffers:
             self.events[i].synchronize()
         return i
 
-    def upload(self, i: int) -> None:
-        self.dev.copy_(self.host[i], non_blocking=True)
-        ev = torch.cuda.Event()
-        ev.record()
-        self.events[i] = ev
+    def upload(self, i: int, section: Optional[str] = None) -> None:
+        """The whole of host slot i, or one section of it, to the device (in stream order)."""
+        if section is None:
+            self.dev.copy_(self.host[i], non_blocking=True)
+        else:
+            sec = self.off[section]
+            self.dev[sec].copy_(self.host[i][sec], non_blocking=True)
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record()
+            self.events[i] = ev
 
     def dev_view(self, name: str) -> torch.Tensor:
         return self.dev[self.off[name]]
@@ -93,17 +118,20 @@ class BatchBuilder:
     """Turns a list of entries into a StepContext: checks it, reserves pages, flattens it into the
     packed buffers and uploads them. It also keeps, per live request, how many tokens are in the cache."""
 
-    def __init__(self, cache: CacheManager, runtime: Runtime, max_requests: int, vocab: int):
+    def __init__(self, cache: CacheManager, runtime: Runtime, max_requests: int, vocab: int, plans=()):
         self.cache = cache
         self.rt = runtime
         self.max_tokens = runtime.max_tokens
         self.max_requests = int(max_requests)
         self.vocab = int(vocab)
-        self.buffers = _StepBuffers(runtime.device, self.max_tokens, self.max_requests,
-                                    {g.gid: g.max_blocks for g in cache.groups})
+        names = set()
+        plans = [p for p in plans if not (p.name in names or names.add(p.name))]
+        self.buffers = _StepBuffers(runtime.device, self.max_tokens, self.max_requests, len(cache.groups),
+                                    cache.max_blocks, cache.page_size, plans)
         self.computed: Dict[Hashable, int] = {}       # tokens each live request has in the cache
         self._dev = {name: self.buffers.dev_view(name) for name in self.buffers.off}
-        self.tables = {g.gid: self._dev[f"table{g.gid}"].view(self.max_requests, g.max_blocks) for g in cache.groups}
+        self.tables = {g.gid: self.buffers.tables[g.gid] for g in cache.groups}      # [request slots, blocks]
+        self.update_launches = 0
 
     def begin(self, request) -> None:
         self.cache.add_request(request)
@@ -120,6 +148,48 @@ class BatchBuilder:
             raise InvalidArgument(f"request {parent!r} is not live")
         self.cache.fork(parent, child, tokens=self.computed[parent])
         self.computed[child] = self.computed[parent]
+
+    def _reserve_all(self, entries: Sequence[StepEntry]) -> None:
+        """Pages for every entry's tokens, or nothing: when one entry cannot get its pages, the requests this call
+        began are ended again and the others give back what this call reserved for them."""
+        begun, grown = [], []
+        try:
+            for e in entries:
+                if e.request not in self.computed:
+                    self.begin(e.request)
+                    begun.append(e.request)
+                else:
+                    grown.append((e.request, self.cache.tokens[e.request]))
+                self.cache.reserve(e.request, self.computed[e.request] + len(e.tokens), write_from=self.computed[e.request])
+        except Exception:
+            for req in begun:
+                self.end(req)
+            for req, before in grown:
+                if self.cache.tokens[req] > before:
+                    self.cache.truncate(req, before, computed_beyond=False)
+            raise
+
+    def _table_updates(self, h, slot: int) -> int:
+        """Write what has changed in the block tables into the step's section (and send whatever does not fit in
+        rounds of its own first). Returns the number of entries that travel with the step."""
+        ups = self.cache.take_table_updates()
+        b = self.buffers
+        sec = b.off["table_updates"]
+        while len(ups) > b.max_updates:
+            head, ups = ups[:b.max_updates], ups[b.max_updates:]
+            h[sec][:4 * len(head)] = np.asarray(head, dtype=np.int32).reshape(-1)
+            b.upload(slot, "table_updates")
+            self._apply(len(head))
+            if b.events[slot] is not None:
+                b.events[slot].synchronize()       # the section is written again right away
+        if ups:
+            h[sec][:4 * len(ups)] = np.asarray(ups, dtype=np.int32).reshape(-1)
+        return len(ups)
+
+    def _apply(self, n: int) -> None:
+        from ..kernels import ops
+        ops.table_updates(self.buffers.tables, self._dev["table_updates"], n)
+        self.update_launches += 1
 
     def build(self, entries: Sequence[StepEntry], reserve: bool = True,
               feedback_src: Optional[Sequence[int]] = None) -> StepContext:
@@ -145,15 +215,14 @@ class BatchBuilder:
                     raise InvalidArgument(f"request {e.request!r} wants place {w} of {len(e.tokens)} tokens")
             if min(e.tokens) < 0 or max(e.tokens) >= self.vocab:
                 raise InvalidArgument(f"request {e.request!r} has a token id outside [0, {self.vocab})")
-        for e in entries:
-            if e.request not in self.computed:
-                if not reserve:
+        if reserve:
+            self._reserve_all(entries)
+        else:
+            for e in entries:
+                if e.request not in self.computed:
                     raise InvalidArgument(f"request {e.request!r} is not live")
-                self.begin(e.request)
-            if reserve:
-                self.cache.reserve(e.request, self.computed[e.request] + len(e.tokens), write_from=self.computed[e.request])
-            elif self.cache.tokens[e.request] < self.computed[e.request] + len(e.tokens):
-                raise InvalidArgument(f"request {e.request!r} has no pages reserved for its tokens")
+                if self.cache.tokens[e.request] < self.computed[e.request] + len(e.tokens):
+                    raise InvalidArgument(f"request {e.request!r} has no pages reserved for its tokens")
 
         b = self.buffers
         i = b.next_host()
@@ -162,63 +231,56 @@ class BatchBuilder:
         tok = h[off["token_ids"]]
         pos = h[off["positions"]]
         rreq = h[off["row_request"]]
+        rslot = h[off["row_slot"]]
         lrows = h[off["logit_rows"]]
         q_start = h[off["q_start"]]
         pos_start = h[off["pos_start"]]
         kv_len = h[off["kv_len"]]
         slots = h[off["state_slots"]]
-        tiles = []
         r0 = 0
         n_logit = 0
-        h_q_len, h_pos_start, h_slots = [], [], []
+        h_q_len, h_q_start, h_pos_start, h_slots = [], [], [], []
         for r, e in enumerate(entries):
             n = len(e.tokens)
             start = self.computed[e.request]
+            slot = self.cache.slot_of(e.request)
             tok[r0:r0 + n] = e.tokens
             pos[r0:r0 + n] = np.arange(start, start + n, dtype=np.int32)
             rreq[r0:r0 + n] = r
+            rslot[r0:r0 + n] = slot
             for w in e.want:
                 lrows[n_logit] = r0 + w
                 n_logit += 1
             q_start[r] = r0
             pos_start[r] = start
             kv_len[r] = start + n
-            slot = self.cache.slot_of(e.request)
             slots[r] = slot
             h_q_len.append(n)
+            h_q_start.append(r0)
             h_pos_start.append(start)
             h_slots.append(slot)
-            for t0 in range(0, n, Q_TILE):
-                tiles.append((r, r0 + t0, min(Q_TILE, n - t0), start + t0))
-            for g in self.cache.groups:
-                mb = g.max_blocks
-                sec = off[f"table{g.gid}"]
-                h[sec.start + r * mb: sec.start + (r + 1) * mb] = self.cache.table_row(g, e.request)
             r0 += n
         q_start[len(entries)] = r0
-        # single-token requests at the head of the step (the scheduler puts decode rows first)
-        lead = 0
-        while lead < len(entries) and len(entries[lead].tokens) == 1:
-            lead += 1
-        # prompt tiles first, those that read the most keys first (the attention grid then ends evenly); then the
-        # one-row tiles of the leading decode rows
-        tiles.sort(key=lambda t: (t[0] < lead, -(t[3] + t[2])))
-        n_tiles = len(tiles)
-        h[off["q_tiles"]][:4 * n_tiles] = np.asarray(tiles, dtype=np.int32).reshape(-1)
+        shape = StepShape(h_q_len, h_q_start, h_pos_start, h_slots, total)
+        extras = {}
+        for plan in b.plans:
+            extras[plan.name] = (self._dev[f"plan:{plan.name}"], plan.fill(h[off[f"plan:{plan.name}"]], shape))
         if feedback_src is not None:
             if total != len(entries) or len(feedback_src) != len(entries):
                 raise InvalidArgument("token feedback needs one token per entry and one source per entry")
             h[off["feedback_src"]][:len(entries)] = feedback_src
+        n_updates = self._table_updates(h, i)
         b.upload(i)
+        if n_updates:
+            self._apply(n_updates)
         d = self._dev
         return StepContext(
             num_tokens=total, num_requests=len(entries), token_ids=d["token_ids"], positions=d["positions"],
-            row_request=d["row_request"], q_start=d["q_start"], pos_start=d["pos_start"], kv_len=d["kv_len"],
-            state_slots=d["state_slots"], logit_rows=d["logit_rows"], num_logit_rows=n_logit,
-            q_tiles=d["q_tiles"], num_q_tiles=n_tiles, num_prompt_q_tiles=n_tiles - lead, leading_decode_rows=lead,
+            row_request=d["row_request"], row_slot=d["row_slot"], q_start=d["q_start"], pos_start=d["pos_start"],
+            kv_len=d["kv_len"], state_slots=d["state_slots"], logit_rows=d["logit_rows"], num_logit_rows=n_logit,
             h_q_len=h_q_len, h_pos_start=h_pos_start, h_state_slots=h_slots, block_tables=self.tables,
             decode_only=all(n == 1 for n in h_q_len), max_q_len=max(h_q_len),
-            max_kv_len=max(s + n for s, n in zip(h_pos_start, h_q_len)))
+            max_kv_len=max(s + n for s, n in zip(h_pos_start, h_q_len)), extras=extras)
 
     def finish(self, entries: Sequence[StepEntry]) -> None:
         """The step has been issued: count its tokens and let windows give pages back."""
@@ -239,7 +301,7 @@ class StepFunction:
         self.max_tokens = runtime.max_tokens
         self.max_requests = int(max_requests)
         self.vocab = model.vocab
-        self.batcher = BatchBuilder(cache, runtime, max_requests, model.vocab)
+        self.batcher = BatchBuilder(cache, runtime, max_requests, model.vocab, model.step_plans())
         self.buffers = self.batcher.buffers
         self.computed = self.batcher.computed
         self._logits: Optional[torch.Tensor] = None

@@ -16,20 +16,64 @@ import torch
 
 from . import ops
 
-SM_COUNT = 148            # B200
+from .device import sm_count
+
 MAX_SPLITS = 32
 CLUSTER_SPLITS = 8          # up to here the tensor-core kernel merges splits inside a thread-block cluster
 LONG_SPLIT_KEYS = 1024      # keys per split from which more than CLUSTER_SPLITS splits pay
 DECODE_FILL = int(os.environ.get('DYNALM_DECODE_FILL', '1'))   # blocks per SM the split count aims for
 
 
-def decode_splits(rows: int, n_heads: int, n_kv_heads: int, max_kv_len: int, tensor_cores: bool = True) -> int:
+Q_TILE = 128      # query rows of one request per tile: the row block of the tcgen05 prompt kernel
+
+
+class QueryTilePlan:
+    """The step plan of the prompt attention kernels: every request of the step cut into tiles of at most Q_TILE
+    consecutive rows, int32 [tiles, 4] = (request slot, first row of the step, rows, first position). The tiles of
+    prompt portions come first, those that read the most keys first (the attention grid then ends evenly); then the
+    one-row tiles of the requests at the head of the step that bring a single token each: a mixer hands those rows
+    to its decode kernel and only the first `prompt_tiles` tiles to its prompt kernel. What `fill` returns:
+    (tiles, prompt_tiles, leading single-token requests)."""
+
+    name = "attention_query_tiles"
+
+    def ints(self, max_tokens: int, max_requests: int) -> int:
+        return 4 * (max_tokens // Q_TILE + max_requests)
+
+    def fill(self, host, shape):
+        lead = 0
+        while lead < len(shape.q_len) and shape.q_len[lead] == 1:
+            lead += 1
+        tiles = []
+        for r, (n, r0, start, slot) in enumerate(zip(shape.q_len, shape.q_start, shape.pos_start, shape.slots)):
+            for t0 in range(0, n, Q_TILE):
+                tiles.append((r >= lead, -(start + t0 + min(Q_TILE, n - t0)), slot, r0 + t0, min(Q_TILE, n - t0), start + t0))
+        tiles.sort(key=lambda t: (not t[0], t[1]))
+        flat = [v for t in tiles for v in t[2:]]
+        host[:len(flat)] = flat
+        return len(tiles), len(tiles) - lead, lead
+
+
+QUERY_TILES = QueryTilePlan()
+
+
+def query_tiles(ctx):
+    """(tiles on the device, number of tiles, of prompt tiles, of leading single-token requests) of this step, or
+    None when the step was built without the plan."""
+    got = ctx.extras.get(QueryTilePlan.name)
+    if got is None:
+        return None
+    return (got[0],) + tuple(got[1])
+
+
+def decode_splits(rows: int, n_heads: int, n_kv_heads: int, max_kv_len: int, tensor_cores: bool = True,
+                  sms: int = 0) -> int:
     """Key splits per row so that the grid fills the GPU, each split at least 128 keys (one 32-key tile for each
     of a block's four warps). The tensor-core kernel merges up to 8 splits inside a thread-block cluster, which
     wins while a split is short; from 1,024 keys per split on, more splits (merged by a second kernel) win."""
     group = n_heads // n_kv_heads
     blocks = rows * n_kv_heads * (-(-group // (16 if tensor_cores else 4)))
-    want = -(-DECODE_FILL * SM_COUNT // max(blocks, 1))
+    want = -(-DECODE_FILL * (sms or sm_count()) // max(blocks, 1))
     splits = max(1, min(want, max(1, max_kv_len // 128), MAX_SPLITS))
     if tensor_cores and splits > CLUSTER_SPLITS and max_kv_len < CLUSTER_SPLITS * LONG_SPLIT_KEYS:
         splits = CLUSTER_SPLITS
@@ -43,7 +87,7 @@ def decode_uses_tensor_cores(spec) -> bool:
 def decode_plan(ctx, spec, rows: int = 0) -> int:
     """The number of key splits for the step's decode rows (all rows unless `rows` says how many); also part
     of the CUDA-graph key."""
-    span = ctx.max_kv_len if spec.window <= 0 else min(ctx.max_kv_len, spec.window)
+    span = ctx.max_kv_len if spec.get("window", 0) <= 0 else min(ctx.max_kv_len, spec.get("window", 0))
     # bucket the span so that a growing context changes the launch shape only now and then
     bucket = 256
     while bucket < span:
@@ -64,7 +108,7 @@ def use_decode_kernel(ctx, spec, dtype: torch.dtype, page_size: int) -> bool:
 
 
 def use_prefill_kernel(ctx, spec, qkv: torch.Tensor, page_size: int) -> bool:
-    return (qkv.dtype == torch.bfloat16 and ctx.q_tiles is not None and page_size & (page_size - 1) == 0
+    return (qkv.dtype == torch.bfloat16 and query_tiles(ctx) is not None and page_size & (page_size - 1) == 0
             and spec.head_dim % 16 == 0 and spec.head_dim <= 128 and qkv.stride(0) % 8 == 0)
 
 
@@ -85,9 +129,9 @@ def _decode_rows(qkv: torch.Tensor, cache, ctx, out: torch.Tensor, spec, runtime
         most_rows = max(runtime.max_requests, rows)
         scratch = runtime.flat(f"attn_split_scratch_{spec.num_heads}x{spec.head_dim}",
                                ops.decode_scratch_floats(most_rows, spec.num_heads, spec.head_dim, MAX_SPLITS))
-    ops.paged_attention_decode(qkv[:rows], k_cache, v_cache, cache.block_table, ctx.positions[:rows], ctx.row_request[:rows],
+    ops.paged_attention_decode(qkv[:rows], k_cache, v_cache, cache.block_table, ctx.positions[:rows], ctx.row_slot[:rows],
                                out[:rows], scratch, spec.num_heads, spec.num_kv_heads, spec.head_dim, cache.page_size,
-                               float(spec.scale), spec.window, n_split,
+                               float(spec.scale), spec.get("window", 0), n_split,
                                tensor_cores=decode_uses_tensor_cores(spec) and qkv.stride(0) % 8 == 0)
 
 
@@ -99,26 +143,26 @@ def paged_attention(qkv: torch.Tensor, cache, ctx, out: torch.Tensor, spec, runt
         return True
     if not use_prefill_kernel(ctx, spec, qkv, cache.page_size):
         return False
-    n_tiles = ctx.num_q_tiles
+    q_tiles, n_tiles, n_prompt_tiles, leading = query_tiles(ctx)
     side = None
-    if ctx.leading_decode_rows >= MIXED_DECODE_ROWS and decode_kernel_takes(spec, qkv.dtype, cache.page_size):
+    if leading >= MIXED_DECODE_ROWS and decode_kernel_takes(spec, qkv.dtype, cache.page_size):
         # a mixed step: the decode rows at its head go through the split-KV kernel (as a one-row query tile each
         # of them would occupy a whole block of the prompt kernel), the prompt portions through the flash kernel.
         # The two kernels read and write different rows and each fills a part of the GPU only: they run side by side,
         # the decode rows on a second stream.
-        n_tiles = ctx.num_prompt_q_tiles
+        n_tiles = n_prompt_tiles
         if SIDE_BY_SIDE and n_tiles > 0:
             side = runtime.side_stream
             ops.stream_fork(side)
             with ops.on_stream(side):
-                _decode_rows(qkv, cache, ctx, out, spec, runtime, ctx.leading_decode_rows)
+                _decode_rows(qkv, cache, ctx, out, spec, runtime, leading)
         else:
-            _decode_rows(qkv, cache, ctx, out, spec, runtime, ctx.leading_decode_rows)
+            _decode_rows(qkv, cache, ctx, out, spec, runtime, leading)
     if n_tiles > 0:
         kernel = (ops.paged_attention_prefill_tcgen05 if use_prefill_tcgen05(spec, qkv, out, cache.page_size)
                   else ops.paged_attention_prefill)
-        kernel(qkv, k_cache, v_cache, cache.block_table, ctx.q_tiles, n_tiles, out, spec.num_heads,
-               spec.num_kv_heads, spec.head_dim, cache.page_size, float(spec.scale), spec.window)
+        kernel(qkv, k_cache, v_cache, cache.block_table, q_tiles, n_tiles, out, spec.num_heads,
+               spec.num_kv_heads, spec.head_dim, cache.page_size, float(spec.scale), spec.get("window", 0))
     if side is not None:
         ops.stream_join(side)
     return True

@@ -21,8 +21,8 @@ import os
 import torch
 
 from . import ops
+from .device import sm_count
 
-SM_COUNT = 148
 _mm_out_dtype_ok: Optional[bool] = None
 LIBRARY_CALLS = 0    # matrix products handed to the library so far
 
@@ -70,7 +70,7 @@ def stream_split_count(n_features: int, k: int) -> int:
     """K splits of the streaming kernel so that its blocks (one per 128 features and split) about fill the GPU, every
     split with at least four 64-wide slices of K."""
     tiles = -(-n_features // 128)
-    want = max(1, (SM_COUNT + tiles // 2) // tiles)
+    want = max(1, (sm_count() + tiles // 2) // tiles)
     return max(1, min(want, STREAM_MAX_SPLITS, k // 256))
 
 
@@ -78,7 +78,7 @@ def split_count(n_features: int, k: int, rows: int) -> int:
     """How many blocks split K for a small N, so that the grid covers the GPU about twice and every
     warp of a block still gets at least one 64-wide piece of K."""
     tiles = -(-n_features // (16 if rows <= 16 else 32))
-    want = -(-2 * SM_COUNT // tiles)
+    want = -(-2 * sm_count() // tiles)
     return max(1, min(want, 8, k // 512))
 
 

@@ -58,6 +58,7 @@ _SIGNATURES = {
         "dl_feedback_tokens": [_P, _P, _P, _I, _P],
     },
     "streams": {"dl_stream_fork": [_P, _P], "dl_stream_join": [_P, _P]},
+    "table_update": {"dl_table_updates": [_P, _P, _I, _I, _I, _I, _P]},
 }
 
 _funcs = {}
@@ -561,7 +562,7 @@ _tcgen05_status = {}
 _pairs: Optional[bool] = None      # whether the variant with pairs of blocks sharing W tiles can be used
 
 
-PAIRS_MIN_TILES = 4 * 148     # 128 x 256 tiles from which sharing W tiles between two blocks pays (measured on B200)
+PAIRS_MIN_WAVES = 4     # rounds of 128 x 256 tiles over the SMs from which sharing W tiles between two blocks pays (measured on B200)
 
 
 def tcgen05_pairs(rows: int, features: int) -> bool:
@@ -573,7 +574,8 @@ def tcgen05_pairs(rows: int, features: int) -> bool:
     if _pairs is None:
         _pairs = os.environ.get("DYNALM_GEMM_PAIRS", "1") != "0" and \
             os.path.isfile(os.path.join(_lib.CSRC, "gemm_tcgen05_cluster.cu"))
-    return _pairs and -(-rows // 128) * -(-features // 256) >= PAIRS_MIN_TILES
+    from .device import sm_count
+    return _pairs and -(-rows // 128) * -(-features // 256) >= PAIRS_MIN_WAVES * sm_count()
 
 
 def _status_word(device: torch.device) -> torch.Tensor:
@@ -800,6 +802,18 @@ def clear_status(device) -> None:
     t = _tcgen05_status.get(torch.device(device))
     if t is not None:
         t.zero_()
+
+
+def table_updates(tables: torch.Tensor, updates: torch.Tensor, n: int) -> None:
+    """tables[g, s, b] = p for the first n quadruples (g, s, b, p) of `updates` (csrc/table_update.cu): the
+    device's block tables [groups, slots, max_blocks], int32, brought up to date with what a step changed."""
+    _cuda(tables, updates)
+    if tables.dtype != torch.int32 or updates.dtype != torch.int32 or tables.dim() != 3 or not tables.is_contiguous() \
+            or updates.numel() < 4 * n or updates.data_ptr() % 16:
+        raise InvalidArgument("table_updates: int32 tables [groups, slots, blocks] and int32 updates [n, 4], 16-byte aligned")
+    check_limits("table_update", requests=tables.shape[1])
+    _check(_fn("table_update", "dl_table_updates")(_p(tables), _p(updates), n, tables.shape[0], tables.shape[1],
+                                                    tables.shape[2], _stream()), "table_updates")
 
 
 def feedback_tokens(token_ids: torch.Tensor, chosen: torch.Tensor, src: torch.Tensor, n: int) -> None:

@@ -83,19 +83,19 @@ class LlamaArchitecture:
                 if has(p + name):
                     mixer_tensors[local] = p + name
             layers.append(BlockSpec(
-                kind="pre_norm",
+                "pre_norm",
                 mixer_norm=NormSpec("rms", cfg.hidden_size, cfg.rms_norm_eps,
                                     {"weight": p + "input_layernorm.weight"}),
                 mixer=MixerSpec(
-                    kind="attention", width=cfg.hidden_size, num_heads=cfg.num_attention_heads,
+                    "attention", cfg.hidden_size, mixer_tensors, num_heads=cfg.num_attention_heads,
                     num_kv_heads=cfg.num_key_value_heads, head_dim=cfg.head_dim,
-                    scale=cfg.attention_scale, window=0, position=position, tensors=mixer_tensors),
+                    scale=cfg.attention_scale, window=0, position=position),
                 ffn_norm=NormSpec("rms", cfg.hidden_size, cfg.rms_norm_eps,
                                   {"weight": p + "post_attention_layernorm.weight"}),
                 ffn=FeedForwardSpec(
-                    kind="gated_mlp", width=cfg.hidden_size, inner=cfg.intermediate_size, activation="silu",
-                    tensors={"gate": p + "mlp.gate_proj.weight", "up": p + "mlp.up_proj.weight",
-                             "down": p + "mlp.down_proj.weight"}),
+                    "gated_mlp", cfg.hidden_size,
+                    {"gate": p + "mlp.gate_proj.weight", "up": p + "mlp.up_proj.weight",
+                     "down": p + "mlp.down_proj.weight"}, inner=cfg.intermediate_size, activation="silu"),
                 residual_scale=cfg.residual_multiplier,
             ))
         # Tied unless the file carries lm_head.weight (arch_llama.cpp:32); without a file

@@ -56,12 +56,18 @@ class PagedAttention:
             self.b_qkv = None
         self.w_o = tensors["o"]
         self.b_o = tensors.get("o_bias")
-        pos = spec.position
+        pos = spec.get("position")
         self.position = POSITIONS.get(pos.kind)(pos, runtime) if pos is not None else None
+
+    def step_plans(self) -> list:
+        """What this mixer wants worked out once per step on the host and sent with the step's integers: the query
+        tiles of its prompt kernels (kernels/attention.py)."""
+        from ..kernels.attention import QUERY_TILES
+        return [QUERY_TILES]
 
     def cache_spec(self) -> Optional[CacheSpec]:
         return CacheSpec(kind="pages", entry_shape=(self.spec.num_kv_heads, self.spec.head_dim), tensors=2,
-                         window=self.spec.window)
+                         window=self.spec.get("window", 0))
 
     def forward(self, x: torch.Tensor, ctx, cache, owns_cache: bool = True) -> torch.Tensor:
         """x: [rows, width] normed input in the compute dtype -> [rows, width]."""
@@ -74,7 +80,7 @@ class PagedAttention:
             qkv = rt.buffer("attn_qkv", (rows, self.q_width + 2 * self.kv_width))
             step_angles = getattr(self.position, "step_angles", None)
             angles = step_angles(ctx, rt) if rows > ops.SKINNY_FAST_ROWS and step_angles is not None else None
-            ops.gemm_qkv_rope(x, self.w_qkv, qkv, ctx.positions, ctx.row_request, cache.block_table, k_cache, v_cache,
+            ops.gemm_qkv_rope(x, self.w_qkv, qkv, ctx.positions, ctx.row_slot, cache.block_table, k_cache, v_cache,
                               table[0], table[2], s.num_heads, s.num_kv_heads, s.head_dim, cache.page_size, angles)
             return self._attend_and_project(qkv, cache, ctx, rows)
         if owns_cache:
@@ -90,7 +96,7 @@ class PagedAttention:
                 if owns_cache else None
             self.position.apply(q, k, ctx.positions[:rows])
         inv_freq, rot, pos_scale = table if table is not None else (None, 0, 1.0)
-        ops.rope_cache_write(qkv, ctx.positions, ctx.row_request, cache.block_table, k_cache, v_cache, inv_freq, rot,
+        ops.rope_cache_write(qkv, ctx.positions, ctx.row_slot, cache.block_table, k_cache, v_cache, inv_freq, rot,
                              pos_scale, s.num_heads, s.num_kv_heads, s.head_dim, cache.page_size, write_cache=owns_cache)
         return self._attend_and_project(qkv, cache, ctx, rows)
 
@@ -126,5 +132,5 @@ class PagedAttention:
         from ..kernels import attention as fast
         if fast.paged_attention(qkv, cache, ctx, out, s, self.rt):
             return
-        ops.paged_attention_generic(qkv, k_cache, v_cache, cache.block_table, ctx.positions, ctx.row_request, out,
-                                    s.num_heads, s.num_kv_heads, s.head_dim, cache.page_size, float(s.scale), s.window)
+        ops.paged_attention_generic(qkv, k_cache, v_cache, cache.block_table, ctx.positions, ctx.row_slot, out,
+                                    s.num_heads, s.num_kv_heads, s.head_dim, cache.page_size, float(s.scale), s.get("window", 0))

@@ -92,6 +92,8 @@ NORMS = _Registry("norm")
 POSITIONS = _Registry("position encoding")
 BLOCKS = _Registry("block arrangement")
 
+REGISTRIES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS, "position": POSITIONS}
+
 register_mixer = MIXERS.register
 register_feed_forward = FEED_FORWARDS.register
 register_norm = NORMS.register
@@ -99,8 +101,23 @@ register_position = POSITIONS.register
 register_block = BLOCKS.register
 
 
-def declared_tensors(registry: _Registry, spec) -> Dict[str, TensorDecl]:
-    """File name -> declaration for one spec, using the names the plan gave it."""
+def registry_of(spec) -> _Registry:
+    """The registry that builds a spec, by the spec's own `registry` word."""
+    try:
+        return REGISTRIES[spec.registry]
+    except KeyError:
+        raise Unsupported(f"a spec of kind '{spec.kind}' names no registry of parts ('{spec.registry}')") from None
+
+
+def build_part(spec, store: Dict[str, Any], runtime):
+    """The part of a spec: its class from the registry, the tensors it declared from the store."""
+    registry = registry_of(spec)
+    return registry.get(spec.kind)(spec, pick_tensors(spec, store, registry), runtime)
+
+
+def declared_tensors(registry: Optional[_Registry], spec) -> Dict[str, TensorDecl]:
+    """File name -> declaration for one spec, using the names the plan gave it (`registry` None: the spec's own)."""
+    registry = registry or registry_of(spec)
     cls = registry.get(spec.kind)
     out: Dict[str, TensorDecl] = {}
     names = getattr(spec, "tensors", {}) or {}

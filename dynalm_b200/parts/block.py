@@ -13,7 +13,7 @@ from typing import Optional
 import torch
 
 from ..kernels import ops
-from .base import FEED_FORWARDS, MIXERS, NORMS, pick_tensors, register_block
+from .base import build_part, register_block
 
 
 @dataclass
@@ -31,24 +31,51 @@ class ResidualStream:
         return self.x
 
 
-@register_block("pre_norm")
-class PreNormBlock:
+class Block:
+    """What every arrangement shares: it builds the parts its spec lists (each from the registry its spec names,
+    kept as attributes under the spec's names), and answers for them where the engine asks a layer as a whole:
+    which cache it keeps, whether its launches may be captured in a CUDA graph or re-issued by address."""
+
+    cache_part = "mixer"        # the name of the part whose cache_spec() is the layer's
+
     def __init__(self, spec, store, runtime):
         self.spec = spec
         self.rt = runtime
-        self.mixer_norm = NORMS.get(spec.mixer_norm.kind)(spec.mixer_norm, pick_tensors(spec.mixer_norm, store, NORMS), runtime)
-        self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, pick_tensors(spec.mixer, store, MIXERS), runtime)
-        self.ffn_norm = NORMS.get(spec.ffn_norm.kind)(spec.ffn_norm, pick_tensors(spec.ffn_norm, store, NORMS), runtime)
-        self.ffn = FEED_FORWARDS.get(spec.ffn.kind)(spec.ffn, pick_tensors(spec.ffn, store, FEED_FORWARDS), runtime)
-        self.scale = float(spec.residual_scale)
-        # whether a later layer of the same kind may re-issue this block's launches by address (engine/launch_memo.py):
-        # only if every part says so of itself
-        parts = [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn, getattr(self.mixer, "position", None)]
-        self.replay_safe = all(getattr(p, "replay_safe", False) for p in parts if p is not None)
+        self.part_names = list(spec.parts)
+        for name, part_spec in spec.parts.items():
+            setattr(self, name, build_part(part_spec, store, runtime))
+        parts = self.parts()
+        # only if every part says so of itself (a position encoding that a mixer holds included)
+        inner = [getattr(p, "position", None) for p in parts]
+        self.replay_safe = all(getattr(p, "replay_safe", False) for p in parts + [p for p in inner if p is not None])
+        self.graph_safe = all(getattr(p, "graph_safe", False) for p in parts)
+
+    def parts(self):
+        return [getattr(self, n) for n in self.part_names]
 
     def cache_spec(self):
-        return self.mixer.cache_spec()
+        part = getattr(self, self.cache_part, None)
+        return part.cache_spec() if part is not None and hasattr(part, "cache_spec") else None
 
+    def step_plans(self) -> list:
+        return [plan for p in self.parts() for plan in (p.step_plans() if hasattr(p, "step_plans") else [])]
+
+    def graph_key(self, ctx) -> tuple:
+        key = ()
+        for p in self.parts():
+            f = getattr(p, "graph_key", None)
+            if f is not None:
+                key += tuple(f(ctx))
+        return key
+
+
+@register_block("pre_norm")
+class PreNormBlock(Block):
+    """parts: mixer_norm, mixer, ffn_norm, ffn; parameter: residual_scale (default 1)."""
+
+    def __init__(self, spec, store, runtime):
+        super().__init__(spec, store, runtime)
+        self.scale = float(spec.get("residual_scale", 1.0))
 
     def forward(self, stream: ResidualStream, ctx, cache, owns_cache: bool) -> ResidualStream:
         rows, width = stream.x.shape

@@ -26,8 +26,8 @@ class GatedMLP:
         }
 
     def __init__(self, spec, tensors: Dict[str, torch.Tensor], runtime):
-        if spec.activation != "silu":
-            raise Unsupported(f"gated_mlp: activation '{spec.activation}' has no kernel (silu does)")
+        if spec.get("activation", "silu") != "silu":
+            raise Unsupported(f"gated_mlp: activation '{spec.get('activation')}' has no kernel (silu does)")
         self.spec = spec
         self.rt = runtime
         self.w_gate_up = torch.cat([tensors["gate"], tensors["up"]], dim=0).contiguous()

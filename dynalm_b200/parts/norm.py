@@ -13,6 +13,7 @@ from .base import TensorDecl, register_norm
 @register_norm("rms")
 class RMSNorm:
     replay_safe = True     # all device work goes through the recorded launches of kernels/ops.py (engine/launch_memo.py)
+    graph_safe = True      # launches depend on row counts only
 
     @staticmethod
     def declare(spec) -> Dict[str, TensorDecl]:

@@ -17,7 +17,7 @@ import torch
 from ..config.plan import ModelPlan
 from ..config.reader import read_json_file
 from ..errors import Corrupt, EngineError, NotFound
-from ..parts.base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, TensorDecl, declared_tensors
+from ..parts.base import BLOCKS, NORMS, TensorDecl, declared_tensors
 from ..registry import Architecture, find_architecture
 from .safetensors import SafeTensorsFile
 
@@ -56,10 +56,8 @@ def expected_tensors(plan: ModelPlan) -> Dict[str, TensorDecl]:
     out.update(declared_tensors(NORMS, plan.final_norm))
     for block in plan.layers:
         BLOCKS.get(block.kind)  # fails early on an unknown arrangement
-        out.update(declared_tensors(NORMS, block.mixer_norm))
-        out.update(declared_tensors(MIXERS, block.mixer))
-        out.update(declared_tensors(NORMS, block.ffn_norm))
-        out.update(declared_tensors(FEED_FORWARDS, block.ffn))
+        for _, part in block:
+            out.update(declared_tensors(None, part))
     return out
 
 

@@ -298,3 +298,75 @@ def test_random_orders_with_forks(seed):
         m.free_request(r)
     m.check()
     assert all(g.pool.num_free == g.pool.num_pages for g in m.groups) and m.free_slots == 6
+
+
+def test_table_updates_follow_what_changed_not_how_long_requests_are():
+    """The device keeps every live request's block table; a step sends only the entries that changed. A request
+    with 131,000 tokens that grows by one token costs at most one entry, and nothing at all inside a page."""
+    from dynalm_b200.engine.step import _StepBuffers
+    spec = CacheSpec("pages", (2, 16))
+    window = CacheSpec("pages", (2, 16), window=64)
+    m = CacheManager([spec, window], 16, 140000 + 4096, 4, 131072, None, torch.float32)
+    m.add_request("long")
+    total_updates = 0
+    for total in range(1000, 131001, 1000):                  # the prompt comes in portions of 1,000 tokens
+        m.reserve("long", total)
+        m.advance("long", total)
+        ups = m.take_table_updates()
+        # all keys: the portion's new blocks; window: the same, and what fell behind the window is given back
+        assert len([u for u in ups if u[0] == 0]) <= 64 and len([u for u in ups if u[0] == 1]) <= 64 + 64 + 8
+        total_updates += len(ups)
+    assert m.take_table_updates() == []
+    assert m.groups[1].pool.num_held <= 6                    # the window keeps 64 keys
+    sizes = []
+    for total in range(131001, 131001 + 40):
+        m.reserve("long", total)
+        m.advance("long", total)
+        ups = m.take_table_updates()
+        sizes.append(len(ups))
+        slot = m.slot_of("long")
+        for gid, s, block, page in ups:
+            assert s == slot and (page == -1 or page == int(m.groups[gid].tables["long"].pages[block]))
+    assert max(sizes) <= 3 and sum(1 for n in sizes if n == 0) >= 30        # a new page every 16 tokens, per group
+    # a second request's entries carry its own slot; freeing forgets what was pending
+    m.add_request("b")
+    m.reserve("b", 40)
+    ups = m.take_table_updates()
+    assert {u[1] for u in ups} == {m.slot_of("b")} and len(ups) == 3 + 3
+    m.reserve("b", 100)
+    m.free_request("b")
+    assert m.take_table_updates() == []
+    m.check()
+    # the step's packed integers do not grow with the context: a few KB for 64 tokens and 4 requests
+    small = _StepBuffers("cpu", 64, 4, n_groups=2, max_blocks=131072 // 16, page_size=16, plans=())
+    assert small.size * 4 < 16 * 1024
+    assert small.tables.shape == (2, 4, 8192)
+
+
+def test_reserve_that_fails_leaves_windowed_tables_as_they_were():
+    spec = CacheSpec("pages", (1, 8), window=32)
+    m = CacheManager([spec], 16, 64, 2, 1024, None, torch.float32)
+    m.add_request("a")
+    m.reserve("a", 20)
+    m.advance("a", 20)
+    t = m.groups[0].tables["a"]
+    before = (t.first, t.length, t.pages.copy())
+    m.add_request("b")
+    m.reserve("b", 32)                    # the pool is now full (4 pages)
+    with pytest.raises(ResourceExhausted):
+        m.reserve("a", 700, write_from=600)      # would skip blocks the window has passed, then run out of pages
+    assert (t.first, t.length) == before[:2] and (t.pages == before[2]).all()
+    m.check()
+
+
+def test_requests_with_state_cannot_be_cut_back():
+    from dynalm_b200.errors import Unsupported
+    m = CacheManager([CacheSpec("pages", (1, 8)), CacheSpec("state", state_shape=(4,))], 16, 256, 2, 256, None, torch.float32)
+    m.add_request("a")
+    m.reserve("a", 40)
+    with pytest.raises(Unsupported, match="cannot be rewound"):
+        m.truncate("a", 20)
+    m.truncate("a", 40)
+    m.fork("a", "b", tokens=33)            # reserved but not computed: nothing to rewind
+    assert m.tokens["b"] == 33
+    m.check()

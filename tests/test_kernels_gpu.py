@@ -473,7 +473,7 @@ def test_gemm_skinny(ops, M, N, K):
 def tile_sharing(request, ops, monkeypatch):
     """Runs a test with the tcgen05 product in which every block loads its own operands, and with the one in which
     two blocks share each tile of W (forced for every size, also those for which the dispatcher would not use it)."""
-    monkeypatch.setattr(ops, "PAIRS_MIN_TILES", 1 if request.param == "pairs" else 1 << 40)
+    monkeypatch.setattr(ops, "PAIRS_MIN_WAVES", 0 if request.param == "pairs" else 1 << 30)
     return request.param
 
 

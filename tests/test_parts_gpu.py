@@ -82,7 +82,7 @@ def test_attention_mixer_alone(dtype):
          "v": torch.randn(kw, H, generator=g) * 0.1, "o": torch.randn(H, qw, generator=g) * 0.1}
     mixer = MIXERS.get("attention")(spec, {n: v.to(DEV, dtype) for n, v in t.items()}, rt)
     cache = CacheManager([mixer.cache_spec()], 16, 256, 8, 256, DEV, dtype)
-    builder = BatchBuilder(cache, rt, 8, 1000)
+    builder = BatchBuilder(cache, rt, 8, 1000, mixer.step_plans())
     lens = {"a": 50, "b": 21}
     xs = {r: torch.randn(n, H, generator=g) for r, n in lens.items()}
     w = {"p.self_attn." + n + "_proj.weight": v.to(dtype).double().numpy() for n, v in t.items()}
@@ -115,7 +115,7 @@ def test_feed_forward_alone(dtype):
     W, F = 80, 112
     t = {"gate": torch.randn(F, W, generator=g) * 0.2, "up": torch.randn(F, W, generator=g) * 0.2,
          "down": torch.randn(W, F, generator=g) * 0.2}
-    part = FEED_FORWARDS.get("gated_mlp")(FeedForwardSpec("gated_mlp", W, F), {n: v.to(DEV, dtype) for n, v in t.items()}, rt)
+    part = FEED_FORWARDS.get("gated_mlp")(FeedForwardSpec("gated_mlp", W, inner=F), {n: v.to(DEV, dtype) for n, v in t.items()}, rt)
     x = torch.randn(9, W, generator=g)
     y = part.forward(x.to(DEV, dtype), None).float().cpu().numpy()
     d = {n: v.to(dtype).double().numpy() for n, v in t.items()}
@@ -177,17 +177,19 @@ def _register_toy():
                 return NormSpec("rms", W, 1e-5, {"weight": n})
 
             def ffn(p):
-                return FeedForwardSpec("gated_mlp", W, c["inner"], "silu",
-                                       {"gate": p + "gate", "up": p + "up", "down": p + "down"})
-            attn = MixerSpec("attention", W, c["heads"], c["kv_heads"], c["head_dim"], c["head_dim"] ** -0.5, 0,
-                             PositionSpec("rotary", c["head_dim"], c["head_dim"], 10000.0),
-                             {"q": "l0.q", "k": "l0.k", "v": "l0.v", "o": "l0.o"})
-            win = MixerSpec("attention", W, c["heads"], c["kv_heads"], c["head_dim"], c["head_dim"] ** -0.5, c["window"],
-                            PositionSpec("none"), {"q": "l2.q", "k": "l2.k", "v": "l2.v", "o": "l2.o"})
-            toy = MixerSpec("toy_decay", W, tensors={"w": "l1.w"})
-            layers = [BlockSpec("pre_norm", norm("l0.n1"), attn, norm("l0.n2"), ffn("l0.")),
-                      BlockSpec("pre_norm", norm("l1.n1"), toy, norm("l1.n2"), ffn("l1.")),
-                      BlockSpec("pre_norm", norm("l2.n1"), win, norm("l2.n2"), ffn("l2."))]
+                return FeedForwardSpec("gated_mlp", W, {"gate": p + "gate", "up": p + "up", "down": p + "down"},
+                                       inner=c["inner"], activation="silu")
+            heads = dict(num_heads=c["heads"], num_kv_heads=c["kv_heads"], head_dim=c["head_dim"], scale=c["head_dim"] ** -0.5)
+            attn = MixerSpec("attention", W, {"q": "l0.q", "k": "l0.k", "v": "l0.v", "o": "l0.o"}, window=0,
+                             position=PositionSpec("rotary", c["head_dim"], c["head_dim"], 10000.0), **heads)
+            win = MixerSpec("attention", W, {"q": "l2.q", "k": "l2.k", "v": "l2.v", "o": "l2.o"}, window=c["window"],
+                            position=PositionSpec("none"), **heads)
+            toy = MixerSpec("toy_decay", W, {"w": "l1.w"})
+
+            def block(n, mixer):
+                return BlockSpec("pre_norm", mixer_norm=norm(f"l{n}.n1"), mixer=mixer, ffn_norm=norm(f"l{n}.n2"),
+                                 ffn=ffn(f"l{n}."))
+            layers = [block(0, attn), block(1, toy), block(2, win)]
             # layer 1 is named twice; the last entry runs layer 0 again on the first entry's cache
             order = [LayerRun(0), LayerRun(1), LayerRun(2), LayerRun(1), LayerRun(0, cache_of=0)]
             return ModelPlan(EmbeddingSpec(V, W, 1.0, {"weight": "emb"}), layers, order, norm("final"),
@@ -290,6 +292,131 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
 
 
 # ---------------------------------------------------------------------------------------------
+# another arrangement of a layer, with a part of a kind of its own and parameters of its own, all defined here
+# ---------------------------------------------------------------------------------------------
+
+def test_toy_block_with_post_norms_and_a_third_part(tmp_path):
+    """A block that nothing in the package knows: no norm before its parts but one after each (x = norm(x + part(x))),
+    three parts instead of two (a mixer with a parameter of its own kind, `taps`; attention; a feed-forward), and a
+    parameter of the arrangement (`skip`). It registers, loads, builds and steps without a change to the package, whole
+    and cut, and matches the same arithmetic written out with NumPy."""
+    from dynalm_b200.config import (BlockSpec, EmbeddingSpec, FeedForwardSpec, HeadSpec, LayerRun, MixerSpec, ModelPlan,
+                                    NormSpec, PositionSpec)
+    from dynalm_b200.engine import StepEntry, build
+    from dynalm_b200.parts import TensorDecl, register_block, register_mixer
+    from dynalm_b200.parts.base import build_part
+    from dynalm_b200.registry import register_architecture
+    from dynalm_b200.weights import write_model_folder
+    W, V, HD = 32, 60, 16
+
+    @register_mixer("toy_shift")
+    class ShiftMix:
+        """y[t] = x[t] W0 + x[t-1] W1 (+ x[t-2] W2 with taps = 3): the last taps-1 rows of a request are its state."""
+
+        @staticmethod
+        def declare(spec):
+            return {f"w{i}": TensorDecl((spec.width, spec.width)) for i in range(spec.taps)}
+
+        def __init__(self, spec, tensors, runtime):
+            self.spec, self.w = spec, [tensors[f"w{i}"].float() for i in range(spec.taps)]
+
+        def cache_spec(self):
+            from dynalm_b200.parts import CacheSpec
+            return CacheSpec(kind="state", state_shape=(self.spec.taps - 1, self.spec.width), dtype="float32")
+
+        def forward(self, x, ctx, cache, owns_cache=True):
+            state = cache.arrays[0]
+            out = torch.empty_like(x, dtype=torch.float32)
+            r0 = 0
+            for n, slot in zip(ctx.h_q_len, ctx.h_state_slots):
+                rows = torch.cat([state[slot], x[r0:r0 + n].float()])          # [taps - 1 + n, W], oldest first
+                k = self.spec.taps - 1
+                out[r0:r0 + n] = sum(rows[k - i:k - i + n] @ self.w[i].t() for i in range(self.spec.taps))
+                state[slot] = rows[-k:]
+                r0 += n
+            return out.to(x.dtype)
+
+    @register_block("toy_post_norm")
+    class PostNormBlock:
+        cache_part = "attn"
+
+        def __init__(self, spec, store, runtime):
+            self.spec, self.rt = spec, runtime
+            self.parts_ = {name: build_part(s, store, runtime) for name, s in spec.parts.items()}
+            self.skip = float(spec.skip)
+
+        def cache_spec(self):
+            return self.parts_[self.spec.cache_part_name].cache_spec()
+
+        def forward(self, stream, ctx, cache, owns_cache):
+            x = stream.flush()
+            p = self.parts_
+            for part, norm in (("first", "norm_a"), ("ffn", "norm_b")):
+                h = x.to(self.rt.dtype)
+                y = p[part].forward(h, ctx, cache, owns_cache) if part == "first" else p[part].forward(h, ctx)
+                y = y.float().sum(0) if y.dim() == 3 else y.float()
+                out = torch.empty_like(h)
+                p[norm].forward(x, out, delta=(self.skip * x + y).to(self.rt.dtype) - h, delta_scale=1.0)
+                x.copy_(out.float())            # what the norm gave becomes the stream
+            return stream
+
+    class Arch:
+        name = "Toy3ForCausalLM"
+        model_types = ("toy3",)
+
+        def read_config(self, obj):
+            return dict(obj)
+
+        def plan(self, c, present=None):
+            def norm(n):
+                return NormSpec("rms", W, 1e-5, {"weight": n})
+
+            def ffn(p):
+                return FeedForwardSpec("gated_mlp", W, {"gate": p + "g", "up": p + "u", "down": p + "d"}, inner=48)
+            shift = MixerSpec("toy_shift", W, {"w0": "s.w0", "w1": "s.w1", "w2": "s.w2"}, taps=3)
+            attn = MixerSpec("attention", W, {"q": "a.q", "k": "a.k", "v": "a.v", "o": "a.o"}, num_heads=2, num_kv_heads=2,
+                             head_dim=HD, scale=HD ** -0.5, position=PositionSpec("rotary", HD, HD, 10000.0))
+            layers = [BlockSpec("toy_post_norm", first=shift, norm_a=norm("l0.na"), ffn=ffn("l0."), norm_b=norm("l0.nb"),
+                                skip=0.5, cache_part_name="first"),
+                      BlockSpec("toy_post_norm", first=attn, norm_a=norm("l1.na"), ffn=ffn("l1."), norm_b=norm("l1.nb"),
+                                skip=1.0, cache_part_name="first")]
+            return ModelPlan(EmbeddingSpec(V, W, 1.0, {"weight": "emb"}), layers, [LayerRun(0), LayerRun(1)], norm("final"),
+                             HeadSpec(V, W, True), 128)
+
+    register_architecture(Arch())
+    folder = str(tmp_path / "toy3")
+    write_model_folder(folder, {"architectures": ["Toy3ForCausalLM"], "model_type": "toy3"}, 11, torch.float32)
+    w = plain.read_safetensors(os.path.join(folder, "model.safetensors"))
+    toks = [int(t) for t in np.random.RandomState(5).randint(0, V, 45)]
+
+    def reference():
+        cfg = {"num_attention_heads": 2, "num_key_value_heads": 2, "head_dim": HD, "rope_theta": 10000.0,
+               "partial_rotary_factor": 1.0, "attention_multiplier": 0.0}
+        x = plain.embed(w["emb"], toks)
+        n = len(toks)
+        pad = np.concatenate([np.zeros((2, W)), x])
+        y = sum(pad[2 - i:2 - i + n] @ w[f"s.w{i}"].T for i in range(3))
+        x = plain.rms_norm(0.5 * x + y, w["l0.na"], 1e-5)
+        x = plain.rms_norm(0.5 * x + plain.gated_mlp(x, w["l0.g"], w["l0.u"], w["l0.d"]), w["l0.nb"], 1e-5)
+        aw = {"p.self_attn." + k + "_proj.weight": w["a." + k] for k in "qkvo"}
+        x = plain.rms_norm(x + plain.attention_block(x, aw, "p.", cfg, np.arange(n)), w["l1.na"], 1e-5)
+        x = plain.rms_norm(x + plain.gated_mlp(x, w["l1.g"], w["l1.u"], w["l1.d"]), w["l1.nb"], 1e-5)
+        return plain.rms_norm(x, w["final"], 1e-5) @ w["emb"].T
+
+    ref = reference()
+    for cuts in ([45], [16, 7, 2, 1, 1, 18]):
+        built = build(folder, dtype="float32", kv_tokens=128, max_batch_tokens=64, max_requests=2)
+        assert set(built.cache.state_arrays) == {0} and len(built.cache.groups) == 1
+        got, pos = [], 0
+        for n in cuts:
+            got.append(built.step_fn.step([StepEntry("r", toks[pos:pos + n], list(range(n)))]).cpu().numpy().copy())
+            pos += n
+        built.step_fn.end("r")
+        err = np.abs(np.concatenate(got) - ref).max()
+        assert err <= 3e-5 * max(1.0, np.abs(ref).max()), f"cuts {cuts}: {err}"
+
+
+# ---------------------------------------------------------------------------------------------
 # another position encoding and a feed-forward with routing, both defined here
 # ---------------------------------------------------------------------------------------------
 
@@ -365,11 +492,12 @@ def test_toy_position_encoding_and_routed_feed_forward(tmp_path):
             for l in range(2):
                 p = f"l{l}."
                 layers.append(BlockSpec(
-                    "pre_norm", norm(p + "n1"),
-                    MixerSpec("attention", W, 2, 1, HD, HD ** -0.5, 0, PositionSpec("toy_adjacent", HD, HD, 100.0),
-                              {"q": p + "q", "k": p + "k", "v": p + "v", "o": p + "o"}),
-                    norm(p + "n2"),
-                    FeedForwardSpec("toy_routed", W, tensors={"router": p + "r", "e0": p + "e0", "e1": p + "e1"})))
+                    "pre_norm", mixer_norm=norm(p + "n1"),
+                    mixer=MixerSpec("attention", W, {"q": p + "q", "k": p + "k", "v": p + "v", "o": p + "o"}, num_heads=2,
+                                    num_kv_heads=1, head_dim=HD, scale=HD ** -0.5,
+                                    position=PositionSpec("toy_adjacent", HD, HD, 100.0)),
+                    ffn_norm=norm(p + "n2"),
+                    ffn=FeedForwardSpec("toy_routed", W, {"router": p + "r", "e0": p + "e0", "e1": p + "e1"})))
             return ModelPlan(EmbeddingSpec(V, W, 1.0, {"weight": "emb"}), layers, [LayerRun(0), LayerRun(1)], norm("final"),
                              HeadSpec(V, W, True), 128)
 
