@@ -337,7 +337,8 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
                            const int* __restrict__ positions, const int* __restrict__ row_request,
                            bf16* __restrict__ out, int out_stride, float* __restrict__ part, int n_heads,
                            int n_kv_heads, int page_shift, float scale_log2, int window, int n_split,
-                           int cluster_merge, int xbuf_offset) {
+                           int cluster_merge, int xbuf_offset, const void* __restrict__ ahead, long long ahead_bytes) {
+  l2_prefetch_share(ahead, ahead_bytes);     // what the kernel after this one will stream (see common.cuh)
   constexpr int LD = HD + 8;
   constexpr int CH = HD / 8;
   constexpr int KS = HD / 16;
@@ -615,7 +616,7 @@ template <int HD, int STAGES, int KT>
 int launch_decode_tc(const void* q, int q_stride, const void* kc, const void* vc, const int* block_table, int max_blocks,
                      const int* positions, const int* row_request, void* out, int out_stride, float* part, int rows,
                      int n_heads, int n_kv_heads, int page_shift, float scale, int window, int n_split,
-                     cudaStream_t stream) {
+                     const void* ahead, long long ahead_bytes, cudaStream_t stream) {
   constexpr size_t pipe = static_cast<size_t>(16 + DT_WARPS * STAGES * 2 * KT) * (HD + 8) * sizeof(bf16);
   constexpr size_t mrg = static_cast<size_t>(DT_WARPS) * 16 * (HD + 2) * sizeof(float);
   constexpr size_t base = ((pipe > mrg ? pipe : mrg) + 15) & ~static_cast<size_t>(15);
@@ -659,7 +660,7 @@ int launch_decode_tc(const void* q, int q_stride, const void* kc, const void* vc
       &cfg, decode_attention_tc_kernel<HD, STAGES, KT>, static_cast<const bf16*>(q), q_stride, static_cast<const bf16*>(kc),
       static_cast<const bf16*>(vc), block_table, max_blocks, positions, row_request, static_cast<bf16*>(out), out_stride,
       part, n_heads, n_kv_heads, page_shift, scale * 1.4426950408889634f, window, n_split, cluster ? 1 : 0,
-      static_cast<int>(base)));
+      static_cast<int>(base), pdl_mode() >= 1 ? ahead : nullptr, pdl_mode() >= 1 ? ahead_bytes : 0ll));
   if (rc != 0 || n_split == 1 || cluster) return rc;
   dim3 cgrid(n_heads, rows);
   const int cthreads = HD <= 32 ? 32 : (HD <= 64 ? 64 : 128);
@@ -697,11 +698,14 @@ DL_EXPORT int dl_paged_attention_decode(int dtype, const void* q, int q_stride, 
 // The tensor-core variant: bfloat16, head_dim a multiple of 16 up to 128, q rows 16-byte aligned. Same
 // arguments as dl_paged_attention_decode. Up to 8 splits are the blocks of a thread-block cluster and merge through
 // distributed shared memory (no scratch is touched); more splits use the scratch and the merge kernel.
+// ahead, ahead_bytes: memory that the kernel after this one will stream (weights), requested into L2 before this
+// kernel waits for the one in front of it; null / 0: nothing.
 DL_EXPORT int dl_paged_attention_decode_tc(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                            const int* block_table, int max_blocks, const int* positions,
                                            const int* row_request, void* out, int out_stride, float* part, int rows,
                                            int n_heads, int n_kv_heads, int head_dim, int page_size, float scale,
-                                           int window, int n_split, cudaStream_t stream) {
+                                           int window, int n_split, const void* ahead, long long ahead_bytes,
+                                           cudaStream_t stream) {
   if (rows <= 0) return 0;
   int page_shift = 0;
   while ((1 << page_shift) < page_size) ++page_shift;
@@ -712,7 +716,7 @@ DL_EXPORT int dl_paged_attention_decode_tc(const void* q, int q_stride, const vo
   case H:                                                                                                             \
     return dl::launch_decode_tc<H, S, T>(q, q_stride, k_cache, v_cache, block_table, max_blocks, positions, row_request, \
                                       out, out_stride, part, rows, n_heads, n_kv_heads, page_shift, scale, window,    \
-                                      n_split, stream)
+                                      n_split, ahead, ahead_bytes, stream)
   switch (head_dim) {
     DL_CASE(16, 4, 32);
     DL_CASE(32, 4, 32);
@@ -779,7 +783,7 @@ DL_EXPORT int dl_paged_attention_decode_noalloc(const void* q, int q_stride, con
   }
   return dl_paged_attention_decode_tc(q, q_stride, k_cache, v_cache, block_table, max_blocks, positions, row_request,
                                       out, out_stride, part, rows, n_heads, n_kv_heads, head_dim, page_size, scale,
-                                      window, n_split, stream);
+                                      window, n_split, nullptr, 0, stream);
 }
 
 DL_EXPORT const char* dl_noalloc_strerror(int code) {

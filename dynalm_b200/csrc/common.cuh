@@ -130,6 +130,23 @@ inline int launch_status() { return static_cast<int>(cudaGetLastError()); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Asks for this block's share of [p, p + bytes) to be brought into L2: pieces of 16 KB dealt to the grid's blocks in
+// turn, each requested by one thread with one bulk prefetch. Nothing waits for it. A kernel that was launched early
+// (programmatic dependent launch) calls it before its wait with the weights that the kernel after it will stream:
+// they cross the memory bus while the kernels in front are still running, and are read from L2 when their turn comes.
+__device__ __forceinline__ void l2_prefetch_share(const void* p, long long bytes) {
+  if (p == nullptr || bytes <= 0 || threadIdx.x != 0 || threadIdx.y != 0 || threadIdx.z != 0) return;
+  constexpr long long PIECE = 16384;
+  const long long blocks = static_cast<long long>(gridDim.x) * gridDim.y * gridDim.z;
+  const long long me = (static_cast<long long>(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+  const char* base = static_cast<const char*>(p);
+  for (long long off = me * PIECE; off < bytes; off += blocks * PIECE) {
+    const long long left = bytes - off;
+    const unsigned n = static_cast<unsigned>(left < PIECE ? (left & ~15ll) : PIECE);
+    if (n > 0) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + off), "r"(n) : "memory");
+  }
+}
+
 // DYNALM_PDL: 2 or unset = only the weight-streaming kernels (`launch_streaming`), which request their first
 // weights before they wait; 1 = every kernel launched through `launch` too; 0 = none. Measured on B200, decode
 // step at batch 8 inside the CUDA graph: 0.99 ms with 0, 1.00 ms with 1, 0.95 ms with 2.

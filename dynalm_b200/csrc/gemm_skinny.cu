@@ -46,7 +46,7 @@ enum { SK_OUT_BF16 = 0, SK_OUT_F32 = 1, SK_OUT_SWIGLU = 2 };
 template <int MT, int NT>
 __device__ __forceinline__ void skinny_accumulate(const bf16* __restrict__ x, int ldx, const bf16* const (&wrow)[MT][2],
                                                   const bool (&wok)[MT][2], int M, int K, int blk_begin, int blk_end,
-                                                  float* red) {
+                                                  float* red, const void* ahead = nullptr, long long ahead_bytes = 0) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const bf16* xrow[NT];
@@ -92,6 +92,7 @@ __device__ __forceinline__ void skinny_accumulate(const bf16* __restrict__ x, in
   uint4 a[MT][2][2], bq[NT][2];
   int blk = blk_begin + warp;
   if (blk < blk_end) load_w(blk, a);
+  l2_prefetch_share(ahead, ahead_bytes);     // what the kernel after this one will stream (see common.cuh)
   pdl_wait();
   pdl_trigger();
   if (X_AHEAD && blk < blk_end) load_x(blk, bq);
@@ -147,7 +148,8 @@ __device__ __forceinline__ void skinny_accumulate(const bf16* __restrict__ x, in
 template <int MT, int NT>
 __global__ void __launch_bounds__(SK_THREADS, (MT == 1 && NT <= 2) ? (NT == 1 ? SK_BLOCKS_8 : SK_BLOCKS_16) : 1)
 gemm_skinny_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w, void* __restrict__ y, int ldy,
-                   int M, int N, int K, int mode, float out_scale, long long split_stride) {
+                   int M, int N, int K, int mode, float out_scale, long long split_stride,
+                   const void* __restrict__ ahead, long long ahead_bytes) {
   extern __shared__ float red[];     // [SK_WARPS][MT * 16][NT * 8]
   const int lane = threadIdx.x & 31;
   const int g = lane >> 2;
@@ -178,7 +180,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
   const int nblk = (K + SK_KB - 1) / SK_KB;
   const int per = (nblk + n_split - 1) / n_split;
   const int blk_begin = split * per, blk_end = min(nblk, blk_begin + per);
-  skinny_accumulate<MT, NT>(x, ldx, wrow, wok, M, K, blk_begin, blk_end, red);
+  skinny_accumulate<MT, NT>(x, ldx, wrow, wok, M, K, blk_begin, blk_end, red, ahead, ahead_bytes);
 
   constexpr int FT = MT * 16, BT = NT * 8;
   if (mode == SK_OUT_SWIGLU) {
@@ -284,7 +286,8 @@ gemm_skinny_qkv_rope_kernel(const bf16* __restrict__ x, int ldx, const bf16* __r
 
 template <int MT, int NT>
 int launch_skinny(const void* x, int ldx, const void* w, void* y, int ldy, int M, int N, int K, int mode,
-                  float out_scale, int n_split, long long split_stride, cudaStream_t stream) {
+                  float out_scale, int n_split, long long split_stride, const void* ahead, long long ahead_bytes,
+                  cudaStream_t stream) {
   const int feats = mode == SK_OUT_SWIGLU ? N / 2 : N;
   const int per_block = mode == SK_OUT_SWIGLU ? MT * 8 : MT * 16;
   dim3 grid((feats + per_block - 1) / per_block, n_split);
@@ -297,7 +300,8 @@ int launch_skinny(const void* x, int ldx, const void* w, void* y, int ldy, int M
     configured = true;
   }
   return launch_streaming(gemm_skinny_kernel<MT, NT>, grid, dim3(SK_THREADS), smem, stream, static_cast<const bf16*>(x), ldx,
-                static_cast<const bf16*>(w), y, ldy, M, N, K, mode, out_scale, split_stride);
+                static_cast<const bf16*>(w), y, ldy, M, N, K, mode, out_scale, split_stride,
+                pdl_mode() >= 1 ? ahead : nullptr, pdl_mode() >= 1 ? ahead_bytes : 0ll);
 }
 
 }  // namespace dl
@@ -305,17 +309,19 @@ int launch_skinny(const void* x, int ldx, const void* w, void* y, int ldy, int M
 // x: bf16 [M, K] rows of ldx elements (16-byte aligned rows), w: bf16 [N, K] contiguous, K a multiple of 8,
 // M <= 64. mode 0: y bf16 [M, N]; mode 1: y fp32, n_split partial results of [M, ldy] floats each,
 // split_stride floats apart; mode 2: w = [gate; up] (N even), y bf16 [M, N / 2] = silu(x Wg^T) * (x Wu^T).
-// n_split > 1 needs mode 1.
+// n_split > 1 needs mode 1. ahead, ahead_bytes: memory that the kernel after this one will stream (weights),
+// requested into L2 before this kernel waits for the one in front of it; null / 0: nothing.
 DL_EXPORT int dl_gemm_skinny(const void* x, int ldx, const void* w, void* y, int ldy, int M, int N, int K, int mode,
-                             float out_scale, int n_split, long long split_stride, cudaStream_t stream) {
+                             float out_scale, int n_split, long long split_stride, const void* ahead,
+                             long long ahead_bytes, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 64 || K <= 0 || (K & 7) || (ldx & 7) || n_split < 1 || n_split > 64 || (n_split > 1 && mode != dl::SK_OUT_F32) ||
       (mode == dl::SK_OUT_SWIGLU && (N & 1)) || mode < 0 || mode > 2)
     return DL_ERR_UNSUPPORTED;
-  if (M <= 8) return dl::launch_skinny<1, 1>(x, ldx, w, y, ldy, M, N, K, mode, out_scale, n_split, split_stride, stream);
-  if (M <= 16) return dl::launch_skinny<1, 2>(x, ldx, w, y, ldy, M, N, K, mode, out_scale, n_split, split_stride, stream);
-  if (M <= 32) return dl::launch_skinny<2, 4>(x, ldx, w, y, ldy, M, N, K, mode, out_scale, n_split, split_stride, stream);
-  return dl::launch_skinny<2, 8>(x, ldx, w, y, ldy, M, N, K, mode, out_scale, n_split, split_stride, stream);
+  if (M <= 8) return dl::launch_skinny<1, 1>(x, ldx, w, y, ldy, M, N, K, mode, out_scale, n_split, split_stride, ahead, ahead_bytes, stream);
+  if (M <= 16) return dl::launch_skinny<1, 2>(x, ldx, w, y, ldy, M, N, K, mode, out_scale, n_split, split_stride, ahead, ahead_bytes, stream);
+  if (M <= 32) return dl::launch_skinny<2, 4>(x, ldx, w, y, ldy, M, N, K, mode, out_scale, n_split, split_stride, ahead, ahead_bytes, stream);
+  return dl::launch_skinny<2, 8>(x, ldx, w, y, ldy, M, N, K, mode, out_scale, n_split, split_stride, ahead, ahead_bytes, stream);
 }
 
 // The fused q | k | v projection (see gemm_skinny_qkv_rope_kernel): x bf16 [M, K], M <= 16; w bf16 [(n_heads +

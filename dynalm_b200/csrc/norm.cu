@@ -76,11 +76,14 @@ template <typename TO, typename TD, int NV>
 __global__ void __launch_bounds__(NORM_VEC_THREADS)
 rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, float delta_scale,
                    const float* __restrict__ w, float eps, TO* __restrict__ out, const int* __restrict__ rows,
-                   int width, int write_residual, int parts, size_t part_stride) {
+                   int width, int write_residual, int parts, size_t part_stride, int n_rows,
+                   const void* __restrict__ ahead, long long ahead_bytes) {
   __shared__ float red[33];
+  l2_prefetch_share(ahead, ahead_bytes);       // the grid may have more blocks than rows for this
   pdl_wait();
   pdl_trigger();
   const int r = blockIdx.x;
+  if (r >= n_rows) return;
   const size_t src = rows ? static_cast<size_t>(ck_row(rows[r])) : static_cast<size_t>(r);
   float* xr = x + src * width;
   const TD* dr = delta ? delta + src * width : nullptr;
@@ -164,16 +167,24 @@ __global__ void residual_add_kernel(float* __restrict__ x, const TD* __restrict_
 // sums of delta lie delta_part_stride elements apart.
 DL_EXPORT int dl_rmsnorm(int out_dtype, int delta_dtype, float* x, const void* delta, float delta_scale,
                          const float* w, float eps, void* out, const int* rows, int n_rows, int width,
-                         int write_residual, int delta_parts, long long delta_part_stride, cudaStream_t stream) {
+                         int write_residual, int delta_parts, long long delta_part_stride, const void* ahead,
+                         long long ahead_bytes, cudaStream_t stream) {
+  // ahead, ahead_bytes: memory that the kernel after this one will stream (its weights), or null: requested into L2
+  // before this kernel waits for the one in front of it (only the vector kernel does)
   if (n_rows <= 0) return 0;
   if (width % 4 == 0 && width <= 8 * 4 * dl::NORM_VEC_THREADS &&
       (delta_part_stride % 4 == 0)) {
     const int nv = (width + 4 * dl::NORM_VEC_THREADS - 1) / (4 * dl::NORM_VEC_THREADS);
     int rc = 0;
+    // with memory to request ahead the kernel starts early (it requests before its wait) and brings blocks for that
+    const bool ahead_on = ahead != nullptr && ahead_bytes > 0 && dl::pdl_mode() >= 1;
+    const bool early = ahead_on || dl::pdl_mode() == 1;
+    const int blocks = ahead_on ? (n_rows > 64 ? n_rows : 64) : n_rows;
+    if (!ahead_on) ahead_bytes = 0;
 #define DL_VEC(TO, TD, NV)                                                                                         \
-  rc = dl::launch(dl::rmsnorm_vec_kernel<TO, TD, NV>, dim3(n_rows), dim3(dl::NORM_VEC_THREADS), 0, stream, x,      \
-                  static_cast<const TD*>(delta), delta_scale, w, eps, static_cast<TO*>(out), rows, width,          \
-                  write_residual, delta_parts, static_cast<size_t>(delta_part_stride))
+  rc = dl::launch_impl(early, dl::rmsnorm_vec_kernel<TO, TD, NV>, dim3(blocks), dim3(dl::NORM_VEC_THREADS), 0, stream, x,  \
+                       static_cast<const TD*>(delta), delta_scale, w, eps, static_cast<TO*>(out), rows, width,          \
+                       write_residual, delta_parts, static_cast<size_t>(delta_part_stride), n_rows, ahead, ahead_bytes)
 #define DL_VEC_NV(TO, TD)                                   \
   do {                                                      \
     if (nv <= 1) DL_VEC(TO, TD, 1);                         \

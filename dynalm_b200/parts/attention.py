@@ -65,6 +65,10 @@ class PagedAttention:
         from ..kernels.attention import QUERY_TILES
         return [QUERY_TILES]
 
+    def first_weights(self) -> torch.Tensor:
+        """The weights this part streams first (a block may say so to the kernel in front, kernels/ops.stream_ahead)."""
+        return self.w_qkv
+
     def cache_spec(self) -> Optional[CacheSpec]:
         return CacheSpec(kind="pages", entry_shape=(self.spec.num_kv_heads, self.spec.head_dim), tensors=2,
                          window=self.spec.get("window", 0))
@@ -115,7 +119,10 @@ class PagedAttention:
     def _attend_and_project(self, qkv: torch.Tensor, cache, ctx, rows: int) -> torch.Tensor:
         s, rt = self.spec, self.rt
         attn = rt.buffer("attn_out", (rows, self.q_width))
+        if rows <= ops.SKINNY_FAST_ROWS:
+            ops.stream_ahead(self.w_o)                 # taken by the decode attention, read by the product after it
         self.attend(qkv, cache, ctx, attn)
+        ops.stream_ahead(None)
         if self.b_o is None:
             return linear_partial(attn, self.w_o, rt, "mixer_out")
         out = rt.buffer("mixer_out", (rows, s.width))

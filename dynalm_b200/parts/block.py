@@ -79,10 +79,15 @@ class PreNormBlock(Block):
 
     def forward(self, stream: ResidualStream, ctx, cache, owns_cache: bool) -> ResidualStream:
         rows, width = stream.x.shape
+        few = rows <= ops.SKINNY_FAST_ROWS         # a step bound by the stream of weights: say early what comes next
         h = self.rt.buffer("normed", (rows, width))
+        if few:
+            ops.stream_ahead(getattr(self.mixer, "first_weights", lambda: None)())
         self.mixer_norm.forward(stream.x, h, delta=stream.pending, delta_scale=stream.pending_scale)
         a = self.mixer.forward(h, ctx, cache, owns_cache)
         h = self.rt.buffer("normed", (rows, width))
+        if few:
+            ops.stream_ahead(getattr(self.ffn, "first_weights", lambda: None)())
         self.ffn_norm.forward(stream.x, h, delta=a, delta_scale=self.scale)
         f = self.ffn.forward(h, ctx)
         stream.pending, stream.pending_scale = f, self.scale

@@ -8,6 +8,7 @@ from typing import Dict
 import torch
 
 from ..errors import Unsupported
+from ..kernels import ops
 from ..kernels.gemm import linear_partial, linear_swiglu
 from .base import TensorDecl, register_feed_forward
 
@@ -33,7 +34,13 @@ class GatedMLP:
         self.w_gate_up = torch.cat([tensors["gate"], tensors["up"]], dim=0).contiguous()
         self.w_down = tensors["down"]
 
+    def first_weights(self) -> torch.Tensor:
+        """The weights this part streams first (a block may say so to the kernel in front, kernels/ops.stream_ahead)."""
+        return self.w_gate_up
+
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         s, rt = self.spec, self.rt
+        if x.shape[0] <= ops.SKINNY_FAST_ROWS:
+            ops.stream_ahead(self.w_down)              # taken by the gate | up product, read by the product after it
         act = linear_swiglu(x, self.w_gate_up, rt, s.inner)
         return linear_partial(act, self.w_down, rt, "ffn_out")

@@ -81,7 +81,7 @@ def test_no_alloc_entry_matches_the_ordinary_one():
     noalloc.argtypes = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, I, P]
     noalloc.restype = c_int
     ordinary = lib.dl_paged_attention_decode_tc
-    ordinary.argtypes = [P, I, P, P, P, I, P, P, P, I, P, I, I, I, I, I, F, I, I, P]
+    ordinary.argtypes = [P, I, P, P, P, I, P, P, P, I, P, I, I, I, I, I, F, I, I, P, ctypes.c_longlong, P]
     ordinary.restype = c_int
     strerror = lib.dl_noalloc_strerror
     strerror.argtypes = [c_int]
@@ -112,7 +112,7 @@ def test_no_alloc_entry_matches_the_ordinary_one():
         scratch = torch.zeros(rows * heads * splits * (hd + 2), dtype=torch.float32, device=DEV)
         rc = ordinary(q.data_ptr(), q.stride(0), kc.data_ptr(), vc.data_ptr(), table.data_ptr(), table.stride(0),
                       pos.data_ptr(), req.data_ptr(), want.data_ptr(), want.stride(0), scratch.data_ptr(), rows, heads,
-                      kvh, hd, page, scale, 0, splits, stream)
+                      kvh, hd, page, scale, 0, splits, None, 0, stream)
         assert rc == 0, strerror(rc)
         got = torch.zeros_like(want)
         torch.cuda.synchronize()
