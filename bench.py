@@ -4,11 +4,15 @@
 
 A step is one decode step of a batch of 8 requests that each hold 2,048 tokens of context. `value` is
 decoded tokens per second over exactly K steps, timed with CUDA events on the launching stream (the
-token ids fed are fixed, nothing is read back inside the timed region); `e2e` is the same through the
-Python entry point's scheduler: host token ids in, sampled token ids out, every step. Beside them: a
-2,048-token prefill with its fraction of the bf16 matrix peak, the decode step's fraction of the HBM
-roofline (every weight read once plus the cache of the live requests), and decode at batch 1 and 64.
-Prints one JSON line.
+token ids fed are fixed, nothing is read back inside the timed region), the median of --repeats (5) such
+measurements with the slowest and the fastest in `spread`; `e2e` is the same through the Python entry
+point's scheduler: host token ids in, sampled token ids out, every step. Beside them: a 2,048-token
+prefill with its fraction of the bf16 matrix peak, the decode step's fraction of the HBM roofline (every
+weight read once plus the cache of the live requests), and as `points` decode at batch 1 and 64, decode
+at batch 1, 8 and 64 with about 8,000 tokens of context each (as many as the 8,192-token benchmark context
+leaves room for while the measurement grows them), and a prefill of 8,192 tokens, each with its fraction
+of the roofline. `--workload serve3b | serve8b` runs the continuous-batching workloads of the 3B and 8B
+shapes instead. Prints one JSON line.
 """
 
 import argparse
@@ -46,6 +50,7 @@ FULL_LAYERS = 16
 CONTEXT = 8192          # benchmark context length: the longest a request may grow
 HELD = 2048             # tokens each sequence holds when decoding
 PREFILL_TOKENS = 2048
+LONG_PREFILL = 8192     # a further point: one prompt of the whole benchmark context
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -298,6 +303,8 @@ def main():
     ap.add_argument("--workload", choices=["decode"] + sorted(SERVING), default="decode",
                     help="decode: the default benchmark; serve3b / serve8b: continuous batching of the 3B / 8B workloads")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--no-long", action="store_true", help="skip the points at 8,192 tokens (prefill and decode)")
+    ap.add_argument("--repeats", type=int, default=5, help="the timed K steps are repeated this often; `value` is the median")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel (for profiling)")
     ap.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
                     help="profiling aid: run only the device-timed decode loop, or only the prefill")
@@ -321,12 +328,18 @@ def main():
     peaks = load_peaks()
     cfg = dict(LLAMA_1B)
     cfg["num_hidden_layers"] = args.layers
+    R = max(1, args.repeats)
     batches = [args.batch] if args.no_points else sorted({1, args.batch, 64})
+    long_batches = [] if (args.no_points or args.no_long) else sorted({1, args.batch, 64})
     max_b = max(batches)
-    held_max = HELD + W + K + 4 * args.batch + 96
+    PRIME_MAX = 8
+    span = PRIME_MAX + W + R * K + 4 * args.batch + 96          # tokens a sequence grows by while it is measured
+    held_long = CONTEXT - span - 16                             # "8,192 tokens of context": as many as fit under it
+    kv_tokens = max(max_b * (-(-(HELD + span) // 16) * 16),
+                    max(long_batches, default=0) * (-(-CONTEXT // 16) * 16)) + 2 * LONG_PREFILL + 4096
     t_build = time.time()
-    eng = Engine(config=cfg, random_seed=0, dtype="bfloat16", ctx=max_b * (-(-held_max // 16) * 16) + 4096,
-                 batch=PREFILL_TOKENS, max_running=max_b,
+    eng = Engine(config=cfg, random_seed=0, dtype="bfloat16", ctx=kv_tokens,
+                 batch=LONG_PREFILL if not args.no_long else PREFILL_TOKENS, max_running=max_b,
                  scheduler=SchedulerConfig(max_running=max_b, decode_token_budget=max_b,
                                            prefill_token_budget=PREFILL_TOKENS - max_b,
                                            max_prefill_chunk=PREFILL_TOKENS - max_b, max_batch_tokens=PREFILL_TOKENS))
@@ -348,29 +361,33 @@ def main():
         torch.cuda.synchronize()
         return a.elapsed_time(b)
 
-    # ---- prefill of one 2,048-token prompt -----------------------------------------------------------
-    prompt = [int(t) for t in rng.randint(0, vocab, PREFILL_TOKENS)]
+    # ---- prefill of one prompt of 2,048 tokens (and of 8,192) ---------------------------------------------------
+    def prefill_point(T, reps):
+        prompt = [int(t) for t in rng.randint(0, vocab, T)]
 
-    def prefill_once():
-        step_fn.step([StepEntry("p", prompt, [PREFILL_TOKENS - 1])])
-        step_fn.end("p")
-    if args.only == "decode":
-        pre_ms = float("nan")
-    else:
+        def once():
+            step_fn.step([StepEntry("p", prompt, [T - 1])])
+            step_fn.end("p")
         for _ in range(3):
-            prefill_once()
-        pre_ms = timed(prefill_once, 5) / 5
+            once()
+        ms = statistics.median(timed(once, 3) / 3 for _ in range(reps))
+        flops = prefill_flops(cfg, args.layers, T)
+        return {"value": round(T / ms * 1e3, 1), "tokens": T, "ms": round(ms, 3),
+                "frac": round(flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
+    prefill = prefill_point(PREFILL_TOKENS, R) if args.only != "decode" else None
     if args.only == "prefill":
-        print(json.dumps({"prefill_ms": pre_ms}))
+        print(json.dumps({"prefill": prefill, "prefill_long": None if args.no_long else prefill_point(LONG_PREFILL, 3)}))
         return 0
-    flops = prefill_flops(cfg, args.layers, PREFILL_TOKENS)
-    prefill = {"value": round(PREFILL_TOKENS / pre_ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
-               "frac": round(flops / (pre_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
+    prefill_long = prefill_point(LONG_PREFILL, 3) if (args.only == "all" and not args.no_long and not args.no_points) else None
 
     # ---- decode: device-timed ------------------------------------------------------------------------------
-    def fill(B):
+    def fill(B, held):
         for r in range(B):
-            step_fn.step([StepEntry(("d", r), [int(t) for t in rng.randint(0, vocab, HELD)], [])])
+            left = held
+            while left > 0:            # a long context comes in portions the engine's step takes
+                n = min(left, step_fn.max_tokens)
+                step_fn.step([StepEntry(("d", r), [int(t) for t in rng.randint(0, vocab, n)], [])])
+                left -= n
 
     def drop(B):
         for r in range(B):
@@ -379,61 +396,99 @@ def main():
     ids_out = torch.zeros(max_b, dtype=torch.int32, device="cuda:0")
     # the step function captures a decode-only launch shape as a CUDA graph when it has come GRAPH_AFTER times: that
     # many steps of setup come before the warm-up, so that warm-up and timed steps are the steady state
-    PRIME = step_fn.GRAPH_AFTER if step_fn.use_graphs else 0
-    results = {}
-    launches = 0
+    PRIME = min(PRIME_MAX, step_fn.GRAPH_AFTER) if step_fn.use_graphs else 0
+    launches = lib_calls = 0
     clocks = None
-    for B in batches:
-        fill(B)
+
+    def decode_point(B, held, main=False):
+        """R repeats of K timed decode steps of B sequences that hold `held` tokens -> (ms per step of each repeat,
+        tokens every sequence held in the middle of the measurement)."""
+        nonlocal launches, lib_calls, clocks
+        fill(B, held)
         toks = [[int(rng.randint(0, vocab))] for _ in range(B)]
 
         def decode_once():
-            logits = step_fn.step([StepEntry(("d", r), toks[r], [0]) for r in range(B)])
-            ops.argmax(logits, ids_out[:B])
+            # greedy: the head picks the most likely token in its product's epilogue where it can
+            logits = step_fn.step([StepEntry(("d", r), toks[r], [0]) for r in range(B)], choose=(ids_out[:B], None))
+            if logits is not None:
+                ops.argmax(logits, ids_out[:B])
         for _ in range(PRIME + W):       # PRIME steps of setup (the launch shape becomes a CUDA graph), then W of warm-up
             decode_once()
-        if B == args.batch:
+        reps = []
+        if main:
             l0, g0, r0 = ops.LAUNCHES, gemm.LIBRARY_CALLS, getattr(step_fn, "graph_kernel_launches", 0)
             with ClockSampler() as cs:
-                ms = timed(decode_once, K)
+                for _ in range(R):
+                    reps.append(timed(decode_once, K) / K)
             clocks = cs.result
-            launches = ops.LAUNCHES - l0 + getattr(step_fn, "graph_kernel_launches", 0) - r0
-            lib_calls = gemm.LIBRARY_CALLS - g0
+            launches = (ops.LAUNCHES - l0 + getattr(step_fn, "graph_kernel_launches", 0) - r0) // R
+            lib_calls = (gemm.LIBRARY_CALLS - g0) // R
         else:
-            ms = timed(decode_once, K)
-        results[B] = ms / K
+            steps = K if B <= 16 else min(K, 32)
+            for _ in range(min(R, 3)):
+                reps.append(timed(decode_once, steps) / steps)
+            mid = held + PRIME + W + len(reps) * steps / 2
+            drop(B)
+            return reps, mid
         drop(B)
+        return reps, held + PRIME + W + R * K / 2
 
-    ms_step = results[args.batch]
+    def frac_of_roofline(B, ms, mid):
+        bytes_step = weight_bytes(cfg, args.layers) + B * mid * kv_bytes_per_token(cfg, args.layers)
+        return bytes_step / (ms * 1e-3) / 1e9
+
+    points = {}
+    main_reps, main_mid = decode_point(args.batch, HELD, main=True)
+    for B in batches:
+        if B != args.batch:
+            reps, mid = decode_point(B, HELD)
+            ms = statistics.median(reps)
+            points[f"decode_b{B}"] = round(B / ms * 1e3, 1)
+            points[f"decode_b{B}_frac"] = round(frac_of_roofline(B, ms, mid) / peaks["hbm_gbs"], 4)
+    for B in long_batches:
+        reps, mid = decode_point(B, held_long)
+        ms = statistics.median(reps)
+        points[f"decode_b{B}_ctx8k"] = round(B / ms * 1e3, 1)
+        points[f"decode_b{B}_ctx8k_frac"] = round(frac_of_roofline(B, ms, mid) / peaks["hbm_gbs"], 4)
+    if prefill_long is not None:
+        points["prefill_8192"] = prefill_long["value"]
+        points["prefill_8192_frac"] = prefill_long["frac"]
+
+    ms_step = statistics.median(main_reps)
     value = args.batch / ms_step * 1e3
-    bytes_step = weight_bytes(cfg, args.layers) + args.batch * (HELD + PRIME + W + K / 2) * kv_bytes_per_token(cfg, args.layers)
-    achieved = bytes_step / (ms_step * 1e-3) / 1e9
+    achieved = frac_of_roofline(args.batch, ms_step, main_mid)
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": round(achieved / peaks["hbm_gbs"], 4), "of": peaks["source"]}
+    spread = {"repeats": len(main_reps), "min": round(args.batch / max(main_reps) * 1e3, 1),
+              "max": round(args.batch / min(main_reps) * 1e3, 1)}
 
     if args.only == "decode":
-        print(json.dumps({"decode_ms_per_step": ms_step, "roofline": roofline}))
+        print(json.dumps({"decode_ms_per_step": ms_step, "spread": spread, "roofline": roofline, "points": points}))
         return 0
 
     # ---- decode end to end through the scheduler: host ids in, host ids out, every step ----------------------
     B = args.batch
     for r in range(B):
-        eng.scheduler.submit(Request([int(t) for t in rng.randint(0, vocab, HELD)], max_new_tokens=PRIME + W + K + 4 * B + 64))
-    while any(s.status != "decode" or s.pending != 1 for s in eng.scheduler.running) or eng.scheduler.waiting \
-            or eng.scheduler.incoming:
+        eng.scheduler.submit(Request([int(t) for t in rng.randint(0, vocab, HELD)], max_new_tokens=span - 8))
+    while not eng.scheduler.idle and (any(s.status != "decode" or s.pending != 1 for s in eng.scheduler.running)
+                                      or eng.scheduler.waiting or eng.scheduler.incoming or not eng.scheduler.running):
         eng.scheduler.step()
     for _ in range(PRIME + W):
         eng.scheduler.step()
     h0, d0 = eng.executor.h2d_bytes, eng.executor.d2h_bytes
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    n_tok = 0
-    for _ in range(K):
-        n_tok += sum(1 for ev in eng.scheduler.step() if ev.token is not None)
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
-    e2e = {"value": round(n_tok / e2e_s, 1), "unit": "tokens/s",
-           "h2d_bytes_per_step": (eng.executor.h2d_bytes - h0) // K, "d2h_bytes_per_step": (eng.executor.d2h_bytes - d0) // K}
+    e2e_reps = []
+    for _ in range(R):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        n_tok = 0
+        for _ in range(K):
+            n_tok += sum(1 for ev in eng.scheduler.step() if ev.token is not None)
+        torch.cuda.synchronize()
+        e2e_reps.append(n_tok / (time.perf_counter() - t0))
+    e2e = {"value": round(statistics.median(e2e_reps), 1), "unit": "tokens/s",
+           "h2d_bytes_per_step": (eng.executor.h2d_bytes - h0) // (R * K),
+           "d2h_bytes_per_step": (eng.executor.d2h_bytes - d0) // (R * K),
+           "min": round(min(e2e_reps), 1), "max": round(max(e2e_reps), 1)}
     for s_ in list(eng.scheduler.running):
         eng.scheduler.cancel(s_.id)
     while not eng.scheduler.idle:
@@ -447,11 +502,10 @@ def main():
         "config": {"model": "llama-3.2-1b-shape", "layers": args.layers, "layers_full": FULL_LAYERS, "hidden": 2048,
                    "heads": 32, "kv_heads": 8, "head_dim": 64, "intermediate": 8192, "vocab": 128256,
                    "global_batch": args.batch, "seq_len": HELD, "context": CONTEXT, "kv_block": 16, "parallelism": "none",
-                   "l2": "inputs larger than L2 (weights + cache >= 2.5 GB per step)", "tied_embeddings": True},
-        "e2e": e2e, "gpu_launches": launches, "library_gemm_calls": lib_calls, "prefill": prefill,
-        "roofline": roofline,
-        "points": {f"decode_b{b}": round(b / results[b] * 1e3, 1) for b in batches if b != args.batch},
-        "clocks": clocks, "impl": "ours",
+                   "l2": "inputs larger than L2 (weights + cache >= 2.5 GB per step)", "tied_embeddings": True,
+                   "value_is": f"median of {len(main_reps)} repeats of {K} steps", "ctx8k_points_hold": held_long},
+        "spread": spread, "e2e": e2e, "gpu_launches": launches, "library_gemm_calls": lib_calls, "prefill": prefill,
+        "roofline": roofline, "points": points, "clocks": clocks, "impl": "ours",
     }
     print(json.dumps(out))
     return 0

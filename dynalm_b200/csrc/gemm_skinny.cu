@@ -38,7 +38,7 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-enum { SK_OUT_BF16 = 0, SK_OUT_F32 = 1, SK_OUT_SWIGLU = 2 };
+enum { SK_OUT_BF16 = 0, SK_OUT_F32 = 1, SK_OUT_SWIGLU = 2, SK_OUT_ARGMAX = 3 };
 
 // The weight stream of one block: y^T tile = W rows (wrow, 16 * MT of them in MMA row order) times x^T, k-blocks
 // [blk_begin, blk_end) dealt to the warps round-robin. Leaves every warp's partial tile in `red`
@@ -201,6 +201,28 @@ gemm_skinny_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
     }
     return;
   }
+  if (mode == SK_OUT_ARGMAX) {
+    // no logits leave the block: per batch row the largest of its FT features and where it is (the lowest feature
+    // among equals), into y as float [M][blocks] followed by int [M][blocks]; a small kernel picks among the blocks
+    const int blocks = gridDim.x;
+    float* pv = static_cast<float*>(y);
+    int* pi = reinterpret_cast<int*>(pv + static_cast<size_t>(M) * blocks);
+    for (int b = threadIdx.x; b < M; b += SK_THREADS) {
+      float best = -INFINITY;
+      int where = 0x7fffffff;
+      for (int fi = 0; fi < FT; ++fi) {
+        if (f0 + fi >= N) break;
+        float v = 0.0f;
+#pragma unroll
+        for (int wv = 0; wv < SK_WARPS; ++wv) v += red[(static_cast<size_t>(wv) * FT + fi) * BT + b];
+        v *= out_scale;
+        if (v > best) { best = v; where = f0 + fi; }
+      }
+      pv[static_cast<size_t>(b) * blocks + blockIdx.x] = best;
+      pi[static_cast<size_t>(b) * blocks + blockIdx.x] = where;
+    }
+    return;
+  }
   for (int idx = threadIdx.x; idx < FT * BT; idx += SK_THREADS) {
     const int b = idx / FT, fi = idx % FT;      // consecutive threads -> consecutive features of one batch row
     const int f = f0 + fi;
@@ -309,6 +331,9 @@ int launch_skinny(const void* x, int ldx, const void* w, void* y, int ldy, int M
 // x: bf16 [M, K] rows of ldx elements (16-byte aligned rows), w: bf16 [N, K] contiguous, K a multiple of 8,
 // M <= 64. mode 0: y bf16 [M, N]; mode 1: y fp32, n_split partial results of [M, ldy] floats each,
 // split_stride floats apart; mode 2: w = [gate; up] (N even), y bf16 [M, N / 2] = silu(x Wg^T) * (x Wu^T).
+// mode 3: nothing but the place of each row's largest output leaves the kernel: y = float [M][blocks] then
+// int [M][blocks] (blocks = ceil(N / features per block), see dl_gemm_skinny_argmax_blocks), the largest value of every
+// block's features and its feature index (the lowest among equals); out_scale must be positive.
 // n_split > 1 needs mode 1. ahead, ahead_bytes: memory that the kernel after this one will stream (weights),
 // requested into L2 before this kernel waits for the one in front of it; null / 0: nothing.
 DL_EXPORT int dl_gemm_skinny(const void* x, int ldx, const void* w, void* y, int ldy, int M, int N, int K, int mode,
@@ -316,12 +341,18 @@ DL_EXPORT int dl_gemm_skinny(const void* x, int ldx, const void* w, void* y, int
                              long long ahead_bytes, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 64 || K <= 0 || (K & 7) || (ldx & 7) || n_split < 1 || n_split > 64 || (n_split > 1 && mode != dl::SK_OUT_F32) ||
-      (mode == dl::SK_OUT_SWIGLU && (N & 1)) || mode < 0 || mode > 2)
+      (mode == dl::SK_OUT_SWIGLU && (N & 1)) || mode < 0 || mode > 3 || (mode == dl::SK_OUT_ARGMAX && !(out_scale > 0.0f)))
     return DL_ERR_UNSUPPORTED;
   if (M <= 8) return dl::launch_skinny<1, 1>(x, ldx, w, y, ldy, M, N, K, mode, out_scale, n_split, split_stride, ahead, ahead_bytes, stream);
   if (M <= 16) return dl::launch_skinny<1, 2>(x, ldx, w, y, ldy, M, N, K, mode, out_scale, n_split, split_stride, ahead, ahead_bytes, stream);
   if (M <= 32) return dl::launch_skinny<2, 4>(x, ldx, w, y, ldy, M, N, K, mode, out_scale, n_split, split_stride, ahead, ahead_bytes, stream);
   return dl::launch_skinny<2, 8>(x, ldx, w, y, ldy, M, N, K, mode, out_scale, n_split, split_stride, ahead, ahead_bytes, stream);
+}
+
+// Blocks (= partial results per row) of dl_gemm_skinny in mode 3 for M rows and N features.
+DL_EXPORT int dl_gemm_skinny_argmax_blocks(int M, int N) {
+  const int per_block = M <= 16 ? 16 : 32;
+  return (N + per_block - 1) / per_block;
 }
 
 // The fused q | k | v projection (see gemm_skinny_qkv_rope_kernel): x bf16 [M, K], M <= 16; w bf16 [(n_heads +

@@ -96,6 +96,37 @@ __global__ void argmax_final_kernel(const float* __restrict__ pv, const int* __r
   if (lane == 0) out[r] = idx == 0x7fffffff ? 0 : idx;
 }
 
+// The same choice among any number of partial results per row (pv, pi: [rows][parts]): one block per row.
+__global__ void __launch_bounds__(256)
+argmax_of_parts_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int parts, int* __restrict__ out,
+                       const int* __restrict__ status_src, int* __restrict__ status_dst) {
+  __shared__ float bv[8];
+  __shared__ int bi[8];
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.x;
+  if (status_dst != nullptr && r == 0 && threadIdx.x == 0) *status_dst = *status_src;
+  float best = -INFINITY;
+  int idx = 0x7fffffff;
+  for (int p = threadIdx.x; p < parts; p += 256) {
+    const float v = pv[static_cast<size_t>(r) * parts + p];
+    const int i = pi[static_cast<size_t>(r) * parts + p];
+    if (v > best || (v == best && i < idx)) { best = v; idx = i; }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = idx; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int wv = 1; wv < 8; ++wv)
+      if (bv[wv] > best || (bv[wv] == best && bi[wv] < idx)) { best = bv[wv]; idx = bi[wv]; }
+    out[r] = idx == 0x7fffffff ? 0 : idx;
+  }
+}
+
 // One block per row. Each thread owns a contiguous run of ids so that the walk is in id order.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_temperature_kernel(const float* __restrict__ logits, int ld, int vocab,
@@ -191,6 +222,16 @@ DL_EXPORT int dl_argmax(const float* logits, int ld, int rows, int vocab, int* o
   }
   dl::argmax_kernel<<<rows, dl::SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, out, status_src, status_dst);
   return dl::launch_status();
+}
+
+// out[r] = the index among `parts` partial results (largest value, lowest index among equals) of row r, as a matrix
+// product with the argmax epilogue leaves them: pv float [rows][parts], pi int [rows][parts].
+DL_EXPORT int dl_argmax_of_parts(const float* pv, const int* pi, int rows, int parts, int* out, const int* status_src,
+                                 int* status_dst, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (parts <= 0) return DL_ERR_UNSUPPORTED;
+  return dl::launch_streaming(dl::argmax_of_parts_kernel, dim3(rows), dim3(256), 0, stream, pv, pi, parts, out,
+                              status_src, status_dst);
 }
 
 // temperature: fp32 [rows] (> 0); uniform: double [rows] in [0, 1).

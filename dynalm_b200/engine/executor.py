@@ -65,8 +65,19 @@ class GpuExecutor:
     def can_launch(batch: List[BatchItem]) -> bool:
         return bool(batch) and all(b.sample and len(b.tokens) == 1 and b.seq.sampler.on_device for b in batch)
 
-    def _sample_on_device(self, logits: torch.Tensor, want: List[BatchItem], slot: int) -> None:
+    def _choose(self, want: List[BatchItem]):
+        """What to hand the step as `choose` when every wanted row is decided by its largest logit on the device."""
+        if want and all(b.seq.sampler.on_device and b.seq.sampler.params.greedy for b in want):
+            return (self._ids[:len(want)], self._ids[2 * self._n:])
+        return None
+
+    def _sample_on_device(self, logits: Optional[torch.Tensor], want: List[BatchItem], slot: int) -> None:
         n = len(want)
+        if logits is None:
+            # the step picked the most likely tokens itself (and brought the status word along)
+            self._ids_host[slot].copy_(self._ids, non_blocking=True)
+            self.d2h_bytes += self._ids_host[slot].numel() * 4
+            return
         ops.argmax(logits, self._ids[:n], status_to=self._ids[2 * self._n:])
         if any(not b.seq.sampler.params.greedy and b.seq.sampler.on_device for b in want):
             th, uh = self._temp_host[slot], self._u_host[slot]
@@ -89,8 +100,8 @@ class GpuExecutor:
         feedback = None
         if after is not None:
             feedback = (self._ids, [after.places[b.seq.id] for b in batch])
-        logits = self.step_fn.step(entries, reserve=False, token_feedback=feedback)
-        self.h2d_bytes += self.step_fn.buffers.size * 4
+        logits = self.step_fn.step(entries, reserve=False, token_feedback=feedback, choose=self._choose(batch))
+        self.h2d_bytes += self.step_fn.batcher.last_upload_bytes
         slot = self._turn
         self._turn ^= 1
         self._sample_on_device(logits, batch, slot)
@@ -121,9 +132,9 @@ class GpuExecutor:
         if self.can_launch(batch):
             return self.collect(self.launch(batch))
         entries = [StepEntry(b.seq.id, b.tokens, [len(b.tokens) - 1] if b.sample else []) for b in batch]
-        logits = self.step_fn.step(entries, reserve=False)
-        self.h2d_bytes += self.step_fn.buffers.size * 4
         want = [b for b in batch if b.sample]
+        logits = self.step_fn.step(entries, reserve=False, choose=self._choose(want))
+        self.h2d_bytes += self.step_fn.batcher.last_upload_bytes
         if not want:
             return {}
         n = len(want)

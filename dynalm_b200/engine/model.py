@@ -16,6 +16,7 @@ from ..parts import BLOCKS, NORMS
 from ..parts.base import CacheSpec, pick_tensors
 from ..parts.block import ResidualStream
 from ..parts.embedding import LogitsHead, TokenEmbedding
+from ..kernels import ops
 from . import launch_memo
 
 
@@ -104,8 +105,25 @@ class Decoder:
                                 rows=ctx.logit_rows)
         return self.head.forward(normed, out[:n])
 
-    def forward(self, ctx, caches, out: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    def choose(self, stream: ResidualStream, ctx, ids: torch.Tensor, status_to=None) -> bool:
+        """The most likely token of every wanted row into `ids`, the logits never leaving the product's kernel; False
+        (and nothing done) when the head cannot do that for this step."""
+        n = ctx.num_logit_rows
+        if n > 8 or self.rt.dtype != torch.bfloat16:
+            return False
+        normed = self.rt.buffer("final_normed", (n, self.width))
+        if not ops.gemm_argmax_applies(normed, self.head.weight):
+            return False
+        self.final_norm.forward(stream.x, normed, delta=stream.pending, delta_scale=stream.pending_scale,
+                                rows=ctx.logit_rows)
+        return self.head.choose(normed, ids, status_to)
+
+    def forward(self, ctx, caches, out: Optional[torch.Tensor], choose=None) -> Optional[torch.Tensor]:
+        """`choose` = (ids, status_to): only the most likely token of each wanted row is wanted, on the device; the
+        head then leaves the logits out when it can (None is returned), else they are returned as always."""
         stream = self.hidden(ctx, caches)
-        if ctx.num_logit_rows == 0 or out is None:
+        if ctx.num_logit_rows == 0 or (out is None and choose is None):
+            return None
+        if choose is not None and self.choose(stream, ctx, choose[0], choose[1]):
             return None
         return self.logits(stream, ctx, out)

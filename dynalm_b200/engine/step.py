@@ -35,6 +35,9 @@ class StepEntry:
     want: Sequence[int] = ()
 
 
+SMALL_STEP_ROWS = 256      # steps of up to this many rows use the small set of step buffers
+
+
 class StepShape:
     """What a step looks like on the host, for the parts' step plans: per entry of the batch its number of rows,
     first row, first position and request slot."""
@@ -58,7 +61,7 @@ class _StepBuffers:
     RING = 4
 
     def __init__(self, device, max_tokens: int, max_requests: int, n_groups: int, max_blocks: int, page_size: int,
-                 plans=()):
+                 plans=(), tables: Optional[torch.Tensor] = None):
         self.max_tokens, self.max_requests = max_tokens, max_requests
         off = 0
         self.off: Dict[str, slice] = {}
@@ -88,8 +91,10 @@ class _StepBuffers:
         self.host_np = [h.numpy() for h in self.host]
         self.events = [None] * self.RING
         self.dev = torch.zeros(self.size, dtype=torch.int32, device=self.device)
-        self.tables = torch.full((max(1, n_groups), max_requests, max_blocks), -1, dtype=torch.int32, device=self.device)
+        self.tables = tables if tables is not None else torch.full((max(1, n_groups), max_requests, max_blocks), -1,
+                                                                  dtype=torch.int32, device=self.device)
         self.turn = 0
+        self.views = {name: self.dev[sl] for name, sl in self.off.items()}
 
     def next_host(self) -> int:
         i = self.turn
@@ -128,10 +133,15 @@ class BatchBuilder:
         plans = [p for p in plans if not (p.name in names or names.add(p.name))]
         self.buffers = _StepBuffers(runtime.device, self.max_tokens, self.max_requests, len(cache.groups),
                                     cache.max_blocks, cache.page_size, plans)
+        # steps of few rows (every decode step) have buffers of their own, a few KB instead of five arrays of
+        # max_tokens entries: what crosses the bus follows the step, and the addresses a CUDA graph holds stay fixed
+        self.small = (_StepBuffers(runtime.device, SMALL_STEP_ROWS, self.max_requests, len(cache.groups), cache.max_blocks,
+                                   cache.page_size, plans, tables=self.buffers.tables)
+                      if self.max_tokens > SMALL_STEP_ROWS else self.buffers)
         self.computed: Dict[Hashable, int] = {}       # tokens each live request has in the cache
-        self._dev = {name: self.buffers.dev_view(name) for name in self.buffers.off}
         self.tables = {g.gid: self.buffers.tables[g.gid] for g in cache.groups}      # [request slots, blocks]
         self.update_launches = 0
+        self.last_upload_bytes = 0
 
     def begin(self, request) -> None:
         self.cache.add_request(request)
@@ -169,26 +179,25 @@ class BatchBuilder:
                     self.cache.truncate(req, before, computed_beyond=False)
             raise
 
-    def _table_updates(self, h, slot: int) -> int:
+    def _table_updates(self, b: _StepBuffers, h, slot: int) -> int:
         """Write what has changed in the block tables into the step's section (and send whatever does not fit in
         rounds of its own first). Returns the number of entries that travel with the step."""
         ups = self.cache.take_table_updates()
-        b = self.buffers
         sec = b.off["table_updates"]
         while len(ups) > b.max_updates:
             head, ups = ups[:b.max_updates], ups[b.max_updates:]
             h[sec][:4 * len(head)] = np.asarray(head, dtype=np.int32).reshape(-1)
             b.upload(slot, "table_updates")
-            self._apply(len(head))
+            self._apply(b, len(head))
             if b.events[slot] is not None:
                 b.events[slot].synchronize()       # the section is written again right away
         if ups:
             h[sec][:4 * len(ups)] = np.asarray(ups, dtype=np.int32).reshape(-1)
         return len(ups)
 
-    def _apply(self, n: int) -> None:
+    def _apply(self, b: _StepBuffers, n: int) -> None:
         from ..kernels import ops
-        ops.table_updates(self.buffers.tables, self._dev["table_updates"], n)
+        ops.table_updates(b.tables, b.views["table_updates"], n)
         self.update_launches += 1
 
     def build(self, entries: Sequence[StepEntry], reserve: bool = True,
@@ -224,7 +233,7 @@ class BatchBuilder:
                 if self.cache.tokens[e.request] < self.computed[e.request] + len(e.tokens):
                     raise InvalidArgument(f"request {e.request!r} has no pages reserved for its tokens")
 
-        b = self.buffers
+        b = self.small if total <= self.small.max_tokens else self.buffers
         i = b.next_host()
         h = b.host_np[i]
         off = b.off
@@ -264,16 +273,18 @@ class BatchBuilder:
         shape = StepShape(h_q_len, h_q_start, h_pos_start, h_slots, total)
         extras = {}
         for plan in b.plans:
-            extras[plan.name] = (self._dev[f"plan:{plan.name}"], plan.fill(h[off[f"plan:{plan.name}"]], shape))
+            extras[plan.name] = (b.views[f"plan:{plan.name}"], plan.fill(h[off[f"plan:{plan.name}"]], shape))
         if feedback_src is not None:
             if total != len(entries) or len(feedback_src) != len(entries):
                 raise InvalidArgument("token feedback needs one token per entry and one source per entry")
             h[off["feedback_src"]][:len(entries)] = feedback_src
-        n_updates = self._table_updates(h, i)
+        n_updates = self._table_updates(b, h, i)
         b.upload(i)
+        self.last_upload_bytes = b.size * 4
         if n_updates:
-            self._apply(n_updates)
-        d = self._dev
+            self._apply(b, n_updates)
+        d = b.views
+        extras["step:feedback_src"] = d["feedback_src"]
         return StepContext(
             num_tokens=total, num_requests=len(entries), token_ids=d["token_ids"], positions=d["positions"],
             row_request=d["row_request"], row_slot=d["row_slot"], q_start=d["q_start"], pos_start=d["pos_start"],
@@ -317,6 +328,7 @@ class StepFunction:
         self._decode_logits: Optional[torch.Tensor] = None
         self.graph_kernel_launches = 0     # kernels replayed through graphs so far
         self._graph_nodes: Dict[tuple, int] = {}
+        self._captured_logits: Dict[tuple, bool] = {}     # whether a captured step leaves logits (or only chosen ids)
         self._shape_seen: Dict[tuple, int] = {}     # decode-only launch shape -> how often it has come
         self._capture_stream: Optional[torch.cuda.Stream] = None
         self.graph_captures = 0            # graphs captured so far, and the host time that took
@@ -353,29 +365,34 @@ class StepFunction:
             self._caches = [self.cache.view(i, self.batcher.tables) for i in range(len(self.model.order))]
         return self._caches
 
-    def step(self, entries: Sequence[StepEntry], reserve: bool = True, token_feedback=None) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], reserve: bool = True, token_feedback=None,
+             choose=None) -> Optional[torch.Tensor]:
         """Run the batch. Returns float32 logits [wanted rows, vocab] on the device (a view of a
         buffer that the next step overwrites), or None when nothing was wanted.
 
         token_feedback = (chosen ids on the device, [source place per entry]): the tokens of this step's
         one-token entries are taken on the device from the ids a previous step chose, so the step can be
-        issued before those ids have reached the host."""
+        issued before those ids have reached the host.
+
+        choose = (ids, status_to), int32 tensors on the device: the caller wants nothing but the most likely token of
+        every wanted row, in ids[0 .. wanted rows). Where the head can pick it in its product's epilogue the logits are
+        never written and None is returned; else the logits are returned as without `choose` and the caller picks."""
         if token_feedback is None:
             ctx = self.batcher.build(entries, reserve)
         else:
             from ..kernels import ops
             chosen, src = token_feedback
             ctx = self.batcher.build(entries, reserve, feedback_src=src)
-            ops.feedback_tokens(ctx.token_ids, chosen, self.batcher._dev["feedback_src"], len(entries))
+            ops.feedback_tokens(ctx.token_ids, chosen, ctx.extras["step:feedback_src"], len(entries))
         if self.use_graphs and ctx.decode_only:
-            logits = self._replay(ctx)
+            logits = self._replay(ctx, choose)
         else:
             out = self._logits_buffer(ctx.num_logit_rows) if ctx.num_logit_rows else None
-            logits = self._forward(ctx, out)
+            logits = self._forward(ctx, out, choose)
         self.batcher.finish(entries)
         return logits
 
-    def _capture(self, key: tuple, ctx: StepContext, out: Optional[torch.Tensor]) -> torch.cuda.CUDAGraph:
+    def _capture(self, key: tuple, ctx: StepContext, out: Optional[torch.Tensor], choose=None) -> torch.cuda.CUDAGraph:
         """The step's launches as a CUDA graph (nothing runs yet). Captured on a stream of its own between
         capture_begin and capture_end, without the collection of garbage and the emptying of the allocator's
         cache that torch's context manager does first: nothing is allocated in here."""
@@ -394,7 +411,7 @@ class StepFunction:
         with torch.cuda.stream(self._capture_stream):
             graph.capture_begin()
             try:
-                self._forward(ctx, out)
+                self._captured_logits[key] = self._forward(ctx, out, choose) is not None
             finally:
                 graph.capture_end()
         current.wait_stream(self._capture_stream)
@@ -404,10 +421,10 @@ class StepFunction:
         self.graph_capture_ms += (time.perf_counter() - started) * 1e3
         return graph
 
-    def _forward(self, ctx: StepContext, out: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    def _forward(self, ctx: StepContext, out: Optional[torch.Tensor], choose=None) -> Optional[torch.Tensor]:
         from ..kernels import ops
         with ops.pinned_stream():
-            return self.model.forward(ctx, self.caches(), out)
+            return self.model.forward(ctx, self.caches(), out, choose)
 
     MAX_GRAPHS = 64
     # A launch shape is captured when it comes for the eighth time. A capture costs 5 to 15 ms on the host; shapes
@@ -417,20 +434,22 @@ class StepFunction:
     # 2.20 s with a capture at first sight (32 captures), 2.05 s at the third time (26), 2.04 s at the eighth (2).
     GRAPH_AFTER = int(os.environ.get("DYNALM_GRAPH_AFTER", "8"))
 
-    def _replay(self, ctx: StepContext) -> Optional[torch.Tensor]:
+    def _replay(self, ctx: StepContext, choose=None) -> Optional[torch.Tensor]:
         if self._decode_logits is None:
             self._decode_logits = torch.empty((self.max_requests, self.vocab), dtype=torch.float32,
                                               device=self.rt.device)
-        key = (ctx.num_requests, ctx.num_logit_rows) + self.model.graph_key(ctx)
+        # a graph holds the addresses it was captured with: the tensors of `choose` are part of its key
+        chosen = None if choose is None else tuple(None if t is None else t.data_ptr() for t in choose)
+        key = (ctx.num_requests, ctx.num_logit_rows, chosen) + self.model.graph_key(ctx)
         out = self._decode_logits if ctx.num_logit_rows else None
         graph = self._graphs.get(key)
         if graph is None:
             seen = self._shape_seen.get(key, 0) + 1
             self._shape_seen[key] = seen
             if seen < self.GRAPH_AFTER:
-                self._forward(ctx, out)
-                return out[:ctx.num_logit_rows] if out is not None else None
-            graph = self._capture(key, ctx, out)
+                got = self._forward(ctx, out, choose)
+                return got[:ctx.num_logit_rows] if got is not None else None
+            graph = self._capture(key, ctx, out, choose)
         graph.replay()
         self.graph_kernel_launches += self._graph_nodes[key]
-        return out[:ctx.num_logit_rows] if out is not None else None
+        return out[:ctx.num_logit_rows] if (out is not None and self._captured_logits[key]) else None

@@ -55,6 +55,7 @@ _SIGNATURES = {
     "sampling": {
         "dl_argmax": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
         "dl_sample_temperature": [_P, _I, _I, _I, _P, _P, _P, _P],
+        "dl_argmax_of_parts": [_P, _P, _I, _I, _P, _P, _P, _P],
         "dl_feedback_tokens": [_P, _P, _P, _I, _P],
     },
     "streams": {"dl_stream_fork": [_P, _P], "dl_stream_join": [_P, _P]},
@@ -843,6 +844,35 @@ def table_updates(tables: torch.Tensor, updates: torch.Tensor, n: int) -> None:
     check_limits("table_update", requests=tables.shape[1])
     _check(_fn("table_update", "dl_table_updates")(_p(tables), _p(updates), n, tables.shape[0], tables.shape[1],
                                                     tables.shape[2], _stream()), "table_updates")
+
+
+def gemm_argmax_applies(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether `gemm_argmax` takes this product: the weight-streaming kernel's shapes, up to 8 rows."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[0] <= 8 and x.shape[1] % 8 == 0
+            and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.is_contiguous()
+            and w.data_ptr() % 16 == 0)
+
+
+def gemm_argmax(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, out_scale: float = 1.0,
+                status_to: Optional[torch.Tensor] = None) -> None:
+    """out[r] = the index of the largest element of (x W^T)[r] * out_scale, the lowest among equals, without the
+    product ever being written: the weight-streaming kernel leaves one candidate per block (csrc/gemm_skinny.cu,
+    mode 3) and a small kernel picks among them. `scratch`: float32, at least 2 * rows * ceil(N / 16) elements.
+    out_scale must be positive. `status_to` as in `argmax`."""
+    _cuda(x, w, out, scratch)
+    if not gemm_argmax_applies(x, w) or w.shape[1] != x.shape[1] or out_scale <= 0:
+        raise Unsupported("gemm_argmax: up to 8 bfloat16 rows, K a multiple of 8, 16-byte aligned rows, a positive scale")
+    M, K = x.shape
+    N = w.shape[0]
+    blocks = -(-N // 16)
+    if scratch.dtype != torch.float32 or scratch.numel() < 2 * M * blocks or out.dtype != torch.int32 or out.numel() < M:
+        raise InvalidArgument("gemm_argmax: float32 scratch of 2 * rows * ceil(N / 16) elements, int32 out of one per row")
+    ahead, ahead_bytes = _take_ahead()
+    _check(_fn("gemm_skinny", "dl_gemm_skinny")(_p(x), x.stride(0), _p(w), _p(scratch), blocks, M, N, K, 3, out_scale,
+                                                 1, 0, ahead, ahead_bytes, _stream()), "gemm_skinny (argmax)")
+    status = _status_word(x.device) if status_to is not None else None
+    _check(_fn("sampling", "dl_argmax_of_parts")(_p(scratch), scratch.data_ptr() + 4 * M * blocks, M, blocks, _p(out),
+                                                  _p(status), _p(status_to), _stream()), "argmax_of_parts")
 
 
 def feedback_tokens(token_ids: torch.Tensor, chosen: torch.Tensor, src: torch.Tensor, n: int) -> None:

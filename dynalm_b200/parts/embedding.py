@@ -47,3 +47,13 @@ class LogitsHead:
     def forward(self, normed_rows: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         linear(normed_rows, self.weight, out, None, self.out_scale)
         return out
+
+    def choose(self, normed_rows: torch.Tensor, ids: torch.Tensor, status_to=None) -> bool:
+        """ids[r] = the most likely token of row r (the lowest id among equals) without the logits being written, when
+        the product's kernel can do that in its epilogue; False when it cannot (the caller then takes the logits)."""
+        if not ops.gemm_argmax_applies(normed_rows, self.weight) or self.out_scale <= 0:
+            return False
+        rows = normed_rows.shape[0]
+        scratch = self.rt.flat("head_argmax_parts", 2 * 8 * -(-self.spec.vocab // 16))
+        ops.gemm_argmax(normed_rows, self.weight, ids, scratch, self.out_scale, status_to)
+        return True

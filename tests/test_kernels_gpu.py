@@ -594,3 +594,31 @@ def test_gemm_stream(ops, M, N, K):
     want = gate * torch.sigmoid(gate) * up
     assert (act.double() - want).abs().max() <= 1e-2 * max(1.0, want.abs().max().item())
     assert ops.gemm_tcgen05_status() == 0
+
+
+@pytest.mark.parametrize("rows,N,K", [(1, 499, 64), (5, 128256, 256), (8, 4099, 2048), (8, 16, 8)])
+def test_gemm_argmax_matches_argmax_of_the_product(ops, rows, N, K):
+    """The product whose epilogue keeps only the place of each row's largest output gives what argmax gives on the
+    logits the same kernel writes (the sums are the same, so the choice is exact), ties going to the lowest index."""
+    g = torch.Generator(device="cpu").manual_seed(rows * 1000 + N)
+    x = torch.randn(rows, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16)
+    if N > 40:
+        w[37] = w[11]                      # two equal outputs in every row ...
+        w[11] *= 0
+        w[37] *= 0
+        w[11, 0], w[37, 0] = 60.0, 60.0    # ... made the largest wherever x[r, 0] > 0
+    w = w.to(DEV)
+    logits = torch.empty(rows, N, dtype=torch.float32, device=DEV)
+    ops.gemm_skinny(x, w, logits, "store", 0.5)
+    want = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops.argmax(logits, want)
+    got = torch.full((rows,), -1, dtype=torch.int32, device=DEV)
+    scratch = torch.empty(2 * rows * -(-N // 16), dtype=torch.float32, device=DEV)
+    status = torch.full((1,), 7, dtype=torch.int32, device=DEV)
+    ops.gemm_argmax(x, w, got, scratch, 0.5, status_to=status)
+    assert got.cpu().tolist() == want.cpu().tolist()
+    assert int(status.item()) == ops.gemm_tcgen05_status(DEV)
+    assert 37 not in got.cpu().tolist()         # of the two equal outputs the lower index
+    if N > 40 and K <= 256:
+        assert any(float(x[r, 0]) > 0.5 and int(got[r]) == 11 for r in range(rows)) or not any(float(x[r, 0]) > 0.5 for r in range(rows))
