@@ -337,7 +337,8 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
                            const int* __restrict__ positions, const int* __restrict__ row_request,
                            bf16* __restrict__ out, int out_stride, float* __restrict__ part, int n_heads,
                            int n_kv_heads, int page_shift, float scale_log2, int window, int n_split,
-                           int cluster_merge, int xbuf_offset, const void* __restrict__ ahead, long long ahead_bytes) {
+                           int cluster_merge, int xbuf_offset, const void* __restrict__ ahead, long long ahead_bytes,
+                           const int* __restrict__ plan, int* __restrict__ counters, int part_stride) {
   l2_prefetch_share(ahead, ahead_bytes);     // what the kernel after this one will stream (see common.cuh)
   constexpr int LD = HD + 8;
   constexpr int CH = HD / 8;
@@ -348,10 +349,22 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
   bf16* KV = Qs + 16 * LD;                               // [warp][stage][K | V][KT][LD]
   float* merge = reinterpret_cast<float*>(dt_smem);      // reused after the loop: [warp][16][HD + 2]
 
-  const int split = blockIdx.x, row = blockIdx.z;
+  // Which keys of which row this block takes. Without a plan the grid says it: (split, KV head and chunk of its
+  // group, row), every row cut into n_split parts. With a plan (see dl_paged_attention_decode_planned) the host has
+  // dealt the keys of all rows into units of about equal size, one block each: int4 (row, KV head chunk, part, parts of
+  // that row), after a header whose first word is the number of units; blocks past it have nothing to do.
+  int split = blockIdx.x, row = blockIdx.z, ychunk = blockIdx.y;
+  if (plan != nullptr) {
+    if (static_cast<int>(blockIdx.x) >= plan[0]) return;
+    const int4 unit = reinterpret_cast<const int4*>(plan)[1 + blockIdx.x];
+    row = ck_row(unit.x);
+    ychunk = unit.y;
+    split = unit.z;
+    n_split = unit.w;
+  }
   const int group = n_heads / n_kv_heads;
   const int chunks = (group + 15) / 16;
-  const int kvh = blockIdx.y / chunks, h0 = (blockIdx.y % chunks) * 16;
+  const int kvh = ychunk / chunks, h0 = (ychunk % chunks) * 16;
   const int ng = min(16, group - h0);
   const int head0 = kvh * group + h0;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -373,6 +386,14 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
   // When the block's key range starts on a multiple of 16 (always, unless a window moves it) and pages hold at
   // least 16 keys, every 16 keys of a tile lie in one page: one table lookup serves 16 key rows.
   const bool by_halves = (k_begin & 15) == 0 && page_shift >= 4;
+  // The pages of this warp's first tiles, one lookup per lane, all on their way at once: lane l holds the page of half
+  // l % HALVES of the warp's tile l / HALVES. A tile's copies then start without a lookup of their own in front of them.
+  constexpr int HALVES = KT / 16, AHEAD_TILES = 32 / HALVES;
+  int my_page = 0;
+  if (by_halves) {
+    const int kb = k_begin + ((lane / HALVES) * DT_WARPS + warp) * KT + (lane % HALVES) * 16;
+    if (kb < k_end) my_page = ck_page(table, kb >> page_shift, max_blocks);
+  }
   auto load_tile = [&](int i, int stage) {          // this warp's i-th tile: block tile i * DT_WARPS + warp
     const int key0 = k_begin + (i * DT_WARPS + warp) * KT;
     bf16* kd = my + static_cast<size_t>(stage) * 2 * TILE_ELEMS;
@@ -382,7 +403,12 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
       for (int hf = 0; hf < KT / 16; ++hf) {
         const int kb = key0 + hf * 16;
         size_t slot0 = 0;
-        if (kb < k_end) slot0 = (static_cast<size_t>(ck_page(table, kb >> page_shift, max_blocks)) << page_shift) + (kb & page_mask);
+        if (i < AHEAD_TILES) {
+          const int page = __shfl_sync(0xffffffffu, my_page, i * HALVES + hf);
+          slot0 = (static_cast<size_t>(page) << page_shift) + (kb & page_mask);
+        } else if (kb < k_end) {
+          slot0 = (static_cast<size_t>(ck_page(table, kb >> page_shift, max_blocks)) << page_shift) + (kb & page_mask);
+        }
 #pragma unroll
         for (int c = lane; c < 16 * CH; c += 32) {
           const int r = c / CH, ch = c % CH;
@@ -583,13 +609,45 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
         dst[HD + 1] = ll;
       }
     } else {
-      float* dst = part + ((static_cast<size_t>(row) * n_heads + head) * n_split + split) * REC;
+      float* dst = part + ((static_cast<size_t>(row) * n_heads + head) * part_stride + split) * REC;
       dst[d] = a;
       if (d == 0) {
         dst[HD] = mm;
         dst[HD + 1] = ll;
       }
     }
+  }
+  if (plan != nullptr && n_split > 1) {
+    // The block that finds all other parts of its (row, group chunk) done merges them, in the order of the parts,
+    // whoever came last: the result does not depend on timing. Its own records are re-read like the others'.
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      int* counter = counters + row * (n_kv_heads * chunks) + ychunk;
+      const int before = atomicAdd(counter, 1);
+      s_last = before == n_split - 1;
+      if (s_last) *counter = 0;               // ready for the next launch
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int idx = tid; idx < ng * HD; idx += DT_THREADS) {
+      const int r = idx / HD, d = idx % HD;
+      const float* rec = part + (static_cast<size_t>(row) * n_heads + head0 + r) * part_stride * REC;
+      float mm = -INFINITY;
+      for (int sp = 0; sp < n_split; ++sp) mm = fmaxf(mm, __ldcg(rec + sp * REC + HD));
+      float a = 0.0f, ll = 0.0f;
+      for (int sp = 0; sp < n_split; ++sp) {
+        const float* src = rec + sp * REC;
+        const float ms = __ldcg(src + HD);
+        const float c = ms == -INFINITY ? 0.0f : exp2f(ms - mm);
+        a += __ldcg(src + d) * c;
+        ll += __ldcg(src + HD + 1) * c;
+      }
+      out[static_cast<size_t>(row) * out_stride + static_cast<size_t>(head0 + r) * HD + d] = __float2bfloat16_rn(a / ll);
+    }
+    return;
   }
   if (n_split > 1 && cluster_merge) {
     cooperative_groups::this_cluster().sync();       // every record has arrived (and is visible) in block 0
@@ -616,7 +674,8 @@ template <int HD, int STAGES, int KT>
 int launch_decode_tc(const void* q, int q_stride, const void* kc, const void* vc, const int* block_table, int max_blocks,
                      const int* positions, const int* row_request, void* out, int out_stride, float* part, int rows,
                      int n_heads, int n_kv_heads, int page_shift, float scale, int window, int n_split,
-                     const void* ahead, long long ahead_bytes, cudaStream_t stream) {
+                     const void* ahead, long long ahead_bytes, cudaStream_t stream, const int* plan = nullptr,
+                     int* counters = nullptr, int unit_cap = 0, int part_stride = 0) {
   constexpr size_t pipe = static_cast<size_t>(16 + DT_WARPS * STAGES * 2 * KT) * (HD + 8) * sizeof(bf16);
   constexpr size_t mrg = static_cast<size_t>(DT_WARPS) * 16 * (HD + 2) * sizeof(float);
   constexpr size_t base = ((pipe > mrg ? pipe : mrg) + 15) & ~static_cast<size_t>(15);
@@ -624,7 +683,7 @@ int launch_decode_tc(const void* q, int q_stride, const void* kc, const void* vc
   // for a handful of rows (batch 1: 1063 against 1010 tokens/s) and loses once the grid is a few dozen clusters
   // (batch 8: 1.24 ms against 1.13 ms per step), where global scratch and the merge kernel do better.
   const int group_blocks = n_kv_heads * ((n_heads / n_kv_heads + 15) / 16);
-  const bool cluster = n_split > 1 && n_split <= 8 && (part == nullptr || rows * group_blocks <= 32);
+  const bool cluster = plan == nullptr && n_split > 1 && n_split <= 8 && (part == nullptr || rows * group_blocks <= 32);
   const size_t smem = base + (cluster ? static_cast<size_t>(n_split) * 16 * (HD + 2) * sizeof(float) : 0);
   static size_t configured = 0;
   if (smem > configured) {
@@ -635,6 +694,7 @@ int launch_decode_tc(const void* q, int q_stride, const void* kc, const void* vc
   }
   const int group = n_heads / n_kv_heads;
   dim3 grid(n_split, n_kv_heads * ((group + 15) / 16), rows);
+  if (plan != nullptr) grid = dim3(unit_cap, 1, 1);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(DT_THREADS);
@@ -660,8 +720,9 @@ int launch_decode_tc(const void* q, int q_stride, const void* kc, const void* vc
       &cfg, decode_attention_tc_kernel<HD, STAGES, KT>, static_cast<const bf16*>(q), q_stride, static_cast<const bf16*>(kc),
       static_cast<const bf16*>(vc), block_table, max_blocks, positions, row_request, static_cast<bf16*>(out), out_stride,
       part, n_heads, n_kv_heads, page_shift, scale * 1.4426950408889634f, window, n_split, cluster ? 1 : 0,
-      static_cast<int>(base), pdl_mode() >= 1 ? ahead : nullptr, pdl_mode() >= 1 ? ahead_bytes : 0ll));
-  if (rc != 0 || n_split == 1 || cluster) return rc;
+      static_cast<int>(base), pdl_mode() >= 1 ? ahead : nullptr, pdl_mode() >= 1 ? ahead_bytes : 0ll, plan, counters,
+      plan != nullptr ? part_stride : n_split));
+  if (rc != 0 || n_split == 1 || cluster || plan != nullptr) return rc;
   dim3 cgrid(n_heads, rows);
   const int cthreads = HD <= 32 ? 32 : (HD <= 64 ? 64 : 128);
   return launch(attention_combine_kernel<bf16>, cgrid, dim3(cthreads), 0, stream, static_cast<const float*>(part),
@@ -731,6 +792,50 @@ DL_EXPORT int dl_paged_attention_decode_tc(const void* q, int q_stride, const vo
   }
 #undef DL_CASE
 }
+
+// The same kernel with the keys of all rows dealt out by the host (the step's attention plan) instead of every row
+// being cut into the same number of parts: plan = int32 [4 + 4 * units]: plan[0] = units, then per unit (row, KV head
+// chunk, part, parts of its row); the grid has unit_cap blocks (a number that does not change from step to step, so
+// that a CUDA graph can hold it), of which the first plan[0] work. A row's keys are cut into its `parts` (at most
+// part_stride) like n_split cuts them above. Rows with several parts leave their records in `part`
+// (rows * n_heads * part_stride * (head_dim + 2) floats) and the last block to finish a (row, chunk) merges them;
+// counters: int32 [rows * KV head chunks], zero before the first launch (the kernel leaves them zero).
+DL_EXPORT int dl_paged_attention_decode_planned(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                                                const int* block_table, int max_blocks, const int* positions,
+                                                const int* row_request, void* out, int out_stride, float* part,
+                                                int rows, int n_heads, int n_kv_heads, int head_dim, int page_size,
+                                                float scale, int window, const int* plan, int* counters, int unit_cap,
+                                                int part_stride, const void* ahead, long long ahead_bytes,
+                                                cudaStream_t stream) {
+  if (rows <= 0 || unit_cap <= 0) return 0;
+  int page_shift = 0;
+  while ((1 << page_shift) < page_size) ++page_shift;
+  if ((1 << page_shift) != page_size || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || part_stride < 1 || rows > 65535 ||
+      (q_stride & 7) || !(scale > 0.0f) || plan == nullptr || counters == nullptr || part == nullptr ||
+      (reinterpret_cast<uintptr_t>(plan) & 15))
+    return DL_ERR_UNSUPPORTED;
+#define DL_CASE(H, S, T)                                                                                               \
+  case H:                                                                                                             \
+    return dl::launch_decode_tc<H, S, T>(q, q_stride, k_cache, v_cache, block_table, max_blocks, positions, row_request, \
+                                      out, out_stride, part, rows, n_heads, n_kv_heads, page_shift, scale, window,    \
+                                      2, ahead, ahead_bytes, stream, plan, counters, unit_cap, part_stride)
+  switch (head_dim) {
+    DL_CASE(16, 4, 32);
+    DL_CASE(32, 4, 32);
+    DL_CASE(48, 3, 32);
+    DL_CASE(64, 3, 32);
+    DL_CASE(80, 3, 32);
+    DL_CASE(96, 3, 16);
+    DL_CASE(112, 3, 16);
+    DL_CASE(128, 3, 16);
+    default:
+      return DL_ERR_UNSUPPORTED;
+  }
+#undef DL_CASE
+}
+
+// Keys per tile of the tensor-core kernel for a head size (what a plan counts the keys in).
+DL_EXPORT int dl_paged_attention_decode_tile(int head_dim) { return head_dim >= 96 ? 16 : 32; }
 
 // ------------------------------------------------------------------------------------------------
 // The entry point that allocates nothing (see dynalm_noalloc.h for who needs it and its rules).

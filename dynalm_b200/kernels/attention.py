@@ -56,6 +56,87 @@ class QueryTilePlan:
 
 QUERY_TILES = QueryTilePlan()
 
+PART_CAP = 32            # most parts a row's keys are cut into
+DECODE_BLOCKS_PER_SM = int(os.environ.get("DYNALM_DECODE_BLOCKS", "2"))     # blocks of the decode kernel that fit an SM
+# 1: the keys of a step's rows are dealt into units by the host (DecodeUnits below); 0 (default): every row is cut
+# into the same number of parts. Measured on B200 (1B shapes, 2,048 tokens of context, decode step): batch 8 0.925 ms
+# planned against 0.900 ms, batch 1 1,148 against 1,335 tokens/s (there the parts merge inside a thread-block cluster),
+# batch 64 equal: the kernel is bound by the latency of a warp's chain of tiles, not by how evenly the blocks are
+# loaded, and the planned units are more and shorter. It stays for steps whose requests differ much in length.
+DECODE_PLANNED = os.environ.get("DYNALM_DECODE_PLANNED", "0") != "0"
+
+
+class DecodeUnits:
+    """The step plan of the split-KV decode attention: the keys of the step's single-token requests dealt into units
+    of about equal size, about one for every block the GPU can hold at a time, so that a step with one long and many
+    short requests, or with few requests, still fills it evenly; a row's share of the units follows its share of the
+    keys. On the device: int32 [4 + 4 * units] = (units, 0, 0, 0), then (row, KV-head chunk, part, parts of the row)
+    per unit. What `fill` returns: (units, rows). The grid the kernel is launched with depends on the number of rows
+    alone (`unit_cap`), so a growing context never changes a CUDA graph."""
+
+    def __init__(self, chunks: int, tile_keys: int, window: int):
+        self.chunks, self.tile, self.window = int(chunks), int(tile_keys), int(window)
+        self.name = f"attention_decode_units:{chunks}:{tile_keys}:{window}"
+
+    def slots(self) -> int:
+        return sm_count() * DECODE_BLOCKS_PER_SM
+
+    def unit_cap(self, rows: int) -> int:
+        # one round of blocks, and room for every row to have a part although its share rounds to none
+        return self.slots() + rows * self.chunks
+
+    def ints(self, max_tokens: int, max_requests: int) -> int:
+        return 4 + 4 * self.unit_cap(max_requests)
+
+    def parts(self, key_counts) -> list:
+        """Parts per row for rows that read `key_counts` keys each."""
+        rows = len(key_counts)
+        tiles = [max(1, -(-n // self.tile)) for n in key_counts]
+        budget = self.slots() // self.chunks               # parts over all rows that one round of blocks holds
+        if rows >= budget:
+            return [1] * rows
+        cap = [max(1, min(PART_CAP, t // 4)) for t in tiles]          # a part keeps a tile for each of a block's four warps
+        total = sum(tiles)
+        parts = [max(1, min(cap[r], budget * tiles[r] // total)) for r in range(rows)]
+        left = budget - sum(parts)
+        while left > 0:
+            best, load = -1, 0.0
+            for r in range(rows):
+                if parts[r] < cap[r] and tiles[r] / parts[r] > load:
+                    best, load = r, tiles[r] / parts[r]
+            if best < 0:
+                break
+            parts[best] += 1
+            left -= 1
+        return parts
+
+    def fill(self, host, shape):
+        rows = 0
+        while rows < len(shape.q_len) and shape.q_len[rows] == 1:
+            rows += 1
+        counts = [(min(p + 1, self.window) if self.window > 0 else p + 1) for p in shape.pos_start[:rows]]
+        parts = self.parts(counts) if rows else []
+        flat = [0, 0, 0, 0]
+        for r in range(rows):
+            for c in range(self.chunks):
+                for p in range(parts[r]):
+                    flat += (r, c, p, parts[r])
+        flat[0] = (len(flat) - 4) // 4
+        host[:len(flat)] = flat
+        return flat[0], rows
+
+
+_decode_units = {}
+
+
+def decode_units_plan(spec) -> DecodeUnits:
+    chunks = spec.num_kv_heads * -(-(spec.num_heads // spec.num_kv_heads) // 16)
+    key = (chunks, ops.decode_tile_keys(spec.head_dim), int(spec.get("window", 0)))
+    plan = _decode_units.get(key)
+    if plan is None:
+        plan = _decode_units[key] = DecodeUnits(*key)
+    return plan
+
 
 def query_tiles(ctx):
     """(tiles on the device, number of tiles, of prompt tiles, of leading single-token requests) of this step, or
@@ -123,6 +204,19 @@ def use_prefill_tcgen05(spec, qkv: torch.Tensor, out: torch.Tensor, page_size: i
 def _decode_rows(qkv: torch.Tensor, cache, ctx, out: torch.Tensor, spec, runtime, rows: int) -> None:
     """The split-KV kernel on rows 0 .. rows - 1 (each the newest token of its request)."""
     k_cache, v_cache = cache.arrays
+    planned = ctx.extras.get(decode_units_plan(spec).name) if (DECODE_PLANNED and decode_uses_tensor_cores(spec)
+                                                              and qkv.stride(0) % 8 == 0) else None
+    if planned is not None and planned[1][1] == rows:
+        plan = decode_units_plan(spec)
+        most_rows = max(runtime.max_requests, rows)
+        scratch = runtime.flat(f"attn_split_scratch_{spec.num_heads}x{spec.head_dim}",
+                               ops.decode_scratch_floats(most_rows, spec.num_heads, spec.head_dim, MAX_SPLITS))
+        counters = runtime.flat(f"attn_unit_counters_{plan.chunks}", most_rows * plan.chunks, torch.int32)
+        ops.paged_attention_decode_planned(qkv[:rows], k_cache, v_cache, cache.block_table, ctx.positions[:rows],
+                                           ctx.row_slot[:rows], out[:rows], scratch, counters, planned[0],
+                                           plan.unit_cap(rows), PART_CAP, spec.num_heads, spec.num_kv_heads, spec.head_dim,
+                                           cache.page_size, float(spec.scale), spec.get("window", 0))
+        return
     n_split = decode_plan(ctx, spec, rows)
     scratch = None
     if n_split > 1:

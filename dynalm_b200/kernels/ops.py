@@ -35,6 +35,8 @@ _SIGNATURES = {
         "dl_paged_attention_generic": [_I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P]},
     "attention_decode": {
         "dl_paged_attention_decode": [_I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+        "dl_paged_attention_decode_planned": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P,
+                                              _I, _I, _P, _L, _P],
         "dl_paged_attention_decode_tc": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _L, _P]},
     "attention_prefill": {
         "dl_paged_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P]},
@@ -521,6 +523,44 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
         dtype_code(q.dtype), _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), block_table.stride(0),
         _p(positions), _p(row_request), _p(out), out.stride(0), _p(scratch), rows, n_heads, n_kv_heads, head_dim,
         page_size, scale, window, n_split, _stream()), "paged_attention_decode")
+
+
+def decode_tile_keys(head_dim: int) -> int:
+    """Keys per tile of the tensor-core decode attention (what its plans count keys in)."""
+    return 16 if head_dim >= 96 else 32
+
+
+def paged_attention_decode_planned(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                                   positions: torch.Tensor, row_request: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor,
+                                   counters: torch.Tensor, plan: torch.Tensor, unit_cap: int, part_stride: int, n_heads: int,
+                                   n_kv_heads: int, head_dim: int, page_size: int, scale: float, window: int) -> None:
+    """The tensor-core split-KV attention with the keys of all rows dealt into units by the host (`plan`, see
+    kernels/attention.DecodeUnits): one block per unit, `unit_cap` blocks launched; the last block of a row's group of
+    heads to finish merges the row's parts. bfloat16, head_dim up to 128. scratch: float32, rows * n_heads * part_stride *
+    (head_dim + 2) elements; counters: int32, rows * KV-head chunks, zero (the kernel leaves them zero)."""
+    _cuda(q, k_cache, v_cache, block_table, positions, row_request, out, scratch, counters, plan)
+    _rows_contiguous(q, "q")
+    _rows_contiguous(out, "out")
+    rows = q.shape[0]
+    chunks = n_kv_heads * -(-(n_heads // n_kv_heads) // 16)
+    if q.dtype != torch.bfloat16 or head_dim % 16 or head_dim > 128 or n_heads % n_kv_heads or page_size & (page_size - 1) \
+            or q.stride(0) % 8 or q.data_ptr() % 16:
+        raise Unsupported("decode attention (planned): bfloat16, head_dim up to 128, 16-byte aligned q rows")
+    if q.dtype != out.dtype or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        raise InvalidArgument("decode attention: q, out and the cache must share one dtype")
+    if tuple(k_cache.shape[1:]) != (page_size, n_kv_heads, head_dim) or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+        raise InvalidArgument("decode attention: cache shape is not [pages, page_size, kv_heads, head_dim]")
+    if scratch.dtype != torch.float32 or scratch.numel() < rows * n_heads * part_stride * (head_dim + 2) \
+            or counters.dtype != torch.int32 or counters.numel() < rows * chunks or plan.dtype != torch.int32 \
+            or plan.numel() < 4 + 4 * unit_cap or plan.data_ptr() % 16:
+        raise InvalidArgument("decode attention (planned): scratch, counters or plan too small or of the wrong type")
+    check_limits("attention_decode", pages=k_cache.shape[0], requests=block_table.shape[0], rows=rows)
+    ahead, ahead_bytes = _take_ahead()
+    _check(_fn("attention_decode", "dl_paged_attention_decode_planned")(
+        _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), block_table.stride(0), _p(positions),
+        _p(row_request), _p(out), out.stride(0), _p(scratch), rows, n_heads, n_kv_heads, head_dim, page_size, scale,
+        window, _p(plan), _p(counters), unit_cap, part_stride, ahead, ahead_bytes, _stream()),
+        "paged_attention_decode_planned")
 
 
 QKV_ROPE_TCGEN05_HEAD_DIMS = (64, 128)

@@ -62,8 +62,8 @@ class PagedAttention:
     def step_plans(self) -> list:
         """What this mixer wants worked out once per step on the host and sent with the step's integers: the query
         tiles of its prompt kernels (kernels/attention.py)."""
-        from ..kernels.attention import QUERY_TILES
-        return [QUERY_TILES]
+        from ..kernels.attention import QUERY_TILES, decode_units_plan
+        return [QUERY_TILES, decode_units_plan(self.spec)]
 
     def first_weights(self) -> torch.Tensor:
         """The weights this part streams first (a block may say so to the kernel in front, kernels/ops.stream_ahead)."""
@@ -131,6 +131,8 @@ class PagedAttention:
 
     def graph_key(self, ctx) -> tuple:
         from ..kernels import attention as fast
+        if fast.DECODE_PLANNED and fast.decode_uses_tensor_cores(self.spec) and fast.decode_units_plan(self.spec).name in ctx.extras:
+            return ()         # the grid of the planned decode kernel depends on the number of rows alone
         return (("attn_splits", fast.decode_plan(ctx, self.spec)),)
 
     def attend(self, qkv: torch.Tensor, cache, ctx, out: torch.Tensor) -> None:

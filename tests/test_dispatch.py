@@ -72,3 +72,35 @@ def test_check_records_are_decoded():
     src = open(os.path.join(os.path.dirname(ops.__file__), "..", "csrc", "check.cuh")).read()
     import re
     assert sorted(int(m) for m in re.findall(r"#define DL_CK_\w+ (\d+)", src)) == sorted(ops.CHECK_CODES)
+
+
+def test_decode_units_deal_keys_evenly():
+    """The plan of the split-KV decode attention: units of about equal size, never more than the grid holds, every row
+    at least one part, short rows not cut below a tile per warp."""
+    from dynalm_b200.kernels.attention import PART_CAP, DecodeUnits
+    from dynalm_b200.engine.step import StepShape
+    import numpy as np
+    plan = DecodeUnits(chunks=8, tile_keys=32, window=0)
+    slots = plan.slots()
+    assert plan.parts([2048] * 8) in ([5, 5, 5, 5, 5, 4, 4, 4],) and sum(plan.parts([2048] * 8)) * 8 <= slots
+    assert plan.parts([2048]) == [16]                      # one row: as many parts as leave a tile per warp
+    assert plan.parts([100]) == [1] and plan.parts([1]) == [1]
+    assert plan.parts([2048] * 64) == [1] * 64             # more rows than a round of blocks: no cutting
+    uneven = plan.parts([8000, 100, 100, 100])
+    assert uneven[0] > 10 and uneven[1:] == [1, 1, 1]      # the long row gets the units
+    assert max(plan.parts([100000] * 2)) <= PART_CAP
+    rng = np.random.RandomState(0)
+    for _ in range(200):
+        rows = int(rng.randint(1, 65))
+        counts = [int(n) for n in rng.randint(1, 9000, rows)]
+        parts = plan.parts(counts)
+        assert len(parts) == rows and min(parts) >= 1 and sum(parts) * 8 <= plan.unit_cap(rows)
+        host = np.zeros(plan.ints(0, 64), dtype=np.int32)
+        shape = StepShape([1] * rows, list(range(rows)), [n - 1 for n in counts], list(range(rows)), rows)
+        units, got_rows = plan.fill(host, shape)
+        assert got_rows == rows and units == sum(parts) * 8 == host[0]
+        listed = host[4:4 + 4 * units].reshape(-1, 4)
+        assert sorted(map(tuple, listed)) == sorted((r, c, p, parts[r]) for r in range(rows) for c in range(8) for p in range(parts[r]))
+    windowed = DecodeUnits(chunks=2, tile_keys=16, window=64)
+    assert windowed.parts([64, 64]) == windowed.parts([64, 64]) and windowed.fill(np.zeros(4000, dtype=np.int32),
+        StepShape([1, 1, 5], [0, 1, 2], [9999, 10, 0], [0, 1, 2], 7))[1] == 2

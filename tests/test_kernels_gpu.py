@@ -622,3 +622,53 @@ def test_gemm_argmax_matches_argmax_of_the_product(ops, rows, N, K):
     assert 37 not in got.cpu().tolist()         # of the two equal outputs the lower index
     if N > 40 and K <= 256:
         assert any(float(x[r, 0]) > 0.5 and int(got[r]) == 11 for r in range(rows)) or not any(float(x[r, 0]) > 0.5 for r in range(rows))
+
+
+@pytest.mark.parametrize("heads,kvh,hd,window", [(8, 2, 64, 0), (6, 2, 32, 0), (3, 1, 128, 0), (32, 8, 64, 0), (4, 4, 80, 37)])
+def test_planned_decode_attention(ops, heads, kvh, hd, window):
+    """The decode kernel with the keys dealt into units by the host, on requests of very different lengths (one long,
+    some of a few keys, one of a single key), twice in a row over the same counters and scratch: against float64."""
+    from dynalm_b200.engine.step import StepShape
+    from dynalm_b200.kernels.attention import PART_CAP, DecodeUnits
+    page = 16
+    g = torch.Generator(device="cpu").manual_seed(heads * 100 + hd)
+    chunks = kvh * -(-(heads // kvh) // 16)
+    plan = DecodeUnits(chunks, ops.decode_tile_keys(hd), window)
+    for lens in ([3000, 1, 77, 640, 33, 129, 2048, 15], [500, 4100]):
+        rows = len(lens)
+        max_blocks = -(-max(lens) // page)
+        pages = sum(-(-l // page) for l in lens) + 3
+        perm = torch.randperm(pages, generator=g)
+        table = torch.full((rows, max_blocks), -1, dtype=torch.int32)
+        kc = torch.randn(pages, page, kvh, hd, generator=g).to(torch.bfloat16)
+        vc = torch.randn(pages, page, kvh, hd, generator=g).to(torch.bfloat16)
+        keys, vals, nxt = [], [], 0
+        for r, l in enumerate(lens):
+            mine = [int(p) for p in perm[nxt:nxt + -(-l // page)]]
+            nxt += len(mine)
+            table[r, :len(mine)] = torch.tensor(mine, dtype=torch.int32)
+            keys.append(kc[mine].reshape(-1, kvh, hd)[:l])
+            vals.append(vc[mine].reshape(-1, kvh, hd)[:l])
+        q = torch.randn(rows, heads * hd, generator=g).to(torch.bfloat16)
+        q[0, :hd] *= 4          # one far key of the long request stands out: a unit that is skipped shows
+        pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32)
+        req = torch.arange(rows, dtype=torch.int32)
+        host = np.zeros(plan.ints(0, rows), dtype=np.int32)
+        units, n_rows = plan.fill(host, StepShape([1] * rows, list(range(rows)), [l - 1 for l in lens], list(range(rows)), rows))
+        assert n_rows == rows and units <= plan.unit_cap(rows)
+        d = [t.to(DEV) for t in (q, kc, vc, table, pos, req)]
+        out = torch.zeros(rows, heads * hd, dtype=torch.bfloat16, device=DEV)
+        scratch = torch.full((rows * heads * PART_CAP * (hd + 2),), float("nan"), device=DEV)
+        counters = torch.zeros(rows * chunks, dtype=torch.int32, device=DEV)
+        plan_dev = torch.from_numpy(host).to(DEV)
+        scale = hd ** -0.5
+        for again in range(2):
+            out.zero_()
+            ops.paged_attention_decode_planned(d[0], d[1], d[2], d[3], d[4], d[5], out, scratch, counters, plan_dev,
+                                               plan.unit_cap(rows), PART_CAP, heads, kvh, hd, page, scale, window)
+            got = out.float().cpu().view(rows, heads, hd)
+            assert int(counters.abs().sum()) == 0
+            for i in range(rows):
+                ref = _attention_ref(q[i].view(heads, hd).double(), keys[i].double(), vals[i].double(), scale, window)
+                err = (got[i] - ref).abs().max().item()
+                assert err <= 2.5e-2, f"lens {lens} row {i} pass {again}: {err}"
