@@ -62,8 +62,11 @@ class PagedAttention:
     def step_plans(self) -> list:
         """What this mixer wants worked out once per step on the host and sent with the step's integers: the query
         tiles of its prompt kernels (kernels/attention.py)."""
-        from ..kernels.attention import QUERY_TILES, decode_units_plan
-        return [QUERY_TILES, decode_units_plan(self.spec)]
+        from ..kernels import attention as fast
+        plans = [fast.QUERY_TILES]
+        if fast.DECODE_PLANNED and fast.decode_uses_tensor_cores(self.spec):
+            plans.append(fast.decode_units_plan(self.spec))
+        return plans
 
     def first_weights(self) -> torch.Tensor:
         """The weights this part streams first (a block may say so to the kernel in front, kernels/ops.stream_ahead)."""
