@@ -65,6 +65,7 @@ class PageGroup:
         self.members: List[int] = []                      # run-order entries
         self.arrays: Dict[int, List[torch.Tensor]] = {}   # entry -> tensors [pages, page_size, *entry_shape]
         self.tables: Dict[Hashable, _Table] = {}
+        self.storage: Optional[torch.Tensor] = None
 
     def first_needed_block(self, next_pos: int) -> int:
         """The lowest block a query at `next_pos` (or later) can still read."""
@@ -135,10 +136,6 @@ class CacheManager:
                     self.groups.append(g)
                 g.members.append(entry)
                 self.entry_group[entry] = g
-                if self.device is not None:
-                    dt = _torch_dtype(spec.dtype, dtype)
-                    g.arrays[entry] = [torch.zeros((self.num_pages, self.page_size) + tuple(spec.entry_shape),
-                                                   dtype=dt, device=self.device) for _ in range(spec.tensors)]
             elif spec.kind == "state":
                 self.state_specs[entry] = spec
                 if self.device is not None:
@@ -147,6 +144,16 @@ class CacheManager:
                                                            dtype=dt, device=self.device)
             else:
                 raise InvalidArgument(f"cache spec of kind '{spec.kind}' is not known (pages, state)")
+        if self.device is not None:
+            # one allocation per group, [member entries, tensors, pages, page_size, *entry_shape]: every entry's arrays
+            # are views of it, and one kernel can clear a page in all of them at once (see take_fresh_pages)
+            for g in self.groups:
+                dt = _torch_dtype(g.spec.dtype, dtype)
+                g.storage = torch.zeros((len(g.members), g.spec.tensors, self.num_pages, self.page_size) + tuple(g.spec.entry_shape),
+                                        dtype=dt, device=self.device)
+                for i, entry in enumerate(g.members):
+                    g.arrays[entry] = [g.storage[i, t] for t in range(g.spec.tensors)]
+        self._fresh: List[tuple] = []              # (group id, page) handed out since take_fresh_pages
         self._free_slots: List[int] = list(range(self.max_requests - 1, -1, -1))
         self.slots: Dict[Hashable, int] = {}
         self.tokens: Dict[Hashable, int] = {}     # tokens reserved so far per request
@@ -221,6 +228,7 @@ class CacheManager:
             t.set(b, page)
             t.length = max(t.length, b + 1)
             self._dirty.add((g.gid, req))
+            self._fresh.append((g.gid, page))
         for g, t, b, shared, private in copies:
             g.copy_page(shared, private)
             t.set(b, private)
@@ -317,6 +325,14 @@ class CacheManager:
 
     def table_row(self, group: PageGroup, req) -> np.ndarray:
         return group.tables[req].pages
+
+    def take_fresh_pages(self) -> List[tuple]:
+        """(group id, page) of every page handed out since the last call. A page keeps what its previous owner wrote;
+        the step function clears these before the step that first writes into them, so that the slots of a request's
+        last page beyond its newest token never hold another request's values (a kernel that copies whole pages
+        multiplies them by a probability of zero, and zero times a stray infinity is not zero)."""
+        out, self._fresh = self._fresh, []
+        return out
 
     def take_table_updates(self) -> List[tuple]:
         """What has changed in the block tables since the last call, as (group id, slot, block, page): the device

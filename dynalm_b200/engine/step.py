@@ -82,6 +82,8 @@ class _StepBuffers:
         # changed table entries of one step: new pages of the tokens it brings, pages windows gave back, a few copies
         self.max_updates = max(1, n_groups) * (max_tokens // max(1, page_size) + 4 * max_requests) + 64
         take("table_updates", 4 * self.max_updates)
+        self.max_fresh = self.max_updates
+        take("fresh_pages", 2 * self.max_fresh)
         self.size = off
         self.device = torch.device(device)
         on_gpu = self.device.type == "cuda"
@@ -195,6 +197,17 @@ class BatchBuilder:
             h[sec][:4 * len(ups)] = np.asarray(ups, dtype=np.int32).reshape(-1)
         return len(ups)
 
+    def _clear(self, b: _StepBuffers, h, slot: int, fresh, upload: bool) -> None:
+        """Pages that were just handed out are set to zero in every array of their group, before the step writes."""
+        from ..kernels import ops
+        if upload:
+            h[b.off["fresh_pages"]][:2 * len(fresh)] = np.asarray(fresh, dtype=np.int32).reshape(-1)
+            b.upload(slot, "fresh_pages")
+        for gid in sorted({g for g, _ in fresh}):
+            ops.zero_pages(self.cache.groups[gid].storage, b.views["fresh_pages"], len(fresh), gid)
+        if upload and b.events[slot] is not None:
+            b.events[slot].synchronize()
+
     def _apply(self, b: _StepBuffers, n: int) -> None:
         from ..kernels import ops
         ops.table_updates(b.tables, b.views["table_updates"], n)
@@ -279,10 +292,18 @@ class BatchBuilder:
                 raise InvalidArgument("token feedback needs one token per entry and one source per entry")
             h[off["feedback_src"]][:len(entries)] = feedback_src
         n_updates = self._table_updates(b, h, i)
+        fresh = self.cache.take_fresh_pages()
+        while len(fresh) > b.max_fresh:             # (more than a step's section holds: in rounds of their own)
+            head, fresh = fresh[:b.max_fresh], fresh[b.max_fresh:]
+            self._clear(b, h, i, head, upload=True)
+        if fresh:
+            h[off["fresh_pages"]][:2 * len(fresh)] = np.asarray(fresh, dtype=np.int32).reshape(-1)
         b.upload(i)
         self.last_upload_bytes = b.size * 4
         if n_updates:
             self._apply(b, n_updates)
+        if fresh:
+            self._clear(b, h, i, fresh, upload=False)
         d = b.views
         extras["step:feedback_src"] = d["feedback_src"]
         return StepContext(

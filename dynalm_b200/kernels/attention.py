@@ -58,12 +58,16 @@ QUERY_TILES = QueryTilePlan()
 
 PART_CAP = 32            # most parts a row's keys are cut into
 DECODE_BLOCKS_PER_SM = int(os.environ.get("DYNALM_DECODE_BLOCKS", "2"))     # blocks of the decode kernel that fit an SM
-# 1: the keys of a step's rows are dealt into units by the host (DecodeUnits below); 0 (default): every row is cut
-# into the same number of parts. Measured on B200 (1B shapes, 2,048 tokens of context, decode step): batch 8 0.925 ms
-# planned against 0.900 ms, batch 1 1,148 against 1,335 tokens/s (there the parts merge inside a thread-block cluster),
-# batch 64 equal: the kernel is bound by the latency of a warp's chain of tiles, not by how evenly the blocks are
-# loaded, and the planned units are more and shorter. It stays for steps whose requests differ much in length.
-DECODE_PLANNED = os.environ.get("DYNALM_DECODE_PLANNED", "0") != "0"
+# Whether the keys of a step's single-token rows are dealt into units by the host (DecodeUnits below) instead of every
+# row being cut into the same number of parts: 1 always, 0 never, auto (default) from PLANNED_MIN_ROWS rows on. Measured
+# on B200: with equal contexts (1B shapes, 2,048 tokens) batch 8 takes 0.925 ms per step planned against 0.900 ms, batch
+# 1 gives 1,148 against 1,335 tokens/s (there the parts merge inside a thread-block cluster), batch 64 is equal: with few
+# rows the kernel is bound by the latency of a warp's chain of tiles, not by how evenly the blocks are loaded. With
+# contexts that differ (continuous batching of the 3B shape, 32 requests of 128 to 4,096 prompt tokens) the decode-only
+# step takes 3.63 ms planned against 3.79 ms, the whole run 4,081 against 4,009 tokens/s.
+_planned = os.environ.get("DYNALM_DECODE_PLANNED", "auto")
+DECODE_PLANNED = _planned != "0"
+PLANNED_MIN_ROWS = 1 if _planned == "1" else 12
 
 
 class DecodeUnits:
@@ -114,6 +118,8 @@ class DecodeUnits:
         rows = 0
         while rows < len(shape.q_len) and shape.q_len[rows] == 1:
             rows += 1
+        if rows < PLANNED_MIN_ROWS:
+            return 0, rows            # few rows: the kernel cuts every row alike (see DECODE_PLANNED)
         counts = [(min(p + 1, self.window) if self.window > 0 else p + 1) for p in shape.pos_start[:rows]]
         parts = self.parts(counts) if rows else []
         flat = [0, 0, 0, 0]
@@ -206,7 +212,7 @@ def _decode_rows(qkv: torch.Tensor, cache, ctx, out: torch.Tensor, spec, runtime
     k_cache, v_cache = cache.arrays
     planned = ctx.extras.get(decode_units_plan(spec).name) if (DECODE_PLANNED and decode_uses_tensor_cores(spec)
                                                               and qkv.stride(0) % 8 == 0) else None
-    if planned is not None and planned[1][1] == rows:
+    if planned is not None and planned[1][1] == rows and planned[1][0] > 0:
         plan = decode_units_plan(spec)
         most_rows = max(runtime.max_requests, rows)
         scratch = runtime.flat(f"attn_split_scratch_{spec.num_heads}x{spec.head_dim}",

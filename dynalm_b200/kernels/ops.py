@@ -61,7 +61,8 @@ _SIGNATURES = {
         "dl_feedback_tokens": [_P, _P, _P, _I, _P],
     },
     "streams": {"dl_stream_fork": [_P, _P], "dl_stream_join": [_P, _P]},
-    "table_update": {"dl_table_updates": [_P, _P, _I, _I, _I, _I, _P]},
+    "table_update": {"dl_table_updates": [_P, _P, _I, _I, _I, _I, _P],
+                     "dl_zero_pages": [_P, _L, _I, _I, _P, _I, _I, _P]},
 }
 
 _funcs = {}
@@ -872,6 +873,18 @@ def clear_status(device) -> None:
     t = _tcgen05_status.get(torch.device(device))
     if t is not None:
         t.zero_()
+
+
+def zero_pages(storage: torch.Tensor, fresh: torch.Tensor, n: int, group: int) -> None:
+    """Clear the pages listed for `group` in the first n pairs (group id, page) of `fresh` (int32) in every array of a
+    cache group's storage [entries, tensors, pages, page_size, ...] (csrc/table_update.cu)."""
+    _cuda(storage, fresh)
+    if not storage.is_contiguous() or storage.dim() < 4 or fresh.dtype != torch.int32 or fresh.numel() < 2 * n:
+        raise InvalidArgument("zero_pages: contiguous storage [entries, tensors, pages, ...] and int32 pairs")
+    pages = storage.shape[2]
+    page_bytes = storage[0, 0, 0].numel() * storage.element_size()
+    _check(_fn("table_update", "dl_zero_pages")(_p(storage), page_bytes, pages, storage.shape[0] * storage.shape[1], _p(fresh),
+                                                 n, group, _stream()), "zero_pages")
 
 
 def table_updates(tables: torch.Tensor, updates: torch.Tensor, n: int) -> None:

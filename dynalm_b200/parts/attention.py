@@ -134,8 +134,10 @@ class PagedAttention:
 
     def graph_key(self, ctx) -> tuple:
         from ..kernels import attention as fast
-        if fast.DECODE_PLANNED and fast.decode_uses_tensor_cores(self.spec) and fast.decode_units_plan(self.spec).name in ctx.extras:
-            return ()         # the grid of the planned decode kernel depends on the number of rows alone
+        if fast.DECODE_PLANNED and fast.decode_uses_tensor_cores(self.spec):
+            planned = ctx.extras.get(fast.decode_units_plan(self.spec).name)
+            if planned is not None and planned[1][0] > 0:
+                return ()         # the grid of the planned decode kernel depends on the number of rows alone
         return (("attn_splits", fast.decode_plan(ctx, self.spec)),)
 
     def attend(self, qkv: torch.Tensor, cache, ctx, out: torch.Tensor) -> None:

@@ -60,9 +60,6 @@ class RotaryEncoding:
             ctx.extras[key] = got
         return got
 
-    def apply(self, q, k, positions) -> None:  # the fused kernel does it
-        raise NotImplementedError
-
 
 @register_position("none")
 class NoPosition:

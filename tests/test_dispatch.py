@@ -77,10 +77,14 @@ def test_check_records_are_decoded():
 def test_decode_units_deal_keys_evenly():
     """The plan of the split-KV decode attention: units of about equal size, never more than the grid holds, every row
     at least one part, short rows not cut below a tile per warp."""
+    from dynalm_b200.kernels import attention as fast
     from dynalm_b200.kernels.attention import PART_CAP, DecodeUnits
     from dynalm_b200.engine.step import StepShape
     import numpy as np
     plan = DecodeUnits(chunks=8, tile_keys=32, window=0)
+    few = plan.fill(np.zeros(plan.ints(0, 64), dtype=np.int32), StepShape([1] * 4, [0, 1, 2, 3], [99] * 4, [0, 1, 2, 3], 4))
+    assert few == (0, 4)                                   # below a dozen rows the engine does not plan
+    fast.PLANNED_MIN_ROWS, before = 1, fast.PLANNED_MIN_ROWS
     slots = plan.slots()
     assert plan.parts([2048] * 8) in ([5, 5, 5, 5, 5, 4, 4, 4],) and sum(plan.parts([2048] * 8)) * 8 <= slots
     assert plan.parts([2048]) == [16]                      # one row: as many parts as leave a tile per warp
@@ -104,3 +108,4 @@ def test_decode_units_deal_keys_evenly():
     windowed = DecodeUnits(chunks=2, tile_keys=16, window=64)
     assert windowed.parts([64, 64]) == windowed.parts([64, 64]) and windowed.fill(np.zeros(4000, dtype=np.int32),
         StepShape([1, 1, 5], [0, 1, 2], [9999, 10, 0], [0, 1, 2], 7))[1] == 2
+    fast.PLANNED_MIN_ROWS = before

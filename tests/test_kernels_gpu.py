@@ -625,11 +625,13 @@ def test_gemm_argmax_matches_argmax_of_the_product(ops, rows, N, K):
 
 
 @pytest.mark.parametrize("heads,kvh,hd,window", [(8, 2, 64, 0), (6, 2, 32, 0), (3, 1, 128, 0), (32, 8, 64, 0), (4, 4, 80, 37)])
-def test_planned_decode_attention(ops, heads, kvh, hd, window):
+def test_planned_decode_attention(ops, heads, kvh, hd, window, monkeypatch):
     """The decode kernel with the keys dealt into units by the host, on requests of very different lengths (one long,
     some of a few keys, one of a single key), twice in a row over the same counters and scratch: against float64."""
     from dynalm_b200.engine.step import StepShape
+    from dynalm_b200.kernels import attention as fast
     from dynalm_b200.kernels.attention import PART_CAP, DecodeUnits
+    monkeypatch.setattr(fast, "PLANNED_MIN_ROWS", 1)        # (the engine plans from a dozen rows on; the kernel takes any)
     page = 16
     g = torch.Generator(device="cpu").manual_seed(heads * 100 + hd)
     chunks = kvh * -(-(heads // kvh) // 16)

@@ -241,3 +241,28 @@ def test_layers_issued_by_address_give_the_same_bits(name, dtype, folders, plain
         assert got[True].keys() == got[False].keys()
         for step in got[True]:
             assert np.array_equal(got[True][step], got[False][step]), f"{name}/{dtype}/{what}: step {step} differs"
+
+
+def test_pages_of_an_ended_request_are_cleared_before_reuse(tiny_folders_bf16):
+    """A request ends and its pages are filled with NaN (as an overflow, or a step that gave up, could leave them);
+    the next request gets those pages and its prompt ends in the middle of one. The prompt kernel that copies whole
+    pages (head size 64) would multiply the stale slots by probabilities of zero: the logits must be finite and those
+    of the plain implementation. The engine clears every page it hands out."""
+    from dynalm_b200.engine import StepEntry, build
+    name = "e"
+    cfg = TINY[name][0]
+    plain = PlainLlama(tiny_folders_bf16[name])
+    built = build(tiny_folders_bf16[name], dtype="bfloat16", kv_tokens=192, max_batch_tokens=192, max_requests=2, context=256)
+    first = random_requests(cfg["vocab_size"], [180], seed=50)["r0"]
+    built.step_fn.step([StepEntry("a", first, [179])])
+    built.step_fn.end("a")
+    for g in built.cache.groups:
+        g.storage.fill_(float("nan"))
+    second = random_requests(cfg["vocab_size"], [150], seed=51)["r0"]
+    got = built.step_fn.step([StepEntry("b", second[:137], [136])]).float().cpu().numpy()
+    more = built.step_fn.step([StepEntry("b", second[137:], list(range(13)))]).float().cpu().numpy()
+    want = plain.logits(second)
+    assert np.isfinite(got).all() and np.isfinite(more).all()
+    assert np.abs(got[0] - want[136]).max() <= TOL["bfloat16"][0]
+    assert np.abs(more - want[137:]).max() <= TOL["bfloat16"][0]
+    built.step_fn.end("b")
