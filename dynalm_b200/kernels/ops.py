@@ -240,7 +240,9 @@ def _take_ahead():
 
 class KernelTimes:
     """Inside the block every kernel launch of this module stands between two CUDA events on its stream;
-    `totals()` then gives {C entry point: (launches, milliseconds)}. The counterpart of the reference's per-op marks
+    `totals()` then gives {C entry point: (launches, milliseconds)}. A kernel launched to start beside the end of
+    the one in front of it (programmatic dependent launch, on by default for the products and the attention) lets the
+    event behind it pass early: run with DYNALM_PDL=0 for times that are each kernel's own. The counterpart of the reference's per-op marks
     in its forward pass (`ForwardProfile`, dynalm/src/model/transformer.h:34-49): off unless asked for, and meant
     for steps that run launch by launch (engine/profile.py sees to that)."""
 
@@ -258,7 +260,10 @@ class KernelTimes:
 
     def timed(self, name: str, f):
         def call(*args):
-            stream = torch.cuda.ExternalStream(_stream())
+            # the stream the launch goes to, as a torch stream: torch's own current stream where that is it (an external
+            # handle of the default stream is not the same stream to torch, and events recorded there wait for nothing)
+            current = torch.cuda.current_stream()
+            stream = current if current.cuda_stream == _stream() else torch.cuda.ExternalStream(_stream())
             begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             begin.record(stream)
             code = f(*args)
