@@ -574,3 +574,27 @@ def test_kernel_times_of_a_step(tiny_folders):
     assert totals["dl_rmsnorm"][0] == 2 * layers + 1 and totals["dl_embed"][0] == 1
     assert all(ms > 0.0 for _, ms in totals.values())
     assert "dl_rmsnorm" in profile.table(totals)
+
+
+def test_kernel_times_measure_the_kernels():
+    from dynalm_b200.kernels import ops
+    """The events of `KernelTimes` stand on the stream the kernels run on: four launches of a product that takes a
+    tenth of a millisecond are reported as about four times that, not as the few microseconds of their launches."""
+    x = torch.randn(2048, 2048, device=DEV).to(torch.bfloat16)
+    w = torch.randn(8192, 2048, device=DEV).to(torch.bfloat16)
+    out = torch.empty(2048, 8192, dtype=torch.bfloat16, device=DEV)
+    for _ in range(3):
+        ops.gemm_tcgen05(x, w, out)
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(4):
+        ops.gemm_tcgen05(x, w, out)
+    end.record()
+    torch.cuda.synchronize()
+    whole = begin.elapsed_time(end)
+    with ops.KernelTimes() as times:
+        for _ in range(4):
+            ops.gemm_tcgen05(x, w, out)
+    launches, ms = next(iter(times.totals().values()))
+    assert launches == 4 and 0.5 * whole <= ms <= 3.0 * whole, (ms, whole)
