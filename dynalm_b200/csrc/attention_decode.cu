@@ -291,14 +291,13 @@ int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, c
 // The tensor-core variant (bf16): the same split-KV scheme, but the group's query heads form the
 // rows of an m16n8k16 tile, and each warp streams its own key tiles through a private multi-stage
 // cp.async pipeline in shared memory, so that many kilobytes stay in flight per warp whatever the
-// register budget. Warp w of a block takes key tiles w, w + 4, ... of the block's key range; tiles are
-// 32 keys. Scores, softmax and the merge are fp32; P is rounded to bf16 for the P V product.
+// register budget. Warp w of a block's W warps takes key tiles w, w + W, ... of the block's key range; tiles are
+// KT keys. Scores, softmax and the merge are fp32; P is rounded to bf16 for the P V product.
+// A warp's tiles are a chain of dependent work (copy, Q K^T, softmax, P V), so a block's time is the length of
+// that chain: eight warps with tiles of 16 keys halve it against four warps with tiles of 32 at the same shared
+// memory. Groups of up to 8 query heads (every Llama shape) use rows 0 to 7 of the 16-row tile only, and the
+// softmax and rescaling of rows 8 to 15 are left out.
 // ------------------------------------------------------------------------------------------------
-
-constexpr int DT_WARPS = 4;
-constexpr int DT_THREADS = DT_WARPS * 32;
-// Keys per tile of a warp (KT): 32, or 16 for the large head sizes, where 32 would leave room for only one block
-// per SM (shared memory) and too few warps to cover the latency of the key and value stream.
 
 __device__ __forceinline__ void dt_cp_async16(void* smem, const void* gmem, bool valid) {
   const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
@@ -330,8 +329,8 @@ __device__ __forceinline__ uint32_t dt_pack(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&p);
 }
 
-template <int HD, int STAGES, int KT>
-__global__ void __launch_bounds__(DT_THREADS)
+template <int HD, int STAGES, int KT, int W>
+__global__ void __launch_bounds__(W * 32)
 decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k_cache,
                            const bf16* __restrict__ v_cache, const int* __restrict__ block_table, int max_blocks,
                            const int* __restrict__ positions, const int* __restrict__ row_request,
@@ -344,6 +343,7 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
   constexpr int CH = HD / 8;
   constexpr int KS = HD / 16;
   constexpr int TILE_ELEMS = KT * LD;                 // one of K or V of one stage
+  constexpr int DT_WARPS = W, DT_THREADS = W * 32;
   extern __shared__ __align__(16) unsigned char dt_smem[];
   bf16* Qs = reinterpret_cast<bf16*>(dt_smem);           // [16][LD]
   bf16* KV = Qs + 16 * LD;                               // [warp][stage][K | V][KT][LD]
@@ -366,6 +366,7 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
   const int chunks = (group + 15) / 16;
   const int kvh = ychunk / chunks, h0 = (ychunk % chunks) * 16;
   const int ng = min(16, group - h0);
+  const bool wide = ng > 8;                           // rows 8 to 15 of the tile hold query heads too
   const int head0 = kvh * group + h0;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
@@ -506,46 +507,61 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
     }
     // raw scores stay in s; the maximum is kept in scaled (base-2) units and the scale is folded into the exponent
     const bool edge = key0 + KT > k_end;
-    float mx[2] = {-INFINITY, -INFINITY};
+    if (edge) {
 #pragma unroll
-    for (int j = 0; j < KT / 8; ++j) {
+      for (int j = 0; j < KT / 8; ++j) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        if (edge && key0 + j * 8 + 2 * t + (e & 1) >= k_end) s[j][e] = -INFINITY;
-        mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
+        for (int e = 0; e < 4; ++e)
+          if (key0 + j * 8 + 2 * t + (e & 1) >= k_end) s[j][e] = -INFINITY;
       }
     }
-    float corr[2], neg_m[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
-      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-      const float m_new = fmaxf(m_run[h], mx[h] * scale_log2);       // finite: the first key of every tile is in range
-      corr[h] = dt_exp2(m_run[h] - m_new);
-      m_run[h] = m_new;
-      neg_m[h] = -m_new;
-    }
-    float ls[2] = {0.0f, 0.0f};
     uint32_t pf[KT / 16][4];
+    {                                                  // rows 0 to 7
+      float mx = -INFINITY;
 #pragma unroll
-    for (int j = 0; j < KT / 8; ++j) {
-      const float p0 = dt_exp2(fmaf(s[j][0], scale_log2, neg_m[0])), p1 = dt_exp2(fmaf(s[j][1], scale_log2, neg_m[0]));
-      const float p2 = dt_exp2(fmaf(s[j][2], scale_log2, neg_m[1])), p3 = dt_exp2(fmaf(s[j][3], scale_log2, neg_m[1]));
-      ls[0] += p0 + p1;
-      ls[1] += p2 + p3;
-      pf[j >> 1][(j & 1) * 2] = dt_pack(p0, p1);
-      pf[j >> 1][(j & 1) * 2 + 1] = dt_pack(p2, p3);
+      for (int j = 0; j < KT / 8; ++j) mx = fmaxf(mx, fmaxf(s[j][0], s[j][1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run[0], mx * scale_log2);          // finite: the first key of every tile is in range
+      const float corr = dt_exp2(m_run[0] - m_new);
+      m_run[0] = m_new;
+      float ls = 0.0f;
+#pragma unroll
+      for (int j = 0; j < KT / 8; ++j) {
+        const float p0 = dt_exp2(fmaf(s[j][0], scale_log2, -m_new)), p1 = dt_exp2(fmaf(s[j][1], scale_log2, -m_new));
+        ls += p0 + p1;
+        pf[j >> 1][(j & 1) * 2] = dt_pack(p0, p1);
+      }
+      ls += __shfl_xor_sync(0xffffffffu, ls, 1);
+      ls += __shfl_xor_sync(0xffffffffu, ls, 2);
+      l_run[0] = l_run[0] * corr + ls;
+#pragma unroll
+      for (int j = 0; j < HD / 8; ++j) { o[j][0] *= corr; o[j][1] *= corr; }
     }
+    if (wide) {                                        // rows 8 to 15
+      float mx = -INFINITY;
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      ls[h] += __shfl_xor_sync(0xffffffffu, ls[h], 1);
-      ls[h] += __shfl_xor_sync(0xffffffffu, ls[h], 2);
-      l_run[h] = l_run[h] * corr[h] + ls[h];
-    }
+      for (int j = 0; j < KT / 8; ++j) mx = fmaxf(mx, fmaxf(s[j][2], s[j][3]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run[1], mx * scale_log2);
+      const float corr = dt_exp2(m_run[1] - m_new);
+      m_run[1] = m_new;
+      float ls = 0.0f;
 #pragma unroll
-    for (int j = 0; j < HD / 8; ++j) {
-      o[j][0] *= corr[0]; o[j][1] *= corr[0];
-      o[j][2] *= corr[1]; o[j][3] *= corr[1];
+      for (int j = 0; j < KT / 8; ++j) {
+        const float p2 = dt_exp2(fmaf(s[j][2], scale_log2, -m_new)), p3 = dt_exp2(fmaf(s[j][3], scale_log2, -m_new));
+        ls += p2 + p3;
+        pf[j >> 1][(j & 1) * 2 + 1] = dt_pack(p2, p3);
+      }
+      ls += __shfl_xor_sync(0xffffffffu, ls, 1);
+      ls += __shfl_xor_sync(0xffffffffu, ls, 2);
+      l_run[1] = l_run[1] * corr + ls;
+#pragma unroll
+      for (int j = 0; j < HD / 8; ++j) { o[j][2] *= corr; o[j][3] *= corr; }
+    } else {                                           // no query heads there: P is zero, O stays zero
+#pragma unroll
+      for (int j = 0; j < KT / 8; ++j) pf[j >> 1][(j & 1) * 2 + 1] = 0u;
     }
 #pragma unroll
     for (int kk = 0; kk < KT / 16; ++kk) {
@@ -670,14 +686,14 @@ decode_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, const bf16*
   }
 }
 
-template <int HD, int STAGES, int KT>
+template <int HD, int STAGES, int KT, int W>
 int launch_decode_tc(const void* q, int q_stride, const void* kc, const void* vc, const int* block_table, int max_blocks,
                      const int* positions, const int* row_request, void* out, int out_stride, float* part, int rows,
                      int n_heads, int n_kv_heads, int page_shift, float scale, int window, int n_split,
                      const void* ahead, long long ahead_bytes, cudaStream_t stream, const int* plan = nullptr,
                      int* counters = nullptr, int unit_cap = 0, int part_stride = 0) {
-  constexpr size_t pipe = static_cast<size_t>(16 + DT_WARPS * STAGES * 2 * KT) * (HD + 8) * sizeof(bf16);
-  constexpr size_t mrg = static_cast<size_t>(DT_WARPS) * 16 * (HD + 2) * sizeof(float);
+  constexpr size_t pipe = static_cast<size_t>(16 + W * STAGES * 2 * KT) * (HD + 8) * sizeof(bf16);
+  constexpr size_t mrg = static_cast<size_t>(W) * 16 * (HD + 2) * sizeof(float);
   constexpr size_t base = ((pipe > mrg ? pipe : mrg) + 15) & ~static_cast<size_t>(15);
   // Up to 8 splits can merge through the shared memory of a cluster's first block. Measured on B200: that wins
   // for a handful of rows (batch 1: 1063 against 1010 tokens/s) and loses once the grid is a few dozen clusters
@@ -687,7 +703,7 @@ int launch_decode_tc(const void* q, int q_stride, const void* kc, const void* vc
   const size_t smem = base + (cluster ? static_cast<size_t>(n_split) * 16 * (HD + 2) * sizeof(float) : 0);
   static size_t configured = 0;
   if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(decode_attention_tc_kernel<HD, STAGES, KT>,
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_tc_kernel<HD, STAGES, KT, W>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = smem;
@@ -697,7 +713,7 @@ int launch_decode_tc(const void* q, int q_stride, const void* kc, const void* vc
   if (plan != nullptr) grid = dim3(unit_cap, 1, 1);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
-  cfg.blockDim = dim3(DT_THREADS);
+  cfg.blockDim = dim3(W * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -717,7 +733,7 @@ int launch_decode_tc(const void* q, int q_stride, const void* kc, const void* vc
   cfg.attrs = attr;
   cfg.numAttrs = n_attr;
   int rc = static_cast<int>(cudaLaunchKernelEx(
-      &cfg, decode_attention_tc_kernel<HD, STAGES, KT>, static_cast<const bf16*>(q), q_stride, static_cast<const bf16*>(kc),
+      &cfg, decode_attention_tc_kernel<HD, STAGES, KT, W>, static_cast<const bf16*>(q), q_stride, static_cast<const bf16*>(kc),
       static_cast<const bf16*>(vc), block_table, max_blocks, positions, row_request, static_cast<bf16*>(out), out_stride,
       part, n_heads, n_kv_heads, page_shift, scale * 1.4426950408889634f, window, n_split, cluster ? 1 : 0,
       static_cast<int>(base), pdl_mode() >= 1 ? ahead : nullptr, pdl_mode() >= 1 ? ahead_bytes : 0ll, plan, counters,
@@ -756,6 +772,18 @@ DL_EXPORT int dl_paged_attention_decode(int dtype, const void* q, int q_stride, 
   return DL_ERR_UNSUPPORTED;
 }
 
+// Head size -> (stages, keys per tile, warps) of the tensor-core kernel. A block's pipeline is warps * stages *
+// 2 * keys * (head_dim + 8) * 2 bytes of shared memory: about 110 KB each, two blocks to an SM.
+#define DL_DECODE_TC_CASES                           \
+  DL_CASE(16, 4, 32, 4);                             \
+  DL_CASE(32, 4, 32, 4);                             \
+  DL_CASE(48, 3, 32, 4);                             \
+  DL_CASE(64, 3, 16, 8);                             \
+  DL_CASE(80, 3, 32, 4);                             \
+  DL_CASE(96, 3, 16, 4);                             \
+  DL_CASE(112, 3, 16, 4);                            \
+  DL_CASE(128, 3, 16, 4);
+
 // The tensor-core variant: bfloat16, head_dim a multiple of 16 up to 128, q rows 16-byte aligned. Same
 // arguments as dl_paged_attention_decode. Up to 8 splits are the blocks of a thread-block cluster and merge through
 // distributed shared memory (no scratch is touched); more splits use the scratch and the merge kernel.
@@ -773,20 +801,13 @@ DL_EXPORT int dl_paged_attention_decode_tc(const void* q, int q_stride, const vo
   if ((1 << page_shift) != page_size || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || n_split < 1 || rows > 65535 ||
       (q_stride & 7) || !(scale > 0.0f) || (n_split > 8 && part == nullptr))   // without scratch, up to 8 splits merge in a cluster
     return DL_ERR_UNSUPPORTED;
-#define DL_CASE(H, S, T)                                                                                               \
+#define DL_CASE(H, S, T, NW)                                                                                           \
   case H:                                                                                                             \
-    return dl::launch_decode_tc<H, S, T>(q, q_stride, k_cache, v_cache, block_table, max_blocks, positions, row_request, \
-                                      out, out_stride, part, rows, n_heads, n_kv_heads, page_shift, scale, window,    \
-                                      n_split, ahead, ahead_bytes, stream)
+    return dl::launch_decode_tc<H, S, T, NW>(q, q_stride, k_cache, v_cache, block_table, max_blocks, positions,        \
+                                          row_request, out, out_stride, part, rows, n_heads, n_kv_heads, page_shift,  \
+                                          scale, window, n_split, ahead, ahead_bytes, stream)
   switch (head_dim) {
-    DL_CASE(16, 4, 32);
-    DL_CASE(32, 4, 32);
-    DL_CASE(48, 3, 32);
-    DL_CASE(64, 3, 32);
-    DL_CASE(80, 3, 32);
-    DL_CASE(96, 3, 16);
-    DL_CASE(112, 3, 16);
-    DL_CASE(128, 3, 16);
+    DL_DECODE_TC_CASES
     default:
       return DL_ERR_UNSUPPORTED;
   }
@@ -814,20 +835,14 @@ DL_EXPORT int dl_paged_attention_decode_planned(const void* q, int q_stride, con
       (q_stride & 7) || !(scale > 0.0f) || plan == nullptr || counters == nullptr || part == nullptr ||
       (reinterpret_cast<uintptr_t>(plan) & 15))
     return DL_ERR_UNSUPPORTED;
-#define DL_CASE(H, S, T)                                                                                               \
+#define DL_CASE(H, S, T, NW)                                                                                           \
   case H:                                                                                                             \
-    return dl::launch_decode_tc<H, S, T>(q, q_stride, k_cache, v_cache, block_table, max_blocks, positions, row_request, \
-                                      out, out_stride, part, rows, n_heads, n_kv_heads, page_shift, scale, window,    \
-                                      2, ahead, ahead_bytes, stream, plan, counters, unit_cap, part_stride)
+    return dl::launch_decode_tc<H, S, T, NW>(q, q_stride, k_cache, v_cache, block_table, max_blocks, positions,        \
+                                          row_request, out, out_stride, part, rows, n_heads, n_kv_heads, page_shift,  \
+                                          scale, window, 2, ahead, ahead_bytes, stream, plan, counters, unit_cap,     \
+                                          part_stride)
   switch (head_dim) {
-    DL_CASE(16, 4, 32);
-    DL_CASE(32, 4, 32);
-    DL_CASE(48, 3, 32);
-    DL_CASE(64, 3, 32);
-    DL_CASE(80, 3, 32);
-    DL_CASE(96, 3, 16);
-    DL_CASE(112, 3, 16);
-    DL_CASE(128, 3, 16);
+    DL_DECODE_TC_CASES
     default:
       return DL_ERR_UNSUPPORTED;
   }
@@ -835,7 +850,17 @@ DL_EXPORT int dl_paged_attention_decode_planned(const void* q, int q_stride, con
 }
 
 // Keys per tile of the tensor-core kernel for a head size (what a plan counts the keys in).
-DL_EXPORT int dl_paged_attention_decode_tile(int head_dim) { return head_dim >= 96 ? 16 : 32; }
+DL_EXPORT int dl_paged_attention_decode_tile(int head_dim) {
+#define DL_CASE(H, S, T, NW) \
+  case H:                    \
+    return T
+  switch (head_dim) {
+    DL_DECODE_TC_CASES
+    default:
+      return 0;
+  }
+#undef DL_CASE
+}
 
 // ------------------------------------------------------------------------------------------------
 // The entry point that allocates nothing (see dynalm_noalloc.h for who needs it and its rules).

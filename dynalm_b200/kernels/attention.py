@@ -57,6 +57,7 @@ class QueryTilePlan:
 QUERY_TILES = QueryTilePlan()
 
 PART_CAP = 32            # most parts a row's keys are cut into
+PART_MIN_KEYS = 128      # fewest keys of a part
 DECODE_BLOCKS_PER_SM = int(os.environ.get("DYNALM_DECODE_BLOCKS", "2"))     # blocks of the decode kernel that fit an SM
 # Whether the keys of a step's single-token rows are dealt into units by the host (DecodeUnits below) instead of every
 # row being cut into the same number of parts: 1 always, 0 never, auto (default) from PLANNED_MIN_ROWS rows on. Measured
@@ -99,7 +100,7 @@ class DecodeUnits:
         budget = self.slots() // self.chunks               # parts over all rows that one round of blocks holds
         if rows >= budget:
             return [1] * rows
-        cap = [max(1, min(PART_CAP, t // 4)) for t in tiles]          # a part keeps a tile for each of a block's four warps
+        cap = [max(1, min(PART_CAP, n // PART_MIN_KEYS)) for n in key_counts]   # a part keeps a tile for each warp of a block
         total = sum(tiles)
         parts = [max(1, min(cap[r], budget * tiles[r] // total)) for r in range(rows)]
         left = budget - sum(parts)
@@ -155,8 +156,8 @@ def query_tiles(ctx):
 
 def decode_splits(rows: int, n_heads: int, n_kv_heads: int, max_kv_len: int, tensor_cores: bool = True,
                   sms: int = 0) -> int:
-    """Key splits per row so that the grid fills the GPU, each split at least 128 keys (one 32-key tile for each
-    of a block's four warps). The tensor-core kernel merges up to 8 splits inside a thread-block cluster, which
+    """Key splits per row so that the grid fills the GPU, each split at least 128 keys (one tile for each of a
+    block's warps: four of 32 keys or eight of 16). The tensor-core kernel merges up to 8 splits inside a thread-block cluster, which
     wins while a split is short; from 1,024 keys per split on, more splits (merged by a second kernel) win."""
     group = n_heads // n_kv_heads
     blocks = rows * n_kv_heads * (-(-group // (16 if tensor_cores else 4)))
