@@ -5,20 +5,25 @@
 // piece of a larger page) per copy, in tiles of BN keys whose boundaries are multiples of BN in absolute
 // position, so the arithmetic of a row does not depend on where its portion was cut.
 //
-//   S = Q K^T      tcgen05.mma, M 128, N BN, both operands K-major from shared memory, S in tensor memory
+//   S = Q K^T      tcgen05.mma, M 128, N BN = 64, both operands K-major from shared memory, S in tensor memory
 //   softmax        128 threads, one row each: S from tensor memory, mask by position, running maximum and
-//                  sum in fp32 with base-2 exponentials, P rounded to bf16 back into tensor memory
+//                  sum in fp32 with base-2 exponentials, P rounded to bf16 back into tensor memory, over the
+//                  first half of S's columns
 //   O += P V       tcgen05.mma, M 128, N head_dim, P from tensor memory, V read as it lies in the cache
 //                  (head dimension contiguous: an MN-major operand), O in tensor memory
 //
 // Roles: warps 0..3 softmax and the final store, warp 4 TMA producer, warp 5 issues the MMAs and owns the
-// tensor-memory allocation (both run their loops as whole warps; one elected lane issues). The MMA warp issues S of tile i+1 as soon as the softmax
-// warps have read S of tile i, so the tensor core works under the softmax. O is rescaled only when a row's
-// maximum has grown by more than 2^8 since the reference point of its exponentials was set; the result is
+// tensor-memory allocation (both run their loops as whole warps; one elected lane issues). O is rescaled only when
+// a row's maximum has grown by more than 2^8 since the reference point of its exponentials was set; the result is
 // the same function of the scores, with probabilities kept below 2^8.
 //
-// Two blocks fit an SM (112 KiB of shared memory: Q and three stages of K and V; 256 tensor-memory columns:
-// S, O and P).
+// S has two buffers in tensor memory, and P takes the place of the S it was made from. The MMA warp keeps S two
+// tiles ahead: behind P V of tile i it issues S of tile i + 2 into the columns that held P of tile i (the tensor
+// core runs one thread's MMAs in the order of issue, so P V has read them by then). The softmax threads thus never
+// wait for the tensor core in the steady state: a block's time per tile is the softmax's own (a tensor-memory
+// load, 64 maxima, 64 exponentials at a quarter of a warp's issue rate, a store), and two blocks keep an SM's
+// exponential unit busy. Tiles are 64 keys, so that S, S and O (64 + 64 + head_dim columns) leave room for two
+// blocks in an SM's tensor memory at both head sizes; shared memory holds Q and three stages of K and V.
 //
 // Every wait on an mbarrier is bounded (tcgen05.cuh); on a timeout all roles fall through to the common
 // exit, where tensor memory is freed, and *status tells the host.
@@ -34,17 +39,17 @@ namespace dl {
 constexpr int FA_BM = 128;             // query rows per block
 constexpr int FA_THREADS = 192;
 constexpr int FA_BOX_KEYS = 16;        // keys per TMA copy
-constexpr uint32_t FA_O_COL = 128;     // first tensor-memory column of O (S starts at 0)
+constexpr uint32_t FA_O_COL = 128;     // first tensor-memory column of O (S of even tiles from 0, of odd tiles from 64; P takes the place of S's first half)
 constexpr uint32_t FA_TMEM_COLS = 256;
 enum { FA_ERR_PRODUCER = 11, FA_ERR_MMA = 12, FA_ERR_SOFTMAX = 13, FA_ERR_ALIGN = 14 };
 
 template <int HD> struct FA {
-  static constexpr int BN = HD == 64 ? 128 : 64;       // keys per tile
+  static constexpr int BN = 64;                        // keys per tile
+  static constexpr int BLOCKS_PER_SM = 2;
   static constexpr int DB = HD / 64;                   // 64-wide blocks of the head dimension (128 bytes: one swizzle row)
   static constexpr uint32_t Q_BYTES = FA_BM * HD * 2;
   static constexpr uint32_t KV_BYTES = BN * HD * 2;    // one K or one V tile
   static constexpr int STAGES = 3;                     // of K and of V
-  static constexpr uint32_t P_COL = HD == 64 ? 192 : 64;   // tensor-memory columns: S from 0, O from 128, P (BN / 2 columns) here
   static constexpr uint32_t BAR_BYTES = 192;
   static constexpr uint32_t SMEM = Q_BYTES + 2 * STAGES * KV_BYTES + BAR_BYTES;
 };
@@ -58,14 +63,14 @@ __device__ __forceinline__ float fa_exp2(float x) {
 
 // tiles[i] = (request, first row of the step, rows <= 128, first position)
 template <int HD>
-__global__ void __launch_bounds__(FA_THREADS, 2)
+__global__ void __launch_bounds__(FA_THREADS, FA<HD>::BLOCKS_PER_SM)
 prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                               const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table, int max_blocks,
                               const int4* __restrict__ tiles, bf16* __restrict__ out, int out_stride, int n_heads,
                               int n_kv_heads, int page_shift, float scale_log2, int window, int* __restrict__ status) {
   constexpr int BN = FA<HD>::BN, DB = FA<HD>::DB;
   constexpr int ST = FA<HD>::STAGES;
-  constexpr uint32_t Q_BYTES = FA<HD>::Q_BYTES, KV_BYTES = FA<HD>::KV_BYTES, P_COL = FA<HD>::P_COL;
+  constexpr uint32_t Q_BYTES = FA<HD>::Q_BYTES, KV_BYTES = FA<HD>::KV_BYTES;
   constexpr uint32_t Q_BLOCK = FA_BM * 128;       // bytes of one 64-wide block of Q (128 rows of 128 bytes)
   constexpr uint32_t KV_BLOCK = BN * 128;         // likewise for a K or V tile
   extern __shared__ __align__(1024) unsigned char fa_raw[];
@@ -78,11 +83,11 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
   uint64_t* v_full = k_full + ST;                 // [ST]
   uint64_t* k_empty = v_full + ST;                // [ST] S of the tile has been computed
   uint64_t* v_empty = k_empty + ST;               // [ST] P V of the tile has been computed
-  uint64_t* s_full = v_empty + ST;                // S is in tensor memory
-  uint64_t* s_empty = s_full + 1;                 // the softmax threads hold S in registers
-  uint64_t* p_full = s_full + 2;                  // P is in tensor memory and O has been rescaled
-  uint64_t* pv_done = s_full + 3;                 // O includes the tile
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 4);
+  uint64_t* s_full = v_empty + ST;                // [2] S of a tile is in its buffer
+  uint64_t* p_full = s_full + 2;                  // [2] P has taken its place and O has been rescaled
+  uint64_t* pv_done = s_full + 4;                 // O includes the tile (one phase per tile)
+  uint64_t* o_done = s_full + 5;                  // O includes the last tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 6);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   if (smem_u32(fa_raw) & 1023u) {                 // the swizzled tiles need 1024-byte alignment
@@ -108,10 +113,12 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
       mbar_init(&k_empty[s], 1);
       mbar_init(&v_empty[s], 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(s_empty, 128);
-    mbar_init(p_full, 128);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&s_full[b], 1);
+      mbar_init(&p_full[b], 128);
+    }
     mbar_init(pv_done, 1);
+    mbar_init(o_done, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -193,57 +200,56 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
         for (int db = 0; db < DB; ++db)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_bf16(tmem_base, q_desc + ((db * Q_BLOCK + k * 32) >> 4), k_desc + ((s * KV_BYTES + db * KV_BLOCK + k * 32) >> 4),
-                      idesc_s, (db > 0 || k > 0) ? 1u : 0u);
+            umma_bf16(tmem_base + (i & 1) * BN, q_desc + ((db * Q_BLOCK + k * 32) >> 4),
+                      k_desc + ((s * KV_BYTES + db * KV_BLOCK + k * 32) >> 4), idesc_s, (db > 0 || k > 0) ? 1u : 0u);
         umma_commit(&k_empty[s]);
-        umma_commit(s_full);
+        umma_commit(&s_full[i & 1]);
       }
       __syncwarp();
       return true;
     };
     bool ok = warp_wait(q_full, 0, status, FA_ERR_MMA, abort_flag);
     ok = ok && issue_s(0);
+    if (n_kt > 1) ok = ok && issue_s(1);
     for (int i = 0; i < n_kt && ok; ++i) {
       const int s = i % ST;
-      if (i + 1 < n_kt) {
-        // S of the next tile overwrites S of this one: the softmax threads must hold it in registers
-        if (!warp_wait(s_empty, i & 1, status, FA_ERR_MMA, abort_flag) || !issue_s(i + 1)) break;
-      }
       if (!warp_wait(&v_full[s], (i / ST) & 1, status, FA_ERR_MMA, abort_flag)) break;
-      if (!warp_wait(p_full, i & 1, status, FA_ERR_MMA, abort_flag)) break;
+      if (!warp_wait(&p_full[i & 1], (i >> 1) & 1, status, FA_ERR_MMA, abort_flag)) break;
       tcgen05_after_sync();
       if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
           // P: 16 keys = 8 tensor-memory columns (two bf16 each). V: 16 keys = 16 rows of 128 bytes; groups of 8
           // keys 1024 bytes apart, blocks of 64 head dimensions KV_BLOCK apart.
-          umma_bf16_ts(tmem_base + FA_O_COL, tmem_base + P_COL + kk * 8, v_desc + ((s * KV_BYTES + kk * (16 * 128)) >> 4),
-                       idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+          umma_bf16_ts(tmem_base + FA_O_COL, tmem_base + (i & 1) * BN + kk * 8,
+                       v_desc + ((s * KV_BYTES + kk * (16 * 128)) >> 4), idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(&v_empty[s]);
         umma_commit(pv_done);
+        if (i + 1 == n_kt) umma_commit(o_done);
       }
       __syncwarp();
+      // S of the tile after the next goes where P of this one lies: issued behind the MMAs that read it
+      if (i + 2 < n_kt && !issue_s(i + 2)) break;
     }
   } else {
     // softmax: thread r owns query row r = tensor-memory lane r
     const int r = threadIdx.x;
-    const uint32_t taddr_s = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-    const uint32_t taddr_o = taddr_s + FA_O_COL;
+    const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    const uint32_t taddr_o = taddr_row + FA_O_COL;
     const int pos_r = pos0 + r;
     const int lo_r = window > 0 ? max(0, pos_r - window + 1) : 0;
     float m_ref = -INFINITY;      // the reference point of this row's exponentials, in base-2 units
     float l_run = 0.0f;
     bool ok = true;
     for (int i = 0; i < n_kt; ++i) {
-      if (!warp_wait(s_full, i & 1, status, FA_ERR_SOFTMAX, abort_flag)) { ok = false; break; }
+      const uint32_t taddr_s = taddr_row + (i & 1) * BN;
+      if (!warp_wait(&s_full[i & 1], (i >> 1) & 1, status, FA_ERR_SOFTMAX, abort_flag)) { ok = false; break; }
       tcgen05_after_sync();
       uint32_t sv[BN];
 #pragma unroll
       for (int c0 = 0; c0 < BN; c0 += 32) tmem_ld32(taddr_s + c0, *reinterpret_cast<uint32_t(*)[32]>(&sv[c0]));
       tmem_ld_wait();
-      tcgen05_before_sync();
-      mbar_arrive(s_empty);
 
       const int key0 = (j_begin + i) * BN;
       const bool edge = key0 + BN - 1 > pos0 + warp * 32 || (window > 0 && key0 < max(0, pos0 + warp * 32 + 31 - window + 1));
@@ -272,68 +278,51 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
         m_ref = mx;
         rescale = true;
       }
-      const float neg_m = m_ref == -INFINITY ? 0.0f : -m_ref;
-      float sum0 = 0.0f, sum1 = 0.0f;
-      // 8 probabilities -> one 16-byte piece of P
-      auto exp8 = [&](int c0, uint32_t (&w)[4]) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float p0 = fa_exp2(fmaf(__uint_as_float(sv[c0 + 2 * e]), scale_log2, neg_m));
-          const float p1 = fa_exp2(fmaf(__uint_as_float(sv[c0 + 2 * e + 1]), scale_log2, neg_m));
-          sum0 += p0;
-          sum1 += p1;
-          w[e] = pack2_bf16(p0, p1);
-        }
-      };
-      // the first 64 keys go to registers while P V of the previous tile may still be reading P
-      uint32_t first[8][4];
-#pragma unroll
-      for (int ch = 0; ch < 8; ++ch) exp8(ch * 8, first[ch]);
-      if (i > 0) {
-        // P V of the previous tile: O is complete up to it and P may be overwritten
+      if (__any_sync(0xffffffffu, rescale)) {
+        // O must hold every tile before this one. S of this tile was committed behind P V of tile i - 2, so that one
+        // is complete and the barrier is in the phase of tile i - 1 or past it: its parity cannot be mistaken.
         if (!warp_wait(pv_done, (i - 1) & 1, status, FA_ERR_SOFTMAX, abort_flag)) { ok = false; break; }
         tcgen05_after_sync();
-        if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < HD; c0 += 8) {          // a few columns at a time: S stays in its registers
+          uint32_t o[8];
+          tmem_ld8(taddr_o + c0, o);
+          tmem_ld_wait();
 #pragma unroll
-          for (int c0 = 0; c0 < HD; c0 += 32) {
-            uint32_t o[32];
-            tmem_ld32(taddr_o + c0, o);
-            tmem_ld_wait();
-#pragma unroll
-            for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * corr);
-            tmem_st32(taddr_o + c0, o);
-          }
-          tmem_st_wait();
+          for (int c = 0; c < 8; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * corr);
+          tmem_st8(taddr_o + c0, o);
         }
       }
-      // P in tensor memory: this thread's lane, column j = keys 2j and 2j + 1
-      const uint32_t taddr_p = taddr_s + P_COL;
-      tmem_st32(taddr_p, *reinterpret_cast<const uint32_t(*)[32]>(&first[0][0]));
-      if constexpr (BN > 64) {
-        uint32_t second[8][4];
+      const float neg_m = m_ref == -INFINITY ? 0.0f : -m_ref;
+      float sum0 = 0.0f, sum1 = 0.0f;
+      // P in tensor memory: this thread's lane, column j = keys 2j and 2j + 1, over the first half of S
+      uint32_t pk[BN / 2];
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) exp8(64 + ch * 8, second[ch]);
-        tmem_st32(taddr_p + 32, *reinterpret_cast<const uint32_t(*)[32]>(&second[0][0]));
+      for (int c = 0; c < BN; c += 2) {
+        const float p0 = fa_exp2(fmaf(__uint_as_float(sv[c]), scale_log2, neg_m));
+        const float p1 = fa_exp2(fmaf(__uint_as_float(sv[c + 1]), scale_log2, neg_m));
+        sum0 += p0;
+        sum1 += p1;
+        pk[c / 2] = pack2_bf16(p0, p1);
       }
+      tmem_st32(taddr_s, pk);
       tmem_st_wait();
       l_run = l_run * corr + (sum0 + sum1);
       tcgen05_before_sync();
-      mbar_arrive(p_full);
+      mbar_arrive(&p_full[i & 1]);
     }
-    if (ok && warp_wait(pv_done, (n_kt - 1) & 1, status, FA_ERR_SOFTMAX, abort_flag)) {
+    if (ok && warp_wait(o_done, 0, status, FA_ERR_SOFTMAX, abort_flag)) {
       tcgen05_after_sync();
       const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
       unsigned char* my_stage = k_s + warp * 4096;      // every K and V stage has been consumed
 #pragma unroll
       for (int c0 = 0; c0 < HD; c0 += 64) {
-        uint32_t va[32], vb[32];
-        tmem_ld32(taddr_o + c0, va);
-        tmem_ld32(taddr_o + c0 + 32, vb);
-        tmem_ld_wait();
         uint4 w[8];
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
-          const uint32_t* v = hh == 0 ? va : vb;
+          uint32_t v[32];
+          tmem_ld32(taddr_o + c0 + hh * 32, v);
+          tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; j += 8)
             w[hh * 4 + j / 8] = make_uint4(pack2_bf16(__uint_as_float(v[j]) * inv, __uint_as_float(v[j + 1]) * inv),
