@@ -23,7 +23,8 @@
 // wait for the tensor core in the steady state: a block's time per tile is the softmax's own (a tensor-memory
 // load, 64 maxima, 64 exponentials at a quarter of a warp's issue rate, a store), and two blocks keep an SM's
 // exponential unit busy. Tiles are 64 keys, so that S, S and O (64 + 64 + head_dim columns) leave room for two
-// blocks in an SM's tensor memory at both head sizes; shared memory holds Q and three stages of K and V.
+// blocks in an SM's tensor memory at both head sizes; shared memory holds Q and three stages of K and V (two at
+// head size 128, so that two blocks fit there as well).
 //
 // Every wait on an mbarrier is bounded (tcgen05.cuh); on a timeout all roles fall through to the common
 // exit, where tensor memory is freed, and *status tells the host.
@@ -49,7 +50,7 @@ template <int HD> struct FA {
   static constexpr int DB = HD / 64;                   // 64-wide blocks of the head dimension (128 bytes: one swizzle row)
   static constexpr uint32_t Q_BYTES = FA_BM * HD * 2;
   static constexpr uint32_t KV_BYTES = BN * HD * 2;    // one K or one V tile
-  static constexpr int STAGES = 3;                     // of K and of V
+  static constexpr int STAGES = HD == 64 ? 3 : 2;      // of K and of V: 64 KiB or 96 KiB of shared memory, two blocks to an SM
   static constexpr uint32_t BAR_BYTES = 192;
   static constexpr uint32_t SMEM = Q_BYTES + 2 * STAGES * KV_BYTES + BAR_BYTES;
 };
@@ -59,6 +60,12 @@ __device__ __forceinline__ float fa_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+__device__ __forceinline__ float fa_max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
 }
 
 // tiles[i] = (request, first row of the step, rows <= 128, first position)
@@ -262,11 +269,11 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
       }
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < BN; c += 4) {
-        mx0 = fmaxf(mx0, __uint_as_float(sv[c]));
-        mx1 = fmaxf(mx1, __uint_as_float(sv[c + 1]));
-        mx2 = fmaxf(mx2, __uint_as_float(sv[c + 2]));
-        mx3 = fmaxf(mx3, __uint_as_float(sv[c + 3]));
+      for (int c = 0; c < BN; c += 8) {
+        mx0 = fa_max3(mx0, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]));
+        mx1 = fa_max3(mx1, __uint_as_float(sv[c + 2]), __uint_as_float(sv[c + 3]));
+        mx2 = fa_max3(mx2, __uint_as_float(sv[c + 4]), __uint_as_float(sv[c + 5]));
+        mx3 = fa_max3(mx3, __uint_as_float(sv[c + 6]), __uint_as_float(sv[c + 7]));
       }
       const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;      // the scale is positive
       float corr = 1.0f;
