@@ -695,11 +695,11 @@ int launch_decode_tc(const void* q, int q_stride, const void* kc, const void* vc
   constexpr size_t pipe = static_cast<size_t>(16 + W * STAGES * 2 * KT) * (HD + 8) * sizeof(bf16);
   constexpr size_t mrg = static_cast<size_t>(W) * 16 * (HD + 2) * sizeof(float);
   constexpr size_t base = ((pipe > mrg ? pipe : mrg) + 15) & ~static_cast<size_t>(15);
-  // Up to 8 splits can merge through the shared memory of a cluster's first block. Measured on B200: that wins
-  // for a handful of rows (batch 1: 1063 against 1010 tokens/s) and loses once the grid is a few dozen clusters
-  // (batch 8: 1.24 ms against 1.13 ms per step), where global scratch and the merge kernel do better.
-  const int group_blocks = n_kv_heads * ((n_heads / n_kv_heads + 15) / 16);
-  const bool cluster = plan == nullptr && n_split > 1 && n_split <= 8 && (part == nullptr || rows * group_blocks <= 32);
+  // Up to 8 splits can merge through the shared memory of a cluster's first block instead of scratch and a second
+  // kernel. Measured on B200 (1B shapes, decode step at batch 8): clusters of 2 blocks 0.832 ms, of 4 0.881 ms, of 3
+  // 0.903 ms; scratch and the merge kernel with 3 splits 0.883 ms, with 4 0.866 ms: clusters whose size is a power of
+  // two place well, the others do not. So a caller that brings scratch gets the cluster for 2, 4 and 8 splits.
+  const bool cluster = plan == nullptr && n_split > 1 && n_split <= 8 && (part == nullptr || (n_split & (n_split - 1)) == 0);
   const size_t smem = base + (cluster ? static_cast<size_t>(n_split) * 16 * (HD + 2) * sizeof(float) : 0);
   static size_t configured = 0;
   if (smem > configured) {

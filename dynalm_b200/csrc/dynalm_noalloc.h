@@ -18,8 +18,8 @@
 //  * A call with n_split > 1 is counted as rows * n_heads * n_split * (head_dim + 2) floats of scratch. More
 //    than DL_NOALLOC_SCRATCH_FLOATS is refused with DL_ERR_NOALLOC_TOO_LARGE before anything is launched;
 //    lower n_split (1 needs no scratch at all) or call per group of rows. The count is made for every call,
-//    also for the small ones (at most 8 splits and at most 32 blocks per split) whose splits the kernel merges
-//    inside a thread-block cluster and which in the end do not touch the array.
+//    also for those (2, 4 or 8 splits) whose splits the kernel merges inside a thread-block cluster and which in
+//    the end do not touch the array.
 //  * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
 //    device current) and keeps it. That first call should come before any stream capture begins.
 //  * All calls on a device share the one array and it keeps what the last call left. Nothing in it has to

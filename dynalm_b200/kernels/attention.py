@@ -20,7 +20,7 @@ from .device import sm_count
 
 MAX_SPLITS = 32
 CLUSTER_SPLITS = 8          # up to here the tensor-core kernel merges splits inside a thread-block cluster
-LONG_SPLIT_KEYS = 1024      # keys per split from which more than CLUSTER_SPLITS splits pay
+LONG_SPLIT_KEYS = 4096      # keys per split from which more than CLUSTER_SPLITS splits pay
 DECODE_FILL = int(os.environ.get('DYNALM_DECODE_FILL', '1'))   # blocks per SM the split count aims for
 
 
@@ -157,14 +157,29 @@ def query_tiles(ctx):
 def decode_splits(rows: int, n_heads: int, n_kv_heads: int, max_kv_len: int, tensor_cores: bool = True,
                   sms: int = 0) -> int:
     """Key splits per row so that the grid fills the GPU, each split at least 128 keys (one tile for each of a
-    block's warps: four of 32 keys or eight of 16). The tensor-core kernel merges up to 8 splits inside a thread-block cluster, which
-    wins while a split is short; from 1,024 keys per split on, more splits (merged by a second kernel) win."""
+    block's warps: four of 32 keys or eight of 16).
+
+    The tensor-core kernel merges 2, 4 or 8 splits inside a thread-block cluster (no second kernel). Measured on
+    B200 (1B shapes, ms per decode step; s = merged by the second kernel): 2,048 keys, batch 1: 4 -> 0.753, 8 ->
+    0.741; batch 2: 4 -> 0.758, 8 -> 0.836; batch 4: 4 -> 0.770, 5 -> 0.847, 8 -> 0.921; batch 6: 2 -> 0.821, 4 -> 0.874;
+    batch 8: 2 -> 0.832, 3 -> 0.903, 3s -> 0.883, 4 -> 0.881, 4s -> 0.866; 8,192 keys, tokens/s at batch 1: 4 -> 1,171,
+    8 -> 1,260, 8s -> 1,131, 16s -> 1,171, 19s -> 1,144; at batch 8: 2 -> 7,423, 3s -> 6,906, 4 -> 7,151, 4s -> 7,070.
+    So: a power of two (clusters of 3 or 5 blocks place badly), as many as keep the grid within about one block per
+    SM, at most 4 unless there are so few rows that 8 still leaves SMs free. Only from 32,768 keys on are more
+    splits taken, merged by the second kernel."""
     group = n_heads // n_kv_heads
     blocks = rows * n_kv_heads * (-(-group // (16 if tensor_cores else 4)))
-    want = -(-DECODE_FILL * (sms or sm_count()) // max(blocks, 1))
-    splits = max(1, min(want, max(1, max_kv_len // 128), MAX_SPLITS))
-    if tensor_cores and splits > CLUSTER_SPLITS and max_kv_len < CLUSTER_SPLITS * LONG_SPLIT_KEYS:
-        splits = CLUSTER_SPLITS
+    sms = sms or sm_count()
+    want = -(-DECODE_FILL * sms // max(blocks, 1))
+    most = max(1, max_kv_len // 128)
+    if not tensor_cores:
+        return max(1, min(want, most, MAX_SPLITS))
+    if want > CLUSTER_SPLITS and max_kv_len >= CLUSTER_SPLITS * LONG_SPLIT_KEYS:
+        return max(1, min(want, most, MAX_SPLITS))
+    cap = CLUSTER_SPLITS if blocks * CLUSTER_SPLITS <= sms // 2 else 4
+    splits = 1
+    while splits * 2 <= min(cap, most) and blocks * splits * 2 * 4 <= 5 * DECODE_FILL * sms:
+        splits *= 2
     return splits
 
 

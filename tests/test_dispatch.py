@@ -51,14 +51,19 @@ def test_the_tcgen05_product_needs_96_tiles_at_its_narrowest_width():
 
 
 def test_decode_attention_splits():
-    # batch 8 of the 1B shape at 2,048 keys: 64 blocks -> 3 splits; batch 64: enough blocks already
-    assert attention.decode_splits(8, 32, 8, 2048) == 3
-    assert attention.decode_splits(64, 32, 8, 2048) == 1
-    # one row: as many splits as the cluster merges, more only when a split still holds 1,024 keys
-    assert attention.decode_splits(1, 32, 8, 2048) == 8
-    assert attention.decode_splits(1, 32, 8, 65536) > 8
+    # the 1B shape at 2,048 keys: powers of two (the splits of a row are one thread-block cluster), about one block per SM
+    assert [attention.decode_splits(rows, 32, 8, 2048, sms=148) for rows in (1, 2, 4, 6, 8, 10)] == [8, 4, 4, 2, 2, 2]
+    assert attention.decode_splits(64, 32, 8, 2048, sms=148) == 1
+    # the same at 8,192 keys; more splits (merged by the second kernel) only from 32,768 keys on
+    assert attention.decode_splits(1, 32, 8, 8192, sms=148) == 8
+    assert attention.decode_splits(8, 32, 8, 8192, sms=148) == 2
+    assert attention.decode_splits(1, 32, 8, 65536, sms=148) > 8
     # never less than 128 keys per split
-    assert attention.decode_splits(1, 32, 8, 256) == 2
+    assert attention.decode_splits(1, 32, 8, 256, sms=148) == 2
+    assert attention.decode_splits(1, 32, 8, 100, sms=148) == 1
+    # the plain kernel (float32, large head sizes) has no cluster: as many splits as fill the GPU
+    assert attention.decode_splits(8, 32, 8, 2048, tensor_cores=False, sms=148) == 3
+    assert attention.decode_splits(1, 32, 8, 2048, tensor_cores=False, sms=148) == 16
 
 
 def test_check_records_are_decoded():

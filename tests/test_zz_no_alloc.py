@@ -6,8 +6,8 @@ its token path (it stalls the whole device). For them `dl_paged_attention_decode
 split-KV scratch inside the library. This test loads the built library with ctypes and calls that symbol
 and the ordinary entry point (which is given scratch by the caller) on the same inputs.
 
-The kernel touches scratch only when it cannot merge a row's key splits inside a thread-block cluster:
-with more than 8 splits, or with more than 32 blocks per split (rows x KV-head blocks). The first cases are
+The kernel touches scratch only when it does not merge a row's key splits inside a thread-block cluster, which it
+does for 2, 4 and 8 splits (clusters of other sizes place badly on the GPU). The first cases are
 of that kind, so the library's own array is what carries the partial results: the output must then be the
 same bits as the ordinary entry point's at the same split count (it is the same kernel on the same
 numbers; only the address of the scratch differs), and both must agree with a float64 attention written
@@ -97,15 +97,15 @@ def test_no_alloc_entry_matches_the_ordinary_one():
     many = [97, 33, 260, 129, 1, 700, 64, 65, 511, 48, 300, 17, 222, 16, 401, 130, 75, 999, 250, 31]
     cases = (
         # (seed, head size, rows, tokens each request holds, key splits, does the kernel merge through scratch?)
-        (1, 64, 20, many, 3, True),                       # 20 rows x 2 KV-head blocks = 40 blocks per split
+        (1, 64, 20, many, 3, True),                       # three splits: no cluster of that size
         (2, 64, 3, [1600, 2100, 1537], 12, True),         # more splits than a cluster can hold
         (3, 128, 24, many[:12], 5, True),                 # other shapes over the records the calls before left
-        (4, 64, 20, many[::-1], 2, True),
-        (5, 64, 4, [700, 33, 260, 129], 5, False),        # few blocks, few splits: merged inside a cluster
+        (4, 64, 20, many[::-1], 6, True),
+        (6, 64, 20, many[::-1], 2, False),                # two splits: a cluster of two, however many rows
+        (5, 64, 4, [700, 33, 260, 129], 4, False),        # four splits: merged inside a cluster
     )
     for seed, hd, rows, lens, splits, through_scratch in cases:
-        group_blocks = kvh * (-(-(heads // kvh) // 16))
-        assert through_scratch == (splits > 8 or rows * group_blocks > 32)
+        assert through_scratch == (splits > 8 or splits & (splits - 1) != 0)
         (q, kc, vc, table, pos, req), keys, vals = _case(seed, rows, heads, kvh, hd, page, lens)
         scale = 1.0 / math.sqrt(hd)
         want = torch.zeros(rows, heads * hd, dtype=torch.bfloat16, device=DEV)
