@@ -532,8 +532,10 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
 
 
 def decode_tile_keys(head_dim: int) -> int:
-    """Keys per tile of the tensor-core decode attention (what its plans count keys in)."""
-    return 16 if head_dim >= 96 else 32
+    """Keys per tile of the tensor-core decode attention (what its plans count keys in); the table of
+    csrc/attention_decode.cu (dl_paged_attention_decode_tile), kept here so that a plan can be made without the
+    library."""
+    return 16 if head_dim >= 96 or head_dim == 64 else 32
 
 
 def paged_attention_decode_planned(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,

@@ -624,6 +624,17 @@ def test_gemm_argmax_matches_argmax_of_the_product(ops, rows, N, K):
         assert any(float(x[r, 0]) > 0.5 and int(got[r]) == 11 for r in range(rows)) or not any(float(x[r, 0]) > 0.5 for r in range(rows))
 
 
+def test_decode_tile_keys_agree_with_the_kernel(ops):
+    """The plan counts a row's keys in the kernel's tiles: the table on the Python side is the kernel's."""
+    import ctypes
+    from dynalm_b200.kernels import lib
+    f = lib.load("attention_decode").dl_paged_attention_decode_tile
+    f.argtypes, f.restype = [ctypes.c_int], ctypes.c_int
+    for hd in range(16, 129, 16):
+        assert ops.decode_tile_keys(hd) == f(hd), hd
+
+
+
 @pytest.mark.parametrize("heads,kvh,hd,window", [(8, 2, 64, 0), (6, 2, 32, 0), (3, 1, 128, 0), (32, 8, 64, 0), (4, 4, 80, 37)])
 def test_planned_decode_attention(ops, heads, kvh, hd, window, monkeypatch):
     """The decode kernel with the keys dealt into units by the host, on requests of very different lengths (one long,
