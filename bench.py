@@ -11,8 +11,9 @@ prefill with its fraction of the bf16 matrix peak, the decode step's fraction of
 weight read once plus the cache of the live requests), and as `points` decode at batch 1 and 64, decode
 at batch 1, 8 and 64 with about 8,000 tokens of context each (as many as the 8,192-token benchmark context
 leaves room for while the measurement grows them), and a prefill of 8,192 tokens, each with its fraction
-of the roofline. `--workload serve3b | serve8b` runs the continuous-batching workloads of the 3B and 8B
-shapes instead. Prints one JSON line.
+of the roofline; last, the continuous-batching workloads of the 3B and 8B shapes (tokens/s over the whole run,
+median time to the first token, decode-only step). `--workload serve3b | serve8b` runs one of those alone and
+prints its full record. Prints one JSON line.
 """
 
 import argparse
@@ -234,9 +235,10 @@ def reference_arm(args):
     return 0
 
 
-def serving(name, layers=None):
+def serving(name, layers=None, emit=True):
     """Continuous batching end to end through the Python entry point: all requests submitted at once, prompts
-    prefilled in chunks beside decode rows, every request decoding its full count. Prints one JSON line."""
+    prefilled in chunks beside decode rows, every request decoding its full count. Prints one JSON line, or
+    (emit=False) returns the record."""
     import numpy as np
     import torch
     from dynalm_b200 import Engine, Request, SchedulerConfig
@@ -288,6 +290,9 @@ def serving(name, layers=None):
                    "decode_tokens": n_decode, "kv_tokens": kv_tokens},
         "clocks": cs.result, "data": "synthetic: random weights, random token ids",
     }
+    if not emit:
+        del eng
+        return out
     print(json.dumps(out))
     return 0
 
@@ -304,6 +309,7 @@ def main():
                     help="decode: the default benchmark; serve3b / serve8b: continuous batching of the 3B / 8B workloads")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-long", action="store_true", help="skip the points at 8,192 tokens (prefill and decode)")
+    ap.add_argument("--no-serve", action="store_true", help="skip the points of the 3B and 8B serving workloads")
     ap.add_argument("--repeats", type=int, default=5, help="the timed K steps are repeated this often; `value` is the median")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel (for profiling)")
     ap.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
@@ -498,6 +504,23 @@ def main():
         eng.scheduler.cancel(s_.id)
     while not eng.scheduler.idle:
         eng.scheduler.step()
+
+    # ---- the serving workloads of the larger shapes, as points (each builds its own engine) ---------------------
+    if not (args.no_points or args.no_serve or args.layers != FULL_LAYERS):
+        import gc
+        del eng
+        gc.collect()
+        torch.cuda.empty_cache()
+        for name in sorted(SERVING):
+            try:
+                got = serving(name, emit=False)
+                points[f"{name}_tokens_per_s"] = got["value"]
+                points[f"{name}_ttft_p50_ms"] = got["ttft_ms"]["p50"]
+                points[f"{name}_decode_step_ms"] = got["decode_step_ms"]
+            except Exception as e:           # a point that fails does not take the line with it
+                points[f"{name}_error"] = f"{type(e).__name__}: {e}"[:200]
+            gc.collect()
+            torch.cuda.empty_cache()
 
     out = {
         "metric": "decode tokens/s, Llama 3.2 1B shape, batch 8, 2048 tokens of context per sequence",
