@@ -348,6 +348,51 @@ def test_paged_attention_prefill_tcgen05(ops, heads, kvh, hd, page, window):
     assert ops.gemm_tcgen05_status() == 0
 
 
+@pytest.mark.parametrize("heads,kvh,hd,page,window", [(4, 2, 64, 16, 0), (2, 1, 128, 64, 0), (2, 2, 64, 32, 1000)])
+def test_paged_attention_prefill_tcgen05_long_context(ops, heads, kvh, hd, page, window):
+    """A request of 3,000 keys (47 tiles of 64: many rounds of the kernel's two S buffers and of its K/V stages): a
+    full 128-row tile at its end and a 70-row one in the middle, with a key far above the running maximum late in the
+    context (rows that see it rescale their sums after dozens of tiles) and one early; against float64."""
+    g = torch.Generator(device="cpu").manual_seed(hd + page)
+    L = 3000
+    k = torch.randn(L, kvh, hd, generator=g).to(torch.bfloat16)
+    v = torch.randn(L, kvh, hd, generator=g).to(torch.bfloat16)
+    k[5] *= 4.0
+    k[2700] *= 6.0
+    n_pages = -(-L // page)
+    perm = torch.randperm(n_pages + 3, generator=g)
+    table = perm[:n_pages].to(torch.int32).view(1, n_pages).contiguous()
+    kc = torch.zeros(n_pages + 3, page, kvh, hd, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    for b in range(n_pages):
+        n = min(page, L - b * page)
+        kc[table[0, b], :n] = k[b * page:b * page + n]
+        vc[table[0, b], :n] = v[b * page:b * page + n]
+    runs = [(L - 128, 128), (1500, 70)]                       # (first position, rows)
+    rows = [p0 + i for p0, n in runs for i in range(n)]
+    tiles, row0 = [], 0
+    for p0, n in runs:
+        tiles.append((0, row0, n, p0))
+        row0 += n
+    q = torch.randn(len(rows), heads, hd, generator=g).to(torch.bfloat16)
+    for i, p in enumerate(rows):
+        if i % 3 == 0:
+            q[i] = (k[2700, 0].float() * 0.2).to(torch.bfloat16)       # sees the late key (if its position is past it)
+        if i % 3 == 1:
+            q[i] = (k[5, 0].float() * 0.5).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(hd)
+    out = torch.zeros(len(rows), heads * hd, dtype=torch.bfloat16, device=DEV)
+    ops.paged_attention_prefill_tcgen05(q.reshape(len(rows), heads * hd).to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV),
+                                        torch.tensor(tiles, dtype=torch.int32).to(DEV), len(tiles), out, heads, kvh, hd, page,
+                                        scale, window)
+    assert ops.gemm_tcgen05_status() == 0, "a wait inside the kernel timed out"
+    got = out.double().cpu().reshape(len(rows), heads, hd)
+    for i, p in enumerate(rows):
+        ref = _attention_ref(q[i].double(), k[:p + 1].double(), v[:p + 1].double(), scale, window)
+        err = (got[i] - ref).abs().max().item()
+        assert err <= 2.5e-2, f"row {i} (position {p}): {err}"
+
+
 def test_paged_attention_prefill_tcgen05_refuses_other_shapes(ops):
     q = torch.zeros(4, 2 * 48, dtype=torch.bfloat16, device=DEV)
     kc = torch.zeros(3, 16, 1, 48, dtype=torch.bfloat16, device=DEV)
