@@ -330,6 +330,51 @@ def test_paged_attention_decode(ops, dtype, heads, kvh, hd, page, window, splits
         assert err <= tol(dtype, 2), f"row {i} (request {r}): {err}"
 
 
+@pytest.mark.parametrize("heads,kvh,hd,splits", [(32, 8, 64, 2), (32, 8, 64, 4), (8, 2, 128, 2), (12, 4, 64, 8), (6, 2, 32, 4)])
+def test_paged_attention_decode_many_rows_in_clusters(ops, heads, kvh, hd, splits):
+    """2, 4 and 8 key splits of a row are one thread-block cluster that merges in its first block's shared memory, at
+    any number of rows: 30 rows over requests of 1 to 2,048 keys (many more clusters than SMs hold at once for the
+    widest shape), the scratch left untouched; against float64."""
+    page = 16
+    g = torch.Generator(device="cpu").manual_seed(77 + hd + splits)
+    lens = [700, 1, 130, 60, 333, 2048, 17, 129]
+    max_blocks = -(-max(lens) // page)
+    pages = sum(-(-l // page) for l in lens) + 5
+    perm = torch.randperm(pages, generator=g)
+    table = torch.full((len(lens), max_blocks), -1, dtype=torch.int32)
+    kc = torch.zeros(pages, page, kvh, hd, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    keys, vals, nxt = [], [], 0
+    for r, l in enumerate(lens):
+        k = torch.randn(l, kvh, hd, generator=g).to(torch.bfloat16)
+        v = torch.randn(l, kvh, hd, generator=g).to(torch.bfloat16)
+        k[min(3, l - 1)] *= 4.0
+        keys.append(k)
+        vals.append(v)
+        for b in range(-(-l // page)):
+            table[r, b] = perm[nxt]
+            nxt += 1
+            n = min(page, l - b * page)
+            kc[table[r, b], :n] = k[b * page:b * page + n]
+            vc[table[r, b], :n] = v[b * page:b * page + n]
+    order = [(5 * i) % len(lens) for i in range(30)]
+    req = torch.tensor(order, dtype=torch.int32)
+    pos = torch.tensor([lens[r] - 1 for r in order], dtype=torch.int32)
+    q = torch.randn(len(order), heads, hd, generator=g).to(torch.bfloat16)
+    q[0] = (keys[order[0]][3, 0].float() * 0.5).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(hd)
+    out = torch.zeros(len(order), heads * hd, dtype=torch.bfloat16, device=DEV)
+    scratch = torch.full((ops.decode_scratch_floats(len(order), heads, hd, splits),), float("nan"), dtype=torch.float32, device=DEV)
+    ops.paged_attention_decode(q.reshape(len(order), heads * hd).to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV), pos.to(DEV),
+                               req.to(DEV), out, scratch, heads, kvh, hd, page, scale, 0, splits, tensor_cores=True)
+    assert bool(torch.isnan(scratch).all()), "the splits were expected to merge inside their cluster"
+    got = out.double().cpu().reshape(len(order), heads, hd)
+    for i, r in enumerate(order):
+        ref = _attention_ref(q[i].double(), keys[r].double(), vals[r].double(), scale, 0)
+        err = (got[i] - ref).abs().max().item()
+        assert err <= tol(torch.bfloat16, 2), f"row {i} (request {r}): {err}"
+
+
 @pytest.mark.parametrize("heads,kvh,hd,page,window", [(4, 2, 16, 16, 0), (6, 2, 32, 16, 0), (5, 1, 48, 16, 0),
                                                         (3, 3, 80, 32, 0), (8, 2, 128, 16, 40), (32, 8, 64, 16, 0),
                                                         (4, 4, 64, 16, 7), (2, 1, 112, 16, 100), (4, 2, 96, 64, 0)])
