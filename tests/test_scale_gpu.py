@@ -1,5 +1,5 @@
-"""The Llama 3.2 1B layer sizes (2 of its 16 layers, the full vocabulary, tied embeddings, llama3 RoPE scaling)
-with random weights, against the plain implementation: whole prompts, portions, and mixed steps of up to four
+"""The Llama 3.2 1B and 3B layer sizes (2 of their layers, the full vocabulary, tied embeddings, llama3 RoPE scaling;
+head size 64 in groups of four, head size 128 in groups of three) with random weights, against the plain implementation: whole prompts, portions, and mixed steps of up to four
 live requests in a pool so small that pages are used again. At these sizes the bfloat16 engine runs what the tiny
 configurations cannot reach: the tcgen05 products (also the one in which two blocks share tiles of W, from 1,184
 rows), the tcgen05 prompt attention over many query tiles, and the library product for the row counts in between.
@@ -29,16 +29,24 @@ CFG = {
     "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
                      "original_max_position_embeddings": 8192},
 }
+CFG_3B = dict(CFG, hidden_size=3072, num_attention_heads=24, head_dim=128)
+SHAPES = {"1B": CFG, "3B": CFG_3B}
 LENGTHS = [300, 170, 230, 129, 90, 200]
 LONG = 1300
 LONG_WANT = list(range(LONG - 6, LONG))
 
 
+@pytest.fixture(scope="module", params=sorted(SHAPES))
+def shape(request):
+    return request.param
+
+
 @pytest.fixture(scope="module")
-def folder(tmp_path_factory):
+def folder(tmp_path_factory, shape):
     from dynalm_b200.registry import find_architecture
     from dynalm_b200.weights import random_tensors, write_safetensors
-    d = str(tmp_path_factory.mktemp("one_b_shape"))
+    CFG = SHAPES[shape]
+    d = str(tmp_path_factory.mktemp(f"shape_{shape}"))
     arch = find_architecture(CFG)
     t = random_tensors(arch.plan(arch.read_config(CFG)), 0, torch.bfloat16)
     # random N(0, 0.02) weights give nearly flat logits; a wider embedding makes the distribution peaked
@@ -86,7 +94,7 @@ def plain(folder):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_one_b_shape_against_plain(dtype, folder, plain):
+def test_layer_shapes_against_plain(dtype, shape, folder, plain):
     from dynalm_b200.engine import build
     from dynalm_b200.kernels import gemm
     _, plans = _plans()
@@ -98,15 +106,15 @@ def test_one_b_shape_against_plain(dtype, folder, plain):
         assert built.cache.free_pages == built.cache.num_pages
         kl, top1 = kl_and_top1(plan, got, plain, near_tie=1e-4 if dtype == "float32" else 0.05)
         if dtype == "float32":
-            worst = compare(plan, got, plain, 0.0, 1e-4, f"1B/{dtype}/{what}")
+            worst = compare(plan, got, plain, 0.0, 1e-4, f"{shape}/{dtype}/{what}")
             assert kl <= 1e-9 and top1 == 1.0
         else:
-            worst = compare(plan, got, plain, 0.0, 5e-2, f"1B/{dtype}/{what}")
+            worst = compare(plan, got, plain, 0.0, 5e-2, f"{shape}/{dtype}/{what}")
             # (rows whose two largest plain logits lie within 0.05 of each other are not counted against it; of the
             # others a few in a thousand still change places under bfloat16 rounding at this logit scale)
-            assert kl <= 0.0025 and top1 >= 0.99, f"1B/{dtype}/{what}: mean KL {kl:.3g}, top-1 agreement {top1:.4f}"
+            assert kl <= 0.0025 and top1 >= 0.99, f"{shape}/{dtype}/{what}: mean KL {kl:.3g}, top-1 agreement {top1:.4f}"
             if what == "mixed":
                 assert gemm.LIBRARY_CALLS > library_before, "no product took the path of 17 to 127 rows"
-        print(f"1B {dtype} {what}: steps {len(plan.steps)} pool {need} worst {worst:.3g} KL {kl:.3g} top-1 {top1:.4f}")
+        print(f"{shape} {dtype} {what}: steps {len(plan.steps)} pool {need} worst {worst:.3g} KL {kl:.3g} top-1 {top1:.4f}")
         del built
         torch.cuda.empty_cache()
