@@ -21,8 +21,8 @@
 // tiles ahead: behind P V of tile i it issues S of tile i + 2 into the columns that held P of tile i (the tensor
 // core runs one thread's MMAs in the order of issue, so P V has read them by then). The softmax threads thus never
 // wait for the tensor core in the steady state: a block's time per tile is the softmax's own (a tensor-memory
-// load, 64 maxima, 64 exponentials at a quarter of a warp's issue rate, a store), and two blocks keep an SM's
-// exponential unit busy. Tiles are 64 keys, so that S, S and O (64 + 64 + head_dim columns) leave room for two
+// load, 64 maxima, 64 exponentials at a quarter of a warp's issue rate, a store), and two blocks share an SM
+// (its exponential unit is then busy about two thirds of the time). Tiles are 64 keys, so that S, S and O (64 + 64 + head_dim columns) leave room for two
 // blocks in an SM's tensor memory at both head sizes; shared memory holds Q and three stages of K and V (two at
 // head size 128, so that two blocks fit there as well).
 //
