@@ -330,7 +330,7 @@ def test_paged_attention_decode(ops, dtype, heads, kvh, hd, page, window, splits
         assert err <= tol(dtype, 2), f"row {i} (request {r}): {err}"
 
 
-@pytest.mark.parametrize("heads,kvh,hd,splits", [(32, 8, 64, 2), (32, 8, 64, 4), (8, 2, 128, 2), (12, 4, 64, 8), (6, 2, 32, 4)])
+@pytest.mark.parametrize("heads,kvh,hd,splits", [(32, 8, 64, 2), (32, 8, 64, 4), (8, 2, 128, 2), (12, 4, 64, 8), (6, 2, 32, 4), (3, 1, 128, 8), (8, 2, 128, 4)])
 def test_paged_attention_decode_many_rows_in_clusters(ops, heads, kvh, hd, splits):
     """2, 4 and 8 key splits of a row are one thread-block cluster that merges in its first block's shared memory, at
     any number of rows: 30 rows over requests of 1 to 2,048 keys (many more clusters than SMs hold at once for the
