@@ -12,7 +12,7 @@ weight read once plus the cache of the live requests), and as `points` decode at
 at batch 1, 8 and 64 with about 8,000 tokens of context each (as many as the 8,192-token benchmark context
 leaves room for while the measurement grows them), and a prefill of 8,192 tokens, each with its fraction
 of the roofline; last, the continuous-batching workloads of the 3B and 8B shapes (tokens/s over the whole run,
-median time to the first token, decode-only step). `--workload serve3b | serve8b` runs one of those alone and
+median time to the first token, decode-only step) and a 32,768-token prompt brought in portions of 512. `--workload serve3b | serve8b` runs one of those alone and
 prints its full record. Prints one JSON line.
 """
 
@@ -297,6 +297,33 @@ def serving(name, layers=None, emit=True):
     return 0
 
 
+def long_prompt(tokens=32768, portion=512):
+    """One prompt of `tokens` tokens brought in portions of `portion` through the step function (the 1B shape with the
+    131,072 positions the model has): tokens/s. What a long request costs a server that cuts prompts into portions:
+    every portion's attention walks all keys so far."""
+    import numpy as np
+    import torch
+    from dynalm_b200 import Engine, StepEntry
+    cfg = dict(LLAMA_1B)
+    cfg["max_position_embeddings"] = 131072
+    eng = Engine(config=cfg, random_seed=0, dtype="bfloat16", ctx=tokens + 1024, batch=max(portion, 512), max_running=2)
+    rng = np.random.RandomState(1)
+    ids = [int(t) for t in rng.randint(0, cfg["vocab_size"], tokens)]
+
+    def once(name):
+        for p in range(0, tokens, portion):
+            eng.step_fn.step([StepEntry(name, ids[p:p + portion], [len(ids[p:p + portion]) - 1] if p + portion >= tokens else [])])
+        eng.step_fn.end(name)
+    once("warm")
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    once("timed")
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    del eng
+    return round(tokens / dt, 1), round(dt * 1e3, 1)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -521,6 +548,12 @@ def main():
                 points[f"{name}_error"] = f"{type(e).__name__}: {e}"[:200]
             gc.collect()
             torch.cuda.empty_cache()
+        try:
+            points["prefill_32768_in_portions_of_512"], points["prefill_32768_in_portions_of_512_ms"] = long_prompt()
+        except Exception as e:
+            points["prefill_32768_in_portions_of_512_error"] = f"{type(e).__name__}: {e}"[:200]
+        gc.collect()
+        torch.cuda.empty_cache()
 
     out = {
         "metric": "decode tokens/s, Llama 3.2 1B shape, batch 8, 2048 tokens of context per sequence",

@@ -26,6 +26,13 @@
 // blocks in an SM's tensor memory at both head sizes; shared memory holds Q and three stages of K and V (two at
 // head size 128, so that two blocks fit there as well).
 //
+// The keys of a query tile may be dealt over several blocks (`unit_parts`): with few tiles (a 512-row portion is four
+// of them per head) every block would walk all of a long context's keys alone and most SMs would idle; 512 rows at
+// 32,768 keys ran at 0.39 PFLOP/s against 0.63 for 2,048 rows. A tile then appears once per part in `tiles`, each
+// part takes a contiguous share of the key tiles and leaves its unnormalised O, its reference point and its sum in
+// scratch; the part that finds the others done (a counter per tile and head) adds them up in the order of the parts
+// and stores the rows.
+//
 // Every wait on an mbarrier is bounded (tcgen05.cuh); on a timeout all roles fall through to the common
 // exit, where tensor memory is freed, and *status tells the host.
 //
@@ -74,7 +81,8 @@ __global__ void __launch_bounds__(FA_THREADS, FA<HD>::BLOCKS_PER_SM)
 prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                               const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table, int max_blocks,
                               const int4* __restrict__ tiles, bf16* __restrict__ out, int out_stride, int n_heads,
-                              int n_kv_heads, int page_shift, float scale_log2, int window, int* __restrict__ status) {
+                              int n_kv_heads, int page_shift, float scale_log2, int window, int* __restrict__ status,
+                              const int* __restrict__ unit_parts, float* __restrict__ partial, int* __restrict__ counters) {
   constexpr int BN = FA<HD>::BN, DB = FA<HD>::DB;
   constexpr int ST = FA<HD>::STAGES;
   constexpr uint32_t Q_BYTES = FA<HD>::Q_BYTES, KV_BYTES = FA<HD>::KV_BYTES;
@@ -110,7 +118,15 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pos_last = pos0 + nrows - 1;
   const int lo_tile = window > 0 ? max(0, pos0 - window + 1) : 0;      // the first key any row of the tile reads
-  const int j_begin = lo_tile / BN, n_kt = pos_last / BN - j_begin + 1;
+  int j_begin = lo_tile / BN, n_kt = pos_last / BN - j_begin + 1;
+  // this block's share of the tile's keys: part `part` of `parts` (word = part | parts << 8 | first scratch slot << 16)
+  const int part_word = unit_parts != nullptr ? unit_parts[blockIdx.y] : 0;
+  const int part = part_word & 0xff, parts = (part_word >> 8) & 0xff, slot0 = part_word >> 16;
+  if (parts > 1) {
+    const int per = (n_kt + parts - 1) / parts;
+    j_begin += part * per;
+    n_kt = max(0, min(per, n_kt - part * per));
+  }
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -216,7 +232,7 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
       return true;
     };
     bool ok = warp_wait(q_full, 0, status, FA_ERR_MMA, abort_flag);
-    ok = ok && issue_s(0);
+    if (n_kt > 0) ok = ok && issue_s(0);
     if (n_kt > 1) ok = ok && issue_s(1);
     for (int i = 0; i < n_kt && ok; ++i) {
       const int s = i % ST;
@@ -318,26 +334,102 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
       tcgen05_before_sync();
       mbar_arrive(&p_full[i & 1]);
     }
-    if (ok && warp_wait(o_done, 0, status, FA_ERR_SOFTMAX, abort_flag)) {
-      tcgen05_after_sync();
-      const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-      unsigned char* my_stage = k_s + warp * 4096;      // every K and V stage has been consumed
+    // (a part without key tiles has nothing to wait for: its O counts as zero)
+    ok = ok && (n_kt == 0 || warp_wait(o_done, 0, status, FA_ERR_SOFTMAX, abort_flag));
+    if (ok) tcgen05_after_sync();
+    unsigned char* my_stage = k_s + warp * 4096;      // every K and V stage has been consumed
+    if (parts <= 1) {
+      if (ok) {
+        const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
 #pragma unroll
-      for (int c0 = 0; c0 < HD; c0 += 64) {
-        uint4 w[8];
+        for (int c0 = 0; c0 < HD; c0 += 64) {
+          uint4 w[8];
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          uint32_t v[32];
-          tmem_ld32(taddr_o + c0 + hh * 32, v);
-          tmem_ld_wait();
+          for (int hh = 0; hh < 2; ++hh) {
+            uint32_t v[32];
+            tmem_ld32(taddr_o + c0 + hh * 32, v);
+            tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; j += 8)
-            w[hh * 4 + j / 8] = make_uint4(pack2_bf16(__uint_as_float(v[j]) * inv, __uint_as_float(v[j + 1]) * inv),
-                                           pack2_bf16(__uint_as_float(v[j + 2]) * inv, __uint_as_float(v[j + 3]) * inv),
-                                           pack2_bf16(__uint_as_float(v[j + 4]) * inv, __uint_as_float(v[j + 5]) * inv),
-                                           pack2_bf16(__uint_as_float(v[j + 6]) * inv, __uint_as_float(v[j + 7]) * inv));
+            for (int j = 0; j < 32; j += 8)
+              w[hh * 4 + j / 8] = make_uint4(pack2_bf16(__uint_as_float(v[j]) * inv, __uint_as_float(v[j + 1]) * inv),
+                                             pack2_bf16(__uint_as_float(v[j + 2]) * inv, __uint_as_float(v[j + 3]) * inv),
+                                             pack2_bf16(__uint_as_float(v[j + 4]) * inv, __uint_as_float(v[j + 5]) * inv),
+                                             pack2_bf16(__uint_as_float(v[j + 6]) * inv, __uint_as_float(v[j + 7]) * inv));
+          }
+          store_rows_bf16(w, my_stage, lane, out, out_stride, row0 + warp * 32, row0 + nrows, head * HD + c0, INT_MAX);
         }
-        store_rows_bf16(w, my_stage, lane, out, out_stride, row0 + warp * 32, row0 + nrows, head * HD + c0, INT_MAX);
+      }
+    } else {
+      // This part's record: [head_dim + 2][128 rows] floats (a column of 128 rows is contiguous: the threads of a warp
+      // write and read neighbouring words): unnormalised O, then the reference point and the sum of each row.
+      constexpr int REC = (HD + 2) * FA_BM;
+      float* mine = partial + (static_cast<size_t>(slot0 + part) * n_heads + head) * REC;
+      if (ok) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < HD; c0 += 32) {
+          uint32_t v[32];
+          if (n_kt > 0) {
+            tmem_ld32(taddr_o + c0, v);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0u;
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) mine[(c0 + j) * FA_BM + r] = __uint_as_float(v[j]);
+        }
+        mine[HD * FA_BM + r] = m_ref;
+        mine[(HD + 1) * FA_BM + r] = l_run;
+        __threadfence();
+      }
+      // The four softmax warps meet (every one of them gets here, whatever happened before); the part that finds all
+      // others done adds the parts up, in the order of the parts whoever came last, and stores the rows.
+      __shared__ int s_last;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 0) {
+        int last = 0;
+        if (*abort_flag == 0) {
+          int* counter = counters + slot0 * n_heads + head;
+          last = atomicAdd(counter, 1) == parts - 1;
+          if (last) *counter = 0;               // ready for the next launch
+        }
+        s_last = last;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (s_last) {
+        __threadfence();
+        const float* first = partial + (static_cast<size_t>(slot0) * n_heads + head) * REC;
+        const size_t step = static_cast<size_t>(n_heads) * REC;          // from one part's record to the next
+        float m = -INFINITY;
+        for (int p = 0; p < parts; ++p) m = fmaxf(m, __ldcg(first + p * step + HD * FA_BM + r));
+        float l = 0.0f;
+        for (int p = 0; p < parts; ++p) {
+          const float mp = __ldcg(first + p * step + HD * FA_BM + r);
+          l += mp == -INFINITY ? 0.0f : __ldcg(first + p * step + (HD + 1) * FA_BM + r) * fa_exp2(mp - m);
+        }
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+#pragma unroll 1
+        for (int c0 = 0; c0 < HD; c0 += 64) {
+          uint4 w[8];
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            float acc[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc[j] = 0.0f;
+            for (int p = 0; p < parts; ++p) {
+              const float mp = __ldcg(first + p * step + HD * FA_BM + r);
+              const float sc = mp == -INFINITY ? 0.0f : fa_exp2(mp - m);
+              const float* src = first + p * step + static_cast<size_t>(c0 + hh * 32) * FA_BM + r;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) acc[j] = fmaf(sc, __ldcg(src + j * FA_BM), acc[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 32; j += 8)
+              w[hh * 4 + j / 8] = make_uint4(pack2_bf16(acc[j] * inv, acc[j + 1] * inv), pack2_bf16(acc[j + 2] * inv, acc[j + 3] * inv),
+                                             pack2_bf16(acc[j + 4] * inv, acc[j + 5] * inv), pack2_bf16(acc[j + 6] * inv, acc[j + 7] * inv));
+          }
+          store_rows_bf16(w, my_stage, lane, out, out_stride, row0 + warp * 32, row0 + nrows, head * HD + c0, INT_MAX);
+        }
       }
     }
   }
@@ -382,7 +474,8 @@ static int make_cache_map(CUtensorMap* map, const void* base, long long n_slots,
 template <int HD>
 int launch_prefill_tc05(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const int* block_table,
                         int max_blocks, const int* tiles, int n_tiles, void* out, int out_stride, int n_heads, int n_kv_heads,
-                        int page_shift, float scale, int window, int* status, cudaStream_t stream) {
+                        int page_shift, float scale, int window, int* status, const int* unit_parts, float* partial, int* counters,
+                        cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -393,7 +486,7 @@ int launch_prefill_tc05(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
   dim3 grid(n_heads, n_tiles);
   return launch_streaming(prefill_attention_tc05_kernel<HD>, grid, dim3(FA_THREADS), FA<HD>::SMEM, stream, mq, mk, mv, block_table,
                           max_blocks, reinterpret_cast<const int4*>(tiles), static_cast<bf16*>(out), out_stride, n_heads,
-                          n_kv_heads, page_shift, scale * 1.4426950408889634f, window, status);
+                          n_kv_heads, page_shift, scale * 1.4426950408889634f, window, status, unit_parts, partial, counters);
 }
 
 }  // namespace dl
@@ -403,11 +496,17 @@ int launch_prefill_tc05(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
 // patterns (a fresh cache is zero-filled); tiles: int32 [n_tiles, 4] = (request, first row, rows <= 128, first
 // position), 16-byte aligned. status: one device int, set to a nonzero code if a wait inside the kernel timed
 // out (left untouched otherwise). Other shapes return "unsupported": the caller has the mma.sync kernel.
+// unit_parts (or null: every tile is whole): int32 [n_tiles], for a tile whose keys are dealt over several entries of
+// `tiles` (equal in their four numbers) which part this entry is: part | parts << 8 | slot << 16, parts up to 255, 0 or
+// 1 = whole; the parts of a tile use the records slot .. slot + parts - 1 of `partial` (float32, (slots in use) *
+// n_heads * (head_dim + 2) * 128 elements) and the counters slot * n_heads .. + n_heads - 1 of `counters` (int32, zero
+// before the first launch; the kernel leaves them zero unless a wait timed out).
 DL_EXPORT int dl_paged_attention_prefill_tcgen05(const void* q, int q_stride, int n_rows, const void* k_cache,
                                                  const void* v_cache, long long n_pages, const int* block_table,
                                                  int max_blocks, const int* tiles, int n_tiles, void* out, int out_stride,
                                                  int n_heads, int n_kv_heads, int head_dim, int page_size, float scale,
-                                                 int window, int* status, cudaStream_t stream) {
+                                                 int window, int* status, const int* unit_parts, float* partial,
+                                                 int* counters, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   int page_shift = 0;
   while ((1 << page_shift) < page_size) ++page_shift;
@@ -416,7 +515,7 @@ DL_EXPORT int dl_paged_attention_prefill_tcgen05(const void* q, int q_stride, in
       (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) ||
       (reinterpret_cast<uintptr_t>(k_cache) & 15) || (reinterpret_cast<uintptr_t>(v_cache) & 15) ||
       (reinterpret_cast<uintptr_t>(tiles) & 15) || status == nullptr || n_rows <= 0 || n_pages <= 0 ||
-      n_pages * page_size > 0x7fffffffll)
+      n_pages * page_size > 0x7fffffffll || (unit_parts != nullptr && (partial == nullptr || counters == nullptr)))
     return DL_ERR_UNSUPPORTED;
   CUtensorMap mq, mk, mv;
   int rc = dl::make_q_map(&mq, q, n_rows, n_heads * head_dim, q_stride);
@@ -427,7 +526,7 @@ DL_EXPORT int dl_paged_attention_prefill_tcgen05(const void* q, int q_stride, in
   if (rc != 0) return rc;
   if (head_dim == 64)
     return dl::launch_prefill_tc05<64>(mq, mk, mv, block_table, max_blocks, tiles, n_tiles, out, out_stride, n_heads,
-                                       n_kv_heads, page_shift, scale, window, status, stream);
+                                       n_kv_heads, page_shift, scale, window, status, unit_parts, partial, counters, stream);
   return dl::launch_prefill_tc05<128>(mq, mk, mv, block_table, max_blocks, tiles, n_tiles, out, out_stride, n_heads,
-                                      n_kv_heads, page_shift, scale, window, status, stream);
+                                      n_kv_heads, page_shift, scale, window, status, unit_parts, partial, counters, stream);
 }

@@ -56,6 +56,93 @@ class QueryTilePlan:
 
 QUERY_TILES = QueryTilePlan()
 
+KEY_TILE = 64                 # keys per tile of the tcgen05 prompt attention
+PART_MIN_TILES = 24           # fewest key tiles of a part of a query tile (see QueryTileParts)
+TILE_PARTS_MAX = 8            # most parts a query tile's keys are dealt into
+PART_SLOTS = 64               # records of parts in scratch (one per part of every split tile of a step)
+TILE_PARTS = os.environ.get("DYNALM_TILE_PARTS", "1") != "0"      # 0: every query tile walks all of its keys alone
+
+
+class QueryTileParts:
+    """The step plan of the tcgen05 prompt attention: the prompt tiles of QueryTilePlan (without the single-token
+    requests at the head of the step, which go to the decode kernel), with the keys of long tiles dealt over several
+    entries. A block walks its tile's key tiles one after the other, so a step is as slow as its longest tile, and
+    a step with few tiles (a 512-row portion: four per head) leaves most SMs idle however long its context is. With
+    the work of all tiles spread evenly over two blocks per SM a block would take `ideal` key tiles; a tile longer
+    than 0.6 of that is cut into parts, each at least PART_MIN_TILES key tiles, at most TILE_PARTS_MAX of them, while
+    the step's PART_SLOTS records of scratch last (the longest tiles first). A part costs a block's set-up, its record
+    in scratch and its share of the merge, so short parts lose. Measured on B200 (32 heads of 64 / of 128, us per
+    launch, whole against dealt): 512 rows at 131,072 keys 1,347 -> 877 / 2,060 -> 1,130; at 32,768 keys 343 -> 234 /
+    528 -> 300; at 8,192 keys (parts of 31 key tiles) 90 -> 71 / 114 -> 88; at 4,096 keys (parts of 13 to 15) 48 -> 46 /
+    62 -> 61; at 2,048 keys (parts of 8 to 10) 28 -> 32 / 34 -> 41; a whole 2,048-token prompt with its eight longest
+    tiles in two parts of 9 to 16: 38 -> 48 / 43 -> 60. On the device: int32 [4 + 5 * cap]: a
+    header, cap tiles of 4 (as QueryTilePlan's), cap words part | parts << 8 | first record << 16 (0: a whole tile);
+    entries with the most key tiles first. What `fill` returns: (entries, records in use, cap)."""
+
+    def __init__(self, n_heads: int, window: int):
+        self.n_heads, self.window = int(n_heads), int(window)
+        self.name = f"attention_tile_parts:{n_heads}:{window}"
+
+    def ints(self, max_tokens: int, max_requests: int) -> int:
+        return 4 + 5 * (max_tokens // Q_TILE + max_requests + PART_SLOTS)
+
+    def key_tiles(self, pos0: int, rows: int) -> int:
+        lo = max(0, pos0 - self.window + 1) if self.window > 0 else 0
+        return (pos0 + rows - 1) // KEY_TILE - lo // KEY_TILE + 1
+
+    def deal(self, lengths) -> list:
+        """Parts per tile for tiles of `lengths` key tiles."""
+        slots = 2 * sm_count()
+        ideal = sum(lengths) * self.n_heads / slots
+        limit = max(0.6 * ideal, float(PART_MIN_TILES))
+        parts = [1] * len(lengths)
+        left = PART_SLOTS
+        for t in sorted(range(len(lengths)), key=lambda t: -lengths[t]):
+            want = min(int(-(-lengths[t] // limit)), TILE_PARTS_MAX, lengths[t] // PART_MIN_TILES)
+            if want > 1 and want <= left:
+                parts[t] = want
+                left -= want
+        return parts
+
+    def fill(self, host, shape):
+        cap = (len(host) - 4) // 5
+        lead = 0
+        while lead < len(shape.q_len) and shape.q_len[lead] == 1:
+            lead += 1
+        tiles = []
+        for r, (n, r0, start, slot) in enumerate(zip(shape.q_len, shape.q_start, shape.pos_start, shape.slots)):
+            if r < lead:
+                continue
+            for t0 in range(0, n, Q_TILE):
+                tiles.append((slot, r0 + t0, min(Q_TILE, n - t0), start + t0))
+        lengths = [self.key_tiles(t[3], t[2]) for t in tiles]
+        parts = self.deal(lengths) if tiles else []
+        entries, record = [], 0
+        for t, n_parts in zip(range(len(tiles)), parts):
+            per = -(-lengths[t] // n_parts)
+            for p in range(n_parts):
+                word = 0 if n_parts == 1 else (p | n_parts << 8 | record << 16)
+                entries.append((-min(per, lengths[t] - p * per), tiles[t], word))
+            if n_parts > 1:
+                record += n_parts
+        entries.sort(key=lambda e: e[0])
+        entries = entries[:cap]
+        flat = [v for e in entries for v in e[1]]
+        host[4:4 + len(flat)] = flat
+        host[4 + 4 * cap:4 + 4 * cap + len(entries)] = [e[2] for e in entries]
+        return len(entries), record, cap
+
+
+_tile_parts = {}
+
+
+def tile_parts_plan(spec) -> QueryTileParts:
+    key = (spec.num_heads, int(spec.get("window", 0)))
+    plan = _tile_parts.get(key)
+    if plan is None:
+        plan = _tile_parts[key] = QueryTileParts(*key)
+    return plan
+
 PART_CAP = 32            # most parts a row's keys are cut into
 PART_MIN_KEYS = 128      # fewest keys of a part
 DECODE_BLOCKS_PER_SM = int(os.environ.get("DYNALM_DECODE_BLOCKS", "2"))     # blocks of the decode kernel that fit an SM
@@ -275,10 +362,22 @@ def paged_attention(qkv: torch.Tensor, cache, ctx, out: torch.Tensor, spec, runt
         else:
             _decode_rows(qkv, cache, ctx, out, spec, runtime, leading)
     if n_tiles > 0:
-        kernel = (ops.paged_attention_prefill_tcgen05 if use_prefill_tcgen05(spec, qkv, out, cache.page_size)
-                  else ops.paged_attention_prefill)
-        kernel(qkv, k_cache, v_cache, cache.block_table, q_tiles, n_tiles, out, spec.num_heads,
-               spec.num_kv_heads, spec.head_dim, cache.page_size, float(spec.scale), spec.get("window", 0))
+        tcgen05 = use_prefill_tcgen05(spec, qkv, out, cache.page_size)
+        dealt = ctx.extras.get(tile_parts_plan(spec).name) if (tcgen05 and TILE_PARTS) else None
+        if dealt is not None and dealt[1][1] > 0:
+            # some tiles' keys are dealt over several blocks: the plan's own list of entries, and scratch for the parts
+            view, (entries, records, cap) = dealt
+            partial = runtime.flat(f"attn_tile_parts_{spec.num_heads}x{spec.head_dim}",
+                                   PART_SLOTS * spec.num_heads * (spec.head_dim + 2) * Q_TILE, torch.float32)
+            counters = runtime.flat(f"attn_tile_part_counters_{spec.num_heads}", PART_SLOTS * spec.num_heads, torch.int32)
+            ops.paged_attention_prefill_tcgen05(qkv, k_cache, v_cache, cache.block_table, view[4:4 + 4 * cap], entries, out,
+                                                spec.num_heads, spec.num_kv_heads, spec.head_dim, cache.page_size,
+                                                float(spec.scale), spec.get("window", 0),
+                                                unit_parts=view[4 + 4 * cap:4 + 5 * cap], partial=partial, counters=counters)
+        else:
+            kernel = ops.paged_attention_prefill_tcgen05 if tcgen05 else ops.paged_attention_prefill
+            kernel(qkv, k_cache, v_cache, cache.block_table, q_tiles, n_tiles, out, spec.num_heads,
+                   spec.num_kv_heads, spec.head_dim, cache.page_size, float(spec.scale), spec.get("window", 0))
     if side is not None:
         ops.stream_join(side)
     return True

@@ -41,7 +41,8 @@ _SIGNATURES = {
     "attention_prefill": {
         "dl_paged_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P]},
     "attention_prefill_tcgen05": {
-        "dl_paged_attention_prefill_tcgen05": [_P, _I, _I, _P, _P, _L, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P]},
+        "dl_paged_attention_prefill_tcgen05": [_P, _I, _I, _P, _P, _L, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P,
+                                               _P, _P, _P]},
     "gemm_skinny": {
         "dl_gemm_skinny": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _L, _P, _L, _P],
         "dl_gemm_skinny_qkv_rope": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P, _F, _I, _I, _I, _I, _P]},
@@ -678,10 +679,16 @@ PREFILL_TCGEN05_HEAD_DIMS = (64, 128)
 
 def paged_attention_prefill_tcgen05(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                                     q_tiles: torch.Tensor, n_tiles: int, out: torch.Tensor, n_heads: int, n_kv_heads: int,
-                                    head_dim: int, page_size: int, scale: float, window: int = 0) -> None:
+                                    head_dim: int, page_size: int, scale: float, window: int = 0,
+                                    unit_parts: Optional[torch.Tensor] = None, partial: Optional[torch.Tensor] = None,
+                                    counters: Optional[torch.Tensor] = None) -> None:
     """Flash attention of query tiles over the paged cache on tcgen05 tensor cores, bfloat16, head_dim 64 or
-    128, pages of at least 16 keys; see csrc/attention_prefill_tcgen05.cu. Arguments as paged_attention_prefill."""
-    _cuda(q, k_cache, v_cache, block_table, q_tiles, out)
+    128, pages of at least 16 keys; see csrc/attention_prefill_tcgen05.cu. Arguments as paged_attention_prefill.
+
+    unit_parts: int32 [n_tiles], when the keys of some tiles are dealt over several entries of q_tiles (see
+    kernels/attention.QueryTileParts): part | parts << 8 | scratch slot << 16 per entry, 0 = whole. Then partial:
+    float32, (slots in use) * n_heads * (head_dim + 2) * 128 elements; counters: int32, (slots in use) * n_heads, zero."""
+    _cuda(q, k_cache, v_cache, block_table, q_tiles, out, unit_parts, partial, counters)
     _rows_contiguous(q, "q")
     _rows_contiguous(out, "out")
     if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or v_cache.dtype != torch.bfloat16:
@@ -697,11 +704,16 @@ def paged_attention_prefill_tcgen05(q: torch.Tensor, k_cache: torch.Tensor, v_ca
         raise InvalidArgument("prefill attention (tcgen05): cache shape is not [pages, page_size, kv_heads, head_dim]")
     if q_tiles.dtype != torch.int32 or q_tiles.numel() < 4 * n_tiles:
         raise InvalidArgument("prefill attention (tcgen05): q_tiles must be int32 [n_tiles, 4]")
+    if unit_parts is not None:
+        if unit_parts.dtype != torch.int32 or unit_parts.numel() < n_tiles or partial is None or counters is None \
+                or partial.dtype != torch.float32 or counters.dtype != torch.int32:
+            raise InvalidArgument("prefill attention (tcgen05): unit_parts int32 [n_tiles] with float32 partial and int32 counters")
+        _status_companions.setdefault(q.device, {})[counters.data_ptr()] = counters
     check_limits("attention_prefill_tcgen05", pages=k_cache.shape[0], requests=block_table.shape[0], rows=q.shape[0])
     _check(_fn("attention_prefill_tcgen05", "dl_paged_attention_prefill_tcgen05")(
         _p(q), q.stride(0), q.shape[0], _p(k_cache), _p(v_cache), k_cache.shape[0], _p(block_table), block_table.stride(0),
         _p(q_tiles), n_tiles, _p(out), out.stride(0), n_heads, n_kv_heads, head_dim, page_size, scale, window,
-        _p(_status_word(q.device)), _stream()), "paged_attention_prefill_tcgen05")
+        _p(_status_word(q.device)), _p(unit_parts), _p(partial), _p(counters), _stream()), "paged_attention_prefill_tcgen05")
 
 
 def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
@@ -875,11 +887,17 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, status_to: Optional[torch.Te
                                          _p(status), _p(status_to), _stream()), "argmax")
 
 
+_status_companions: dict = {}      # device -> {address: counters that a kernel leaves nonzero only when a wait timed out}
+
+
 def clear_status(device) -> None:
-    """Zero the device's status word after its code has been reported."""
+    """Zero the device's status word after its code has been reported, and the counters that a kernel which gave up
+    may have left half counted (the prompt attention's parts)."""
     t = _tcgen05_status.get(torch.device(device))
     if t is not None:
         t.zero_()
+    for counters in _status_companions.get(torch.device(device), {}).values():
+        counters.zero_()
 
 
 def zero_pages(storage: torch.Tensor, fresh: torch.Tensor, n: int, group: int) -> None:

@@ -66,6 +66,8 @@ class PagedAttention:
         plans = [fast.QUERY_TILES]
         if fast.DECODE_PLANNED and fast.decode_uses_tensor_cores(self.spec):
             plans.append(fast.decode_units_plan(self.spec))
+        if fast.TILE_PARTS and self.spec.head_dim in ops.PREFILL_TCGEN05_HEAD_DIMS:
+            plans.append(fast.tile_parts_plan(self.spec))
         return plans
 
     def first_weights(self) -> torch.Tensor:

@@ -114,3 +114,44 @@ def test_decode_units_deal_keys_evenly():
     assert windowed.parts([64, 64]) == windowed.parts([64, 64]) and windowed.fill(np.zeros(4000, dtype=np.int32),
         StepShape([1, 1, 5], [0, 1, 2], [9999, 10, 0], [0, 1, 2], 7))[1] == 2
     fast.PLANNED_MIN_ROWS = before
+
+
+def test_query_tile_parts_deal_long_tiles(monkeypatch):
+    """The plan of the tcgen05 prompt attention: tiles far longer than an even share of the step's work are cut into
+    parts of at least 8 key tiles; short steps and steps with plenty of tiles are left whole; every entry names its
+    part, the number of parts and the first record of its tile."""
+    import numpy as np
+    from dynalm_b200.engine.step import StepShape
+    from dynalm_b200.kernels import attention as fast
+    monkeypatch.setattr(fast, "sm_count", lambda: 148)
+    plan = fast.QueryTileParts(n_heads=32, window=0)
+    assert plan.key_tiles(0, 128) == 2 and plan.key_tiles(1920, 128) == 32 and plan.key_tiles(64, 1) == 2
+    assert fast.QueryTileParts(8, 100).key_tiles(1000, 10) == 2              # a window: keys 901 .. 1009
+    # one 2,048-token prompt: 16 tiles of 2 .. 32 key tiles: parts of fewer than 24 key tiles do not pay, all whole
+    assert plan.deal([2 * (t + 1) for t in range(16)]) == [1] * 16
+    # a 512-row portion at 32,768 keys: four tiles of about 510 key tiles, 128 blocks for 296 places: in four parts each
+    assert plan.deal([506, 508, 510, 512]) == [4, 4, 4, 4]
+    # the same at 8,192 keys (125 key tiles: parts of 31) and at 4,096 (62: two parts of 31); at 2,048 whole
+    assert plan.deal([122, 124, 126, 128]) == [4, 4, 4, 4] and plan.deal([58, 60, 62, 64]) == [2, 2, 2, 2]
+    assert plan.deal([26, 28, 30, 32]) == [1, 1, 1, 1]
+    assert plan.deal([3, 4, 5]) == [1, 1, 1] and plan.deal([]) == []
+    assert plan.deal([2 * (t + 1) for t in range(64)]) == [1] * 64            # an 8,192-token prompt: enough tiles
+    assert sum(p for p in plan.deal([600] * 40) if p > 1) <= fast.PART_SLOTS   # no more parts than records
+    host = np.zeros(plan.ints(2048, 8), dtype=np.int32)
+    shape = StepShape([1, 1, 510], [0, 1, 2], [70, 9, 6000], [5, 6, 7], 512)   # two decode rows, then a portion at 6,000
+    entries, records, cap = plan.fill(host, shape)
+    assert cap == 2048 // 128 + 8 + fast.PART_SLOTS and records == 16 and entries == 4 * 4
+    tiles = host[4:4 + 4 * entries].reshape(-1, 4)
+    words = host[4 + 4 * cap:4 + 4 * cap + entries]
+    assert set(tiles[:, 0]) == {7} and tiles[:, 1].min() == 2                  # the prompt's rows only
+    seen = {}
+    for (slot, row0, rows, pos0), w in zip(tiles.tolist(), words.tolist()):
+        part, parts, record = w & 0xff, (w >> 8) & 0xff, w >> 16
+        seen.setdefault((row0, rows, pos0), []).append((part, parts, record))
+    assert len(seen) == 4
+    for key, got in seen.items():
+        parts = got[0][1]
+        assert (parts == 0 and got == [(0, 0, 0)]) or (sorted(p for p, _, _ in got) == list(range(parts)) and
+                                                       len({(n, r) for _, n, r in got}) == 1)
+    firsts = sorted(got[0][2] for got in seen.values() if got[0][1] > 1)
+    assert firsts == list(range(0, records, 4))                                # records of the split tiles do not overlap

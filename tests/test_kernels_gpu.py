@@ -438,6 +438,65 @@ def test_paged_attention_prefill_tcgen05_long_context(ops, heads, kvh, hd, page,
         assert err <= 2.5e-2, f"row {i} (position {p}): {err}"
 
 
+@pytest.mark.parametrize("heads,kvh,hd,page,window", [(4, 2, 64, 16, 0), (3, 1, 128, 32, 0), (2, 2, 64, 16, 900)])
+def test_paged_attention_prefill_tcgen05_keys_dealt_over_blocks(ops, heads, kvh, hd, page, window):
+    """The keys of a query tile dealt over several blocks that leave their parts in scratch, the last one adding them
+    up: a 128-row tile at the end of 3,000 keys in 3 parts, a 70-row tile in the middle in 2, a short tile whole;
+    twice over the same counters; against float64 and against the same tiles whole."""
+    g = torch.Generator(device="cpu").manual_seed(3 * hd + page)
+    L = 3000
+    k = torch.randn(L, kvh, hd, generator=g).to(torch.bfloat16)
+    v = torch.randn(L, kvh, hd, generator=g).to(torch.bfloat16)
+    k[5] *= 4.0
+    k[2700] *= 6.0
+    n_pages = -(-L // page)
+    perm = torch.randperm(n_pages + 3, generator=g)
+    table = perm[:n_pages].to(torch.int32).view(1, n_pages).contiguous()
+    kc = torch.zeros(n_pages + 3, page, kvh, hd, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    for b in range(n_pages):
+        n = min(page, L - b * page)
+        kc[table[0, b], :n] = k[b * page:b * page + n]
+        vc[table[0, b], :n] = v[b * page:b * page + n]
+    runs = [(L - 128, 128, 3), (1500, 70, 2), (40, 9, 1)]                 # (first position, rows, parts)
+    rows = [p0 + i for p0, n, _ in runs for i in range(n)]
+    whole, dealt, words, row0, record = [], [], [], 0, 0
+    for p0, n, parts in runs:
+        whole.append((0, row0, n, p0))
+        for p in range(parts):
+            dealt.append((0, row0, n, p0))
+            words.append(0 if parts == 1 else (p | parts << 8 | record << 16))
+        record += parts if parts > 1 else 0
+        row0 += n
+    q = torch.randn(len(rows), heads, hd, generator=g).to(torch.bfloat16)
+    for i, p in enumerate(rows):
+        if i % 3 == 0:
+            q[i] = (k[2700, 0].float() * 0.2).to(torch.bfloat16)
+        if i % 3 == 1:
+            q[i] = (k[5, 0].float() * 0.5).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(hd)
+    dev = [t.to(DEV) for t in (q.reshape(len(rows), heads * hd), kc, vc, table)]
+    ref_out = torch.zeros(len(rows), heads * hd, dtype=torch.bfloat16, device=DEV)
+    ops.paged_attention_prefill_tcgen05(*dev, torch.tensor(whole, dtype=torch.int32).to(DEV), len(whole), ref_out, heads, kvh, hd,
+                                        page, scale, window)
+    partial = torch.full((record * heads * (hd + 2) * 128,), float("nan"), dtype=torch.float32, device=DEV)
+    counters = torch.zeros(record * heads, dtype=torch.int32, device=DEV)
+    for again in range(2):
+        out = torch.zeros_like(ref_out)
+        ops.paged_attention_prefill_tcgen05(*dev, torch.tensor(dealt, dtype=torch.int32).to(DEV), len(dealt), out, heads, kvh, hd,
+                                            page, scale, window, unit_parts=torch.tensor(words, dtype=torch.int32).to(DEV),
+                                            partial=partial, counters=counters)
+        assert ops.gemm_tcgen05_status() == 0, "a wait inside the kernel timed out"
+        assert int(counters.abs().sum()) == 0, "the counters are left at zero"
+        got = out.double().cpu().reshape(len(rows), heads, hd)
+        for i, p in enumerate(rows):
+            ref = _attention_ref(q[i].double(), k[:p + 1].double(), v[:p + 1].double(), scale, window)
+            err = (got[i] - ref).abs().max().item()
+            assert err <= 2.5e-2, f"pass {again} row {i} (position {p}): {err}"
+        assert (out.float() - ref_out.float()).abs().max().item() <= 2e-2       # the same tiles whole: bf16 rounding apart
+        assert torch.equal(out[128 + 70:], ref_out[128 + 70:])                   # the whole tile among them: the same bits
+
+
 def test_paged_attention_prefill_tcgen05_refuses_other_shapes(ops):
     q = torch.zeros(4, 2 * 48, dtype=torch.bfloat16, device=DEV)
     kc = torch.zeros(3, 16, 1, 48, dtype=torch.bfloat16, device=DEV)
