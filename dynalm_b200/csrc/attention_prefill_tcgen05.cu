@@ -82,7 +82,8 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
                               const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table, int max_blocks,
                               const int4* __restrict__ tiles, bf16* __restrict__ out, int out_stride, int n_heads,
                               int n_kv_heads, int page_shift, float scale_log2, int window, int* __restrict__ status,
-                              const int* __restrict__ unit_parts, float* __restrict__ partial, int* __restrict__ counters) {
+                              const int* __restrict__ unit_parts, float* __restrict__ partial, int* __restrict__ counters,
+                              int part_records) {
   constexpr int BN = FA<HD>::BN, DB = FA<HD>::DB;
   constexpr int ST = FA<HD>::STAGES;
   constexpr uint32_t Q_BYTES = FA<HD>::Q_BYTES, KV_BYTES = FA<HD>::KV_BYTES;
@@ -120,7 +121,7 @@ prefill_attention_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const _
   const int lo_tile = window > 0 ? max(0, pos0 - window + 1) : 0;      // the first key any row of the tile reads
   int j_begin = lo_tile / BN, n_kt = pos_last / BN - j_begin + 1;
   // this block's share of the tile's keys: part `part` of `parts` (word = part | parts << 8 | first scratch slot << 16)
-  const int part_word = unit_parts != nullptr ? unit_parts[blockIdx.y] : 0;
+  const int part_word = unit_parts != nullptr ? ck_part_word(unit_parts[blockIdx.y], part_records) : 0;
   const int part = part_word & 0xff, parts = (part_word >> 8) & 0xff, slot0 = part_word >> 16;
   if (parts > 1) {
     const int per = (n_kt + parts - 1) / parts;
@@ -475,7 +476,7 @@ template <int HD>
 int launch_prefill_tc05(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const int* block_table,
                         int max_blocks, const int* tiles, int n_tiles, void* out, int out_stride, int n_heads, int n_kv_heads,
                         int page_shift, float scale, int window, int* status, const int* unit_parts, float* partial, int* counters,
-                        cudaStream_t stream) {
+                        int part_records, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -486,7 +487,7 @@ int launch_prefill_tc05(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
   dim3 grid(n_heads, n_tiles);
   return launch_streaming(prefill_attention_tc05_kernel<HD>, grid, dim3(FA_THREADS), FA<HD>::SMEM, stream, mq, mk, mv, block_table,
                           max_blocks, reinterpret_cast<const int4*>(tiles), static_cast<bf16*>(out), out_stride, n_heads,
-                          n_kv_heads, page_shift, scale * 1.4426950408889634f, window, status, unit_parts, partial, counters);
+                          n_kv_heads, page_shift, scale * 1.4426950408889634f, window, status, unit_parts, partial, counters, part_records);
 }
 
 }  // namespace dl
@@ -500,13 +501,14 @@ int launch_prefill_tc05(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
 // `tiles` (equal in their four numbers) which part this entry is: part | parts << 8 | slot << 16, parts up to 255, 0 or
 // 1 = whole; the parts of a tile use the records slot .. slot + parts - 1 of `partial` (float32, (slots in use) *
 // n_heads * (head_dim + 2) * 128 elements) and the counters slot * n_heads .. + n_heads - 1 of `counters` (int32, zero
-// before the first launch; the kernel leaves them zero unless a wait timed out).
+// before the first launch; the kernel leaves them zero unless a wait timed out). part_records: how many records
+// `partial` holds (what a checked build compares the words with).
 DL_EXPORT int dl_paged_attention_prefill_tcgen05(const void* q, int q_stride, int n_rows, const void* k_cache,
                                                  const void* v_cache, long long n_pages, const int* block_table,
                                                  int max_blocks, const int* tiles, int n_tiles, void* out, int out_stride,
                                                  int n_heads, int n_kv_heads, int head_dim, int page_size, float scale,
                                                  int window, int* status, const int* unit_parts, float* partial,
-                                                 int* counters, cudaStream_t stream) {
+                                                 int* counters, int part_records, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   int page_shift = 0;
   while ((1 << page_shift) < page_size) ++page_shift;
@@ -526,7 +528,7 @@ DL_EXPORT int dl_paged_attention_prefill_tcgen05(const void* q, int q_stride, in
   if (rc != 0) return rc;
   if (head_dim == 64)
     return dl::launch_prefill_tc05<64>(mq, mk, mv, block_table, max_blocks, tiles, n_tiles, out, out_stride, n_heads,
-                                       n_kv_heads, page_shift, scale, window, status, unit_parts, partial, counters, stream);
+                                       n_kv_heads, page_shift, scale, window, status, unit_parts, partial, counters, part_records, stream);
   return dl::launch_prefill_tc05<128>(mq, mk, mv, block_table, max_blocks, tiles, n_tiles, out, out_stride, n_heads,
-                                      n_kv_heads, page_shift, scale, window, status, unit_parts, partial, counters, stream);
+                                      n_kv_heads, page_shift, scale, window, status, unit_parts, partial, counters, part_records, stream);
 }

@@ -25,6 +25,7 @@
 #define DL_CK_PAGE 5      // a page id outside the pool (-1: a page that a window has given back)
 #define DL_CK_PLACE 6     // a place in the chosen ids outside the array
 #define DL_CK_TILE 7      // a query tile whose rows lie outside the step
+#define DL_CK_PART 8      // a part of a query tile outside its parts, or its records outside the scratch
 
 namespace dl {
 
@@ -81,8 +82,20 @@ __device__ __forceinline__ int4 ck_tile(int4 t) {
   return ok ? t : make_int4(0, 0, 0, 0);
 }
 
+// a word that names one part of a query tile whose keys are dealt over blocks (part | parts << 8 | first record << 16):
+// the part among its parts, its records among the `records` of scratch; after a violation 0 (a whole tile), so that
+// nothing is written to scratch
+__device__ __forceinline__ int ck_part_word(int word, int records) {
+  const int part = word & 0xff, parts = (word >> 8) & 0xff, first = word >> 16;
+  if (parts <= 1) return word;
+  const bool ok = check_range(DL_CK_PART, part, 0, parts) && check_range(DL_CK_PART, static_cast<long long>(first) + parts, 0,
+                                                                        static_cast<long long>(records) + 1);
+  return ok ? word : 0;
+}
+
 #else
 
+__device__ __forceinline__ int ck_part_word(int word, int) { return word; }
 __device__ __forceinline__ int ck_token(int id, int) { return id; }
 __device__ __forceinline__ int ck_row(int r, int) { return r; }
 __device__ __forceinline__ int ck_row(int r) { return r; }

@@ -42,7 +42,7 @@ _SIGNATURES = {
         "dl_paged_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P]},
     "attention_prefill_tcgen05": {
         "dl_paged_attention_prefill_tcgen05": [_P, _I, _I, _P, _P, _L, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P,
-                                               _P, _P, _P]},
+                                               _P, _P, _I, _P]},
     "gemm_skinny": {
         "dl_gemm_skinny": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _L, _P, _L, _P],
         "dl_gemm_skinny_qkv_rope": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P, _F, _I, _I, _I, _I, _P]},
@@ -85,6 +85,7 @@ CHECK_CODES = {
     5: "a page id outside the pool",
     6: "a place outside the array of chosen ids",
     7: "a query tile whose rows lie outside the step",
+    8: "a part of a query tile outside its parts, or its records outside the scratch",
 }
 
 
@@ -704,16 +705,19 @@ def paged_attention_prefill_tcgen05(q: torch.Tensor, k_cache: torch.Tensor, v_ca
         raise InvalidArgument("prefill attention (tcgen05): cache shape is not [pages, page_size, kv_heads, head_dim]")
     if q_tiles.dtype != torch.int32 or q_tiles.numel() < 4 * n_tiles:
         raise InvalidArgument("prefill attention (tcgen05): q_tiles must be int32 [n_tiles, 4]")
+    records = 0
     if unit_parts is not None:
         if unit_parts.dtype != torch.int32 or unit_parts.numel() < n_tiles or partial is None or counters is None \
                 or partial.dtype != torch.float32 or counters.dtype != torch.int32:
             raise InvalidArgument("prefill attention (tcgen05): unit_parts int32 [n_tiles] with float32 partial and int32 counters")
+        records = min(partial.numel() // (n_heads * (head_dim + 2) * 128), counters.numel() // n_heads)
         _status_companions.setdefault(q.device, {})[counters.data_ptr()] = counters
     check_limits("attention_prefill_tcgen05", pages=k_cache.shape[0], requests=block_table.shape[0], rows=q.shape[0])
     _check(_fn("attention_prefill_tcgen05", "dl_paged_attention_prefill_tcgen05")(
         _p(q), q.stride(0), q.shape[0], _p(k_cache), _p(v_cache), k_cache.shape[0], _p(block_table), block_table.stride(0),
         _p(q_tiles), n_tiles, _p(out), out.stride(0), n_heads, n_kv_heads, head_dim, page_size, scale, window,
-        _p(_status_word(q.device)), _p(unit_parts), _p(partial), _p(counters), _stream()), "paged_attention_prefill_tcgen05")
+        _p(_status_word(q.device)), _p(unit_parts), _p(partial), _p(counters), records, _stream()),
+        "paged_attention_prefill_tcgen05")
 
 
 def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,

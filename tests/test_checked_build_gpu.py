@@ -80,6 +80,18 @@ expect(lambda: ops.embed(tab, ids, x), ["a token id outside the vocabulary", "10
 rows = torch.tensor([0, 3], dtype=torch.int32, device=dev)
 y = torch.zeros(2, 32, device=dev)
 expect(lambda: ops.rmsnorm(x, torch.ones(32, device=dev), 1e-5, y, rows=rows), ["a gathered row outside the rows of the step", "3 is not in [0, 3)"])
+# the prompt attention's part words: a tile whose parts name records beyond the scratch is run whole instead, and said
+table[0, 2], table[1, 2] = 2, 6
+qp = torch.randn(64, heads * hd, device=dev).to(torch.bfloat16)
+outp = torch.zeros_like(qp)
+tiles = torch.tensor([[0, 0, 64, 0], [0, 0, 64, 0]], dtype=torch.int32, device=dev)
+words = torch.tensor([0 | 2 << 8 | 3 << 16, 1 | 2 << 8 | 3 << 16], dtype=torch.int32, device=dev)       # records 3 and 4 of 4
+partial = torch.zeros(4 * heads * (hd + 2) * 128, device=dev)
+counters = torch.zeros(4 * heads, dtype=torch.int32, device=dev)
+expect(lambda: ops.paged_attention_prefill_tcgen05(qp, kc, vc, table, tiles, 2, outp, heads, kvh, hd, page, 0.125,
+                                                    unit_parts=words, partial=partial, counters=counters),
+       ["a part of a query tile", "5 is not in [0, 5)"])
+assert float(partial.abs().sum()) == 0.0 and int(counters.abs().sum()) == 0        # nothing was written beyond (or into) the scratch
 torch.cuda.synchronize()
 print("checked build ok")
 '''
