@@ -232,7 +232,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         const float4* my_angles = rope.angles != nullptr && live
                                       ? reinterpret_cast<const float4*>(rope.angles + static_cast<size_t>(row) * (hd / 2))
                                       : nullptr;       // two (cos, sin) pairs per 16-byte load
-        for (int h0 = 0; h0 < T5_BN && n0 + h0 < N; h0 += hd) {
+        // A warp past the last row has nothing to read or write; a row past it inside a live warp is carried along
+        // unrotated (its sines and cosines are not looked up or worked out).
+        const bool warp_live = row - lane < M;
+        for (int h0 = 0; warp_live && h0 < T5_BN && n0 + h0 < N; h0 += hd) {
           const int head = (n0 + h0) / hd;                // q heads, then k heads, then v heads
           const bool rotated = head < rope.n_heads + rope.n_kv_heads;
           bf16* dst = nullptr;
@@ -252,7 +255,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             tmem_ld_wait();
             // (cos, sin) of the piece's 32 pairs, two pairs per float4: all requested before any is used
             float4 cs[16];
-            if (rotated) {
+            if (rotated && live) {
               if (my_angles != nullptr) {
 #pragma unroll
                 for (int i = 0; i < 16; ++i) cs[i] = my_angles[piece * 16 + i];

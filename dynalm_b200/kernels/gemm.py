@@ -96,6 +96,16 @@ def tcgen05_ok(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, features: in
     return tiles >= 96
 
 
+def rotating_epilogue_pays(rows: int, features: int, head_dim: int) -> bool:
+    """Whether the q | k | v product over `rows` rows should rotate and write the cache in its own epilogue (the
+    tcgen05 kernel): the head size is one it takes and its tiles make enough rounds over the SMs to hide that
+    epilogue (ops.QKV_ROPE_TCGEN05_MIN_ROUNDS); otherwise the product is followed by the rotation kernel."""
+    if head_dim not in ops.QKV_ROPE_TCGEN05_HEAD_DIMS:
+        return False
+    tiles = -(-rows // 128) * -(-features // 256)
+    return tiles >= ops.QKV_ROPE_TCGEN05_MIN_ROUNDS[head_dim] * sm_count()
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
            out_scale: float = 1.0) -> torch.Tensor:
     """out[M, N] = (x[M, K] @ w[N, K].T + bias[N]) * out_scale. x and w share a dtype; out may be

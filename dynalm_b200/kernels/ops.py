@@ -574,6 +574,15 @@ def paged_attention_decode_planned(q: torch.Tensor, k_cache: torch.Tensor, v_cac
 
 
 QKV_ROPE_TCGEN05_HEAD_DIMS = (64, 128)
+# From how many rounds of 256-wide tiles over the SMs the tcgen05 product with the rotating epilogue is ahead of the
+# product followed by the rotation kernel. The rotating epilogue of a tile takes about 10 us more than the plain one
+# and only hides behind the next tile of the same block. Measured in CUDA graphs (us: fused / own product + rotation /
+# library product + rotation), head size 128, width 3072 with 24+8+8 heads: 544 rows 27.7 / 21.1 / 20.4, 1,024 rows
+# 43.8 / 35.5 / 29.8, 2,048 rows (2.2 rounds) 63.1 / 58.1 / 55.0, 4,096 rows 103 / 112 / 102; width 4096 with 32+8+8
+# heads: 1,024 rows 58.4 / 51.2 / 44.0, 2,048 rows (2.6 rounds) 90.1 / 94.7 / 85.4, 4,096 rows 169 / 191 / 188. At
+# head size 64 (width 2048, 32+8+8 heads) the two are level from 544 rows on (15.6 / 15.4, 27.5 / 28.8 at 2,048 rows),
+# and one launch less is worth more to a step that waits for the host.
+QKV_ROPE_TCGEN05_MIN_ROUNDS = {64: 0.0, 128: 2.4}
 
 
 def rope_angles(positions: torch.Tensor, inv_freq: torch.Tensor, pos_scale: float, rows: int, out: torch.Tensor) -> None:

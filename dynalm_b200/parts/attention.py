@@ -111,15 +111,17 @@ class PagedAttention:
 
     def _fused_projection_applies(self, x: torch.Tensor, table) -> bool:
         """bfloat16, no bias, the rotation covers the whole head, and either few rows (the weight-streaming
-        kernel) or enough tiles for the tcgen05 kernel with a head size it takes."""
+        kernel) or enough tiles for the tcgen05 kernel with a head size it takes (ops.QKV_ROPE_TCGEN05_MIN_ROUNDS)."""
         if not (table is not None and table[0] is not None and table[1] == self.spec.head_dim and self.b_qkv is None
                 and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0):
             return False
         if x.shape[0] <= ops.SKINNY_FAST_ROWS:
             return True
-        from ..kernels.gemm import tcgen05_ok
+        from ..kernels.gemm import rotating_epilogue_pays, tcgen05_ok
+        if not rotating_epilogue_pays(x.shape[0], self.w_qkv.shape[0], self.spec.head_dim):
+            return False
         qkv = self.rt.buffer("attn_qkv", (x.shape[0], self.q_width + 2 * self.kv_width))
-        return self.spec.head_dim in ops.QKV_ROPE_TCGEN05_HEAD_DIMS and tcgen05_ok(x, self.w_qkv, qkv, self.w_qkv.shape[0])
+        return tcgen05_ok(x, self.w_qkv, qkv, self.w_qkv.shape[0])
 
     def _attend_and_project(self, qkv: torch.Tensor, cache, ctx, rows: int) -> torch.Tensor:
         s, rt = self.spec, self.rt

@@ -50,6 +50,18 @@ def test_the_tcgen05_product_needs_96_tiles_at_its_narrowest_width():
     assert not ok(2048, 2052)               # rows of the output must be 16-byte aligned
 
 
+def test_the_rotating_epilogue_needs_rounds_of_tiles_at_head_size_128():
+    # head size 64: wherever the tcgen05 product runs
+    assert gemm.rotating_epilogue_pays(17, 3072, 64) and gemm.rotating_epilogue_pays(2048, 3072, 64)
+    # head size 128: from 2.4 rounds of 256-wide tiles over 148 SMs (356 tiles)
+    assert not gemm.rotating_epilogue_pays(544, 5120, 128)           # 5 x 20 tiles: a 512-token portion of the 3B shape
+    assert not gemm.rotating_epilogue_pays(2048, 5120, 128)          # 16 x 20 = 320
+    assert gemm.rotating_epilogue_pays(2048, 6144, 128)              # 16 x 24 = 384
+    assert gemm.rotating_epilogue_pays(4096, 5120, 128)
+    # a head size the epilogue does not take
+    assert not gemm.rotating_epilogue_pays(4096, 5120, 96)
+
+
 def test_decode_attention_splits():
     # the 1B shape at 2,048 keys: powers of two (the splits of a row are one thread-block cluster), about one block per SM
     assert [attention.decode_splits(rows, 32, 8, 2048, sms=148) for rows in (1, 2, 4, 6, 8, 10)] == [8, 4, 4, 2, 2, 2]
