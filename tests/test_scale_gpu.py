@@ -2,7 +2,8 @@
 head size 64 in groups of four, head size 128 in groups of three) with random weights, against the plain implementation: whole prompts, portions, and mixed steps of up to four
 live requests in a pool so small that pages are used again. At these sizes the bfloat16 engine runs what the tiny
 configurations cannot reach: the tcgen05 products (also the one in which two blocks share tiles of W, from 1,184
-rows), the tcgen05 prompt attention over many query tiles, and the library product for the row counts in between.
+rows), the tcgen05 prompt attention over many query tiles (in the 3,500-token prompt brought in portions of 512 also
+with the keys of a query tile dealt over several blocks), and the library product for the row counts in between.
 
 32-bit: logits within 1e-4 of each row's largest logit. bfloat16: what the reference asks of its own GPU path
 against 32-bit, a mean KL divergence of at most 0.0025 and the same most likely token in at least 99 rows of 100
@@ -34,6 +35,11 @@ SHAPES = {"1B": CFG, "3B": CFG_3B}
 LENGTHS = [300, 170, 230, 129, 90, 200]
 LONG = 1300
 LONG_WANT = list(range(LONG - 6, LONG))
+# A prompt long enough for the keys of its last query tiles to be dealt over several blocks (from 48 key tiles of
+# 64), brought in portions of 512; wanted: rows of the first portion with dealt keys and of the last.
+FAR = 3500
+FAR_PORTION = 512
+FAR_WANT = [3071, 3072, 3199, 3327, 3328] + list(range(FAR - 4, FAR))
 
 
 @pytest.fixture(scope="module", params=sorted(SHAPES))
@@ -72,7 +78,14 @@ def _plans():
         pos += n
     short = {r: t for r, t in reqs.items() if r != "long"}
     mixed = plan_mixed(short, seed=8, max_live=4, decode_tail=6, sizes=(2, 33, 130, 64, 257))
-    return reqs, {"whole": whole, "cut": cut, "mixed": mixed}
+    far = random_requests(CFG["vocab_size"], [FAR], seed=5)["r0"]
+    reqs["far"] = far
+    portions = Plan()
+    for pos in range(0, FAR, FAR_PORTION):
+        n = min(FAR_PORTION, FAR - pos)
+        portions.add([("far", far[pos:pos + n], pos, [w - pos for w in FAR_WANT if pos <= w < pos + n])],
+                     end=["far"] if pos + n == FAR else [])
+    return reqs, {"whole": whole, "cut": cut, "mixed": mixed, "portions": portions}
 
 
 @pytest.fixture(scope="module")
@@ -101,9 +114,13 @@ def test_layer_shapes_against_plain(dtype, shape, folder, plain):
     for what, plan in plans.items():
         need = plan.max_live_tokens(64)
         library_before = gemm.LIBRARY_CALLS
-        built = build(folder, dtype=dtype, kv_tokens=need, max_batch_tokens=1408, max_requests=4, context=2048)
+        built = build(folder, dtype=dtype, kv_tokens=need, max_batch_tokens=1408, max_requests=4,
+                      context=4096 if what == "portions" else 2048)
         got = run_plan_in_process(built.step_fn, plan)
         assert built.cache.free_pages == built.cache.num_pages
+        if what == "portions" and dtype == "bfloat16":
+            dealt = [key for key in built.runtime._buffers if str(key[0]).startswith("attn_tile_parts_")]
+            assert dealt, "no query tile had its keys dealt over several blocks"
         kl, top1 = kl_and_top1(plan, got, plain, near_tie=1e-4 if dtype == "float32" else 0.05)
         if dtype == "float32":
             worst = compare(plan, got, plain, 0.0, 1e-4, f"{shape}/{dtype}/{what}")
