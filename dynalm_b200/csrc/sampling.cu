@@ -56,12 +56,27 @@ argmax_part_kernel(const float* __restrict__ logits, int ld, int vocab, float* _
   __shared__ float bv[8];
   __shared__ int bi[8];
   const int r = blockIdx.y, part = blockIdx.x;
-  const int per = (vocab + ARGMAX_PARTS - 1) / ARGMAX_PARTS;
+  const int per = ((vocab + ARGMAX_PARTS - 1) / ARGMAX_PARTS + 3) & ~3;      // slices start at multiples of 4
   const int b = min(vocab, part * per), e = min(vocab, b + per);
   const float* row = logits + static_cast<size_t>(r) * ld;
   float best = -INFINITY;
   int idx = 0x7fffffff;
-  for (int i = b + threadIdx.x; i < e; i += blockDim.x) {
+  int i0 = b;
+  if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    // 16 bytes a load, a thread's loads of the slice all issued before the first comparison; within a thread the
+    // indices still rise, so the strict comparison keeps the lowest index among equal values
+    const int e4 = b + ((e - b) & ~3);
+#pragma unroll 4
+    for (int i = b + threadIdx.x * 4; i < e4; i += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(row + i);
+      if (v.x > best) { best = v.x; idx = i; }
+      if (v.y > best) { best = v.y; idx = i + 1; }
+      if (v.z > best) { best = v.z; idx = i + 2; }
+      if (v.w > best) { best = v.w; idx = i + 3; }
+    }
+    i0 = e4;
+  }
+  for (int i = i0 + threadIdx.x; i < e; i += blockDim.x) {
     const float v = row[i];
     if (v > best) { best = v; idx = i; }
   }

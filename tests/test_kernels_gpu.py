@@ -225,12 +225,17 @@ def test_paged_attention_generic(ops, dtype, heads, kvh, hd, page, window):
 
 def test_argmax_ties_and_sizes(ops):
     g = torch.Generator(device="cpu").manual_seed(7)
-    for vocab in (7, 499, 128256):
+    # 50,001: rows that do not start on 16 bytes and a last slice that is no multiple of 4 (the scan's scalar ends)
+    for vocab in (7, 499, 50001, 50004, 128256):
         logits = torch.randn(5, vocab, generator=g)
         logits[1, 3] = logits[1].max() + 1
         logits[1, min(6, vocab - 1)] = logits[1, 3]              # a tie: the lowest id wins
         logits[2, vocab - 1] = 50.0
         logits[3, 0] = 50.0
+        if vocab > 45000:                                        # a tie between two slices of the scan
+            logits[4, 10001] = 60.0
+            logits[4, 40002] = 60.0
+            logits[2, vocab - 3] = 50.0                          # and one inside the last slice's ragged end
         d = logits.to(DEV)
         out = torch.empty(5, dtype=torch.int32, device=DEV)
         ops.argmax(d, out)
