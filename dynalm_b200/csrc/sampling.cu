@@ -6,6 +6,8 @@
 // (Sampler::distribution and ::draw, :120-137,209-220). The uniform u comes from the host, where the
 // per-request xoshiro256** generator lives. The reference samples on the host from downloaded logits;
 // here only the chosen ids leave the device.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace dl {
@@ -142,66 +144,116 @@ argmax_of_parts_kernel(const float* __restrict__ pv, const int* __restrict__ pi,
   }
 }
 
-// One block per row. Each thread owns a contiguous run of ids so that the walk is in id order.
+// A thread-block cluster per row (one block for a small vocabulary, up to eight for a large one). Thread
+// g = block's rank * SAMPLE_THREADS + thread owns the ids [g * per, (g + 1) * per), so that runs, threads and blocks
+// are all in id order. Three passes over the row, each thread over its own run (the second and third find it in the
+// caches): the largest logit (block tree, then the blocks' results read from one another's shared memory); the mass
+// of each run in double and its place in the running total (a scan over the block, then the blocks' totals read
+// the same way); the walk down the one run in which u * total falls. That run is the last whose start is at or
+// below u * total; the walk inside it subtracts id by id as the reference does, and where rounding leaves it
+// unfinished at the run's end it goes on to the next id with any mass, else the last id.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
-sample_temperature_kernel(const float* __restrict__ logits, int ld, int vocab,
+sample_temperature_kernel(const float* __restrict__ logits, int ld, int vocab, int per,
                           const float* __restrict__ temperature, const double* __restrict__ uniform,
                           int* __restrict__ out) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
   __shared__ float red[33];
-  __shared__ double seg[SAMPLE_THREADS];
-  __shared__ int chosen;
-  const int r = blockIdx.x;
+  __shared__ float block_m;          // read by the other blocks of the cluster
+  __shared__ double block_total;     // likewise
+  __shared__ double warp_before[32];
+  __shared__ int winner;             // the first block's copy is the cluster's
+  const int nblocks = static_cast<int>(cluster.num_blocks());
+  const int rank = static_cast<int>(cluster.block_rank());
+  const int r = blockIdx.x / nblocks;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float* row = logits + static_cast<size_t>(r) * ld;
   const float inv_t = 1.0f / temperature[r];
-  float m = -INFINITY;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) m = fmaxf(m, row[i]);
-  m = block_max(m, red);
+  const int g = rank * SAMPLE_THREADS + static_cast<int>(threadIdx.x);
+  const int b = static_cast<int>(min(static_cast<long long>(vocab), static_cast<long long>(g) * per));
+  const int e = min(vocab, b + per);
+  const bool vec = (reinterpret_cast<uintptr_t>(row) & 15) == 0;      // per is a multiple of 4, so b is one too
 
-  const int per = (vocab + blockDim.x - 1) / blockDim.x;
-  const int b = min(vocab, static_cast<int>(threadIdx.x) * per), e = min(vocab, b + per);
-  double s = 0.0;
-  for (int i = b; i < e; ++i) s += static_cast<double>(expf((row[i] - m) * inv_t));
-  seg[threadIdx.x] = s;
-  if (threadIdx.x == 0) chosen = -1;
-  __syncthreads();
-  // thread 0 finds the segment: a serial scan of 1024 doubles keeps the order of the reference's walk
-  __shared__ int seg_idx;
-  __shared__ double seg_rest;
+  float m = -INFINITY;
+  {
+    int i = b;
+    if (vec)
+      for (; i + 4 <= e; i += 4) {
+        const float4 v = *reinterpret_cast<const float4*>(row + i);
+        m = fmaxf(fmaxf(m, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
+      }
+    for (; i < e; ++i) m = fmaxf(m, row[i]);
+  }
+  m = block_max(m, red);
   if (threadIdx.x == 0) {
-    double total = 0.0;
-    for (int i = 0; i < blockDim.x; ++i) total += seg[i];
-    double u = uniform[r] * total;
-    int k = 0;
-    for (; k < blockDim.x - 1; ++k) {
-      if (u - seg[k] < 0.0) break;
-      u -= seg[k];
+    block_m = m;
+    winner = 0;
+  }
+  cluster.sync();
+  for (int c = 0; c < nblocks; ++c) m = fmaxf(m, *cluster.map_shared_rank(&block_m, c));
+
+  double s = 0.0;
+  {
+    int i = b;
+    if (vec)
+      for (; i + 4 <= e; i += 4) {
+        const float4 v = *reinterpret_cast<const float4*>(row + i);
+        s += static_cast<double>(expf((v.x - m) * inv_t));
+        s += static_cast<double>(expf((v.y - m) * inv_t));
+        s += static_cast<double>(expf((v.z - m) * inv_t));
+        s += static_cast<double>(expf((v.w - m) * inv_t));
+      }
+    for (; i < e; ++i) s += static_cast<double>(expf((row[i] - m) * inv_t));
+  }
+  // running totals in id order: over the warp, over the block's warps, over the cluster's blocks
+  double incl = s;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const double v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  if (lane == 31) warp_before[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    const double w = warp_before[lane];
+    double wi = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const double v = __shfl_up_sync(0xffffffffu, wi, o);
+      if (lane >= o) wi += v;
     }
-    seg_idx = k;
-    seg_rest = u;
+    warp_before[lane] = wi - w;
+    if (lane == 31) block_total = wi;
   }
   __syncthreads();
-  if (threadIdx.x == seg_idx) {
-    double u = seg_rest;
+  const double before_in_block = warp_before[warp] + (incl - s);
+  cluster.sync();
+  double before = 0.0, total = 0.0;
+  for (int c = 0; c < nblocks; ++c) {
+    const double t = *cluster.map_shared_rank(&block_total, c);
+    if (c < rank) before += t;
+    total += t;
+  }
+  const double target = uniform[r] * total;
+  const double begin = before + before_in_block;
+  if (g == 0 || (s > 0.0 && begin <= target)) atomicMax(cluster.map_shared_rank(&winner, 0), g);
+  cluster.sync();
+  if (g == *cluster.map_shared_rank(&winner, 0)) {
+    double u = target - begin;
     int pick = -1;
     for (int i = b; i < e; ++i) {
       u -= static_cast<double>(expf((row[i] - m) * inv_t));
       if (u < 0.0) { pick = i; break; }
     }
-    chosen = pick;
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int pick = chosen;
     if (pick < 0) {
-      // rounding left u >= 0 at the end of the segment: the next id with any mass, else the last id
       pick = vocab - 1;
-      const int e_idx = min(vocab, (seg_idx + 1) * per);
-      for (int i = e_idx; i < vocab; ++i) {
+      for (int i = e; i < vocab; ++i) {
         if (expf((row[i] - m) * inv_t) > 0.0f) { pick = i; break; }
       }
     }
     out[r] = pick;
   }
+  cluster.sync();        // nobody leaves while another block may still read its shared memory
 }
 
 // Token feedback for a step launched before the previous step's tokens have reached the host: row r of the new
@@ -254,6 +306,23 @@ DL_EXPORT int dl_sample_temperature(const float* logits, int ld, int rows, int v
                                     const double* uniform, int* out, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0) return DL_ERR_UNSUPPORTED;
-  dl::sample_temperature_kernel<<<rows, dl::SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, temperature, uniform, out);
-  return dl::launch_status();
+  // blocks per row: enough for runs of at most 16 ids a thread, a power of two, at most 8 (a portable cluster)
+  int nblocks = 1;
+  while (nblocks < 8 && static_cast<long long>(nblocks) * dl::SAMPLE_THREADS * 16 < vocab) nblocks *= 2;
+  if (static_cast<long long>(rows) * nblocks > 0x7fffffffll) return DL_ERR_UNSUPPORTED;
+  const long long threads = static_cast<long long>(nblocks) * dl::SAMPLE_THREADS;
+  const int per = static_cast<int>(((vocab + threads - 1) / threads + 3) & ~3ll);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(rows * nblocks));
+  cfg.blockDim = dim3(dl::SAMPLE_THREADS);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(nblocks);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return static_cast<int>(cudaLaunchKernelEx(&cfg, dl::sample_temperature_kernel, logits, ld, vocab, per, temperature,
+                                             uniform, out));
 }

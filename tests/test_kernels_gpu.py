@@ -246,20 +246,28 @@ def test_argmax_ties_and_sizes(ops):
 def test_sample_temperature_matches_walk(ops):
     from plain_llama import sample_temperature
     g = torch.Generator(device="cpu").manual_seed(8)
-    for vocab in (11, 499, 5000):
-        logits = torch.randn(64, vocab, generator=g) * 3
-        temps = torch.full((64,), 0.8)
-        u = torch.rand(64, generator=g, dtype=torch.float64)
-        out = torch.empty(64, dtype=torch.int32, device=DEV)
+    # one block a row up to 16,384 ids, then clusters of 2, 4 and 8 blocks; 50,001: rows that do not start on 16 bytes
+    for vocab, rows in ((11, 64), (499, 64), (5000, 64), (20000, 16), (50001, 16), (128256, 16), (300000, 8)):
+        logits = torch.randn(rows, vocab, generator=g) * 3
+        temps = torch.full((rows,), 0.8)
+        u = torch.rand(rows, generator=g, dtype=torch.float64)
+        u[0] = 0.0                                              # the first id with any mass
+        u[1] = 0.9999999                                        # the far end of the walk
+        if vocab > 1000:
+            logits[0, :700] = -float("inf")                     # ... which lies past the first threads' runs
+            logits[1, vocab - 900:] = -float("inf")             # ... and the last mass before the last threads' runs
+        out = torch.empty(rows, dtype=torch.int32, device=DEV)
         ops.sample_temperature(logits.to(DEV), temps.to(DEV), u.to(DEV), out)
         got = out.cpu().tolist()
         agree = 0
-        for r in range(64):
+        for r in range(rows):
             ref = sample_temperature(logits[r].numpy(), 0.8, float(u[r]))
             # a draw that lands within rounding of a boundary may fall to the neighbour
             agree += got[r] == ref
-            assert abs(got[r] - ref) <= 1, f"row {r}: {got[r]} vs {ref}"
-        assert agree >= 62
+            assert abs(got[r] - ref) <= 1, f"vocab {vocab} row {r}: {got[r]} vs {ref}"
+        assert agree >= rows - 2
+        if vocab > 1000:
+            assert got[0] == 700
 
 
 def test_sample_temperature_frequencies(ops):
