@@ -155,7 +155,7 @@ argmax_of_parts_kernel(const float* __restrict__ pv, const int* __restrict__ pi,
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_temperature_kernel(const float* __restrict__ logits, int ld, int vocab, int per,
                           const float* __restrict__ temperature, const double* __restrict__ uniform,
-                          int* __restrict__ out) {
+                          const double* __restrict__ cut_offset, int* __restrict__ out) {
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
   __shared__ float red[33];
@@ -191,6 +191,11 @@ sample_temperature_kernel(const float* __restrict__ logits, int ld, int vocab, i
   }
   cluster.sync();
   for (int c = 0; c < nblocks; ++c) m = fmaxf(m, *cluster.map_shared_rank(&block_m, c));
+  // min-p (cut_offset[r] = temperature * log(min_p), -inf or no array: off): logits below max + offset have no mass
+  const double cut = cut_offset != nullptr ? static_cast<double>(m) + cut_offset[r] : -INFINITY;
+  auto mass = [&](float l) {
+    return static_cast<double>(l) >= cut ? static_cast<double>(expf((l - m) * inv_t)) : 0.0;
+  };
 
   double s = 0.0;
   {
@@ -198,12 +203,12 @@ sample_temperature_kernel(const float* __restrict__ logits, int ld, int vocab, i
     if (vec)
       for (; i + 4 <= e; i += 4) {
         const float4 v = *reinterpret_cast<const float4*>(row + i);
-        s += static_cast<double>(expf((v.x - m) * inv_t));
-        s += static_cast<double>(expf((v.y - m) * inv_t));
-        s += static_cast<double>(expf((v.z - m) * inv_t));
-        s += static_cast<double>(expf((v.w - m) * inv_t));
+        s += mass(v.x);
+        s += mass(v.y);
+        s += mass(v.z);
+        s += mass(v.w);
       }
-    for (; i < e; ++i) s += static_cast<double>(expf((row[i] - m) * inv_t));
+    for (; i < e; ++i) s += mass(row[i]);
   }
   // running totals in id order: over the warp, over the block's warps, over the cluster's blocks
   double incl = s;
@@ -242,18 +247,306 @@ sample_temperature_kernel(const float* __restrict__ logits, int ld, int vocab, i
     double u = target - begin;
     int pick = -1;
     for (int i = b; i < e; ++i) {
-      u -= static_cast<double>(expf((row[i] - m) * inv_t));
+      u -= mass(row[i]);
       if (u < 0.0) { pick = i; break; }
     }
     if (pick < 0) {
       pick = vocab - 1;
       for (int i = e; i < vocab; ++i) {
-        if (expf((row[i] - m) * inv_t) > 0.0f) { pick = i; break; }
+        if (mass(row[i]) > 0.0) { pick = i; break; }
       }
     }
     out[r] = pick;
   }
   cluster.sync();        // nobody leaves while another block may still read its shared memory
+}
+
+// ---- penalties and the filtered draw (top-k, min-p, top-p) -----------------------------------------------------
+//
+// The reference's pipeline, penalties -> top-k -> temperature -> min-p -> top-p -> draw
+// (dynalm/src/sampling/sampler.cpp:96-220), works on the candidates in the order (logit descending, id ascending).
+// Here one block per row narrows the vocabulary to at most SAMPLE_CAP candidates that are certain to hold every id
+// the pipeline can still choose, sorts those, and finishes the pipeline on them in double precision; a row whose
+// candidates do not fit gives -1 and is done by the host from its logits.
+
+// Repetition, frequency and presence penalties (sampler.cpp:96-116): triple j = (selection, token id, count of the
+// id in the request's recent context), ids unique within a selection; params[selection] = (repetition, frequency,
+// presence). float32 arithmetic in the order of the host's, no fused multiply-add.
+__global__ void apply_penalties_kernel(float* __restrict__ logits, int ld, int vocab, const int* __restrict__ rows,
+                                       const int* __restrict__ triples, int n_triples,
+                                       const float* __restrict__ params) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= n_triples) return;
+  const int sel = triples[3 * j], id = triples[3 * j + 1], count = triples[3 * j + 2];
+  if (id < 0 || id >= vocab) return;
+  float* at = logits + static_cast<size_t>(ck_row(rows[sel])) * ld + id;
+  const float rep = params[3 * sel], freq = params[3 * sel + 1], pres = params[3 * sel + 2];
+  float l = *at;
+  if (rep != 1.0f) l = l > 0.0f ? __fdiv_rn(l, rep) : __fmul_rn(l, rep);
+  *at = __fsub_rn(l, __fadd_rn(__fmul_rn(static_cast<float>(count), freq), pres));
+}
+
+constexpr int SAMPLE_CAP = 1024;          // candidates a row may keep (= threads of its block)
+constexpr int SAMPLE_BINS = 2048;
+constexpr double SAMPLE_FIXED = 1099511627776.0;      // 2^40: masses as integers, so that their sums have no order
+
+// Sum over the block in a fixed order; every thread gets it. `red`: 33 doubles.
+__device__ __forceinline__ double block_sum_f64(double v, double* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    double t = red[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+// Inclusive running sum over the block's threads in thread order. `red`: 33 doubles.
+__device__ __forceinline__ double block_scan_f64(double v, double* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const double x = __shfl_up_sync(0xffffffffu, v, o);
+    if (lane >= o) v += x;
+  }
+  __syncthreads();
+  if (lane == 31) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    const double w = red[lane];
+    double wi = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const double x = __shfl_up_sync(0xffffffffu, wi, o);
+      if (lane >= o) wi += x;
+    }
+    red[lane] = wi - w;
+  }
+  __syncthreads();
+  return v + red[warp];
+}
+
+__device__ __forceinline__ int block_count(bool flag, int* red_i) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = __popc(__ballot_sync(0xffffffffu, flag));
+  __syncthreads();
+  if (lane == 0) red_i[warp] = c;
+  __syncthreads();
+  int t = 0;
+  for (int w = 0; w < 32; ++w) t += red_i[w];
+  __syncthreads();
+  return t;
+}
+
+// Where a logit falls among SAMPLE_BINS equal steps from `lo` up (non-decreasing in l, whatever the rounding).
+__device__ __forceinline__ int sample_bin(float l, float lo, float scale) {
+  const float x = (l - lo) * scale;
+  return x <= 0.0f ? 0 : (x >= static_cast<float>(SAMPLE_BINS - 1) ? SAMPLE_BINS - 1 : static_cast<int>(x));
+}
+
+// From the top bin down: the highest bin b whose bins b.. together reach `target`; *rest = what of the target is
+// still to find inside b. All of the block's threads call it; hist has been filled and synchronised. If even all
+// bins do not reach the target the answer is bin 0.
+__device__ __forceinline__ int sample_pick_bin(const unsigned long long* hist, unsigned long long target,
+                                               unsigned long long* rest, double* red, int* shared_bin,
+                                               unsigned long long* shared_rest) {
+  // thread t owns bins SAMPLE_BINS-1-2t and SAMPLE_BINS-2-2t: a running sum over threads runs from the top bin down
+  const int b_hi = SAMPLE_BINS - 1 - 2 * static_cast<int>(threadIdx.x), b_lo = b_hi - 1;
+  const unsigned long long h_hi = hist[b_hi], h_lo = hist[b_lo];
+  // masses are below 2^58 in all: doubles would round them, so the running sum is made of two 32-bit halves
+  const double lo_part = block_scan_f64(static_cast<double>((h_hi + h_lo) & 0xffffffffull), red);
+  const double hi_part = block_scan_f64(static_cast<double>((h_hi + h_lo) >> 32), red);
+  const unsigned long long incl = static_cast<unsigned long long>(lo_part) + (static_cast<unsigned long long>(hi_part) << 32);
+  const unsigned long long before = incl - (h_hi + h_lo);
+  if (threadIdx.x == 0) { *shared_bin = 0; *shared_rest = target; }
+  __syncthreads();
+  if (before < target && incl >= target) {          // exactly one thread (none if the target is out of reach)
+    if (before + h_hi >= target) { *shared_bin = b_hi; *shared_rest = target - before; }
+    else { *shared_bin = b_lo; *shared_rest = target - before - h_hi; }
+  }
+  __syncthreads();
+  *rest = *shared_rest;
+  return *shared_bin;
+}
+
+// dparams[sel] = (temperature, temperature * log(min_p) or -inf, top_p, uniform); top_k[sel]: 0 = off.
+__global__ void __launch_bounds__(SAMPLE_CAP)
+sample_filtered_kernel(const float* __restrict__ logits, int ld, int vocab, const int* __restrict__ rows,
+                       const double* __restrict__ dparams, const int* __restrict__ top_k, int* __restrict__ out) {
+  __shared__ unsigned long long hist[SAMPLE_BINS];
+  __shared__ unsigned long long cand[SAMPLE_CAP];
+  __shared__ double red[33];
+  __shared__ float redf[33];
+  __shared__ int red_i[32];
+  __shared__ int n_cand, picked_bin;
+  __shared__ unsigned long long picked_rest;
+  const int sel = blockIdx.x, t = threadIdx.x;
+  const int out_at = ck_row(rows[sel]);
+  const float* row = logits + static_cast<size_t>(out_at) * ld;
+  const double temp = dparams[4 * sel], cut_off = dparams[4 * sel + 1], top_p = dparams[4 * sel + 2];
+  const double u = dparams[4 * sel + 3];
+  const int k = top_k[sel];
+  const bool use_k = k > 0 && k < vocab, use_p = top_p < 1.0;
+  const float inv_t = static_cast<float>(1.0 / temp);
+  if (!use_k && !use_p) {
+    // neither filter is in effect: the reference then walks the ids in their own order, not in that of their
+    // logits, which is the other kernel's walk; asked of this one, the row goes to the host
+    if (t == 0) out[out_at] = -1;
+    return;
+  }
+
+  // the largest and the smallest finite logit (NaN and -inf take no part anywhere below)
+  float hi = -INFINITY, lo = INFINITY;
+  for (int i = t; i < vocab; i += SAMPLE_CAP) {
+    const float l = row[i];
+    if (l > -INFINITY) { hi = fmaxf(hi, l); lo = fminf(lo, l); }
+  }
+  hi = block_max(hi, redf);
+  lo = -block_max(-lo, redf);
+  if (!(hi > -INFINITY) || !(hi < INFINITY)) {       // nothing finite to choose from: the host decides
+    if (t == 0) out[out_at] = -1;
+    return;
+  }
+  const double cut = static_cast<double>(hi) + cut_off;      // min-p: logits below it are out (sampler.cpp:146)
+
+  // the mass after min-p over the whole vocabulary, which top-p without top-k measures its share against
+  double total = 0.0;
+  if (use_p && !use_k) {
+    double mine = 0.0;
+    for (int i = t; i < vocab; i += SAMPLE_CAP) {
+      const float l = row[i];
+      if (l > -INFINITY && static_cast<double>(l) >= cut) mine += exp((static_cast<double>(l) - static_cast<double>(hi)) / temp);
+    }
+    total = block_sum_f64(mine, red);
+  }
+
+  // Two rounds of SAMPLE_BINS equal steps, the second inside the bin in which the first found the boundary: by count
+  // (the top_k-th logit) or by mass (where the running mass from the top reaches top_p of the whole, with room for
+  // the rounding of the integer masses). Everything at or above the boundary bin is a candidate.
+  unsigned long long target;
+  if (use_k) {
+    target = static_cast<unsigned long long>(k);
+  } else {
+    target = 0;           // set after the first histogram, from its own total
+  }
+  float lo1 = lo, scale1 = hi > lo ? static_cast<float>(SAMPLE_BINS) / (hi - lo) : 0.0f;
+  int bin1 = 0, bin2 = 0;
+  float lo2 = lo, scale2 = 0.0f;
+  for (int round = 0; round < 2; ++round) {
+    for (int b = t; b < SAMPLE_BINS; b += SAMPLE_CAP) hist[b] = 0;
+    __syncthreads();
+    for (int i = t; i < vocab; i += SAMPLE_CAP) {
+      const float l = row[i];
+      if (!(l > -INFINITY)) continue;
+      const int b1 = sample_bin(l, lo1, scale1);
+      if (round == 1 && b1 != bin1) continue;
+      const int b = round == 0 ? b1 : sample_bin(l, lo2, scale2);
+      const unsigned long long w = use_k ? 1ull
+          : static_cast<unsigned long long>(static_cast<double>(expf((l - hi) * inv_t)) * SAMPLE_FIXED);
+      atomicAdd(&hist[b], w);
+    }
+    __syncthreads();
+    if (round == 0 && !use_k) {
+      // top-p alone: the share of the integer masses' own sum, a little more than asked for
+      unsigned long long mine = 0;
+      for (int b = t; b < SAMPLE_BINS; b += SAMPLE_CAP) mine += hist[b];
+      const double lo_part = block_sum_f64(static_cast<double>(mine & 0xffffffffull), red);
+      const double hi_part = block_sum_f64(static_cast<double>(mine >> 32), red);
+      const double all = lo_part + hi_part * 4294967296.0;
+      target = static_cast<unsigned long long>(top_p * all * (1.0 + 1e-5)) + static_cast<unsigned long long>(vocab);
+    }
+    unsigned long long rest;
+    const int b = sample_pick_bin(hist, target, &rest, red, &picked_bin, &picked_rest);
+    if (round == 0) {
+      bin1 = b;
+      lo2 = lo1 + static_cast<float>(b) / scale1;
+      scale2 = scale1 * static_cast<float>(SAMPLE_BINS);
+      if (!(scale1 > 0.0f)) { lo2 = lo1; scale2 = 0.0f; }
+      target = rest;
+    } else {
+      bin2 = b;
+    }
+  }
+
+  // the candidates, in whatever order they arrive: (logit descending, id ascending) as one integer to sort by
+  if (t == 0) n_cand = 0;
+  __syncthreads();
+  for (int i = t; i < vocab; i += SAMPLE_CAP) {
+    const float l = row[i];
+    if (!(l > -INFINITY)) continue;
+    const int b1 = sample_bin(l, lo1, scale1);
+    if (b1 < bin1 || (b1 == bin1 && sample_bin(l, lo2, scale2) < bin2)) continue;
+    const int at = atomicAdd(&n_cand, 1);
+    if (at < SAMPLE_CAP) {
+      const unsigned int bits = __float_as_uint(l);
+      const unsigned int rising = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);     // grows with the logit
+      cand[at] = (static_cast<unsigned long long>(~rising) << 32) | static_cast<unsigned int>(i);
+    }
+  }
+  __syncthreads();
+  const int n = n_cand;
+  if (n > SAMPLE_CAP || n == 0) {
+    if (t == 0) out[out_at] = -1;
+    return;
+  }
+  if (t >= n) cand[t] = ~0ull;
+  __syncthreads();
+  for (int size = 2; size <= SAMPLE_CAP; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      const int other = t ^ stride;
+      if (other > t) {
+        const unsigned long long a = cand[t], b = cand[other];
+        const bool up = (t & size) == 0;
+        if ((a > b) == up) { cand[t] = b; cand[other] = a; }
+      }
+      __syncthreads();
+    }
+  }
+
+  // the pipeline on the sorted candidates, thread i = candidate i
+  const int id = static_cast<int>(cand[t] & 0xffffffffull);
+  const double l = t < n ? static_cast<double>(row[id]) : 0.0;
+  const int k_eff = use_k ? min(k, n) : n;
+  const bool valid = t < k_eff && l >= cut;
+  const int m = block_count(valid, red_i);             // sorted: the valid ones are the first m
+  if (m == 0) {
+    if (t == 0) out[out_at] = static_cast<int>(cand[0] & 0xffffffffull);        // cannot be: the largest logit passes
+    return;
+  }
+  // a boundary found by count holds all of the first k; one found by mass must reach the share asked for (checked
+  // below)
+  double prob = valid ? exp((l - static_cast<double>(hi)) / temp) : 0.0;
+  double cum = block_scan_f64(prob, red);
+  __shared__ double kept_s;
+  if (t == m - 1) kept_s = cum;
+  __syncthreads();
+  double kept = kept_s;
+  int keep = m;
+  const bool some_left_out = bin1 > 0 || bin2 > 0;      // finite logits below the boundary exist, or may
+  if (use_p) {
+    const double share = top_p * (use_k ? kept : total);
+    if (!use_k && kept < share && some_left_out) {     // the candidates do not hold the whole nucleus
+      if (t == 0) out[out_at] = -1;
+      return;
+    }
+    keep = block_count(valid && cum < share, red_i) + 1;           // first place where the running mass reaches it
+    keep = max(1, min(keep, m));
+    if (t >= keep) prob = 0.0;
+    if (t == keep - 1) kept_s = cum;
+    __syncthreads();
+    kept = kept_s;
+  }
+  const double aim = u * kept;
+  int pick = block_count(t < keep && cum <= aim, red_i);           // first place where the running mass exceeds it
+  pick = min(pick, keep - 1);
+  if (t == pick) out[out_at] = id;
 }
 
 // Token feedback for a step launched before the previous step's tokens have reached the host: row r of the new
@@ -301,9 +594,31 @@ DL_EXPORT int dl_argmax_of_parts(const float* pv, const int* pi, int rows, int p
                               status_src, status_dst);
 }
 
+// rows: the logits rows of the n_sel selections; triples: int32 [n_triples][3] = (selection, token id, count);
+// params: fp32 [n_sel][3] = (repetition, frequency, presence). In place.
+DL_EXPORT int dl_apply_penalties(float* logits, int ld, int vocab, const int* rows, const int* triples, int n_triples,
+                                 const float* params, cudaStream_t stream) {
+  if (n_triples <= 0) return 0;
+  if (vocab <= 0) return DL_ERR_UNSUPPORTED;
+  dl::apply_penalties_kernel<<<(n_triples + 127) / 128, 128, 0, stream>>>(logits, ld, vocab, rows, triples, n_triples, params);
+  return dl::launch_status();
+}
+
+// One draw per selection through top-k, min-p and top-p. rows: int32 [n_sel], the logits row of each;
+// dparams: double [n_sel][4] = (temperature, temperature * log(min_p) or -inf, top_p, uniform in [0, 1));
+// top_k: int32 [n_sel], 0 = off. out[rows[sel]]: the id, or -1 where the row has to be done by the host.
+DL_EXPORT int dl_sample_filtered(const float* logits, int ld, int vocab, const int* rows, int n_sel,
+                                 const double* dparams, const int* top_k, int* out, cudaStream_t stream) {
+  if (n_sel <= 0) return 0;
+  if (vocab <= 0) return DL_ERR_UNSUPPORTED;
+  dl::sample_filtered_kernel<<<n_sel, dl::SAMPLE_CAP, 0, stream>>>(logits, ld, vocab, rows, dparams, top_k, out);
+  return dl::launch_status();
+}
+
 // temperature: fp32 [rows] (> 0); uniform: double [rows] in [0, 1).
+// cut_offset (may be null): double [rows], temperature * log(min_p) per row, -inf where min-p is off.
 DL_EXPORT int dl_sample_temperature(const float* logits, int ld, int rows, int vocab, const float* temperature,
-                                    const double* uniform, int* out, cudaStream_t stream) {
+                                    const double* uniform, const double* cut_offset, int* out, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0) return DL_ERR_UNSUPPORTED;
   // blocks per row: enough for runs of at most 16 ids a thread, a power of two, at most 8 (a portable cluster)
@@ -324,5 +639,5 @@ DL_EXPORT int dl_sample_temperature(const float* logits, int ld, int rows, int v
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return static_cast<int>(cudaLaunchKernelEx(&cfg, dl::sample_temperature_kernel, logits, ld, vocab, per, temperature,
-                                             uniform, out));
+                                             uniform, cut_offset, out));
 }

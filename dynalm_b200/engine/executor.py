@@ -5,6 +5,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional
 
+import numpy as np
 import torch
 
 from ..errors import EngineError
@@ -24,9 +25,9 @@ class Launched:
 
 class GpuExecutor:
     """`run(batch)`: one step of the model for the whole batch, then one token for every item that
-    completed its pending work. Greedy and temperature-only requests are sampled by kernels from
-    the logits on the device and only their ids come back; requests with filters or penalties get
-    their logits row on the host (see dynalm_b200.sampling.sampler).
+    completed its pending work. Every request is sampled by kernels from the logits on the device and only the ids
+    come back; a row of a request with top-k or top-p whose candidates do not fit the kernel gets its logits on the
+    host (see dynalm_b200.sampling.sampler).
 
     `launch(batch, after)` / `collect(launched)` split that in two for decode batches whose requests
     are all sampled on the device: the ids stay on the device, and a following batch can be launched
@@ -47,8 +48,11 @@ class GpuExecutor:
         self._ids_host = [torch.zeros(2 * n + 1, dtype=torch.int32).pin_memory() for _ in range(2)]
         self._temp_host = [torch.ones(n, dtype=torch.float32).pin_memory() for _ in range(2)]
         self._u_host = [torch.zeros(n, dtype=torch.float64).pin_memory() for _ in range(2)]
+        self._cut_host = [torch.zeros(n, dtype=torch.float64).pin_memory() for _ in range(2)]
         self._temp = torch.ones(n, dtype=torch.float32, device=dev)
         self._u = torch.zeros(n, dtype=torch.float64, device=dev)
+        self._cut = torch.zeros(n, dtype=torch.float64, device=dev)
+        self.host_sampled = 0      # rows that the filtered kernel left to the host so far
         self._turn = 0
         self.h2d_bytes = 0
         self.d2h_bytes = 0
@@ -71,27 +75,71 @@ class GpuExecutor:
             return (self._ids[:len(want)], self._ids[2 * self._n:])
         return None
 
-    def _sample_on_device(self, logits: Optional[torch.Tensor], want: List[BatchItem], slot: int) -> None:
+    def _sample_on_device(self, logits: Optional[torch.Tensor], want: List[BatchItem], slot: int) -> Dict[int, float]:
+        """Choose a token for every wanted row on the device and start the copy of the ids to the host: the largest
+        logit for every row (place i), and for the rows that draw, a draw (place n + i): a walk down the ids for
+        temperature and min-p, the filtered kernel for top-k and top-p, which may leave -1 for the host to finish.
+        Rows with penalties have them applied to their logits first. Returns row -> the uniform number it drew with,
+        for the rows of the filtered kernel."""
         n = len(want)
         if logits is None:
             # the step picked the most likely tokens itself (and brought the status word along)
             self._ids_host[slot].copy_(self._ids, non_blocking=True)
             self.d2h_bytes += self._ids_host[slot].numel() * 4
-            return
+            return {}
+        dev = logits.device
+        samplers = [b.seq.sampler for b in want]
+        penalised = [i for i, s in enumerate(samplers) if s.params.has_penalties]
+        if penalised:
+            # the context the penalties see: everything up to and including the tokens just computed
+            triples, params = [], np.zeros((len(penalised), 3), dtype=np.float32)
+            for j, i in enumerate(penalised):
+                p = samplers[i].params
+                ids, counts = samplers[i].penalty_counts(want[i].seq.tokens, self.vocab)
+                params[j] = (p.repetition_penalty, p.frequency_penalty, p.presence_penalty)
+                if ids.size:
+                    triples.append(np.stack([np.full(ids.size, j, dtype=np.int64), ids, counts], axis=1))
+            if triples:
+                flat = np.concatenate(triples).astype(np.int32)
+                ops.apply_penalties(logits, torch.tensor(penalised, dtype=torch.int32, device=dev),
+                                    torch.from_numpy(flat).to(dev), flat.shape[0], torch.from_numpy(params).to(dev))
+                self.h2d_bytes += flat.nbytes + params.nbytes + 4 * len(penalised)
         ops.argmax(logits, self._ids[:n], status_to=self._ids[2 * self._n:])
-        if any(not b.seq.sampler.params.greedy and b.seq.sampler.on_device for b in want):
-            th, uh = self._temp_host[slot], self._u_host[slot]
-            for i, b in enumerate(want):
-                p = b.seq.sampler.params
-                on = not p.greedy and b.seq.sampler.on_device
-                th[i] = p.temperature if on else 1.0
-                uh[i] = b.seq.sampler.next_uniform() if on else 0.0
+        # top-k of the whole vocabulary or more is no filter (sampler.cpp:118): such a draw walks the ids in their order
+        sorted_draw = [not s.params.greedy and (0 < s.params.top_k < self.vocab or s.params.top_p < 1.0) for s in samplers]
+        walk = [i for i, s in enumerate(samplers) if not s.params.greedy and not sorted_draw[i]]
+        if walk:
+            th, uh, ch = self._temp_host[slot], self._u_host[slot], self._cut_host[slot]
+            th[:n] = 1.0
+            uh[:n] = 0.0
+            ch[:n] = -np.inf
+            for i in walk:
+                th[i] = samplers[i].params.temperature
+                uh[i] = samplers[i].next_uniform()
+                ch[i] = samplers[i].cut_offset
             self._temp[:n].copy_(th[:n], non_blocking=True)
             self._u[:n].copy_(uh[:n], non_blocking=True)
-            self.h2d_bytes += 12 * n
-            ops.sample_temperature(logits, self._temp, self._u, self._ids[self._n:self._n + n])
+            with_cut = any(samplers[i].params.min_p > 0.0 for i in walk)
+            if with_cut:
+                self._cut[:n].copy_(ch[:n], non_blocking=True)
+            self.h2d_bytes += (20 if with_cut else 12) * n
+            ops.sample_temperature(logits, self._temp, self._u, self._ids[self._n:self._n + n],
+                                   cut_offset=self._cut if with_cut else None)
+        drawn: Dict[int, float] = {}
+        filtered = [i for i in range(n) if sorted_draw[i]]
+        if filtered:
+            dparams = np.zeros((len(filtered), 4), dtype=np.float64)
+            for j, i in enumerate(filtered):
+                p = samplers[i].params
+                drawn[i] = samplers[i].next_uniform()
+                dparams[j] = (p.temperature, samplers[i].cut_offset, p.top_p, drawn[i])
+            ints = torch.tensor([filtered, [samplers[i].params.top_k for i in filtered]], dtype=torch.int32, device=dev)
+            ops.sample_filtered(logits, ints[0], len(filtered), torch.from_numpy(dparams).to(dev), ints[1],
+                                self._ids[self._n:self._n + n])
+            self.h2d_bytes += dparams.nbytes + 8 * len(filtered)
         self._ids_host[slot].copy_(self._ids, non_blocking=True)
         self.d2h_bytes += self._ids_host[slot].numel() * 4
+        return drawn
 
     def launch(self, batch: List[BatchItem], after: Optional[Launched] = None) -> Launched:
         """Issue a decode batch whose requests are all sampled on the device. With `after`, every request of the
@@ -140,22 +188,25 @@ class GpuExecutor:
         n = len(want)
         slot = self._turn
         self._turn ^= 1
-        self._sample_on_device(logits, want, slot)
-        host_rows = [(i, b) for i, b in enumerate(want) if not b.seq.sampler.on_device]
-        rows = None
-        if host_rows:
-            idx = torch.tensor([i for i, _ in host_rows], device=logits.device)
-            rows = logits[:n].index_select(0, idx).to("cpu", non_blocking=False).numpy()
-            self.d2h_bytes += rows.nbytes
+        drawn = self._sample_on_device(logits, want, slot)
         torch.cuda.current_stream().synchronize()
         ids = self._ids_host[slot].numpy()
         self._check_status(ids)
         out: Dict[Hashable, int] = {}
+        host_rows = []
         for i, b in enumerate(want):
-            s = b.seq.sampler
-            if s.on_device:
-                out[b.seq.id] = int(ids[i] if s.params.greedy else ids[self._n + i])
-        for k, (i, b) in enumerate(host_rows):
-            # the context the penalties see: everything up to and including the tokens just computed
-            out[b.seq.id] = b.seq.sampler.sample_host(rows[k], b.seq.tokens)
+            token = int(ids[i] if b.seq.sampler.params.greedy else ids[self._n + i])
+            if token == ops.SAMPLE_FILTERED_HOST:
+                host_rows.append((i, b))
+            else:
+                out[b.seq.id] = token
+        if host_rows:
+            # rows whose candidates did not fit the filtered kernel: the same pipeline on the host, from the row's
+            # logits (which have their penalties already) and with the uniform number the kernel was given
+            idx = torch.tensor([i for i, _ in host_rows], device=logits.device)
+            rows = logits[:n].index_select(0, idx).to("cpu", non_blocking=False).numpy()
+            self.d2h_bytes += rows.nbytes
+            self.host_sampled += len(host_rows)
+            for k, (i, b) in enumerate(host_rows):
+                out[b.seq.id] = b.seq.sampler.sample_host(rows[k], b.seq.tokens, u=drawn[i], penalties_applied=True)
         return out

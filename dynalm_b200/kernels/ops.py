@@ -57,7 +57,9 @@ _SIGNATURES = {
     "gemm_simt": {"dl_gemm_simt": [_I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _P]},
     "sampling": {
         "dl_argmax": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
-        "dl_sample_temperature": [_P, _I, _I, _I, _P, _P, _P, _P],
+        "dl_sample_temperature": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
+        "dl_apply_penalties": [_P, _I, _I, _P, _P, _I, _P, _P],
+        "dl_sample_filtered": [_P, _I, _I, _P, _I, _P, _P, _P, _P],
         "dl_argmax_of_parts": [_P, _P, _I, _I, _P, _P, _P, _P],
         "dl_feedback_tokens": [_P, _P, _P, _I, _P],
     },
@@ -975,13 +977,56 @@ def feedback_tokens(token_ids: torch.Tensor, chosen: torch.Tensor, src: torch.Te
     _check(_fn("sampling", "dl_feedback_tokens")(_p(token_ids), _p(chosen), _p(src), n, _stream()), "feedback_tokens")
 
 
-def sample_temperature(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor) -> None:
-    """Draw out[r] from softmax(logits[r] / temperature[r]) by walking the ids in order with uniform[r]."""
-    _cuda(logits, temperature, uniform, out)
+def sample_temperature(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor,
+                       cut_offset: Optional[torch.Tensor] = None) -> None:
+    """Draw out[r] from softmax(logits[r] / temperature[r]) by walking the ids in order with uniform[r]. With
+    cut_offset (float64 [rows]: temperature * log(min_p), -inf where off) the ids whose logit lies below the row's
+    largest plus the offset have no mass (min-p)."""
+    _cuda(logits, temperature, uniform, out, cut_offset)
     _rows_contiguous(logits, "logits")
     rows = logits.shape[0]
     if (logits.dtype != torch.float32 or temperature.dtype != torch.float32 or uniform.dtype != torch.float64
             or out.dtype != torch.int32 or min(temperature.numel(), uniform.numel(), out.numel()) < rows):
         raise InvalidArgument("sample_temperature: logits/temperature float32, uniform float64, out int32, one per row")
+    if cut_offset is not None and (cut_offset.dtype != torch.float64 or cut_offset.numel() < rows):
+        raise InvalidArgument("sample_temperature: cut_offset float64, one per row")
     _check(_fn("sampling", "dl_sample_temperature")(_p(logits), logits.stride(0), rows, logits.shape[1], _p(temperature),
-                                                     _p(uniform), _p(out), _stream()), "sample_temperature")
+                                                     _p(uniform), _p(cut_offset), _p(out), _stream()), "sample_temperature")
+
+
+def apply_penalties(logits: torch.Tensor, rows: torch.Tensor, triples: torch.Tensor, n_triples: int,
+                    params: torch.Tensor) -> None:
+    """Repetition, frequency and presence penalties, in place: triple j = (selection, token id, count) changes
+    logits[rows[selection], id] with params[selection] = (repetition, frequency, presence). The ids of one selection
+    are distinct. rows int32, triples int32 [>= n_triples, 3], params float32 [selections, 3]."""
+    _cuda(logits, rows, triples, params)
+    _rows_contiguous(logits, "logits")
+    if (logits.dtype != torch.float32 or rows.dtype != torch.int32 or triples.dtype != torch.int32
+            or params.dtype != torch.float32 or triples.numel() < 3 * n_triples or not triples.is_contiguous()
+            or not params.is_contiguous()):
+        raise InvalidArgument("apply_penalties: logits/params float32, rows/triples int32, triples [n, 3]")
+    if CHECKED:
+        check_limits("sampling", rows=logits.shape[0])
+    _check(_fn("sampling", "dl_apply_penalties")(_p(logits), logits.stride(0), logits.shape[1], _p(rows), _p(triples),
+                                                  int(n_triples), _p(params), _stream()), "apply_penalties")
+
+
+SAMPLE_FILTERED_HOST = -1      # what sample_filtered leaves for a row that the host has to finish
+
+
+def sample_filtered(logits: torch.Tensor, rows: torch.Tensor, n_sel: int, dparams: torch.Tensor, top_k: torch.Tensor,
+                    out: torch.Tensor) -> None:
+    """One draw per selection through top-k, min-p and top-p in the reference's order. rows int32 [n_sel]: the
+    logits row of each selection; dparams float64 [n_sel, 4] = (temperature, temperature * log(min_p) or -inf, top_p,
+    uniform in [0, 1)); top_k int32 [n_sel] (0 = off); out int32 with a place for every row named: out[rows[sel]] gets the id,
+    or SAMPLE_FILTERED_HOST where the row's candidates do not fit the kernel (a nucleus of more than 1,024 ids, say)."""
+    _cuda(logits, rows, dparams, top_k, out)
+    _rows_contiguous(logits, "logits")
+    if (logits.dtype != torch.float32 or rows.dtype != torch.int32 or dparams.dtype != torch.float64
+            or top_k.dtype != torch.int32 or out.dtype != torch.int32 or not dparams.is_contiguous()
+            or min(rows.numel(), top_k.numel(), out.numel()) < n_sel or dparams.numel() < 4 * n_sel):
+        raise InvalidArgument("sample_filtered: logits float32, rows/top_k/out int32, dparams float64 [n, 4]")
+    if CHECKED:
+        check_limits("sampling", rows=min(logits.shape[0], out.numel()))      # a row is also a place in `out`
+    _check(_fn("sampling", "dl_sample_filtered")(_p(logits), logits.stride(0), logits.shape[1], _p(rows), int(n_sel),
+                                                  _p(dparams), _p(top_k), _p(out), _stream()), "sample_filtered")

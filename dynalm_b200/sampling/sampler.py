@@ -1,15 +1,18 @@
 """Per-request samplers.
 
-Greedy and temperature-only requests are sampled on the device (csrc/sampling.cu) from the logits
-rows of the step; only token ids come back. Requests with top-k / top-p / min-p or penalties take
-the reference's full pipeline, penalties -> top-k -> temperature -> min-p -> top-p -> draw
-(dynalm/src/sampling/sampler.cpp:96-220), on the host from their one logits row, as the reference
-does for every request.
+Every request is sampled on the device (csrc/sampling.cu) from the logits rows of the step, and only token ids come
+back: greedy, temperature and min-p by kernels that need nothing from the host but a uniform number (such requests
+can be decoded a step ahead); penalties by a kernel that gets the counts of the recent tokens from the host; top-k and
+top-p by a kernel that narrows the vocabulary to the candidates the pipeline can still choose and finishes the
+reference's pipeline, penalties -> top-k -> temperature -> min-p -> top-p -> draw
+(dynalm/src/sampling/sampler.cpp:96-220), on those. Where the candidates do not fit that kernel (a nucleus of more
+than a thousand ids) the row comes to the host, which runs the same pipeline here, as the reference does for
+every request.
 """
 
 from __future__ import annotations
 
-from typing import Sequence
+from typing import Optional, Sequence
 
 import numpy as np
 
@@ -36,35 +39,60 @@ class Sampler:
 
     @property
     def on_device(self) -> bool:
+        """Whether the device can choose this request's token with nothing from the host but a uniform number:
+        greedy, temperature, min-p. Penalties need the context, top-k and top-p may need the host to finish."""
         p = self.params
-        return not p.has_penalties and (p.greedy or not p.has_filters)
+        return not p.has_penalties and (p.greedy or not self.wants_filtered)
+
+    @property
+    def wants_filtered(self) -> bool:
+        """Top-k or top-p is set: the draw goes down the candidates in the order of their logits."""
+        return self.params.top_k > 0 or self.params.top_p < 1.0
+
+    @property
+    def cut_offset(self) -> float:
+        """min-p as an offset below the largest logit: temperature * log(min_p) (sampler.cpp:146); -inf when off."""
+        p = self.params
+        return float(p.temperature) * float(np.log(p.min_p)) if p.min_p > 0.0 and not p.greedy else -np.inf
 
     def next_uniform(self) -> float:
         return self.rng.uniform()
+
+    def penalty_counts(self, context: Sequence[int], vocab: int):
+        """The distinct ids among the last `penalty_last_n` tokens of the context, and how often each occurs
+        (what the penalties act on, sampler.cpp:96-116); two empty arrays where there is nothing to penalise."""
+        p = self.params
+        none = np.zeros(0, dtype=np.int64)
+        if not p.has_penalties or len(context) == 0:
+            return none, none
+        n = len(context) if p.penalty_last_n < 0 else min(len(context), p.penalty_last_n)
+        if n == 0:
+            return none, none
+        ids, counts = np.unique(np.asarray(context[len(context) - n:], dtype=np.int64), return_counts=True)
+        ok = (ids >= 0) & (ids < vocab)
+        return ids[ok], counts[ok]
 
     # ---- the host pipeline -----------------------------------------------------------------------
     def apply_penalties(self, logits: np.ndarray, context: Sequence[int]) -> None:
         """Repetition, frequency and presence penalties over the last `penalty_last_n` tokens
         (sampler.cpp:96-116). In place."""
         p = self.params
-        if not p.has_penalties or len(context) == 0:
+        ids, counts = self.penalty_counts(context, logits.size)
+        if ids.size == 0:
             return
-        n = len(context) if p.penalty_last_n < 0 else min(len(context), p.penalty_last_n)
-        if n == 0:
-            return
-        ids, counts = np.unique(np.asarray(context[len(context) - n:], dtype=np.int64), return_counts=True)
-        ok = (ids >= 0) & (ids < logits.size)
-        ids, counts = ids[ok], counts[ok]
         l = logits[ids]
         if p.repetition_penalty != 1.0:
             l = np.where(l > 0, l / np.float32(p.repetition_penalty), l * np.float32(p.repetition_penalty))
         l = l - (counts.astype(np.float32) * np.float32(p.frequency_penalty) + np.float32(p.presence_penalty))
         logits[ids] = l
 
-    def sample_host(self, logits: np.ndarray, context: Sequence[int]) -> int:
-        """The whole pipeline on one float32 logits row (which it may modify)."""
+    def sample_host(self, logits: np.ndarray, context: Sequence[int], u: Optional[float] = None,
+                    penalties_applied: bool = False) -> int:
+        """The whole pipeline on one float32 logits row (which it may modify). `u`: the uniform number to draw
+        with (one is taken from the request's generator otherwise); `penalties_applied`: the row has them already."""
         p = self.params
-        self.apply_penalties(logits, context)
+        if not penalties_applied:
+            self.apply_penalties(logits, context)
         if p.greedy:
             return greedy_token(logits)
         vocab = logits.size
@@ -73,7 +101,7 @@ class Sampler:
         use_k = 0 < p.top_k < vocab
         if not use_k and p.top_p >= 1.0 and p.min_p <= 0.0:
             probs = np.exp((logits.astype(np.float64) - max_l) / t)
-            return self._draw(np.arange(vocab), probs, float(probs.sum()))
+            return self._draw(np.arange(vocab), probs, float(probs.sum()), u)
         # min-p: keep logits within T * log(min_p) of the maximum (sampler.cpp:146)
         cut = max_l + t * np.log(p.min_p) if p.min_p > 0.0 else -np.inf
         ids = np.flatnonzero(logits >= cut)
@@ -96,12 +124,12 @@ class Sampler:
             keep = max(1, min(keep, probs.size))
             ids, probs = ids[:keep], probs[:keep]
             kept = float(probs.sum())
-        return self._draw(ids, probs, kept)
+        return self._draw(ids, probs, kept, u)
 
-    def _draw(self, ids: np.ndarray, probs: np.ndarray, total: float) -> int:
+    def _draw(self, ids: np.ndarray, probs: np.ndarray, total: float, u: Optional[float] = None) -> int:
         """u * total walked down the candidates until it goes negative; the last one on rounding
         (sampler.cpp:209-220)."""
-        u = self.rng.uniform() * total
+        u = (self.rng.uniform() if u is None else u) * total
         cum = np.cumsum(probs)
         i = int(np.searchsorted(cum, u, side="right"))
         return int(ids[min(i, ids.size - 1)])

@@ -98,7 +98,7 @@ def test_temperature_sampling_is_seeded_and_follows_the_walk(tiny_folders):
     logits = plain.logits((prompt + a)[:-1])
     same = sum(sample_temperature(logits[len(prompt) - 1 + i], 0.8, rng.uniform()) == t for i, t in enumerate(a))
     assert same >= len(a) - 1
-    # greedy beside sampling in one batch; filters and penalties take the host path
+    # greedy beside sampling in one batch, with filters and penalties
     from dynalm_b200 import SamplingParams
     mixed = eng.generate([prompt, prompt, prompt], max_tokens=12,
                          sampling=[SamplingParams(), SamplingParams(temperature=0.8, seed=4),
@@ -106,6 +106,41 @@ def test_temperature_sampling_is_seeded_and_follows_the_walk(tiny_folders):
     assert mixed[0].tokens == eng.generate(prompt, max_tokens=12).tokens
     assert mixed[1].tokens == a[:12]
     assert len(mixed[2].tokens) == 12
+
+
+def test_filters_and_penalties_follow_the_reference_pipeline(tiny_folders):
+    """Top-k, top-p, min-p and the penalties through the entry point (kernels on the device) against the host's
+    pipeline run teacher-forced over the plain implementation's logits with the same generator: the same ids, but
+    for a draw that lands within rounding of a boundary."""
+    from dynalm_b200 import SamplingParams
+    from dynalm_b200.sampling.sampler import Sampler
+    name = "b"
+    cfg = TINY[name][0]
+    prompt = random_requests(cfg["vocab_size"], [29], seed=5)["r0"]
+    eng = _engine(tiny_folders[name], "float32")
+    plain = PlainLlama(tiny_folders[name])
+    cases = [dict(temperature=0.9, top_k=5), dict(temperature=1.2, top_p=0.9), dict(temperature=0.8, min_p=0.1),
+             dict(temperature=1.0, top_k=8, top_p=0.8, repetition_penalty=1.2, frequency_penalty=0.1),
+             dict(temperature=0.0, repetition_penalty=1.5, presence_penalty=0.5),
+             dict(temperature=0.8, presence_penalty=0.5, penalty_last_n=-1),
+             dict(temperature=1.1, top_k=cfg["vocab_size"] + 3, min_p=0.05)]
+    params = [SamplingParams(seed=10 + i, **c) for i, c in enumerate(cases)]
+    before = eng.executor.host_sampled
+    outs = eng.generate([prompt] * len(cases), max_tokens=20, sampling=params)
+    assert eng.executor.host_sampled == before           # a vocabulary this small always fits the kernel
+    for case, p, out in zip(cases, params, outs):
+        a = out.tokens
+        assert len(a) == 20
+        logits = plain.logits((prompt + a)[:-1]).astype(np.float32)
+        host = Sampler(p)
+        same = 0
+        for i, tok in enumerate(a):
+            row = logits[len(prompt) - 1 + i].copy()
+            same += host.sample_host(row, prompt + a[:i]) == tok
+        assert same >= len(a) - 1, f"{case}: {same} of {len(a)} ids as the host pipeline"
+    # and the same request twice gives the same ids
+    again = eng.generate([prompt] * len(cases), max_tokens=20, sampling=params)
+    assert [o.tokens for o in again] == [o.tokens for o in outs]
 
 
 def test_command_line(tiny_folders_bf16):

@@ -286,6 +286,131 @@ def test_sample_temperature_frequencies(ops):
     assert (freq - p).abs().max() < 0.015
 
 
+def test_apply_penalties_matches_the_host(ops):
+    """The penalties kernel against the host's (sampler.cpp:96-116): the same float32 bits on the rows it names, the
+    other rows untouched."""
+    from dynalm_b200.sampling import SamplingParams
+    from dynalm_b200.sampling.sampler import Sampler
+    g = torch.Generator(device="cpu").manual_seed(12)
+    vocab = 5003
+    logits = torch.randn(6, vocab, generator=g) * 4
+    contexts = {1: [7, 7, 7, 12, 5002, 0, 12], 4: list(range(40, 140)) + [41] * 5, 5: []}
+    params = {1: SamplingParams(temperature=0.7, repetition_penalty=1.3, frequency_penalty=0.2, presence_penalty=-0.4),
+              4: SamplingParams(temperature=0.7, repetition_penalty=0.8, penalty_last_n=-1),
+              5: SamplingParams(temperature=0.7, presence_penalty=1.0)}
+    want = logits.clone().numpy()
+    rows, triples, pp = [], [], []
+    for j, r in enumerate(sorted(contexts)):
+        s = Sampler(params[r])
+        s.apply_penalties(want[r], contexts[r])
+        ids, counts = s.penalty_counts(contexts[r], vocab)
+        rows.append(r)
+        pp.append((params[r].repetition_penalty, params[r].frequency_penalty, params[r].presence_penalty))
+        triples += [(j, int(i), int(c)) for i, c in zip(ids, counts)]
+    d = logits.to(DEV)
+    ops.apply_penalties(d, torch.tensor(rows, dtype=torch.int32, device=DEV),
+                        torch.tensor(triples, dtype=torch.int32, device=DEV), len(triples),
+                        torch.tensor(pp, dtype=torch.float32, device=DEV))
+    assert np.array_equal(d.cpu().numpy(), want)
+    assert not np.array_equal(want[1], logits[1].numpy()) and np.array_equal(want[0], logits[0].numpy())
+
+
+def _peaked_logits(rows, vocab, g, spread):
+    """Logits like a model's: a few ids stand out, the rest fall away (so that a nucleus is tens of ids, not most of
+    the vocabulary), with some exactly equal values among the largest."""
+    logits = torch.randn(rows, vocab, generator=g) * spread - 12.0
+    top = torch.randint(0, vocab, (rows, 12), generator=g)
+    for r in range(rows):
+        logits[r, top[r]] += torch.linspace(9.0, 4.0, 12)
+        logits[r, top[r, 5]] = logits[r, top[r, 4]]              # a tie inside every top-k of 5 or more
+    return logits
+
+
+@pytest.mark.parametrize("vocab", [300, 5003, 128256])
+def test_sample_filtered_matches_the_host_pipeline(ops, vocab):
+    """Top-k, min-p and top-p on the device against the host's pipeline (sampler.cpp:120-220) with the same uniform
+    numbers: the same id, except where the draw lands within rounding of a boundary between two candidates (then
+    the neighbour in the pipeline's order, which for the test must at least be one of the row's candidates)."""
+    from dynalm_b200.sampling import SamplingParams
+    from dynalm_b200.sampling.sampler import Sampler
+    g = torch.Generator(device="cpu").manual_seed(vocab)
+    combos = [dict(top_k=40), dict(top_k=5), dict(top_k=1000), dict(top_p=0.9), dict(top_p=0.5), dict(top_k=50, top_p=0.8),
+              dict(top_k=40, min_p=0.05), dict(top_p=0.95, min_p=0.02), dict(top_k=20, top_p=0.9, min_p=0.1),
+              dict(top_k=vocab + 5, top_p=0.7), dict(top_k=2), dict(top_p=0.999)]
+    rows = 4 * len(combos)
+    logits = _peaked_logits(rows, vocab, g, 1.0)
+    logits[3, :17] = -float("inf")                           # masked ids take no part
+    u = torch.rand(rows, generator=g, dtype=torch.float64)
+    u[0], u[1] = 0.0, 1.0 - 2.0 ** -40
+    temps = [0.7, 1.0, 1.6, 0.3]
+    params = [SamplingParams(temperature=temps[r % 4], **combos[r // 4]) for r in range(rows)]
+    samplers = [Sampler(p) for p in params]
+    dparams = torch.tensor([[p.temperature, s.cut_offset, p.top_p, float(u[r])] for r, (p, s) in enumerate(zip(params, samplers))],
+                           dtype=torch.float64)
+    order = torch.randperm(rows, generator=g)                # selections in another order than the rows
+    out = torch.full((rows,), -7, dtype=torch.int32, device=DEV)
+    ops.sample_filtered(logits.to(DEV), order.to(torch.int32).to(DEV), rows, dparams[order].to(DEV),
+                        torch.tensor([params[int(r)].top_k for r in order], dtype=torch.int32, device=DEV), out)
+    got = out.cpu().tolist()
+    same = host = 0
+    for r in range(rows):
+        ref = samplers[r].sample_host(logits[r].numpy().copy(), [], u=float(u[r]))
+        if got[r] == ops.SAMPLE_FILTERED_HOST:
+            # allowed where no filter is in effect (top-k of the vocabulary or more, no top-p), or where top-p alone
+            # keeps more ids than the kernel holds
+            p = params[r]
+            l = logits[r].double()
+            probs = torch.sort(torch.exp((l - l.max()) / p.temperature), descending=True).values
+            nucleus = int((torch.cumsum(probs, 0) < p.top_p * probs.sum()).sum()) + 1
+            assert (p.top_k >= vocab and p.top_p >= 1.0) or (not 0 < p.top_k < vocab and nucleus > 900), \
+                f"vocab {vocab} row {r} {combos[r // 4]}: left to the host with a nucleus of {nucleus}"
+            host += 1
+            continue
+        same += got[r] == ref
+        assert got[r] == ref or abs(float(logits[r, got[r]]) - float(logits[r, ref])) < 0.2, \
+            f"vocab {vocab} row {r} {combos[r // 4]}: {got[r]} vs {ref}"
+    assert host <= rows // 3 and same >= rows - host - 1, (same, host)
+
+
+def test_sample_filtered_leaves_a_wide_nucleus_to_the_host(ops):
+    """Nearly flat logits: top-p 0.9 needs most of 128,256 ids, which is more than the kernel keeps; it says so
+    instead of answering. Top-k on the same row is still answered."""
+    g = torch.Generator(device="cpu").manual_seed(3)
+    logits = (torch.randn(2, 128256, generator=g) * 0.1).to(DEV)
+    out = torch.full((2,), -7, dtype=torch.int32, device=DEV)
+    dparams = torch.tensor([[0.8, -float("inf"), 0.9, 0.5], [0.8, -float("inf"), 1.0, 0.5]], dtype=torch.float64, device=DEV)
+    ops.sample_filtered(logits, torch.tensor([0, 1], dtype=torch.int32, device=DEV), 2, dparams,
+                        torch.tensor([0, 40], dtype=torch.int32, device=DEV), out)
+    got = out.cpu().tolist()
+    assert got[0] == ops.SAMPLE_FILTERED_HOST
+    top40 = torch.topk(logits[1], 40).indices.cpu().tolist()
+    assert got[1] in top40
+
+
+def test_sample_temperature_with_min_p(ops):
+    """min-p in the walk down the ids: against the host's pipeline with the same uniform numbers."""
+    from dynalm_b200.sampling import SamplingParams
+    from dynalm_b200.sampling.sampler import Sampler
+    g = torch.Generator(device="cpu").manual_seed(21)
+    vocab, rows = 20011, 24
+    logits = _peaked_logits(rows, vocab, g, 1.0)
+    u = torch.rand(rows, generator=g, dtype=torch.float64)
+    params = [SamplingParams(temperature=0.9, min_p=(0.0 if r % 3 == 0 else 0.02 * r)) for r in range(rows)]
+    samplers = [Sampler(p) for p in params]
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops.sample_temperature(logits.to(DEV), torch.full((rows,), 0.9, device=DEV), u.to(DEV), out,
+                           cut_offset=torch.tensor([s.cut_offset for s in samplers], dtype=torch.float64, device=DEV))
+    got = out.cpu().tolist()
+    same = 0
+    for r in range(rows):
+        ref = samplers[r].sample_host(logits[r].numpy().copy(), [], u=float(u[r]))
+        same += got[r] == ref
+        if params[r].min_p > 0:
+            cut = float(logits[r].max()) + samplers[r].cut_offset
+            assert float(logits[r, got[r]]) >= cut
+    assert same >= rows - 1
+
+
 @pytest.mark.parametrize("dtype", DTYPES + ["tensor_cores"])
 @pytest.mark.parametrize("heads,kvh,hd,page,window,splits", [(4, 2, 16, 16, 0, 1), (6, 2, 32, 16, 0, 3), (5, 1, 48, 16, 0, 4),
                                                                (3, 3, 80, 32, 0, 2), (8, 2, 128, 16, 40, 2),
