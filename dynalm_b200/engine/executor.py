@@ -33,6 +33,8 @@ class GpuExecutor:
     are all sampled on the device: the ids stay on the device, and a following batch can be launched
     `after` it, taking its tokens from those ids there, before the host has seen them."""
 
+    PENALTY_TRIPLES = 1 << 16      # distinct recent tokens over all penalised rows of a step
+
     def __init__(self, step_fn: StepFunction):
         self.step_fn = step_fn
         self.cache = step_fn.cache
@@ -48,10 +50,16 @@ class GpuExecutor:
         self._ids_host = [torch.zeros(2 * n + 1, dtype=torch.int32).pin_memory() for _ in range(2)]
         self._temp_host = [torch.ones(n, dtype=torch.float32).pin_memory() for _ in range(2)]
         self._u_host = [torch.zeros(n, dtype=torch.float64).pin_memory() for _ in range(2)]
-        self._cut_host = [torch.zeros(n, dtype=torch.float64).pin_memory() for _ in range(2)]
         self._temp = torch.ones(n, dtype=torch.float32, device=dev)
         self._u = torch.zeros(n, dtype=torch.float64, device=dev)
-        self._cut = torch.zeros(n, dtype=torch.float64, device=dev)
+        # what penalties and filters need from the host, two pinned copies of each as above. Integers: the rows with
+        # penalties [n] | the rows of the filtered kernel [n] | their top-k [n] | the penalties' (repetition,
+        # frequency, presence) as float32 bits [3n] | triples (selection, id, count) [3 x PENALTY_TRIPLES].
+        # Doubles: the filtered kernel's (temperature, min-p offset, top-p, uniform) [4n] | the walk's min-p offsets [n].
+        self._stage_i = torch.zeros(6 * n + 3 * self.PENALTY_TRIPLES, dtype=torch.int32, device=dev)
+        self._stage_d = torch.zeros(5 * n, dtype=torch.float64, device=dev)
+        self._stage_i_host = [torch.zeros(self._stage_i.numel(), dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._stage_d_host = [torch.zeros(self._stage_d.numel(), dtype=torch.float64).pin_memory() for _ in range(2)]
         self.host_sampled = 0      # rows that the filtered kernel left to the host so far
         self._turn = 0
         self.h2d_bytes = 0
@@ -87,56 +95,75 @@ class GpuExecutor:
             self._ids_host[slot].copy_(self._ids, non_blocking=True)
             self.d2h_bytes += self._ids_host[slot].numel() * 4
             return {}
-        dev = logits.device
         samplers = [b.seq.sampler for b in want]
+        # top-k of the whole vocabulary or more is no filter (sampler.cpp:118): such a draw walks the ids in their order
+        sorted_draw = [not s.params.greedy and (0 < s.params.top_k < self.vocab or s.params.top_p < 1.0) for s in samplers]
         penalised = [i for i, s in enumerate(samplers) if s.params.has_penalties]
+        filtered = [i for i in range(n) if sorted_draw[i]]
+        walk = [i for i, s in enumerate(samplers) if not s.params.greedy and not sorted_draw[i]]
+        drawn: Dict[int, float] = {}
+        # Everything the sampling kernels need from the host goes over in two copies from pinned memory: integers
+        # (and the penalties' float32 parameters among them, as bits) and doubles.
+        N = self._n
+        ih, dh = self._stage_i_host[slot], self._stage_d_host[slot]
+        ints, dbls = ih.numpy(), dh.numpy()
+        n_triples = 0
         if penalised:
             # the context the penalties see: everything up to and including the tokens just computed
-            triples, params = [], np.zeros((len(penalised), 3), dtype=np.float32)
+            found = []
             for j, i in enumerate(penalised):
                 p = samplers[i].params
                 ids, counts = samplers[i].penalty_counts(want[i].seq.tokens, self.vocab)
-                params[j] = (p.repetition_penalty, p.frequency_penalty, p.presence_penalty)
+                ints[j] = i
+                ints[3 * N + 3 * j:3 * N + 3 * j + 3] = np.array(
+                    [p.repetition_penalty, p.frequency_penalty, p.presence_penalty], dtype=np.float32).view(np.int32)
                 if ids.size:
-                    triples.append(np.stack([np.full(ids.size, j, dtype=np.int64), ids, counts], axis=1))
-            if triples:
-                flat = np.concatenate(triples).astype(np.int32)
-                ops.apply_penalties(logits, torch.tensor(penalised, dtype=torch.int32, device=dev),
-                                    torch.from_numpy(flat).to(dev), flat.shape[0], torch.from_numpy(params).to(dev))
-                self.h2d_bytes += flat.nbytes + params.nbytes + 4 * len(penalised)
+                    found.append(np.stack([np.full(ids.size, j, dtype=np.int64), ids, counts], axis=1))
+            if found:
+                flat = np.concatenate(found).astype(np.int32).ravel()
+                n_triples = flat.size // 3
+                if 6 * N + flat.size > ints.size:
+                    raise EngineError(f"penalties over {n_triples} distinct recent tokens in one step; the executor "
+                                      f"has room for {(ints.size - 6 * N) // 3}")
+                ints[6 * N:6 * N + flat.size] = flat
+        for j, i in enumerate(filtered):
+            p = samplers[i].params
+            drawn[i] = samplers[i].next_uniform()
+            ints[N + j] = i
+            ints[2 * N + j] = p.top_k
+            dbls[4 * j:4 * j + 4] = (p.temperature, samplers[i].cut_offset, p.top_p, drawn[i])
+        with_cut = any(samplers[i].params.min_p > 0.0 for i in walk)
+        if with_cut:
+            dbls[4 * N:4 * N + n] = -np.inf
+            for i in walk:
+                dbls[4 * N + i] = samplers[i].cut_offset
+        if penalised or filtered:
+            used = 6 * N + 3 * n_triples
+            self._stage_i[:used].copy_(ih[:used], non_blocking=True)
+            self.h2d_bytes += 4 * used
+        if filtered or with_cut:
+            used = 4 * N + (n if with_cut else 0)
+            self._stage_d[:used].copy_(dh[:used], non_blocking=True)
+            self.h2d_bytes += 8 * used
+        if n_triples:
+            ops.apply_penalties(logits, self._stage_i[:len(penalised)], self._stage_i[6 * N:6 * N + 3 * n_triples], n_triples,
+                                self._stage_i[3 * N:3 * N + 3 * len(penalised)].view(torch.float32))
         ops.argmax(logits, self._ids[:n], status_to=self._ids[2 * self._n:])
-        # top-k of the whole vocabulary or more is no filter (sampler.cpp:118): such a draw walks the ids in their order
-        sorted_draw = [not s.params.greedy and (0 < s.params.top_k < self.vocab or s.params.top_p < 1.0) for s in samplers]
-        walk = [i for i, s in enumerate(samplers) if not s.params.greedy and not sorted_draw[i]]
         if walk:
-            th, uh, ch = self._temp_host[slot], self._u_host[slot], self._cut_host[slot]
+            th, uh = self._temp_host[slot], self._u_host[slot]
             th[:n] = 1.0
             uh[:n] = 0.0
-            ch[:n] = -np.inf
             for i in walk:
                 th[i] = samplers[i].params.temperature
                 uh[i] = samplers[i].next_uniform()
-                ch[i] = samplers[i].cut_offset
             self._temp[:n].copy_(th[:n], non_blocking=True)
             self._u[:n].copy_(uh[:n], non_blocking=True)
-            with_cut = any(samplers[i].params.min_p > 0.0 for i in walk)
-            if with_cut:
-                self._cut[:n].copy_(ch[:n], non_blocking=True)
-            self.h2d_bytes += (20 if with_cut else 12) * n
+            self.h2d_bytes += 12 * n
             ops.sample_temperature(logits, self._temp, self._u, self._ids[self._n:self._n + n],
-                                   cut_offset=self._cut if with_cut else None)
-        drawn: Dict[int, float] = {}
-        filtered = [i for i in range(n) if sorted_draw[i]]
+                                   cut_offset=self._stage_d[4 * N:4 * N + n] if with_cut else None)
         if filtered:
-            dparams = np.zeros((len(filtered), 4), dtype=np.float64)
-            for j, i in enumerate(filtered):
-                p = samplers[i].params
-                drawn[i] = samplers[i].next_uniform()
-                dparams[j] = (p.temperature, samplers[i].cut_offset, p.top_p, drawn[i])
-            ints = torch.tensor([filtered, [samplers[i].params.top_k for i in filtered]], dtype=torch.int32, device=dev)
-            ops.sample_filtered(logits, ints[0], len(filtered), torch.from_numpy(dparams).to(dev), ints[1],
-                                self._ids[self._n:self._n + n])
-            self.h2d_bytes += dparams.nbytes + 8 * len(filtered)
+            ops.sample_filtered(logits, self._stage_i[N:N + len(filtered)], len(filtered), self._stage_d[:4 * len(filtered)],
+                                self._stage_i[2 * N:2 * N + len(filtered)], self._ids[self._n:self._n + n])
         self._ids_host[slot].copy_(self._ids, non_blocking=True)
         self.d2h_bytes += self._ids_host[slot].numel() * 4
         return drawn
