@@ -265,9 +265,8 @@ sample_temperature_kernel(const float* __restrict__ logits, int ld, int vocab, i
 //
 // The reference's pipeline, penalties -> top-k -> temperature -> min-p -> top-p -> draw
 // (dynalm/src/sampling/sampler.cpp:96-220), works on the candidates in the order (logit descending, id ascending).
-// Here one block per row narrows the vocabulary to at most SAMPLE_CAP candidates that are certain to hold every id
-// the pipeline can still choose, sorts those, and finishes the pipeline on them in double precision; a row whose
-// candidates do not fit gives -1 and is done by the host from its logits.
+// Here one block per row narrows the vocabulary down to the places in that order on which the pipeline turns (see
+// sample_filtered_kernel); a row that does not fit gives -1 and is done by the host from its logits.
 
 // Repetition, frequency and presence penalties (sampler.cpp:96-116): triple j = (selection, token id, count of the
 // id in the request's recent context), ids unique within a selection; params[selection] = (repetition, frequency,
@@ -289,24 +288,6 @@ __global__ void apply_penalties_kernel(float* __restrict__ logits, int ld, int v
 constexpr int SAMPLE_CAP = 1024;          // candidates a row may keep (= threads of its block)
 constexpr int SAMPLE_BINS = 2048;
 constexpr double SAMPLE_FIXED = 1099511627776.0;      // 2^40: masses as integers, so that their sums have no order
-
-// Sum over the block in a fixed order; every thread gets it. `red`: 33 doubles.
-__device__ __forceinline__ double block_sum_f64(double v, double* red) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  __syncthreads();
-  if (lane == 0) red[warp] = v;
-  __syncthreads();
-  if (warp == 0) {
-    double t = red[lane];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-    if (lane == 0) red[32] = t;
-  }
-  __syncthreads();
-  return red[32];
-}
 
 // Inclusive running sum over the block's threads in thread order. `red`: 33 doubles.
 __device__ __forceinline__ double block_scan_f64(double v, double* red) {
@@ -351,42 +332,73 @@ __device__ __forceinline__ int sample_bin(float l, float lo, float scale) {
   return x <= 0.0f ? 0 : (x >= static_cast<float>(SAMPLE_BINS - 1) ? SAMPLE_BINS - 1 : static_cast<int>(x));
 }
 
-// From the top bin down: the highest bin b whose bins b.. together reach `target`; *rest = what of the target is
-// still to find inside b. All of the block's threads call it; hist has been filled and synchronised. If even all
-// bins do not reach the target the answer is bin 0.
-__device__ __forceinline__ int sample_pick_bin(const unsigned long long* hist, unsigned long long target,
-                                               unsigned long long* rest, double* red, int* shared_bin,
-                                               unsigned long long* shared_rest) {
-  // thread t owns bins SAMPLE_BINS-1-2t and SAMPLE_BINS-2-2t: a running sum over threads runs from the top bin down
-  const int b_hi = SAMPLE_BINS - 1 - 2 * static_cast<int>(threadIdx.x), b_lo = b_hi - 1;
-  const unsigned long long h_hi = hist[b_hi], h_lo = hist[b_lo];
-  // masses are below 2^58 in all: doubles would round them, so the running sum is made of two 32-bit halves
-  const double lo_part = block_scan_f64(static_cast<double>((h_hi + h_lo) & 0xffffffffull), red);
-  const double hi_part = block_scan_f64(static_cast<double>((h_hi + h_lo) >> 32), red);
-  const unsigned long long incl = static_cast<unsigned long long>(lo_part) + (static_cast<unsigned long long>(hi_part) << 32);
-  const unsigned long long before = incl - (h_hi + h_lo);
-  if (threadIdx.x == 0) { *shared_bin = 0; *shared_rest = target; }
-  __syncthreads();
-  if (before < target && incl >= target) {          // exactly one thread (none if the target is out of reach)
-    if (before + h_hi >= target) { *shared_bin = b_hi; *shared_rest = target - before; }
-    else { *shared_bin = b_lo; *shared_rest = target - before - h_hi; }
+// Inclusive running sum of integers over the block's threads in thread order. `red`: 33 words.
+__device__ __forceinline__ unsigned long long block_scan_u64(unsigned long long v, unsigned long long* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned long long x = __shfl_up_sync(0xffffffffu, v, o);
+    if (lane >= o) v += x;
   }
   __syncthreads();
-  *rest = *shared_rest;
-  return *shared_bin;
+  if (lane == 31) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    const unsigned long long w = red[lane];
+    unsigned long long wi = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned long long x = __shfl_up_sync(0xffffffffu, wi, o);
+      if (lane >= o) wi += x;
+    }
+    red[lane] = wi - w;
+    if (lane == 31) red[32] = wi;
+  }
+  __syncthreads();
+  return v + red[warp];
 }
 
+// The bins that narrow a row down, level by level: level n + 1 divides the chosen bin of level n again.
+struct SampleBins {
+  float lo[3], scale[3];
+  int bin[3];
+  int depth;
+  // +1 above the chosen bins, 0 inside them, -1 below
+  __device__ __forceinline__ int side(float l) const {
+    for (int level = 0; level < depth; ++level) {
+      const int b = sample_bin(l, lo[level], scale[level]);
+      if (b != bin[level]) return b > bin[level] ? 1 : -1;
+    }
+    return 0;
+  }
+};
+
 // dparams[sel] = (temperature, temperature * log(min_p) or -inf, top_p, uniform); top_k[sel]: 0 = off.
+//
+// Both filters come down to finding a place in the order (logit descending, id ascending) by a running total from
+// the top: of ids for top-k, of mass for top-p and for the draw. The row is narrowed to that place by histograms
+// over equal steps of the logit, up to three levels deep, until the bin that holds the place has at most SAMPLE_CAP
+// ids; those are sorted and the place is found among them. Masses are integers (expf(...) * 2^40, cut off), so that
+// their sums do not depend on the order in which threads add them and a running total is exact.
+//   top-k (with or without top-p): the ids at or above the bin of the k-th are the candidates (at most SAMPLE_CAP,
+//     else the host); on them, sorted, the reference's pipeline in double precision.
+//   top-p alone: the nucleus may be most of the vocabulary, so nothing but the bin of its last id is gathered:
+//     the place where the running mass reaches top_p of the whole gives the mass kept, the place where it exceeds
+//     uniform * kept gives the id.
 __global__ void __launch_bounds__(SAMPLE_CAP)
 sample_filtered_kernel(const float* __restrict__ logits, int ld, int vocab, const int* __restrict__ rows,
                        const double* __restrict__ dparams, const int* __restrict__ top_k, int* __restrict__ out) {
-  __shared__ unsigned long long hist[SAMPLE_BINS];
+  __shared__ unsigned long long hist[SAMPLE_BINS];       // mass (or count) per bin
+  __shared__ unsigned int cnt[SAMPLE_BINS];              // ids per bin
   __shared__ unsigned long long cand[SAMPLE_CAP];
+  __shared__ unsigned long long red_u[33];
   __shared__ double red[33];
   __shared__ float redf[33];
   __shared__ int red_i[32];
-  __shared__ int n_cand, picked_bin;
-  __shared__ unsigned long long picked_rest;
+  __shared__ int n_cand, picked_bin, picked_in_bin, picked_count_above;
+  __shared__ unsigned long long picked_rest, found_cum;
+  __shared__ int found_id;
+  __shared__ double kept_s;
   const int sel = blockIdx.x, t = threadIdx.x;
   const int out_at = ck_row(rows[sel]);
   const float* row = logits + static_cast<size_t>(out_at) * ld;
@@ -415,130 +427,188 @@ sample_filtered_kernel(const float* __restrict__ logits, int ld, int vocab, cons
     return;
   }
   const double cut = static_cast<double>(hi) + cut_off;      // min-p: logits below it are out (sampler.cpp:146)
+  auto counted = [&](float l) { return l > -INFINITY; };
+  auto mass = [&](float l) -> unsigned long long {
+    return l > -INFINITY && static_cast<double>(l) >= cut
+               ? static_cast<unsigned long long>(static_cast<double>(expf((l - hi) * inv_t)) * SAMPLE_FIXED) : 0ull;
+  };
 
-  // the mass after min-p over the whole vocabulary, which top-p without top-k measures its share against
-  double total = 0.0;
-  if (use_p && !use_k) {
-    double mine = 0.0;
-    for (int i = t; i < vocab; i += SAMPLE_CAP) {
-      const float l = row[i];
-      if (l > -INFINITY && static_cast<double>(l) >= cut) mine += exp((static_cast<double>(l) - static_cast<double>(hi)) / temp);
+  SampleBins bins;
+  // Narrows the row to the bin in which the running total from the top (of ids if by_count, else of mass) reaches
+  // x >= 1. Returns what of x is left to find inside that bin; *ids_above = the ids in the bins above it.
+  // `whole`: stop as soon as the ids above and inside fit the candidates (top-k), not only those inside.
+  auto narrow = [&](unsigned long long x, bool by_count, bool whole, int* ids_above, int* ids_inside) -> unsigned long long {
+    unsigned long long rest = x;
+    int above = 0, inside = 0;
+    bins.depth = 0;
+    for (int level = 0; level < 3; ++level) {
+      bins.lo[level] = level == 0 ? lo : bins.lo[level - 1] + static_cast<float>(bins.bin[level - 1]) / bins.scale[level - 1];
+      bins.scale[level] = level == 0 ? (hi > lo ? static_cast<float>(SAMPLE_BINS) / (hi - lo) : 0.0f)
+                                     : bins.scale[level - 1] * static_cast<float>(SAMPLE_BINS);
+      if (level > 0 && !(bins.scale[level - 1] > 0.0f)) { bins.lo[level] = lo; bins.scale[level] = 0.0f; }
+      for (int b = t; b < SAMPLE_BINS; b += SAMPLE_CAP) { hist[b] = 0; cnt[b] = 0; }
+      __syncthreads();
+      for (int i = t; i < vocab; i += SAMPLE_CAP) {
+        const float l = row[i];
+        if (!counted(l) || bins.side(l) != 0) continue;
+        const int b = sample_bin(l, bins.lo[level], bins.scale[level]);
+        const unsigned long long w = by_count ? 1ull : mass(l);
+        if (w != 0) atomicAdd(&hist[b], w);
+        atomicAdd(&cnt[b], 1u);
+      }
+      __syncthreads();
+      // thread t owns bins SAMPLE_BINS-1-2t and SAMPLE_BINS-2-2t: a running sum over threads runs from the top bin down
+      const int b_hi = SAMPLE_BINS - 1 - 2 * t, b_lo = b_hi - 1;
+      const unsigned long long h_hi = hist[b_hi], h_lo = hist[b_lo];
+      const unsigned int c_hi = cnt[b_hi], c_lo = cnt[b_lo];
+      const unsigned long long incl = block_scan_u64(h_hi + h_lo, red_u);
+      const unsigned long long c_incl = block_scan_u64(c_hi + c_lo, red_u);
+      const unsigned long long before = incl - (h_hi + h_lo);
+      const int c_before = static_cast<int>(c_incl - (c_hi + c_lo));
+      if (t == 0) {      // out of reach (x beyond the whole): the lowest bin, everything above it
+        picked_bin = 0;
+        picked_rest = rest;
+        picked_count_above = -1;
+      }
+      __syncthreads();
+      if (before < rest && incl >= rest) {          // exactly one thread (none if out of reach)
+        if (before + h_hi >= rest) {
+          picked_bin = b_hi; picked_rest = rest - before; picked_count_above = c_before; picked_in_bin = static_cast<int>(c_hi);
+        } else {
+          picked_bin = b_lo; picked_rest = rest - before - h_hi; picked_count_above = c_before + static_cast<int>(c_hi);
+          picked_in_bin = static_cast<int>(c_lo);
+        }
+      }
+      __syncthreads();
+      if (picked_count_above < 0) {                // every id of this level lies at or above bin 0
+        unsigned int all = 0;
+        for (int b = 1; b < SAMPLE_BINS; ++b) all += cnt[b];
+        above += static_cast<int>(all);
+        inside = static_cast<int>(cnt[0]);
+      } else {
+        above += picked_count_above;
+        inside = picked_in_bin;
+      }
+      bins.bin[level] = picked_bin;
+      rest = picked_rest;
+      bins.depth = level + 1;
+      __syncthreads();
+      if ((whole ? above + inside : inside) <= SAMPLE_CAP) break;
     }
-    total = block_sum_f64(mine, red);
-  }
-
-  // Two rounds of SAMPLE_BINS equal steps, the second inside the bin in which the first found the boundary: by count
-  // (the top_k-th logit) or by mass (where the running mass from the top reaches top_p of the whole, with room for
-  // the rounding of the integer masses). Everything at or above the boundary bin is a candidate.
-  unsigned long long target;
-  if (use_k) {
-    target = static_cast<unsigned long long>(k);
-  } else {
-    target = 0;           // set after the first histogram, from its own total
-  }
-  float lo1 = lo, scale1 = hi > lo ? static_cast<float>(SAMPLE_BINS) / (hi - lo) : 0.0f;
-  int bin1 = 0, bin2 = 0;
-  float lo2 = lo, scale2 = 0.0f;
-  for (int round = 0; round < 2; ++round) {
-    for (int b = t; b < SAMPLE_BINS; b += SAMPLE_CAP) hist[b] = 0;
+    *ids_above = above;
+    *ids_inside = inside;
+    return rest;
+  };
+  // The ids inside the chosen bins (and above them, if `with_above`) into cand, sorted by (logit descending, id
+  // ascending); the number of them, or -1 if they do not fit.
+  auto gather_sorted = [&](bool with_above) -> int {
+    if (t == 0) n_cand = 0;
     __syncthreads();
     for (int i = t; i < vocab; i += SAMPLE_CAP) {
       const float l = row[i];
-      if (!(l > -INFINITY)) continue;
-      const int b1 = sample_bin(l, lo1, scale1);
-      if (round == 1 && b1 != bin1) continue;
-      const int b = round == 0 ? b1 : sample_bin(l, lo2, scale2);
-      const unsigned long long w = use_k ? 1ull
-          : static_cast<unsigned long long>(static_cast<double>(expf((l - hi) * inv_t)) * SAMPLE_FIXED);
-      atomicAdd(&hist[b], w);
+      if (!counted(l)) continue;
+      const int side = bins.side(l);
+      if (side < 0 || (side > 0 && !with_above)) continue;
+      const int at = atomicAdd(&n_cand, 1);
+      if (at < SAMPLE_CAP) {
+        const unsigned int bits = __float_as_uint(l);
+        const unsigned int rising = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);     // grows with the logit
+        cand[at] = (static_cast<unsigned long long>(~rising) << 32) | static_cast<unsigned int>(i);
+      }
     }
     __syncthreads();
-    if (round == 0 && !use_k) {
-      // top-p alone: the share of the integer masses' own sum, a little more than asked for
-      unsigned long long mine = 0;
-      for (int b = t; b < SAMPLE_BINS; b += SAMPLE_CAP) mine += hist[b];
-      const double lo_part = block_sum_f64(static_cast<double>(mine & 0xffffffffull), red);
-      const double hi_part = block_sum_f64(static_cast<double>(mine >> 32), red);
-      const double all = lo_part + hi_part * 4294967296.0;
-      target = static_cast<unsigned long long>(top_p * all * (1.0 + 1e-5)) + static_cast<unsigned long long>(vocab);
+    const int n = n_cand;
+    __syncthreads();
+    if (n > SAMPLE_CAP || n == 0) return -1;
+    if (t >= n) cand[t] = ~0ull;
+    __syncthreads();
+    for (int size = 2; size <= SAMPLE_CAP; size <<= 1) {
+      for (int stride = size >> 1; stride > 0; stride >>= 1) {
+        const int other = t ^ stride;
+        if (other > t) {
+          const unsigned long long a = cand[t], b = cand[other];
+          const bool up = (t & size) == 0;
+          if ((a > b) == up) { cand[t] = b; cand[other] = a; }
+        }
+        __syncthreads();
+      }
     }
-    unsigned long long rest;
-    const int b = sample_pick_bin(hist, target, &rest, red, &picked_bin, &picked_rest);
-    if (round == 0) {
-      bin1 = b;
-      lo2 = lo1 + static_cast<float>(b) / scale1;
-      scale2 = scale1 * static_cast<float>(SAMPLE_BINS);
-      if (!(scale1 > 0.0f)) { lo2 = lo1; scale2 = 0.0f; }
-      target = rest;
-    } else {
-      bin2 = b;
+    return n;
+  };
+
+  if (!use_k) {
+    // ---- top-p alone ----
+    unsigned long long mine = 0;
+    for (int i = t; i < vocab; i += SAMPLE_CAP) mine += mass(row[i]);
+    block_scan_u64(mine, red_u);
+    const unsigned long long total = red_u[32];
+    __syncthreads();
+    // The first place (in the order) where the running mass reaches x: its id, and the running mass there.
+    auto locate = [&](unsigned long long x) -> bool {
+      int ids_above, ids_inside;
+      const unsigned long long rest = narrow(x, false, false, &ids_above, &ids_inside);
+      const int n = gather_sorted(false);
+      if (n < 0) return false;
+      const int id = static_cast<int>(cand[t] & 0xffffffffull);
+      const unsigned long long w = t < n ? mass(row[id]) : 0ull;
+      const unsigned long long cum = block_scan_u64(w, red_u);
+      const int pos = block_count(t < n && cum < rest, red_i);
+      if (pos >= n) return false;                      // the bin does not hold the place after all
+      if (t == pos) { found_id = id; found_cum = (x - rest) + cum; }
+      __syncthreads();
+      return true;
+    };
+    if (total == 0) {
+      if (t == 0) out[out_at] = -1;
+      return;
     }
+    unsigned long long share = static_cast<unsigned long long>(top_p * static_cast<double>(total));
+    share = share < 1 ? 1 : (share > total ? total : share);
+    if (!locate(share)) {
+      if (t == 0) out[out_at] = -1;
+      return;
+    }
+    const unsigned long long kept = found_cum;          // the mass of the nucleus (sampler.cpp:196-205)
+    __syncthreads();
+    unsigned long long aim = static_cast<unsigned long long>(u * static_cast<double>(kept));
+    if (aim >= kept) aim = kept - 1;
+    if (!locate(aim + 1)) {                             // the first place where the running mass exceeds u * kept
+      if (t == 0) out[out_at] = -1;
+      return;
+    }
+    if (t == 0) out[out_at] = found_id;
+    return;
   }
 
-  // the candidates, in whatever order they arrive: (logit descending, id ascending) as one integer to sort by
-  if (t == 0) n_cand = 0;
-  __syncthreads();
-  for (int i = t; i < vocab; i += SAMPLE_CAP) {
-    const float l = row[i];
-    if (!(l > -INFINITY)) continue;
-    const int b1 = sample_bin(l, lo1, scale1);
-    if (b1 < bin1 || (b1 == bin1 && sample_bin(l, lo2, scale2) < bin2)) continue;
-    const int at = atomicAdd(&n_cand, 1);
-    if (at < SAMPLE_CAP) {
-      const unsigned int bits = __float_as_uint(l);
-      const unsigned int rising = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);     // grows with the logit
-      cand[at] = (static_cast<unsigned long long>(~rising) << 32) | static_cast<unsigned int>(i);
-    }
-  }
-  __syncthreads();
-  const int n = n_cand;
-  if (n > SAMPLE_CAP || n == 0) {
+  // ---- top-k, with or without top-p ----
+  int ids_above, ids_inside;
+  narrow(static_cast<unsigned long long>(k), true, true, &ids_above, &ids_inside);
+  const int n = gather_sorted(true);
+  if (n < 0) {
     if (t == 0) out[out_at] = -1;
     return;
   }
-  if (t >= n) cand[t] = ~0ull;
-  __syncthreads();
-  for (int size = 2; size <= SAMPLE_CAP; size <<= 1) {
-    for (int stride = size >> 1; stride > 0; stride >>= 1) {
-      const int other = t ^ stride;
-      if (other > t) {
-        const unsigned long long a = cand[t], b = cand[other];
-        const bool up = (t & size) == 0;
-        if ((a > b) == up) { cand[t] = b; cand[other] = a; }
-      }
-      __syncthreads();
-    }
-  }
-
   // the pipeline on the sorted candidates, thread i = candidate i
   const int id = static_cast<int>(cand[t] & 0xffffffffull);
   const double l = t < n ? static_cast<double>(row[id]) : 0.0;
-  const int k_eff = use_k ? min(k, n) : n;
+  const int k_eff = min(k, n);
   const bool valid = t < k_eff && l >= cut;
   const int m = block_count(valid, red_i);             // sorted: the valid ones are the first m
   if (m == 0) {
     if (t == 0) out[out_at] = static_cast<int>(cand[0] & 0xffffffffull);        // cannot be: the largest logit passes
     return;
   }
-  // a boundary found by count holds all of the first k; one found by mass must reach the share asked for (checked
-  // below)
   double prob = valid ? exp((l - static_cast<double>(hi)) / temp) : 0.0;
   double cum = block_scan_f64(prob, red);
-  __shared__ double kept_s;
   if (t == m - 1) kept_s = cum;
   __syncthreads();
   double kept = kept_s;
   int keep = m;
-  const bool some_left_out = bin1 > 0 || bin2 > 0;      // finite logits below the boundary exist, or may
   if (use_p) {
-    const double share = top_p * (use_k ? kept : total);
-    if (!use_k && kept < share && some_left_out) {     // the candidates do not hold the whole nucleus
-      if (t == 0) out[out_at] = -1;
-      return;
-    }
+    const double share = top_p * kept;                   // with top-k, top-p applies to what top-k kept
     keep = block_count(valid && cum < share, red_i) + 1;           // first place where the running mass reaches it
     keep = max(1, min(keep, m));
-    if (t >= keep) prob = 0.0;
+    __syncthreads();
     if (t == keep - 1) kept_s = cum;
     __syncthreads();
     kept = kept_s;

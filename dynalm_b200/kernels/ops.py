@@ -1019,7 +1019,7 @@ def sample_filtered(logits: torch.Tensor, rows: torch.Tensor, n_sel: int, dparam
     """One draw per selection through top-k, min-p and top-p in the reference's order. rows int32 [n_sel]: the
     logits row of each selection; dparams float64 [n_sel, 4] = (temperature, temperature * log(min_p) or -inf, top_p,
     uniform in [0, 1)); top_k int32 [n_sel] (0 = off); out int32 with a place for every row named: out[rows[sel]] gets the id,
-    or SAMPLE_FILTERED_HOST where the row's candidates do not fit the kernel (a nucleus of more than 1,024 ids, say)."""
+    or SAMPLE_FILTERED_HOST where the row does not fit the kernel (top-k above 1,024, say)."""
     _cuda(logits, rows, dparams, top_k, out)
     _rows_contiguous(logits, "logits")
     if (logits.dtype != torch.float32 or rows.dtype != torch.int32 or dparams.dtype != torch.float64

@@ -372,19 +372,33 @@ def test_sample_filtered_matches_the_host_pipeline(ops, vocab):
     assert host <= rows // 3 and same >= rows - host - 1, (same, host)
 
 
-def test_sample_filtered_leaves_a_wide_nucleus_to_the_host(ops):
-    """Nearly flat logits: top-p 0.9 needs most of 128,256 ids, which is more than the kernel keeps; it says so
-    instead of answering. Top-k on the same row is still answered."""
+def test_sample_filtered_with_a_wide_nucleus(ops):
+    """Nearly flat logits: top-p keeps most of 128,256 ids, far more than the kernel can hold as candidates; it finds
+    the end of the nucleus and the drawn id by narrowing the row down to one bin at a time. Against the host's
+    pipeline with the same uniform numbers. Top-k of more than the kernel holds is left to the host."""
+    from dynalm_b200.sampling import SamplingParams
+    from dynalm_b200.sampling.sampler import Sampler
     g = torch.Generator(device="cpu").manual_seed(3)
-    logits = (torch.randn(2, 128256, generator=g) * 0.1).to(DEV)
-    out = torch.full((2,), -7, dtype=torch.int32, device=DEV)
-    dparams = torch.tensor([[0.8, -float("inf"), 0.9, 0.5], [0.8, -float("inf"), 1.0, 0.5]], dtype=torch.float64, device=DEV)
-    ops.sample_filtered(logits, torch.tensor([0, 1], dtype=torch.int32, device=DEV), 2, dparams,
-                        torch.tensor([0, 40], dtype=torch.int32, device=DEV), out)
+    vocab, rows = 128256, 9
+    logits = torch.randn(rows, vocab, generator=g) * 0.1
+    logits[2, 1000:1200] = logits[2, 999]                    # two hundred equal logits in the middle of a nucleus
+    logits[5] = 0.25                                         # a row of equal logits: no bin can divide them
+    u = torch.rand(rows, generator=g, dtype=torch.float64)
+    params = [SamplingParams(temperature=0.8, top_p=[0.9, 0.5, 0.99][r % 3], min_p=0.5 if r == 7 else 0.0,
+                             top_k=5000 if r == 8 else 0) for r in range(rows)]
+    samplers = [Sampler(p) for p in params]
+    dparams = torch.tensor([[p.temperature, s.cut_offset, p.top_p, float(u[r])] for r, (p, s) in enumerate(zip(params, samplers))],
+                           dtype=torch.float64, device=DEV)
+    out = torch.full((rows,), -7, dtype=torch.int32, device=DEV)
+    ops.sample_filtered(logits.to(DEV), torch.arange(rows, dtype=torch.int32, device=DEV), rows, dparams,
+                        torch.tensor([p.top_k for p in params], dtype=torch.int32, device=DEV), out)
     got = out.cpu().tolist()
-    assert got[0] == ops.SAMPLE_FILTERED_HOST
-    top40 = torch.topk(logits[1], 40).indices.cpu().tolist()
-    assert got[1] in top40
+    assert got[8] == ops.SAMPLE_FILTERED_HOST and got[5] == ops.SAMPLE_FILTERED_HOST
+    answered = [r for r in range(rows) if r not in (5, 8)]
+    refs = {r: samplers[r].sample_host(logits[r].numpy().copy(), [], u=float(u[r])) for r in answered}
+    assert sum(got[r] == refs[r] for r in answered) >= len(answered) - 1, (got, refs)
+    for r in answered:
+        assert got[r] == refs[r] or abs(float(logits[r, got[r]]) - float(logits[r, refs[r]])) < 1e-3, (r, got[r], refs[r])
 
 
 def test_sample_temperature_with_min_p(ops):
