@@ -30,8 +30,7 @@ enum { T5_ERR_PRODUCER = 1, T5_ERR_MMA = 2, T5_ERR_EPILOGUE = 3 };
 // [n0, n0 + 128) and [F + n0, F + n0 + 128). Otherwise unused.
 //
 // The kernel is persistent: gridDim.x blocks (at most one per SM) walk the output tiles in the order
-// tile = blockIdx.x, blockIdx.x + gridDim.x, ...; tiles with consecutive numbers share their rows of x
-// (tile -> row block tile / tiles_n, column block tile % tiles_n), so x stays in L2 while W streams.
+// tile = blockIdx.x, blockIdx.x + gridDim.x, ...; see t5_tile_coords for which tile a number stands for.
 // The accumulator is double-buffered in tensor memory (2 x 256 columns): the epilogue warps drain
 // one tile while the MMA warp fills the next.
 //
@@ -41,11 +40,29 @@ enum { T5_ERR_PRODUCER = 1, T5_ERR_MMA = 2, T5_ERR_EPILOGUE = 3 };
 // from L2 once per pair (measured: the kernel is bound by operand traffic from L2; loading a third less made it
 // a fifth faster). A stage is then free only when both blocks' MMAs have read it: each block's commit arrives on
 // the stage's barrier in both blocks, and the barrier counts two arrivals.
+// Which output tile a tile number stands for. Tiles are numbered in groups of `group_m` row blocks: inside a
+// group the row block changes fastest, then the column block; the groups follow one another. The blocks of the grid
+// work on consecutive numbers at any time, so together they hold group_m row blocks of x and gridDim.x / group_m
+// column blocks of W: both stay in L2 while they are used, and over the whole product W comes from memory once
+// per group and x once. (Numbered along the columns first, as this kernel did at first, every row block brings all
+// of W in again: with the 235 MB of a 4096 -> 2 x 14336 gate|up matrix that bound the product to memory, 1,684 us
+// for 8,192 rows where the arithmetic needs 1,300.)
+__device__ __forceinline__ void t5_tile_coords(int tile, int tiles_n, int num_tiles, int group_m, int* m_tile, int* n_tile) {
+  const int tiles_m = num_tiles / tiles_n;
+  const int per_group = group_m * tiles_n;
+  const int g = tile / per_group;
+  const int first_m = g * group_m;
+  const int rows = min(group_m, tiles_m - first_m);
+  const int r = tile - g * per_group;
+  *m_tile = first_m + r % rows;
+  *n_tile = r / rows;
+}
+
 template <int T5_BN, class P>
 __global__ void __launch_bounds__(T5_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     void* __restrict__ y, int ldy, int M, int N, int K, int mode, float out_scale, int gate_rows,
-                    int tiles_n, int num_tiles, int* __restrict__ status, const QkvRope rope) {
+                    int tiles_n, int num_tiles, int group_m, int* __restrict__ status, const QkvRope rope) {
   constexpr int T5_STAGES = T5<T5_BN>::STAGES;
   constexpr uint32_t T5_B_BYTES = T5<T5_BN>::B_BYTES, T5_STAGE_BYTES = T5<T5_BN>::STAGE_BYTES, T5_TMEM_COLS = T5<T5_BN>::TMEM_COLS;
   extern __shared__ unsigned char t5_raw[];
@@ -110,7 +127,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     };
     const int ahead = first_tile < num_tiles ? min(k_tiles, T5_STAGES) : 0;
     if (ahead > 0) {
-      const int m0 = ((first_tile / tiles_n) * P::CLUSTER + rank) * T5_BM, n0 = (first_tile % tiles_n) * n_per_tile;
+      int m_tile, n_tile;
+      t5_tile_coords(first_tile, tiles_n, num_tiles, group_m, &m_tile, &n_tile);
+      const int m0 = (m_tile * P::CLUSTER + rank) * T5_BM, n0 = n_tile * n_per_tile;
       if (elect_one()) {
         for (int kt = 0; kt < ahead; ++kt) {
           mbar_expect_tx(&full_bar[kt], T5_STAGE_BYTES);
@@ -131,7 +150,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     uint32_t it = ahead;                           // k-slices issued so far, over all tiles
     bool ok = true;
     for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
-      const int m0 = ((tile / tiles_n) * P::CLUSTER + rank) * T5_BM, n0 = (tile % tiles_n) * n_per_tile;
+      int m_tile, n_tile;
+      t5_tile_coords(tile, tiles_n, num_tiles, group_m, &m_tile, &n_tile);
+      const int m0 = (m_tile * P::CLUSTER + rank) * T5_BM, n0 = n_tile * n_per_tile;
       for (int kt = tile == first_tile ? ahead : 0; kt < k_tiles; ++kt, ++it) {
         const int s = it % T5_STAGES;
         if (it >= T5_STAGES && !warp_wait(&empty_bar[s], ((it / T5_STAGES) & 1) ^ 1, status, T5_ERR_PRODUCER, abort_flag)) {
@@ -190,7 +211,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     uint32_t local = 0;
     for (int tile = first_tile; tile < num_tiles; tile += tile_step, ++local) {
       const uint32_t buf = local & 1;
-      const int m0 = ((tile / tiles_n) * P::CLUSTER + rank) * T5_BM, n0 = (tile % tiles_n) * n_per_tile;
+      int m_tile, n_tile;
+      t5_tile_coords(tile, tiles_n, num_tiles, group_m, &m_tile, &n_tile);
+      const int m0 = (m_tile * P::CLUSTER + rank) * T5_BM, n0 = n_tile * n_per_tile;
       const int row = m0 + quarter * 32 + lane;
       if (!warp_wait(&acc_full[buf], (local >> 1) & 1, status, T5_ERR_EPILOGUE, abort_flag)) break;
       tcgen05_after_sync();
@@ -415,6 +438,14 @@ static int t5_launch(const void* x, int ldx, const void* w, void* y, int ldy, in
   if (rc != 0) return rc;
   rc = dl::make_map(&map_w, w, N, K, K, bn / 2);
   if (rc != 0) return rc;
+  // Row blocks to a group of tiles (t5_tile_coords): as many as keep the group's rows of x within about 32 MB of L2,
+  // 4 to 16. DYNALM_GEMM_GROUP_M overrides it (1: along the columns first).
+  static int forced_group = -1;
+  if (forced_group < 0) { const char* e = getenv("DYNALM_GEMM_GROUP_M"); forced_group = e ? atoi(e) : 0; }
+  long long group = (32ll << 20) / (2ll * dl::T5_BM * P::CLUSTER * K);
+  group = group < 4 ? 4 : (group > 16 ? 16 : group);
+  if (forced_group > 0) group = forced_group;
+  const int group_m = static_cast<int>(group < m_tiles ? group : m_tiles);
   const int blocks = static_cast<int>(tiles < units ? tiles : units) * P::CLUSTER;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(blocks);
@@ -447,7 +478,7 @@ static int t5_launch(const void* x, int ldx, const void* w, void* y, int ldy, in
     }
     cfg.dynamicSmemBytes = dl::T5<256>::SMEM;
     return static_cast<int>(cudaLaunchKernelEx(&cfg, dl::gemm_tcgen05_kernel<256, P>, map_x, map_w, y, ldy, M, N, K, mode,
-                                               out_scale, gate_rows, tiles_n, static_cast<int>(tiles), status, rope));
+                                               out_scale, gate_rows, tiles_n, static_cast<int>(tiles), group_m, status, rope));
   } else if (bn == 192) {
     static bool configured = false;
     if (!configured) {
@@ -458,7 +489,7 @@ static int t5_launch(const void* x, int ldx, const void* w, void* y, int ldy, in
     }
     cfg.dynamicSmemBytes = dl::T5<192>::SMEM;
     return static_cast<int>(cudaLaunchKernelEx(&cfg, dl::gemm_tcgen05_kernel<192, P>, map_x, map_w, y, ldy, M, N, K, mode,
-                                               out_scale, gate_rows, tiles_n, static_cast<int>(tiles), status, rope));
+                                               out_scale, gate_rows, tiles_n, static_cast<int>(tiles), group_m, status, rope));
   } else {
     static bool configured = false;
     if (!configured) {
@@ -469,7 +500,7 @@ static int t5_launch(const void* x, int ldx, const void* w, void* y, int ldy, in
     }
     cfg.dynamicSmemBytes = dl::T5<128>::SMEM;
     return static_cast<int>(cudaLaunchKernelEx(&cfg, dl::gemm_tcgen05_kernel<128, P>, map_x, map_w, y, ldy, M, N, K, mode,
-                                               out_scale, gate_rows, tiles_n, static_cast<int>(tiles), status, rope));
+                                               out_scale, gate_rows, tiles_n, static_cast<int>(tiles), group_m, status, rope));
   }
 }
 

@@ -652,7 +652,8 @@ _tcgen05_status = {}
 _pairs: Optional[bool] = None      # whether the variant with pairs of blocks sharing W tiles can be used
 
 
-PAIRS_MIN_WAVES = 4     # rounds of 128 x 256 tiles over the SMs from which sharing W tiles between two blocks pays (measured on B200)
+# rounds of 128 x 256 tiles over the SMs from which sharing W tiles between two blocks pays (measured on B200)
+PAIRS_MIN_WAVES = float(os.environ.get("DYNALM_GEMM_PAIRS_MIN_WAVES", "4"))
 
 
 def tcgen05_pairs(rows: int, features: int) -> bool:
