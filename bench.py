@@ -12,7 +12,8 @@ weight read once plus the cache of the live requests), and as `points` decode at
 at batch 1, 8 and 64 with about 8,000 tokens of context each (as many as the 8,192-token benchmark context
 leaves room for while the measurement grows them), and a prefill of 8,192 tokens, each with its fraction
 of the roofline; last, the continuous-batching workloads of the 3B and 8B shapes (tokens/s over the whole run,
-median time to the first token, decode-only step) and a 32,768-token prompt brought in portions of 512. `--workload serve3b | serve8b` runs one of those alone and
+median time to the first token, decode-only step), a 32,768-token prompt brought in portions of 512, and the
+end-to-end decode again with requests that draw their tokens (temperature, top-k, top-p, a penalty). `--workload serve3b | serve8b` runs one of those alone and
 prints its full record. Prints one JSON line.
 """
 
@@ -531,6 +532,38 @@ def main():
         eng.scheduler.cancel(s_.id)
     while not eng.scheduler.idle:
         eng.scheduler.step()
+
+    # ---- the same end to end with requests that draw their tokens: through the sampling kernels, ids out ---------
+    if not args.no_points:
+        from dynalm_b200 import SamplingParams
+        drawn = {"temperature": dict(temperature=0.8), "top_k40": dict(temperature=0.8, top_k=40),
+                 "top_p0.9": dict(temperature=0.8, top_p=0.9),
+                 "top_k40_top_p0.9_penalty": dict(temperature=0.8, top_k=40, top_p=0.9, repetition_penalty=1.1)}
+        for name, how in drawn.items():
+            try:
+                for r in range(B):
+                    eng.scheduler.submit(Request([int(t) for t in rng.randint(0, vocab, HELD)], max_new_tokens=span - 8,
+                                                 sampling=SamplingParams(seed=r, **how)))
+                while not eng.scheduler.idle and (any(s.status != "decode" or s.pending != 1 for s in eng.scheduler.running)
+                                                  or eng.scheduler.waiting or eng.scheduler.incoming
+                                                  or not eng.scheduler.running):
+                    eng.scheduler.step()
+                for _ in range(PRIME + W):
+                    eng.scheduler.step()
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                n_tok = 0
+                for _ in range(K):
+                    n_tok += sum(1 for ev in eng.scheduler.step() if ev.token is not None)
+                torch.cuda.synchronize()
+                points[f"e2e_b{B}_{name}"] = round(n_tok / (time.perf_counter() - t0), 1)
+            except Exception as e:           # a point that fails does not take the line with it
+                points[f"e2e_b{B}_{name}_error"] = f"{type(e).__name__}: {e}"[:200]
+            for s_ in list(eng.scheduler.running):
+                eng.scheduler.cancel(s_.id)
+            while not eng.scheduler.idle:
+                eng.scheduler.step()
+        points["rows_sampled_on_the_host"] = eng.executor.host_sampled
 
     # ---- the serving workloads of the larger shapes, as points (each builds its own engine) ---------------------
     if not (args.no_points or args.no_serve or args.layers != FULL_LAYERS):

@@ -422,7 +422,8 @@ sample_filtered_kernel(const float* __restrict__ logits, int ld, int vocab, cons
   }
   hi = block_max(hi, redf);
   lo = -block_max(-lo, redf);
-  if (!(hi > -INFINITY) || !(hi < INFINITY)) {       // nothing finite to choose from: the host decides
+  if (!(hi > -INFINITY) || !(hi < INFINITY)) {
+    // nothing finite to choose from, or an infinite logit: no distribution to draw from; the row says so
     if (t == 0) out[out_at] = -1;
     return;
   }
@@ -499,21 +500,66 @@ sample_filtered_kernel(const float* __restrict__ logits, int ld, int vocab, cons
     *ids_inside = inside;
     return rest;
   };
-  // The ids inside the chosen bins (and above them, if `with_above`) into cand, sorted by (logit descending, id
-  // ascending); the number of them, or -1 if they do not fit.
-  auto gather_sorted = [&](bool with_above) -> int {
-    if (t == 0) n_cand = 0;
-    __syncthreads();
+  // Thread t's own stretch of ids, for what has to go by the order of the ids.
+  const int per = (vocab + SAMPLE_CAP - 1) / SAMPLE_CAP;
+  const int own_b = min(vocab, t * per), own_e = min(vocab, own_b + per);
+  // Whether the ids inside the chosen bins all have one logit (after three levels a bin is narrower than the
+  // step between two floats, unless the row's range is absurd); *value = that logit.
+  auto one_value = [&](float* value) -> bool {
+    float most = -INFINITY, least = INFINITY;
     for (int i = t; i < vocab; i += SAMPLE_CAP) {
       const float l = row[i];
-      if (!counted(l)) continue;
-      const int side = bins.side(l);
-      if (side < 0 || (side > 0 && !with_above)) continue;
+      if (counted(l) && bins.side(l) == 0) { most = fmaxf(most, l); least = fminf(least, l); }
+    }
+    most = block_max(most, redf);
+    least = -block_max(-least, redf);
+    *value = most;
+    return most == least;
+  };
+  // The id of the j-th (from 0) of the ids inside the chosen bins, in the order of the ids; -1 if there are fewer.
+  auto nth_inside = [&](unsigned long long j) -> int {
+    unsigned long long mine = 0;
+    for (int i = own_b; i < own_e; ++i) mine += counted(row[i]) && bins.side(row[i]) == 0;
+    const unsigned long long incl = block_scan_u64(mine, red_u);
+    if (t == 0) found_id = -1;
+    __syncthreads();
+    if (incl - mine <= j && j < incl) {
+      unsigned long long seen = incl - mine;
+      for (int i = own_b; i < own_e; ++i) {
+        if (counted(row[i]) && bins.side(row[i]) == 0 && seen++ == j) { found_id = i; break; }
+      }
+    }
+    __syncthreads();
+    return found_id;
+  };
+  // The ids inside the chosen bins (and above them, if `with_above`) into cand, sorted by (logit descending, id
+  // ascending); the number of them, or -1 if they do not fit. inside_limit >= 0: of those inside only the first
+  // inside_limit in the order of the ids (they have one logit, so these come first in the order of the candidates).
+  auto gather_sorted = [&](bool with_above, long long inside_limit) -> int {
+    if (t == 0) n_cand = 0;
+    __syncthreads();
+    auto put = [&](int i, float l) {
       const int at = atomicAdd(&n_cand, 1);
       if (at < SAMPLE_CAP) {
         const unsigned int bits = __float_as_uint(l);
         const unsigned int rising = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);     // grows with the logit
         cand[at] = (static_cast<unsigned long long>(~rising) << 32) | static_cast<unsigned int>(i);
+      }
+    };
+    for (int i = t; i < vocab; i += SAMPLE_CAP) {
+      const float l = row[i];
+      if (!counted(l)) continue;
+      const int side = bins.side(l);
+      if (side < 0 || (side > 0 && !with_above) || (side == 0 && inside_limit >= 0)) continue;
+      put(i, l);
+    }
+    if (inside_limit >= 0) {
+      unsigned long long mine = 0;
+      for (int i = own_b; i < own_e; ++i) mine += counted(row[i]) && bins.side(row[i]) == 0;
+      unsigned long long rank = block_scan_u64(mine, red_u) - mine;
+      for (int i = own_b; i < own_e; ++i) {
+        const float l = row[i];
+        if (counted(l) && bins.side(l) == 0 && rank++ < static_cast<unsigned long long>(inside_limit)) put(i, l);
       }
     }
     __syncthreads();
@@ -547,7 +593,21 @@ sample_filtered_kernel(const float* __restrict__ logits, int ld, int vocab, cons
     auto locate = [&](unsigned long long x) -> bool {
       int ids_above, ids_inside;
       const unsigned long long rest = narrow(x, false, false, &ids_above, &ids_inside);
-      const int n = gather_sorted(false);
+      if (ids_inside > SAMPLE_CAP) {
+        // more ids at the place than can be sorted: they have one logit, so one mass, and their order is that of
+        // the ids
+        float value;
+        if (!one_value(&value)) return false;
+        const unsigned long long w = mass(value);
+        if (w == 0) return false;
+        const unsigned long long j = (rest + w - 1) / w - 1;
+        const int id = nth_inside(j);
+        if (id < 0) return false;
+        if (t == 0) found_cum = (x - rest) + (j + 1) * w;
+        __syncthreads();
+        return true;
+      }
+      const int n = gather_sorted(false, -1);
       if (n < 0) return false;
       const int id = static_cast<int>(cand[t] & 0xffffffffull);
       const unsigned long long w = t < n ? mass(row[id]) : 0ull;
@@ -582,8 +642,14 @@ sample_filtered_kernel(const float* __restrict__ logits, int ld, int vocab, cons
 
   // ---- top-k, with or without top-p ----
   int ids_above, ids_inside;
-  narrow(static_cast<unsigned long long>(k), true, true, &ids_above, &ids_inside);
-  const int n = gather_sorted(true);
+  const unsigned long long inside_wanted = narrow(static_cast<unsigned long long>(k), true, true, &ids_above, &ids_inside);
+  long long inside_limit = -1;
+  if (ids_above + ids_inside > SAMPLE_CAP && k <= SAMPLE_CAP) {
+    // more ids with the k-th logit than can be kept: of those (one logit) the first in the order of the ids
+    float value;
+    if (one_value(&value)) inside_limit = static_cast<long long>(inside_wanted);
+  }
+  const int n = gather_sorted(true, inside_limit);
   if (n < 0) {
     if (t == 0) out[out_at] = -1;
     return;
@@ -624,7 +690,11 @@ sample_filtered_kernel(const float* __restrict__ logits, int ld, int vocab, cons
 __global__ void feedback_tokens_kernel(int* __restrict__ token_ids, const int* __restrict__ chosen,
                                        const int* __restrict__ src, int n) {
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
-  if (r < n && src[r] >= 0) token_ids[r] = chosen[ck_row(src[r])];   // checked against the length of `chosen`
+  if (r < n && src[r] >= 0) {
+    const int id = chosen[ck_row(src[r])];   // checked against the length of `chosen`
+    token_ids[r] = id < 0 ? 0 : id;          // a row the sampling kernel could not decide (-1): the host finds it when
+                                             // it reads the ids and fails the request; the step in flight stays in bounds
+  }
 }
 
 }  // namespace dl

@@ -189,7 +189,13 @@ class GpuExecutor:
         launched.event.synchronize()
         ids = self._ids_host[launched.slot].numpy()
         self._check_status(ids)
-        return {req: int(ids[place]) for req, place in launched.places.items()}
+        out = {req: int(ids[place]) for req, place in launched.places.items()}
+        undecided = [req for req, token in out.items() if token < 0]
+        if undecided:
+            # the filtered kernel gives up on a row without a finite largest logit, or whose range is so wide that
+            # bins of it still hold different logits; the row's logits are gone by now (the next step is in flight)
+            raise EngineError(f"request(s) {undecided}: the logits could not be sampled from (not finite, or of absurd range)")
+        return out
 
     def _check_status(self, ids) -> None:
         """`ids`: the host copy of a step's chosen ids, whose last element is the status word as that step left it.
@@ -204,8 +210,9 @@ class GpuExecutor:
 
     # ---- any batch, synchronously ------------------------------------------------------------------------
     def run(self, batch: List[BatchItem]) -> Dict[Hashable, int]:
-        if self.can_launch(batch):
+        if self.can_launch(batch) and not any(b.seq.sampler.wants_filtered and not b.seq.sampler.params.greedy for b in batch):
             return self.collect(self.launch(batch))
+        # (with the logits still at hand a row that the filtered kernel leaves undecided can be finished on the host)
         entries = [StepEntry(b.seq.id, b.tokens, [len(b.tokens) - 1] if b.sample else []) for b in batch]
         want = [b for b in batch if b.sample]
         logits = self.step_fn.step(entries, reserve=False, choose=self._choose(want))

@@ -36,12 +36,15 @@ class Sampler:
         self.params = params
         self.rng = Xoshiro256(params.seed)
 
+    DEVICE_TOP_K = 1024      # the candidates the filtered kernel keeps (SAMPLE_CAP in csrc/sampling.cu)
+
     @property
     def on_device(self) -> bool:
-        """Whether the device can choose this request's token with nothing from the host but a uniform number:
-        greedy, temperature, min-p. Penalties need the context, top-k and top-p may need the host to finish."""
+        """Whether the device can choose this request's token with nothing from the host but a uniform number, so
+        that the request can be decoded a step ahead: greedy, temperature, min-p, top-p, top-k up to DEVICE_TOP_K.
+        Penalties need the context; a larger top-k the host, to finish."""
         p = self.params
-        return not p.has_penalties and (p.greedy or not self.wants_filtered)
+        return not p.has_penalties and (p.greedy or p.top_k <= self.DEVICE_TOP_K)
 
     @property
     def wants_filtered(self) -> bool:
