@@ -1,12 +1,12 @@
 """Per-request samplers.
 
 Every request is sampled on the device (csrc/sampling.cu) from the logits rows of the step, and only token ids come
-back: greedy, temperature and min-p by kernels that need nothing from the host but a uniform number (such requests
-can be decoded a step ahead); penalties by a kernel that gets the counts of the recent tokens from the host; top-k and
-top-p by a kernel that narrows the vocabulary down to the places the reference's pipeline, penalties -> top-k ->
-temperature -> min-p -> top-p -> draw (dynalm/src/sampling/sampler.cpp:96-220), turns on. Where a row does not fit
-that kernel (top-k above 1,024, more than 1,024 equal logits at such a place) it comes to the host, which runs the
-same pipeline here, as the reference does for every request.
+back: greedy, temperature, min-p, top-p and top-k up to 1,024 by kernels that need nothing from the host but a uniform
+number (such requests can be decoded a step ahead); penalties by a kernel that gets the counts of the recent tokens
+from the host. Top-k and top-p follow the reference's pipeline, penalties -> top-k -> temperature -> min-p -> top-p
+-> draw (dynalm/src/sampling/sampler.cpp:96-220), by narrowing the vocabulary down to the places that pipeline turns
+on. A row with top-k above 1,024 comes to the host, which runs the same pipeline here, as the reference does for
+every request.
 """
 
 from __future__ import annotations
