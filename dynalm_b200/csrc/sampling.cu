@@ -269,20 +269,43 @@ sample_temperature_kernel(const float* __restrict__ logits, int ld, int vocab, i
 // sample_filtered_kernel); a row that does not fit gives -1 and is done by the host from its logits.
 
 // Repetition, frequency and presence penalties (sampler.cpp:96-116): triple j = (selection, token id, count of the
-// id in the request's recent context), ids unique within a selection; params[selection] = (repetition, frequency,
-// presence). float32 arithmetic in the order of the host's, no fused multiply-add.
-__global__ void apply_penalties_kernel(float* __restrict__ logits, int ld, int vocab, const int* __restrict__ rows,
-                                       const int* __restrict__ triples, int n_triples,
-                                       const float* __restrict__ params) {
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= n_triples) return;
-  const int sel = triples[3 * j], id = triples[3 * j + 1], count = triples[3 * j + 2];
-  if (id < 0 || id >= vocab) return;
-  float* at = logits + static_cast<size_t>(ck_row(rows[sel])) * ld + id;
-  const float rep = params[3 * sel], freq = params[3 * sel + 1], pres = params[3 * sel + 2];
+// id in the request's recent context), ids unique within a selection and the triples of a selection next to one
+// another (first[sel] .. first[sel + 1]); params[selection] = (repetition, frequency, presence). float32 arithmetic
+// in the order of the host's, no fused multiply-add.
+//
+// A request that is decoded a step ahead has one token the host has not seen yet: the one the step in flight chose,
+// chosen[pending[sel]] (pending[sel] < 0: none). It counts as the newest token of the context (the host leaves room
+// for it in the window): a triple with its id counts one more, and if no triple has it, it is penalised as an id
+// seen once (thread n_triples + sel looks for it among the selection's triples).
+__device__ __forceinline__ void penalise(float* at, float rep, float freq, float pres, int count) {
   float l = *at;
   if (rep != 1.0f) l = l > 0.0f ? __fdiv_rn(l, rep) : __fmul_rn(l, rep);
   *at = __fsub_rn(l, __fadd_rn(__fmul_rn(static_cast<float>(count), freq), pres));
+}
+
+__global__ void apply_penalties_kernel(float* __restrict__ logits, int ld, int vocab, const int* __restrict__ rows,
+                                       const int* __restrict__ triples, int n_triples, const float* __restrict__ params,
+                                       const int* __restrict__ first, int n_sel, const int* __restrict__ chosen,
+                                       const int* __restrict__ pending) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= n_triples + (pending != nullptr ? n_sel : 0)) return;
+  if (j < n_triples) {
+    const int sel = triples[3 * j], id = triples[3 * j + 1];
+    int count = triples[3 * j + 2];
+    if (id < 0 || id >= vocab) return;
+    if (pending != nullptr && pending[sel] >= 0 && chosen[pending[sel]] == id) ++count;
+    penalise(logits + static_cast<size_t>(ck_row(rows[sel])) * ld + id, params[3 * sel], params[3 * sel + 1],
+             params[3 * sel + 2], count);
+    return;
+  }
+  const int sel = j - n_triples;
+  if (pending[sel] < 0) return;
+  const int id = chosen[pending[sel]];
+  if (id < 0 || id >= vocab) return;
+  for (int k = first[sel]; k < first[sel + 1]; ++k)
+    if (triples[3 * k + 1] == id) return;                // counted there
+  penalise(logits + static_cast<size_t>(ck_row(rows[sel])) * ld + id, params[3 * sel], params[3 * sel + 1],
+           params[3 * sel + 2], 1);
 }
 
 constexpr int SAMPLE_CAP = 1024;          // candidates a row may keep (= threads of its block)
@@ -734,13 +757,18 @@ DL_EXPORT int dl_argmax_of_parts(const float* pv, const int* pi, int rows, int p
                               status_src, status_dst);
 }
 
-// rows: the logits rows of the n_sel selections; triples: int32 [n_triples][3] = (selection, token id, count);
-// params: fp32 [n_sel][3] = (repetition, frequency, presence). In place.
+// rows: the logits rows of the n_sel selections; triples: int32 [n_triples][3] = (selection, token id, count), those
+// of a selection next to one another, first: int32 [n_sel + 1] where each selection's begin; params: fp32 [n_sel][3] =
+// (repetition, frequency, presence). chosen, pending (both or neither): pending[sel] >= 0 names the place in `chosen`
+// of a token of that selection's context that only the device knows yet. In place.
 DL_EXPORT int dl_apply_penalties(float* logits, int ld, int vocab, const int* rows, const int* triples, int n_triples,
-                                 const float* params, cudaStream_t stream) {
-  if (n_triples <= 0) return 0;
-  if (vocab <= 0) return DL_ERR_UNSUPPORTED;
-  dl::apply_penalties_kernel<<<(n_triples + 127) / 128, 128, 0, stream>>>(logits, ld, vocab, rows, triples, n_triples, params);
+                                 const float* params, const int* first, int n_sel, const int* chosen,
+                                 const int* pending, cudaStream_t stream) {
+  if (n_sel <= 0 || (n_triples <= 0 && pending == nullptr)) return 0;
+  if (vocab <= 0 || n_triples < 0 || first == nullptr || (pending != nullptr && chosen == nullptr)) return DL_ERR_UNSUPPORTED;
+  const int threads = n_triples + (pending != nullptr ? n_sel : 0);
+  dl::apply_penalties_kernel<<<(threads + 127) / 128, 128, 0, stream>>>(logits, ld, vocab, rows, triples, n_triples, params,
+                                                                        first, n_sel, chosen, pending);
   return dl::launch_status();
 }
 

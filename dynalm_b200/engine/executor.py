@@ -54,9 +54,11 @@ class GpuExecutor:
         self._u = torch.zeros(n, dtype=torch.float64, device=dev)
         # what penalties and filters need from the host, two pinned copies of each as above. Integers: the rows with
         # penalties [n] | the rows of the filtered kernel [n] | their top-k [n] | the penalties' (repetition,
-        # frequency, presence) as float32 bits [3n] | triples (selection, id, count) [3 x PENALTY_TRIPLES].
+        # frequency, presence) as float32 bits [3n] | where each penalised row's triples begin [n + 1] | the place among
+        # the ids of the token a step in flight chose for it, or -1 [n] | triples (selection, id, count)
+        # [3 x PENALTY_TRIPLES].
         # Doubles: the filtered kernel's (temperature, min-p offset, top-p, uniform) [4n] | the walk's min-p offsets [n].
-        self._stage_i = torch.zeros(6 * n + 3 * self.PENALTY_TRIPLES, dtype=torch.int32, device=dev)
+        self._stage_i = torch.zeros(8 * n + 1 + 3 * self.PENALTY_TRIPLES, dtype=torch.int32, device=dev)
         self._stage_d = torch.zeros(5 * n, dtype=torch.float64, device=dev)
         self._stage_i_host = [torch.zeros(self._stage_i.numel(), dtype=torch.int32).pin_memory() for _ in range(2)]
         self._stage_d_host = [torch.zeros(self._stage_d.numel(), dtype=torch.float64).pin_memory() for _ in range(2)]
@@ -79,16 +81,18 @@ class GpuExecutor:
 
     def _choose(self, want: List[BatchItem]):
         """What to hand the step as `choose` when every wanted row is decided by its largest logit on the device."""
-        if want and all(b.seq.sampler.on_device and b.seq.sampler.params.greedy for b in want):
+        if want and all(b.seq.sampler.params.greedy and not b.seq.sampler.params.has_penalties for b in want):
             return (self._ids[:len(want)], self._ids[2 * self._n:])
         return None
 
-    def _sample_on_device(self, logits: Optional[torch.Tensor], want: List[BatchItem], slot: int) -> Dict[int, float]:
+    def _sample_on_device(self, logits: Optional[torch.Tensor], want: List[BatchItem], slot: int,
+                          after: Optional[Launched] = None) -> Dict[int, float]:
         """Choose a token for every wanted row on the device and start the copy of the ids to the host: the largest
         logit for every row (place i), and for the rows that draw, a draw (place n + i): a walk down the ids for
         temperature and min-p, the filtered kernel for top-k and top-p, which may leave -1 for the host to finish.
-        Rows with penalties have them applied to their logits first. Returns row -> the uniform number it drew with,
-        for the rows of the filtered kernel."""
+        Rows with penalties have them applied to their logits first; with `after`, the token that launch chose for
+        the request is in no context yet, and the penalties kernel counts it from the ids on the device. Returns
+        row -> the uniform number it drew with, for the rows of the filtered kernel."""
         n = len(want)
         if logits is None:
             # the step picked the most likely tokens itself (and brought the status word along)
@@ -108,24 +112,29 @@ class GpuExecutor:
         ih, dh = self._stage_i_host[slot], self._stage_d_host[slot]
         ints, dbls = ih.numpy(), dh.numpy()
         n_triples = 0
+        T0 = 8 * N + 1                       # where the triples begin
         if penalised:
             # the context the penalties see: everything up to and including the tokens just computed
             found = []
             for j, i in enumerate(penalised):
                 p = samplers[i].params
-                ids, counts = samplers[i].penalty_counts(want[i].seq.tokens, self.vocab)
+                unseen = 1 if after is not None and want[i].seq.id in after.places else 0
+                ids, counts = samplers[i].penalty_counts(want[i].seq.tokens, self.vocab, unseen=unseen)
                 ints[j] = i
                 ints[3 * N + 3 * j:3 * N + 3 * j + 3] = np.array(
                     [p.repetition_penalty, p.frequency_penalty, p.presence_penalty], dtype=np.float32).view(np.int32)
+                ints[6 * N + j] = n_triples
+                ints[7 * N + 1 + j] = after.places[want[i].seq.id] if unseen and p.penalty_last_n != 0 else -1
                 if ids.size:
                     found.append(np.stack([np.full(ids.size, j, dtype=np.int64), ids, counts], axis=1))
+                    n_triples += ids.size
+            ints[6 * N + len(penalised)] = n_triples
             if found:
                 flat = np.concatenate(found).astype(np.int32).ravel()
-                n_triples = flat.size // 3
-                if 6 * N + flat.size > ints.size:
+                if T0 + flat.size > ints.size:
                     raise EngineError(f"penalties over {n_triples} distinct recent tokens in one step; the executor "
-                                      f"has room for {(ints.size - 6 * N) // 3}")
-                ints[6 * N:6 * N + flat.size] = flat
+                                      f"has room for {(ints.size - T0) // 3}")
+                ints[T0:T0 + flat.size] = flat
         for j, i in enumerate(filtered):
             p = samplers[i].params
             drawn[i] = samplers[i].next_uniform()
@@ -138,16 +147,20 @@ class GpuExecutor:
             for i in walk:
                 dbls[4 * N + i] = samplers[i].cut_offset
         if penalised or filtered:
-            used = 6 * N + 3 * n_triples
+            used = T0 + 3 * n_triples
             self._stage_i[:used].copy_(ih[:used], non_blocking=True)
             self.h2d_bytes += 4 * used
         if filtered or with_cut:
             used = 4 * N + (n if with_cut else 0)
             self._stage_d[:used].copy_(dh[:used], non_blocking=True)
             self.h2d_bytes += 8 * used
-        if n_triples:
-            ops.apply_penalties(logits, self._stage_i[:len(penalised)], self._stage_i[6 * N:6 * N + 3 * n_triples], n_triples,
-                                self._stage_i[3 * N:3 * N + 3 * len(penalised)].view(torch.float32))
+        if penalised:
+            ahead = after is not None
+            ops.apply_penalties(logits, self._stage_i[:len(penalised)], self._stage_i[T0:T0 + 3 * n_triples], n_triples,
+                                self._stage_i[3 * N:3 * N + 3 * len(penalised)].view(torch.float32),
+                                self._stage_i[6 * N:6 * N + len(penalised) + 1],
+                                chosen=self._ids if ahead else None,
+                                pending=self._stage_i[7 * N + 1:7 * N + 1 + len(penalised)] if ahead else None)
         ops.argmax(logits, self._ids[:n], status_to=self._ids[2 * self._n:])
         if walk:
             th, uh = self._temp_host[slot], self._u_host[slot]
@@ -179,7 +192,7 @@ class GpuExecutor:
         self.h2d_bytes += self.step_fn.batcher.last_upload_bytes
         slot = self._turn
         self._turn ^= 1
-        self._sample_on_device(logits, batch, slot)
+        self._sample_on_device(logits, batch, slot, after=after)
         ev = torch.cuda.Event()
         ev.record()
         places = {b.seq.id: (i if b.seq.sampler.params.greedy else self._n + i) for i, b in enumerate(batch)}

@@ -58,7 +58,7 @@ _SIGNATURES = {
     "sampling": {
         "dl_argmax": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
         "dl_sample_temperature": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
-        "dl_apply_penalties": [_P, _I, _I, _P, _P, _I, _P, _P],
+        "dl_apply_penalties": [_P, _I, _I, _P, _P, _I, _P, _P, _I, _P, _P, _P],
         "dl_sample_filtered": [_P, _I, _I, _P, _I, _P, _P, _P, _P],
         "dl_argmax_of_parts": [_P, _P, _I, _I, _P, _P, _P, _P],
         "dl_feedback_tokens": [_P, _P, _P, _I, _P],
@@ -996,20 +996,30 @@ def sample_temperature(logits: torch.Tensor, temperature: torch.Tensor, uniform:
 
 
 def apply_penalties(logits: torch.Tensor, rows: torch.Tensor, triples: torch.Tensor, n_triples: int,
-                    params: torch.Tensor) -> None:
+                    params: torch.Tensor, first: torch.Tensor, chosen: Optional[torch.Tensor] = None,
+                    pending: Optional[torch.Tensor] = None) -> None:
     """Repetition, frequency and presence penalties, in place: triple j = (selection, token id, count) changes
     logits[rows[selection], id] with params[selection] = (repetition, frequency, presence). The ids of one selection
-    are distinct. rows int32, triples int32 [>= n_triples, 3], params float32 [selections, 3]."""
-    _cuda(logits, rows, triples, params)
+    are distinct and its triples lie next to one another, from first[selection] to first[selection + 1]. rows int32
+    [selections], triples int32 [>= n_triples, 3], params float32 [selections, 3], first int32 [selections + 1].
+    chosen and pending (int32, both or neither): pending[selection] >= 0 is the place in `chosen` of one more token
+    of that selection's context, which only the device knows yet; it counts as seen once more."""
+    _cuda(logits, rows, triples, params, first, chosen, pending)
     _rows_contiguous(logits, "logits")
+    n_sel = rows.numel()
     if (logits.dtype != torch.float32 or rows.dtype != torch.int32 or triples.dtype != torch.int32
-            or params.dtype != torch.float32 or triples.numel() < 3 * n_triples or not triples.is_contiguous()
-            or not params.is_contiguous()):
-        raise InvalidArgument("apply_penalties: logits/params float32, rows/triples int32, triples [n, 3]")
+            or params.dtype != torch.float32 or first.dtype != torch.int32 or triples.numel() < 3 * n_triples
+            or not triples.is_contiguous() or not params.is_contiguous() or params.numel() < 3 * n_sel
+            or first.numel() < n_sel + 1):
+        raise InvalidArgument("apply_penalties: logits/params float32, rows/triples/first int32, triples [n, 3]")
+    if (chosen is None) != (pending is None) or (pending is not None and (
+            pending.dtype != torch.int32 or chosen.dtype != torch.int32 or pending.numel() < n_sel)):
+        raise InvalidArgument("apply_penalties: chosen and pending int32, together, pending one per selection")
     if CHECKED:
         check_limits("sampling", rows=logits.shape[0])
     _check(_fn("sampling", "dl_apply_penalties")(_p(logits), logits.stride(0), logits.shape[1], _p(rows), _p(triples),
-                                                  int(n_triples), _p(params), _stream()), "apply_penalties")
+                                                  int(n_triples), _p(params), _p(first), n_sel, _p(chosen), _p(pending),
+                                                  _stream()), "apply_penalties")
 
 
 SAMPLE_FILTERED_HOST = -1      # what sample_filtered leaves for a row that the host has to finish

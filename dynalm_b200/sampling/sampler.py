@@ -2,8 +2,8 @@
 
 Every request is sampled on the device (csrc/sampling.cu) from the logits rows of the step, and only token ids come
 back: greedy, temperature, min-p, top-p and top-k up to 1,024 by kernels that need nothing from the host but a uniform
-number (such requests can be decoded a step ahead); penalties by a kernel that gets the counts of the recent tokens
-from the host. Top-k and top-p follow the reference's pipeline, penalties -> top-k -> temperature -> min-p -> top-p
+number; penalties by a kernel that gets the counts of the recent tokens from the host (and reads the token of a
+step still in flight from the device). All of these can be decoded a step ahead. Top-k and top-p follow the reference's pipeline, penalties -> top-k -> temperature -> min-p -> top-p
 -> draw (dynalm/src/sampling/sampler.cpp:96-220), by narrowing the vocabulary down to the places that pipeline turns
 on. A row with top-k above 1,024 comes to the host, which runs the same pipeline here, as the reference does for
 every request.
@@ -40,11 +40,12 @@ class Sampler:
 
     @property
     def on_device(self) -> bool:
-        """Whether the device can choose this request's token with nothing from the host but a uniform number, so
-        that the request can be decoded a step ahead: greedy, temperature, min-p, top-p, top-k up to DEVICE_TOP_K.
-        Penalties need the context; a larger top-k the host, to finish."""
+        """Whether the device can choose this request's token without the host's seeing the logits, so that the
+        request can be decoded a step ahead: greedy, temperature, min-p, top-p, top-k up to DEVICE_TOP_K, and the
+        penalties (the host counts the tokens it knows, the device adds the one in flight). A larger top-k needs
+        the host to finish."""
         p = self.params
-        return not p.has_penalties and (p.greedy or p.top_k <= self.DEVICE_TOP_K)
+        return p.greedy or p.top_k <= self.DEVICE_TOP_K
 
     @property
     def wants_filtered(self) -> bool:
@@ -60,15 +61,18 @@ class Sampler:
     def next_uniform(self) -> float:
         return self.rng.uniform()
 
-    def penalty_counts(self, context: Sequence[int], vocab: int):
+    def penalty_counts(self, context: Sequence[int], vocab: int, unseen: int = 0):
         """The distinct ids among the last `penalty_last_n` tokens of the context, and how often each occurs
-        (what the penalties act on, sampler.cpp:96-116); two empty arrays where there is nothing to penalise."""
+        (what the penalties act on, sampler.cpp:96-116); two empty arrays where there is nothing to penalise.
+        `unseen`: tokens that follow `context` and are not known here yet (a step in flight chose them); they take
+        their places in the window, so that many fewer of `context` are counted."""
         p = self.params
         none = np.zeros(0, dtype=np.int64)
-        if not p.has_penalties or len(context) == 0:
+        if not p.has_penalties or len(context) + unseen == 0:
             return none, none
-        n = len(context) if p.penalty_last_n < 0 else min(len(context), p.penalty_last_n)
-        if n == 0:
+        n = len(context) + unseen if p.penalty_last_n < 0 else min(len(context) + unseen, p.penalty_last_n)
+        n -= unseen
+        if n <= 0:
             return none, none
         ids, counts = np.unique(np.asarray(context[len(context) - n:], dtype=np.int64), return_counts=True)
         ok = (ids >= 0) & (ids < vocab)

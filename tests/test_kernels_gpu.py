@@ -298,21 +298,52 @@ def test_apply_penalties_matches_the_host(ops):
     params = {1: SamplingParams(temperature=0.7, repetition_penalty=1.3, frequency_penalty=0.2, presence_penalty=-0.4),
               4: SamplingParams(temperature=0.7, repetition_penalty=0.8, penalty_last_n=-1),
               5: SamplingParams(temperature=0.7, presence_penalty=1.0)}
+    def triples_of(contexts, unseen):
+        rows, triples, pp, first = [], [], [], [0]
+        for j, r in enumerate(sorted(contexts)):
+            s = Sampler(params[r])
+            ids, counts = s.penalty_counts(contexts[r], vocab, unseen=unseen.get(r, 0))
+            rows.append(r)
+            pp.append((params[r].repetition_penalty, params[r].frequency_penalty, params[r].presence_penalty))
+            triples += [(j, int(i), int(c)) for i, c in zip(ids, counts)]
+            first.append(len(triples))
+        return (torch.tensor(rows, dtype=torch.int32, device=DEV),
+                torch.tensor(triples or [(0, 0, 0)], dtype=torch.int32, device=DEV), len(triples),
+                torch.tensor(pp, dtype=torch.float32, device=DEV), torch.tensor(first, dtype=torch.int32, device=DEV))
+
     want = logits.clone().numpy()
-    rows, triples, pp = [], [], []
-    for j, r in enumerate(sorted(contexts)):
-        s = Sampler(params[r])
-        s.apply_penalties(want[r], contexts[r])
-        ids, counts = s.penalty_counts(contexts[r], vocab)
-        rows.append(r)
-        pp.append((params[r].repetition_penalty, params[r].frequency_penalty, params[r].presence_penalty))
-        triples += [(j, int(i), int(c)) for i, c in zip(ids, counts)]
+    for r in contexts:
+        Sampler(params[r]).apply_penalties(want[r], contexts[r])
     d = logits.to(DEV)
-    ops.apply_penalties(d, torch.tensor(rows, dtype=torch.int32, device=DEV),
-                        torch.tensor(triples, dtype=torch.int32, device=DEV), len(triples),
-                        torch.tensor(pp, dtype=torch.float32, device=DEV))
+    rows, triples, n, pp, first = triples_of(contexts, {})
+    ops.apply_penalties(d, rows, triples, n, pp, first)
     assert np.array_equal(d.cpu().numpy(), want)
     assert not np.array_equal(want[1], logits[1].numpy()) and np.array_equal(want[0], logits[0].numpy())
+    # The last token of each context known to the device only (a step in flight chose it): a token that is in
+    # the context already (7 in row 1), one that is new to it (41 leaves row 4's list when it is taken away ... it
+    # does not: it occurs six times), and one that is the whole context (row 5).
+    contexts2 = {1: contexts[1] + [7], 4: contexts[4] + [4000], 5: [321]}
+    want2 = logits.clone().numpy()
+    for r in contexts2:
+        Sampler(params[r]).apply_penalties(want2[r], contexts2[r])
+    d2 = logits.to(DEV)
+    rows, triples, n, pp, first = triples_of({r: c[:-1] for r, c in contexts2.items()}, {r: 1 for r in contexts2})
+    chosen = torch.tensor([0, 4000, 7, 0, 321], dtype=torch.int32, device=DEV)
+    pending = torch.tensor([2, 1, 4], dtype=torch.int32, device=DEV)
+    ops.apply_penalties(d2, rows, triples, n, pp, first, chosen=chosen, pending=pending)
+    assert np.array_equal(d2.cpu().numpy(), want2)
+    # with a window, the token in flight takes the place of the oldest one
+    windowed = SamplingParams(temperature=0.7, repetition_penalty=1.2, frequency_penalty=0.3, penalty_last_n=4)
+    params[2] = windowed
+    ctx = [9, 8, 7, 6, 5]
+    want3 = logits.clone().numpy()
+    Sampler(windowed).apply_penalties(want3[2], ctx)
+    d3 = logits.to(DEV)
+    rows, triples, n, pp, first = triples_of({2: ctx[:-1]}, {2: 1})
+    ops.apply_penalties(d3, rows, triples, n, pp, first, chosen=torch.tensor([5], dtype=torch.int32, device=DEV),
+                        pending=torch.tensor([0], dtype=torch.int32, device=DEV))
+    assert np.array_equal(d3.cpu().numpy(), want3)
+    assert want3[2, 9] == logits[2, 9] and want3[2, 8] != logits[2, 8]
 
 
 def _peaked_logits(rows, vocab, g, spread):

@@ -82,7 +82,11 @@ def test_penalties_arithmetic():
     assert out[3] == 3.0 and out[2] == 0.5            # outside the window / absent
     assert math.isclose(out[0], 2.0 / 2.0 - (1 * 0.5 + 0.25), rel_tol=1e-6)
     assert math.isclose(out[1], -1.0 * 2.0 - (2 * 0.5 + 0.25), rel_tol=1e-6)
-    assert not s.on_device
+    assert s.on_device            # penalties do not keep a request from being decoded a step ahead
+    assert not Sampler(SamplingParams(temperature=0.8, top_k=5000)).on_device     # a top-k that the kernel leaves to the host
+    # a token still in flight takes its place in the window: the last three are then 1, 0 and the unseen one
+    ids, counts = s.penalty_counts([3, 0, 1, 1, 0], 4, unseen=1)
+    assert ids.tolist() == [0, 1] and counts.tolist() == [1, 1]
     whole = Sampler(SamplingParams(presence_penalty=1.0, penalty_last_n=-1))
     out = logits.copy()
     whole.apply_penalties(out, [3, 0, 1, 1, 0])
