@@ -52,13 +52,20 @@ class GpuExecutor:
         self._u_host = [torch.zeros(n, dtype=torch.float64).pin_memory() for _ in range(2)]
         self._temp = torch.ones(n, dtype=torch.float32, device=dev)
         self._u = torch.zeros(n, dtype=torch.float64, device=dev)
-        # what penalties and filters need from the host, two pinned copies of each as above. Integers: the rows with
-        # penalties [n] | the rows of the filtered kernel [n] | their top-k [n] | the penalties' (repetition,
-        # frequency, presence) as float32 bits [3n] | where each penalised row's triples begin [n + 1] | the place among
-        # the ids of the token a step in flight chose for it, or -1 [n] | triples (selection, id, count)
-        # [3 x PENALTY_TRIPLES].
-        # Doubles: the filtered kernel's (temperature, min-p offset, top-p, uniform) [4n] | the walk's min-p offsets [n].
-        self._stage_i = torch.zeros(8 * n + 1 + 3 * self.PENALTY_TRIPLES, dtype=torch.int32, device=dev)
+        # What penalties and filters need from the host, two pinned copies of each as above, sent in one copy of
+        # integers and one of doubles. Integers, by name -> (first element, elements): the rows with penalties, the
+        # rows of the filtered kernel, their top-k, the penalties' (repetition, frequency, presence) as float32 bits,
+        # where each penalised row's triples begin, the place among the ids of the token a step in flight chose for
+        # it (or -1), and the triples (selection, id, count). Doubles: the filtered kernel's (temperature, min-p
+        # offset, top-p, uniform) and the walk's min-p offsets.
+        self._int_at = {}
+        at = 0
+        for name, count in (("penalised_rows", n), ("filtered_rows", n), ("top_k", n), ("penalty_params", 3 * n),
+                            ("first_triple", n + 1), ("pending", n), ("triples", 3 * self.PENALTY_TRIPLES)):
+            self._int_at[name] = (at, count)
+            at += count
+        self._dbl_at = {"filtered_params": (0, 4 * n), "cut_offsets": (4 * n, n)}
+        self._stage_i = torch.zeros(at, dtype=torch.int32, device=dev)
         self._stage_d = torch.zeros(5 * n, dtype=torch.float64, device=dev)
         self._stage_i_host = [torch.zeros(self._stage_i.numel(), dtype=torch.int32).pin_memory() for _ in range(2)]
         self._stage_d_host = [torch.zeros(self._stage_d.numel(), dtype=torch.float64).pin_memory() for _ in range(2)]
@@ -85,6 +92,44 @@ class GpuExecutor:
             return (self._ids[:len(want)], self._ids[2 * self._n:])
         return None
 
+    def _ints(self, name: str, count: Optional[int] = None, host=None):
+        """The named stretch of the staged integers (its first `count` elements): on the device, or of the host copy
+        `host` (a NumPy view)."""
+        at, most = self._int_at[name]
+        count = most if count is None else count
+        return (self._stage_i if host is None else host)[at:at + count]
+
+    def _doubles(self, name: str, count: Optional[int] = None, host=None):
+        at, most = self._dbl_at[name]
+        count = most if count is None else count
+        return (self._stage_d if host is None else host)[at:at + count]
+
+    def _stage_penalties(self, ints, want: List[BatchItem], penalised: List[int], after: Optional[Launched]) -> int:
+        """Writes what the penalties kernel needs for the rows `penalised` into the host copy `ints`; returns the
+        number of triples. The context the penalties see: everything up to and including the tokens just computed."""
+        n_triples, found = 0, []
+        params = self._ints("penalty_params", host=ints).view(np.float32)
+        first, pending = self._ints("first_triple", host=ints), self._ints("pending", host=ints)
+        for j, i in enumerate(penalised):
+            sampler, seq = want[i].seq.sampler, want[i].seq
+            p = sampler.params
+            unseen = 1 if after is not None and seq.id in after.places else 0
+            ids, counts = sampler.penalty_counts(seq.tokens, self.vocab, unseen=unseen)
+            params[3 * j:3 * j + 3] = (p.repetition_penalty, p.frequency_penalty, p.presence_penalty)
+            first[j] = n_triples
+            pending[j] = after.places[seq.id] if unseen and p.penalty_last_n != 0 else -1
+            if ids.size:
+                found.append(np.stack([np.full(ids.size, j, dtype=np.int64), ids, counts], axis=1))
+                n_triples += ids.size
+        first[len(penalised)] = n_triples
+        self._ints("penalised_rows", len(penalised), host=ints)[:] = penalised
+        if n_triples > self.PENALTY_TRIPLES:
+            raise EngineError(f"penalties over {n_triples} distinct recent tokens in one step; the executor has room "
+                              f"for {self.PENALTY_TRIPLES}")
+        if found:
+            self._ints("triples", 3 * n_triples, host=ints)[:] = np.concatenate(found).astype(np.int32).ravel()
+        return n_triples
+
     def _sample_on_device(self, logits: Optional[torch.Tensor], want: List[BatchItem], slot: int,
                           after: Optional[Launched] = None) -> Dict[int, float]:
         """Choose a token for every wanted row on the device and start the copy of the ids to the host: the largest
@@ -105,62 +150,41 @@ class GpuExecutor:
         penalised = [i for i, s in enumerate(samplers) if s.params.has_penalties]
         filtered = [i for i in range(n) if sorted_draw[i]]
         walk = [i for i, s in enumerate(samplers) if not s.params.greedy and not sorted_draw[i]]
-        drawn: Dict[int, float] = {}
-        # Everything the sampling kernels need from the host goes over in two copies from pinned memory: integers
-        # (and the penalties' float32 parameters among them, as bits) and doubles.
-        N = self._n
-        ih, dh = self._stage_i_host[slot], self._stage_d_host[slot]
-        ints, dbls = ih.numpy(), dh.numpy()
-        n_triples = 0
-        T0 = 8 * N + 1                       # where the triples begin
-        if penalised:
-            # the context the penalties see: everything up to and including the tokens just computed
-            found = []
-            for j, i in enumerate(penalised):
-                p = samplers[i].params
-                unseen = 1 if after is not None and want[i].seq.id in after.places else 0
-                ids, counts = samplers[i].penalty_counts(want[i].seq.tokens, self.vocab, unseen=unseen)
-                ints[j] = i
-                ints[3 * N + 3 * j:3 * N + 3 * j + 3] = np.array(
-                    [p.repetition_penalty, p.frequency_penalty, p.presence_penalty], dtype=np.float32).view(np.int32)
-                ints[6 * N + j] = n_triples
-                ints[7 * N + 1 + j] = after.places[want[i].seq.id] if unseen and p.penalty_last_n != 0 else -1
-                if ids.size:
-                    found.append(np.stack([np.full(ids.size, j, dtype=np.int64), ids, counts], axis=1))
-                    n_triples += ids.size
-            ints[6 * N + len(penalised)] = n_triples
-            if found:
-                flat = np.concatenate(found).astype(np.int32).ravel()
-                if T0 + flat.size > ints.size:
-                    raise EngineError(f"penalties over {n_triples} distinct recent tokens in one step; the executor "
-                                      f"has room for {(ints.size - T0) // 3}")
-                ints[T0:T0 + flat.size] = flat
-        for j, i in enumerate(filtered):
-            p = samplers[i].params
-            drawn[i] = samplers[i].next_uniform()
-            ints[N + j] = i
-            ints[2 * N + j] = p.top_k
-            dbls[4 * j:4 * j + 4] = (p.temperature, samplers[i].cut_offset, p.top_p, drawn[i])
         with_cut = any(samplers[i].params.min_p > 0.0 for i in walk)
+        drawn: Dict[int, float] = {}
+
+        # ---- what the kernels need from the host: two copies from pinned memory, integers and doubles ----
+        ints, dbls = self._stage_i_host[slot].numpy(), self._stage_d_host[slot].numpy()
+        n_triples = self._stage_penalties(ints, want, penalised, after) if penalised else 0
+        if filtered:
+            self._ints("filtered_rows", len(filtered), host=ints)[:] = filtered
+            self._ints("top_k", len(filtered), host=ints)[:] = [samplers[i].params.top_k for i in filtered]
+            params = self._doubles("filtered_params", host=dbls)
+            for j, i in enumerate(filtered):
+                p = samplers[i].params
+                drawn[i] = samplers[i].next_uniform()
+                params[4 * j:4 * j + 4] = (p.temperature, samplers[i].cut_offset, p.top_p, drawn[i])
         if with_cut:
-            dbls[4 * N:4 * N + n] = -np.inf
+            cuts = self._doubles("cut_offsets", n, host=dbls)
+            cuts[:] = -np.inf
             for i in walk:
-                dbls[4 * N + i] = samplers[i].cut_offset
+                cuts[i] = samplers[i].cut_offset
         if penalised or filtered:
-            used = T0 + 3 * n_triples
-            self._stage_i[:used].copy_(ih[:used], non_blocking=True)
+            used = self._int_at["triples"][0] + 3 * n_triples
+            self._stage_i[:used].copy_(self._stage_i_host[slot][:used], non_blocking=True)
             self.h2d_bytes += 4 * used
         if filtered or with_cut:
-            used = 4 * N + (n if with_cut else 0)
-            self._stage_d[:used].copy_(dh[:used], non_blocking=True)
+            used = self._dbl_at["cut_offsets"][0] + (n if with_cut else 0)
+            self._stage_d[:used].copy_(self._stage_d_host[slot][:used], non_blocking=True)
             self.h2d_bytes += 8 * used
+
+        # ---- the kernels, in the pipeline's order ----
         if penalised:
             ahead = after is not None
-            ops.apply_penalties(logits, self._stage_i[:len(penalised)], self._stage_i[T0:T0 + 3 * n_triples], n_triples,
-                                self._stage_i[3 * N:3 * N + 3 * len(penalised)].view(torch.float32),
-                                self._stage_i[6 * N:6 * N + len(penalised) + 1],
-                                chosen=self._ids if ahead else None,
-                                pending=self._stage_i[7 * N + 1:7 * N + 1 + len(penalised)] if ahead else None)
+            ops.apply_penalties(logits, self._ints("penalised_rows", len(penalised)), self._ints("triples", 3 * n_triples),
+                                n_triples, self._ints("penalty_params", 3 * len(penalised)).view(torch.float32),
+                                self._ints("first_triple", len(penalised) + 1), chosen=self._ids if ahead else None,
+                                pending=self._ints("pending", len(penalised)) if ahead else None)
         ops.argmax(logits, self._ids[:n], status_to=self._ids[2 * self._n:])
         if walk:
             th, uh = self._temp_host[slot], self._u_host[slot]
@@ -173,10 +197,11 @@ class GpuExecutor:
             self._u[:n].copy_(uh[:n], non_blocking=True)
             self.h2d_bytes += 12 * n
             ops.sample_temperature(logits, self._temp, self._u, self._ids[self._n:self._n + n],
-                                   cut_offset=self._stage_d[4 * N:4 * N + n] if with_cut else None)
+                                   cut_offset=self._doubles("cut_offsets", n) if with_cut else None)
         if filtered:
-            ops.sample_filtered(logits, self._stage_i[N:N + len(filtered)], len(filtered), self._stage_d[:4 * len(filtered)],
-                                self._stage_i[2 * N:2 * N + len(filtered)], self._ids[self._n:self._n + n])
+            ops.sample_filtered(logits, self._ints("filtered_rows", len(filtered)), len(filtered),
+                                self._doubles("filtered_params", 4 * len(filtered)), self._ints("top_k", len(filtered)),
+                                self._ids[self._n:self._n + n])
         self._ids_host[slot].copy_(self._ids, non_blocking=True)
         self.d2h_bytes += self._ids_host[slot].numel() * 4
         return drawn
