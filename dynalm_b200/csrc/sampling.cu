@@ -381,6 +381,36 @@ __device__ __forceinline__ unsigned long long block_scan_u64(unsigned long long 
   return v + red[warp];
 }
 
+// f(id, logit) for every id of the row, each thread of the block taking every SAMPLE_CAP-th group of four: sixteen
+// logits are asked for before the first is used (a loop of single loads waits a trip to L2 per logit: 20 us a pass
+// over 128,256 logits instead of 3). In no particular order: what the callers add up has none.
+template <typename F>
+__device__ __forceinline__ void sample_for_each(const float* __restrict__ row, int vocab, F f) {
+  const int t = threadIdx.x;
+  int done = 0;
+  if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    const int n4 = vocab >> 2;
+    const float4* r4 = reinterpret_cast<const float4*>(row);
+    int i = t;
+    for (; i + 3 * SAMPLE_CAP < n4; i += 4 * SAMPLE_CAP) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = r4[i + u * SAMPLE_CAP];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int b = (i + u * SAMPLE_CAP) * 4;
+        f(b, v[u].x); f(b + 1, v[u].y); f(b + 2, v[u].z); f(b + 3, v[u].w);
+      }
+    }
+    for (; i < n4; i += SAMPLE_CAP) {
+      const float4 v = r4[i];
+      f(4 * i, v.x); f(4 * i + 1, v.y); f(4 * i + 2, v.z); f(4 * i + 3, v.w);
+    }
+    done = n4 << 2;
+  }
+  for (int i = done + t; i < vocab; i += SAMPLE_CAP) f(i, row[i]);
+}
+
 // The bins that narrow a row down, level by level: level n + 1 divides the chosen bin of level n again.
 struct SampleBins {
   float lo[3], scale[3];
@@ -388,9 +418,12 @@ struct SampleBins {
   int depth;
   // +1 above the chosen bins, 0 inside them, -1 below
   __device__ __forceinline__ int side(float l) const {
-    for (int level = 0; level < depth; ++level) {
-      const int b = sample_bin(l, lo[level], scale[level]);
-      if (b != bin[level]) return b > bin[level] ? 1 : -1;
+#pragma unroll
+    for (int level = 0; level < 3; ++level) {
+      if (level < depth) {
+        const int b = sample_bin(l, lo[level], scale[level]);
+        if (b != bin[level]) return b > bin[level] ? 1 : -1;
+      }
     }
     return 0;
   }
@@ -411,15 +444,16 @@ struct SampleBins {
 __global__ void __launch_bounds__(SAMPLE_CAP)
 sample_filtered_kernel(const float* __restrict__ logits, int ld, int vocab, const int* __restrict__ rows,
                        const double* __restrict__ dparams, const int* __restrict__ top_k, int* __restrict__ out) {
-  __shared__ unsigned long long hist[SAMPLE_BINS];       // mass (or count) per bin
-  __shared__ unsigned int cnt[SAMPLE_BINS];              // ids per bin
+  // mass (or count) per bin, in two 32-bit halves: a 32-bit atomic add in shared memory is one instruction, and its
+  // old value tells whether it carried
+  __shared__ unsigned int hist_lo[SAMPLE_BINS], hist_hi[SAMPLE_BINS];
   __shared__ unsigned long long cand[SAMPLE_CAP];
   __shared__ unsigned long long red_u[33];
   __shared__ double red[33];
   __shared__ float redf[33];
   __shared__ int red_i[32];
-  __shared__ int n_cand, picked_bin, picked_in_bin, picked_count_above;
-  __shared__ unsigned long long picked_rest, found_cum;
+  __shared__ int n_cand, picked_bin;
+  __shared__ unsigned long long picked_rest, picked_above, picked_inside, found_cum;
   __shared__ int found_id;
   __shared__ double kept_s;
   const int sel = blockIdx.x, t = threadIdx.x;
@@ -439,10 +473,10 @@ sample_filtered_kernel(const float* __restrict__ logits, int ld, int vocab, cons
 
   // the largest and the smallest finite logit (NaN and -inf take no part anywhere below)
   float hi = -INFINITY, lo = INFINITY;
-  for (int i = t; i < vocab; i += SAMPLE_CAP) {
-    const float l = row[i];
+  sample_for_each(row, vocab, [&](int, float l) {
     if (l > -INFINITY) { hi = fmaxf(hi, l); lo = fminf(lo, l); }
-  }
+  });
+  const float mine_hi = hi;        // the largest logit this thread has seen: the threads' largest bound the place from below
   hi = block_max(hi, redf);
   lo = -block_max(-lo, redf);
   if (!(hi > -INFINITY) || !(hi < INFINITY)) {
@@ -451,76 +485,119 @@ sample_filtered_kernel(const float* __restrict__ logits, int ld, int vocab, cons
     return;
   }
   const double cut = static_cast<double>(hi) + cut_off;      // min-p: logits below it are out (sampler.cpp:146)
-  auto counted = [&](float l) { return l > -INFINITY; };
+  // (in float32 alone: the smallest float at or above the cut stands for it, and the product with 2^40 is exact)
+  float cut_f = static_cast<float>(cut);
+  if (static_cast<double>(cut_f) < cut) cut_f = nextafterf(cut_f, INFINITY);
   auto mass = [&](float l) -> unsigned long long {
-    return l > -INFINITY && static_cast<double>(l) >= cut
-               ? static_cast<unsigned long long>(static_cast<double>(expf((l - hi) * inv_t)) * SAMPLE_FIXED) : 0ull;
+    return l >= cut_f ? __float2ull_rz(expf((l - hi) * inv_t) * static_cast<float>(SAMPLE_FIXED)) : 0ull;
   };
+  auto sort_key = [](float l, unsigned int id) {            // ascending in this key = (logit descending, id ascending)
+    const unsigned int bits = __float_as_uint(l);
+    const unsigned int rising = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);     // grows with the logit
+    return (static_cast<unsigned long long>(~rising) << 32) | id;
+  };
+  auto key_logit = [](unsigned long long key) {
+    const unsigned int rising = ~static_cast<unsigned int>(key >> 32);
+    return __uint_as_float((rising & 0x80000000u) ? (rising & 0x7fffffffu) : ~rising);
+  };
+  auto sort_cand = [&]() {                                  // all SAMPLE_CAP places of cand, ascending
+    for (int size = 2; size <= SAMPLE_CAP; size <<= 1) {
+      for (int stride = size >> 1; stride > 0; stride >>= 1) {
+        const int other = t ^ stride;
+        if (other > t) {
+          const unsigned long long a = cand[t], b = cand[other];
+          const bool up = (t & size) == 0;
+          if ((a > b) == up) { cand[t] = b; cand[other] = a; }
+        }
+        __syncthreads();
+      }
+    }
+  };
+  // A floor under the place that is looked for, from the threads' largest logits alone (every one of them is a logit
+  // of the row, so at least j ids lie at or above the j-th largest of them, with at least their mass): ids below the
+  // floor need not be counted or weighed, which leaves the histograms a few thousand ids instead of the vocabulary.
+  // `reach`: how many ids (by_count) or how much mass the place needs from the top.
+  auto floor_from_thread_maxima = [&](unsigned long long reach, bool by_count) -> float {
+    __syncthreads();
+    cand[t] = mine_hi > -INFINITY ? sort_key(mine_hi, static_cast<unsigned int>(t)) : ~0ull;
+    __syncthreads();
+    sort_cand();
+    const bool real = cand[t] != ~0ull;
+    const float mine = real ? key_logit(cand[t]) : 0.0f;
+    const unsigned long long w = !real ? 0ull : (by_count ? 1ull : mass(mine));
+    const unsigned long long incl = block_scan_u64(w, red_u);
+    if (t == 0) found_id = -1;
+    __syncthreads();
+    if (incl - w < reach && incl >= reach) found_id = t;     // the first thread maximum at which the running total reaches it
+    __syncthreads();
+    const int at = found_id;
+    const float floor = at >= 0 ? key_logit(cand[at]) : -INFINITY;
+    __syncthreads();
+    return floor;
+  };
+  float floor = -INFINITY;
+  auto counted = [&](float l) { return l > -INFINITY && l >= floor; };
 
   SampleBins bins;
-  // Narrows the row to the bin in which the running total from the top (of ids if by_count, else of mass) reaches
-  // x >= 1. Returns what of x is left to find inside that bin; *ids_above = the ids in the bins above it.
-  // `whole`: stop as soon as the ids above and inside fit the candidates (top-k), not only those inside.
-  auto narrow = [&](unsigned long long x, bool by_count, bool whole, int* ids_above, int* ids_inside) -> unsigned long long {
-    unsigned long long rest = x;
-    int above = 0, inside = 0;
-    bins.depth = 0;
+  // One or more levels of narrowing: the row (at level 0) or the bin chosen at the level before is divided into
+  // SAMPLE_BINS equal steps, and the bin is chosen in which the running total from the top (of ids if by_count, else
+  // of mass) reaches `rest` >= 1. Returns what of `rest` is left to find inside that bin. By count, *ids_above grows
+  // by the ids in the bins above it and *ids_inside becomes the ids in it (by mass nobody counts: one atomic less
+  // per id). If even the lowest bin does not reach it, that bin is chosen.
+  auto narrow = [&](unsigned long long rest, bool by_count, int first_level, int last_level, int* ids_above,
+                    int* ids_inside) -> unsigned long long {
+#pragma unroll
     for (int level = 0; level < 3; ++level) {
+      if (level < first_level || level > last_level) continue;
+      bins.depth = level;
       bins.lo[level] = level == 0 ? lo : bins.lo[level - 1] + static_cast<float>(bins.bin[level - 1]) / bins.scale[level - 1];
       bins.scale[level] = level == 0 ? (hi > lo ? static_cast<float>(SAMPLE_BINS) / (hi - lo) : 0.0f)
                                      : bins.scale[level - 1] * static_cast<float>(SAMPLE_BINS);
       if (level > 0 && !(bins.scale[level - 1] > 0.0f)) { bins.lo[level] = lo; bins.scale[level] = 0.0f; }
-      for (int b = t; b < SAMPLE_BINS; b += SAMPLE_CAP) { hist[b] = 0; cnt[b] = 0; }
+      for (int b = t; b < SAMPLE_BINS; b += SAMPLE_CAP) { hist_lo[b] = 0; hist_hi[b] = 0; }
       __syncthreads();
-      for (int i = t; i < vocab; i += SAMPLE_CAP) {
-        const float l = row[i];
-        if (!counted(l) || bins.side(l) != 0) continue;
-        const int b = sample_bin(l, bins.lo[level], bins.scale[level]);
+      sample_for_each(row, vocab, [&](int, float l) {
+        if (!counted(l) || bins.side(l) != 0) return;
         const unsigned long long w = by_count ? 1ull : mass(l);
-        if (w != 0) atomicAdd(&hist[b], w);
-        atomicAdd(&cnt[b], 1u);
-      }
+        if (w == 0) return;
+        const int b = sample_bin(l, bins.lo[level], bins.scale[level]);
+        const unsigned int low = static_cast<unsigned int>(w), high = static_cast<unsigned int>(w >> 32);
+        const unsigned int old = atomicAdd(&hist_lo[b], low);
+        const unsigned int carry = old + low < old ? 1u : 0u;
+        if (high + carry != 0) atomicAdd(&hist_hi[b], high + carry);
+      });
       __syncthreads();
+      auto hist = [&](int b) { return (static_cast<unsigned long long>(hist_hi[b]) << 32) | hist_lo[b]; };
       // thread t owns bins SAMPLE_BINS-1-2t and SAMPLE_BINS-2-2t: a running sum over threads runs from the top bin down
       const int b_hi = SAMPLE_BINS - 1 - 2 * t, b_lo = b_hi - 1;
-      const unsigned long long h_hi = hist[b_hi], h_lo = hist[b_lo];
-      const unsigned int c_hi = cnt[b_hi], c_lo = cnt[b_lo];
+      const unsigned long long h_hi = hist(b_hi), h_lo = hist(b_lo);
       const unsigned long long incl = block_scan_u64(h_hi + h_lo, red_u);
-      const unsigned long long c_incl = block_scan_u64(c_hi + c_lo, red_u);
+      const unsigned long long all = red_u[32];
       const unsigned long long before = incl - (h_hi + h_lo);
-      const int c_before = static_cast<int>(c_incl - (c_hi + c_lo));
-      if (t == 0) {      // out of reach (x beyond the whole): the lowest bin, everything above it
+      if (t == 0) {      // out of reach (more than the whole): the lowest bin, everything else above it
         picked_bin = 0;
         picked_rest = rest;
-        picked_count_above = -1;
+        picked_above = all - hist(0);
+        picked_inside = hist(0);
       }
       __syncthreads();
       if (before < rest && incl >= rest) {          // exactly one thread (none if out of reach)
         if (before + h_hi >= rest) {
-          picked_bin = b_hi; picked_rest = rest - before; picked_count_above = c_before; picked_in_bin = static_cast<int>(c_hi);
+          picked_bin = b_hi; picked_rest = rest - before; picked_above = before; picked_inside = h_hi;
         } else {
-          picked_bin = b_lo; picked_rest = rest - before - h_hi; picked_count_above = c_before + static_cast<int>(c_hi);
-          picked_in_bin = static_cast<int>(c_lo);
+          picked_bin = b_lo; picked_rest = rest - before - h_hi; picked_above = before + h_hi; picked_inside = h_lo;
         }
       }
       __syncthreads();
-      if (picked_count_above < 0) {                // every id of this level lies at or above bin 0
-        unsigned int all = 0;
-        for (int b = 1; b < SAMPLE_BINS; ++b) all += cnt[b];
-        above += static_cast<int>(all);
-        inside = static_cast<int>(cnt[0]);
-      } else {
-        above += picked_count_above;
-        inside = picked_in_bin;
-      }
       bins.bin[level] = picked_bin;
-      rest = picked_rest;
       bins.depth = level + 1;
+      rest = picked_rest;
+      if (by_count) {
+        *ids_above += static_cast<int>(picked_above);
+        *ids_inside = static_cast<int>(picked_inside);
+      }
       __syncthreads();
-      if ((whole ? above + inside : inside) <= SAMPLE_CAP) break;
     }
-    *ids_above = above;
-    *ids_inside = inside;
     return rest;
   };
   // Thread t's own stretch of ids, for what has to go by the order of the ids.
@@ -530,10 +607,9 @@ sample_filtered_kernel(const float* __restrict__ logits, int ld, int vocab, cons
   // step between two floats, unless the row's range is absurd); *value = that logit.
   auto one_value = [&](float* value) -> bool {
     float most = -INFINITY, least = INFINITY;
-    for (int i = t; i < vocab; i += SAMPLE_CAP) {
-      const float l = row[i];
+    sample_for_each(row, vocab, [&](int, float l) {
       if (counted(l) && bins.side(l) == 0) { most = fmaxf(most, l); least = fminf(least, l); }
-    }
+    });
     most = block_max(most, redf);
     least = -block_max(-least, redf);
     *value = most;
@@ -556,26 +632,21 @@ sample_filtered_kernel(const float* __restrict__ logits, int ld, int vocab, cons
     return found_id;
   };
   // The ids inside the chosen bins (and above them, if `with_above`) into cand, sorted by (logit descending, id
-  // ascending); the number of them, or -1 if they do not fit. inside_limit >= 0: of those inside only the first
+  // ascending); the number of them, or -1 if they are more than cand holds. inside_limit >= 0: of those inside only the first
   // inside_limit in the order of the ids (they have one logit, so these come first in the order of the candidates).
   auto gather_sorted = [&](bool with_above, long long inside_limit) -> int {
     if (t == 0) n_cand = 0;
     __syncthreads();
     auto put = [&](int i, float l) {
       const int at = atomicAdd(&n_cand, 1);
-      if (at < SAMPLE_CAP) {
-        const unsigned int bits = __float_as_uint(l);
-        const unsigned int rising = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);     // grows with the logit
-        cand[at] = (static_cast<unsigned long long>(~rising) << 32) | static_cast<unsigned int>(i);
-      }
+      if (at < SAMPLE_CAP) cand[at] = sort_key(l, static_cast<unsigned int>(i));
     };
-    for (int i = t; i < vocab; i += SAMPLE_CAP) {
-      const float l = row[i];
-      if (!counted(l)) continue;
+    sample_for_each(row, vocab, [&](int i, float l) {
+      if (!counted(l)) return;
       const int side = bins.side(l);
-      if (side < 0 || (side > 0 && !with_above) || (side == 0 && inside_limit >= 0)) continue;
+      if (side < 0 || (side > 0 && !with_above) || (side == 0 && inside_limit >= 0)) return;
       put(i, l);
-    }
+    });
     if (inside_limit >= 0) {
       unsigned long long mine = 0;
       for (int i = own_b; i < own_e; ++i) mine += counted(row[i]) && bins.side(row[i]) == 0;
@@ -588,35 +659,30 @@ sample_filtered_kernel(const float* __restrict__ logits, int ld, int vocab, cons
     __syncthreads();
     const int n = n_cand;
     __syncthreads();
-    if (n > SAMPLE_CAP || n == 0) return -1;
+    if (n > SAMPLE_CAP) return -1;
+    if (n == 0) return 0;
     if (t >= n) cand[t] = ~0ull;
     __syncthreads();
-    for (int size = 2; size <= SAMPLE_CAP; size <<= 1) {
-      for (int stride = size >> 1; stride > 0; stride >>= 1) {
-        const int other = t ^ stride;
-        if (other > t) {
-          const unsigned long long a = cand[t], b = cand[other];
-          const bool up = (t & size) == 0;
-          if ((a > b) == up) { cand[t] = b; cand[other] = a; }
-        }
-        __syncthreads();
-      }
-    }
+    sort_cand();
     return n;
   };
 
   if (!use_k) {
     // ---- top-p alone ----
     unsigned long long mine = 0;
-    for (int i = t; i < vocab; i += SAMPLE_CAP) mine += mass(row[i]);
+    sample_for_each(row, vocab, [&](int, float l) { mine += mass(l); });
     block_scan_u64(mine, red_u);
     const unsigned long long total = red_u[32];
     __syncthreads();
     // The first place (in the order) where the running mass reaches x: its id, and the running mass there.
     auto locate = [&](unsigned long long x) -> bool {
-      int ids_above, ids_inside;
-      const unsigned long long rest = narrow(x, false, false, &ids_above, &ids_inside);
-      if (ids_inside > SAMPLE_CAP) {
+      unsigned long long rest = narrow(x, false, 0, 1, nullptr, nullptr);
+      int n = gather_sorted(false, -1);
+      if (n < 0) {                                       // the bin of two levels holds too many: a third
+        rest = narrow(rest, false, 2, 2, nullptr, nullptr);
+        n = gather_sorted(false, -1);
+      }
+      if (n < 0) {
         // more ids at the place than can be sorted: they have one logit, so one mass, and their order is that of
         // the ids
         float value;
@@ -630,8 +696,7 @@ sample_filtered_kernel(const float* __restrict__ logits, int ld, int vocab, cons
         __syncthreads();
         return true;
       }
-      const int n = gather_sorted(false, -1);
-      if (n < 0) return false;
+      if (n == 0) return false;
       const int id = static_cast<int>(cand[t] & 0xffffffffull);
       const unsigned long long w = t < n ? mass(row[id]) : 0ull;
       const unsigned long long cum = block_scan_u64(w, red_u);
@@ -647,6 +712,8 @@ sample_filtered_kernel(const float* __restrict__ logits, int ld, int vocab, cons
     }
     unsigned long long share = static_cast<unsigned long long>(top_p * static_cast<double>(total));
     share = share < 1 ? 1 : (share > total ? total : share);
+    floor = floor_from_thread_maxima(share, false);          // the draw's place lies at or above the nucleus' end
+    if (floor > lo) lo = floor;
     if (!locate(share)) {
       if (t == 0) out[out_at] = -1;
       return;
@@ -664,8 +731,14 @@ sample_filtered_kernel(const float* __restrict__ logits, int ld, int vocab, cons
   }
 
   // ---- top-k, with or without top-p ----
-  int ids_above, ids_inside;
-  const unsigned long long inside_wanted = narrow(static_cast<unsigned long long>(k), true, true, &ids_above, &ids_inside);
+  floor = floor_from_thread_maxima(static_cast<unsigned long long>(k), true);
+  if (floor > lo) lo = floor;
+  int ids_above = 0, ids_inside = 0;
+  unsigned long long inside_wanted = static_cast<unsigned long long>(k);
+  for (int level = 0; level < 3; ++level) {              // until the ids above and inside fit the candidates
+    inside_wanted = narrow(inside_wanted, true, level, level, &ids_above, &ids_inside);
+    if (ids_above + ids_inside <= SAMPLE_CAP) break;
+  }
   long long inside_limit = -1;
   if (ids_above + ids_inside > SAMPLE_CAP && k <= SAMPLE_CAP) {
     // more ids with the k-th logit than can be kept: of those (one logit) the first in the order of the ids
@@ -673,7 +746,7 @@ sample_filtered_kernel(const float* __restrict__ logits, int ld, int vocab, cons
     if (one_value(&value)) inside_limit = static_cast<long long>(inside_wanted);
   }
   const int n = gather_sorted(true, inside_limit);
-  if (n < 0) {
+  if (n <= 0) {
     if (t == 0) out[out_at] = -1;
     return;
   }
