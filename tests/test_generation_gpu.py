@@ -143,6 +143,31 @@ def test_filters_and_penalties_follow_the_reference_pipeline(tiny_folders):
     assert [o.tokens for o in again] == [o.tokens for o in outs]
 
 
+def test_a_top_k_beyond_the_kernel_is_finished_on_the_host(tmp_path):
+    """Top-k above the 1,024 candidates the filtered kernel keeps: the kernel hands the row back and the host runs the
+    pipeline on its logits with the uniform number the kernel was given; beside it in the batch, a request the
+    kernel does answer. Both follow the host pipeline over the plain implementation's logits."""
+    import torch
+    from dynalm_b200 import SamplingParams
+    from dynalm_b200.sampling.sampler import Sampler
+    from dynalm_b200.weights import write_model_folder
+    cfg = dict(TINY["a"][0], vocab_size=3001)
+    write_model_folder(str(tmp_path), cfg, 11, dtype=torch.float32)
+    prompt = random_requests(cfg["vocab_size"], [19], seed=6)["r0"]
+    eng = _engine(str(tmp_path), "float32")
+    plain = PlainLlama(str(tmp_path))
+    params = [SamplingParams(temperature=1.0, top_k=2000, top_p=0.95, seed=3), SamplingParams(temperature=1.0, top_k=50, seed=4)]
+    assert not Sampler(params[0]).on_device and Sampler(params[1]).on_device
+    outs = eng.generate([prompt, prompt], max_tokens=10, sampling=params)
+    assert eng.executor.host_sampled == 10
+    for p, out in zip(params, outs):
+        a = out.tokens
+        logits = plain.logits((prompt + a)[:-1]).astype(np.float32)
+        host = Sampler(p)
+        same = sum(host.sample_host(logits[len(prompt) - 1 + i].copy(), prompt + a[:i]) == tok for i, tok in enumerate(a))
+        assert len(a) == 10 and same >= 9, (p, same)
+
+
 def test_command_line(tiny_folders_bf16):
     proc = subprocess.run([os.path.join(ROOT, "bin", "dynalm"), "run", tiny_folders_bf16["a"], "--tokens", "5,17,3,99",
                            "-n", "8", "--ctx", "256", "--batch", "64", "--no-stream"], capture_output=True, text=True,
