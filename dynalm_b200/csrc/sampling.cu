@@ -1,4 +1,5 @@
-// Token selection on the device: greedy argmax and temperature sampling over fp32 logits rows.
+// Token selection on the device over fp32 logits rows: greedy argmax, temperature and min-p sampling by a walk down
+// the ids, the penalties, and top-k / top-p sampling (further down, with their own account).
 //
 // Greedy: the index of the largest logit, ties to the lowest id (sample_greedy,
 // dynalm/src/sampling/sampler.cpp:31-38). Temperature: p_i = exp((l_i - max) / T), the total summed in
