@@ -38,6 +38,14 @@ struct T5Alone {
 
 }  // namespace dl
 
+// The output tile (row block, column block) that tile number `tile` stands for when num_tiles tiles in tiles_n
+// columns are numbered in groups of group_m row blocks: the kernel's own numbering, for tests on the host.
+DL_EXPORT int dl_gemm_tcgen05_tile_coords(int tile, int tiles_n, int num_tiles, int group_m, int* m_tile, int* n_tile) {
+  if (tiles_n <= 0 || num_tiles <= 0 || num_tiles % tiles_n || group_m <= 0 || tile < 0 || tile >= num_tiles) return DL_ERR_UNSUPPORTED;
+  dl::t5_tile_coords(tile, tiles_n, num_tiles, group_m, m_tile, n_tile);
+  return 0;
+}
+
 DL_EXPORT int dl_gemm_tcgen05(const void* x, int ldx, const void* w, void* y, int ldy, int M, int N, int K, int mode,
                               float out_scale, int* status, cudaStream_t stream) {
   if (mode < 0 || mode > 2) return DL_ERR_UNSUPPORTED;

@@ -26,6 +26,24 @@ template <int BN> struct T5 {
 enum { T5_OUT_BF16 = 0, T5_OUT_F32 = 1, T5_OUT_SWIGLU = 2, T5_OUT_QKV_ROPE = 3 };
 enum { T5_ERR_PRODUCER = 1, T5_ERR_MMA = 2, T5_ERR_EPILOGUE = 3 };
 
+// Which output tile a tile number stands for. Tiles are numbered in groups of `group_m` row blocks: inside a
+// group the row block changes fastest, then the column block; the groups follow one another. The blocks of the grid
+// work on consecutive numbers at any time, so together they hold group_m row blocks of x and gridDim.x / group_m
+// column blocks of W: both stay in L2 while they are used, and over the whole product W comes from memory once
+// per group and x once. (Numbered along the columns first, as this kernel did at first, every row block brings all
+// of W in again: with the 235 MB of a 4096 -> 2 x 14336 gate|up matrix that bound the product to memory, 1,684 us
+// for 8,192 rows where the arithmetic needs 1,300.)
+__host__ __device__ __forceinline__ void t5_tile_coords(int tile, int tiles_n, int num_tiles, int group_m, int* m_tile, int* n_tile) {
+  const int tiles_m = num_tiles / tiles_n;
+  const int per_group = group_m * tiles_n;
+  const int g = tile / per_group;
+  const int first_m = g * group_m;
+  const int rows = group_m < tiles_m - first_m ? group_m : tiles_m - first_m;
+  const int r = tile - g * per_group;
+  *m_tile = first_m + r % rows;
+  *n_tile = r / rows;
+}
+
 // gate_rows: for SwiGLU the number of gate features F (W has 2F rows); the tile's W rows are
 // [n0, n0 + 128) and [F + n0, F + n0 + 128). Otherwise unused.
 //
@@ -40,24 +58,6 @@ enum { T5_ERR_PRODUCER = 1, T5_ERR_MMA = 2, T5_ERR_EPILOGUE = 3 };
 // from L2 once per pair (measured: the kernel is bound by operand traffic from L2; loading a third less made it
 // a fifth faster). A stage is then free only when both blocks' MMAs have read it: each block's commit arrives on
 // the stage's barrier in both blocks, and the barrier counts two arrivals.
-// Which output tile a tile number stands for. Tiles are numbered in groups of `group_m` row blocks: inside a
-// group the row block changes fastest, then the column block; the groups follow one another. The blocks of the grid
-// work on consecutive numbers at any time, so together they hold group_m row blocks of x and gridDim.x / group_m
-// column blocks of W: both stay in L2 while they are used, and over the whole product W comes from memory once
-// per group and x once. (Numbered along the columns first, as this kernel did at first, every row block brings all
-// of W in again: with the 235 MB of a 4096 -> 2 x 14336 gate|up matrix that bound the product to memory, 1,684 us
-// for 8,192 rows where the arithmetic needs 1,300.)
-__device__ __forceinline__ void t5_tile_coords(int tile, int tiles_n, int num_tiles, int group_m, int* m_tile, int* n_tile) {
-  const int tiles_m = num_tiles / tiles_n;
-  const int per_group = group_m * tiles_n;
-  const int g = tile / per_group;
-  const int first_m = g * group_m;
-  const int rows = min(group_m, tiles_m - first_m);
-  const int r = tile - g * per_group;
-  *m_tile = first_m + r % rows;
-  *n_tile = r / rows;
-}
-
 template <int T5_BN, class P>
 __global__ void __launch_bounds__(T5_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,

@@ -48,6 +48,7 @@ _SIGNATURES = {
         "dl_gemm_skinny_qkv_rope": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P, _F, _I, _I, _I, _I, _P]},
     "gemm_tcgen05": {
         "dl_gemm_tcgen05": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
+        "dl_gemm_tcgen05_tile_coords": [_I, _I, _I, _I, _P, _P],
         "dl_gemm_tcgen05_qkv_rope": [_P, _I, _P, _P, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P, _F, _I, _I, _I, _I, _P, _P]},
     "gemm_tcgen05_cluster": {
         "dl_gemm_tcgen05_cluster": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
@@ -844,6 +845,17 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str 
                      else ("gemm_tcgen05", "dl_gemm_tcgen05"))
     _check(_fn(library, name)(_p(x), x.stride(0), _p(w), _p(out), out.stride(0), M, N, K, code, out_scale, _p(status),
                               _stream()), "gemm_tcgen05")
+
+
+def gemm_tcgen05_tile_coords(tile: int, tiles_n: int, num_tiles: int, group_m: int):
+    """(row block, column block) of tile number `tile` in the tcgen05 product's numbering of num_tiles output tiles in
+    tiles_n columns, groups of group_m row blocks (csrc/gemm_tcgen05_impl.cuh, t5_tile_coords). Runs on the host: it
+    is there so that the numbering can be tested without a GPU."""
+    from ctypes import byref, c_int
+    m, n = c_int(-1), c_int(-1)
+    _check(_fn("gemm_tcgen05", "dl_gemm_tcgen05_tile_coords")(tile, tiles_n, num_tiles, group_m, byref(m), byref(n)),
+           "gemm_tcgen05_tile_coords")
+    return m.value, n.value
 
 
 STREAM_MAX_ROWS = 64       # what the tcgen05 weight-streaming product takes

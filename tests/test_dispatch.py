@@ -62,6 +62,34 @@ def test_the_rotating_epilogue_needs_rounds_of_tiles_at_head_size_128():
     assert not gemm.rotating_epilogue_pays(4096, 5120, 96)
 
 
+def test_the_tcgen05_product_numbers_every_output_tile_once():
+    """The kernel's own numbering of its output tiles (groups of row blocks, the row block changing fastest inside a
+    group), called on the host: every tile of the grid has exactly one number, whatever the sizes, and consecutive
+    numbers inside a group share their column block."""
+    import pytest
+    from dynalm_b200.kernels import ops
+    if ops.CHECKED:
+        pytest.skip("the checked build reads its record from the device after every call")
+    import random
+    rnd = random.Random(5)
+    shapes = [(1, 1, 1), (5, 20, 16), (16, 112, 16), (64, 16, 9), (7, 3, 4), (33, 5, 16), (3, 7, 8)]
+    shapes += [(rnd.randint(1, 70), rnd.randint(1, 40), rnd.randint(1, 20)) for _ in range(12)]
+    for tiles_m, tiles_n, group_m in shapes:
+        total = tiles_m * tiles_n
+        seen = {}
+        for tile in range(total):
+            m, n = ops.gemm_tcgen05_tile_coords(tile, tiles_n, total, group_m)
+            assert 0 <= m < tiles_m and 0 <= n < tiles_n, (tiles_m, tiles_n, group_m, tile, m, n)
+            assert (m, n) not in seen, f"tiles {seen[(m, n)]} and {tile} are both ({m}, {n})"
+            seen[(m, n)] = tile
+        assert len(seen) == total
+        rows = min(group_m, tiles_m)                          # the first group: numbers 0 .. rows - 1 are one column block
+        first = [ops.gemm_tcgen05_tile_coords(t, tiles_n, total, group_m) for t in range(rows)]
+        assert [m for m, _ in first] == list(range(rows)) and {n for _, n in first} == {0}
+    with pytest.raises(Exception):
+        ops.gemm_tcgen05_tile_coords(20, 4, 20, 2)           # past the last tile
+
+
 def test_decode_attention_splits():
     # the 1B shape at 2,048 keys: powers of two (the splits of a row are one thread-block cluster), about one block per SM
     assert [attention.decode_splits(rows, 32, 8, 2048, sms=148) for rows in (1, 2, 4, 6, 8, 10)] == [8, 4, 4, 2, 2, 2]
