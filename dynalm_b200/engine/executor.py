@@ -227,13 +227,10 @@ class GpuExecutor:
         launched.event.synchronize()
         ids = self._ids_host[launched.slot].numpy()
         self._check_status(ids)
-        out = {req: int(ids[place]) for req, place in launched.places.items()}
-        undecided = [req for req, token in out.items() if token < 0]
-        if undecided:
-            # the filtered kernel gives up on a row without a finite largest logit, or whose range is so wide that
-            # bins of it still hold different logits; the row's logits are gone by now (the next step is in flight)
-            raise EngineError(f"request(s) {undecided}: the logits could not be sampled from (not finite, or of absurd range)")
-        return out
+        # (a negative id: the filtered kernel gave up on the row, whose largest logit is not finite or whose range is
+        # so wide that bins of it still hold different logits; its logits are gone by now, the next step being in
+        # flight, and the scheduler fails that request alone)
+        return {req: int(ids[place]) for req, place in launched.places.items()}
 
     def _check_status(self, ids) -> None:
         """`ids`: the host copy of a step's chosen ids, whose last element is the status word as that step left it.

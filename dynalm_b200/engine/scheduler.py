@@ -649,6 +649,11 @@ class Scheduler:
             if not b.sample:
                 continue
             tok = sampled[seq.id]
+            if tok < 0:
+                # the executor could not choose a token for this request (its logits are not finite, say); the others
+                # of the batch have theirs
+                self._fail(seq, "no token could be sampled from the logits (not finite, or of absurd range)", events)
+                continue
             if seq.trace is not None and seq.trace.first_token_s == 0.0:
                 seq.trace.first_token_s = self.clock()
             seq.append_token(tok)

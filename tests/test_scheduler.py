@@ -47,6 +47,23 @@ class FakeExecutor:
         return out
 
 
+class UndecidedExecutor(FakeExecutor):
+    """Gives no token (-1) to one request at its third sampled token, as the filtered sampling kernel does for a row
+    it cannot sample from."""
+
+    def __init__(self, victim, **kw):
+        super().__init__(**kw)
+        self.victim, self.seen = victim, 0
+
+    def run(self, batch):
+        out = super().run(batch)
+        if self.victim in out:
+            self.seen += 1
+            if self.seen == 3:
+                out[self.victim] = -1
+        return out
+
+
 def run_all(s, limit=10000):
     events = []
     n = 0
@@ -579,3 +596,15 @@ def test_submit_and_cancel_from_other_threads():
             assert final[rid].status == FINISHED and toks[rid] == alone[i]
     assert not ex.live and ex.cache.free_pages == ex.cache.num_pages
     ex.cache.check()
+
+
+def test_a_request_without_a_token_fails_alone():
+    ex = UndecidedExecutor(victim=None)
+    s = Scheduler(ex, SchedulerConfig(max_running=4))
+    ids = [s.submit(Request(p, 6)) for p in prompts(3, [5, 9, 4])]
+    ex.victim = ids[1]
+    toks, final = collect(run_all(s))
+    assert final[ids[1]].status == "error" and "no token could be sampled" in final[ids[1]].error
+    assert len(toks[ids[1]]) == 2
+    assert all(final[i].status == "finished" and len(toks[i]) == 6 for i in (ids[0], ids[2]))
+    assert ex.cache.free_pages == ex.cache.num_pages and not ex.live
