@@ -316,6 +316,43 @@ def test_a_failed_step_with_a_batch_in_flight_fails_both_and_frees_everything():
     assert final[again].status == FINISHED and len(toks[again]) == 5
 
 
+def test_a_request_without_a_token_fails_alone_with_a_batch_in_flight():
+    """One step ahead: the batch after the one in which a request got no token (-1) is on its way already, with a
+    row of that request in it; the request fails, that row's result is dropped, and the others get the tokens they
+    get without it."""
+    class Undecided(FakeAsyncExecutor):
+        victim, seen = None, 0
+
+        def collect(self, handle):
+            handle = [(seq, start) for seq, start in handle if not seq.terminal]
+            out = super().collect(handle)
+            if self.victim in out:
+                self.seen += 1
+                if self.seen == 4:
+                    out[self.victim] = -1
+            return out
+
+    ps = prompts(3, [12, 20, 7])
+
+    def run(ex, which=None):
+        s = Scheduler(ex, SchedulerConfig(max_running=8, decode_token_budget=8, prefill_token_budget=64,
+                                          max_prefill_chunk=32, max_batch_tokens=128))
+        ids = [s.submit(Request(p, max_new_tokens=12)) for p in ps]
+        if which is not None:
+            ex.victim = ids[which]
+        toks, final = collect(run_all(s))
+        assert not ex.live and ex.cache.free_pages == ex.cache.num_pages
+        return [toks[i] for i in ids], [final[i] for i in ids]
+
+    want, _ = run(FakeAsyncExecutor())
+    ex = Undecided()
+    got, final = run(ex, which=1)
+    assert ex.ahead > 5
+    assert final[1].status == "error" and "no token could be sampled" in final[1].error
+    assert got[1] == want[1][:len(got[1])] and len(got[1]) < 12
+    assert got[0] == want[0] and got[2] == want[2] and final[0].status == final[2].status == FINISHED
+
+
 def test_one_step_ahead_with_arrivals_cancels_and_few_pages():
     """Requests arriving, being cancelled and being preempted while batches are in flight: the scheduler falls
     back to the ordinary iteration whenever the steady state does not hold, and the tokens stay the same."""
